@@ -1,0 +1,94 @@
+"""ctypes binding of libhelium_b200.so (the C ABI declared in include/helium_b200.h).
+
+The shared library is the product.  If it has not been built, importing this module raises: there
+is no Python or CPU fallback for any kernel.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+HE_MAX_RANK = 8
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "lib", "libhelium_b200.so")
+
+
+class HeNode(C.Structure):
+    """struct he_node of include/helium_b200.h."""
+
+    _fields_ = [
+        ("kind", C.c_int32),
+        ("sub_op", C.c_int32),
+        ("inp", C.c_int32 * 3),
+        ("dtype", C.c_int32),
+        ("rank", C.c_int32),
+        ("shape", C.c_int64 * HE_MAX_RANK),
+        ("const_bits", C.c_uint32),
+        ("axis_a", C.c_int32),
+        ("axis_b", C.c_int32),
+        ("axes", C.c_uint32),
+    ]
+
+
+class HeGraphDesc(C.Structure):
+    """struct he_graph_desc of include/helium_b200.h."""
+
+    _fields_ = [
+        ("num_nodes", C.c_int32),
+        ("nodes", C.POINTER(HeNode)),
+        ("num_outputs", C.c_int32),
+        ("outputs", C.POINTER(C.c_int32)),
+    ]
+
+
+#: every symbol include/helium_b200.h declares: name -> (restype, argtypes)
+SIGNATURES = {
+    "he_ctx_create": (C.c_int32, [C.c_int32, C.POINTER(C.c_void_p)]),
+    "he_ctx_destroy": (None, [C.c_void_p]),
+    "he_ctx_poll_device_status": (C.c_int32, [C.c_void_p, C.c_void_p]),
+    "he_plan_pointwise": (C.c_int32, [C.c_void_p, C.POINTER(HeGraphDesc), C.POINTER(C.c_void_p)]),
+    "he_plan_permute": (C.c_int32, [C.c_void_p, C.c_int32, C.POINTER(C.c_int64), C.POINTER(C.c_int64), C.c_int32,
+                                    C.POINTER(C.c_void_p)]),
+    "he_permute_output_strides": (C.c_int32, [C.c_int32, C.POINTER(C.c_int64), C.c_int32, C.POINTER(C.c_int32),
+                                              C.c_int32, C.POINTER(C.c_int64)]),
+    "he_plan_fused_matmul": (C.c_int32, [C.c_void_p, C.POINTER(HeGraphDesc), C.POINTER(C.c_void_p)]),
+    "he_plan_supported": (C.c_int32, [C.c_void_p, C.POINTER(HeGraphDesc), C.c_int32]),
+    "he_plan_workspace_bytes": (C.c_int32, [C.c_void_p, C.POINTER(C.c_size_t)]),
+    "he_launch": (C.c_int32, [C.c_void_p, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.c_void_p, C.c_void_p]),
+    "he_plan_last_launch_count": (C.c_int32, [C.c_void_p]),
+    "he_plan_describe": (C.c_char_p, [C.c_void_p]),
+    "he_plan_destroy": (None, [C.c_void_p]),
+    "he_debug_dump_program": (C.c_int32, [C.POINTER(HeGraphDesc), C.c_int32, C.c_void_p, C.c_size_t, C.POINTER(C.c_size_t)]),
+    "he_debug_canonical_text": (C.c_int32, [C.POINTER(HeGraphDesc), C.c_char_p, C.c_size_t]),
+    "he_last_error_string": (C.c_char_p, []),
+    "he_version": (C.c_char_p, []),
+}
+
+
+class HeliumError(RuntimeError):
+    def __init__(self, status: int, message: str):
+        super().__init__(f"helium_b200 status {status}: {message}")
+        self.status = status
+        self.message = message
+
+
+def _load() -> C.CDLL:
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(
+            f"{LIB_PATH} is missing. Build it with `python helium_b200/build.py` "
+            "(nvcc, sm_100a). helium_b200 has no fallback path without its CUDA library.")
+    lib = C.CDLL(LIB_PATH)
+    for name, (restype, argtypes) in SIGNATURES.items():
+        fn = getattr(lib, name)  # AttributeError here = header and library disagree
+        fn.restype = restype
+        fn.argtypes = argtypes
+    return lib
+
+
+lib = _load()
+
+
+def check(status: int) -> None:
+    if status != 0:
+        raise HeliumError(status, lib.he_last_error_string().decode("utf-8", "replace"))

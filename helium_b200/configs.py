@@ -1,0 +1,179 @@
+"""The benchmark configurations of this path as op graphs plus seeded synthetic inputs.
+
+Graphs are built the way helium's front end would record them (helium/src/raw_tensor.rs) or, for
+the fused matmul, the way the playground prints them (README.md:33-79).  Inputs are numpy storage
+arrays (uint16 bit patterns for bf16) drawn from a counter-based generator (Philox) with the seed
+each configuration names, so that every consumer -- kernels, oracle, CPU baseline -- reads identical
+bytes.  No dataset is involved.
+"""
+from __future__ import annotations
+
+import numpy as np
+
+from . import ir
+
+
+def rng(seed: int) -> np.random.Generator:
+    return np.random.Generator(np.random.Philox(seed))
+
+
+def f32_to_bf16_bits(x: np.ndarray) -> np.ndarray:
+    """Round-to-nearest-even f32 -> bf16 bit patterns (host-side input preparation only)."""
+    b = np.ascontiguousarray(x, dtype=np.float32).view(np.uint32).astype(np.uint64)
+    return ((b + 0x7FFF + ((b >> 16) & 1)) >> 16).astype(np.uint16)
+
+
+def bf16_normal(g: np.random.Generator, shape, std: float = 1.0) -> np.ndarray:
+    return f32_to_bf16_bits(g.standard_normal(shape, dtype=np.float32) * np.float32(std))
+
+
+def bf16_bernoulli(g: np.random.Generator, shape, p: float = 0.5) -> np.ndarray:
+    return f32_to_bf16_bits((g.random(shape, dtype=np.float32) < p).astype(np.float32))
+
+
+def graph_affine_relu_permute(n, c, h, w, x_dtype=ir.BF16, p_dtype=ir.F32) -> ir.Graph:
+    """BASELINE config 2a: relu(x * s_c + b_c) on NCHW, written NHWC (swap_dims(1,2).swap_dims(2,3))."""
+    g = ir.Graph()
+    x = g.new_input([n, c, h, w], x_dtype)
+    s = g.new_input([c], p_dtype)
+    b = g.new_input([c], p_dtype)
+    sb = g.broadcast_to(g.reshape(s, [c, 1, 1]), [n, c, h, w])
+    bb = g.broadcast_to(g.reshape(b, [c, 1, 1]), [n, c, h, w])
+    y = g.unary(ir.UN_RELU, g.binary(ir.BIN_ADD, g.binary(ir.BIN_MUL, x, sb), bb))
+    y = g.swap_dims(g.swap_dims(y, 1, 2), 2, 3)
+    g.new_output(y)
+    return g
+
+
+def graph_c3(m: int, n: int, k: int, with_e: bool = False, dtype=ir.BF16):
+    """The fused graph of the reference README (README.md:33-79), node numbers in comments.
+
+    Inputs in order: A [1,m,k], Mk [1,m,k] (mainloop mask), B [1,k,n], b1 [1,1,n], b2 [1,1,n],
+    M [1,m,n] (epilogue mask; the same tensor as Mk when k == n), Y [1,m,n] (, E1, E2).
+    Outputs: LOSS [1,1,1], DB2 [1,1,n], DB1 [1,1,n], gt [1,m,n], gz1 [1,m,n].
+    """
+    inv = 1.0 / n
+    g = ir.Graph()
+    a = g.new_input([1, m, k], dtype)            # 22
+    mk_ml = g.new_input([1, m, k], dtype)        # 9 (mainloop use)
+    bmat = g.new_input([1, k, n], dtype)
+    b1 = g.new_input([1, 1, n], dtype)           # 6
+    b2 = g.new_input([1, 1, n], dtype)           # 8
+    mk = g.new_input([1, m, n], dtype)           # 9 (epilogue use)
+    y = g.new_input([1, m, n], dtype)            # 11
+    a2 = g.binary(ir.BIN_MUL, g.unary(ir.UN_RELU, a), mk_ml)   # 23, 25
+    acc = g.matmul(a2, bmat, ir.PREC_BF16_F32)
+    n14 = n27 = acc
+    if with_e:
+        e1 = g.new_input([1, m, n], dtype)       # 13
+        e2 = g.new_input([1, m, n], dtype)       # 26
+        n14 = g.binary(ir.BIN_ADD, acc, e1)      # 14
+        n27 = g.binary(ir.BIN_ADD, acc, e2)      # 27
+    n16 = g.binary(ir.BIN_ADD, n14, g.broadcast(b1, 3, [(1, m)]))     # 15, 16
+    n17 = g.unary(ir.UN_RELU, n16)                                     # 17
+    n29 = g.binary(ir.BIN_ADD, n27, g.broadcast(b2, 3, [(1, m)]))     # 28, 29
+    n30 = g.unary(ir.UN_TANH, n29)                                     # 30
+    n32 = g.unary(ir.UN_ADD_CONST, g.unary(ir.UN_NEG, n17), 1.0)       # 31, 32
+    n33 = g.binary(ir.BIN_MUL, n32, mk)                                # 33
+    n34 = g.binary(ir.BIN_MUL, n17, n30)                               # 34
+    n35 = g.binary(ir.BIN_ADD, n33, n34)                               # 35
+    n36 = g.binary(ir.BIN_SUB, n35, y)                                 # 36
+    n37 = g.unary(ir.UN_POW_CONST, n36, 2.0)                           # 37
+    n38 = g.unary(ir.UN_MUL_CONST, n37, inv)                           # 38
+    n39 = g.reduce_axes(ir.RED_SUM, n38, [0, 1, 2])                    # 39 Batch
+    n41 = g.constant(1.0, [1, 1, 1])                                   # 41
+    n44 = g.broadcast(g.broadcast(g.broadcast(n41, 3, [(1, m)]), 3, [(2, n)]), 3, [(0, 1)])  # 42-44
+    n45 = g.unary(ir.UN_MUL_CONST, n44, inv)                           # 45
+    n46 = g.constant(2.0, [1, m, n])                                   # 46
+    n47 = g.constant(1.0, [1, m, n])                                   # 47
+    n48 = g.binary(ir.BIN_POW, n36, n47)                               # 48
+    n49 = g.binary(ir.BIN_MUL, n48, n46)                               # 49
+    n50 = g.binary(ir.BIN_MUL, n49, n45)                               # 50
+    n52 = g.binary(ir.BIN_MUL, n50, n30)                               # 52
+    n53 = g.binary(ir.BIN_MUL, n17, n50)                               # 53
+    n56 = g.unary(ir.UN_ADD_CONST, g.unary(ir.UN_NEG, g.unary(ir.UN_POW_CONST, n30, 2.0)), 1.0)  # 54-56
+    n57 = g.binary(ir.BIN_MUL, n53, n56)                               # 57
+    n58 = g.reduce_axes(ir.RED_SUM, n57, [1])                          # 58 Columns
+    n81 = g.binary(ir.BIN_MUL, n50, mk)                                # 81
+    n85 = g.binary(ir.BIN_ADD, n52, g.unary(ir.UN_NEG, n81))           # 84, 85
+    n86 = g.binary(ir.BIN_DRELU, n85, n16)                             # 86
+    n87 = g.reduce_axes(ir.RED_SUM, n86, [1])                          # 87 Columns
+    gt = g.cast(n57, dtype)
+    gz1 = g.cast(n86, dtype)
+    for o in (n39, n58, n87, gt, gz1):
+        g.new_output(o)
+    return g
+
+
+def graph_linear(m, n, k, bias=True, act=None, resid=False, store_z=False, a_t=False, b_t=False, dtype=ir.BF16,
+                 out_dtype=None, gate=None, colsum=None, batch=None):
+    """act(A @ B + bias (+ resid)) (* gate(G)) with optional transposed operand storage.
+
+    a_t: A is stored [k, m] and transposed in the graph; b_t: B stored [n, k] and transposed.
+    Input order: A, B, [bias], [resid], [gate].  Output order: y, [z], [colsum]."""
+    g = ir.Graph()
+    lead = [] if batch is None else [batch]
+    a = g.new_input(lead + ([k, m] if a_t else [m, k]), dtype)
+    b = g.new_input(lead + ([n, k] if b_t else [k, n]), dtype)
+    am = g.transpose(a) if a_t else a
+    bm = g.transpose(b) if b_t else b
+    prec = {ir.BF16: ir.PREC_BF16_F32, ir.F16: ir.PREC_F16_F32, ir.F32: ir.PREC_TF32_F32}[dtype]
+    t = g.matmul(am, bm, prec)
+    rnk = len(lead) + 2
+    r_in = None
+    if bias:
+        bv = g.new_input([n], dtype)
+        t = g.binary(ir.BIN_ADD, t, g.broadcast_to(bv, lead + [m, n]))
+    if resid:
+        r_in = g.new_input(lead + [m, n], dtype)
+        t = g.binary(ir.BIN_ADD, t, r_in)
+    z = t
+    y = t
+    if act is not None:
+        y = g.unary(act, y)
+    if gate is not None:
+        gi = g.new_input(lead + [m, n], dtype)
+        if gate == "mul":
+            y = g.binary(ir.BIN_MUL, y, gi)
+        elif gate == "dgelu":
+            y = g.binary(ir.BIN_MUL, y, g.unary(ir.UN_DGELU, gi))
+        elif gate == "drelu":
+            y = g.binary(ir.BIN_DRELU, y, gi)
+    od = out_dtype if out_dtype is not None else dtype
+    g.new_output(g.cast(y, od))
+    if store_z:
+        g.new_output(g.cast(z, od))
+    if colsum == "resid":
+        g.new_output(g.reduce_axes(ir.RED_SUM, r_in, [rnk - 2]))
+    elif colsum == "y":
+        g.new_output(g.reduce_axes(ir.RED_SUM, y, [rnk - 2]))
+    return g
+
+
+
+def c2_inputs(seed: int = 1):
+    """configs[1]: x bf16 [64,256,56,56] ~ N(0,1), s ~ U[0.5,1.5], b ~ N(0,0.1) per channel (f32),
+    and the f32 tensor [4096,4096,8] ~ N(0,1) of the stand-alone permutation."""
+    g = rng(seed)
+    x = bf16_normal(g, (64, 256, 56, 56))
+    s = g.random(256, dtype=np.float32) + np.float32(0.5)
+    b = g.standard_normal(256, dtype=np.float32) * np.float32(0.1)
+    p = g.standard_normal((4096, 4096, 8), dtype=np.float32)
+    return x, s, b, p
+
+
+def c3_inputs(m: int, n: int, k: int, with_e: bool = False, seed: int = 2):
+    """configs[2] operands in graph_c3 input order: A ~ N(0,1), mask ~ Bernoulli(0.5), B ~ N(0,1/sqrt(k)),
+    b1, b2 ~ N(0,0.02), epilogue mask (the mainloop mask when k == n), Y ~ N(0,1) (, E1, E2 ~ N(0,1))."""
+    r = rng(seed)
+    a = bf16_normal(r, (1, m, k))
+    mk_ml = bf16_bernoulli(r, (1, m, k))
+    b = bf16_normal(r, (1, k, n), 1 / np.sqrt(k))
+    b1 = bf16_normal(r, (1, 1, n), 0.02)
+    b2 = bf16_normal(r, (1, 1, n), 0.02)
+    mk = mk_ml if k == n else bf16_bernoulli(r, (1, m, n))
+    y = bf16_normal(r, (1, m, n))
+    ins = [a, mk_ml, b, b1, b2, mk, y]
+    if with_e:
+        ins += [bf16_normal(r, (1, m, n)), bf16_normal(r, (1, m, n))]
+    return ins

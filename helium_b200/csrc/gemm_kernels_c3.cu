@@ -1,0 +1,15 @@
+// Instantiations of the tcgen05 GEMM with the README-graph epilogue (loss + two column sums +
+// two backward tiles) and the mainloop relu(A) * mask fusion.
+#include "gemm_launch.cuh"
+
+namespace he {
+
+int32_t launch_gemm_c3(const GemmLaunchCfg& cfg, const GemmParams<EpiC3Params>& p, cudaStream_t stream) {
+  if (cfg.bn == 256) {
+    if (cfg.ml == ML_NONE) return launch_majors<256, 4, ML_NONE, 8, EpiC3>(cfg, p, stream);
+    if (cfg.ml == ML_RELU_MASK) return launch_majors<256, 3, ML_RELU_MASK, 8, EpiC3>(cfg, p, stream);
+  }
+  HE_FAIL(HE_ERR_UNSUPPORTED, "fused matmul: no kernel compiled for bn=%d mainloop=%d with this epilogue", cfg.bn, cfg.ml);
+}
+
+}  // namespace he

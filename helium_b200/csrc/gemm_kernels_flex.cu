@@ -1,0 +1,54 @@
+// Instantiations of the tcgen05 GEMM with the bias / residual / activation / gate epilogue.
+#include "gemm_launch.cuh"
+
+namespace he {
+
+// ---- reduction finalisers (fixed summation order => bit-stable results) --------------------------
+// out[b][n] = sum_{tm} partials[b][tm][n]
+__global__ void gemm_colsum_finalize(const float* __restrict__ partials, float* __restrict__ out, int batch, int tiles_m, int N) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= batch * N) return;
+  const int b = i / N, n = i - b * N;
+  const float* p = partials + (size_t)b * tiles_m * N + n;
+  float s = 0.0f;
+  for (int t = 0; t < tiles_m; ++t) s += p[(size_t)t * N];
+  out[i] = s;
+}
+// out[0] = sum_t partials[t], one CTA, tree in a fixed order
+__global__ void gemm_scalar_finalize(const float* __restrict__ partials, float* __restrict__ out, int n) {
+  __shared__ float s[256];
+  float v = 0.0f;
+  for (int i = threadIdx.x; i < n; i += 256) v += partials[i];
+  s[threadIdx.x] = v;
+  __syncthreads();
+  for (int off = 128; off > 0; off >>= 1) {
+    if ((int)threadIdx.x < off) s[threadIdx.x] += s[threadIdx.x + off];
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) out[0] = s[0];
+}
+
+int32_t launch_gemm_flex(const GemmLaunchCfg& cfg, const GemmParams<EpiFlexParams>& p, cudaStream_t stream) {
+  if (cfg.bn == 256) {
+    if (cfg.ml == ML_NONE) return launch_majors<256, 4, ML_NONE, 4, EpiFlex>(cfg, p, stream);
+    if (cfg.ml == ML_RELU_MASK) return launch_majors<256, 3, ML_RELU_MASK, 4, EpiFlex>(cfg, p, stream);
+  } else if (cfg.bn == 128) {
+    if (cfg.ml == ML_NONE) return launch_majors<128, 6, ML_NONE, 4, EpiFlex>(cfg, p, stream);
+  }
+  HE_FAIL(HE_ERR_UNSUPPORTED, "fused matmul: no kernel compiled for bn=%d mainloop=%d with this epilogue", cfg.bn, cfg.ml);
+}
+
+int32_t launch_colsum_finalize(const float* partials, float* out, int batch, int tiles_m, int N, cudaStream_t stream) {
+  const int n = batch * N;
+  gemm_colsum_finalize<<<(n + 255) / 256, 256, 0, stream>>>(partials, out, batch, tiles_m, N);
+  HE_CUDA(cudaGetLastError());
+  return HE_OK;
+}
+
+int32_t launch_scalar_finalize(const float* partials, float* out, int n, cudaStream_t stream) {
+  gemm_scalar_finalize<<<1, 256, 0, stream>>>(partials, out, n);
+  HE_CUDA(cudaGetLastError());
+  return HE_OK;
+}
+
+}  // namespace he

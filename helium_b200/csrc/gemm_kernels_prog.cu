@@ -1,0 +1,14 @@
+// Instantiations of the tcgen05 GEMM with the generic (interpreted) epilogue tier.
+#include "gemm_launch.cuh"
+
+namespace he {
+
+int32_t launch_gemm_program(const GemmLaunchCfg& cfg, const GemmParams<EpiProgramParams>& p, cudaStream_t stream) {
+  if (cfg.bn == 256) {
+    if (cfg.ml == ML_NONE) return launch_majors<256, 4, ML_NONE, 8, EpiProgram>(cfg, p, stream);
+    if (cfg.ml == ML_RELU_MASK) return launch_majors<256, 3, ML_RELU_MASK, 8, EpiProgram>(cfg, p, stream);
+  }
+  HE_FAIL(HE_ERR_UNSUPPORTED, "fused matmul: no kernel compiled for bn=%d mainloop=%d with this epilogue", cfg.bn, cfg.ml);
+}
+
+}  // namespace he

@@ -1,0 +1,697 @@
+// Planner for fused matmul subgraphs (hot-path rows G0-G3, F1-F2).
+//
+// Replaces, on the host side, MatmulGenerator::new / find_root / find_and_verify_leafs
+// (helium-kernel-generator/src/generators/matmul.rs:88-130, 234-318) and the playground's
+// KernelGenerator::generate (helium-playground/src/kernel_generator.rs:51-117): it splits the
+// subgraph into operand side (mainloop) and result side (epilogue), decides operand majors from
+// swap_dims nodes, and maps the epilogue onto either a hand-written functor (catalogue match on a
+// canonical text of the epilogue program) or the interpreted tier.
+#include <cuda.h>
+
+#include <algorithm>
+#include <memory>
+#include <mutex>
+
+#include "gemm_plan.cuh"
+
+namespace he {
+namespace {
+
+// ------------------------------------------------------------------------------------------------
+// TMA descriptor encoding through the driver entry point (no link-time dependency on libcuda)
+// ------------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+
+// Operand tensor [batch, R, K] (K-major) or [batch, K, R] (MN-major), 2-byte elements.
+int32_t make_operand_tmap(CUtensorMap* out, const void* ptr, int ab_format, bool mn_major, int64_t R, int64_t K,
+                          int64_t batch, int box_rows) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) HE_FAIL(HE_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  if ((uintptr_t)ptr % 16 != 0) HE_FAIL(HE_ERR_UNSUPPORTED, "fused matmul: operand pointer is not 16-byte aligned");
+  cuuint64_t dims[3], strides[2];
+  cuuint32_t box[3], estr[3] = {1, 1, 1};
+  if (!mn_major) {
+    dims[0] = (cuuint64_t)K; dims[1] = (cuuint64_t)R; dims[2] = (cuuint64_t)batch;
+    strides[0] = (cuuint64_t)K * 2; strides[1] = (cuuint64_t)R * K * 2;
+    box[0] = kBK; box[1] = (cuuint32_t)box_rows; box[2] = 1;
+  } else {
+    dims[0] = (cuuint64_t)R; dims[1] = (cuuint64_t)K; dims[2] = (cuuint64_t)batch;
+    strides[0] = (cuuint64_t)R * 2; strides[1] = (cuuint64_t)R * K * 2;
+    box[0] = 64; box[1] = kBK; box[2] = 1;
+  }
+  if (strides[0] % 16 != 0) HE_FAIL(HE_ERR_UNSUPPORTED, "fused matmul: operand row pitch %llu B is not a multiple of 16", (unsigned long long)strides[0]);
+  CUresult r = fn(out, ab_format == 1 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3,
+                  const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) HE_FAIL(HE_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+  return HE_OK;
+}
+
+// ------------------------------------------------------------------------------------------------
+// operand (mainloop) side
+// ------------------------------------------------------------------------------------------------
+struct OperandInfo {
+  int root = -1;      // graph node of the tensor that feeds the MMA
+  int mask = -1;      // second tensor multiplied in (relu(A) * M)
+  bool relu = false;
+  bool transposed = false;  // root is stored with its last two dims swapped w.r.t. what matmul sees
+  bool ok = true;
+  bool pure() const { return ok && mask < 0 && !relu; }
+};
+
+OperandInfo trace_operand(const Graph& g, int node, bool transposed) {
+  const he_node& n = g.nodes[node];
+  OperandInfo r;
+  switch (n.kind) {
+    case HE_OP_INPUT:
+      r.root = node;
+      r.transposed = transposed;
+      return r;
+    case HE_OP_CAST:
+      if (n.dtype == g.nodes[n.in[0]].dtype) return trace_operand(g, n.in[0], transposed);
+      break;
+    case HE_OP_RESHAPE: {
+      const he_node& a = g.nodes[n.in[0]];
+      // only leading size-1 dims may come and go
+      if (n.rank >= 2 && a.rank >= 2 && n.shape[n.rank - 1] == a.shape[a.rank - 1] && n.shape[n.rank - 2] == a.shape[a.rank - 2])
+        return trace_operand(g, n.in[0], transposed);
+      break;
+    }
+    case HE_OP_SWAP_DIMS: {
+      const int lo = std::min(n.axis_a, n.axis_b), hi = std::max(n.axis_a, n.axis_b);
+      if (lo == hi) return trace_operand(g, n.in[0], transposed);
+      if (lo == n.rank - 2 && hi == n.rank - 1) return trace_operand(g, n.in[0], !transposed);
+      break;
+    }
+    case HE_OP_UNARY:
+      if (n.sub_op == HE_UN_RELU) {
+        r = trace_operand(g, n.in[0], transposed);
+        if (r.pure()) {
+          r.relu = true;
+          return r;
+        }
+      }
+      break;
+    case HE_OP_BINARY:
+      if (n.sub_op == HE_BIN_MUL) {
+        OperandInfo l = trace_operand(g, n.in[0], transposed), rr = trace_operand(g, n.in[1], transposed);
+        if (l.ok && rr.ok) {
+          if (!rr.pure() && l.pure()) std::swap(l, rr);
+          if (rr.pure() && l.mask < 0 && l.transposed == rr.transposed) {
+            l.mask = rr.root;
+            return l;
+          }
+        }
+      }
+      break;
+    default: break;
+  }
+  r.ok = false;
+  return r;
+}
+
+// ------------------------------------------------------------------------------------------------
+// small graph builder for the catalogue patterns
+// ------------------------------------------------------------------------------------------------
+struct GB {
+  std::vector<he_node> nodes;
+  std::vector<int> outputs;
+  int add(he_node n) {
+    nodes.push_back(n);
+    return (int)nodes.size() - 1;
+  }
+  static he_node base(int kind, int dtype, std::initializer_list<int64_t> shape) {
+    he_node n{};
+    n.kind = kind;
+    n.dtype = dtype;
+    n.rank = (int)shape.size();
+    int i = 0;
+    for (int64_t d : shape) n.shape[i++] = d;
+    n.in[0] = n.in[1] = n.in[2] = -1;
+    return n;
+  }
+  int input(int dtype, std::initializer_list<int64_t> shape) { return add(base(HE_OP_INPUT, dtype, shape)); }
+  int like(int kind, int src) {
+    he_node n = nodes[src];
+    n.kind = kind;
+    n.in[0] = n.in[1] = n.in[2] = -1;
+    n.sub_op = 0;
+    n.const_bits = 0;
+    return add(n);
+  }
+  int unary(int op, int a, float c = 0.0f) {
+    int i = like(HE_OP_UNARY, a);
+    nodes[i].sub_op = op;
+    nodes[i].in[0] = a;
+    memcpy(&nodes[i].const_bits, &c, 4);
+    return i;
+  }
+  int binary(int op, int a, int b) {
+    int i = like(HE_OP_BINARY, a);
+    nodes[i].sub_op = op;
+    nodes[i].in[0] = a;
+    nodes[i].in[1] = b;
+    return i;
+  }
+  int constant(float v, std::initializer_list<int64_t> shape) {
+    he_node n = base(HE_OP_CONSTANT, HE_F32, shape);
+    memcpy(&n.const_bits, &v, 4);
+    return add(n);
+  }
+  int broadcast(int a, int axis, int64_t amount) {
+    int i = like(HE_OP_BROADCAST, a);
+    nodes[i].in[0] = a;
+    nodes[i].shape[axis] = amount;
+    return i;
+  }
+  int reduce_sum(int a, uint32_t axes) {
+    int i = like(HE_OP_REDUCE, a);
+    nodes[i].in[0] = a;
+    nodes[i].sub_op = HE_RED_SUM;
+    nodes[i].axes = axes;
+    nodes[i].dtype = HE_F32;
+    for (int k = 0; k < nodes[i].rank; ++k)
+      if ((axes >> k) & 1u) nodes[i].shape[k] = 1;
+    return i;
+  }
+  int matmul(int a, int b) {
+    he_node n = base(HE_OP_MATMUL, HE_F32, {nodes[a].shape[0], nodes[a].shape[1], nodes[b].shape[2]});
+    n.in[0] = a;
+    n.in[1] = b;
+    n.sub_op = HE_PREC_BF16_F32;
+    return add(n);
+  }
+  Graph graph() const {
+    Graph g;
+    he_graph_desc d{(int32_t)nodes.size(), nodes.data(), (int32_t)outputs.size(), outputs.data()};
+    parse_graph(&d, &g);
+    return g;
+  }
+};
+
+constexpr int64_t kPM = 8, kPN = 16, kPK = 8;  // pattern graphs only need distinct M and N
+
+struct FlexCombo {
+  bool bias, resid, store_z;
+  int act, gate, colsum;
+};
+
+struct FlexPattern {
+  FlexCombo combo;
+  PwCanon canon;
+  int bias_slot = -1, resid_slot = -1, gate_slot = -1;  // pattern-graph epilogue input slots
+  int y_out = -1, z_out = -1, colsum_out = -1;
+};
+
+struct C3Roles {
+  int b1 = -1, b2 = -1, mask = -1, y = -1, e1 = -1, e2 = -1;               // input slots
+  int loss = -1, db2 = -1, db1 = -1, gt = -1, gz1 = -1;                      // output indices
+};
+
+int32_t canon_of(const Graph& g, int matmul_node, PwCompiled* c, PwCanon* canon) {
+  PwCompileOptions opt;
+  opt.acc_node = matmul_node;
+  opt.fuse_fma = false;
+  opt.epilogue = true;
+  HE_TRY(compile_pointwise(g, opt, c));
+  const int r = c->iter_rank;
+  return canonicalize_program(g, *c, r - 2, r - 1, canon);
+}
+
+// Pattern graphs put the two matmul operands first, so graph input slot s >= 2 is epilogue input.
+bool build_flex_pattern(const FlexCombo& fc, FlexPattern* out) {
+  GB b;
+  int a = b.input(HE_BF16, {1, kPM, kPK}), w = b.input(HE_BF16, {1, kPK, kPN});
+  int acc = b.matmul(a, w);
+  int next_slot = 2;
+  int t = acc;
+  out->combo = fc;
+  if (fc.bias) {
+    int bias = b.input(HE_BF16, {1, 1, kPN});
+    out->bias_slot = next_slot++;
+    t = b.binary(HE_BIN_ADD, t, b.broadcast(bias, 1, kPM));
+  }
+  int resid = -1;
+  if (fc.resid) {
+    resid = b.input(HE_BF16, {1, kPM, kPN});
+    out->resid_slot = next_slot++;
+    t = b.binary(HE_BIN_ADD, t, resid);
+  }
+  int nout = 0;
+  int z = t;
+  int y = t;
+  if (fc.act == ACT_RELU) y = b.unary(HE_UN_RELU, y);
+  else if (fc.act == ACT_GELU) y = b.unary(HE_UN_GELU, y);
+  else if (fc.act == ACT_TANH) y = b.unary(HE_UN_TANH, y);
+  if (fc.gate != GATE_NONE) {
+    int gi = b.input(HE_BF16, {1, kPM, kPN});
+    out->gate_slot = next_slot++;
+    if (fc.gate == GATE_MUL) y = b.binary(HE_BIN_MUL, y, gi);
+    else if (fc.gate == GATE_DGELU) y = b.binary(HE_BIN_MUL, y, b.unary(HE_UN_DGELU, gi));
+    else if (fc.gate == GATE_DRELU) y = b.binary(HE_BIN_DRELU, y, gi);
+    else return false;
+  }
+  b.outputs.push_back(y);
+  out->y_out = nout++;
+  if (fc.store_z) {
+    if (z == y) return false;
+    b.outputs.push_back(z);
+    out->z_out = nout++;
+  }
+  if (fc.colsum == 1) {
+    if (!fc.resid) return false;
+    b.outputs.push_back(b.reduce_sum(resid, 1u << 1));
+    out->colsum_out = nout++;
+  } else if (fc.colsum == 2) {
+    b.outputs.push_back(b.reduce_sum(y, 1u << 1));
+    out->colsum_out = nout++;
+  }
+  Graph g = b.graph();
+  PwCompiled c;
+  return canon_of(g, acc, &c, &out->canon) == HE_OK;
+}
+
+const std::vector<FlexPattern>& flex_catalogue() {
+  static std::vector<FlexPattern> cat;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    for (int bias = 0; bias < 2; ++bias)
+      for (int resid = 0; resid < 2; ++resid)
+        for (int sz = 0; sz < 2; ++sz)
+          for (int act = ACT_NONE; act <= ACT_TANH; ++act)
+            for (int gate = GATE_NONE; gate <= GATE_DRELU; ++gate)
+              for (int cs = 0; cs < 3; ++cs) {
+                FlexPattern p;
+                if (build_flex_pattern(FlexCombo{bias != 0, resid != 0, sz != 0, act, gate, cs}, &p)) cat.push_back(p);
+              }
+  });
+  return cat;
+}
+
+// README.md:33-79, node numbers in comments.
+bool build_c3_pattern(bool with_e, float inv_n, PwCanon* canon, C3Roles* roles) {
+  GB b;
+  int a = b.input(HE_BF16, {1, kPM, kPK}), w = b.input(HE_BF16, {1, kPK, kPN});
+  int acc = b.matmul(a, w);
+  int slot = 2;
+  int b1 = b.input(HE_BF16, {1, 1, kPN}); roles->b1 = slot++;      // 6
+  int b2 = b.input(HE_BF16, {1, 1, kPN}); roles->b2 = slot++;      // 8
+  int mk = b.input(HE_BF16, {1, kPM, kPN}); roles->mask = slot++;  // 9
+  int yy = b.input(HE_BF16, {1, kPM, kPN}); roles->y = slot++;     // 11
+  int n14 = acc, n27 = acc;
+  if (with_e) {
+    int e1 = b.input(HE_BF16, {1, kPM, kPN}); roles->e1 = slot++;  // 13
+    int e2 = b.input(HE_BF16, {1, kPM, kPN}); roles->e2 = slot++;  // 26
+    n14 = b.binary(HE_BIN_ADD, acc, e1);                           // 14
+    n27 = b.binary(HE_BIN_ADD, acc, e2);                           // 27
+  }
+  int n16 = b.binary(HE_BIN_ADD, n14, b.broadcast(b1, 1, kPM));    // 15, 16
+  int n17 = b.unary(HE_UN_RELU, n16);                              // 17
+  int n29 = b.binary(HE_BIN_ADD, n27, b.broadcast(b2, 1, kPM));    // 28, 29
+  int n30 = b.unary(HE_UN_TANH, n29);                              // 30
+  int n32 = b.unary(HE_UN_ADD_CONST, b.unary(HE_UN_NEG, n17), 1.0f);  // 31, 32
+  int n33 = b.binary(HE_BIN_MUL, n32, mk);                         // 33
+  int n34 = b.binary(HE_BIN_MUL, n17, n30);                        // 34
+  int n35 = b.binary(HE_BIN_ADD, n33, n34);                        // 35
+  int n36 = b.binary(HE_BIN_SUB, n35, yy);                         // 36
+  int n37 = b.unary(HE_UN_POW_CONST, n36, 2.0f);                   // 37
+  int n38 = b.unary(HE_UN_MUL_CONST, n37, inv_n);                  // 38
+  int n39 = b.reduce_sum(n38, 7u);                                 // 39 Batch
+  int n41 = b.constant(1.0f, {1, 1, 1});                           // 41
+  int n44 = b.broadcast(b.broadcast(b.broadcast(n41, 1, kPM), 2, kPN), 0, 1);  // 42-44
+  int n45 = b.unary(HE_UN_MUL_CONST, n44, inv_n);                  // 45
+  int n46 = b.constant(2.0f, {1, kPM, kPN});                       // 46
+  int n47 = b.constant(1.0f, {1, kPM, kPN});                       // 47
+  int n48 = b.binary(HE_BIN_POW, n36, n47);                        // 48
+  int n49 = b.binary(HE_BIN_MUL, n48, n46);                        // 49
+  int n50 = b.binary(HE_BIN_MUL, n49, n45);                        // 50
+  int n52 = b.binary(HE_BIN_MUL, n50, n30);                        // 52
+  int n53 = b.binary(HE_BIN_MUL, n17, n50);                        // 53
+  int n56 = b.unary(HE_UN_ADD_CONST, b.unary(HE_UN_NEG, b.unary(HE_UN_POW_CONST, n30, 2.0f)), 1.0f);  // 54-56
+  int n57 = b.binary(HE_BIN_MUL, n53, n56);                        // 57
+  int n58 = b.reduce_sum(n57, 1u << 1);                            // 58 Columns
+  int n81 = b.binary(HE_BIN_MUL, n50, mk);                         // 81
+  int n85 = b.binary(HE_BIN_ADD, n52, b.unary(HE_UN_NEG, n81));    // 84, 85
+  int n86 = b.binary(HE_BIN_DRELU, n85, n16);                      // 86
+  int n87 = b.reduce_sum(n86, 1u << 1);                            // 87 Columns
+  b.outputs = {n39, n58, n87, n57, n86};
+  roles->loss = 0; roles->db2 = 1; roles->db1 = 2; roles->gt = 3; roles->gz1 = 4;
+  Graph g = b.graph();
+  PwCompiled c;
+  return canon_of(g, acc, &c, canon) == HE_OK;
+}
+
+// ------------------------------------------------------------------------------------------------
+// the plan
+// ------------------------------------------------------------------------------------------------
+enum class EpiKind { Flex, C3, Program, Sgemm };
+
+struct MatmulPlan : he_plan {
+  GemmCore core{};
+  GemmLaunchCfg cfg{};
+  EpiKind kind = EpiKind::Flex;
+  int a_slot = -1, b_slot = -1, mask_slot = -1;  // he_launch input slots
+  // Flex
+  EpiFlexParams flex{};
+  int f_bias = -1, f_resid = -1, f_gate = -1, f_y = -1, f_z = -1, f_colsum = -1;
+  // C3
+  EpiC3Params c3{};
+  C3Roles r3;
+  // Program
+  PwCompiled prog;
+  int n_inputs = 0, n_outputs = 0;
+  // Sgemm
+  int s_bias = -1, s_act = 0, s_in_dt = HE_F32, s_out_dt = HE_F32, s_bias_dt = HE_F32;
+  // workspace layout (floats)
+  size_t ws_col_off[2] = {0, 0}, ws_scalar_off = 0;
+
+  int32_t launch(const void* const* inputs, void* const* outputs, void* workspace, cudaStream_t stream) override {
+    for (int i = 0; i < n_inputs; ++i)
+      if (!inputs || !inputs[i]) HE_FAIL(HE_ERR_INVALID, "fused matmul launch: input %d is null", i);
+    for (int i = 0; i < n_outputs; ++i)
+      if (!outputs || !outputs[i]) HE_FAIL(HE_ERR_INVALID, "fused matmul launch: output %d is null", i);
+    if (core.M == 0 || core.N == 0 || core.batch == 0) return HE_OK;
+    if (kind == EpiKind::Sgemm) {
+      HE_TRY(launch_sgemm(inputs[a_slot], inputs[b_slot], outputs[0], s_in_dt, s_out_dt, core.batch, core.M, core.N, core.K,
+                          cfg.a_mn, cfg.b_mn, s_bias >= 0 ? inputs[s_bias] : nullptr, s_bias_dt, s_act, stream));
+      last_launches = 1;
+      return HE_OK;
+    }
+    float* ws = reinterpret_cast<float*>(workspace);
+    CUtensorMap ta, tb, tm;
+    memset(&tm, 0, sizeof tm);
+    HE_TRY(make_operand_tmap(&ta, inputs[a_slot], core.ab_format, cfg.a_mn, core.M, core.K, core.batch, kBM));
+    HE_TRY(make_operand_tmap(&tb, inputs[b_slot], core.ab_format, cfg.b_mn, core.N, core.K, core.batch, cfg.bn));
+    if (mask_slot >= 0) HE_TRY(make_operand_tmap(&tm, inputs[mask_slot], core.ab_format, cfg.a_mn, core.M, core.K, core.batch, kBM));
+    GemmCore c = core;
+    c.status = ctx ? ctx->d_status : nullptr;
+    if (kind == EpiKind::Flex) {
+      GemmParams<EpiFlexParams> p;
+      p.tma_a = ta; p.tma_b = tb; p.tma_mask = tm;
+      p.core = c;
+      p.epi = flex;
+      p.epi.out = outputs[f_y];
+      p.epi.out_z = f_z >= 0 ? outputs[f_z] : nullptr;
+      p.epi.bias = f_bias >= 0 ? inputs[f_bias] : nullptr;
+      p.epi.resid = f_resid >= 0 ? inputs[f_resid] : nullptr;
+      p.epi.gate_in = f_gate >= 0 ? inputs[f_gate] : nullptr;
+      p.epi.colsum_partials = ws ? ws + ws_col_off[0] : nullptr;
+      bool vec = c.N % 8 == 0;
+      const void* ptrs[] = {p.epi.out, p.epi.out_z, p.epi.resid, p.epi.gate_in};
+      for (const void* q : ptrs) vec = vec && ((uintptr_t)q % 16 == 0);
+      p.epi.vec_ok = vec ? 1 : 0;
+      HE_TRY(launch_gemm_flex(cfg, p, stream));
+      last_launches = 1;
+      if (flex.colsum_src != 0) {
+        HE_TRY(launch_colsum_finalize(ws + ws_col_off[0], (float*)outputs[f_colsum], c.batch, c.tiles_m, c.N, stream));
+        ++last_launches;
+      }
+      return HE_OK;
+    }
+    if (kind == EpiKind::C3) {
+      GemmParams<EpiC3Params> p;
+      p.tma_a = ta; p.tma_b = tb; p.tma_mask = tm;
+      p.core = c;
+      p.epi = c3;
+      p.epi.mask = inputs[r3.mask];
+      p.epi.y = inputs[r3.y];
+      p.epi.b1 = inputs[r3.b1];
+      p.epi.b2 = inputs[r3.b2];
+      p.epi.e1 = r3.e1 >= 0 ? inputs[r3.e1] : nullptr;
+      p.epi.e2 = r3.e2 >= 0 ? inputs[r3.e2] : nullptr;
+      p.epi.out_gt = outputs[r3.gt];
+      p.epi.out_gz1 = outputs[r3.gz1];
+      p.epi.db2_partials = ws + ws_col_off[0];
+      p.epi.db1_partials = ws + ws_col_off[1];
+      p.epi.loss_partials = ws + ws_scalar_off;
+      bool vec = c.N % 8 == 0;
+      const void* ptrs[] = {p.epi.mask, p.epi.y, p.epi.e1, p.epi.e2, p.epi.out_gt, p.epi.out_gz1};
+      for (const void* q : ptrs) vec = vec && ((uintptr_t)q % 16 == 0);
+      p.epi.vec_ok = vec ? 1 : 0;
+      HE_TRY(launch_gemm_c3(cfg, p, stream));
+      HE_TRY(launch_colsum_finalize(ws + ws_col_off[0], (float*)outputs[r3.db2], c.batch, c.tiles_m, c.N, stream));
+      HE_TRY(launch_colsum_finalize(ws + ws_col_off[1], (float*)outputs[r3.db1], c.batch, c.tiles_m, c.N, stream));
+      HE_TRY(launch_scalar_finalize(ws + ws_scalar_off, (float*)outputs[r3.loss], c.num_tiles, stream));
+      last_launches = 4;
+      return HE_OK;
+    }
+    GemmParams<EpiProgramParams> p;
+    p.tma_a = ta; p.tma_b = tb; p.tma_mask = tm;
+    p.core = c;
+    p.epi.prog = prog.prog;
+    for (int i = 0; i < n_inputs; ++i) p.epi.prog.in[i] = inputs[i];
+    for (int i = 0; i < n_outputs; ++i) p.epi.prog.out[i] = outputs[i];
+    HE_TRY(launch_gemm_program(cfg, p, stream));
+    last_launches = 1;
+    return HE_OK;
+  }
+};
+
+}  // namespace
+
+int32_t plan_fused_matmul(he_ctx* ctx, const Graph& g, he_plan** out, int* tier_only) {
+  int mm = -1;
+  for (int i = 0; i < (int)g.nodes.size(); ++i)
+    if (g.nodes[i].kind == HE_OP_MATMUL) {
+      if (mm >= 0) HE_FAIL(HE_ERR_UNSUPPORTED, "fused matmul: more than one matmul in the subgraph");
+      mm = i;
+    }
+  if (mm < 0) HE_FAIL(HE_ERR_INVALID, "fused matmul: subgraph has no matmul (matmul.rs:222-232)");
+  const he_node& M = g.nodes[mm];
+  const int r = M.rank;
+  const OperandInfo A = trace_operand(g, M.in[0], false), B = trace_operand(g, M.in[1], false);
+  if (!A.ok || !B.ok)
+    HE_FAIL(HE_ERR_UNSUPPORTED, "fused matmul: operand side uses ops outside {cast, reshape, transpose, relu, elementwise mask}");
+  if (!B.pure()) HE_FAIL(HE_ERR_UNSUPPORTED, "fused matmul: mainloop fusion on the B operand is not implemented");
+  const he_node& An = g.nodes[A.root];
+  const he_node& Bn = g.nodes[B.root];
+
+  MatmulPlan* plan = new MatmulPlan();
+  std::unique_ptr<MatmulPlan> guard(plan);
+  plan->ctx = ctx;
+  GemmCore& c = plan->core;
+  c.M = (int)M.shape[r - 2];
+  c.N = (int)M.shape[r - 1];
+  c.K = (int)g.nodes[M.in[0]].shape[r - 1];
+  int64_t batch = 1;
+  for (int k = 0; k < r - 2; ++k) batch *= M.shape[k];
+  c.batch = (int)batch;
+  if (num_elements(M) >= (1ll << 31)) HE_FAIL(HE_ERR_UNSUPPORTED, "fused matmul: output exceeds the 32-bit index range");
+  auto slot_of = [&](int node) {
+    for (size_t k = 0; k < g.inputs.size(); ++k)
+      if (g.inputs[k] == node) return (int)k;
+    return -1;
+  };
+  plan->a_slot = slot_of(A.root);
+  plan->b_slot = slot_of(B.root);
+  plan->mask_slot = A.mask >= 0 ? slot_of(A.mask) : -1;
+  plan->n_inputs = (int)g.inputs.size();
+  plan->n_outputs = (int)g.outputs.size();
+  plan->cfg.a_mn = A.transposed;
+  plan->cfg.b_mn = !B.transposed;  // helium stores B as [K, N] row-major = N-major
+  plan->cfg.ml = (A.relu ? ML_RELU : 0) | (A.mask >= 0 ? ML_MASK : 0);
+
+  // ---- SIMT path: f32 operands (exact f32 products; the precision setting is a minimum,
+  // precision.rs:3-9) and 2-byte operands that break the TMA pitch rules
+  auto try_simt = [&](const char* why) -> int32_t {
+    if (plan->cfg.ml != ML_NONE) HE_FAIL(HE_ERR_UNSUPPORTED, "fused matmul: mainloop fusion needs the tensor-core path (%s)", why);
+    PwCompiled pc;
+    PwCanon canon;
+    HE_TRY(canon_of(g, mm, &pc, &canon));
+    int bias_slot = -1, act = 0;
+    bool ok = false;
+    if (canon.text == "store(A);") ok = true;
+    else if (canon.text == "store(sum(A,I0:R));") { ok = true; bias_slot = canon.slot_order[0]; }
+    else if (canon.text == "store(u8(sum(A,I0:R)));") { ok = true; bias_slot = canon.slot_order[0]; act = 1; }
+    else if (canon.text == "store(u8(A));") { ok = true; act = 1; }
+    const int odt = g.nodes[g.outputs[0]].dtype;
+    if (!ok || dclass(odt) != DClass::Float || (bias_slot >= 0 && dclass(g.nodes[g.inputs[bias_slot]].dtype) != DClass::Float))
+      HE_FAIL(HE_ERR_UNSUPPORTED, "fused matmul: the SIMT path (%s) supports only store / +bias / relu epilogues", why);
+    if (tier_only) { *tier_only = 2; return HE_OK; }
+    plan->kind = EpiKind::Sgemm;
+    plan->s_bias = bias_slot;
+    plan->s_act = act;
+    plan->s_in_dt = An.dtype;
+    plan->s_out_dt = odt;
+    plan->s_bias_dt = bias_slot >= 0 ? g.nodes[g.inputs[bias_slot]].dtype : HE_F32;
+    plan->description = std::string("fused matmul: SIMT FFMA kernel, 64x64 tiles (") + why + ")";
+    *out = guard.release();
+    return HE_OK;
+  };
+  if (An.dtype == HE_F32 && Bn.dtype == HE_F32) return try_simt("f32 operands");
+  if (!((An.dtype == HE_BF16 && Bn.dtype == HE_BF16) || (An.dtype == HE_F16 && Bn.dtype == HE_F16)))
+    HE_FAIL(HE_ERR_UNSUPPORTED, "fused matmul: operands must both be bf16, both f16 or both f32 (got %s x %s)", dtype_name(An.dtype), dtype_name(Bn.dtype));
+  c.ab_format = An.dtype == HE_BF16 ? 1 : 0;
+  if (plan->cfg.ml != ML_NONE && plan->cfg.ml != ML_RELU_MASK)
+    HE_FAIL(HE_ERR_UNSUPPORTED, "fused matmul: only the relu(A) * mask mainloop fusion is compiled in");
+  if (plan->cfg.ml != ML_NONE && (An.dtype != HE_BF16 || g.nodes[A.mask].dtype != HE_BF16))
+    HE_FAIL(HE_ERR_UNSUPPORTED, "fused matmul: mainloop fusion needs bf16 A and mask");
+  // TMA pitch rules (16-byte multiples)
+  if ((plan->cfg.a_mn ? c.M : c.K) % 8 != 0 || (plan->cfg.b_mn ? c.N : c.K) % 8 != 0) {
+    const int32_t st = try_simt("operand rows are not multiples of 8 elements, TMA needs 16-byte pitches");
+    if (st != HE_OK)
+      HE_FAIL(HE_ERR_UNSUPPORTED, "fused matmul: operand row lengths must be multiples of 8 elements for TMA (M=%d N=%d K=%d) and the epilogue is beyond the SIMT path", c.M, c.N, c.K);
+    return st;
+  }
+
+  // ---- epilogue
+  PwCompiled pc;
+  PwCanon canon;
+  HE_TRY(canon_of(g, mm, &pc, &canon));
+  if ((int64_t)pc.prog.n_elems != num_elements(M))
+    HE_FAIL(HE_ERR_UNSUPPORTED, "fused matmul: epilogue outputs must have the matmul's element count");
+
+  plan->cfg.bn = 256;
+  auto finish_tiles = [&]() {
+    c.tiles_m = (c.M + kBM - 1) / kBM;
+    c.tiles_n = (c.N + plan->cfg.bn - 1) / plan->cfg.bn;
+    c.num_tiles = c.tiles_m * c.tiles_n * c.batch;
+    c.k_blocks = (c.K + kBK - 1) / kBK;
+    plan->cfg.grid = std::max(1, std::min(c.num_tiles, ctx_sm_count(ctx)));
+  };
+  auto out_dt = [&](int out_idx) { return g.nodes[g.outputs[out_idx]].dtype; };
+  auto in_dt = [&](int slot) { return g.nodes[g.inputs[slot]].dtype; };
+  char desc[320];
+
+  // (1) Flex catalogue
+  for (const FlexPattern& fp : flex_catalogue()) {
+    if (fp.canon.text != canon.text) continue;
+    auto cand_slot = [&](int pattern_slot) {
+      for (size_t k = 0; k < fp.canon.slot_order.size(); ++k)
+        if (fp.canon.slot_order[k] == pattern_slot) return canon.slot_order[k];
+      return -1;
+    };
+    auto cand_out = [&](int pattern_out) {
+      for (size_t k = 0; k < fp.canon.out_order.size(); ++k)
+        if (fp.canon.out_order[k] == pattern_out) return canon.out_order[k];
+      return -1;
+    };
+    if (tier_only) { *tier_only = 2; return HE_OK; }
+    plan->kind = EpiKind::Flex;
+    plan->f_bias = fp.bias_slot >= 0 ? cand_slot(fp.bias_slot) : -1;
+    plan->f_resid = fp.resid_slot >= 0 ? cand_slot(fp.resid_slot) : -1;
+    plan->f_gate = fp.gate_slot >= 0 ? cand_slot(fp.gate_slot) : -1;
+    plan->f_y = cand_out(fp.y_out);
+    plan->f_z = fp.z_out >= 0 ? cand_out(fp.z_out) : -1;
+    plan->f_colsum = fp.colsum_out >= 0 ? cand_out(fp.colsum_out) : -1;
+    EpiFlexParams& f = plan->flex;
+    f.act = fp.combo.act;
+    f.gate = fp.combo.gate;
+    f.colsum_src = fp.combo.colsum;
+    f.out_dt = out_dt(plan->f_y);
+    f.z_dt = plan->f_z >= 0 ? out_dt(plan->f_z) : HE_F32;
+    f.bias_dt = plan->f_bias >= 0 ? in_dt(plan->f_bias) : HE_F32;
+    f.resid_dt = plan->f_resid >= 0 ? in_dt(plan->f_resid) : HE_F32;
+    f.gate_dt = plan->f_gate >= 0 ? in_dt(plan->f_gate) : HE_F32;
+    const int dts[] = {f.out_dt, f.z_dt, f.bias_dt, f.resid_dt, f.gate_dt};
+    for (int dt : dts)
+      if (dclass(dt) != DClass::Float) HE_FAIL(HE_ERR_UNSUPPORTED, "fused matmul: epilogue tensors must be float");
+    // a narrow N wastes half of a 256-wide tile
+    if (c.N <= 128 && plan->cfg.ml == ML_NONE) plan->cfg.bn = 128;
+    finish_tiles();
+    if (f.colsum_src != 0) {
+      plan->ws_col_off[0] = 0;
+      plan->workspace_bytes = (size_t)c.batch * c.tiles_m * c.N * sizeof(float);
+    }
+    snprintf(desc, sizeof desc,
+             "fused matmul tier 2: tcgen05 128x%dx64, %s-major A, %s-major B, mainloop %d, epilogue flex(bias=%d resid=%d act=%d gate=%d z=%d colsum=%d), grid %d",
+             plan->cfg.bn, plan->cfg.a_mn ? "M" : "K", plan->cfg.b_mn ? "N" : "K", plan->cfg.ml, plan->f_bias >= 0, plan->f_resid >= 0,
+             f.act, f.gate, plan->f_z >= 0, f.colsum_src, plan->cfg.grid);
+    plan->description = desc;
+    *out = guard.release();
+    return HE_OK;
+  }
+
+  // (2) the README graph: find the MulConstant operand, rebuild the pattern with it, compare
+  {
+    float inv_n = 0.0f;
+    bool have = false;
+    for (const he_node& n : g.nodes)
+      if (n.kind == HE_OP_UNARY && n.sub_op == HE_UN_MUL_CONST && !have) {
+        memcpy(&inv_n, &n.const_bits, 4);
+        have = true;
+      }
+    for (int with_e = 0; have && with_e < 2; ++with_e) {
+      PwCanon pat;
+      C3Roles roles;
+      if (!build_c3_pattern(with_e != 0, inv_n, &pat, &roles) || pat.text != canon.text) continue;
+      auto cand_slot = [&](int pattern_slot) {
+        for (size_t k = 0; k < pat.slot_order.size(); ++k)
+          if (pat.slot_order[k] == pattern_slot) return canon.slot_order[k];
+        return -1;
+      };
+      auto cand_out = [&](int pattern_out) {
+        for (size_t k = 0; k < pat.out_order.size(); ++k)
+          if (pat.out_order[k] == pattern_out) return canon.out_order[k];
+        return -1;
+      };
+      C3Roles rr;
+      rr.b1 = cand_slot(roles.b1); rr.b2 = cand_slot(roles.b2); rr.mask = cand_slot(roles.mask); rr.y = cand_slot(roles.y);
+      rr.e1 = roles.e1 >= 0 ? cand_slot(roles.e1) : -1;
+      rr.e2 = roles.e2 >= 0 ? cand_slot(roles.e2) : -1;
+      rr.loss = cand_out(roles.loss); rr.db2 = cand_out(roles.db2); rr.db1 = cand_out(roles.db1);
+      rr.gt = cand_out(roles.gt); rr.gz1 = cand_out(roles.gz1);
+      const int full_dt = in_dt(rr.mask);
+      bool dt_ok = in_dt(rr.y) == full_dt && out_dt(rr.gt) == full_dt && out_dt(rr.gz1) == full_dt &&
+                   in_dt(rr.b1) == in_dt(rr.b2) && dclass(full_dt) == DClass::Float && dclass(in_dt(rr.b1)) == DClass::Float;
+      if (rr.e1 >= 0) dt_ok = dt_ok && in_dt(rr.e1) == full_dt && in_dt(rr.e2) == full_dt;
+      if (!dt_ok) continue;  // falls through to the interpreter tier
+      if (tier_only) { *tier_only = 2; return HE_OK; }
+      plan->kind = EpiKind::C3;
+      plan->r3 = rr;
+      plan->c3.inv_n = inv_n;
+      plan->c3.full_dt = full_dt;
+      plan->c3.vec_dt = in_dt(rr.b1);
+      finish_tiles();
+      const size_t col = ((size_t)c.batch * c.tiles_m * c.N + 63) / 64 * 64;
+      plan->ws_col_off[0] = 0;
+      plan->ws_col_off[1] = col;
+      plan->ws_scalar_off = 2 * col;
+      plan->workspace_bytes = (2 * col + (size_t)c.num_tiles) * sizeof(float);
+      snprintf(desc, sizeof desc,
+               "fused matmul tier 2: tcgen05 128x256x64, %s-major A, %s-major B, mainloop %d, epilogue README graph (loss + 2 column sums + 2 tiles%s), grid %d",
+               plan->cfg.a_mn ? "M" : "K", plan->cfg.b_mn ? "N" : "K", plan->cfg.ml, with_e ? ", E1/E2" : "", plan->cfg.grid);
+      plan->description = desc;
+      *out = guard.release();
+      return HE_OK;
+    }
+  }
+
+  // (3) interpreter tier: any pointwise epilogue without reductions
+  {
+    PwCompileOptions opt;
+    opt.acc_node = mm;
+    opt.fuse_fma = true;
+    opt.epilogue = true;
+    HE_TRY(compile_pointwise(g, opt, &plan->prog));
+    if (plan->prog.prog.n_reductions > 0)
+      HE_FAIL(HE_ERR_UNSUPPORTED, "fused matmul: this epilogue contains a reduction that matches no hand-written kernel");
+    if (plan->prog.has_bool_io) HE_FAIL(HE_ERR_UNSUPPORTED, "fused matmul: bool tensors in the epilogue are not supported");
+    if (tier_only) { *tier_only = 1; return HE_OK; }
+    plan->kind = EpiKind::Program;
+    finish_tiles();
+    snprintf(desc, sizeof desc,
+             "fused matmul tier 1: tcgen05 128x256x64, %s-major A, %s-major B, mainloop %d, interpreted epilogue (%d instr), grid %d",
+             plan->cfg.a_mn ? "M" : "K", plan->cfg.b_mn ? "N" : "K", plan->cfg.ml, plan->prog.prog.n_instr, plan->cfg.grid);
+    plan->description = desc;
+    *out = guard.release();
+    return HE_OK;
+  }
+}
+
+}  // namespace he

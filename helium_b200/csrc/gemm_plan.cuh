@@ -1,0 +1,26 @@
+// Host-side interface between the fused-matmul planner and the kernel instantiations.
+#pragma once
+#include "gemm_sm100.cuh"
+
+namespace he {
+
+struct GemmLaunchCfg {
+  int bn;        // 256 or 128
+  bool a_mn;     // A operand is M-major in global memory ([K, M] row-major)
+  bool b_mn;     // B operand is N-major in global memory ([K, N] row-major, the helium layout)
+  int ml;        // MainloopKind
+  int grid;
+};
+
+// One function per epilogue family; each switches over the instantiated (bn, majors, ml) set and
+// returns HE_ERR_UNSUPPORTED for combinations that were not compiled in.
+int32_t launch_gemm_flex(const GemmLaunchCfg& cfg, const GemmParams<EpiFlexParams>& p, cudaStream_t stream);
+int32_t launch_gemm_c3(const GemmLaunchCfg& cfg, const GemmParams<EpiC3Params>& p, cudaStream_t stream);
+int32_t launch_gemm_program(const GemmLaunchCfg& cfg, const GemmParams<EpiProgramParams>& p, cudaStream_t stream);
+int32_t launch_colsum_finalize(const float* partials, float* out, int batch, int tiles_m, int N, cudaStream_t stream);
+int32_t launch_scalar_finalize(const float* partials, float* out, int n, cudaStream_t stream);
+// SIMT matmul: f32 operands, or 2-byte operands whose shapes break the TMA alignment rules
+int32_t launch_sgemm(const void* a, const void* b, void* c, int in_dt, int out_dt, int batch, int M, int N, int K,
+                     bool a_mn, bool b_mn, const void* bias, int bias_dt, int act, cudaStream_t stream);
+
+}  // namespace he

@@ -1,0 +1,649 @@
+// tcgen05 / TMEM / TMA GEMM core for sm_100a with mainloop and epilogue fusion (hot-path rows
+// G0-G3, F1-F2).
+//
+// What it replaces: the sm_80 `mma.sync` + `cp.async` CuTe kernel the reference's generator emits
+// (helium-kernel-generator/templates/matmul/sm80.cu:202-274, src/generators/matmul/sm80.rs:551-695)
+// and the sm_90a WGMMA template of the playground (helium-playground/src/templates/matmul.cu).
+// Nothing is shared with either: one persistent CTA per SM, warp-specialised --
+//   warp 0        TMA producer: A / B (/ mask) tiles, 128-byte swizzle, STAGES-deep mbarrier ring
+//   warp 1        single-thread tcgen05.mma issuer, 128 x BN x 16 per instruction, f32 accumulators
+//                 in TMEM, two accumulator buffers so the epilogue of tile i overlaps tile i+1
+//   warps 2..     epilogue: tcgen05.ld 32x32b -> registers -> fused functor -> global
+//   last 4 warps  (mainloop fusion only) rewrite the A tile in shared memory between TMA arrival
+//                 and MMA issue, then fence.proxy.async + mbarrier arrive
+// Operands may be K-major or MN-major in global memory; the transposed case only changes the TMA
+// box and the shared-memory descriptor, no data is moved.
+#pragma once
+#include "device_utils.cuh"
+#include "pointwise_interp.cuh"
+#include "sm100_ptx.cuh"
+
+namespace he {
+
+constexpr int kBM = 128;
+constexpr int kBK = 64;                       // 64 bf16 = one 128-byte swizzle row
+constexpr int kATileBytes = kBM * kBK * 2;    // 16 KiB
+constexpr int kUmmaK = 16;
+
+enum MainloopKind : int { ML_NONE = 0, ML_RELU = 1, ML_MASK = 2, ML_RELU_MASK = 3 };
+enum ActKind : int { ACT_NONE = 0, ACT_RELU = 1, ACT_GELU = 2, ACT_TANH = 3 };
+enum GateKind : int { GATE_NONE = 0, GATE_MUL = 1, GATE_DGELU = 2, GATE_DRELU = 3, GATE_DTANH = 4 };
+
+struct GemmCore {
+  int M, N, K, batch;
+  int tiles_m, tiles_n, num_tiles, k_blocks;
+  int ab_format;  // 0 = f16, 1 = bf16
+  DeviceStatus* status;
+};
+
+struct TileInfo {
+  int m0, n0, b, tile_m, tile_n, tile_idx;
+};
+
+// ---- row-segment load / store helpers (one thread owns CH consecutive columns of one row) -------
+template <int CH>
+__device__ __forceinline__ void load_row(const void* base, int dt, size_t elem_off, int nvalid, bool vec, float (&o)[CH]) {
+  if (dt == HE_F32) {
+    const float* p = reinterpret_cast<const float*>(base) + elem_off;
+    if (vec && nvalid == CH) {
+#pragma unroll
+      for (int i = 0; i < CH / 4; ++i) {
+        const float4 v = __ldg(reinterpret_cast<const float4*>(p) + i);
+        o[4 * i] = v.x; o[4 * i + 1] = v.y; o[4 * i + 2] = v.z; o[4 * i + 3] = v.w;
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < CH; ++i) o[i] = i < nvalid ? __ldg(p + i) : 0.0f;
+    }
+  } else {
+    const unsigned short* p = reinterpret_cast<const unsigned short*>(base) + elem_off;
+    if (vec && nvalid == CH && dt == HE_BF16) {
+#pragma unroll
+      for (int i = 0; i < CH / 8; ++i) {
+        const uint4 v = __ldg(reinterpret_cast<const uint4*>(p) + i);
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          o[8 * i + 2 * j] = __uint_as_float(w[j] << 16);
+          o[8 * i + 2 * j + 1] = __uint_as_float(w[j] & 0xffff0000u);
+        }
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < CH; ++i) {
+        const uint32_t h = i < nvalid ? (uint32_t)__ldg(p + i) : 0u;
+        o[i] = dt == HE_BF16 ? bf16_bits_to_f32(h) : f16_bits_to_f32(h);
+      }
+    }
+  }
+}
+
+template <int CH>
+__device__ __forceinline__ void store_row(void* base, int dt, size_t elem_off, int nvalid, bool vec, const float (&v)[CH]) {
+  if (dt == HE_F32) {
+    float* p = reinterpret_cast<float*>(base) + elem_off;
+    if (vec && nvalid == CH) {
+#pragma unroll
+      for (int i = 0; i < CH / 4; ++i) reinterpret_cast<float4*>(p)[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+    } else {
+#pragma unroll
+      for (int i = 0; i < CH; ++i)
+        if (i < nvalid) p[i] = v[i];
+    }
+  } else {
+    unsigned short* p = reinterpret_cast<unsigned short*>(base) + elem_off;
+    if (vec && nvalid == CH && dt == HE_BF16) {
+#pragma unroll
+      for (int i = 0; i < CH / 8; ++i) {
+        uint4 w;
+        w.x = f32x2_to_bf16x2(v[8 * i], v[8 * i + 1]);
+        w.y = f32x2_to_bf16x2(v[8 * i + 2], v[8 * i + 3]);
+        w.z = f32x2_to_bf16x2(v[8 * i + 4], v[8 * i + 5]);
+        w.w = f32x2_to_bf16x2(v[8 * i + 6], v[8 * i + 7]);
+        reinterpret_cast<uint4*>(p)[i] = w;
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < CH; ++i)
+        if (i < nvalid) p[i] = (unsigned short)(dt == HE_BF16 ? f32_to_bf16_bits(v[i]) : f32_to_f16_bits(v[i]));
+    }
+  }
+}
+
+// Column sums over the 32 lanes (= 32 rows) of a warp for CH per-lane values.  Recursive halving
+// (CH - 1 shuffles) followed by 5 - log2(CH) all-reduce steps.  Afterwards the lanes whose low
+// (5 - log2 CH) bits are zero hold the total of column (lane >> (5 - log2 CH)); this helper writes
+// those totals to dst[0 .. CH).
+template <int CH>
+__device__ __forceinline__ void warp_colsum_store(float (&v)[CH], float* dst) {
+  const int lane = threadIdx.x & 31;
+  constexpr int kLog = CH == 32 ? 5 : CH == 16 ? 4 : 3;
+  int bit = 16;
+#pragma unroll
+  for (int s = CH / 2; s >= 1; s >>= 1) {
+    const bool upper = (lane & bit) != 0;
+#pragma unroll
+    for (int i = 0; i < s; ++i) {
+      const float send = upper ? v[i] : v[i + s];
+      const float keep = upper ? v[i + s] : v[i];
+      v[i] = keep + __shfl_xor_sync(0xffffffffu, send, bit);
+    }
+    bit >>= 1;
+  }
+#pragma unroll
+  for (int b = (1 << (5 - kLog)) >> 1; b >= 1; b >>= 1) v[0] += __shfl_xor_sync(0xffffffffu, v[0], b);
+  if ((lane & ((1 << (5 - kLog)) - 1)) == 0) dst[lane >> (5 - kLog)] = v[0];
+}
+
+// =================================================================================================
+// Epilogue functors.  Interface:
+//   Params                      POD passed by value inside the kernel parameter block
+//   kColReductions              number of per-column Sum reductions (shared scratch rows)
+//   State                       per-thread state that lives across the chunks of one tile
+//   chunk(...)                  called once per (row, 32-column chunk) with the f32 accumulators
+//   tile_end(...)               called by every epilogue thread after the accumulator was released
+// Column partial layout in the workspace: [reduction][batch][tile_m][N]; scalar partials: [tile].
+// =================================================================================================
+struct EpiEnv {
+  const GemmCore* core;
+  float* scratch;      // shared: [kColReductions][4 quadrants][BN] then [n_epi_warps] scalars
+  int bn;
+  int n_epi_threads;
+  int epi_tid;         // 0 .. n_epi_threads-1
+  int quadrant;        // TMEM lane quadrant of this warp (row block within the tile)
+  int epi_warp;
+};
+
+__device__ __forceinline__ void col_partials_flush(const EpiEnv& env, const TileInfo& t, int nred, float* const* partials) {
+  ptx::named_barrier_sync(1, env.n_epi_threads);
+  const GemmCore& c = *env.core;
+  for (int col = env.epi_tid; col < env.bn; col += env.n_epi_threads) {
+    const int gc = t.n0 + col;
+    if (gc < c.N) {
+      for (int r = 0; r < nred; ++r) {
+        const float* s = env.scratch + (size_t)r * 4 * env.bn;
+        const float v = ((s[col] + s[env.bn + col]) + s[2 * env.bn + col]) + s[3 * env.bn + col];
+        partials[r][((size_t)t.b * c.tiles_m + t.tile_m) * c.N + gc] = v;
+      }
+    }
+  }
+  ptx::named_barrier_sync(1, env.n_epi_threads);
+}
+
+// ---- EpiFlex: bias / residual / activation / gate / column sum ----------------------------------
+//   t = acc (+ bias[col]) (+ resid[row, col]);  Z = t (optional);  y = act(t);
+//   y *= gate(G[row, col]) (optional);  Y = y;  colsum over {nothing, resid, y}
+struct EpiFlexParams {
+  void* out; void* out_z;
+  const void* bias; const void* resid; const void* gate_in;
+  float* colsum_partials;
+  int out_dt, z_dt, bias_dt, resid_dt, gate_dt;
+  int act, gate, colsum_src;  // colsum_src: 0 none, 1 resid, 2 y
+  int vec_ok;
+};
+
+struct EpiFlex {
+  using Params = EpiFlexParams;
+  static constexpr int kColReductions = 1;
+  static constexpr int kChunk = 32;
+  struct State {};
+  __device__ static void tile_begin(State&) {}
+  __device__ static float activation(int act, float x) {
+    switch (act) {
+      case ACT_RELU: return fmaxf(x, 0.0f);
+      case ACT_GELU: return pw_gelu(x);
+      case ACT_TANH: return tanhf(x);
+      default: return x;
+    }
+  }
+  __device__ static float gate_fn(int g, float x) {
+    switch (g) {
+      case GATE_DGELU: return pw_dgelu(x);
+      case GATE_DRELU: return x > 0.0f ? 1.0f : 0.0f;
+      case GATE_DTANH: return 1.0f - x * x;  // x is tanh(z)
+      default: return x;
+    }
+  }
+  __device__ static void chunk(const Params& p, const EpiEnv& env, const TileInfo& t, State&, int row, int col, float (&v)[kChunk]) {
+    const GemmCore& c = *env.core;
+    const int grow = t.m0 + row, gcol = t.n0 + col;
+    const int nvalid = grow < c.M ? max(0, min(kChunk, c.N - gcol)) : 0;
+    const size_t off = ((size_t)t.b * c.M + grow) * c.N + gcol;
+    const bool vec = p.vec_ok != 0;
+    float aux[kChunk];
+    if (p.bias) {
+#pragma unroll
+      for (int i = 0; i < kChunk; ++i) v[i] += (gcol + i < c.N) ? load_param_as_f32(p.bias, p.bias_dt, gcol + i) : 0.0f;
+    }
+    if (p.resid) {
+      load_row<kChunk>(p.resid, p.resid_dt, off, nvalid, vec, aux);
+#pragma unroll
+      for (int i = 0; i < kChunk; ++i) v[i] += aux[i];
+      if (p.colsum_src == 1) warp_colsum_store<kChunk>(aux, env.scratch + env.quadrant * env.bn + col);
+    }
+    if (p.out_z && nvalid > 0) store_row<kChunk>(p.out_z, p.z_dt, off, nvalid, vec, v);
+    if (p.act != ACT_NONE) {
+#pragma unroll
+      for (int i = 0; i < kChunk; ++i) v[i] = activation(p.act, v[i]);
+    }
+    if (p.gate != GATE_NONE) {
+      load_row<kChunk>(p.gate_in, p.gate_dt, off, nvalid, vec, aux);
+#pragma unroll
+      for (int i = 0; i < kChunk; ++i) v[i] *= gate_fn(p.gate, aux[i]);
+    }
+    if (nvalid > 0) store_row<kChunk>(p.out, p.out_dt, off, nvalid, vec, v);
+    if (p.colsum_src == 2) {
+#pragma unroll
+      for (int i = 0; i < kChunk; ++i) v[i] = i < nvalid ? v[i] : 0.0f;
+      warp_colsum_store<kChunk>(v, env.scratch + env.quadrant * env.bn + col);
+    }
+  }
+  __device__ static void tile_end(const Params& p, const EpiEnv& env, const TileInfo& t, State&) {
+    if (p.colsum_src != 0) {
+      float* parts[1] = {p.colsum_partials};
+      col_partials_flush(env, t, 1, parts);
+    }
+  }
+};
+
+// ---- EpiC3: the fused graph of the reference README (README.md:33-79) ---------------------------
+//   z1 = C (+E1) + b1[col];  u = relu(z1);      z2 = C (+E2) + b2[col];  t = tanh(z2)
+//   h  = (1 - u) * Mk + u * t;   d = h - Y;   l = d*d * inv_n;   LOSS = sum_all(l)
+//   g  = d * 2 * inv_n;          gt = (u * g) * (1 - t*t);       DB2 = colsum(gt)
+//   gu = g * t - g * Mk;         gz1 = z1 > 0 ? gu : 0;          DB1 = colsum(gz1)
+struct EpiC3Params {
+  const void* mask; const void* y; const void* b1; const void* b2; const void* e1; const void* e2;
+  void* out_gt; void* out_gz1;
+  float* db2_partials; float* db1_partials; float* loss_partials;
+  float inv_n;       // MulConstant operand of README node 38 / 45
+  int full_dt;       // dtype of mask / y / e1 / e2 / gt / gz1
+  int vec_dt;        // dtype of b1 / b2
+  int vec_ok;
+};
+
+struct EpiC3 {
+  using Params = EpiC3Params;
+  static constexpr int kColReductions = 2;
+  static constexpr int kChunk = 16;
+  struct State { float loss; };
+  __device__ static void tile_begin(State& s) { s.loss = 0.0f; }
+  __device__ static void chunk(const Params& p, const EpiEnv& env, const TileInfo& t, State& st, int row, int col, float (&v)[kChunk]) {
+    const GemmCore& c = *env.core;
+    const int grow = t.m0 + row, gcol = t.n0 + col;
+    const int nvalid = grow < c.M ? max(0, min(kChunk, c.N - gcol)) : 0;
+    const size_t off = ((size_t)t.b * c.M + grow) * c.N + gcol;
+    const bool vec = p.vec_ok != 0;
+    float tnh[kChunk], a[kChunk];
+    if (p.e2) {
+      load_row<kChunk>(p.e2, p.full_dt, off, nvalid, vec, a);
+#pragma unroll
+      for (int i = 0; i < kChunk; ++i) tnh[i] = v[i] + a[i];
+    } else {
+#pragma unroll
+      for (int i = 0; i < kChunk; ++i) tnh[i] = v[i];
+    }
+    if (p.e1) {
+      load_row<kChunk>(p.e1, p.full_dt, off, nvalid, vec, a);
+#pragma unroll
+      for (int i = 0; i < kChunk; ++i) v[i] += a[i];
+    }
+#pragma unroll
+    for (int i = 0; i < kChunk; ++i) {
+      const bool ok = gcol + i < c.N;
+      const float b1 = ok ? load_param_as_f32(p.b1, p.vec_dt, gcol + i) : 0.0f;
+      const float b2 = ok ? load_param_as_f32(p.b2, p.vec_dt, gcol + i) : 0.0f;
+      v[i] += b1;                       // z1
+      tnh[i] = tanhf(tnh[i] + b2);      // t
+    }
+    float mk[kChunk];
+    load_row<kChunk>(p.mask, p.full_dt, off, nvalid, vec, mk);
+    load_row<kChunk>(p.y, p.full_dt, off, nvalid, vec, a);
+    float loss = 0.0f;
+#pragma unroll
+    for (int i = 0; i < kChunk; ++i) {
+      const float z1 = v[i], tt = tnh[i], m = mk[i];
+      const float u = fmaxf(z1, 0.0f);
+      const float h = (1.0f - u) * m + u * tt;
+      const float d = h - a[i];
+      const float l = (d * d) * p.inv_n;
+      const float g = (d * 2.0f) * p.inv_n;
+      const float gt = (u * g) * (1.0f - tt * tt);
+      const float gu = g * tt + (-(g * m));
+      const float gz1 = z1 > 0.0f ? gu : 0.0f;
+      const bool ok = i < nvalid;
+      loss += ok ? l : 0.0f;
+      v[i] = ok ? gt : 0.0f;
+      tnh[i] = ok ? gz1 : 0.0f;
+    }
+    st.loss += loss;
+    if (nvalid > 0) {
+      store_row<kChunk>(p.out_gt, p.full_dt, off, nvalid, vec, v);
+      store_row<kChunk>(p.out_gz1, p.full_dt, off, nvalid, vec, tnh);
+    }
+    warp_colsum_store<kChunk>(v, env.scratch + env.quadrant * env.bn + col);
+    warp_colsum_store<kChunk>(tnh, env.scratch + (4 + env.quadrant) * env.bn + col);
+  }
+  __device__ static void tile_end(const Params& p, const EpiEnv& env, const TileInfo& t, State& st) {
+    float l = st.loss;
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) l += __shfl_down_sync(0xffffffffu, l, off);
+    float* scal = env.scratch + (size_t)kColReductions * 4 * env.bn;
+    if ((threadIdx.x & 31) == 0) scal[env.epi_warp] = l;
+    float* parts[2] = {p.db2_partials, p.db1_partials};
+    col_partials_flush(env, t, 2, parts);   // its first barrier also publishes scal[]
+    if (env.epi_tid == 0) {
+      float tot = 0.0f;
+      for (int w = 0; w < env.n_epi_threads / 32; ++w) tot += scal[w];
+      p.loss_partials[t.tile_idx] = tot;
+    }
+    // scal[] is rewritten only after the next tile's flush barrier pair, which orders it after this read
+  }
+};
+
+// ---- EpiProgram: generic tier, the pointwise interpreter fed with accumulator values -------------
+struct EpiProgramParams {
+  PwProgram prog;  // by value: lives in the kernel parameter block (constant bank)
+};
+struct EpiProgram {
+  using Params = EpiProgramParams;
+  static constexpr int kColReductions = 0;
+  static constexpr int kChunk = 32;
+  struct State {};
+  __device__ static void tile_begin(State&) {}
+  __device__ static void chunk(const Params& p, const EpiEnv& env, const TileInfo& t, State&, int row, int col, float (&v)[kChunk]) {
+    const GemmCore& c = *env.core;
+    const int grow = t.m0 + row, gcol = t.n0 + col;
+    if (grow >= c.M) return;
+    const uint32_t base = (uint32_t)(((size_t)t.b * c.M + grow) * c.N + gcol);
+    const bool row_aligned = (c.N & 3) == 0;
+#pragma unroll 1
+    for (int i = 0; i < kChunk; i += 4) {
+      const int nv = max(0, min(4, c.N - (gcol + i)));
+      if (nv == 0) break;
+      const float acc4[4] = {v[i], v[i + 1], v[i + 2], v[i + 3]};
+      if (row_aligned) {
+        pw_run<4>(p.prog, base + i, nv, acc4, nullptr);
+      } else {
+        for (int j = 0; j < nv; ++j) pw_run<1>(p.prog, base + i + j, 1, acc4 + j, nullptr);
+      }
+    }
+  }
+  __device__ static void tile_end(const Params&, const EpiEnv&, const TileInfo&, State&) {}
+};
+
+// =================================================================================================
+// The kernel
+// =================================================================================================
+template <class EP>
+struct alignas(64) GemmParams {
+  CUtensorMap tma_a, tma_b, tma_mask;
+  GemmCore core;
+  EP epi;
+};
+
+template <int BN, int STAGES, int ML, int N_COLRED>
+struct GemmSmem {
+  static constexpr int kBTileBytes = BN * kBK * 2;
+  static constexpr bool kHasMask = (ML & ML_MASK) != 0;
+  static constexpr int off_a = 0;
+  static constexpr int off_b = off_a + STAGES * kATileBytes;
+  static constexpr int off_mask = off_b + STAGES * kBTileBytes;
+  static constexpr int off_scratch = off_mask + (kHasMask ? STAGES * kATileBytes : 0);
+  static constexpr int scratch_bytes = (N_COLRED * 4 * BN + 16) * 4;
+  static constexpr int off_bar = off_scratch + scratch_bytes;
+  static constexpr int n_bars = 3 * STAGES + 4;
+  static constexpr int off_misc = off_bar + n_bars * 8;
+  static constexpr int total = off_misc + 16;
+  static constexpr int dynamic_bytes = total + 1024;  // slack for the manual 1024-byte alignment
+};
+
+template <int CH>
+__device__ __forceinline__ void tmem_ld_chunk(uint32_t taddr, float (&v)[CH]) {
+  if constexpr (CH == 32) {
+    uint32_t r[32];
+    ptx::tmem_ld_32x32(taddr, r);
+    ptx::tmem_ld_wait();
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+  } else {
+    static_assert(CH == 16, "chunk width");
+    uint32_t r[16];
+    ptx::tmem_ld_32x16(taddr, r);
+    ptx::tmem_ld_wait();
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+  }
+}
+
+template <int BN, int STAGES, bool A_MN, bool B_MN, int ML, int NE_WARPS, class Epi>
+__global__ void __launch_bounds__(32 * (2 + NE_WARPS + (ML != ML_NONE ? 4 : 0)), 1)
+gemm_tcgen05_kernel(const __grid_constant__ GemmParams<typename Epi::Params> p) {
+  using SM = GemmSmem<BN, STAGES, ML, Epi::kColReductions>;
+  constexpr int kXformWarp0 = 2 + NE_WARPS;
+  constexpr int kTmemCols = 2 * BN <= 32 ? 32 : 2 * BN <= 64 ? 64 : 2 * BN <= 128 ? 128 : 2 * BN <= 256 ? 256 : 512;
+  constexpr int CH = Epi::kChunk;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  const uint32_t smem_base = ptx::smem_u32(smem);
+  const uint32_t bar0 = smem_base + SM::off_bar;
+  auto bar_full = [&](int s) { return bar0 + 8u * s; };
+  auto bar_empty = [&](int s) { return bar0 + 8u * (STAGES + s); };
+  auto bar_xform = [&](int s) { return bar0 + 8u * (2 * STAGES + s); };
+  auto bar_tmem_full = [&](int a) { return bar0 + 8u * (3 * STAGES + a); };
+  auto bar_tmem_empty = [&](int a) { return bar0 + 8u * (3 * STAGES + 2 + a); };
+  volatile uint32_t* tmem_holder = reinterpret_cast<volatile uint32_t*>(smem + SM::off_misc);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + SM::off_misc + 4);
+  float* scratch = reinterpret_cast<float*>(smem + SM::off_scratch);
+
+  const GemmCore& c = p.core;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    for (int s = 0; s < STAGES; ++s) {
+      ptx::mbar_init(bar_full(s), 1);
+      ptx::mbar_init(bar_empty(s), 1);
+      ptx::mbar_init(bar_xform(s), 128);
+    }
+    for (int a = 0; a < 2; ++a) {
+      ptx::mbar_init(bar_tmem_full(a), 1);
+      ptx::mbar_init(bar_tmem_empty(a), NE_WARPS * 32);
+    }
+    ptx::fence_mbar_init();
+  }
+  if (warp == 0 && lane == 0) {
+    ptx::prefetch_tmap(&p.tma_a);
+    ptx::prefetch_tmap(&p.tma_b);
+    if (SM::kHasMask) ptx::prefetch_tmap(&p.tma_mask);
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc(ptx::smem_u32(const_cast<uint32_t*>(tmem_holder)), kTmemCols);
+    ptx::tmem_relinquish();
+  }
+  ptx::tcgen05_fence_before();
+  __syncthreads();
+  ptx::tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+
+  auto decode_tile = [&](int tile) {
+    TileInfo t;
+    t.tile_idx = tile;
+    const int per_batch = c.tiles_m * c.tiles_n;
+    t.b = tile / per_batch;
+    const int r = tile - t.b * per_batch;
+    t.tile_n = r / c.tiles_m;
+    t.tile_m = r - t.tile_n * c.tiles_m;
+    t.m0 = t.tile_m * kBM;
+    t.n0 = t.tile_n * BN;
+    return t;
+  };
+
+  if (warp == 0) {
+    // ===================== TMA producer =====================
+    if (lane == 0) {
+      constexpr uint32_t kStageBytes = kATileBytes + SM::kBTileBytes + (SM::kHasMask ? kATileBytes : 0);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool alive = true;
+      for (int tile = blockIdx.x; alive && tile < c.num_tiles; tile += gridDim.x) {
+        const TileInfo t = decode_tile(tile);
+        for (int kb = 0; kb < c.k_blocks; ++kb) {
+          if (!ptx::mbar_wait(bar_empty(stage), phase ^ 1u, abort_flag, c.status, 1, stage)) { alive = false; break; }
+          ptx::mbar_arrive_expect_tx(bar_full(stage), kStageBytes);
+          const int k0 = kb * kBK;
+          const uint32_t a_dst = smem_base + SM::off_a + stage * kATileBytes;
+          const uint32_t b_dst = smem_base + SM::off_b + stage * SM::kBTileBytes;
+          if (A_MN) {
+#pragma unroll
+            for (int j = 0; j < kBM / 64; ++j)
+              ptx::tma_load_3d(a_dst + j * (kBK * 128), &p.tma_a, bar_full(stage), t.m0 + 64 * j, k0, t.b);
+          } else {
+            ptx::tma_load_3d(a_dst, &p.tma_a, bar_full(stage), k0, t.m0, t.b);
+          }
+          if (SM::kHasMask) {
+            const uint32_t m_dst = smem_base + SM::off_mask + stage * kATileBytes;
+            if (A_MN) {
+#pragma unroll
+              for (int j = 0; j < kBM / 64; ++j)
+                ptx::tma_load_3d(m_dst + j * (kBK * 128), &p.tma_mask, bar_full(stage), t.m0 + 64 * j, k0, t.b);
+            } else {
+              ptx::tma_load_3d(m_dst, &p.tma_mask, bar_full(stage), k0, t.m0, t.b);
+            }
+          }
+          if (B_MN) {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j)
+              ptx::tma_load_3d(b_dst + j * (kBK * 128), &p.tma_b, bar_full(stage), t.n0 + 64 * j, k0, t.b);
+          } else {
+            ptx::tma_load_3d(b_dst, &p.tma_b, bar_full(stage), k0, t.n0, t.b);
+          }
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ===================== MMA issuer =====================
+    if (lane == 0) {
+      const uint32_t idesc = ptx::make_idesc_f16(c.ab_format, A_MN ? 1 : 0, B_MN ? 1 : 0, kBM, BN);
+      // K-major: 8-row groups 1024 B apart (SBO), K advances 32 B inside the swizzle row.
+      // MN-major: 64-element blocks kBK*128 B apart (LBO), 8-k groups 1024 B apart (SBO),
+      //           K advances two k-groups = 2048 B per MMA.
+      constexpr uint32_t a_lbo = A_MN ? kBK * 128 : 16, b_lbo = B_MN ? kBK * 128 : 16;
+      constexpr uint32_t a_kadv = A_MN ? 2048 : 32, b_kadv = B_MN ? 2048 : 32;
+      int stage = 0;
+      uint32_t phase = 0;
+      int it = 0;
+      bool alive = true;
+      for (int tile = blockIdx.x; alive && tile < c.num_tiles; tile += gridDim.x, ++it) {
+        const int acc = it & 1;
+        const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
+        if (!ptx::mbar_wait(bar_tmem_empty(acc), acc_phase ^ 1u, abort_flag, c.status, 2, acc)) { alive = false; break; }
+        ptx::tcgen05_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
+        for (int kb = 0; kb < c.k_blocks; ++kb) {
+          const uint32_t ready = (ML != ML_NONE) ? bar_xform(stage) : bar_full(stage);
+          if (!ptx::mbar_wait(ready, phase, abort_flag, c.status, 3, stage)) { alive = false; break; }
+          ptx::tcgen05_fence_after();
+          const uint32_t a_addr = smem_base + SM::off_a + stage * kATileBytes;
+          const uint32_t b_addr = smem_base + SM::off_b + stage * SM::kBTileBytes;
+#pragma unroll
+          for (int k = 0; k < kBK / kUmmaK; ++k) {
+            const uint64_t adesc = ptx::make_smem_desc_sw128(a_addr + k * a_kadv, a_lbo, 1024);
+            const uint64_t bdesc = ptx::make_smem_desc_sw128(b_addr + k * b_kadv, b_lbo, 1024);
+            ptx::umma_f16(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          ptx::umma_commit(bar_empty(stage));   // frees the smem stage when these MMAs retire
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+        if (alive) ptx::umma_commit(bar_tmem_full(acc));
+      }
+    }
+  } else if (warp < kXformWarp0) {
+    // ===================== epilogue =====================
+    EpiEnv env;
+    env.core = &c;
+    env.scratch = scratch;
+    env.bn = BN;
+    env.n_epi_threads = NE_WARPS * 32;
+    env.epi_warp = warp - 2;
+    env.epi_tid = env.epi_warp * 32 + lane;
+    env.quadrant = warp & 3;  // a warp may only touch TMEM lanes 32*(warp%4) .. +31
+    constexpr int kColsPerWarp = BN / (NE_WARPS / 4);
+    const int col_begin = (env.epi_warp / 4) * kColsPerWarp;
+    int it = 0;
+    bool dead = false;
+    for (int tile = blockIdx.x; tile < c.num_tiles; tile += gridDim.x, ++it) {
+      const int acc = it & 1;
+      const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
+      const TileInfo t = decode_tile(tile);
+      // After an abandoned wait the thread keeps walking the tile list without touching TMEM so
+      // that the named barriers inside tile_end() still see every epilogue thread.
+      if (!dead && !ptx::mbar_wait(bar_tmem_full(acc), acc_phase, abort_flag, c.status, 4, acc)) dead = true;
+      typename Epi::State st;
+      Epi::tile_begin(st);
+      if (!dead) {
+        ptx::tcgen05_fence_after();
+        const int row = env.quadrant * 32 + lane;
+#pragma unroll 1
+        for (int col = col_begin; col < col_begin + kColsPerWarp; col += CH) {
+          if (t.n0 + col >= c.N) break;
+          float v[CH];
+          const uint32_t taddr = tmem_base + ((uint32_t)(env.quadrant * 32) << 16) + (uint32_t)(acc * BN + col);
+          tmem_ld_chunk<CH>(taddr, v);
+          Epi::chunk(p.epi, env, t, st, row, col, v);
+        }
+        ptx::tcgen05_fence_before();
+        ptx::mbar_arrive(bar_tmem_empty(acc));
+      }
+      Epi::tile_end(p.epi, env, t, st);
+    }
+  } else {
+    // ===================== mainloop transform =====================
+    if (ML != ML_NONE) {
+      const int tt = (warp - kXformWarp0) * 32 + lane;  // 0..127
+      int stage = 0;
+      uint32_t phase = 0;
+      bool alive = true;
+      for (int tile = blockIdx.x; alive && tile < c.num_tiles; tile += gridDim.x) {
+        for (int kb = 0; kb < c.k_blocks; ++kb) {
+          if (!ptx::mbar_wait(bar_full(stage), phase, abort_flag, c.status, 5, stage)) { alive = false; break; }
+          uint4* a = reinterpret_cast<uint4*>(smem + SM::off_a + stage * kATileBytes);
+          const uint4* mk = reinterpret_cast<const uint4*>(smem + SM::off_mask + stage * kATileBytes);
+          // A and the mask were loaded with the same box and swizzle, so equal smem offsets hold
+          // the same (row, k) element: the rewrite is position-wise.
+#pragma unroll
+          for (int i = 0; i < kATileBytes / 16 / 128; ++i) {
+            const int idx = tt + i * 128;
+            uint4 va = a[idx];
+            __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&va);
+            if (ML & ML_RELU) {
+              const __nv_bfloat162 z = __float2bfloat162_rn(0.0f);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) h[j] = __hmax2(h[j], z);
+            }
+            if (ML & ML_MASK) {
+              uint4 vm = mk[idx];
+              const __nv_bfloat162* hm = reinterpret_cast<const __nv_bfloat162*>(&vm);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) h[j] = __hmul2(h[j], hm[j]);
+            }
+            a[idx] = va;
+          }
+          ptx::fence_proxy_async_smem();
+          ptx::mbar_arrive(bar_xform(stage));
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+  }
+
+  // ---- teardown: every thread arrives here, also after an abandoned wait -----------------------
+  ptx::tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    ptx::tcgen05_fence_after();
+    ptx::tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+}  // namespace he

@@ -1,0 +1,110 @@
+// Internal declarations shared by the translation units of libhelium_b200.so.
+#pragma once
+#include <cuda_runtime.h>
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+#include <cstring>
+#include <string>
+#include <vector>
+
+#include "helium_b200.h"
+
+namespace he {
+
+// ---- errors -----------------------------------------------------------------------------------
+void set_error(const char* fmt, ...);
+#define HE_FAIL(code, ...)        \
+  do {                            \
+    ::he::set_error(__VA_ARGS__); \
+    return (code);                \
+  } while (0)
+#define HE_CUDA(expr)                                                                     \
+  do {                                                                                    \
+    cudaError_t e__ = (expr);                                                             \
+    if (e__ != cudaSuccess)                                                               \
+      HE_FAIL(HE_ERR_CUDA, "%s failed: %s (%s:%d)", #expr, cudaGetErrorString(e__), __FILE__, \
+              __LINE__);                                                                  \
+  } while (0)
+#define HE_TRY(expr)           \
+  do {                         \
+    int32_t s__ = (expr);      \
+    if (s__ != HE_OK) return s__; \
+  } while (0)
+
+// ---- dtype helpers ----------------------------------------------------------------------------
+enum class DClass { Float, Int, Bool };
+inline DClass dclass(int32_t dt) {
+  return dt == HE_U32 ? DClass::Int : dt == HE_BOOL ? DClass::Bool : DClass::Float;
+}
+inline int dtype_bytes(int32_t dt) {  // bytes per element; 0 for bit-packed bool
+  switch (dt) {
+    case HE_F16: case HE_BF16: return 2;
+    case HE_F32: case HE_U32: return 4;
+    default: return 0;
+  }
+}
+inline bool dtype_valid(int32_t dt) { return dt >= HE_F16 && dt <= HE_BOOL; }
+const char* dtype_name(int32_t dt);
+
+inline int64_t num_elements(const he_node& n) {
+  int64_t c = 1;
+  for (int i = 0; i < n.rank; ++i) c *= n.shape[i];
+  return c;
+}
+inline size_t storage_bytes(int32_t dt, int64_t elems) {
+  if (dt == HE_BOOL) return size_t((elems + 31) / 32) * 4;
+  return size_t(elems) * dtype_bytes(dt);
+}
+
+// ---- device status block ----------------------------------------------------------------------
+// Word 0: 0 = fine, otherwise (site << 16 | detail) of the first bounded wait that gave up.
+struct DeviceStatus {
+  unsigned int code;
+  unsigned int block;
+  unsigned int aux0;
+  unsigned int aux1;
+};
+
+}  // namespace he
+
+struct he_ctx {
+  int device = 0;
+  int sm_count = 0;
+  int max_smem_optin = 0;
+  he::DeviceStatus* d_status = nullptr;  // device memory
+};
+
+// A plan may be created with a null context ("planning only": tier, tile shape and workspace can
+// be inspected, launching is refused); such plans assume the SM count of a B200.
+inline int ctx_sm_count(const he_ctx* c) { return c ? c->sm_count : 148; }
+
+// Base of every plan.  Immutable after creation except for the launch counter.
+struct he_plan {
+  he_ctx* ctx = nullptr;
+  size_t workspace_bytes = 0;
+  int last_launches = 0;
+  std::string description;
+  virtual ~he_plan() {}
+  virtual int32_t launch(const void* const* inputs, void* const* outputs, void* workspace,
+                         cudaStream_t stream) = 0;
+};
+
+namespace he {
+
+// ---- validated subgraph -----------------------------------------------------------------------
+struct Graph {
+  std::vector<he_node> nodes;
+  std::vector<int> inputs;   // node indices of HE_OP_INPUT, in order
+  std::vector<int> outputs;  // leaf node indices, in caller order
+};
+// Copies and validates a descriptor (operand indices, shapes, dtypes of every op).
+int32_t parse_graph(const he_graph_desc* desc, Graph* out);
+
+// planners (one per translation unit)
+int32_t plan_pointwise(he_ctx* ctx, const Graph& g, he_plan** out, int* tier_only);
+int32_t plan_permute(he_ctx* ctx, int rank, const int64_t* in_shape, const int64_t* out_strides,
+                     int32_t dtype, he_plan** out);
+int32_t plan_fused_matmul(he_ctx* ctx, const Graph& g, he_plan** out, int* tier_only);
+
+}  // namespace he

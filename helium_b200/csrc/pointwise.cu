@@ -1,0 +1,413 @@
+// Stand-alone pointwise kernels (hot-path rows P1-P4).
+//
+// The reference JIT-compiles one kernel per subgraph: one element per thread, scalar loads and a
+// `/`-`%` chain per broadcast or swap (helium/src/cuda/instr/pointwise/jit.rs:19-121, 616-729),
+// reductions through a shared-memory tree, warp shuffles and float atomics (jit.rs:402-458).
+// JIT is not available to this library, so a subgraph is served by one of two tiers:
+//   tier 2  hand-written kernels for catalogued shapes of graph -- today the
+//           "x * scale[c] + bias[c] (relu) + permutation" family, run by the tiled transpose kernel
+//           of permute.cu in a single pass over HBM;
+//   tier 1  a register-program interpreter (pointwise_interp.cuh): 4 consecutive elements per
+//           thread with 16-byte loads/stores where the operand is contiguous, strided views with
+//           precomputed magic-number division elsewhere.
+// Reductions are deterministic: a CTA (or a warp, for short groups) reduces its slice in a fixed
+// order; groups that span several CTAs write partials to the workspace and a second small kernel
+// folds them in index order (the reference's float atomics are order-dependent).
+#include "permute.cuh"
+#include "pointwise_interp.cuh"
+
+#include <algorithm>
+
+namespace he {
+
+constexpr int kPwThreads = 256;
+
+template <int V>
+__global__ void __launch_bounds__(kPwThreads) pw_elementwise_kernel(const __grid_constant__ PwProgram P) {
+  const uint32_t idx0 = (blockIdx.x * (uint32_t)kPwThreads + threadIdx.x) * V;
+  int nvalid = 0;
+  if (idx0 < P.n_elems) nvalid = min((uint32_t)V, P.n_elems - idx0);
+  if (V > 1 && nvalid == 0) return;  // V == 1 keeps whole warps alive for the bool ballot
+  pw_run<V>(P, idx0, nvalid, nullptr, nullptr);
+}
+
+struct PwReduceLaunch {
+  uint32_t num_groups;
+  uint32_t blocks_per_group;   // CTAs per group (block mode) -- 1 in warp mode
+  uint32_t chunk;              // elements of a group handled by one CTA
+  int warp_mode;               // 1: one warp per group, 8 groups per CTA
+  int red_ops[4];
+  int red_out_slot[4];
+  float* partials;             // [n_red][num_groups][blocks_per_group] when blocks_per_group > 1
+};
+
+// Reduction kernel.  Iteration space = [num_groups][group_size] (the reduce input, row-major with
+// the reduced dims trailing, jit.rs:137-162).
+__global__ void __launch_bounds__(kPwThreads) pw_reduce_kernel(const __grid_constant__ PwProgram P,
+                                                               const __grid_constant__ PwReduceLaunch L) {
+  __shared__ float sred[4][kPwThreads / 32];
+  float red[4];
+#pragma unroll
+  for (int s = 0; s < 4; ++s) red[s] = s < P.n_reductions ? pw_reduce_identity(L.red_ops[s]) : 0.0f;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (L.warp_mode) {
+    const uint32_t group = blockIdx.x * (kPwThreads / 32) + warp;
+    if (group >= L.num_groups) return;  // whole warp leaves together
+    const uint32_t base = group * P.group_size;
+    const uint32_t iters = (P.group_size + 31) / 32;
+    for (uint32_t it = 0; it < iters; ++it) {
+      const uint32_t e = it * 32 + lane;
+      pw_run<1>(P, base + e, e < P.group_size ? 1 : 0, nullptr, red);
+    }
+#pragma unroll
+    for (int s = 0; s < 4; ++s) {
+      if (s >= P.n_reductions) break;
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) red[s] = pw_reduce_combine(L.red_ops[s], red[s], __shfl_down_sync(0xffffffffu, red[s], off));
+      if (lane == 0) reinterpret_cast<float*>(P.out[L.red_out_slot[s]])[group] = red[s];
+    }
+    return;
+  }
+  const uint32_t group = blockIdx.x / L.blocks_per_group;
+  const uint32_t blk = blockIdx.x - group * L.blocks_per_group;
+  const uint32_t start = blk * L.chunk;
+  const uint32_t end = min(start + L.chunk, P.group_size);
+  const uint32_t base = group * P.group_size;
+  const uint32_t iters = (end - start + kPwThreads - 1) / kPwThreads;
+  for (uint32_t it = 0; it < iters; ++it) {
+    const uint32_t e = start + it * kPwThreads + threadIdx.x;
+    pw_run<1>(P, base + e, e < end ? 1 : 0, nullptr, red);
+  }
+#pragma unroll
+  for (int s = 0; s < 4; ++s) {
+    if (s >= P.n_reductions) break;
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) red[s] = pw_reduce_combine(L.red_ops[s], red[s], __shfl_down_sync(0xffffffffu, red[s], off));
+    if (lane == 0) sred[s][warp] = red[s];
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < P.n_reductions; ++s) {
+      float v = sred[s][0];
+      for (int w = 1; w < kPwThreads / 32; ++w) v = pw_reduce_combine(L.red_ops[s], v, sred[s][w]);
+      if (L.blocks_per_group == 1) reinterpret_cast<float*>(P.out[L.red_out_slot[s]])[group] = v;
+      else L.partials[((size_t)s * L.num_groups + group) * L.blocks_per_group + blk] = v;
+    }
+  }
+}
+
+struct PwFinalize {
+  uint32_t num_groups, blocks_per_group;
+  int n_red;
+  int red_ops[4];
+  float* out[4];
+  const float* partials;
+};
+
+__global__ void __launch_bounds__(kPwThreads) pw_reduce_finalize_kernel(const __grid_constant__ PwFinalize F) {
+  const uint32_t i = blockIdx.x * kPwThreads + threadIdx.x;
+  if (i >= F.num_groups * (uint32_t)F.n_red) return;
+  const uint32_t s = i / F.num_groups, g = i - s * F.num_groups;
+  const float* p = F.partials + ((size_t)s * F.num_groups + g) * F.blocks_per_group;
+  float v = p[0];
+  for (uint32_t b = 1; b < F.blocks_per_group; ++b) v = pw_reduce_combine(F.red_ops[s], v, p[b]);
+  F.out[s][g] = v;
+}
+
+namespace {
+
+struct PointwisePlan : he_plan {
+  PwCompiled c;
+  bool reduce = false;
+  PwReduceLaunch rl{};
+  int n_inputs = 0, n_outputs = 0;
+
+  int32_t launch(const void* const* inputs, void* const* outputs, void* workspace, cudaStream_t stream) override {
+    PwProgram P = c.prog;
+    if (P.n_elems == 0) return HE_OK;
+    for (int i = 0; i < n_inputs; ++i) {
+      if (!inputs || !inputs[i]) HE_FAIL(HE_ERR_INVALID, "pointwise launch: input %d is null", i);
+      P.in[i] = inputs[i];
+    }
+    for (int i = 0; i < n_outputs; ++i) {
+      if (!outputs || !outputs[i]) HE_FAIL(HE_ERR_INVALID, "pointwise launch: output %d is null", i);
+      P.out[i] = outputs[i];
+    }
+    if (!reduce) {
+      if (c.has_bool_io) {
+        unsigned grid = (P.n_elems + kPwThreads - 1) / kPwThreads;
+        pw_elementwise_kernel<1><<<grid, kPwThreads, 0, stream>>>(P);
+      } else {
+        unsigned grid = (unsigned)(((uint64_t)P.n_elems + kPwThreads * 4 - 1) / (kPwThreads * 4));
+        pw_elementwise_kernel<4><<<grid, kPwThreads, 0, stream>>>(P);
+      }
+      HE_CUDA(cudaGetLastError());
+      last_launches = 1;
+      return HE_OK;
+    }
+    PwReduceLaunch L = rl;
+    L.partials = reinterpret_cast<float*>(workspace);
+    unsigned grid = L.warp_mode ? (L.num_groups + 7) / 8 : L.num_groups * L.blocks_per_group;
+    pw_reduce_kernel<<<grid, kPwThreads, 0, stream>>>(P, L);
+    HE_CUDA(cudaGetLastError());
+    last_launches = 1;
+    if (!L.warp_mode && L.blocks_per_group > 1) {
+      PwFinalize F{};
+      F.num_groups = L.num_groups;
+      F.blocks_per_group = L.blocks_per_group;
+      F.n_red = P.n_reductions;
+      for (int s = 0; s < P.n_reductions; ++s) {
+        F.red_ops[s] = L.red_ops[s];
+        F.out[s] = reinterpret_cast<float*>(P.out[L.red_out_slot[s]]);
+      }
+      F.partials = L.partials;
+      unsigned fg = (L.num_groups * P.n_reductions + kPwThreads - 1) / kPwThreads;
+      pw_reduce_finalize_kernel<<<fg, kPwThreads, 0, stream>>>(F);
+      HE_CUDA(cudaGetLastError());
+      last_launches = 2;
+    }
+    return HE_OK;
+  }
+};
+
+// Tier-2 matcher: store(relu?(x * s + b)) where x is read through a pure axis permutation and
+// s / b vary along exactly one axis of x.  Returns true and fills the permute arguments.
+bool match_affine_permute(const Graph& g, const PwCompiled& c, AffineFunctor* f, int* rank,
+                          int64_t* in_shape, int64_t* out_strides, int* dtype) {
+  const PwProgram& P = c.prog;
+  if (P.n_outputs != 1 || P.n_reductions != 0 || c.has_bool_io) return false;
+  // instruction shapes accepted (after FMA fusion):
+  //   LOAD x [LOAD s] [LOAD b] (MUL | FMA | ADD) [RELU] STORE   in compiler emission order
+  int x_load = -1;
+  std::vector<const PwLoadInfo*> params;
+  for (const PwLoadInfo& li : c.loads) {
+    const he_node& n = g.nodes[li.node];
+    if (dclass(n.dtype) != DClass::Float) return false;
+    if (!li.single_view) return false;
+    if (num_elements(n) == (int64_t)P.n_elems && !li.identity) {
+      if (x_load >= 0) return false;
+      x_load = (int)(&li - &c.loads[0]);
+    } else {
+      params.push_back(&li);
+    }
+  }
+  if (x_load < 0 || params.size() > 2) return false;
+  const PwLoadInfo& X = c.loads[x_load];
+  const he_node& xn = g.nodes[X.node];
+  // x's view must be a bijection: every iteration dim walks a distinct axis of x with that axis' extent
+  int64_t xst[HE_MAX_RANK];
+  {
+    int64_t s = 1;
+    for (int i = xn.rank - 1; i >= 0; --i) { xst[i] = s; s *= xn.shape[i]; }
+  }
+  int64_t iter_packed[HE_MAX_RANK];
+  {
+    int64_t s = 1;
+    for (int k = c.iter_rank - 1; k >= 0; --k) { iter_packed[k] = s; s *= c.iter_shape[k]; }
+  }
+  int axis_of_iter[HE_MAX_RANK];
+  bool used[HE_MAX_RANK] = {false};
+  for (int k = 0; k < c.iter_rank; ++k) {
+    axis_of_iter[k] = -1;
+    if (c.iter_shape[k] == 1) continue;
+    for (int j = 0; j < xn.rank; ++j)
+      if (!used[j] && xn.shape[j] == c.iter_shape[k] && xst[j] == X.iter_stride[k] && xn.shape[j] != 1) {
+        axis_of_iter[k] = j;
+        used[j] = true;
+        break;
+      }
+    if (axis_of_iter[k] < 0) return false;
+  }
+  for (int j = 0; j < xn.rank; ++j)
+    if (!used[j] && xn.shape[j] != 1) return false;
+  *rank = xn.rank;
+  for (int j = 0; j < xn.rank; ++j) { in_shape[j] = xn.shape[j]; out_strides[j] = 1; }
+  for (int k = 0; k < c.iter_rank; ++k)
+    if (axis_of_iter[k] >= 0) out_strides[axis_of_iter[k]] = iter_packed[k];
+  // parameters: one non-zero stride (== 1 after collapsing), along an iteration dim that maps to an x axis
+  int param_axis = -1;
+  for (const PwLoadInfo* pl : params) {
+    int dim = -1;
+    for (int k = 0; k < c.iter_rank; ++k) {
+      if (pl->identity) return false;
+      if (pl->iter_stride[k] != 0 && c.iter_shape[k] != 1) {
+        if (dim >= 0 || pl->iter_stride[k] != 1) return false;
+        dim = k;
+      }
+    }
+    int axis = dim >= 0 ? axis_of_iter[dim] : 0;
+    if (dim >= 0 && num_elements(g.nodes[pl->node]) != c.iter_shape[dim]) return false;
+    if (dim < 0 && num_elements(g.nodes[pl->node]) != 1) return false;
+    if (param_axis >= 0 && axis != param_axis && dim >= 0) return false;
+    if (dim >= 0) param_axis = axis;
+  }
+  if (param_axis < 0) param_axis = 0;
+  // walk the instruction stream
+  auto load_slot_of_reg_def = [&](int instr_idx) -> const PwLoadInfo* {
+    for (const PwLoadInfo& li : c.loads)
+      if (li.instr == instr_idx) return &li;
+    return nullptr;
+  };
+  // symbolic evaluation: each register holds one of {x, s, b (raw loads), expr}
+  struct Val { int kind; int scale_slot, bias_slot; bool relu; };  // kind: 0 none 1 x-expr 2 param
+  Val regs[kPwMaxRegs];
+  int param_slot[kPwMaxRegs];
+  for (int r = 0; r < kPwMaxRegs; ++r) { regs[r] = {0, -1, -1, false}; param_slot[r] = -1; }
+  Val result{0, -1, -1, false};
+  for (int i = 0; i < P.n_instr; ++i) {
+    const PwInstr& in = P.instr[i];
+    switch (in.op) {
+      case PW_LOAD: {
+        const PwLoadInfo* li = load_slot_of_reg_def(i);
+        if (!li) return false;
+        if (li == &X) regs[in.dst] = {1, -1, -1, false};
+        else { regs[in.dst] = {2, -1, -1, false}; param_slot[in.dst] = li->input_slot; }
+        break;
+      }
+      case PW_BIN_F: {
+        Val a = regs[in.a], b = regs[in.b];
+        int pa = param_slot[in.a], pb = param_slot[in.b];
+        if (a.kind == 2 && b.kind == 1) { std::swap(a, b); std::swap(pa, pb); }
+        if (a.kind != 1 || b.kind != 2 || a.relu) return false;
+        if (in.sub == HE_BIN_MUL) {
+          if (a.scale_slot >= 0 || a.bias_slot >= 0) return false;
+          a.scale_slot = pb;
+        } else if (in.sub == HE_BIN_ADD) {
+          if (a.bias_slot >= 0) return false;
+          a.bias_slot = pb;
+        } else return false;
+        regs[in.dst] = a;
+        param_slot[in.dst] = -1;
+        break;
+      }
+      case PW_FMA: {
+        Val a = regs[in.a], b = regs[in.b], cc = regs[in.c];
+        int pa = param_slot[in.a], pb = param_slot[in.b], pc = param_slot[in.c];
+        if (a.kind == 2 && b.kind == 1) { std::swap(a, b); std::swap(pa, pb); }
+        if (a.kind != 1 || b.kind != 2 || cc.kind != 2 || a.relu || a.scale_slot >= 0 || a.bias_slot >= 0) return false;
+        a.scale_slot = pb;
+        a.bias_slot = pc;
+        regs[in.dst] = a;
+        param_slot[in.dst] = -1;
+        break;
+      }
+      case PW_UNARY: {
+        Val a = regs[in.a];
+        if (in.sub != HE_UN_RELU || a.kind != 1 || a.relu) return false;
+        a.relu = true;
+        regs[in.dst] = a;
+        param_slot[in.dst] = -1;
+        break;
+      }
+      case PW_STORE:
+        result = regs[in.a];
+        if (result.kind != 1) return false;
+        if (in.dt != xn.dtype) return false;
+        break;
+      default: return false;
+    }
+  }
+  if (result.kind != 1) return false;
+  if (result.scale_slot < 0 && result.bias_slot < 0 && !result.relu) return false;  // plain permute: not ours
+  f->enabled = true;
+  f->axis = param_axis;
+  f->x_dtype = xn.dtype;
+  f->x_input = X.input_slot;
+  f->has_scale = result.scale_slot >= 0;
+  f->has_bias = result.bias_slot >= 0;
+  f->relu = result.relu;
+  f->scale_input = result.scale_slot;
+  f->bias_input = result.bias_slot;
+  if (f->has_scale) f->scale_dtype = g.nodes[g.inputs[result.scale_slot]].dtype;
+  if (f->has_bias) f->bias_dtype = g.nodes[g.inputs[result.bias_slot]].dtype;
+  *dtype = xn.dtype;
+  return true;
+}
+
+}  // namespace
+
+int32_t plan_pointwise(he_ctx* ctx, const Graph& g, he_plan** out, int* tier_only) {
+  for (const he_node& n : g.nodes)
+    if (n.kind == HE_OP_MATMUL) HE_FAIL(HE_ERR_UNSUPPORTED, "pointwise: subgraph contains a matmul");
+  PointwisePlan* plan = new PointwisePlan();
+  int32_t st = compile_pointwise(g, PwCompileOptions{}, &plan->c);
+  if (st != HE_OK) {
+    delete plan;
+    return st;
+  }
+  // tier 2
+  {
+    AffineFunctor f;
+    int rank, dtype;
+    int64_t in_shape[HE_MAX_RANK], out_strides[HE_MAX_RANK];
+    if (match_affine_permute(g, plan->c, &f, &rank, in_shape, out_strides, &dtype)) {
+      he_plan* pp = nullptr;
+      // the tile kernel needs the innermost axis to move; otherwise the interpreter is already coalesced
+      std::string saved = he_last_error_string();
+      if (make_permute_plan(ctx, rank, in_shape, out_strides, dtype, &f, &pp) == HE_OK) {
+        delete plan;
+        if (tier_only) {
+          *tier_only = 2;
+          delete pp;
+          return HE_OK;
+        }
+        pp->description = "pointwise tier 2 (fused affine + " + pp->description + ")";
+        *out = pp;
+        return HE_OK;
+      }
+      set_error("%s", saved.c_str());
+    }
+  }
+  if (tier_only) {
+    *tier_only = 1;
+    delete plan;
+    return HE_OK;
+  }
+  plan->ctx = ctx;
+  plan->n_inputs = plan->c.prog.n_inputs;
+  plan->n_outputs = plan->c.prog.n_outputs;
+  const PwProgram& P = plan->c.prog;
+  plan->reduce = P.n_reductions > 0;
+  char desc[256];
+  if (plan->reduce) {
+    PwReduceLaunch& L = plan->rl;
+    L.num_groups = P.group_size ? P.n_elems / P.group_size : 0;
+    int s = 0;
+    for (size_t o = 0; o < plan->c.out_is_reduce.size(); ++o)
+      if (plan->c.out_is_reduce[o] >= 0) {
+        L.red_ops[s] = plan->c.out_is_reduce[o];
+        L.red_out_slot[s] = (int)o;
+        ++s;
+      }
+    if (P.group_size <= 2048) {
+      L.warp_mode = 1;
+      L.blocks_per_group = 1;
+      L.chunk = P.group_size;
+    } else {
+      L.warp_mode = 0;
+      // ~16 elements per thread per CTA, but never more CTAs than ~8 waves' worth of the GPU
+      uint32_t chunk = kPwThreads * 16;
+      uint32_t bpg = (P.group_size + chunk - 1) / chunk;
+      uint64_t max_ctas = (uint64_t)ctx_sm_count(ctx) * 64;
+      if ((uint64_t)bpg * L.num_groups > max_ctas) {
+        bpg = (uint32_t)std::max<uint64_t>(1, max_ctas / std::max<uint32_t>(1, L.num_groups));
+        chunk = (P.group_size + bpg - 1) / bpg;
+        chunk = (chunk + kPwThreads - 1) / kPwThreads * kPwThreads;
+        bpg = (P.group_size + chunk - 1) / chunk;
+      }
+      L.blocks_per_group = bpg;
+      L.chunk = chunk;
+      if (bpg > 1) plan->workspace_bytes = (size_t)P.n_reductions * L.num_groups * bpg * sizeof(float);
+    }
+    snprintf(desc, sizeof desc, "pointwise tier 1 (interpreter, %d instr, %d regs), reduce: %u groups of %u, %s, %u CTAs/group",
+             P.n_instr, plan->c.n_regs, L.num_groups, P.group_size, L.warp_mode ? "warp per group" : "CTA slices", L.blocks_per_group);
+  } else {
+    snprintf(desc, sizeof desc, "pointwise tier 1 (interpreter, %d instr, %d regs, %d elems/thread)", P.n_instr,
+             plan->c.n_regs, plan->c.has_bool_io ? 1 : 4);
+  }
+  plan->description = desc;
+  *out = plan;
+  return HE_OK;
+}
+
+}  // namespace he

@@ -1,0 +1,194 @@
+"""Thin object layer over the C ABI: Context and Plan.
+
+PyTorch is used only as the device-memory and stream provider (what helium's allocator and
+CudaContext do in the reference, helium/src/cuda/context.rs, allocator/*).  Every compute call
+goes through `he_launch`; nothing here computes on the host.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import List, Optional, Sequence
+
+import numpy as np
+
+from . import ir
+from ._lib import HeliumError, check, lib
+
+_TORCH_DTYPES = None
+
+
+def _torch():
+    import torch
+
+    global _TORCH_DTYPES
+    if _TORCH_DTYPES is None:
+        _TORCH_DTYPES = {ir.F16: torch.float16, ir.BF16: torch.bfloat16, ir.F32: torch.float32,
+                         ir.U32: torch.int32, ir.BOOL: torch.int32}
+    return torch
+
+
+def storage_elems(dtype: int, n: int) -> int:
+    """Elements of the backing torch tensor (bool tensors are bit-packed u32 words)."""
+    return (n + 31) // 32 if dtype == ir.BOOL else n
+
+
+class Context:
+    """he_ctx: one per device."""
+
+    def __init__(self, device: int = 0):
+        h = C.c_void_p()
+        check(lib.he_ctx_create(device, C.byref(h)))
+        self._h = h
+        self.device = device
+
+    def poll(self, stream=None) -> None:
+        check(lib.he_ctx_poll_device_status(self._h, C.c_void_p(_stream_ptr(stream))))
+
+    def close(self) -> None:
+        if self._h:
+            lib.he_ctx_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def _stream_ptr(stream) -> int:
+    if stream is None:
+        torch = _torch()
+        return torch.cuda.current_stream().cuda_stream
+    if isinstance(stream, int):
+        return stream
+    return stream.cuda_stream
+
+
+class Plan:
+    """he_plan plus the descriptors needed to allocate outputs."""
+
+    def __init__(self, handle: C.c_void_p, out_shapes: List[tuple], out_dtypes: List[int], n_inputs: int,
+                 ctx: Optional[Context]):
+        self._h = handle
+        self.out_shapes = out_shapes
+        self.out_dtypes = out_dtypes
+        self.n_inputs = n_inputs
+        self.ctx = ctx
+        self._workspace = None
+
+    # -- constructors ------------------------------------------------------------------------------
+    @staticmethod
+    def pointwise(ctx: Optional[Context], graph: ir.Graph) -> "Plan":
+        return Plan._from_graph(lib.he_plan_pointwise, ctx, graph)
+
+    @staticmethod
+    def fused_matmul(ctx: Optional[Context], graph: ir.Graph) -> "Plan":
+        return Plan._from_graph(lib.he_plan_fused_matmul, ctx, graph)
+
+    @staticmethod
+    def _from_graph(fn, ctx, graph: ir.Graph) -> "Plan":
+        desc, keep = graph.to_desc()
+        h = C.c_void_p()
+        check(fn(ctx._h if ctx else None, C.byref(desc), C.byref(h)))
+        del keep
+        shapes = [graph.nodes[o].shape for o in graph.outputs]
+        dtypes = [graph.nodes[o].dtype for o in graph.outputs]
+        return Plan(h, shapes, dtypes, len(graph.inputs), ctx)
+
+    @staticmethod
+    def permute(ctx: Optional[Context], in_shape: Sequence[int], out_strides: Sequence[int], dtype: int,
+                out_shape: Optional[Sequence[int]] = None) -> "Plan":
+        rank = len(in_shape)
+        shp = (C.c_int64 * rank)(*in_shape)
+        st = (C.c_int64 * rank)(*out_strides)
+        h = C.c_void_p()
+        check(lib.he_plan_permute(ctx._h if ctx else None, rank, shp, st, dtype, C.byref(h)))
+        if out_shape is None:
+            order = sorted(range(rank), key=lambda i: -out_strides[i])
+            out_shape = [in_shape[i] for i in order]
+        return Plan(h, [tuple(out_shape)], [dtype], 1, ctx)
+
+    # -- queries -----------------------------------------------------------------------------------
+    @property
+    def workspace_bytes(self) -> int:
+        n = C.c_size_t()
+        check(lib.he_plan_workspace_bytes(self._h, C.byref(n)))
+        return n.value
+
+    @property
+    def description(self) -> str:
+        return lib.he_plan_describe(self._h).decode()
+
+    @property
+    def last_launch_count(self) -> int:
+        return lib.he_plan_last_launch_count(self._h)
+
+    # -- launching ---------------------------------------------------------------------------------
+    def alloc_outputs(self, device: str = "cuda"):
+        torch = _torch()
+        outs = []
+        for shape, dt in zip(self.out_shapes, self.out_dtypes):
+            n = int(np.prod(shape, dtype=np.int64)) if len(shape) else 1
+            if dt == ir.BOOL:
+                outs.append(torch.empty(storage_elems(dt, n), dtype=torch.int32, device=device))
+            else:
+                outs.append(torch.empty(tuple(shape), dtype=_TORCH_DTYPES[dt], device=device))
+        return outs
+
+    def launch_ptrs(self, in_ptrs: Sequence[int], out_ptrs: Sequence[int], workspace_ptr: int = 0, stream=None) -> None:
+        """Direct call of he_launch with raw device addresses."""
+        ins = (C.c_void_p * max(1, len(in_ptrs)))(*in_ptrs)
+        outs = (C.c_void_p * max(1, len(out_ptrs)))(*out_ptrs)
+        check(lib.he_launch(self._h, ins, outs, C.c_void_p(workspace_ptr), C.c_void_p(_stream_ptr(stream))))
+
+    def launch(self, inputs: Sequence, outputs: Optional[Sequence] = None, stream=None):
+        """Runs the plan on torch CUDA tensors; allocates outputs (and the workspace once) if needed."""
+        torch = _torch()
+        if len(inputs) != self.n_inputs:
+            raise ValueError(f"plan takes {self.n_inputs} inputs, got {len(inputs)}")
+        for t in inputs:
+            if not t.is_cuda or not t.is_contiguous():
+                raise ValueError("inputs must be contiguous CUDA tensors")
+        if outputs is None:
+            outputs = self.alloc_outputs(inputs[0].device if inputs else "cuda")
+        ws = self.workspace_bytes
+        if ws and (self._workspace is None or self._workspace.numel() < ws):
+            self._workspace = torch.empty(ws + 256, dtype=torch.uint8, device=outputs[0].device)
+        wptr = 0
+        if ws:
+            wptr = (self._workspace.data_ptr() + 255) // 256 * 256
+        self.launch_ptrs([t.data_ptr() for t in inputs], [t.data_ptr() for t in outputs], wptr, stream)
+        return outputs
+
+    def close(self) -> None:
+        if self._h:
+            lib.he_plan_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def plan_supported(graph: ir.Graph, kind: int, ctx: Optional[Context] = None) -> int:
+    """he_plan_supported: 0 unsupported, 1 interpreter tier, 2 hand-written kernel."""
+    desc, keep = graph.to_desc()
+    r = lib.he_plan_supported(ctx._h if ctx else None, C.byref(desc), kind)
+    del keep
+    return r
+
+
+def permute_output_strides(in_shape: Sequence[int], swaps: Sequence[tuple], reference_compat: bool = False) -> List[int]:
+    rank = len(in_shape)
+    shp = (C.c_int64 * rank)(*in_shape)
+    flat = [a for s in swaps for a in s]
+    sw = (C.c_int32 * max(1, len(flat)))(*flat)
+    out = (C.c_int64 * rank)()
+    check(lib.he_permute_output_strides(rank, shp, len(swaps), sw, 1 if reference_compat else 0, out))
+    return list(out)
+
+
+__all__ = ["Context", "Plan", "HeliumError", "plan_supported", "permute_output_strides", "storage_elems"]

@@ -1,0 +1,196 @@
+/*
+ * helium_b200 -- C ABI of the B200 (sm_100a) fused-kernel library that sits behind helium's
+ * `Backend` / `Instruction` traits.
+ *
+ * Every entry point takes plain pointers and sizes.  Device pointers are raw CUdeviceptr values
+ * of dense row-major tensors (helium aligns tensor storage to 64 bytes,
+ * helium/src/cuda/tensor_storage.rs:53), `cu_stream` is a CUstream / cudaStream_t cast to void*.
+ * Nothing here synchronises the device: work is enqueued on the caller's stream, exactly like
+ * `Instr::execute` does in the reference (helium/src/cuda/instr.rs:27-52).
+ *
+ * All functions returning `int32_t` return HE_OK (0) on success or a negative he_status; the
+ * message of the last failure on the calling thread is available from he_last_error_string().
+ * The library never aborts, traps or falls back to a CPU path.
+ */
+#ifndef HELIUM_B200_H
+#define HELIUM_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define HE_MAX_RANK 8
+
+typedef enum he_status {
+  HE_OK = 0,
+  HE_ERR_INVALID = -1,      /* malformed descriptor / argument                               */
+  HE_ERR_UNSUPPORTED = -2,  /* well-formed but outside what the kernels implement             */
+  HE_ERR_CUDA = -3,         /* a CUDA runtime / driver call failed (message has the detail)    */
+  HE_ERR_WORKSPACE = -4,    /* workspace pointer missing or too small                          */
+  HE_ERR_DEVICE_TIMEOUT = -5 /* a bounded device-side wait gave up (see he_ctx_poll_device_status) */
+} he_status;
+
+/* Mirrors helium_ir::data_type::DataType (helium-ir/src/data_type.rs:9-24).
+ * HE_BOOL is bit-packed, 1 bit per element in little-endian u32 words, LSB first
+ * (helium/src/cuda/instr/pointwise/jit.rs:107-114,234-237). */
+typedef enum he_dtype { HE_F16 = 0, HE_BF16 = 1, HE_F32 = 2, HE_U32 = 3, HE_BOOL = 4 } he_dtype;
+
+/* Node kinds: the helium-ir `Op` enum (helium-ir/src/opgraph/op.rs:15-30) minus the convolutions,
+ * plus HE_OP_INPUT for tensors that enter the subgraph from outside. */
+typedef enum he_op_kind {
+  HE_OP_INPUT = 0,
+  HE_OP_CONSTANT = 1,   /* op.rs:469-474   value in const_bits (bit pattern of `dtype`)          */
+  HE_OP_UNARY = 2,      /* op.rs:285-304   sub_op = he_unary_op                                   */
+  HE_OP_BINARY = 3,     /* op.rs:308-328   sub_op = he_binary_op; result dtype = lhs dtype         */
+  HE_OP_CAST = 4,       /* op.rs:331-335   ChangeDataType                                          */
+  HE_OP_REDUCE = 5,     /* op.rs:338-356   sub_op = he_reduce_op; axes = bitmask of reduced dims   */
+  HE_OP_BROADCAST = 6,  /* op.rs:369-395   input left-padded with 1s to `rank`, then axes widened  */
+  HE_OP_RESHAPE = 7,    /* op.rs:409-413                                                           */
+  HE_OP_SWAP_DIMS = 8,  /* op.rs:415-420   axis_a, axis_b                                          */
+  HE_OP_COMPARE = 9,    /* op.rs:422-437   sub_op = he_compare_op; output HE_BOOL                  */
+  HE_OP_SELECT = 10,    /* op.rs:439-445   in = {lhs, rhs, selector}; selector ? rhs : lhs         */
+  HE_OP_MATMUL = 11     /* op.rs:272-282   in = {a, b}; sub_op = he_precision                      */
+} he_op_kind;
+
+/* UnaryPointwiseOp (op.rs:291-304) followed by the playground-only unary ops
+ * (helium-playground/src/opgraph.rs: UnaryPointwiseOp). The *_CONST ops take their constant
+ * as an f32 bit pattern in const_bits. */
+typedef enum he_unary_op {
+  HE_UN_RECIP = 0, HE_UN_NEG, HE_UN_EXP, HE_UN_SIN, HE_UN_COS, HE_UN_TAN, HE_UN_SIGMOID,
+  HE_UN_TANH, HE_UN_RELU, HE_UN_SQRT, HE_UN_LOG,
+  HE_UN_GELU = 16,      /* exact erf form, the torch F.gelu default (torch_synthesizer.rs:48)     */
+  HE_UN_ADD_CONST = 17, HE_UN_MUL_CONST = 18, HE_UN_POW_CONST = 19,
+  HE_UN_DGELU = 20      /* d/dx gelu(x); used by backward graphs of HE_UN_GELU                     */
+} he_unary_op;
+
+/* BinaryPointwiseOp (op.rs:315-328) followed by the playground-only binary ops. */
+typedef enum he_binary_op {
+  HE_BIN_ADD = 0, HE_BIN_MUL, HE_BIN_POW, HE_BIN_MIN, HE_BIN_MAX, HE_BIN_AND, HE_BIN_OR, HE_BIN_XOR,
+  HE_BIN_SUB = 16, HE_BIN_DIV = 17,
+  HE_BIN_DRELU = 18     /* rhs > 0 ? lhs : 0  (helium-playground/src/kernel_generator.rs:409-411)  */
+} he_binary_op;
+
+typedef enum he_compare_op { HE_CMP_EQ = 0, HE_CMP_NE, HE_CMP_LT, HE_CMP_LE, HE_CMP_GT, HE_CMP_GE } he_compare_op;
+typedef enum he_reduce_op { HE_RED_SUM = 0, HE_RED_MEAN, HE_RED_MAX, HE_RED_MIN } he_reduce_op;
+
+/* helium_ir Precision (helium-ir/src/opgraph/op/precision.rs:36-81). */
+typedef enum he_precision {
+  HE_PREC_F32_F32 = 0,   /* MulF32AccumF32  */
+  HE_PREC_TF32_F32 = 1,  /* MulTf32AccumF32 (a minimum: served with full f32 products here)        */
+  HE_PREC_BF16_F32 = 2,  /* MulBf16AccumF32 */
+  HE_PREC_F16_F32 = 3    /* MulF16AccumF32  */
+} he_precision;
+
+/* One node of a subgraph, in topological order (every `in[i]` is a smaller index, or -1).
+ * `shape`/`rank`/`dtype` describe the node's OUTPUT (the reference's `Descriptor`,
+ * helium-ir/src/opgraph.rs:241-257).  For HE_OP_REDUCE the helium-ir form "collapse the last
+ * `depth` dims into one dim of size 1" (op.rs:78-89) is axes = the last `depth` bits with
+ * shape = [.., 1]; the playground forms Rows/Columns/Item/Batch
+ * (helium-playground/src/opgraph.rs:397-413) keep rank 3 and set the reduced dims to 1. */
+typedef struct he_node {
+  int32_t kind;        /* he_op_kind */
+  int32_t sub_op;      /* he_unary_op / he_binary_op / he_compare_op / he_reduce_op / he_precision */
+  int32_t in[3];       /* operand node indices, -1 when unused */
+  int32_t dtype;       /* he_dtype of the output */
+  int32_t rank;
+  int64_t shape[HE_MAX_RANK];
+  uint32_t const_bits; /* HE_OP_CONSTANT value / *_CONST operand */
+  int32_t axis_a;      /* HE_OP_SWAP_DIMS */
+  int32_t axis_b;      /* HE_OP_SWAP_DIMS */
+  uint32_t axes;       /* HE_OP_REDUCE: bitmask over the INPUT's dims */
+} he_node;
+
+/* Flat mirror of `OpSubgraph` (helium-ir/src/opgraph/subgraph.rs:12-18): nodes, and the leafs
+ * that become kernel outputs.  Kernel inputs are the HE_OP_INPUT nodes in order of appearance;
+ * he_launch's `inputs[i]` / `outputs[j]` follow those two orders. */
+typedef struct he_graph_desc {
+  int32_t num_nodes;
+  const he_node* nodes;
+  int32_t num_outputs;
+  const int32_t* outputs;
+} he_graph_desc;
+
+typedef struct he_ctx he_ctx;
+typedef struct he_plan he_plan;
+
+/* Replaces CudaContext::global (helium/src/cuda/context.rs:50-69) for the purposes of this
+ * library: binds to `device_ordinal`'s primary context, queries SM count / smem limits and
+ * allocates one 64-byte device status block used by bounded device-side waits. */
+int32_t he_ctx_create(int32_t device_ordinal, he_ctx** out);
+void he_ctx_destroy(he_ctx* ctx);
+/* Reads (synchronously, after syncing `cu_stream`) and clears the device status word.
+ * Returns HE_OK or HE_ERR_DEVICE_TIMEOUT; detail in he_last_error_string(). */
+int32_t he_ctx_poll_device_status(he_ctx* ctx, void* cu_stream);
+
+/* Replaces PointwiseGraph::{precompile,get_kernel} (helium/src/cuda/instr/pointwise.rs:40-54) and
+ * pointwise::jit::generate_kernel (pointwise/jit.rs:19-121).  Accepts what `supports_subgraph`
+ * accepts (pointwise.rs:121-186) and, beyond it, any number of swap_dims / broadcasts. */
+int32_t he_plan_pointwise(he_ctx* ctx, const he_graph_desc* desc, he_plan** out);
+
+/* Replaces PermuteDims::{precompile,build_kernel} (helium/src/cuda/instr/permute_dims.rs:55-83)
+ * and permute_dims::jit::generate_kernel (permute_dims/jit.rs:15-117): out[sum_i out_strides[i] *
+ * c[i]] = in[c] for every coordinate c of the row-major input of shape `in_shape`.
+ * `out_strides[i]` is the stride, in elements, that INPUT axis i has in the output
+ * (permute_dims.rs:158-172).  dtype may be F16/BF16/F32/U32. */
+int32_t he_plan_permute(he_ctx* ctx, int32_t rank, const int64_t* in_shape,
+                        const int64_t* out_strides, int32_t dtype, he_plan** out);
+
+/* Host helper replacing compute_output_strides (permute_dims.rs:158-172).  `swaps` holds
+ * num_swaps (axis_a, axis_b) pairs applied in order.  With reference_compat = 0 the strides
+ * realise the composition of the swaps (what the IR's output shape describes, op.rs:102-110).
+ * With reference_compat = 1 they reproduce the reference function verbatim, which yields the
+ * INVERSE permutation for chains that are not their own inverse (its unit test
+ * permute_dims.rs:183-187 pins exactly that). */
+int32_t he_permute_output_strides(int32_t rank, const int64_t* in_shape, int32_t num_swaps,
+                                  const int32_t* swaps, int32_t reference_compat,
+                                  int64_t* out_strides);
+
+/* Replaces MatmulGenerator::new + generate (helium-kernel-generator/src/generators/matmul.rs:
+ * 88-153) and the playground's KernelGenerator (helium-playground/src/kernel_generator.rs:51-117):
+ * one HE_OP_MATMUL node, mainloop pointwise ops on the operand side, epilogue pointwise /
+ * broadcast / Sum-reduction ops on the result side.  Shapes are [.., M, K] x [.., K, N] row-major
+ * (op.rs:272-282); a SWAP_DIMS of the last two dims feeding an operand selects the transposed
+ * shared-memory descriptor instead of moving data. */
+int32_t he_plan_fused_matmul(he_ctx* ctx, const he_graph_desc* desc, he_plan** out);
+
+/* Backs Instruction::can_fuse_with (helium/src/backend.rs:85-95): 0 = cannot run as one kernel,
+ * 1 = runs through the generic interpreter tier, 2 = matches a hand-written fast kernel.
+ * kind: 0 pointwise, 1 permute (swap chain on one input), 2 fused matmul. */
+int32_t he_plan_supported(he_ctx* ctx, const he_graph_desc* desc, int32_t kind);
+
+/* Scratch the launch needs (caller-allocated from its stream allocator with 256-byte alignment,
+ * like the cuDNN workspace in helium/src/cuda/instr/cudnn_graph.rs:75-92). */
+int32_t he_plan_workspace_bytes(const he_plan* plan, size_t* out);
+
+/* Replaces {PointwiseGraph,PermuteDims,CudnnGraph}::execute (pointwise.rs:57-86,
+ * permute_dims.rs:33-53, cudnn_graph.rs:64-105).  Pre-filling of reduction / bool outputs
+ * (pointwise.rs:62-74) happens inside, on the same stream. */
+int32_t he_launch(he_plan* plan, const void* const* inputs, void* const* outputs,
+                  void* workspace, void* cu_stream);
+
+/* Number of kernels (not memsets) the last he_launch of this plan enqueued. */
+int32_t he_plan_last_launch_count(const he_plan* plan);
+/* Short human-readable description of the kernel tier / tile configuration chosen. */
+const char* he_plan_describe(const he_plan* plan);
+void he_plan_destroy(he_plan* plan);
+
+/* Introspection for tests (no counterpart in the reference, whose generated CUDA source is
+ * inspected through insta snapshots instead, helium/src/cuda/instr/pointwise/jit.rs:752-803).
+ * he_debug_dump_program lowers a subgraph to the interpreter program and copies the raw PwProgram
+ * struct (layout: helium_b200/csrc/pointwise_program.h) into `buf`; `epilogue` != 0 treats the
+ * graph's matmul node as the accumulator source, like the generic fused-matmul tier does.
+ * he_debug_canonical_text returns the canonical text the kernel catalogue is matched on. */
+int32_t he_debug_dump_program(const he_graph_desc* desc, int32_t epilogue, void* buf, size_t cap,
+                              size_t* size_out);
+int32_t he_debug_canonical_text(const he_graph_desc* desc, char* buf, size_t cap);
+
+const char* he_last_error_string(void);
+const char* he_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* HELIUM_B200_H */

@@ -1,0 +1,169 @@
+"""Fused matmul (tcgen05 core, mainloop + epilogue fusion, SIMT fallback) against the oracle.
+
+Tolerances (the path's stated bar): rel-L2 <= 1e-2 for bf16/f16 outputs, <= 1e-5 for f32 outputs
+of contractions and reductions, measured against the f64 oracle on the same input bits."""
+import numpy as np
+import pytest
+
+import helium_b200 as hb
+from helium_b200 import ir
+from helpers import (O, bf16_bernoulli, bf16_normal, graph_c3, graph_linear, rng, storage_to_torch, torch_to_storage)
+
+pytestmark = pytest.mark.gpu
+
+TOL = {ir.BF16: 1e-2, ir.F16: 1e-2, ir.F32: 1e-5}
+
+
+def _run(ctx, graph, inputs):
+    import torch
+    plan = hb.Plan.fused_matmul(ctx, graph)
+    ins = [storage_to_torch(a, graph.nodes[i].dtype) for a, i in zip(inputs, graph.inputs)]
+    outs = plan.launch(ins)
+    torch.cuda.synchronize()
+    ctx.poll()  # a bounded wait that gave up would surface here as HE_ERR_DEVICE_TIMEOUT
+    return [torch_to_storage(t, graph.nodes[o].dtype) for t, o in zip(outs, graph.outputs)], plan
+
+
+def _gen(graph, seed, scale=None):
+    r = rng(seed)
+    ins = []
+    for k, i in enumerate(graph.inputs):
+        n = graph.nodes[i]
+        std = 1.0 if scale is None else scale.get(k, 1.0)
+        v = r.standard_normal(n.shape, dtype=np.float32) * np.float32(std)
+        ins.append(O.encode(v.astype(np.float64), n.dtype))
+    return ins
+
+
+def _compare(graph, got, want, desc):
+    for o, g_, w_ in zip(graph.outputs, got, want):
+        node = graph.nodes[o]
+        a = O.decode(g_, node.dtype, node.shape)
+        b = O.decode(w_, node.dtype, node.shape)
+        err = O.rel_l2(a, b)
+        assert err <= TOL[node.dtype], f"rel-L2 {err:.3e} > {TOL[node.dtype]} for output {o} {node.shape}: {desc}"
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 256, 64), (128, 256, 512), (256, 512, 128), (384, 768, 320),
+                                   (200, 264, 136), (8, 8, 8), (1000, 40, 72), (130, 1000, 4096)])
+@pytest.mark.parametrize("a_t,b_t", [(False, False), (False, True), (True, False), (True, True)])
+def test_plain_matmul_bf16(ctx, m, n, k, a_t, b_t):
+    g = graph_linear(m, n, k, bias=False, a_t=a_t, b_t=b_t, out_dtype=ir.F32)
+    ins = _gen(g, 21, {1: 1.0 / np.sqrt(k)})
+    got, plan = _run(ctx, g, ins)
+    assert "tcgen05" in plan.description
+    _compare(g, got, O.evaluate(g, ins), plan.description)
+
+
+def test_matmul_f16_and_bf16_outputs(ctx):
+    for dt in (ir.F16, ir.BF16):
+        g = graph_linear(256, 256, 256, bias=True, act=ir.UN_RELU, dtype=dt)
+        ins = _gen(g, 22, {1: 1 / 16.0})
+        got, plan = _run(ctx, g, ins)
+        _compare(g, got, O.evaluate(g, ins), plan.description)
+
+
+def test_batched_matmul(ctx):
+    g = graph_linear(136, 264, 72, bias=False, batch=3, out_dtype=ir.F32)
+    ins = _gen(g, 23, {1: 1 / 8.0})
+    got, plan = _run(ctx, g, ins)
+    _compare(g, got, O.evaluate(g, ins), plan.description)
+
+
+@pytest.mark.parametrize("kw", [
+    dict(bias=True, act=ir.UN_GELU, store_z=True),                 # config 4 forward GEMM 1
+    dict(bias=True, resid=True),                                   # config 4 forward GEMM 2
+    dict(bias=False, resid=True, colsum="resid"),                  # dX = dZ W1^T + dOut, db2 = colsum(dOut)
+    dict(bias=False, gate="dgelu", colsum="y", b_t=True),          # dZ = (dOut W2^T) * gelu'(Z), db1 = colsum(dZ)
+    dict(bias=False, a_t=True),                                    # dW = X^T dZ
+    dict(bias=True, act=ir.UN_TANH, gate="mul"),
+    dict(bias=False, act=None, gate="drelu", out_dtype=ir.F32),
+])
+@pytest.mark.parametrize("m,n,k", [(256, 512, 192), (200, 136, 64)])
+def test_flex_epilogues(ctx, kw, m, n, k):
+    g = graph_linear(m, n, k, **kw)
+    ins = _gen(g, 24, {1: 1.0 / np.sqrt(k)})
+    got, plan = _run(ctx, g, ins)
+    assert "flex" in plan.description
+    _compare(g, got, O.evaluate(g, ins), plan.description)
+    got2, _ = _run(ctx, g, ins)
+    for x, y in zip(got, got2):
+        assert np.array_equal(x, y), "results must be bit-stable across launches"
+
+
+def test_mainloop_relu_mask(ctx):
+    for (m, n, k) in [(128, 256, 64), (256, 264, 200), (512, 512, 1024)]:
+        g = ir.Graph()
+        a = g.new_input([m, k], ir.BF16); mk = g.new_input([m, k], ir.BF16); b = g.new_input([k, n], ir.BF16)
+        g.new_output(g.matmul(g.binary(ir.BIN_MUL, g.unary(ir.UN_RELU, a), mk), b))
+        r = rng(25)
+        ins = [bf16_normal(r, (m, k)), bf16_bernoulli(r, (m, k)), bf16_normal(r, (k, n), 1 / np.sqrt(k))]
+        got, plan = _run(ctx, g, ins)
+        assert "mainloop 3" in plan.description
+        _compare(g, got, O.evaluate(g, ins), plan.description)
+
+
+from helpers import c3_inputs as _c3_inputs  # noqa: E402
+
+
+@pytest.mark.parametrize("m,n,k,with_e", [(128, 256, 64, False), (256, 512, 128, False), (384, 520, 200, True), (1024, 1024, 1024, False)])
+def test_readme_graph(ctx, m, n, k, with_e):
+    g = graph_c3(m, n, k, with_e)
+    ins = _c3_inputs(m, n, k, with_e)
+    got, plan = _run(ctx, g, ins)
+    assert "README graph" in plan.description
+    _compare(g, got, O.evaluate(g, ins), plan.description)
+    got2, _ = _run(ctx, g, ins)
+    for x, y in zip(got, got2):
+        assert np.array_equal(x, y), "reductions must be bit-stable across launches"
+
+
+def test_readme_graph_full_size_against_c_oracle(ctx):
+    """BASELINE config 3 at 4096^3.  The numpy oracle would take minutes, so: 256 sampled rows go
+    through the C oracle (bit-identical semantics, f32), and the reductions are cross-checked
+    against sums of the kernel's own tile outputs."""
+    from oracle import oracle_c as OC
+    m = n = k = 4096
+    g = graph_c3(m, n, k, False)
+    ins = _c3_inputs(m, n, k, False)
+    got, plan = _run(ctx, g, ins)
+    loss, db2, db1, gt, gz1 = got
+    a, mk_ml, b, b1, b2, mk, y = [x.reshape(x.shape[-2], x.shape[-1]) for x in ins]
+    for m0 in (0, 1920, 3968):
+        acc = OC.gemm_bf16(a, b, mk_ml, m0, m0 + 128)
+        l, d2, d1, gt_ref, gz_ref = OC.c3_epilogue(acc, mk, y, b1.reshape(-1), b2.reshape(-1), 1.0 / n, m0, m)
+        for name, mine, ref in (("gt", gt, gt_ref), ("gz1", gz1, gz_ref)):
+            mine_v = O.bf16_bits_to_f32(mine.reshape(m, n)[m0:m0 + 128]).astype(np.float64)
+            err = O.rel_l2(mine_v, O.bf16_bits_to_f32(ref).astype(np.float64))
+            assert err <= 1e-2, (name, m0, err)
+    # column sums / loss agree with sums over the kernel's own bf16 tiles up to bf16 rounding of the tiles
+    gt_v = O.bf16_bits_to_f32(gt.reshape(m, n)).astype(np.float64)
+    gz_v = O.bf16_bits_to_f32(gz1.reshape(m, n)).astype(np.float64)
+    assert O.rel_l2(db2.reshape(-1), gt_v.sum(0)) <= 1e-2
+    assert O.rel_l2(db1.reshape(-1), gz_v.sum(0)) <= 1e-2
+    assert np.isfinite(loss).all() and loss.reshape(-1)[0] > 0
+
+
+def test_interpreted_epilogue(ctx):
+    for (m, n, k) in [(128, 256, 64), (200, 264, 136)]:
+        g = ir.Graph()
+        a = g.new_input([m, k], ir.BF16); b = g.new_input([k, n], ir.BF16); s = g.new_input([m, 1], ir.F32)
+        t = g.matmul(a, b)
+        t = g.binary(ir.BIN_MUL, g.unary(ir.UN_SIN, t), g.broadcast_to(s, [m, n]))
+        g.new_output(g.cast(t, ir.BF16))
+        g.new_output(g.unary(ir.UN_SIGMOID, t))
+        ins = _gen(g, 26, {1: 1.0 / np.sqrt(k)})
+        got, plan = _run(ctx, g, ins)
+        assert "interpreted" in plan.description
+        _compare(g, got, O.evaluate(g, ins), plan.description)
+
+
+def test_simt_paths(ctx):
+    # f32 operands (config 1 shapes), and bf16 shapes that break the TMA pitch rule (4097-style)
+    for (m, n, k, dt, bias, act) in [(256, 512, 784, ir.F32, True, ir.UN_RELU), (256, 10, 512, ir.F32, True, None),
+                                     (129, 257, 131, ir.BF16, False, None), (2, 2, 2, ir.BF16, False, None)]:
+        g = graph_linear(m, n, k, bias=bias, act=act, dtype=dt, out_dtype=ir.F32)
+        ins = _gen(g, 27, {1: 1.0 / np.sqrt(k)})
+        got, plan = _run(ctx, g, ins)
+        assert "SIMT" in plan.description
+        _compare(g, got, O.evaluate(g, ins), plan.description)

@@ -1,0 +1,128 @@
+"""Pointwise kernels (both tiers) against the oracle."""
+import numpy as np
+import pytest
+
+import helium_b200 as hb
+from helium_b200 import ir
+from helpers import O, graph_affine_relu_permute, rng, storage_to_torch, torch_to_storage
+
+pytestmark = pytest.mark.gpu
+
+
+def _run(ctx, graph, inputs):
+    import torch
+    plan = hb.Plan.pointwise(ctx, graph)
+    ins = [storage_to_torch(a, graph.nodes[i].dtype) for a, i in zip(inputs, graph.inputs)]
+    outs = plan.launch(ins)
+    torch.cuda.synchronize()
+    return [torch_to_storage(t, graph.nodes[o].dtype) for t, o in zip(outs, graph.outputs)], plan
+
+
+def _close(graph, got, want, tol):
+    for o, g_, w_ in zip(graph.outputs, got, want):
+        node = graph.nodes[o]
+        if node.dtype in (ir.BOOL, ir.U32):
+            n_words = (node.num_elements + 31) // 32 if node.dtype == ir.BOOL else node.num_elements
+            assert np.array_equal(np.asarray(g_).reshape(-1)[:n_words], np.asarray(w_).reshape(-1)[:n_words])
+        else:
+            a = O.decode(g_, node.dtype, node.shape).reshape(-1)
+            b = O.decode(w_, node.dtype, node.shape).reshape(-1)
+            assert np.allclose(a, b, rtol=tol, atol=tol), float(np.abs(a - b).max())
+
+
+@pytest.mark.parametrize("shape", [(2, 8, 3, 8), (3, 16, 7, 8), (2, 256, 8, 8), (1, 24, 5, 3)])
+@pytest.mark.parametrize("x_dtype,p_dtype", [(ir.BF16, ir.F32), (ir.F32, ir.F32), (ir.F16, ir.F16), (ir.BF16, ir.BF16)])
+def test_affine_relu_permute_tier2(ctx, shape, x_dtype, p_dtype):
+    n, c, h, w = shape
+    g = graph_affine_relu_permute(n, c, h, w, x_dtype, p_dtype)
+    r = rng(11)
+    x = r.standard_normal(shape, dtype=np.float32)
+    s = r.random(c, dtype=np.float32) + 0.5
+    b = r.standard_normal(c, dtype=np.float32) * 0.1
+    ins = [O.encode(x.astype(np.float64), x_dtype), O.encode(s.astype(np.float64), p_dtype), O.encode(b.astype(np.float64), p_dtype)]
+    got, plan = _run(ctx, g, ins)
+    assert "tier 2" in plan.description
+    want = O.evaluate(g, ins)
+    a = O.decode(got[0], x_dtype, (n, h, w, c)).reshape(-1)
+    bb = O.decode(want[0], x_dtype, (n, h, w, c)).reshape(-1)
+    # one fused multiply-add then one rounding: the f64 oracle can differ only on double-rounding ties
+    ulp = {ir.BF16: 2.0 ** -8, ir.F16: 2.0 ** -11, ir.F32: 2.0 ** -23}[x_dtype]
+    assert np.all(np.abs(a - bb) <= ulp * np.maximum(np.abs(bb), 1e-30) * 1.01 + 1e-38)
+    assert np.mean(a != bb) < 1e-3
+    # zeros of the relu must be exact
+    assert np.array_equal(a == 0, bb == 0)
+
+
+def test_config_2a_full_size(ctx):
+    """BASELINE config 2a at full size: [64,256,56,56] bf16; checked against the numpy oracle."""
+    g = graph_affine_relu_permute(64, 256, 56, 56)
+    r = rng(1)
+    x = O.f32_to_bf16_bits(r.standard_normal((64, 256, 56, 56), dtype=np.float32))
+    s = r.random(256, dtype=np.float32) + 0.5
+    b = r.standard_normal(256, dtype=np.float32) * 0.1
+    got, plan = _run(ctx, g, [x, s, b])
+    want = O.affine_relu_nchw_to_nhwc(x, s, b).reshape(-1)
+    assert "tier 2" in plan.description
+    assert np.array_equal(got[0].reshape(-1), want), plan.description
+
+
+def test_interpreter_mixed_graph(ctx):
+    g = ir.Graph()
+    x = g.new_input([33, 17, 5], ir.BF16)
+    y = g.new_input([17, 1], ir.F32)
+    yb = g.broadcast_to(y, [33, 17, 5])
+    t = g.binary(ir.BIN_ADD, g.unary(ir.UN_TANH, x), g.binary(ir.BIN_MUL, yb, g.unary(ir.UN_SIGMOID, x)))
+    g.new_output(t)                                        # bf16
+    g.new_output(g.cast(g.unary(ir.UN_EXP, t), ir.F32))    # f32
+    g.new_output(g.compare(ir.CMP_GT, t, yb))              # bool, bit-packed
+    g.new_output(g.swap_dims(g.cast(t, ir.F16), 0, 2))     # would break the equal-size rule? no: same count
+    r = rng(12)
+    ins = [O.f32_to_bf16_bits(r.standard_normal((33, 17, 5), dtype=np.float32)), r.standard_normal((17, 1), dtype=np.float32)]
+    got, plan = _run(ctx, g, ins)
+    assert "tier 1" in plan.description
+    want = O.evaluate(g, ins)
+    _close(g, got[:2] + got[3:], want[:2] + want[3:], 1e-2)
+    # the comparison may flip where t == yb up to rounding; demand equality away from ties
+    tv = O.decode(want[0], ir.BF16, (33, 17, 5)).reshape(-1)
+    yv = np.broadcast_to(ins[1].reshape(1, 17, 1), (33, 17, 5)).reshape(-1)
+    far = np.abs(tv - yv) > 1e-2 * np.maximum(1.0, np.abs(yv))
+    gb = O.unpack_bools(got[2], tv.size)
+    wb = O.unpack_bools(want[2], tv.size)
+    assert np.array_equal(gb[far], wb[far])
+
+
+@pytest.mark.parametrize("shape,depth,op", [
+    ((256, 10), 1, ir.RED_MAX), ((256, 10), 1, ir.RED_SUM), ((256, 10), 2, ir.RED_SUM),
+    ((2, 1000, 100), 2, ir.RED_SUM), ((2, 1000, 100), 3, ir.RED_MEAN), ((7, 5000), 1, ir.RED_MIN),
+    ((3, 70000), 1, ir.RED_SUM), ((1, 1 << 20), 2, ir.RED_MEAN),
+])
+def test_reductions(ctx, shape, depth, op):
+    g = ir.Graph()
+    x = g.new_input(list(shape), ir.F32)
+    g.new_output(g.reduce(op, g.binary(ir.BIN_MUL, x, x), depth))
+    ins = [rng(13).standard_normal(shape, dtype=np.float32)]
+    got, plan = _run(ctx, g, ins)
+    want = O.evaluate(g, ins)
+    a, b = got[0].reshape(-1).astype(np.float64), want[0].reshape(-1).astype(np.float64)
+    assert O.rel_l2(a, b) <= 1e-5, (O.rel_l2(a, b), plan.description)   # f32 reductions: rel-L2 <= 1e-5
+    # bit-stable across launches (fixed summation order; helium/tests/stress_test.rs:38 asks for this)
+    got2, _ = _run(ctx, g, ins)
+    assert np.array_equal(got[0], got2[0])
+
+
+def test_softmax_cross_entropy_pieces(ctx):
+    """The reductions of config 1's loss: row max, row sum of exp, and the scalar loss."""
+    g = ir.Graph()
+    z = g.new_input([256, 10], ir.F32)
+    t = g.new_input([256, 10], ir.F32)
+    m = g.new_input([256, 1], ir.F32)
+    zs = g.binary(ir.BIN_ADD, z, g.unary(ir.UN_NEG, g.broadcast_to(m, [256, 10])))
+    e = g.unary(ir.UN_EXP, zs)
+    g.new_output(g.reduce(ir.RED_SUM, e, 1))
+    r = rng(14)
+    zv = r.standard_normal((256, 10), dtype=np.float32) * 3
+    onehot = np.eye(10, dtype=np.float32)[r.integers(0, 10, 256)]
+    ins = [zv, onehot, zv.max(1, keepdims=True)]
+    got, _ = _run(ctx, g, ins)
+    want = O.evaluate(g, ins)
+    assert O.rel_l2(got[0], want[0]) <= 1e-5
