@@ -56,7 +56,7 @@ def load_traffic(name: str):
 
 # ---- clock sampling during the timed region ----------------------------------------------------------
 class ClockSampler:
-    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+    FIELDS = ("utilization.gpu,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
               "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, gpu_id: str):
@@ -85,20 +85,30 @@ class ClockSampler:
             self.proc.wait(timeout=2)
         except Exception:
             self.proc.kill()
-        sm, mx, reasons = [], [], set()
+        sm, mx, power, reasons = [], [], [], set()
+        total = 0
         for ln in self.lines:
             f = [x.strip() for x in ln.split(",")]
             if len(f) < 9:
                 continue
             try:
-                sm.append(float(f[1])); mx.append(float(f[2]))
+                util, clk, cmax = float(f[0]), float(f[1]), float(f[2])
             except ValueError:
                 continue
+            total += 1
+            if util <= 0:
+                continue  # idle sample (before the first launch / between legs)
+            sm.append(clk); mx.append(cmax)
+            try:
+                power.append(float(f[3]))
+            except ValueError:
+                pass
             for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
                 if v.lower().startswith("active"):
                     reasons.add(name)
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": sorted(reasons), "samples": len(sm)}
+                "reasons": sorted(reasons), "samples_under_load": len(sm), "samples": total,
+                "power_w_max": max(power) if power else None}
 
 
 # ---- workloads ---------------------------------------------------------------------------------------
@@ -137,7 +147,7 @@ def run_reference_arm(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c2", choices=["c2", "c3"])
@@ -267,16 +277,23 @@ def main():
         l2_note = "256 MiB buffer written between iterations to flush L2 (inside the timed region; its ~40 us are included)"
 
     # ---- warm-up, then the timed region ------------------------------------------------------------
-    for _ in range(args.warmup):
-        step()
-    barrier()
     try:
         gpu_id = "GPU-" + str(torch.cuda.get_device_properties(local_rank).uuid)
     except Exception:
         gpu_id = str(local_rank)
+    # nvidia-smi needs ~0.2 s to deliver its first sample, so it is started before the warm-up and
+    # read until the end-to-end leg finishes; only samples taken while the GPU was busy are used
     sampler = ClockSampler(gpu_id)
     if rank == 0:
         sampler.start()
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    # keep the device busy long enough for the clock record to cover the measurement
+    t_busy = time.perf_counter()
+    while time.perf_counter() - t_busy < 0.6:
+        step()
+        torch.cuda.synchronize()
     records = []
     t_start = torch.cuda.Event(enable_timing=True); t_end = torch.cuda.Event(enable_timing=True)
     barrier()
@@ -285,7 +302,6 @@ def main():
         step(records)
     t_end.record()
     barrier()
-    clocks = sampler.stop() if rank == 0 else None
     elapsed_ms = t_start.elapsed_time(t_end)
     if world > 1:
         t = torch.tensor([elapsed_ms], device=dev, dtype=torch.float64)
@@ -310,6 +326,7 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_sec = float(t.item())
 
+    clocks = sampler.stop() if rank == 0 else None
     if rank == 0:
         name, work, bound, peak, punit, traffic_key = dominant
         achieved = work / (kernel_ms * 1e-3) / (1e9 if bound == "hbm" else 1e12)
