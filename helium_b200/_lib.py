@@ -59,6 +59,17 @@ SIGNATURES = {
     "he_plan_last_launch_count": (C.c_int32, [C.c_void_p]),
     "he_plan_describe": (C.c_char_p, [C.c_void_p]),
     "he_plan_destroy": (None, [C.c_void_p]),
+    "heh_graph_create": (C.c_int32, [C.POINTER(C.c_void_p)]),
+    "heh_graph_destroy": (None, [C.c_void_p]),
+    "heh_graph_new_input": (C.c_int32, [C.c_void_p, C.c_int32, C.c_int32, C.POINTER(C.c_int64), C.POINTER(C.c_int32)]),
+    "heh_graph_new_op": (C.c_int32, [C.c_void_p, C.POINTER(HeNode), C.POINTER(C.c_int32)]),
+    "heh_graph_new_output": (C.c_int32, [C.c_void_p, C.c_int32]),
+    "heh_graph_plan_text": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_char_p, C.c_size_t]),
+    "heh_exec_create": (C.c_int32, [C.c_void_p, C.c_void_p, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.c_int32,
+                                    C.POINTER(C.c_void_p)]),
+    "heh_exec_run": (C.c_int32, [C.c_void_p, C.c_void_p]),
+    "heh_exec_stats": (C.c_int32, [C.c_void_p, C.POINTER(C.c_int32), C.POINTER(C.c_int32), C.POINTER(C.c_int32)]),
+    "heh_exec_destroy": (None, [C.c_void_p]),
     "he_debug_dump_program": (C.c_int32, [C.POINTER(HeGraphDesc), C.c_int32, C.c_void_p, C.c_size_t, C.POINTER(C.c_size_t)]),
     "he_debug_canonical_text": (C.c_int32, [C.POINTER(HeGraphDesc), C.c_char_p, C.c_size_t]),
     "he_last_error_string": (C.c_char_p, []),

@@ -32,6 +32,7 @@ SOURCES = [
     "gemm_kernels_c3.cu",
     "gemm_kernels_prog.cu",
     "sgemm.cu",
+    "host_graph.cu",
 ]
 
 NVCC_FLAGS = [

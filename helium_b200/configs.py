@@ -177,3 +177,65 @@ def c3_inputs(m: int, n: int, k: int, with_e: bool = False, seed: int = 2):
     if with_e:
         ins += [bf16_normal(r, (1, m, n)), bf16_normal(r, (1, m, n))]
     return ins
+
+
+def graph_mlp_train_step(batch: int = 256, d_in: int = 784, d_hidden: int = 512, d_out: int = 10, lr: float = 0.01):
+    """configs[0]: one SGD step of the MLP 784 -> 512 -> 10 (ReLU, softmax cross-entropy) in f32,
+    recorded op by op the way helium's front end would: `Linear::forward` (modules/linear.rs:44-57),
+    `cross_entropy_loss` / `log_softmax` (loss.rs:5-8, tensor.rs:584-592), the backward formulas of
+    tensor.rs:316-580 (matmul: dA = flow @ B^T, dB = A^T @ flow, tensor.rs:446-447; relu:
+    select(x < 0, 0, 1) * flow, tensor.rs:374-387; broadcast: sum over the broadcast axis) and
+    `Sgd::step` without momentum (optimizer/sgd.rs:48).
+
+    Inputs: x [B,d_in], targets (one-hot) [B,d_out], W1 [d_in,H], b1 [H], W2 [H,d_out], b2 [d_out].
+    Outputs: loss [1], W1', b1', W2', b2'."""
+    g = ir.Graph()
+    F = ir.F32
+    B, H, O = batch, d_hidden, d_out
+    x = g.new_input([B, d_in], F)
+    t = g.new_input([B, O], F)
+    w1 = g.new_input([d_in, H], F)
+    b1 = g.new_input([H], F)
+    w2 = g.new_input([H, O], F)
+    b2 = g.new_input([O], F)
+    prec = ir.PREC_TF32_F32
+    # forward
+    z1 = g.binary(ir.BIN_ADD, g.matmul(x, w1, prec), g.broadcast_to(b1, [B, H]))
+    h = g.unary(ir.UN_RELU, z1)
+    z2 = g.binary(ir.BIN_ADD, g.matmul(h, w2, prec), g.broadcast_to(b2, [B, O]))
+    mx = g.broadcast_to(g.reduce(ir.RED_MAX, z2, 1), [B, O])
+    zs = g.binary(ir.BIN_ADD, z2, g.unary(ir.UN_NEG, mx))
+    se = g.reduce(ir.RED_SUM, g.unary(ir.UN_EXP, zs), 1)                       # [B,1]
+    ls = g.binary(ir.BIN_ADD, zs, g.unary(ir.UN_NEG, g.broadcast_to(g.unary(ir.UN_LOG, se), [B, O])))
+    prod = g.binary(ir.BIN_MUL, ls, t)
+    total = g.reduce(ir.RED_SUM, prod, 2)                                       # [1]
+    loss = g.binary(ir.BIN_MUL, g.unary(ir.UN_NEG, total), g.constant(1.0 / B, [1]))
+    # backward: d loss / d z2 = (softmax - t * sum(t)) / B; targets are one-hot so sum(t) = 1
+    sm = g.unary(ir.UN_EXP, ls)
+    dz2 = g.binary(ir.BIN_MUL, g.binary(ir.BIN_ADD, sm, g.unary(ir.UN_NEG, t)), g.constant(1.0 / B, [B, O]))
+    dw2 = g.matmul(g.transpose(h), dz2, prec)                                   # [H,O]
+    db2 = g.reshape(g.reduce(ir.RED_SUM, g.transpose(dz2), 1), [O])             # sum over the batch
+    dh = g.matmul(dz2, g.transpose(w2), prec)                                   # [B,H]
+    neg = g.compare(ir.CMP_LT, z1, g.constant(0.0, [B, H]))
+    dz1 = g.binary(ir.BIN_MUL, g.select(g.constant(1.0, [B, H]), g.constant(0.0, [B, H]), neg), dh)
+    dw1 = g.matmul(g.transpose(x), dz1, prec)                                   # [d_in,H]
+    db1 = g.reshape(g.reduce(ir.RED_SUM, g.transpose(dz1), 1), [H])
+    # SGD: w - g * lr
+    def sgd(w, grad, shape):
+        return g.binary(ir.BIN_ADD, w, g.unary(ir.UN_NEG, g.binary(ir.BIN_MUL, grad, g.constant(lr, shape))))
+    outs = [loss, sgd(w1, dw1, [d_in, H]), sgd(b1, db1, [H]), sgd(w2, dw2, [H, O]), sgd(b2, db2, [O])]
+    for o in outs:
+        g.new_output(o)
+    return g
+
+
+def mlp_inputs(batch: int = 256, d_in: int = 784, d_hidden: int = 512, d_out: int = 10, seed: int = 0):
+    """x ~ U[-1,1], labels uniform -> one-hot, weights N(0, 1/sqrt(fan_out)) (helium's "Kaiming",
+    initializer.rs:29-31,48-50), biases zero."""
+    r = rng(seed)
+    x = (r.random((batch, d_in), dtype=np.float32) * 2 - 1).astype(np.float32)
+    labels = r.integers(0, d_out, batch)
+    t = np.eye(d_out, dtype=np.float32)[labels]
+    w1 = (r.standard_normal((d_in, d_hidden), dtype=np.float32) / np.float32(np.sqrt(d_hidden))).astype(np.float32)
+    w2 = (r.standard_normal((d_hidden, d_out), dtype=np.float32) / np.float32(np.sqrt(d_out))).astype(np.float32)
+    return [x, t, w1, np.zeros(d_hidden, np.float32), w2, np.zeros(d_out, np.float32)]

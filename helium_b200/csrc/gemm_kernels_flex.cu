@@ -29,9 +29,13 @@ __global__ void gemm_scalar_finalize(const float* __restrict__ partials, float* 
 }
 
 int32_t launch_gemm_flex(const GemmLaunchCfg& cfg, const GemmParams<EpiFlexParams>& p, cudaStream_t stream) {
+  if (cfg.two_cta && cfg.bn == 256) {
+    if (cfg.ml == ML_NONE) return launch_majors_2cta<6, ML_NONE, 8, EpiFlex>(cfg, p, stream);
+    if (cfg.ml == ML_RELU_MASK) return launch_majors_2cta<4, ML_RELU_MASK, 8, EpiFlex>(cfg, p, stream);
+  }
   if (cfg.bn == 256) {
-    if (cfg.ml == ML_NONE) return launch_majors<256, 4, ML_NONE, 4, EpiFlex>(cfg, p, stream);
-    if (cfg.ml == ML_RELU_MASK) return launch_majors<256, 3, ML_RELU_MASK, 4, EpiFlex>(cfg, p, stream);
+    if (cfg.ml == ML_NONE) return launch_majors<256, 4, ML_NONE, 8, EpiFlex>(cfg, p, stream);
+    if (cfg.ml == ML_RELU_MASK) return launch_majors<256, 3, ML_RELU_MASK, 8, EpiFlex>(cfg, p, stream);
   } else if (cfg.bn == 128) {
     if (cfg.ml == ML_NONE) return launch_majors<128, 6, ML_NONE, 4, EpiFlex>(cfg, p, stream);
   }

@@ -4,6 +4,10 @@
 namespace he {
 
 int32_t launch_gemm_program(const GemmLaunchCfg& cfg, const GemmParams<EpiProgramParams>& p, cudaStream_t stream) {
+  if (cfg.two_cta && cfg.bn == 256) {
+    if (cfg.ml == ML_NONE) return launch_majors_2cta<6, ML_NONE, 8, EpiProgram>(cfg, p, stream);
+    if (cfg.ml == ML_RELU_MASK) return launch_majors_2cta<4, ML_RELU_MASK, 8, EpiProgram>(cfg, p, stream);
+  }
   if (cfg.bn == 256) {
     if (cfg.ml == ML_NONE) return launch_majors<256, 4, ML_NONE, 8, EpiProgram>(cfg, p, stream);
     if (cfg.ml == ML_RELU_MASK) return launch_majors<256, 3, ML_RELU_MASK, 8, EpiProgram>(cfg, p, stream);

@@ -396,7 +396,7 @@ struct MatmulPlan : he_plan {
     CUtensorMap ta, tb, tm;
     memset(&tm, 0, sizeof tm);
     HE_TRY(make_operand_tmap(&ta, inputs[a_slot], core.ab_format, cfg.a_mn, core.M, core.K, core.batch, kBM));
-    HE_TRY(make_operand_tmap(&tb, inputs[b_slot], core.ab_format, cfg.b_mn, core.N, core.K, core.batch, cfg.bn));
+    HE_TRY(make_operand_tmap(&tb, inputs[b_slot], core.ab_format, cfg.b_mn, core.N, core.K, core.batch, cfg.two_cta ? 128 : cfg.bn));
     if (mask_slot >= 0) HE_TRY(make_operand_tmap(&tm, inputs[mask_slot], core.ab_format, cfg.a_mn, core.M, core.K, core.batch, kBM));
     GemmCore c = core;
     c.status = ctx ? ctx->d_status : nullptr;
@@ -537,6 +537,12 @@ int32_t plan_fused_matmul(he_ctx* ctx, const Graph& g, he_plan** out, int* tier_
   if (!((An.dtype == HE_BF16 && Bn.dtype == HE_BF16) || (An.dtype == HE_F16 && Bn.dtype == HE_F16)))
     HE_FAIL(HE_ERR_UNSUPPORTED, "fused matmul: operands must both be bf16, both f16 or both f32 (got %s x %s)", dtype_name(An.dtype), dtype_name(Bn.dtype));
   c.ab_format = An.dtype == HE_BF16 ? 1 : 0;
+  {
+    const char* dbg = getenv("HE_GEMM_DEBUG");
+    c.debug = dbg ? atoi(dbg) : 0;
+    const char* pf = getenv("HE_GEMM_PREFETCH");
+    c.prefetch_kb = pf ? atoi(pf) : 0;
+  }
   if (plan->cfg.ml != ML_NONE && plan->cfg.ml != ML_RELU_MASK)
     HE_FAIL(HE_ERR_UNSUPPORTED, "fused matmul: only the relu(A) * mask mainloop fusion is compiled in");
   if (plan->cfg.ml != ML_NONE && (An.dtype != HE_BF16 || g.nodes[A.mask].dtype != HE_BF16))
@@ -557,12 +563,24 @@ int32_t plan_fused_matmul(he_ctx* ctx, const Graph& g, he_plan** out, int* tier_
     HE_FAIL(HE_ERR_UNSUPPORTED, "fused matmul: epilogue outputs must have the matmul's element count");
 
   plan->cfg.bn = 256;
+  plan->cfg.two_cta = false;
   auto finish_tiles = [&]() {
     c.tiles_m = (c.M + kBM - 1) / kBM;
     c.tiles_n = (c.N + plan->cfg.bn - 1) / plan->cfg.bn;
-    c.num_tiles = c.tiles_m * c.tiles_n * c.batch;
     c.k_blocks = (c.K + kBK - 1) / kBK;
-    plan->cfg.grid = std::max(1, std::min(c.num_tiles, ctx_sm_count(ctx)));
+    // Two SMs per 256 x 256 tile whenever there are at least two row tiles to pair up; the
+    // environment switch keeps the single-CTA kernel reachable for comparisons.
+    const char* force1 = getenv("HE_GEMM_ONE_CTA");
+    plan->cfg.two_cta = plan->cfg.bn == 256 && c.tiles_m >= 2 && !(force1 && force1[0] == '1');
+    if (plan->cfg.two_cta) {
+      const int tiles_m2 = (c.M + 255) / 256;
+      c.tiles_m = 2 * tiles_m2;                       // partial-sum rows: the odd CTA of the last pair may be empty
+      c.num_tiles = c.tiles_m * c.tiles_n * c.batch;  // one scalar partial per CTA tile
+      plan->cfg.grid = 2 * std::max(1, std::min(tiles_m2 * c.tiles_n * c.batch, ctx_sm_count(ctx) / 2));
+    } else {
+      c.num_tiles = c.tiles_m * c.tiles_n * c.batch;
+      plan->cfg.grid = std::max(1, std::min(c.num_tiles, ctx_sm_count(ctx)));
+    }
   };
   auto out_dt = [&](int out_idx) { return g.nodes[g.outputs[out_idx]].dtype; };
   auto in_dt = [&](int slot) { return g.nodes[g.inputs[slot]].dtype; };
@@ -609,8 +627,8 @@ int32_t plan_fused_matmul(he_ctx* ctx, const Graph& g, he_plan** out, int* tier_
       plan->workspace_bytes = (size_t)c.batch * c.tiles_m * c.N * sizeof(float);
     }
     snprintf(desc, sizeof desc,
-             "fused matmul tier 2: tcgen05 128x%dx64, %s-major A, %s-major B, mainloop %d, epilogue flex(bias=%d resid=%d act=%d gate=%d z=%d colsum=%d), grid %d",
-             plan->cfg.bn, plan->cfg.a_mn ? "M" : "K", plan->cfg.b_mn ? "N" : "K", plan->cfg.ml, plan->f_bias >= 0, plan->f_resid >= 0,
+             "fused matmul tier 2: tcgen05 %sx%dx64, %s-major A, %s-major B, mainloop %d, epilogue flex(bias=%d resid=%d act=%d gate=%d z=%d colsum=%d), grid %d",
+             plan->cfg.two_cta ? "2-CTA 256" : "128", plan->cfg.bn, plan->cfg.a_mn ? "M" : "K", plan->cfg.b_mn ? "N" : "K", plan->cfg.ml, plan->f_bias >= 0, plan->f_resid >= 0,
              f.act, f.gate, plan->f_z >= 0, f.colsum_src, plan->cfg.grid);
     plan->description = desc;
     *out = guard.release();
@@ -664,8 +682,8 @@ int32_t plan_fused_matmul(he_ctx* ctx, const Graph& g, he_plan** out, int* tier_
       plan->ws_scalar_off = 2 * col;
       plan->workspace_bytes = (2 * col + (size_t)c.num_tiles) * sizeof(float);
       snprintf(desc, sizeof desc,
-               "fused matmul tier 2: tcgen05 128x256x64, %s-major A, %s-major B, mainloop %d, epilogue README graph (loss + 2 column sums + 2 tiles%s), grid %d",
-               plan->cfg.a_mn ? "M" : "K", plan->cfg.b_mn ? "N" : "K", plan->cfg.ml, with_e ? ", E1/E2" : "", plan->cfg.grid);
+               "fused matmul tier 2: tcgen05 %sx256x64, %s-major A, %s-major B, mainloop %d, epilogue README graph (loss + 2 column sums + 2 tiles%s), grid %d",
+               plan->cfg.two_cta ? "2-CTA 256" : "128", plan->cfg.a_mn ? "M" : "K", plan->cfg.b_mn ? "N" : "K", plan->cfg.ml, with_e ? ", E1/E2" : "", plan->cfg.grid);
       plan->description = desc;
       *out = guard.release();
       return HE_OK;
@@ -686,8 +704,8 @@ int32_t plan_fused_matmul(he_ctx* ctx, const Graph& g, he_plan** out, int* tier_
     plan->kind = EpiKind::Program;
     finish_tiles();
     snprintf(desc, sizeof desc,
-             "fused matmul tier 1: tcgen05 128x256x64, %s-major A, %s-major B, mainloop %d, interpreted epilogue (%d instr), grid %d",
-             plan->cfg.a_mn ? "M" : "K", plan->cfg.b_mn ? "N" : "K", plan->cfg.ml, plan->prog.prog.n_instr, plan->cfg.grid);
+             "fused matmul tier 1: tcgen05 %sx256x64, %s-major A, %s-major B, mainloop %d, interpreted epilogue (%d instr), grid %d",
+             plan->cfg.two_cta ? "2-CTA 256" : "128", plan->cfg.a_mn ? "M" : "K", plan->cfg.b_mn ? "N" : "K", plan->cfg.ml, plan->prog.prog.n_instr, plan->cfg.grid);
     plan->description = desc;
     *out = guard.release();
     return HE_OK;

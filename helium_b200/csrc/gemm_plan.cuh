@@ -9,7 +9,8 @@ struct GemmLaunchCfg {
   bool a_mn;     // A operand is M-major in global memory ([K, M] row-major)
   bool b_mn;     // B operand is N-major in global memory ([K, N] row-major, the helium layout)
   int ml;        // MainloopKind
-  int grid;
+  int grid;      // CTAs
+  bool two_cta;  // cluster-of-2 kernel (256 x 256 pair tiles); grid is then even
 };
 
 // One function per epilogue family; each switches over the instantiated (bn, majors, ml) set and

@@ -33,6 +33,8 @@ struct GemmCore {
   int M, N, K, batch;
   int tiles_m, tiles_n, num_tiles, k_blocks;
   int ab_format;  // 0 = f16, 1 = bf16
+  int prefetch_kb; // k-blocks of L2 prefetch distance (0 = off)
+  int debug;      // timing experiments only (HE_GEMM_DEBUG): bit 0 skips the mainloop rewrite, bit 1 its proxy fence
   DeviceStatus* status;
 };
 
@@ -182,6 +184,25 @@ struct EpiFlexParams {
   int vec_ok;
 };
 
+// erf by Abramowitz & Stegun 7.1.26 (|error| <= 1.5e-7, below f32 rounding of the results it feeds):
+// one reciprocal, one exp2 and a 5-term Horner chain instead of libm's branchy erff.  Used only in
+// the GEMM epilogues, where the functor shares the SM with the tensor pipe.
+__device__ __forceinline__ float fast_erf(float x) {
+  const float ax = fabsf(x);
+  const float t = __fdividef(1.0f, fmaf(0.3275911f, ax, 1.0f));
+  float poly = fmaf(1.061405429f, t, -1.453152027f);
+  poly = fmaf(poly, t, 1.421413741f);
+  poly = fmaf(poly, t, -0.284496736f);
+  poly = fmaf(poly, t, 0.254829592f);
+  const float y = 1.0f - poly * t * __expf(-ax * ax);
+  return copysignf(y, x);
+}
+__device__ __forceinline__ float fast_gelu(float x) { return 0.5f * x * (1.0f + fast_erf(x * 0.70710678118654752440f)); }
+__device__ __forceinline__ float fast_dgelu(float x) {
+  const float cdf = 0.5f * (1.0f + fast_erf(x * 0.70710678118654752440f));
+  return fmaf(x * 0.39894228040143267794f, __expf(-0.5f * x * x), cdf);
+}
+
 struct EpiFlex {
   using Params = EpiFlexParams;
   static constexpr int kColReductions = 1;
@@ -191,14 +212,14 @@ struct EpiFlex {
   __device__ static float activation(int act, float x) {
     switch (act) {
       case ACT_RELU: return fmaxf(x, 0.0f);
-      case ACT_GELU: return pw_gelu(x);
+      case ACT_GELU: return fast_gelu(x);
       case ACT_TANH: return tanhf(x);
       default: return x;
     }
   }
   __device__ static float gate_fn(int g, float x) {
     switch (g) {
-      case GATE_DGELU: return pw_dgelu(x);
+      case GATE_DGELU: return fast_dgelu(x);
       case GATE_DRELU: return x > 0.0f ? 1.0f : 0.0f;
       case GATE_DTANH: return 1.0f - x * x;  // x is tanh(z)
       default: return x;
@@ -443,11 +464,11 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmParams<typename Epi::Params> p) 
     for (int s = 0; s < STAGES; ++s) {
       ptx::mbar_init(bar_full(s), 1);
       ptx::mbar_init(bar_empty(s), 1);
-      ptx::mbar_init(bar_xform(s), 128);
+      ptx::mbar_init(bar_xform(s), 4);              // one arrival per transform warp
     }
     for (int a = 0; a < 2; ++a) {
       ptx::mbar_init(bar_tmem_full(a), 1);
-      ptx::mbar_init(bar_tmem_empty(a), NE_WARPS * 32);
+      ptx::mbar_init(bar_tmem_empty(a), NE_WARPS);  // one arrival per epilogue warp
     }
     ptx::fence_mbar_init();
   }
@@ -491,6 +512,21 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmParams<typename Epi::Params> p) 
           if (!ptx::mbar_wait(bar_empty(stage), phase ^ 1u, abort_flag, c.status, 1, stage)) { alive = false; break; }
           ptx::mbar_arrive_expect_tx(bar_full(stage), kStageBytes);
           const int k0 = kb * kBK;
+          if (c.prefetch_kb > 0 && kb + c.prefetch_kb < c.k_blocks) {
+            const int kp = k0 + c.prefetch_kb * kBK;
+            if (A_MN) { ptx::tma_prefetch_l2_3d(&p.tma_a, t.m0, kp, t.b); ptx::tma_prefetch_l2_3d(&p.tma_a, t.m0 + 64, kp, t.b); }
+            else ptx::tma_prefetch_l2_3d(&p.tma_a, kp, t.m0, t.b);
+            if (SM::kHasMask) {
+              if (A_MN) { ptx::tma_prefetch_l2_3d(&p.tma_mask, t.m0, kp, t.b); ptx::tma_prefetch_l2_3d(&p.tma_mask, t.m0 + 64, kp, t.b); }
+              else ptx::tma_prefetch_l2_3d(&p.tma_mask, kp, t.m0, t.b);
+            }
+            if (B_MN) {
+#pragma unroll
+              for (int j = 0; j < BN / 64; ++j) ptx::tma_prefetch_l2_3d(&p.tma_b, t.n0 + 64 * j, kp, t.b);
+            } else {
+              ptx::tma_prefetch_l2_3d(&p.tma_b, kp, t.n0, t.b);
+            }
+          }
           const uint32_t a_dst = smem_base + SM::off_a + stage * kATileBytes;
           const uint32_t b_dst = smem_base + SM::off_b + stage * SM::kBTileBytes;
           if (A_MN) {
@@ -579,6 +615,7 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmParams<typename Epi::Params> p) 
       // After an abandoned wait the thread keeps walking the tile list without touching TMEM so
       // that the named barriers inside tile_end() still see every epilogue thread.
       if (!dead && !ptx::mbar_wait(bar_tmem_full(acc), acc_phase, abort_flag, c.status, 4, acc)) dead = true;
+      dead = __any_sync(0xffffffffu, dead);   // the warp decides together (it shares a __syncwarp below)
       typename Epi::State st;
       Epi::tile_begin(st);
       if (!dead) {
@@ -593,7 +630,8 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmParams<typename Epi::Params> p) 
           Epi::chunk(p.epi, env, t, st, row, col, v);
         }
         ptx::tcgen05_fence_before();
-        ptx::mbar_arrive(bar_tmem_empty(acc));
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(bar_tmem_empty(acc));   // 128+ arrivals on one word would serialise
       }
       Epi::tile_end(p.epi, env, t, st);
     }
@@ -606,11 +644,13 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmParams<typename Epi::Params> p) 
       bool alive = true;
       for (int tile = blockIdx.x; alive && tile < c.num_tiles; tile += gridDim.x) {
         for (int kb = 0; kb < c.k_blocks; ++kb) {
-          if (!ptx::mbar_wait(bar_full(stage), phase, abort_flag, c.status, 5, stage)) { alive = false; break; }
+          const bool ok = ptx::mbar_wait(bar_full(stage), phase, abort_flag, c.status, 5, stage);
+          if (!__all_sync(0xffffffffu, ok)) { alive = false; break; }
           uint4* a = reinterpret_cast<uint4*>(smem + SM::off_a + stage * kATileBytes);
           const uint4* mk = reinterpret_cast<const uint4*>(smem + SM::off_mask + stage * kATileBytes);
           // A and the mask were loaded with the same box and swizzle, so equal smem offsets hold
           // the same (row, k) element: the rewrite is position-wise.
+          if (!(c.debug & 1))
 #pragma unroll
           for (int i = 0; i < kATileBytes / 16 / 128; ++i) {
             const int idx = tt + i * 128;
@@ -629,8 +669,9 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmParams<typename Epi::Params> p) 
             }
             a[idx] = va;
           }
-          ptx::fence_proxy_async_smem();
-          ptx::mbar_arrive(bar_xform(stage));
+          if (!(c.debug & 2)) ptx::fence_proxy_async_smem();   // every writer publishes its own stores to the async proxy
+          __syncwarp();
+          if (lane == 0) ptx::mbar_arrive(bar_xform(stage));
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
       }

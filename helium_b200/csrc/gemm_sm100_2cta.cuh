@@ -1,0 +1,357 @@
+// Two-CTA variant of the tcgen05 GEMM core: a cluster of two CTAs (two SMs) works on one
+// 256 x 256 output tile with `tcgen05.mma.cta_group::2`.  Each CTA owns 128 rows of A (and of the
+// mainloop mask) and loads only half of the B tile (128 of the 256 columns); the tensor cores of
+// both SMs read both halves.  Per SM and k-block that is 32 KB of operands instead of 48 KB
+// (48 KB instead of 64 KB with a mask tile), which is what the L2 -> SM path can sustain, and the
+// shared-memory ring gets six stages instead of four (four instead of three with a mask).
+//
+// No load uses cluster multicast: each CTA fetches its own boxes with `.cta_group::2` TMA loads
+// whose mbarrier is the leader CTA's.  Cross-CTA signalling uses remote mbarrier arrives and
+// `tcgen05.commit` to the peer's barrier.
+#pragma once
+#include "gemm_sm100.cuh"
+
+namespace he {
+namespace ptx {
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// shared::cluster address of the same shared-memory offset in CTA `rank` of this cluster
+__device__ __forceinline__ uint32_t mapa(uint32_t smem_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tma_load_3d_2cta(uint32_t dst, const CUtensorMap* m, uint32_t leader_bar, int c0, int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(leader_bar), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_2cta(uint32_t dst_smem, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_2cta() { asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_dealloc_2cta(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void umma_f16_2cta(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t"
+      "}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// `bar` is a shared::cluster address (own or peer CTA)
+__device__ __forceinline__ void umma_commit_2cta(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+}  // namespace ptx
+
+constexpr int kBN2 = 256;            // N of the pair tile
+constexpr int kBHalfBytes = 128 * kBK * 2;   // this CTA's half of the B tile: 16 KiB
+
+template <int STAGES, int ML, int N_COLRED>
+struct GemmSmem2 {
+  static constexpr bool kHasMask = (ML & ML_MASK) != 0;
+  static constexpr int off_a = 0;
+  static constexpr int off_b = off_a + STAGES * kATileBytes;
+  static constexpr int off_mask = off_b + STAGES * kBHalfBytes;
+  static constexpr int off_scratch = off_mask + (kHasMask ? STAGES * kATileBytes : 0);
+  static constexpr int scratch_bytes = (N_COLRED * 4 * kBN2 + 16) * 4;
+  static constexpr int off_bar = off_scratch + scratch_bytes;
+  // full_b[S] (leader), full_a[S] (local, mainloop fusion only), empty[S] (local), xform[S] (leader),
+  // tmem_full[2] (local), tmem_empty[2] (leader)
+  static constexpr int n_bars = 4 * STAGES + 4;
+  static constexpr int off_misc = off_bar + n_bars * 8;
+  static constexpr int total = off_misc + 16;
+  static constexpr int dynamic_bytes = total + 1024;
+};
+
+template <int STAGES, bool A_MN, bool B_MN, int ML, int NE_WARPS, class Epi>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(32 * (2 + NE_WARPS + (ML != ML_NONE ? 4 : 0)), 1)
+gemm_tcgen05_2cta_kernel(const __grid_constant__ GemmParams<typename Epi::Params> p) {
+  using SM = GemmSmem2<STAGES, ML, Epi::kColReductions>;
+  constexpr int BN = kBN2;
+  constexpr int kXformWarp0 = 2 + NE_WARPS;
+  constexpr int kTmemCols = 512;
+  constexpr int CH = Epi::kChunk;
+  constexpr bool kFused = ML != ML_NONE;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  const uint32_t smem_base = ptx::smem_u32(smem);
+  const uint32_t bar0 = smem_base + SM::off_bar;
+  auto bar_full_b = [&](int s) { return bar0 + 8u * s; };
+  auto bar_full_a = [&](int s) { return bar0 + 8u * (STAGES + s); };
+  auto bar_empty = [&](int s) { return bar0 + 8u * (2 * STAGES + s); };
+  auto bar_xform = [&](int s) { return bar0 + 8u * (3 * STAGES + s); };
+  auto bar_tmem_full = [&](int a) { return bar0 + 8u * (4 * STAGES + a); };
+  auto bar_tmem_empty = [&](int a) { return bar0 + 8u * (4 * STAGES + 2 + a); };
+  volatile uint32_t* tmem_holder = reinterpret_cast<volatile uint32_t*>(smem + SM::off_misc);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + SM::off_misc + 4);
+  float* scratch = reinterpret_cast<float*>(smem + SM::off_scratch);
+
+  const GemmCore& c = p.core;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = ptx::cluster_ctarank();   // 0 = leader
+  const bool leader = rank == 0;
+  const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+  const int tiles_m2 = (c.M + 255) / 256;
+  const int pair_tiles = tiles_m2 * c.tiles_n * c.batch;
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    for (int s = 0; s < STAGES; ++s) {
+      ptx::mbar_init(bar_full_b(s), 1);          // leader's arrive.expect_tx; bytes from both CTAs
+      ptx::mbar_init(bar_full_a(s), 1);          // local arrive.expect_tx (A + mask of this CTA)
+      ptx::mbar_init(bar_empty(s), 1);           // one tcgen05.commit per CTA, issued by the leader
+      ptx::mbar_init(bar_xform(s), 2 * 4);       // one arrival per transform warp of both CTAs
+    }
+    for (int a = 0; a < 2; ++a) {
+      ptx::mbar_init(bar_tmem_full(a), 1);
+      ptx::mbar_init(bar_tmem_empty(a), 2 * NE_WARPS);   // one arrival per epilogue warp of both CTAs
+    }
+    ptx::fence_mbar_init();
+  }
+  if (warp == 0 && lane == 0) {
+    ptx::prefetch_tmap(&p.tma_a);
+    ptx::prefetch_tmap(&p.tma_b);
+    if (SM::kHasMask) ptx::prefetch_tmap(&p.tma_mask);
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc_2cta(ptx::smem_u32(const_cast<uint32_t*>(tmem_holder)), kTmemCols);
+    ptx::tmem_relinquish_2cta();
+  }
+  ptx::tcgen05_fence_before();
+  __syncthreads();
+  ptx::cluster_sync();   // both CTAs' barriers are initialised before anyone signals across
+  ptx::tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+
+  // pair tile -> (batch, m2, n); this CTA's rows start at m2 * 256 + rank * 128
+  auto decode_tile = [&](int tile) {
+    TileInfo t;
+    const int per_batch = tiles_m2 * c.tiles_n;
+    t.b = tile / per_batch;
+    const int r = tile - t.b * per_batch;
+    t.tile_n = r / tiles_m2;
+    const int m2 = r - t.tile_n * tiles_m2;
+    t.tile_m = m2 * 2 + (int)rank;
+    t.m0 = t.tile_m * kBM;
+    t.n0 = t.tile_n * BN;
+    t.tile_idx = tile * 2 + (int)rank;
+    return t;
+  };
+
+  if (warp == 0) {
+    // ===================== TMA producer (both CTAs) =====================
+    if (lane == 0) {
+      constexpr uint32_t kABytes = kATileBytes + (SM::kHasMask ? kATileBytes : 0);
+      // bytes the leader's barrier sees per stage: both B halves, plus both A tiles when they are
+      // not routed through the local barrier
+      constexpr uint32_t kLeaderBytes = 2 * kBHalfBytes + (kFused ? 0 : 2 * kATileBytes);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool alive = true;
+      for (int tile = pair; alive && tile < pair_tiles; tile += n_pairs) {
+        const TileInfo t = decode_tile(tile);
+        for (int kb = 0; kb < c.k_blocks; ++kb) {
+          if (!ptx::mbar_wait(bar_empty(stage), phase ^ 1u, abort_flag, c.status, 1, stage)) { alive = false; break; }
+          const uint32_t leader_full = ptx::mapa(bar_full_b(stage), 0);
+          if (leader) ptx::mbar_arrive_expect_tx(bar_full_b(stage), kLeaderBytes);
+          if (kFused) ptx::mbar_arrive_expect_tx(bar_full_a(stage), kABytes);
+          const int k0 = kb * kBK;
+          const uint32_t a_dst = smem_base + SM::off_a + stage * kATileBytes;
+          const uint32_t b_dst = smem_base + SM::off_b + stage * kBHalfBytes;
+          if (c.prefetch_kb > 0 && kb + c.prefetch_kb < c.k_blocks) {
+            const int kp = k0 + c.prefetch_kb * kBK;
+            const int nbp = t.n0 + 128 * (int)rank;
+            if (A_MN) { ptx::tma_prefetch_l2_3d(&p.tma_a, t.m0, kp, t.b); ptx::tma_prefetch_l2_3d(&p.tma_a, t.m0 + 64, kp, t.b); }
+            else ptx::tma_prefetch_l2_3d(&p.tma_a, kp, t.m0, t.b);
+            if (SM::kHasMask) {
+              if (A_MN) { ptx::tma_prefetch_l2_3d(&p.tma_mask, t.m0, kp, t.b); ptx::tma_prefetch_l2_3d(&p.tma_mask, t.m0 + 64, kp, t.b); }
+              else ptx::tma_prefetch_l2_3d(&p.tma_mask, kp, t.m0, t.b);
+            }
+            if (B_MN) { ptx::tma_prefetch_l2_3d(&p.tma_b, nbp, kp, t.b); ptx::tma_prefetch_l2_3d(&p.tma_b, nbp + 64, kp, t.b); }
+            else ptx::tma_prefetch_l2_3d(&p.tma_b, kp, nbp, t.b);
+          }
+          // A (and the mask): this CTA's 128 rows
+          if (kFused) {
+            if (A_MN) {
+#pragma unroll
+              for (int j = 0; j < 2; ++j) ptx::tma_load_3d(a_dst + j * (kBK * 128), &p.tma_a, bar_full_a(stage), t.m0 + 64 * j, k0, t.b);
+            } else {
+              ptx::tma_load_3d(a_dst, &p.tma_a, bar_full_a(stage), k0, t.m0, t.b);
+            }
+            if (SM::kHasMask) {
+              const uint32_t m_dst = smem_base + SM::off_mask + stage * kATileBytes;
+              if (A_MN) {
+#pragma unroll
+                for (int j = 0; j < 2; ++j) ptx::tma_load_3d(m_dst + j * (kBK * 128), &p.tma_mask, bar_full_a(stage), t.m0 + 64 * j, k0, t.b);
+              } else {
+                ptx::tma_load_3d(m_dst, &p.tma_mask, bar_full_a(stage), k0, t.m0, t.b);
+              }
+            }
+          } else {
+            if (A_MN) {
+#pragma unroll
+              for (int j = 0; j < 2; ++j) ptx::tma_load_3d_2cta(a_dst + j * (kBK * 128), &p.tma_a, leader_full, t.m0 + 64 * j, k0, t.b);
+            } else {
+              ptx::tma_load_3d_2cta(a_dst, &p.tma_a, leader_full, k0, t.m0, t.b);
+            }
+          }
+          // B: this CTA's 128 columns of the 256-wide tile
+          const int nb0 = t.n0 + 128 * (int)rank;
+          if (B_MN) {
+#pragma unroll
+            for (int j = 0; j < 2; ++j) ptx::tma_load_3d_2cta(b_dst + j * (kBK * 128), &p.tma_b, leader_full, nb0 + 64 * j, k0, t.b);
+          } else {
+            ptx::tma_load_3d_2cta(b_dst, &p.tma_b, leader_full, k0, nb0, t.b);
+          }
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ===================== MMA issuer (leader CTA only) =====================
+    if (lane == 0 && leader) {
+      const uint32_t idesc = ptx::make_idesc_f16(c.ab_format, A_MN ? 1 : 0, B_MN ? 1 : 0, 256, BN);
+      constexpr uint32_t a_lbo = A_MN ? kBK * 128 : 16, b_lbo = B_MN ? kBK * 128 : 16;
+      constexpr uint32_t a_kadv = A_MN ? 2048 : 32, b_kadv = B_MN ? 2048 : 32;
+      int stage = 0;
+      uint32_t phase = 0;
+      int it = 0;
+      bool alive = true;
+      for (int tile = pair; alive && tile < pair_tiles; tile += n_pairs, ++it) {
+        const int acc = it & 1;
+        const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
+        if (!ptx::mbar_wait(bar_tmem_empty(acc), acc_phase ^ 1u, abort_flag, c.status, 2, acc)) { alive = false; break; }
+        ptx::tcgen05_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
+        for (int kb = 0; kb < c.k_blocks; ++kb) {
+          if (!ptx::mbar_wait(bar_full_b(stage), phase, abort_flag, c.status, 3, stage)) { alive = false; break; }
+          if (kFused && !ptx::mbar_wait(bar_xform(stage), phase, abort_flag, c.status, 6, stage)) { alive = false; break; }
+          ptx::tcgen05_fence_after();
+          const uint32_t a_addr = smem_base + SM::off_a + stage * kATileBytes;
+          const uint32_t b_addr = smem_base + SM::off_b + stage * kBHalfBytes;
+#pragma unroll
+          for (int k = 0; k < kBK / kUmmaK; ++k) {
+            const uint64_t adesc = ptx::make_smem_desc_sw128(a_addr + k * a_kadv, a_lbo, 1024);
+            const uint64_t bdesc = ptx::make_smem_desc_sw128(b_addr + k * b_kadv, b_lbo, 1024);
+            ptx::umma_f16_2cta(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          // free the stage in both CTAs once these MMAs retire
+          ptx::umma_commit_2cta(bar_empty(stage));
+          ptx::umma_commit_2cta(ptx::mapa(bar_empty(stage), 1));
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+        if (alive) {
+          ptx::umma_commit_2cta(bar_tmem_full(acc));
+          ptx::umma_commit_2cta(ptx::mapa(bar_tmem_full(acc), 1));
+        }
+      }
+    }
+  } else if (warp < kXformWarp0) {
+    // ===================== epilogue (both CTAs, own 128 rows x 256 columns) =====================
+    EpiEnv env;
+    env.core = &c;
+    env.scratch = scratch;
+    env.bn = BN;
+    env.n_epi_threads = NE_WARPS * 32;
+    env.epi_warp = warp - 2;
+    env.epi_tid = env.epi_warp * 32 + lane;
+    env.quadrant = warp & 3;
+    constexpr int kColsPerWarp = BN / (NE_WARPS / 4);
+    const int col_begin = (env.epi_warp / 4) * kColsPerWarp;
+    int it = 0;
+    bool dead = false;
+    for (int tile = pair; tile < pair_tiles; tile += n_pairs, ++it) {
+      const int acc = it & 1;
+      const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
+      const TileInfo t = decode_tile(tile);
+      if (!dead && !ptx::mbar_wait(bar_tmem_full(acc), acc_phase, abort_flag, c.status, 4, acc)) dead = true;
+      dead = __any_sync(0xffffffffu, dead);   // the warp decides together (it shares a __syncwarp below)
+      typename Epi::State st;
+      Epi::tile_begin(st);
+      if (!dead) {
+        ptx::tcgen05_fence_after();
+        const int row = env.quadrant * 32 + lane;
+#pragma unroll 1
+        for (int col = col_begin; col < col_begin + kColsPerWarp; col += CH) {
+          if (t.n0 + col >= c.N) break;
+          float v[CH];
+          const uint32_t taddr = tmem_base + ((uint32_t)(env.quadrant * 32) << 16) + (uint32_t)(acc * BN + col);
+          tmem_ld_chunk<CH>(taddr, v);
+          Epi::chunk(p.epi, env, t, st, row, col, v);
+        }
+        ptx::tcgen05_fence_before();
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive_cluster(ptx::mapa(bar_tmem_empty(acc), 0));
+      }
+      Epi::tile_end(p.epi, env, t, st);
+    }
+  } else {
+    // ===================== mainloop transform (both CTAs, own A tile) =====================
+    if (kFused) {
+      const int tt = (warp - kXformWarp0) * 32 + lane;
+      int stage = 0;
+      uint32_t phase = 0;
+      bool alive = true;
+      for (int tile = pair; alive && tile < pair_tiles; tile += n_pairs) {
+        for (int kb = 0; kb < c.k_blocks; ++kb) {
+          const bool ok = ptx::mbar_wait(bar_full_a(stage), phase, abort_flag, c.status, 5, stage);
+          if (!__all_sync(0xffffffffu, ok)) { alive = false; break; }
+          uint4* a = reinterpret_cast<uint4*>(smem + SM::off_a + stage * kATileBytes);
+          const uint4* mk = reinterpret_cast<const uint4*>(smem + SM::off_mask + stage * kATileBytes);
+          if (!(c.debug & 1))
+#pragma unroll
+          for (int i = 0; i < kATileBytes / 16 / 128; ++i) {
+            const int idx = tt + i * 128;
+            uint4 va = a[idx];
+            __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&va);
+            if (ML & ML_RELU) {
+              const __nv_bfloat162 z = __float2bfloat162_rn(0.0f);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) h[j] = __hmax2(h[j], z);
+            }
+            if (ML & ML_MASK) {
+              uint4 vm = mk[idx];
+              const __nv_bfloat162* hm = reinterpret_cast<const __nv_bfloat162*>(&vm);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) h[j] = __hmul2(h[j], hm[j]);
+            }
+            a[idx] = va;
+          }
+          if (!(c.debug & 2)) ptx::fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) ptx::mbar_arrive_cluster(ptx::mapa(bar_xform(stage), 0));
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+  }
+
+  // ---- teardown ---------------------------------------------------------------------------------
+  ptx::tcgen05_fence_before();
+  __syncthreads();
+  ptx::cluster_sync();   // the peer may still be signalling this CTA's barriers / reading its smem
+  if (warp == 1) {
+    ptx::tcgen05_fence_after();
+    ptx::tmem_dealloc_2cta(tmem_base, kTmemCols);
+  }
+}
+
+}  // namespace he

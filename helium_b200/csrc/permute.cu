@@ -15,6 +15,7 @@
 #include "device_utils.cuh"
 
 #include <algorithm>
+#include <cmath>
 
 namespace he {
 
@@ -99,7 +100,9 @@ struct TileParams {
   long long out_sX;      // output stride of X (elements); output stride of Y is 1
   int nb;
   long long b_ext[kMaxBatchDims], b_in[kMaxBatchDims], b_out[kMaxBatchDims];
-  int TX, TY, P;         // tile extents in elements, shared-memory pitch in 32-bit words
+  int TX, TY, P;         // tile extents in elements (powers of two), shared-memory pitch in 32-bit words
+  int lg_chunks_x;       // log2 of 16-byte chunks per tile row
+  int lg_y_blocks;       // log2(TY / 32)
   unsigned tiles_x, tiles_y;
   // affine functor
   int f_mode, f_batch, relu, has_scale, has_bias, s_dt, b_dt;
@@ -144,6 +147,8 @@ __device__ __forceinline__ float affine(float x, float s, float b, int relu) {
 }
 
 // XDT: -1 = plain permutation, otherwise the he_dtype of the element for the affine functor.
+// The host picks power-of-two tile extents, so every index decode below is a shift or a mask, and
+// offsets inside a tile are 32-bit (the planner routes tensors of 2^32 elements or more elsewhere).
 template <int EB, int XDT>
 __global__ void __launch_bounds__(kThreads) permute_tile_vec(const __grid_constant__ TileParams p) {
   extern __shared__ uint32_t sm[];
@@ -156,48 +161,68 @@ __global__ void __launch_bounds__(kThreads) permute_tile_vec(const __grid_consta
   blk /= p.tiles_y;
   const BatchOffsets bo = decode_batch(p, blk);
   const long long x0 = (long long)tx * p.TX, y0 = (long long)ty * p.TY;
-  const int TXW = p.TX / EPW;            // tile width in words
   const int P = p.P;
+  // rows / columns of this tile that exist (tiles at the border are partial)
+  const unsigned nx = (unsigned)min((long long)p.TX, p.X - x0), ny = (unsigned)min((long long)p.TY, p.Y - y0);
+  const char* in_tile = reinterpret_cast<const char*>(p.in) + (bo.in_base + y0 * p.in_sY + x0) * EB;
+  char* out_tile = reinterpret_cast<char*>(p.out) + (bo.out_base + x0 * p.out_sX + y0) * EB;
+  const unsigned in_sY = (unsigned)p.in_sY, out_sX = (unsigned)p.out_sX;
+
+  // ---- fused-affine parameters: one (scale, bias) pair per row / column / CTA, staged in smem ----
+  float* par = reinterpret_cast<float*>(sm + p.TY * P);
+  if constexpr (XDT >= 0) {
+    const int n_par = p.f_mode == F_AXIS_Y ? p.TY : p.f_mode == F_AXIS_X ? p.TX : 1;
+    const long long c0 = p.f_mode == F_AXIS_Y ? y0 : p.f_mode == F_AXIS_X ? x0 : p.f_mode == F_BATCH ? bo.f_coord : 0;
+    const long long c_end = p.f_mode == F_AXIS_Y ? p.Y : p.f_mode == F_AXIS_X ? p.X : c0 + 1;
+    for (int i = threadIdx.x; i < n_par; i += kThreads) {
+      const bool ok = c0 + i < c_end;
+      par[2 * i] = (ok && p.has_scale) ? load_param_as_f32(p.scale, p.s_dt, c0 + i) : 1.0f;
+      par[2 * i + 1] = (ok && p.has_bias) ? load_param_as_f32(p.bias, p.b_dt, c0 + i) : 0.0f;
+    }
+    __syncthreads();
+  }
 
   // ---- phase 1: global (vector along X) -> shared [y][xw] -------------------------------------
   {
-    const int chunks_x = TXW / 4;
-    const int total = chunks_x * p.TY;
-    const char* in = reinterpret_cast<const char*>(p.in);
+    const int lg_cx = p.lg_chunks_x;           // chunks (16 B) per tile row = 1 << lg_cx
+    const int total = p.TY << lg_cx;
     for (int q = threadIdx.x; q < total; q += kThreads) {
-      const int cx = q % chunks_x, y = q / chunks_x;
-      const long long gx = x0 + (long long)cx * VE, gy = y0 + y;
-      if (gx < p.X && gy < p.Y) {
-        const long long off = bo.in_base + gy * p.in_sY + gx;
-        uint4 v = __ldcs(reinterpret_cast<const uint4*>(in + off * EB));
+      const unsigned cx = q & ((1u << lg_cx) - 1u), y = (unsigned)q >> lg_cx;
+      const unsigned x = cx * VE;
+      if (x < nx && y < ny) {
+        uint4 v = __ldcs(reinterpret_cast<const uint4*>(in_tile + (size_t)(y * in_sY + x) * EB));
         if constexpr (XDT >= 0) {
-          float s = 1.0f, b = 0.0f;
-          if (p.f_mode != F_AXIS_X) {
-            const long long c = p.f_mode == F_AXIS_Y ? gy : p.f_mode == F_BATCH ? bo.f_coord : 0;
-            if (p.has_scale) s = load_param_as_f32(p.scale, p.s_dt, c);
-            if (p.has_bias) b = load_param_as_f32(p.bias, p.b_dt, c);
-          }
+          const int relu = p.relu;
           uint32_t w[4] = {v.x, v.y, v.z, v.w};
+          if (p.f_mode == F_AXIS_X) {
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            if constexpr (EB == 4) {
-              if (p.f_mode == F_AXIS_X) {
-                if (p.has_scale) s = load_param_as_f32(p.scale, p.s_dt, gx + j);
-                if (p.has_bias) b = load_param_as_f32(p.bias, p.b_dt, gx + j);
-              }
-              w[j] = __float_as_uint(affine(__uint_as_float(w[j]), s, b, p.relu));
-            } else {
-              float s1 = s, b1 = b;
-              if (p.f_mode == F_AXIS_X) {
-                if (p.has_scale) { s = load_param_as_f32(p.scale, p.s_dt, gx + 2 * j); s1 = load_param_as_f32(p.scale, p.s_dt, gx + 2 * j + 1); }
-                if (p.has_bias) { b = load_param_as_f32(p.bias, p.b_dt, gx + 2 * j); b1 = load_param_as_f32(p.bias, p.b_dt, gx + 2 * j + 1); }
-              }
-              if constexpr (XDT == HE_BF16) {
-                float2 f = bf16x2_to_f32(w[j]);
-                w[j] = f32x2_to_bf16x2(affine(f.x, s, b, p.relu), affine(f.y, s1, b1, p.relu));
+            for (int j = 0; j < 4; ++j) {
+              if constexpr (EB == 4) {
+                const float2 sb = *reinterpret_cast<const float2*>(par + 2 * (x + j));
+                w[j] = __float_as_uint(affine(__uint_as_float(w[j]), sb.x, sb.y, relu));
               } else {
-                float lo = f16_bits_to_f32(w[j] & 0xffffu), hi = f16_bits_to_f32(w[j] >> 16);
-                w[j] = f32_to_f16_bits(affine(lo, s, b, p.relu)) | (f32_to_f16_bits(affine(hi, s1, b1, p.relu)) << 16);
+                const float4 sb = *reinterpret_cast<const float4*>(par + 2 * (x + 2 * j));
+                if constexpr (XDT == HE_BF16) {
+                  const float2 f = bf16x2_to_f32(w[j]);
+                  w[j] = f32x2_to_bf16x2(affine(f.x, sb.x, sb.y, relu), affine(f.y, sb.z, sb.w, relu));
+                } else {
+                  w[j] = f32_to_f16_bits(affine(f16_bits_to_f32(w[j] & 0xffffu), sb.x, sb.y, relu)) |
+                         (f32_to_f16_bits(affine(f16_bits_to_f32(w[j] >> 16), sb.z, sb.w, relu)) << 16);
+                }
+              }
+            }
+          } else {
+            const float2 sb = *reinterpret_cast<const float2*>(par + 2 * (p.f_mode == F_AXIS_Y ? y : 0u));
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              if constexpr (EB == 4) {
+                w[j] = __float_as_uint(affine(__uint_as_float(w[j]), sb.x, sb.y, relu));
+              } else if constexpr (XDT == HE_BF16) {
+                const float2 f = bf16x2_to_f32(w[j]);
+                w[j] = f32x2_to_bf16x2(affine(f.x, sb.x, sb.y, relu), affine(f.y, sb.x, sb.y, relu));
+              } else {
+                w[j] = f32_to_f16_bits(affine(f16_bits_to_f32(w[j] & 0xffffu), sb.x, sb.y, relu)) |
+                       (f32_to_f16_bits(affine(f16_bits_to_f32(w[j] >> 16), sb.x, sb.y, relu)) << 16);
               }
             }
           }
@@ -210,32 +235,31 @@ __global__ void __launch_bounds__(kThreads) permute_tile_vec(const __grid_consta
   }
   __syncthreads();
   // ---- phase 2: shared (transposed read) -> global (vector along Y) ---------------------------
-  char* out = reinterpret_cast<char*>(p.out);
+  const int lg_yb = p.lg_y_blocks;              // TY / 32 = 1 << lg_yb
   if constexpr (EB == 4) {
     // warp = 8 lanes along y-chunks (4 y each) x 4 lanes along x: banks (4*ly + x) distinct.
-    const int y_blocks = p.TY / 32;
     const int total = p.TX * (p.TY / 4);
     for (int q = threadIdx.x; q < total; q += kThreads) {
-      const int yq_lo = q & 7, x_lo = (q >> 3) & 3, rest = q >> 5;
-      const int yq = (rest % y_blocks) * 8 + yq_lo, x = (rest / y_blocks) * 4 + x_lo;
-      const long long gx = x0 + x, gy = y0 + yq * 4;
-      if (gx < p.X && gy < p.Y) {
-        const uint32_t* src = sm + (yq * 4) * P + x;
-        uint4 v = make_uint4(src[0], src[P], src[2 * P], src[3 * P]);
-        __stcs(reinterpret_cast<uint4*>(out + (bo.out_base + gx * p.out_sX + gy) * 4), v);
+      const unsigned yq_lo = q & 7, x_lo = (q >> 3) & 3, rest = (unsigned)q >> 5;
+      const unsigned yq = ((rest & ((1u << lg_yb) - 1u)) << 3) + yq_lo, x = ((rest >> lg_yb) << 2) + x_lo;
+      const unsigned y = yq * 4;
+      if (x < nx && y < ny) {
+        const uint32_t* src = sm + y * P + x;
+        const uint4 v = make_uint4(src[0], src[P], src[2 * P], src[3 * P]);
+        __stcs(reinterpret_cast<uint4*>(out_tile + (size_t)(x * out_sX + y) * 4), v);
       }
     }
   } else {
     // a thread owns one word column (2 x) and 8 consecutive y: two 16-byte output vectors.
     // warp = 4 lanes along y-chunks x 8 lanes along xw: banks (8*ly + xw) distinct.
-    const int y_blocks = p.TY / 32;
+    const int TXW = p.TX / EPW;
     const int total = TXW * (p.TY / 8);
     for (int q = threadIdx.x; q < total; q += kThreads) {
-      const int yq_lo = q & 3, xw_lo = (q >> 2) & 7, rest = q >> 5;
-      const int yq = (rest % y_blocks) * 4 + yq_lo, xw = (rest / y_blocks) * 8 + xw_lo;
-      const long long gx = x0 + 2 * xw, gy = y0 + yq * 8;
-      if (gx < p.X && gy < p.Y) {
-        const uint32_t* src = sm + (yq * 8) * P + xw;
+      const unsigned yq_lo = q & 3, xw_lo = (q >> 2) & 7, rest = (unsigned)q >> 5;
+      const unsigned yq = ((rest & ((1u << lg_yb) - 1u)) << 2) + yq_lo, xw = ((rest >> lg_yb) << 3) + xw_lo;
+      const unsigned x = 2 * xw, y = yq * 8;
+      if (x < nx && y < ny) {
+        const uint32_t* src = sm + y * P + xw;
         uint32_t w[8];
 #pragma unroll
         for (int k = 0; k < 8; ++k) w[k] = src[k * P];
@@ -244,10 +268,10 @@ __global__ void __launch_bounds__(kThreads) permute_tile_vec(const __grid_consta
         lo.y = __byte_perm(w[2], w[3], 0x5410); hi.y = __byte_perm(w[2], w[3], 0x7632);
         lo.z = __byte_perm(w[4], w[5], 0x5410); hi.z = __byte_perm(w[4], w[5], 0x7632);
         lo.w = __byte_perm(w[6], w[7], 0x5410); hi.w = __byte_perm(w[6], w[7], 0x7632);
-        const long long o = bo.out_base + gx * p.out_sX + gy;
-        __stcs(reinterpret_cast<uint4*>(out + o * 2), lo);
-        // X is a multiple of 8 on this path, so gx + 1 is in range whenever gx is.
-        __stcs(reinterpret_cast<uint4*>(out + (o + p.out_sX) * 2), hi);
+        char* o = out_tile + (size_t)(x * out_sX + y) * 2;
+        __stcs(reinterpret_cast<uint4*>(o), lo);
+        // X is a multiple of 8 on this path, so x + 1 is in range whenever x is.
+        __stcs(reinterpret_cast<uint4*>(o + (size_t)out_sX * 2), hi);
       }
     }
   }
@@ -542,12 +566,38 @@ int32_t make_permute_plan(he_ctx* ctx, int rank, const int64_t* in_shape, const 
   txw = std::max(txw, eb == 4 ? 4 : 8);
   int ty = (4096 / txw);
   ty = std::min(ty, 512);
-  long long y_round = ((tp.Y + 31) / 32) * 32;
-  if (ty > y_round) ty = (int)y_round;
+  while (ty > 32 && ty / 2 >= tp.Y) ty /= 2;   // stays a power of two
   ty = std::max(ty, 32);
+  {
+    // A CTA loads, synchronises, then stores, so the last partial wave of CTAs costs a full tile
+    // time.  Among {ty, ty/2, ty/4} take the tile height with the best
+    // (full waves / launched waves) x (output run length factor).
+    const int sms = ctx_sm_count(ctx);
+    double best = -1.0;
+    int best_ty = ty;
+    for (int cand = ty; cand >= 32 && cand >= ty / 4; cand /= 2) {
+      const long long tiles = ((tp.X + txw * epw - 1) / (txw * epw)) * ((tp.Y + cand - 1) / cand) * batch;
+      const size_t smem_c = (size_t)cand * (std::max(txw, 8) + 1) * 4 + 1024;
+      const int per_sm = (int)std::max<size_t>(1, std::min<size_t>(2048 / kThreads, (size_t)(220 * 1024) / smem_c));
+      const double waves = (double)tiles / ((double)sms * per_sm);
+      const double quant = waves / std::ceil(waves);
+      const long long run_bytes = (long long)std::min<long long>(cand, tp.Y) * eb;
+      const double run = run_bytes >= 256 ? 1.0 : run_bytes >= 128 ? 0.96 : 0.85;
+      const double score = quant * run;
+      if (score > best + 1e-9) { best = score; best_ty = cand; }
+    }
+    ty = best_ty;
+  }
   tp.TX = txw * epw;
   tp.TY = ty;
   tp.P = std::max(txw, 8) + 1;
+  tp.lg_chunks_x = 0;
+  while ((1 << tp.lg_chunks_x) < txw / 4) ++tp.lg_chunks_x;
+  tp.lg_y_blocks = 0;
+  while ((32 << tp.lg_y_blocks) < ty) ++tp.lg_y_blocks;
+  // in-tile offsets are 32-bit in the vector kernel
+  if (pr.total >= (1ll << 32)) vec = false;
+  plan->vec = vec;
   tp.tiles_x = (unsigned)((tp.X + tp.TX - 1) / tp.TX);
   tp.tiles_y = (unsigned)((tp.Y + tp.TY - 1) / tp.TY);
   long long g64 = (long long)tp.tiles_x * tp.tiles_y * batch;
@@ -556,7 +606,7 @@ int32_t make_permute_plan(he_ctx* ctx, int rank, const int64_t* in_shape, const 
     HE_FAIL(HE_ERR_UNSUPPORTED, "permute: too many tiles");
   }
   plan->grid = g64;
-  plan->smem = (size_t)tp.TY * tp.P * 4;
+  plan->smem = (size_t)tp.TY * tp.P * 4 + (fn ? (size_t)std::max(tp.TX, tp.TY) * 8 : 0);
   snprintf(desc, sizeof desc, "permute: tile %dx%d (%d-byte elems, pitch %d words, %s%s), grid %lld",
            tp.TX, tp.TY, eb, tp.P, vec ? "16-byte vectors" : "scalar fallback", fn ? ", fused affine" : "", g64);
   plan->description = desc;

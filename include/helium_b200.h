@@ -177,6 +177,48 @@ int32_t he_plan_last_launch_count(const he_plan* plan);
 const char* he_plan_describe(const he_plan* plan);
 void he_plan_destroy(he_plan* plan);
 
+/* ------------------------------------------------------------------------------------------------
+ * Host runtime: a C++ mirror of the pieces of helium that sit between a recorded op graph and the
+ * three calls above, so that whole graphs can be driven without the Rust front end:
+ *   OpGraph / OpSubgraph          helium-ir/src/opgraph.rs:12-191, opgraph/subgraph.rs:12-120
+ *   Backend::make_instr_for_op    helium/src/cuda.rs:33-60 (Op::Matmul goes to the fused matmul)
+ *   Instruction::can_fuse_with    helium/src/cuda/instr.rs:71-99, backed by he_plan_supported
+ *   generate_plan                 helium/src/backend/plan_generation.rs:22-26,195-321,325-416
+ *   BackendExt::execute_graph     helium/src/backend.rs:40-80, with the steps' instructions issued
+ *                                 on several streams (the reference's executor uses one,
+ *                                 helium/src/cuda.rs:117-118) and the plan optionally captured in a
+ *                                 CUDA graph.
+ * Node ids are the values returned by heh_graph_new_*; `op->in[]` holds node ids of this graph.
+ * ------------------------------------------------------------------------------------------------ */
+typedef struct heh_graph heh_graph;
+typedef struct heh_exec heh_exec;
+
+int32_t heh_graph_create(heh_graph** out);
+void heh_graph_destroy(heh_graph* g);
+/* OpGraph::new_input (opgraph.rs:73-85). */
+int32_t heh_graph_new_input(heh_graph* g, int32_t dtype, int32_t rank, const int64_t* shape, int32_t* node_out);
+/* OpGraph::new_op (opgraph.rs:87-110): `op` carries kind / sub_op / operands / attributes and the
+ * output descriptor, which is validated against Op::output_descriptor's rules. */
+int32_t heh_graph_new_op(heh_graph* g, const he_node* op, int32_t* node_out);
+/* OpGraph::new_output (opgraph.rs:112-125): marks `node` as a value the caller wants back. */
+int32_t heh_graph_new_output(heh_graph* g, int32_t node);
+
+/* Plans the graph (instruction per op, greedy pairwise fusion, Kahn-layered steps, delayed
+ * instructions, tensor release points) and writes a human-readable listing: one line per
+ * instruction "step <i> <Kind> tier=<t> nodes=[..] in=[..] out=[..]". */
+int32_t heh_graph_plan_text(he_ctx* ctx, heh_graph* g, char* buf, size_t cap);
+
+/* Prepares an execution: plans, creates every he_plan, allocates intermediates and workspaces
+ * once, binds the caller's device buffers (`inputs[i]` for the i-th new_input, `outputs[j]` for the
+ * j-th new_output) and, if `capture_cuda_graph` != 0, records the whole plan into a CUDA graph.
+ * heh_exec_run enqueues one evaluation on `cu_stream`. */
+int32_t heh_exec_create(he_ctx* ctx, heh_graph* g, const void* const* inputs, void* const* outputs,
+                        int32_t capture_cuda_graph, heh_exec** out);
+int32_t heh_exec_run(heh_exec* e, void* cu_stream);
+/* Kernels launched per run, number of steps, number of instructions after fusion. */
+int32_t heh_exec_stats(const heh_exec* e, int32_t* launches, int32_t* steps, int32_t* instrs);
+void heh_exec_destroy(heh_exec* e);
+
 /* Introspection for tests (no counterpart in the reference, whose generated CUDA source is
  * inspected through insta snapshots instead, helium/src/cuda/instr/pointwise/jit.rs:752-803).
  * he_debug_dump_program lowers a subgraph to the interpreter program and copies the raw PwProgram
