@@ -150,7 +150,7 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="c2", choices=["c2", "c3"])
+    ap.add_argument("--workload", default="c2", choices=["c2", "c3", "gemm"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
@@ -232,6 +232,48 @@ def main():
         to_value = lambda sec_per_step: step_bytes * world / sec_per_step / 1e9
         dominant = ("permute_tile_vec<4> on [4096,4096,8] f32", C2B_BYTES, "hbm", peaks["hbm_gbs"], "GB/s", "permute_c2b")
         l2_note = "inputs exceed L2 (512 MiB permute input; the 103 MB pointwise input is evicted by the 1 GiB permute between its uses)"
+    elif args.workload == "gemm":
+        # plain bf16 matmul (the G0 contract): A [8192,8192] K-major, B [8192,8192] N-major, bf16 out
+        from helium_b200.configs import graph_linear
+        m = n = k = 8192
+        g = graph_linear(m, n, k, bias=False)
+        plan = hb.Plan.fused_matmul(ctx, g)
+        gen = torch.Generator(device=dev).manual_seed(2)
+        a_d = torch.randn((m, k), generator=gen, device=dev).to(torch.bfloat16)
+        b_d = (torch.randn((k, n), generator=gen, device=dev) / 90.0).to(torch.bfloat16)
+        a_pin = a_d.cpu().pin_memory(); b_pin = b_d.cpu().pin_memory()
+        outs_d = plan.alloc_outputs(dev)
+        out_pin = torch.empty((m, n), dtype=torch.bfloat16).pin_memory()
+        flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+        stream = torch.cuda.current_stream()
+        plan_desc = plan.description
+
+        def step(record=None):
+            flush.zero_()
+            if record is not None:
+                e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
+                e0.record(stream)
+                plan.launch([a_d, b_d], outs_d)
+                e1.record(stream)
+                record.append((e0, e1))
+            else:
+                plan.launch([a_d, b_d], outs_d)
+
+        def step_e2e():
+            a_d.copy_(a_pin, non_blocking=True); b_d.copy_(b_pin, non_blocking=True)
+            plan.launch([a_d, b_d], outs_d)
+            out_pin.copy_(outs_d[0], non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+
+        launches_per_step = 1
+        h2d = 2 * m * k * 2
+        d2h = m * n * 2
+        flops = 2.0 * m * n * k
+        metric, unit, dtype = "gemm_tflops", "TFLOP/s", "bf16 x bf16 -> f32 accumulate"
+        workload = "plain matmul 8192^3 bf16 (Op::Matmul contract, no fusion), bf16 output"
+        to_value = lambda sec_per_step: flops * world / sec_per_step / 1e12
+        dominant = (plan_desc, flops, "tensor", peaks["bf16_tflops"], "TFLOP/s", "gemm_plain")
+        l2_note = "256 MiB buffer written between iterations to flush L2 (inside the timed region)"
     else:
         m, n, k = C3_MNK
         g = graph_c3(m, n, k, False)
@@ -273,7 +315,7 @@ def main():
         workload = ("configs[2]: fused matmul 4096^3 bf16, mainloop relu(A)*M, epilogue bias/relu/tanh/gate/MSE + "
                     "Sum over Batch and Columns + two backward tiles (README graph)")
         to_value = lambda sec_per_step: C3_FLOPS * world / sec_per_step / 1e12
-        dominant = ("gemm_tcgen05_kernel<256,3,K-major A,N-major B,relu*mask,EpiC3>", C3_FLOPS, "tensor", peaks["bf16_tflops"], "TFLOP/s", "gemm_c3")
+        dominant = (plan.description, C3_FLOPS, "tensor", peaks["bf16_tflops"], "TFLOP/s", "gemm_c3")
         l2_note = "256 MiB buffer written between iterations to flush L2 (inside the timed region; its ~40 us are included)"
 
     # ---- warm-up, then the timed region ------------------------------------------------------------

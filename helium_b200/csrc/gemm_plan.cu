@@ -540,8 +540,7 @@ int32_t plan_fused_matmul(he_ctx* ctx, const Graph& g, he_plan** out, int* tier_
   {
     const char* dbg = getenv("HE_GEMM_DEBUG");
     c.debug = dbg ? atoi(dbg) : 0;
-    const char* pf = getenv("HE_GEMM_PREFETCH");
-    c.prefetch_kb = pf ? atoi(pf) : 0;
+    c.group_m = 1;
   }
   if (plan->cfg.ml != ML_NONE && plan->cfg.ml != ML_RELU_MASK)
     HE_FAIL(HE_ERR_UNSUPPORTED, "fused matmul: only the relu(A) * mask mainloop fusion is compiled in");
@@ -577,10 +576,13 @@ int32_t plan_fused_matmul(he_ctx* ctx, const Graph& g, he_plan** out, int* tier_
       c.tiles_m = 2 * tiles_m2;                       // partial-sum rows: the odd CTA of the last pair may be empty
       c.num_tiles = c.tiles_m * c.tiles_n * c.batch;  // one scalar partial per CTA tile
       plan->cfg.grid = 2 * std::max(1, std::min(tiles_m2 * c.tiles_n * c.batch, ctx_sm_count(ctx) / 2));
+      c.group_m = 8;    // 2048 rows of A per group
     } else {
+      c.group_m = 16;
       c.num_tiles = c.tiles_m * c.tiles_n * c.batch;
       plan->cfg.grid = std::max(1, std::min(c.num_tiles, ctx_sm_count(ctx)));
     }
+    if (const char* gm = getenv("HE_GEMM_GROUP_M")) c.group_m = std::max(1, atoi(gm));
   };
   auto out_dt = [&](int out_idx) { return g.nodes[g.outputs[out_idx]].dtype; };
   auto in_dt = [&](int slot) { return g.nodes[g.inputs[slot]].dtype; };

@@ -33,7 +33,7 @@ struct GemmCore {
   int M, N, K, batch;
   int tiles_m, tiles_n, num_tiles, k_blocks;
   int ab_format;  // 0 = f16, 1 = bf16
-  int prefetch_kb; // k-blocks of L2 prefetch distance (0 = off)
+  int group_m;    // tile rasterisation: row tiles per group (see decode_tile)
   int debug;      // timing experiments only (HE_GEMM_DEBUG): bit 0 skips the mainloop rewrite, bit 1 its proxy fence
   DeviceStatus* status;
 };
@@ -492,8 +492,15 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmParams<typename Epi::Params> p) 
     const int per_batch = c.tiles_m * c.tiles_n;
     t.b = tile / per_batch;
     const int r = tile - t.b * per_batch;
-    t.tile_n = r / c.tiles_m;
-    t.tile_m = r - t.tile_n * c.tiles_m;
+    // Grouped order: `group_m` row tiles x all column tiles at a time, rows fastest, so that the
+    // CTAs running together share a small set of A row panels and B column panels in L2.
+    const int gsz = c.group_m * c.tiles_n;
+    const int g = r / gsz;
+    const int first_m = g * c.group_m;
+    const int gm = min(c.group_m, c.tiles_m - first_m);
+    const int w = r - g * gsz;
+    t.tile_n = w / gm;
+    t.tile_m = first_m + (w - t.tile_n * gm);
     t.m0 = t.tile_m * kBM;
     t.n0 = t.tile_n * BN;
     return t;
@@ -512,21 +519,6 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmParams<typename Epi::Params> p) 
           if (!ptx::mbar_wait(bar_empty(stage), phase ^ 1u, abort_flag, c.status, 1, stage)) { alive = false; break; }
           ptx::mbar_arrive_expect_tx(bar_full(stage), kStageBytes);
           const int k0 = kb * kBK;
-          if (c.prefetch_kb > 0 && kb + c.prefetch_kb < c.k_blocks) {
-            const int kp = k0 + c.prefetch_kb * kBK;
-            if (A_MN) { ptx::tma_prefetch_l2_3d(&p.tma_a, t.m0, kp, t.b); ptx::tma_prefetch_l2_3d(&p.tma_a, t.m0 + 64, kp, t.b); }
-            else ptx::tma_prefetch_l2_3d(&p.tma_a, kp, t.m0, t.b);
-            if (SM::kHasMask) {
-              if (A_MN) { ptx::tma_prefetch_l2_3d(&p.tma_mask, t.m0, kp, t.b); ptx::tma_prefetch_l2_3d(&p.tma_mask, t.m0 + 64, kp, t.b); }
-              else ptx::tma_prefetch_l2_3d(&p.tma_mask, kp, t.m0, t.b);
-            }
-            if (B_MN) {
-#pragma unroll
-              for (int j = 0; j < BN / 64; ++j) ptx::tma_prefetch_l2_3d(&p.tma_b, t.n0 + 64 * j, kp, t.b);
-            } else {
-              ptx::tma_prefetch_l2_3d(&p.tma_b, kp, t.n0, t.b);
-            }
-          }
           const uint32_t a_dst = smem_base + SM::off_a + stage * kATileBytes;
           const uint32_t b_dst = smem_base + SM::off_b + stage * SM::kBTileBytes;
           if (A_MN) {

@@ -147,8 +147,13 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ GemmParams<typename Epi::Params
     const int per_batch = tiles_m2 * c.tiles_n;
     t.b = tile / per_batch;
     const int r = tile - t.b * per_batch;
-    t.tile_n = r / tiles_m2;
-    const int m2 = r - t.tile_n * tiles_m2;
+    const int gsz = c.group_m * c.tiles_n;   // group_m counts 256-row pair tiles here
+    const int g = r / gsz;
+    const int first_m = g * c.group_m;
+    const int gm = min(c.group_m, tiles_m2 - first_m);
+    const int w = r - g * gsz;
+    t.tile_n = w / gm;
+    const int m2 = first_m + (w - t.tile_n * gm);
     t.tile_m = m2 * 2 + (int)rank;
     t.m0 = t.tile_m * kBM;
     t.n0 = t.tile_n * BN;
@@ -176,18 +181,6 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ GemmParams<typename Epi::Params
           const int k0 = kb * kBK;
           const uint32_t a_dst = smem_base + SM::off_a + stage * kATileBytes;
           const uint32_t b_dst = smem_base + SM::off_b + stage * kBHalfBytes;
-          if (c.prefetch_kb > 0 && kb + c.prefetch_kb < c.k_blocks) {
-            const int kp = k0 + c.prefetch_kb * kBK;
-            const int nbp = t.n0 + 128 * (int)rank;
-            if (A_MN) { ptx::tma_prefetch_l2_3d(&p.tma_a, t.m0, kp, t.b); ptx::tma_prefetch_l2_3d(&p.tma_a, t.m0 + 64, kp, t.b); }
-            else ptx::tma_prefetch_l2_3d(&p.tma_a, kp, t.m0, t.b);
-            if (SM::kHasMask) {
-              if (A_MN) { ptx::tma_prefetch_l2_3d(&p.tma_mask, t.m0, kp, t.b); ptx::tma_prefetch_l2_3d(&p.tma_mask, t.m0 + 64, kp, t.b); }
-              else ptx::tma_prefetch_l2_3d(&p.tma_mask, kp, t.m0, t.b);
-            }
-            if (B_MN) { ptx::tma_prefetch_l2_3d(&p.tma_b, nbp, kp, t.b); ptx::tma_prefetch_l2_3d(&p.tma_b, nbp + 64, kp, t.b); }
-            else ptx::tma_prefetch_l2_3d(&p.tma_b, kp, nbp, t.b);
-          }
           // A (and the mask): this CTA's 128 rows
           if (kFused) {
             if (A_MN) {

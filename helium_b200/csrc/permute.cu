@@ -104,6 +104,7 @@ struct TileParams {
   int lg_chunks_x;       // log2 of 16-byte chunks per tile row
   int lg_y_blocks;       // log2(TY / 32)
   unsigned tiles_x, tiles_y;
+  FastDiv fd_tiles_x, fd_tiles_y, fd_b[kMaxBatchDims];   // 32-bit magic division for the CTA prologue
   // affine functor
   int f_mode, f_batch, relu, has_scale, has_bias, s_dt, b_dt;
   const void* scale;
@@ -123,6 +124,28 @@ struct RowParams {
 struct BatchOffsets {
   long long in_base, out_base, f_coord;
 };
+
+// Block index -> (tile x, tile y, batch offsets) with 32-bit magic-number divisions: the prologue
+// runs in every thread of every CTA and a CTA only moves a few thousand elements, so 64-bit
+// divisions here used to cost more instructions than the data movement itself.
+__device__ __forceinline__ BatchOffsets decode_block(const TileParams& p, unsigned& tx, unsigned& ty) {
+  unsigned blk = blockIdx.x, q;
+  p.fd_tiles_x.divmod(blk, q, tx);
+  blk = q;
+  p.fd_tiles_y.divmod(blk, q, ty);
+  blk = q;
+  BatchOffsets o{0, 0, 0};
+#pragma unroll 1
+  for (int k = p.nb - 1; k >= 0; --k) {
+    unsigned c;
+    p.fd_b[k].divmod(blk, q, c);
+    blk = q;
+    o.in_base += (long long)c * p.b_in[k];
+    o.out_base += (long long)c * p.b_out[k];
+    if (p.f_mode == F_BATCH && k == p.f_batch) o.f_coord = (long long)c;
+  }
+  return o;
+}
 
 __device__ __forceinline__ BatchOffsets decode_batch(const TileParams& p, unsigned long long b) {
   BatchOffsets o{0, 0, 0};
@@ -145,33 +168,40 @@ __device__ __forceinline__ float affine(float x, float s, float b, int relu) {
   float v = fmaf(x, s, b);
   return relu ? fmaxf(v, 0.0f) : v;
 }
+// Same with the relu folded into a floor value (0 or -inf): one FMNMX, no select.  fmaxf returns
+// the non-NaN operand, so a NaN input becomes the floor exactly as fmaxf(v, 0.0) would make it 0.
+__device__ __forceinline__ float affine_floor(float x, float s, float b, float floor_v) {
+  return fmaxf(fmaf(x, s, b), floor_v);
+}
 
 // XDT: -1 = plain permutation, otherwise the he_dtype of the element for the affine functor.
 // The host picks power-of-two tile extents, so every index decode below is a shift or a mask, and
 // offsets inside a tile are 32-bit (the planner routes tensors of 2^32 elements or more elsewhere).
-template <int EB, int XDT>
+constexpr int ilog2_c(int v) { return v <= 1 ? 0 : 1 + ilog2_c(v / 2); }
+
+// TXW_C / TY_C > 0 fix the tile shape at compile time (the common shapes), which unrolls both
+// loops and folds every shift, mask and pitch; 0 keeps them as kernel parameters.
+template <int EB, int XDT, int TXW_C = 0, int TY_C = 0>
 __global__ void __launch_bounds__(kThreads) permute_tile_vec(const __grid_constant__ TileParams p) {
   extern __shared__ uint32_t sm[];
   constexpr int EPW = 4 / EB;            // elements per 32-bit word
   constexpr int VE = 16 / EB;            // elements per 16-byte vector
-  unsigned long long blk = blockIdx.x;
-  const unsigned tx = (unsigned)(blk % p.tiles_x);
-  blk /= p.tiles_x;
-  const unsigned ty = (unsigned)(blk % p.tiles_y);
-  blk /= p.tiles_y;
-  const BatchOffsets bo = decode_batch(p, blk);
-  const long long x0 = (long long)tx * p.TX, y0 = (long long)ty * p.TY;
-  const int P = p.P;
+  constexpr bool kFixed = TXW_C > 0;
+  unsigned tx, ty;
+  const BatchOffsets bo = decode_block(p, tx, ty);
+  const int TX = kFixed ? TXW_C * EPW : p.TX, TY = kFixed ? TY_C : p.TY;
+  const int P = kFixed ? (TXW_C > 8 ? TXW_C : 8) + 1 : p.P;
+  const long long x0 = (long long)tx * TX, y0 = (long long)ty * TY;
   // rows / columns of this tile that exist (tiles at the border are partial)
-  const unsigned nx = (unsigned)min((long long)p.TX, p.X - x0), ny = (unsigned)min((long long)p.TY, p.Y - y0);
+  const unsigned nx = (unsigned)min((long long)TX, p.X - x0), ny = (unsigned)min((long long)TY, p.Y - y0);
   const char* in_tile = reinterpret_cast<const char*>(p.in) + (bo.in_base + y0 * p.in_sY + x0) * EB;
   char* out_tile = reinterpret_cast<char*>(p.out) + (bo.out_base + x0 * p.out_sX + y0) * EB;
   const unsigned in_sY = (unsigned)p.in_sY, out_sX = (unsigned)p.out_sX;
 
   // ---- fused-affine parameters: one (scale, bias) pair per row / column / CTA, staged in smem ----
-  float* par = reinterpret_cast<float*>(sm + p.TY * P);
+  float* par = reinterpret_cast<float*>(sm + TY * P);
   if constexpr (XDT >= 0) {
-    const int n_par = p.f_mode == F_AXIS_Y ? p.TY : p.f_mode == F_AXIS_X ? p.TX : 1;
+    const int n_par = p.f_mode == F_AXIS_Y ? TY : p.f_mode == F_AXIS_X ? TX : 1;
     const long long c0 = p.f_mode == F_AXIS_Y ? y0 : p.f_mode == F_AXIS_X ? x0 : p.f_mode == F_BATCH ? bo.f_coord : 0;
     const long long c_end = p.f_mode == F_AXIS_Y ? p.Y : p.f_mode == F_AXIS_X ? p.X : c0 + 1;
     for (int i = threadIdx.x; i < n_par; i += kThreads) {
@@ -184,30 +214,31 @@ __global__ void __launch_bounds__(kThreads) permute_tile_vec(const __grid_consta
 
   // ---- phase 1: global (vector along X) -> shared [y][xw] -------------------------------------
   {
-    const int lg_cx = p.lg_chunks_x;           // chunks (16 B) per tile row = 1 << lg_cx
-    const int total = p.TY << lg_cx;
+    const int lg_cx = kFixed ? ilog2_c(TXW_C / 4) : p.lg_chunks_x;   // chunks (16 B) per tile row = 1 << lg_cx
+    const int total = TY << lg_cx;
+    const float floor_v = p.relu ? 0.0f : -INFINITY;
+#pragma unroll
     for (int q = threadIdx.x; q < total; q += kThreads) {
       const unsigned cx = q & ((1u << lg_cx) - 1u), y = (unsigned)q >> lg_cx;
       const unsigned x = cx * VE;
       if (x < nx && y < ny) {
         uint4 v = __ldcs(reinterpret_cast<const uint4*>(in_tile + (size_t)(y * in_sY + x) * EB));
         if constexpr (XDT >= 0) {
-          const int relu = p.relu;
           uint32_t w[4] = {v.x, v.y, v.z, v.w};
           if (p.f_mode == F_AXIS_X) {
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
               if constexpr (EB == 4) {
                 const float2 sb = *reinterpret_cast<const float2*>(par + 2 * (x + j));
-                w[j] = __float_as_uint(affine(__uint_as_float(w[j]), sb.x, sb.y, relu));
+                w[j] = __float_as_uint(affine_floor(__uint_as_float(w[j]), sb.x, sb.y, floor_v));
               } else {
                 const float4 sb = *reinterpret_cast<const float4*>(par + 2 * (x + 2 * j));
                 if constexpr (XDT == HE_BF16) {
                   const float2 f = bf16x2_to_f32(w[j]);
-                  w[j] = f32x2_to_bf16x2(affine(f.x, sb.x, sb.y, relu), affine(f.y, sb.z, sb.w, relu));
+                  w[j] = f32x2_to_bf16x2(affine_floor(f.x, sb.x, sb.y, floor_v), affine_floor(f.y, sb.z, sb.w, floor_v));
                 } else {
-                  w[j] = f32_to_f16_bits(affine(f16_bits_to_f32(w[j] & 0xffffu), sb.x, sb.y, relu)) |
-                         (f32_to_f16_bits(affine(f16_bits_to_f32(w[j] >> 16), sb.z, sb.w, relu)) << 16);
+                  w[j] = f32_to_f16_bits(affine_floor(f16_bits_to_f32(w[j] & 0xffffu), sb.x, sb.y, floor_v)) |
+                         (f32_to_f16_bits(affine_floor(f16_bits_to_f32(w[j] >> 16), sb.z, sb.w, floor_v)) << 16);
                 }
               }
             }
@@ -216,13 +247,13 @@ __global__ void __launch_bounds__(kThreads) permute_tile_vec(const __grid_consta
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
               if constexpr (EB == 4) {
-                w[j] = __float_as_uint(affine(__uint_as_float(w[j]), sb.x, sb.y, relu));
+                w[j] = __float_as_uint(affine_floor(__uint_as_float(w[j]), sb.x, sb.y, floor_v));
               } else if constexpr (XDT == HE_BF16) {
                 const float2 f = bf16x2_to_f32(w[j]);
-                w[j] = f32x2_to_bf16x2(affine(f.x, sb.x, sb.y, relu), affine(f.y, sb.x, sb.y, relu));
+                w[j] = f32x2_to_bf16x2(affine_floor(f.x, sb.x, sb.y, floor_v), affine_floor(f.y, sb.x, sb.y, floor_v));
               } else {
-                w[j] = f32_to_f16_bits(affine(f16_bits_to_f32(w[j] & 0xffffu), sb.x, sb.y, relu)) |
-                       (f32_to_f16_bits(affine(f16_bits_to_f32(w[j] >> 16), sb.x, sb.y, relu)) << 16);
+                w[j] = f32_to_f16_bits(affine_floor(f16_bits_to_f32(w[j] & 0xffffu), sb.x, sb.y, floor_v)) |
+                       (f32_to_f16_bits(affine_floor(f16_bits_to_f32(w[j] >> 16), sb.x, sb.y, floor_v)) << 16);
               }
             }
           }
@@ -235,10 +266,11 @@ __global__ void __launch_bounds__(kThreads) permute_tile_vec(const __grid_consta
   }
   __syncthreads();
   // ---- phase 2: shared (transposed read) -> global (vector along Y) ---------------------------
-  const int lg_yb = p.lg_y_blocks;              // TY / 32 = 1 << lg_yb
+  const int lg_yb = kFixed ? ilog2_c(TY_C / 32) : p.lg_y_blocks;   // TY / 32 = 1 << lg_yb
   if constexpr (EB == 4) {
     // warp = 8 lanes along y-chunks (4 y each) x 4 lanes along x: banks (4*ly + x) distinct.
-    const int total = p.TX * (p.TY / 4);
+    const int total = TX * (TY / 4);
+#pragma unroll
     for (int q = threadIdx.x; q < total; q += kThreads) {
       const unsigned yq_lo = q & 7, x_lo = (q >> 3) & 3, rest = (unsigned)q >> 5;
       const unsigned yq = ((rest & ((1u << lg_yb) - 1u)) << 3) + yq_lo, x = ((rest >> lg_yb) << 2) + x_lo;
@@ -252,8 +284,9 @@ __global__ void __launch_bounds__(kThreads) permute_tile_vec(const __grid_consta
   } else {
     // a thread owns one word column (2 x) and 8 consecutive y: two 16-byte output vectors.
     // warp = 4 lanes along y-chunks x 8 lanes along xw: banks (8*ly + xw) distinct.
-    const int TXW = p.TX / EPW;
-    const int total = TXW * (p.TY / 8);
+    const int TXW = TX / EPW;
+    const int total = TXW * (TY / 8);
+#pragma unroll
     for (int q = threadIdx.x; q < total; q += kThreads) {
       const unsigned yq_lo = q & 3, xw_lo = (q >> 2) & 7, rest = (unsigned)q >> 5;
       const unsigned yq = ((rest & ((1u << lg_yb) - 1u)) << 2) + yq_lo, xw = ((rest >> lg_yb) << 3) + xw_lo;
@@ -414,8 +447,12 @@ struct PermutePlan : he_plan {
       unsigned g = (unsigned)grid;
 #define HE_LAUNCH_TILE(EB_, XDT_)                                                              \
   do {                                                                                         \
-    HE_CUDA(cudaFuncSetAttribute(permute_tile_vec<EB_, XDT_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
-    permute_tile_vec<EB_, XDT_><<<g, kThreads, smem, stream>>>(p);                              \
+    const int txw_ = p.TX / (4 / EB_);                                                         \
+    if (EB_ == 2 && txw_ == 32 && p.TY == 64) permute_tile_vec<EB_, XDT_, 32, 64><<<g, kThreads, smem, stream>>>(p);        \
+    else if (EB_ == 2 && txw_ == 32 && p.TY == 128) permute_tile_vec<EB_, XDT_, 32, 128><<<g, kThreads, smem, stream>>>(p); \
+    else if (EB_ == 4 && txw_ == 32 && p.TY == 128) permute_tile_vec<EB_, XDT_, 32, 128><<<g, kThreads, smem, stream>>>(p); \
+    else if (EB_ == 4 && txw_ == 8 && p.TY == 512) permute_tile_vec<EB_, XDT_, 8, 512><<<g, kThreads, smem, stream>>>(p);   \
+    else permute_tile_vec<EB_, XDT_><<<g, kThreads, smem, stream>>>(p);                         \
   } while (0)
       if (eb == 4) {
         if (xdt == HE_F32) HE_LAUNCH_TILE(4, HE_F32); else HE_LAUNCH_TILE(4, -1);
@@ -584,7 +621,8 @@ int32_t make_permute_plan(he_ctx* ctx, int rank, const int64_t* in_shape, const 
       const long long run_bytes = (long long)std::min<long long>(cand, tp.Y) * eb;
       const double run = run_bytes >= 256 ? 1.0 : run_bytes >= 128 ? 0.96 : 0.85;
       const double score = quant * run;
-      if (score > best + 1e-9) { best = score; best_ty = cand; }
+      // smaller tiles carry fewer bytes in flight per thread: switch only for a clear gain
+      if (score > best * 1.03) { best = score; best_ty = cand; }
     }
     ty = best_ty;
   }
@@ -605,6 +643,9 @@ int32_t make_permute_plan(he_ctx* ctx, int rank, const int64_t* in_shape, const 
     delete plan;
     HE_FAIL(HE_ERR_UNSUPPORTED, "permute: too many tiles");
   }
+  tp.fd_tiles_x = FastDiv(tp.tiles_x);
+  tp.fd_tiles_y = FastDiv(tp.tiles_y);
+  for (int k = 0; k < tp.nb; ++k) tp.fd_b[k] = FastDiv((uint32_t)tp.b_ext[k]);
   plan->grid = g64;
   plan->smem = (size_t)tp.TY * tp.P * 4 + (fn ? (size_t)std::max(tp.TX, tp.TY) * 8 : 0);
   snprintf(desc, sizeof desc, "permute: tile %dx%d (%d-byte elems, pitch %d words, %s%s), grid %lld",

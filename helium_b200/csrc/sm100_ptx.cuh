@@ -86,14 +86,6 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* m, 
       : "memory");
 }
 
-// Pulls the box into L2 only (no shared-memory destination, no barrier): issued a few k-blocks
-// ahead of the real load so that the load's latency is an L2 hit rather than an HBM access.
-__device__ __forceinline__ void tma_prefetch_l2_3d(const CUtensorMap* m, int c0, int c1, int c2) {
-  asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global [%0, {%1, %2, %3}];"
-               ::"l"(reinterpret_cast<uint64_t>(m)), "r"(c0), "r"(c1), "r"(c2)
-               : "memory");
-}
-
 // ---- TMEM / tcgen05 ----------------------------------------------------------------------------
 // Whole warp; writes the allocated base address to `dst_smem`.
 __device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t ncols) {

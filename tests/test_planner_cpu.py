@@ -67,7 +67,7 @@ def test_pointwise_tiers():
     g = graph_affine_relu_permute(64, 256, 56, 56)
     assert hb.plan_supported(g, 0) == 2
     d = hb.Plan.pointwise(None, g).description
-    assert "tier 2" in d and "fused affine" in d and "tile 64x128" in d
+    assert "tier 2" in d and "fused affine" in d and "tile 64x" in d
     # same graph with the multiplication operands swapped still matches
     g2 = ir.Graph()
     x = g2.new_input([4, 16, 8, 8], ir.BF16); s = g2.new_input([16], ir.BF16)
