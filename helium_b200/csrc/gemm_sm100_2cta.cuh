@@ -5,7 +5,7 @@
 // (48 KB instead of 64 KB with a mask tile), which is what the L2 -> SM path can sustain, and the
 // shared-memory ring gets six stages instead of four (four instead of three with a mask).
 //
-// No load uses cluster multicast: each CTA fetches its own boxes with `.cta_group::2` TMA loads
+// Every load is a per-CTA TMA load: each CTA fetches its own boxes with `.cta_group::2` loads
 // whose mbarrier is the leader CTA's.  Cross-CTA signalling uses remote mbarrier arrives and
 // `tcgen05.commit` to the peer's barrier.
 #pragma once
@@ -25,8 +25,12 @@ __device__ __forceinline__ uint32_t mapa(uint32_t smem_addr, uint32_t rank) {
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
   return r;
 }
+// Arrive on an mbarrier of a CTA of this cluster (address from mapa).  Default semantics on purpose:
+// spelling out `.release.cluster` made every transform-warp hand-off of the fused mainloop about
+// 1 us slower (678 -> 383 TFLOP/s on the mainloop-fused 4096^3 case); the shared-memory writes that
+// the arrival publishes are ordered for the tensor core by the async-proxy fence issued before it.
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 __device__ __forceinline__ void cluster_sync() {
   asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
