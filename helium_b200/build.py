@@ -33,6 +33,7 @@ SOURCES = [
     "gemm_kernels_prog.cu",
     "sgemm.cu",
     "host_graph.cu",
+    "reduce_noalloc.cu",
 ]
 
 NVCC_FLAGS = [

@@ -229,6 +229,35 @@ int32_t he_debug_dump_program(const he_graph_desc* desc, int32_t epilogue, void*
                               size_t* size_out);
 int32_t he_debug_canonical_text(const he_graph_desc* desc, char* buf, size_t cap);
 
+/* Sum over the trailing dims of an f32 tensor viewed as [num_groups, group_size], written to
+ * out[num_groups], with no workspace argument and no device allocation by anyone.
+ *
+ * No counterpart in the reference.  It is here for callers that have no way to hand a kernel
+ * scratch memory: a body for `PointwiseGraph::execute(tensors, stream, cx)`
+ * (helium/src/cuda/instr/pointwise.rs:57) is given tensors and a stream but, unlike the cuDNN
+ * instruction (helium/src/cuda/instr.rs:27-52), no allocator handle, and it must not call
+ * cudaMalloc itself because that stalls the device and bypasses the executor's stream-ordered
+ * pool.  he_launch needs a caller workspace once a reduction group is split over several CTAs;
+ * this call keeps those partial sums in a fixed array inside the library instead.
+ *
+ * Limits and rules:
+ *  - the array holds HE_NOALLOC_MAX_PARTIALS floats (256 KiB of device memory on every GPU the
+ *    process uses this library on, for the life of the process).  A shape that needs more partial
+ *    sums -- num_groups * ceil(group_size / 4096) when group_size > 4096 -- is refused with
+ *    HE_ERR_WORKSPACE and a message naming both numbers; num_groups * group_size must be < 2^31;
+ *  - the first call on each device looks the array's address up (a CUDA runtime query, no
+ *    allocation).  Make that first call before starting any stream capture on that device;
+ *  - all calls on a device share the one array, which keeps whatever the previous call left.
+ *    Nothing in it has to start at zero: every partial is written by the call before the call reads
+ *    it.  Two calls that can run at the same time (different streams, or different host threads
+ *    on different streams) race on it; order them on one stream or with events;
+ *  - the summation order is fixed, so results repeat bit for bit; they agree with he_launch's to
+ *    f32 rounding (he_launch may slice a group differently).  `in` and `out` are device pointers
+ *    on the current device. */
+#define HE_NOALLOC_MAX_PARTIALS 65536
+int32_t he_reduce_sum_f32_noalloc(const float* in, float* out, int64_t num_groups, int64_t group_size,
+                                  void* cu_stream);
+
 const char* he_last_error_string(void);
 const char* he_version(void);
 
