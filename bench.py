@@ -1,17 +1,20 @@
 #!/usr/bin/env python
 """Benchmark of the fused-kernel hot path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2|c3] [--impl ours|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c1|c2|c3|c4|gemm] [--impl ours|reference]
 
 Default workload = BASELINE.json configs[1] ("c2"): one step is
   (a) y = relu(x * s_c + b_c) on bf16 [64,256,56,56] NCHW written as NHWC, one fused kernel, and
   (b) the f32 permutation [4096,4096,8] -> axes (2,0,1),
 on synthetic seeded inputs; the metric is algorithmic HBM bytes moved per second.
-`--workload c3` times the fused 4096^3 GEMM of configs[2] (TFLOP/s).
+Other workloads: c1 = configs[0] (MLP training step, steps/s, whole graph through the C++ host
+runtime as one CUDA graph), c3 = configs[2] (fused 4096^3 GEMM, TFLOP/s), c4 = configs[3]
+(transformer MLP block forward+backward, 8192 tokens per GPU, weight gradients all-reduced over
+NCCL), gemm = a plain 8192^3 bf16 matmul.
 
-Rank 0 prints exactly one JSON line.  With N > 1 (launched under torch.distributed.run) every rank
-runs an independent replica of the step (the path has no cross-GPU dependency) and the whole-job
-value is N x bytes / max-over-ranks time.
+Rank 0 prints exactly one JSON line.  With N > 1 (launched under torch.distributed.run) c1-c3 run
+an independent replica per rank (those configurations have no cross-GPU dependency); c4 shards
+tokens over ranks and exchanges gradients.  The whole-job value is N x work / max-over-ranks time.
 """
 from __future__ import annotations
 
@@ -112,47 +115,408 @@ class ClockSampler:
 
 
 # ---- workloads ---------------------------------------------------------------------------------------
-def make_c2_inputs(seed=1):
-    """Seeded synthetic inputs of configs[1] as host (numpy) storage arrays."""
-    from helium_b200.configs import c2_inputs
-    return c2_inputs(seed)
+# A workload object owns its device buffers and exposes:
+#   step(record)   one pass over resident inputs; when `record` is a list, CUDA events bracketing the
+#                  dominant kernel are appended to it as (name, start, end)
+#   step_e2e()     the same pass fed from pinned host buffers, results read back to the host
+#   cpu_sample()   (static) a bounded sample of the same work on the host cores -> (value, cores, text)
+def _events(torch):
+    return torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+
+class WorkloadC2:
+    key = "c2"
+    metric, unit = "pointwise_permute_hbm_gbs", "GB/s"
+    dtype = "bf16 (f32 fma) + f32 bit moves"
+    description = ("configs[1]: y=relu(x*s_c+b_c) bf16 [64,256,56,56] NCHW->NHWC fused in one kernel; "
+                   "permute f32 [4096,4096,8] axes (2,0,1)")
+    l2_note = "inputs exceed L2 (512 MiB permute input; the 103 MB pointwise input is evicted by the 1 GiB permute between its uses)"
+    launches_per_step = 2
+    work_per_step = C2A_BYTES + C2B_BYTES
+    work_scale = 1e9
+
+    def __init__(self, ctx, dev, world, rank, peaks, reducer):
+        import torch
+        import helium_b200 as hb
+        from helium_b200 import ir
+        from helium_b200.configs import c2_inputs, graph_affine_relu_permute
+        self.torch = torch
+        x_h, s_h, b_h, p_h = c2_inputs(1)
+        self.plan_a = hb.Plan.pointwise(ctx, graph_affine_relu_permute(*C2A_SHAPE))
+        st = hb.permute_output_strides(list(C2B_SHAPE), [(1, 2), (0, 1)])
+        self.plan_b = hb.Plan.permute(ctx, list(C2B_SHAPE), st, ir.F32)
+        self.x_pin = torch.from_numpy(x_h.view(np.int16)).pin_memory()
+        self.p_pin = torch.from_numpy(p_h).pin_memory()
+        self.s_pin = torch.from_numpy(s_h).pin_memory(); self.b_pin = torch.from_numpy(b_h).pin_memory()
+        self.x_d = self.x_pin.to(dev).view(torch.bfloat16); self.s_d = self.s_pin.to(dev); self.b_d = self.b_pin.to(dev)
+        self.p_d = self.p_pin.to(dev)
+        self.y_d = torch.empty((64, 56, 56, 256), dtype=torch.bfloat16, device=dev)
+        self.q_d = torch.empty((8, 4096, 4096), dtype=torch.float32, device=dev)
+        self.y_pin = torch.empty((64, 56, 56, 256), dtype=torch.int16).pin_memory()
+        self.q_pin = torch.empty((8, 4096, 4096), dtype=torch.float32).pin_memory()
+        self.h2d = self.x_pin.numel() * 2 + self.p_pin.numel() * 4 + 2 * 256 * 4
+        self.d2h = self.y_pin.numel() * 2 + self.q_pin.numel() * 4
+        self.dominant = {"permute_c2b": ("permute_tile_vec<4> on [4096,4096,8] f32", C2B_BYTES, "hbm", peaks["hbm_gbs"], "GB/s"),
+                         "pointwise_c2a": ("affine+relu+NCHW->NHWC tile kernel on bf16 [64,256,56,56]", C2A_BYTES, "hbm", peaks["hbm_gbs"], "GB/s")}
+        self.dominant_key = "permute_c2b"
+
+    def step(self, record=None):
+        torch = self.torch
+        st = torch.cuda.current_stream()
+        if record is None:
+            self.plan_a.launch([self.x_d, self.s_d, self.b_d], [self.y_d])
+            self.plan_b.launch([self.p_d], [self.q_d])
+            return
+        a0, a1 = _events(torch); b0, b1 = _events(torch)
+        a0.record(st); self.plan_a.launch([self.x_d, self.s_d, self.b_d], [self.y_d]); a1.record(st)
+        b0.record(st); self.plan_b.launch([self.p_d], [self.q_d]); b1.record(st)
+        record.append(("pointwise_c2a", a0, a1)); record.append(("permute_c2b", b0, b1))
+
+    def step_e2e(self):
+        torch = self.torch
+        self.x_d.view(torch.int16).copy_(self.x_pin, non_blocking=True)
+        self.s_d.copy_(self.s_pin, non_blocking=True); self.b_d.copy_(self.b_pin, non_blocking=True)
+        self.p_d.copy_(self.p_pin, non_blocking=True)
+        self.plan_a.launch([self.x_d, self.s_d, self.b_d], [self.y_d])
+        self.plan_b.launch([self.p_d], [self.q_d])
+        self.y_pin.copy_(self.y_d.view(torch.int16), non_blocking=True)
+        self.q_pin.copy_(self.q_d, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    @staticmethod
+    def cpu_sample(max_steps=3):
+        from helium_b200.configs import c2_inputs
+        from oracle import oracle_c as OC
+        x, s, b, p = c2_inputs(1)
+        st = [4096, 1, 4096 * 4096]
+        OC.affine_relu_nchw_nhwc(x, s, b); OC.permute(p, st)      # first call also builds / loads the C object
+        t0 = time.perf_counter()
+        for _ in range(max_steps):
+            OC.affine_relu_nchw_nhwc(x, s, b)
+            OC.permute(p, st)
+        dt = (time.perf_counter() - t0) / max_steps
+        return (C2A_BYTES + C2B_BYTES) / dt / 1e9, OC.num_threads(), \
+            f"{max_steps} full configs[1] steps of the C+OpenMP restatement (oracle/oracle_c.c); the reference has no CPU path", dt
+
+
+class _GemmBase:
+    """Shared pieces of the tensor-core workloads: L2 flush buffer, TFLOP/s bookkeeping."""
+    work_scale = 1e12
+    l2_note = "256 MiB buffer written between iterations to flush L2 (inside the timed region; its ~40 us are included)"
+
+    def _flush_buffer(self, dev):
+        return self.torch.empty(256 << 20, dtype=self.torch.uint8, device=dev)
+
+    @staticmethod
+    def _cpu_gemm_sample(m, n, k, rows, masked, seed):
+        """`rows` output rows of an [m,k]x[k,n] bf16 GEMM on the host cores, scaled linearly to m rows."""
+        from helium_b200.configs import bf16_bernoulli, bf16_normal, rng
+        from oracle import oracle_c as OC
+        r = rng(seed)
+        a = bf16_normal(r, (rows, k)); b = bf16_normal(r, (k, n), 1.0 / np.sqrt(k))
+        mk = bf16_bernoulli(r, (rows, k)) if masked else None
+        OC.gemm_bf16(a[:8], b, None if mk is None else mk[:8], 0, 8)   # builds / loads the C object, warms the caches
+        t0 = time.perf_counter()
+        OC.gemm_bf16(a, b, mk, 0, rows)
+        dt = (time.perf_counter() - t0) * (m / rows)
+        return dt, OC.num_threads()
+
+
+class WorkloadGemm(_GemmBase):
+    key = "gemm"
+    metric, unit = "gemm_tflops", "TFLOP/s"
+    dtype = "bf16 x bf16 -> f32 accumulate"
+    description = "plain matmul 8192^3 bf16 (Op::Matmul contract, no fusion), bf16 output"
+    launches_per_step = 1
+    M = N = K = 8192
+    work_per_step = 2.0 * 8192 ** 3
+
+    def __init__(self, ctx, dev, world, rank, peaks, reducer):
+        import torch
+        import helium_b200 as hb
+        from helium_b200.configs import graph_linear
+        self.torch = torch
+        m, n, k = self.M, self.N, self.K
+        self.plan = hb.Plan.fused_matmul(ctx, graph_linear(m, n, k, bias=False))
+        gen = torch.Generator(device=dev).manual_seed(2)
+        self.a_d = torch.randn((m, k), generator=gen, device=dev).to(torch.bfloat16)
+        self.b_d = (torch.randn((k, n), generator=gen, device=dev) / 90.0).to(torch.bfloat16)
+        self.a_pin = self.a_d.cpu().pin_memory(); self.b_pin = self.b_d.cpu().pin_memory()
+        self.outs_d = self.plan.alloc_outputs(dev)
+        self.out_pin = torch.empty((m, n), dtype=torch.bfloat16).pin_memory()
+        self.flush = self._flush_buffer(dev)
+        self.h2d, self.d2h = 2 * m * k * 2, m * n * 2
+        self.dominant = {"gemm_plain": (self.plan.description, self.work_per_step, "tensor", peaks["bf16_tflops"], "TFLOP/s")}
+        self.dominant_key = "gemm_plain"
+
+    def step(self, record=None):
+        self.flush.zero_()
+        if record is None:
+            self.plan.launch([self.a_d, self.b_d], self.outs_d)
+            return
+        st = self.torch.cuda.current_stream()
+        e0, e1 = _events(self.torch)
+        e0.record(st); self.plan.launch([self.a_d, self.b_d], self.outs_d); e1.record(st)
+        record.append(("gemm_plain", e0, e1))
+
+    def step_e2e(self):
+        self.a_d.copy_(self.a_pin, non_blocking=True); self.b_d.copy_(self.b_pin, non_blocking=True)
+        self.plan.launch([self.a_d, self.b_d], self.outs_d)
+        self.out_pin.copy_(self.outs_d[0], non_blocking=True)
+        self.torch.cuda.current_stream().synchronize()
+
+    @staticmethod
+    def cpu_sample(max_steps=1):
+        rows = 4096
+        dt, cores = _GemmBase._cpu_gemm_sample(8192, 8192, 8192, rows, False, 2)
+        return 2.0 * 8192 ** 3 / dt / 1e12, cores, f"{rows} of 8192 output rows, C+OpenMP restatement (oracle/oracle_c.c), scaled linearly", dt
+
+
+class WorkloadC3(_GemmBase):
+    key = "c3"
+    metric, unit = "fused_gemm_tflops", "TFLOP/s"
+    dtype = "bf16 x bf16 -> f32 accumulate, f32 epilogue"
+    description = ("configs[2]: fused matmul 4096^3 bf16, mainloop relu(A)*M, epilogue bias/relu/tanh/gate/MSE + "
+                   "Sum over Batch and Columns + two backward tiles (README graph)")
+    work_per_step = float(C3_FLOPS)
+
+    def __init__(self, ctx, dev, world, rank, peaks, reducer):
+        import torch
+        import helium_b200 as hb
+        from helium_b200.configs import c3_inputs, graph_c3
+        self.torch = torch
+        m, n, k = C3_MNK
+        ins_h = c3_inputs(m, n, k, False)
+        self.plan = hb.Plan.fused_matmul(ctx, graph_c3(m, n, k, False))
+        self.pins = [torch.from_numpy(np.ascontiguousarray(a).view(np.int16)).pin_memory() for a in ins_h]
+        self.ins_d = [p.to(dev).view(torch.bfloat16) for p in self.pins]
+        self.ins_d[5] = self.ins_d[1]  # the epilogue mask is the mainloop mask (k == n)
+        self.outs_d = self.plan.alloc_outputs(dev)
+        self.outs_pin = [torch.empty(o.shape, dtype=torch.int16 if o.dtype == torch.bfloat16 else torch.float32).pin_memory()
+                         for o in self.outs_d]
+        self.flush = self._flush_buffer(dev)
+        self.h2d = sum(p.numel() * 2 for i, p in enumerate(self.pins) if i != 5)
+        self.d2h = sum(p.numel() * p.element_size() for p in self.outs_pin)
+        self.plan.launch(self.ins_d, self.outs_d)
+        self.launches_per_step = self.plan.last_launch_count
+        self.dominant = {"gemm_c3": (self.plan.description, self.work_per_step, "tensor", peaks["bf16_tflops"], "TFLOP/s")}
+        self.dominant_key = "gemm_c3"
+
+    def step(self, record=None):
+        self.flush.zero_()  # operands (201 MB) partly fit the 126 MB L2: evict between iterations
+        if record is None:
+            self.plan.launch(self.ins_d, self.outs_d)
+            return
+        st = self.torch.cuda.current_stream()
+        e0, e1 = _events(self.torch)
+        e0.record(st); self.plan.launch(self.ins_d, self.outs_d); e1.record(st)
+        record.append(("gemm_c3", e0, e1))
+
+    def step_e2e(self):
+        torch = self.torch
+        for i, (d, p) in enumerate(zip(self.ins_d, self.pins)):
+            if i != 5:
+                d.view(torch.int16).copy_(p, non_blocking=True)
+        self.plan.launch(self.ins_d, self.outs_d)
+        for o, p in zip(self.outs_d, self.outs_pin):
+            p.copy_(o.view(torch.int16) if o.dtype == torch.bfloat16 else o, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    @staticmethod
+    def cpu_sample(max_steps=1):
+        rows = 4096
+        dt, cores = _GemmBase._cpu_gemm_sample(4096, 4096, 4096, rows, True, 2)
+        return C3_FLOPS / dt / 1e12, cores, \
+            f"{rows} of 4096 output rows of the mainloop-fused GEMM (epilogue not included), C+OpenMP restatement, scaled linearly", dt
+
+
+class WorkloadC4(_GemmBase):
+    key = "c4"
+    metric, unit = "fused_gemm_tflops", "TFLOP/s"
+    dtype = "bf16 x bf16 -> f32 accumulate, f32 epilogue"
+    TOKENS, D, FF = 8192, 4096, 16384
+    description = ("configs[3]: transformer MLP block forward+backward, 8192 tokens per GPU, d=4096, ff=16384, bf16; six fused GEMMs "
+                   "(bias+GELU, bias+residual, dgelu-gate+colsum, two weight-gradient GEMMs, residual+colsum); "
+                   "weight/bias gradients averaged over ranks with NCCL, overlapped with the remaining GEMMs")
+    l2_note = "every GEMM streams operands larger than L2 (W1/W2/H/Z are 128-256 MiB each); no flush needed"
+    work_per_step = 6 * 2.0 * 8192 * 4096 * 16384
+
+    def __init__(self, ctx, dev, world, rank, peaks, reducer):
+        import torch
+        from helium_b200.mlp_block import MlpBlock, mlp_block_inputs
+        self.torch = torch
+        self.reducer = reducer
+        T, d, ff = self.TOKENS, self.D, self.FF
+        self.blk = MlpBlock(ctx, T, d, ff, dev)
+        host = mlp_block_inputs(T, d, ff, seed=3, shard=rank)       # same weights on every rank, a different token shard each
+        self.blk.load(host)
+        as_pin = lambda v: torch.from_numpy(np.ascontiguousarray(v).view(np.int16)).pin_memory()
+        self.x_pin, self.do_pin = as_pin(host["X"]), as_pin(host["dO"])
+        self.dx_pin = torch.empty((T, d), dtype=torch.int16).pin_memory()
+        self.db_pin = torch.empty(ff + d, dtype=torch.float32).pin_memory()
+        self.h2d = 2 * T * d * 2
+        self.d2h = T * d * 2 + (ff + d) * 4
+        self.blk.step(self.reducer)
+        self.launches_per_step = self.blk.launch_count()
+        peak = peaks.get("bf16_tflops_sustained") or peaks["bf16_tflops"]
+        gemm_flops = self.work_per_step / 6
+        self.dominant = {k: (f"{k}: {self.blk.plans[k].description}", gemm_flops, "tensor", peak, "TFLOP/s") for k in self.blk.plans}
+        self.dominant_key = None       # chosen after timing: the GEMM with the largest share of the step
+        self.peak_note = "sustained cuBLAS bf16 figure (the kernels run inside a multi-millisecond step under the power cap)"
+
+    def step(self, record=None):
+        blk, red = self.blk, self.reducer
+        if record is None:
+            blk.step(red)
+            return
+        torch = self.torch
+        st = torch.cuda.current_stream()
+        p = blk.plans
+
+        def timed(name, ins, outs):
+            e0, e1 = _events(torch)
+            e0.record(st); p[name].launch(ins, outs); e1.record(st)
+            record.append((name, e0, e1))
+
+        timed("H", [blk.X, blk.W1, blk.b1], [blk.H, blk.Z])
+        timed("O", [blk.H, blk.W2, blk.b2, blk.X], [blk.O])
+        timed("dZ", [blk.dO, blk.W2, blk.Z], [blk.dZ, blk.db1])
+        timed("dW1", [blk.X, blk.dZ], [blk.dW1])
+        if red is not None:
+            red.reduce_bucket([blk.dW1])
+        timed("dW2", [blk.H, blk.dO], [blk.dW2])
+        if red is not None:
+            red.reduce_bucket([blk.dW2])
+        timed("dX", [blk.dZ, blk.W1, blk.dO], [blk.dX, blk.db2])
+        if red is not None:
+            red.reduce_bucket([blk.db_flat])
+            red.finish()
+
+    def step_e2e(self):
+        torch = self.torch
+        blk = self.blk
+        blk.X.view(torch.int16).copy_(self.x_pin, non_blocking=True)
+        blk.dO.view(torch.int16).copy_(self.do_pin, non_blocking=True)
+        blk.step(self.reducer)
+        self.dx_pin.copy_(blk.dX.view(torch.int16), non_blocking=True)
+        self.db_pin.copy_(blk.db_flat, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    @staticmethod
+    def cpu_sample(max_steps=1):
+        rows = 2048
+        dt, cores = _GemmBase._cpu_gemm_sample(8192, 16384, 4096, rows, False, 3)
+        dt *= 6     # six GEMMs of equal flop count per step
+        return WorkloadC4.work_per_step / dt / 1e12, cores, \
+            (f"{rows} of 8192 rows of the X*W1 GEMM, C+OpenMP restatement, scaled linearly to the six equal-sized GEMMs of a step "
+             "(epilogues not included)"), dt
+
+
+class WorkloadC1:
+    key = "c1"
+    metric, unit = "train_steps_per_s", "step/s"
+    dtype = "f32 (SIMT FFMA products, f32 accumulate)"
+    description = ("configs[0]: MLP 784->512->10 training step, batch 256, f32: forward, softmax cross-entropy, backward, SGD lr 0.01; "
+                   "the whole op graph planned (fusion + steps) by the C++ host runtime and replayed as one CUDA graph")
+    l2_note = "working set 4.1 MB is L2-resident by construction (weights are re-read every step, as in training)"
+    work_per_step = 1.0
+    work_scale = 1.0
+    COMPULSORY_BYTES = 4.1e6
+
+    def __init__(self, ctx, dev, world, rank, peaks, reducer):
+        import torch
+        import helium_b200 as hb
+        from helium_b200 import configs
+        self.torch = torch
+        g = configs.graph_mlp_train_step()
+        ins = configs.mlp_inputs()
+        self.x_pin = torch.from_numpy(ins[0]).pin_memory(); self.t_pin = torch.from_numpy(ins[1]).pin_memory()
+        self.x_d, self.t_d = self.x_pin.to(dev), self.t_pin.to(dev)
+        w_a = [torch.from_numpy(a).to(dev) for a in ins[2:]]
+        w_b = [torch.empty_like(w) for w in w_a]
+        self.loss_d = torch.zeros(1, dtype=torch.float32, device=dev)
+        self.loss_pin = torch.zeros(1, dtype=torch.float32).pin_memory()
+        hg = hb.HostGraph(g)
+        # two executors that ping-pong the parameters, so consecutive steps really train: A reads w_a and
+        # writes w_b, B reads w_b and writes w_a
+        self.ex = [hb.Executor(ctx, hg, [self.x_d, self.t_d] + w_a, [self.loss_d] + w_b, capture=True),
+                   hb.Executor(ctx, hg, [self.x_d, self.t_d] + w_b, [self.loss_d] + w_a, capture=True)]
+        self._keep = (hg, w_a, w_b)
+        self.parity = 0
+        st = self.ex[0].stats()
+        self.launches_per_step = st["launches"]
+        self.plan_stats = st
+        self.h2d = self.x_pin.numel() * 4 + self.t_pin.numel() * 4
+        self.d2h = 4
+        self.dominant = {"mlp_step_graph": (f"CUDA graph of {st['launches']} kernels ({st['instrs']} fused instructions, {st['steps']} plan steps)",
+                                            self.COMPULSORY_BYTES, "hbm", peaks["hbm_gbs"], "GB/s")}
+        self.dominant_key = "mlp_step_graph"
+
+    def step(self, record=None):
+        ex = self.ex[self.parity]
+        self.parity ^= 1
+        if record is None:
+            ex.run()
+            return
+        st = self.torch.cuda.current_stream()
+        e0, e1 = _events(self.torch)
+        e0.record(st); ex.run(); e1.record(st)
+        record.append(("mlp_step_graph", e0, e1))
+
+    def step_e2e(self):
+        self.x_d.copy_(self.x_pin, non_blocking=True); self.t_d.copy_(self.t_pin, non_blocking=True)
+        self.step()
+        self.loss_pin.copy_(self.loss_d, non_blocking=True)
+        self.torch.cuda.current_stream().synchronize()
+
+    @staticmethod
+    def cpu_sample(max_steps=20):
+        from helium_b200 import configs
+        from oracle import oracle as O
+        g = configs.graph_mlp_train_step()
+        ins = configs.mlp_inputs()
+        O.evaluate(g, ins)
+        t0 = time.perf_counter()
+        for _ in range(max_steps):
+            O.evaluate(g, ins)
+        dt = (time.perf_counter() - t0) / max_steps
+        try:
+            from threadpoolctl import threadpool_info
+            cores = max([i.get("num_threads", 1) for i in threadpool_info()] or [1])
+        except Exception:
+            cores = 1
+        return 1.0 / dt, cores, f"{max_steps} steps of the numpy f64 restatement (oracle/oracle.py) of the same op graph; the reference's CPU backend is a stub", dt
+
+
+WORKLOADS = {w.key: w for w in (WorkloadC1, WorkloadC2, WorkloadC3, WorkloadC4, WorkloadGemm)}
 
 
 def run_reference_arm(args):
-    """`--impl reference`: the reference has no CPU (or runnable GPU) implementation of this path here,
-    so the arm times the C restatement of its kernels (oracle/oracle_c.c) on all host cores."""
-    from oracle import oracle_c as OC
-    x, s, b, p = make_c2_inputs()
-    st = [4096, 1, 4096 * 4096]
-    threads = OC.num_threads()
-    for _ in range(max(1, min(args.warmup, 1))):
-        OC.affine_relu_nchw_nhwc(x, s, b); OC.permute(p, st)
-    steps = max(1, min(args.steps, 5))
-    t0 = time.perf_counter()
-    for _ in range(steps):
-        OC.affine_relu_nchw_nhwc(x, s, b)
-        OC.permute(p, st)
-    dt = (time.perf_counter() - t0) / steps
-    val = (C2A_BYTES + C2B_BYTES) / dt / 1e9
-    line = {"impl": "reference", "metric": "pointwise_permute_hbm_gbs", "value": val, "unit": "GB/s", "n_gpus": args.gpus,
-            "steps": steps, "warmup": 1, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "bf16+f32 (bit moves, f32 fma)", "data": "synthetic",
-            "config": {"workload": "configs[1]: affine+relu+NCHW->NHWC bf16 [64,256,56,56]; permute f32 [4096,4096,8] axes (2,0,1)"},
-            "cpu_baseline": {"value": val, "unit": "GB/s", "cores": threads, "kind": "port",
-                             "sample": f"full configs[1] step, {steps} steps, C+OpenMP restatement (the reference has no CPU path)"},
-            "e2e": {"value": val, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    """`--impl reference`: the reference is Rust + run-time generated CUDA, has no CPU implementation of
+    this path and cannot be built in this image, so the arm times the CPU restatement of the same work
+    (oracle/) on all host cores, on a bounded sample of the workload."""
+    wl = WORKLOADS[args.workload]
+    n = {"c2": min(args.steps, 3), "c1": min(args.steps, 20)}.get(args.workload, 1)
+    value, cores, sample, dt = wl.cpu_sample(max(1, n))
+    line = {"impl": "reference", "metric": wl.metric, "value": value, "unit": wl.unit, "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic", "config": {"workload": wl.description},
+            "cpu_baseline": {"value": value, "unit": wl.unit, "cores": cores, "kind": "port", "sample": sample},
+            "e2e": {"value": value, "unit": wl.unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line))
 
 
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--steps", type=int, default=None)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="c2", choices=["c2", "c3", "gemm"])
+    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
+    if args.steps is None:
+        args.steps = {"c1": 2000, "c2": 200, "c3": 200, "c4": 30, "gemm": 100}[args.workload]
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -168,8 +532,7 @@ def main():
     import torch.distributed as dist
 
     import helium_b200 as hb
-    from helium_b200 import ir
-    from helium_b200.configs import c3_inputs, graph_affine_relu_permute, graph_c3
+    from helium_b200.grad_sync import GradReducer
 
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: helium_b200 has no CPU path")
@@ -185,138 +548,9 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
-    if args.workload == "c2":
-        x_h, s_h, b_h, p_h = make_c2_inputs()
-        plan_a = hb.Plan.pointwise(ctx, graph_affine_relu_permute(*C2A_SHAPE))
-        st = hb.permute_output_strides(list(C2B_SHAPE), [(1, 2), (0, 1)])
-        plan_b = hb.Plan.permute(ctx, list(C2B_SHAPE), st, ir.F32)
-        # pinned host buffers for the end-to-end leg
-        x_pin = torch.from_numpy(x_h.view(np.int16)).pin_memory()
-        p_pin = torch.from_numpy(p_h).pin_memory()
-        s_pin = torch.from_numpy(s_h).pin_memory(); b_pin = torch.from_numpy(b_h).pin_memory()
-        x_d = x_pin.to(dev).view(torch.bfloat16); s_d = s_pin.to(dev); b_d = b_pin.to(dev); p_d = p_pin.to(dev)
-        y_d = torch.empty((64, 56, 56, 256), dtype=torch.bfloat16, device=dev)
-        q_d = torch.empty((8, 4096, 4096), dtype=torch.float32, device=dev)
-        y_pin = torch.empty((64, 56, 56, 256), dtype=torch.int16).pin_memory()
-        q_pin = torch.empty((8, 4096, 4096), dtype=torch.float32).pin_memory()
-        step_bytes = C2A_BYTES + C2B_BYTES
-        stream = torch.cuda.current_stream()
-
-        def step(record=None):
-            plan_a.launch([x_d, s_d, b_d], [y_d])
-            if record is not None:
-                e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
-                e0.record(stream)
-                plan_b.launch([p_d], [q_d])
-                e1.record(stream)
-                record.append((e0, e1))
-            else:
-                plan_b.launch([p_d], [q_d])
-
-        def step_e2e():
-            x_d.view(torch.int16).copy_(x_pin, non_blocking=True)
-            s_d.copy_(s_pin, non_blocking=True); b_d.copy_(b_pin, non_blocking=True)
-            p_d.copy_(p_pin, non_blocking=True)
-            plan_a.launch([x_d, s_d, b_d], [y_d])
-            plan_b.launch([p_d], [q_d])
-            y_pin.copy_(y_d.view(torch.int16), non_blocking=True)
-            q_pin.copy_(q_d, non_blocking=True)
-            torch.cuda.current_stream().synchronize()
-
-        launches_per_step = 2
-        h2d = x_pin.numel() * 2 + p_pin.numel() * 4 + 2 * 256 * 4
-        d2h = y_pin.numel() * 2 + q_pin.numel() * 4
-        metric, unit, dtype = "pointwise_permute_hbm_gbs", "GB/s", "bf16 (f32 fma) + f32 bit moves"
-        workload = ("configs[1]: y=relu(x*s_c+b_c) bf16 [64,256,56,56] NCHW->NHWC fused in one kernel; "
-                    "permute f32 [4096,4096,8] axes (2,0,1)")
-        to_value = lambda sec_per_step: step_bytes * world / sec_per_step / 1e9
-        dominant = ("permute_tile_vec<4> on [4096,4096,8] f32", C2B_BYTES, "hbm", peaks["hbm_gbs"], "GB/s", "permute_c2b")
-        l2_note = "inputs exceed L2 (512 MiB permute input; the 103 MB pointwise input is evicted by the 1 GiB permute between its uses)"
-    elif args.workload == "gemm":
-        # plain bf16 matmul (the G0 contract): A [8192,8192] K-major, B [8192,8192] N-major, bf16 out
-        from helium_b200.configs import graph_linear
-        m = n = k = 8192
-        g = graph_linear(m, n, k, bias=False)
-        plan = hb.Plan.fused_matmul(ctx, g)
-        gen = torch.Generator(device=dev).manual_seed(2)
-        a_d = torch.randn((m, k), generator=gen, device=dev).to(torch.bfloat16)
-        b_d = (torch.randn((k, n), generator=gen, device=dev) / 90.0).to(torch.bfloat16)
-        a_pin = a_d.cpu().pin_memory(); b_pin = b_d.cpu().pin_memory()
-        outs_d = plan.alloc_outputs(dev)
-        out_pin = torch.empty((m, n), dtype=torch.bfloat16).pin_memory()
-        flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
-        stream = torch.cuda.current_stream()
-        plan_desc = plan.description
-
-        def step(record=None):
-            flush.zero_()
-            if record is not None:
-                e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
-                e0.record(stream)
-                plan.launch([a_d, b_d], outs_d)
-                e1.record(stream)
-                record.append((e0, e1))
-            else:
-                plan.launch([a_d, b_d], outs_d)
-
-        def step_e2e():
-            a_d.copy_(a_pin, non_blocking=True); b_d.copy_(b_pin, non_blocking=True)
-            plan.launch([a_d, b_d], outs_d)
-            out_pin.copy_(outs_d[0], non_blocking=True)
-            torch.cuda.current_stream().synchronize()
-
-        launches_per_step = 1
-        h2d = 2 * m * k * 2
-        d2h = m * n * 2
-        flops = 2.0 * m * n * k
-        metric, unit, dtype = "gemm_tflops", "TFLOP/s", "bf16 x bf16 -> f32 accumulate"
-        workload = "plain matmul 8192^3 bf16 (Op::Matmul contract, no fusion), bf16 output"
-        to_value = lambda sec_per_step: flops * world / sec_per_step / 1e12
-        dominant = (plan_desc, flops, "tensor", peaks["bf16_tflops"], "TFLOP/s", "gemm_plain")
-        l2_note = "256 MiB buffer written between iterations to flush L2 (inside the timed region)"
-    else:
-        m, n, k = C3_MNK
-        g = graph_c3(m, n, k, False)
-        ins_h = c3_inputs(m, n, k, False)
-        plan = hb.Plan.fused_matmul(ctx, g)
-        pins = [torch.from_numpy(np.ascontiguousarray(a).view(np.int16)).pin_memory() for a in ins_h]
-        ins_d = [p.to(dev).view(torch.bfloat16) for p in pins]
-        ins_d[5] = ins_d[1]  # the epilogue mask is the mainloop mask (k == n)
-        outs_d = plan.alloc_outputs(dev)
-        flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
-        stream = torch.cuda.current_stream()
-
-        def step(record=None):
-            flush.zero_()  # operands fit L2 (201 MB vs 126 MB partly): evict between iterations
-            if record is not None:
-                e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
-                e0.record(stream)
-                plan.launch(ins_d, outs_d)
-                e1.record(stream)
-                record.append((e0, e1))
-            else:
-                plan.launch(ins_d, outs_d)
-
-        outs_pin = [torch.empty(o.shape, dtype=torch.int16 if o.dtype == torch.bfloat16 else torch.float32).pin_memory() for o in outs_d]
-
-        def step_e2e():
-            for d, p in zip(ins_d[:1] + ins_d[2:5] + ins_d[6:], pins[:1] + pins[2:5] + pins[6:]):
-                d.view(torch.int16).copy_(p, non_blocking=True)
-            ins_d[1].view(torch.int16).copy_(pins[1], non_blocking=True)
-            plan.launch(ins_d, outs_d)
-            for o, p in zip(outs_d, outs_pin):
-                p.copy_(o.view(torch.int16) if o.dtype == torch.bfloat16 else o, non_blocking=True)
-            torch.cuda.current_stream().synchronize()
-
-        launches_per_step = 4
-        h2d = sum(p.numel() * 2 for i, p in enumerate(pins) if i != 5)
-        d2h = sum(p.numel() * p.element_size() for p in outs_pin)
-        metric, unit, dtype = "fused_gemm_tflops", "TFLOP/s", "bf16 x bf16 -> f32 accumulate, f32 epilogue"
-        workload = ("configs[2]: fused matmul 4096^3 bf16, mainloop relu(A)*M, epilogue bias/relu/tanh/gate/MSE + "
-                    "Sum over Batch and Columns + two backward tiles (README graph)")
-        to_value = lambda sec_per_step: C3_FLOPS * world / sec_per_step / 1e12
-        dominant = (plan.description, C3_FLOPS, "tensor", peaks["bf16_tflops"], "TFLOP/s", "gemm_c3")
-        l2_note = "256 MiB buffer written between iterations to flush L2 (inside the timed region; its ~40 us are included)"
+    reducer = GradReducer() if (world > 1 and args.workload == "c4") else None
+    wl = WORKLOADS[args.workload](ctx, dev, world, rank, peaks, reducer)
+    step, step_e2e = wl.step, wl.step_e2e
 
     # ---- warm-up, then the timed region ------------------------------------------------------------
     try:
@@ -350,14 +584,17 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         elapsed_ms = float(t.item())
     ms_per_step = elapsed_ms / args.steps
-    kernel_ms = statistics.mean(a.elapsed_time(b) for a, b in records)
+    per_kernel = {}
+    for name, a, b in records:
+        per_kernel.setdefault(name, []).append(a.elapsed_time(b))
+    kernel_ms = {k: statistics.mean(v) for k, v in per_kernel.items()}
     ctx.poll()
 
     # ---- end-to-end leg: host buffers in, host buffers out, copies inside the timed region ----------
     for _ in range(2):
         step_e2e()
     barrier()
-    e2e_steps = max(3, min(args.steps, 10))
+    e2e_steps = max(3, min(args.steps, 10)) if args.workload != "c1" else min(args.steps, 500)
     t0 = time.perf_counter()
     for _ in range(e2e_steps):
         step_e2e()
@@ -370,43 +607,42 @@ def main():
 
     clocks = sampler.stop() if rank == 0 else None
     if rank == 0:
-        name, work, bound, peak, punit, traffic_key = dominant
-        achieved = work / (kernel_ms * 1e-3) / (1e9 if bound == "hbm" else 1e12)
+        to_value = lambda sec: wl.work_per_step * world / sec / wl.work_scale
+        dom_key = wl.dominant_key or max(kernel_ms, key=kernel_ms.get)
+        name, work, bound, peak, punit = wl.dominant[dom_key]
+        k_ms = kernel_ms[dom_key]
+        achieved = work / (k_ms * 1e-3) / (1e9 if bound == "hbm" else 1e12)
+        roofline = {"bound": bound, "kernel": name, "achieved": achieved, "peak": peak, "unit": punit, "frac": achieved / peak,
+                    "peak_source": peaks["source"] + (": " + wl.peak_note if hasattr(wl, "peak_note") else ""),
+                    "kernel_ms": k_ms, "traffic": load_traffic(dom_key)}
+        if len(kernel_ms) > 1:
+            roofline["kernels"] = {}
+            for k, ms in kernel_ms.items():
+                _, w_k, b_k, p_k, _ = wl.dominant[k]
+                a_k = w_k / (ms * 1e-3) / (1e9 if b_k == "hbm" else 1e12)
+                roofline["kernels"][k] = {"ms": ms, "achieved": a_k, "frac": a_k / p_k, "share_of_step": ms / ms_per_step}
+        config = {"workload": wl.description, "l2": wl.l2_note}
+        if args.workload == "c4":
+            config.update({"tokens_per_gpu": wl.TOKENS, "sharding": "tokens", "grad_allreduce": "nccl avg, 3 buckets" if world > 1 else "none (1 rank)"})
+            if reducer is not None:
+                config["allreduce_bytes_per_step"] = reducer.bytes_reduced // max(1, (args.steps + args.warmup + 3 + e2e_steps))
+        else:
+            config["replicas"] = world
         line = {
-            "metric": metric, "value": to_value(ms_per_step * 1e-3), "unit": unit, "n_gpus": world, "steps": args.steps,
+            "metric": wl.metric, "value": to_value(ms_per_step * 1e-3), "unit": wl.unit, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": dtype, "data": "synthetic",
-            "config": {"workload": workload, "l2": l2_note, "replicas": world},
-            "roofline": {"bound": bound, "kernel": name, "achieved": achieved, "peak": peak, "unit": punit, "frac": achieved / peak,
-                         "peak_source": peaks["source"], "kernel_ms": kernel_ms, "traffic": load_traffic(traffic_key)},
-            "e2e": {"value": to_value(e2e_sec), "unit": unit, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+            "dtype": wl.dtype, "data": "synthetic", "config": config, "roofline": roofline,
+            "e2e": {"value": to_value(e2e_sec), "unit": wl.unit, "h2d_bytes_per_step": wl.h2d, "d2h_bytes_per_step": wl.d2h,
                     "ms_per_step": e2e_sec * 1e3},
-            "gpu_launches": launches_per_step * args.steps,
+            "gpu_launches": wl.launches_per_step * args.steps,
             "clocks": clocks,
         }
-        if args.workload == "c2" and not args.no_cpu_baseline:
-            from oracle import oracle_c as OC
-            x, s, b, p = x_h, s_h, b_h, p_h
-            OC.affine_relu_nchw_nhwc(x, s, b)  # first call also builds / loads the C object
-            reps = 3
-            t0 = time.perf_counter()
-            for _ in range(reps):
-                OC.affine_relu_nchw_nhwc(x, s, b)
-                OC.permute(p, [4096, 1, 4096 * 4096])
-            cpu_sec = (time.perf_counter() - t0) / reps
-            line["cpu_baseline"] = {"value": (C2A_BYTES + C2B_BYTES) / cpu_sec / 1e9, "unit": "GB/s", "cores": OC.num_threads(),
-                                    "kind": "port", "sample": f"{reps} full configs[1] steps of the C+OpenMP restatement (oracle/oracle_c.c); the reference has no CPU path"}
-        elif args.workload == "c3" and not args.no_cpu_baseline:
-            from oracle import oracle_c as OC
-            a, mk, bm = (np.ascontiguousarray(v).reshape(4096, 4096) for v in (ins_h[0], ins_h[1], ins_h[2]))
-            rows = 256
-            t0 = time.perf_counter()
-            OC.gemm_bf16(a, bm, mk, 0, rows)
-            cpu_sec = (time.perf_counter() - t0) * (4096 / rows)
-            line["cpu_baseline"] = {"value": C3_FLOPS / cpu_sec / 1e12, "unit": "TFLOP/s", "cores": OC.num_threads(), "kind": "port",
-                                    "sample": f"{rows} of 4096 output rows of the mainloop-fused GEMM, C+OpenMP restatement, scaled linearly"}
+        if not args.no_cpu_baseline and world == 1:
+            value, cores, sample, _ = wl.cpu_sample()
+            line["cpu_baseline"] = {"value": value, "unit": wl.unit, "cores": cores, "kind": "port", "sample": sample}
         print(json.dumps(line))
     if world > 1:
+        dist.barrier()
         dist.destroy_process_group()
     return 0
 

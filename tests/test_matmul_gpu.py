@@ -167,3 +167,29 @@ def test_simt_paths(ctx):
         got, plan = _run(ctx, g, ins)
         assert "SIMT" in plan.description
         _compare(g, got, O.evaluate(g, ins), plan.description)
+
+
+def test_mlp_block_forward_backward(ctx):
+    """configs[3] at a small size: every one of the six fused GEMMs against the oracle evaluated on
+    the operands that GEMM actually read (so an upstream rounding does not hide a downstream error)."""
+    import torch
+    from helium_b200.mlp_block import MlpBlock, mlp_block_inputs
+    tokens, d, ff = 384, 256, 512
+    blk = MlpBlock(ctx, tokens, d, ff)
+    host = mlp_block_inputs(tokens, d, ff)
+    blk.load(host)
+    blk.step()
+    torch.cuda.synchronize()
+    ctx.poll()
+    bits = lambda t: t.contiguous().view(torch.int16).cpu().numpy().view(np.uint16) if t.dtype == torch.bfloat16 else t.cpu().numpy()
+    dev = {k: bits(getattr(blk, k)) for k in ("X", "W1", "W2", "b1", "b2", "dO", "H", "Z", "O", "dZ", "dX", "dW1", "dW2", "db1", "db2")}
+    cases = {
+        "H": (["X", "W1", "b1"], ["H", "Z"]), "O": (["H", "W2", "b2", "X"], ["O"]),
+        "dZ": (["dO", "W2", "Z"], ["dZ", "db1"]), "dW1": (["X", "dZ"], ["dW1"]),
+        "dW2": (["H", "dO"], ["dW2"]), "dX": (["dZ", "W1", "dO"], ["dX", "db2"]),
+    }
+    for name, (ins, outs) in cases.items():
+        g = blk.graphs[name]
+        want = O.evaluate(g, [dev[k] for k in ins])
+        _compare(g, [dev[k] for k in outs], want, f"{name}: {blk.plans[name].description}")
+    assert blk.launch_count() >= 6

@@ -202,3 +202,18 @@ def test_invalid_descriptors_are_rejected_with_a_message():
     with pytest.raises(HeliumError) as e:
         hb.Plan.pointwise(None, g)
     assert "unary output descriptor" in str(e.value)
+
+
+def test_mlp_block_plans_at_full_size():
+    """configs[3]: all six GEMMs of the transformer MLP block map onto hand-written tcgen05 kernels."""
+    import helium_b200 as hb
+    from helium_b200.mlp_block import flops_per_token, mlp_block_graphs
+    graphs = mlp_block_graphs(8192, 4096, 16384)
+    assert set(graphs) == {"H", "O", "dZ", "dW1", "dW2", "dX"}
+    for name, g in graphs.items():
+        assert hb.plan_supported(g, 2) == 2, name
+        d = hb.Plan.fused_matmul(None, g).description
+        assert "tcgen05" in d and "flex" in d, (name, d)
+    assert "K-major B" in hb.Plan.fused_matmul(None, graphs["dZ"]).description
+    assert "M-major A" in hb.Plan.fused_matmul(None, graphs["dW1"]).description
+    assert flops_per_token(4096, 16384) * 8192 == 6 * 2 * 8192 * 4096 * 16384
