@@ -50,10 +50,15 @@ def load_peaks():
 
 
 def load_traffic(name: str):
-    """Per-launch DRAM traffic (bytes) of the dominant kernel from the committed ncu summary, or None."""
-    path = os.path.join(ROOT, "profiles", "traffic.json")
-    if os.path.exists(path):
-        return json.load(open(path)).get(name)
+    """Per-launch DRAM traffic (bytes) of the dominant kernel, read from the committed ncu summary
+    profiles/dram_traffic.txt (lines `key bytes  # comment`), or None when the kernel has no capture."""
+    path = os.path.join(ROOT, "profiles", "dram_traffic.txt")
+    if not os.path.exists(path):
+        return None
+    for ln in open(path):
+        f = ln.split("#")[0].split()
+        if len(f) >= 2 and f[0] == name:
+            return int(float(f[1]))
     return None
 
 
@@ -491,10 +496,21 @@ class WorkloadC1:
 WORKLOADS = {w.key: w for w in (WorkloadC1, WorkloadC2, WorkloadC3, WorkloadC4, WorkloadGemm)}
 
 
+def _use_all_host_threads():
+    """torch.distributed.run exports OMP_NUM_THREADS=1 to every rank; the CPU legs run on one rank only and
+    are meant to use every host core the process may run on, so undo that before the OpenMP library loads."""
+    if os.environ.get("OMP_NUM_THREADS") == "1" and "TORCHELASTIC_RUN_ID" in os.environ:
+        try:
+            os.environ["OMP_NUM_THREADS"] = str(len(os.sched_getaffinity(0)))
+        except AttributeError:
+            os.environ["OMP_NUM_THREADS"] = str(os.cpu_count() or 1)
+
+
 def run_reference_arm(args):
     """`--impl reference`: the reference is Rust + run-time generated CUDA, has no CPU implementation of
     this path and cannot be built in this image, so the arm times the CPU restatement of the same work
     (oracle/) on all host cores, on a bounded sample of the workload."""
+    _use_all_host_threads()
     wl = WORKLOADS[args.workload]
     n = {"c2": min(args.steps, 3), "c1": min(args.steps, 20)}.get(args.workload, 1)
     value, cores, sample, dt = wl.cpu_sample(max(1, n))
@@ -514,6 +530,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--brief", action="store_true",
+                    help="profiler captures only: no busy loop before the timed region, no end-to-end leg, no CPU baseline "
+                         "(the printed line is then not a bench value)")
     args = ap.parse_args()
     if args.steps is None:
         args.steps = {"c1": 2000, "c2": 200, "c3": 200, "c4": 30, "gemm": 100}[args.workload]
@@ -567,7 +586,7 @@ def main():
     barrier()
     # keep the device busy long enough for the clock record to cover the measurement
     t_busy = time.perf_counter()
-    while time.perf_counter() - t_busy < 0.6:
+    while not args.brief and time.perf_counter() - t_busy < 0.6:
         step()
         torch.cuda.synchronize()
     records = []
@@ -591,15 +610,17 @@ def main():
     ctx.poll()
 
     # ---- end-to-end leg: host buffers in, host buffers out, copies inside the timed region ----------
-    for _ in range(2):
+    e2e_steps = max(3, min(args.steps, 10)) if args.workload != "c1" else min(args.steps, 500)
+    if args.brief:
+        e2e_steps = 0
+    for _ in range(2 if e2e_steps else 0):
         step_e2e()
     barrier()
-    e2e_steps = max(3, min(args.steps, 10)) if args.workload != "c1" else min(args.steps, 500)
     t0 = time.perf_counter()
     for _ in range(e2e_steps):
         step_e2e()
     barrier()
-    e2e_sec = (time.perf_counter() - t0) / e2e_steps
+    e2e_sec = (time.perf_counter() - t0) / e2e_steps if e2e_steps else float("nan")
     if world > 1:
         t = torch.tensor([e2e_sec], device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -624,20 +645,21 @@ def main():
         config = {"workload": wl.description, "l2": wl.l2_note}
         if args.workload == "c4":
             config.update({"tokens_per_gpu": wl.TOKENS, "sharding": "tokens", "grad_allreduce": "nccl avg, 3 buckets" if world > 1 else "none (1 rank)"})
-            if reducer is not None:
-                config["allreduce_bytes_per_step"] = reducer.bytes_reduced // max(1, (args.steps + args.warmup + 3 + e2e_steps))
+            config["allreduce_bytes_per_step"] = (wl.blk.dW_flat.numel() * 2 + wl.blk.db_flat.numel() * 4) if world > 1 else 0
         else:
             config["replicas"] = world
         line = {
             "metric": wl.metric, "value": to_value(ms_per_step * 1e-3), "unit": wl.unit, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": wl.dtype, "data": "synthetic", "config": config, "roofline": roofline,
-            "e2e": {"value": to_value(e2e_sec), "unit": wl.unit, "h2d_bytes_per_step": wl.h2d, "d2h_bytes_per_step": wl.d2h,
-                    "ms_per_step": e2e_sec * 1e3},
+            "e2e": None if args.brief else {"value": to_value(e2e_sec), "unit": wl.unit, "h2d_bytes_per_step": wl.h2d,
+                                            "d2h_bytes_per_step": wl.d2h, "ms_per_step": e2e_sec * 1e3},
             "gpu_launches": wl.launches_per_step * args.steps,
             "clocks": clocks,
         }
-        if not args.no_cpu_baseline and world == 1:
+        if args.brief:
+            line["note"] = "--brief run for a profiler capture: not a bench value"
+        if not args.no_cpu_baseline and not args.brief and world == 1:
             value, cores, sample, _ = wl.cpu_sample()
             line["cpu_baseline"] = {"value": value, "unit": wl.unit, "cores": cores, "kind": "port", "sample": sample}
         print(json.dumps(line))
