@@ -415,6 +415,7 @@ struct MatmulPlan : he_plan {
       const void* ptrs[] = {p.epi.out, p.epi.out_z, p.epi.resid, p.epi.gate_in};
       for (const void* q : ptrs) vec = vec && ((uintptr_t)q % 16 == 0);
       p.epi.vec_ok = vec ? 1 : 0;
+      p.epi.bias_vec = (c.N % 8 == 0 && (uintptr_t)p.epi.bias % 16 == 0) ? 1 : 0;
       HE_TRY(launch_gemm_flex(cfg, p, stream));
       last_launches = 1;
       if (flex.colsum_src != 0) {
@@ -443,6 +444,7 @@ struct MatmulPlan : he_plan {
       const void* ptrs[] = {p.epi.mask, p.epi.y, p.epi.e1, p.epi.e2, p.epi.out_gt, p.epi.out_gz1};
       for (const void* q : ptrs) vec = vec && ((uintptr_t)q % 16 == 0);
       p.epi.vec_ok = vec ? 1 : 0;
+      p.epi.bias_vec = (c.N % 8 == 0 && (uintptr_t)p.epi.b1 % 16 == 0 && (uintptr_t)p.epi.b2 % 16 == 0) ? 1 : 0;
       HE_TRY(launch_gemm_c3(cfg, p, stream));
       HE_TRY(launch_colsum_finalize(ws + ws_col_off[0], (float*)outputs[r3.db2], c.batch, c.tiles_m, c.N, stream));
       HE_TRY(launch_colsum_finalize(ws + ws_col_off[1], (float*)outputs[r3.db1], c.batch, c.tiles_m, c.N, stream));

@@ -180,6 +180,7 @@ struct EpiFlexParams {
   const void* bias; const void* resid; const void* gate_in;
   float* colsum_partials;
   int out_dt, z_dt, bias_dt, resid_dt, gate_dt;
+  int bias_vec;   // bias pointer and N allow 16-byte loads
   int act, gate, colsum_src;  // colsum_src: 0 none, 1 resid, 2 y
   int vec_ok;
 };
@@ -197,6 +198,10 @@ __device__ __forceinline__ float fast_erf(float x) {
   const float y = 1.0f - poly * t * __expf(-ax * ax);
   return copysignf(y, x);
 }
+// tanh x = 1 - 2 / (1 + e^(2x)) on the exp2 / reciprocal units: absolute error ~2e-7 (libm's tanhf
+// costs ~30 instructions per element, which made the README epilogue outlast its mainloop).
+// Saturates correctly: e = inf gives 1, e = 0 gives -1.
+__device__ __forceinline__ float fast_tanh(float x) { return 1.0f - __fdividef(2.0f, 1.0f + __expf(2.0f * x)); }
 __device__ __forceinline__ float fast_gelu(float x) { return 0.5f * x * (1.0f + fast_erf(x * 0.70710678118654752440f)); }
 __device__ __forceinline__ float fast_dgelu(float x) {
   const float cdf = 0.5f * (1.0f + fast_erf(x * 0.70710678118654752440f));
@@ -209,20 +214,42 @@ struct EpiFlex {
   static constexpr int kChunk = 32;
   struct State {};
   __device__ static void tile_begin(State&) {}
-  __device__ static float activation(int act, float x) {
+  // The op selectors are uniform per launch: switch once per chunk, not once per element.
+  __device__ static void activate(int act, float (&v)[kChunk]) {
     switch (act) {
-      case ACT_RELU: return fmaxf(x, 0.0f);
-      case ACT_GELU: return fast_gelu(x);
-      case ACT_TANH: return tanhf(x);
-      default: return x;
+      case ACT_RELU:
+#pragma unroll
+        for (int i = 0; i < kChunk; ++i) v[i] = fmaxf(v[i], 0.0f);
+        break;
+      case ACT_GELU:
+#pragma unroll
+        for (int i = 0; i < kChunk; ++i) v[i] = fast_gelu(v[i]);
+        break;
+      case ACT_TANH:
+#pragma unroll
+        for (int i = 0; i < kChunk; ++i) v[i] = fast_tanh(v[i]);
+        break;
+      default: break;
     }
   }
-  __device__ static float gate_fn(int g, float x) {
+  __device__ static void apply_gate(int g, float (&v)[kChunk], const float (&x)[kChunk]) {
     switch (g) {
-      case GATE_DGELU: return fast_dgelu(x);
-      case GATE_DRELU: return x > 0.0f ? 1.0f : 0.0f;
-      case GATE_DTANH: return 1.0f - x * x;  // x is tanh(z)
-      default: return x;
+      case GATE_DGELU:
+#pragma unroll
+        for (int i = 0; i < kChunk; ++i) v[i] *= fast_dgelu(x[i]);
+        break;
+      case GATE_DRELU:
+#pragma unroll
+        for (int i = 0; i < kChunk; ++i) v[i] = x[i] > 0.0f ? v[i] : 0.0f;
+        break;
+      case GATE_DTANH:   // x is tanh(z)
+#pragma unroll
+        for (int i = 0; i < kChunk; ++i) v[i] *= 1.0f - x[i] * x[i];
+        break;
+      default:
+#pragma unroll
+        for (int i = 0; i < kChunk; ++i) v[i] *= x[i];
+        break;
     }
   }
   __device__ static void chunk(const Params& p, const EpiEnv& env, const TileInfo& t, State&, int row, int col, float (&v)[kChunk]) {
@@ -233,8 +260,10 @@ struct EpiFlex {
     const bool vec = p.vec_ok != 0;
     float aux[kChunk];
     if (p.bias) {
+      // every lane of the warp reads the same kChunk bias values: vector loads that hit L1
+      load_row<kChunk>(p.bias, p.bias_dt, (size_t)gcol, max(0, min(kChunk, c.N - gcol)), p.bias_vec != 0, aux);
 #pragma unroll
-      for (int i = 0; i < kChunk; ++i) v[i] += (gcol + i < c.N) ? load_param_as_f32(p.bias, p.bias_dt, gcol + i) : 0.0f;
+      for (int i = 0; i < kChunk; ++i) v[i] += aux[i];
     }
     if (p.resid) {
       load_row<kChunk>(p.resid, p.resid_dt, off, nvalid, vec, aux);
@@ -243,14 +272,10 @@ struct EpiFlex {
       if (p.colsum_src == 1) warp_colsum_store<kChunk>(aux, env.scratch + env.quadrant * env.bn + col);
     }
     if (p.out_z && nvalid > 0) store_row<kChunk>(p.out_z, p.z_dt, off, nvalid, vec, v);
-    if (p.act != ACT_NONE) {
-#pragma unroll
-      for (int i = 0; i < kChunk; ++i) v[i] = activation(p.act, v[i]);
-    }
+    if (p.act != ACT_NONE) activate(p.act, v);
     if (p.gate != GATE_NONE) {
       load_row<kChunk>(p.gate_in, p.gate_dt, off, nvalid, vec, aux);
-#pragma unroll
-      for (int i = 0; i < kChunk; ++i) v[i] *= gate_fn(p.gate, aux[i]);
+      apply_gate(p.gate, v, aux);
     }
     if (nvalid > 0) store_row<kChunk>(p.out, p.out_dt, off, nvalid, vec, v);
     if (p.colsum_src == 2) {
@@ -280,6 +305,7 @@ struct EpiC3Params {
   int full_dt;       // dtype of mask / y / e1 / e2 / gt / gz1
   int vec_dt;        // dtype of b1 / b2
   int vec_ok;
+  int bias_vec;      // b1 / b2 pointers and N allow 16-byte loads
 };
 
 struct EpiC3 {
@@ -308,14 +334,13 @@ struct EpiC3 {
 #pragma unroll
       for (int i = 0; i < kChunk; ++i) v[i] += a[i];
     }
+    const int ncols = max(0, min(kChunk, c.N - gcol));
+    load_row<kChunk>(p.b1, p.vec_dt, (size_t)gcol, ncols, p.bias_vec != 0, a);
 #pragma unroll
-    for (int i = 0; i < kChunk; ++i) {
-      const bool ok = gcol + i < c.N;
-      const float b1 = ok ? load_param_as_f32(p.b1, p.vec_dt, gcol + i) : 0.0f;
-      const float b2 = ok ? load_param_as_f32(p.b2, p.vec_dt, gcol + i) : 0.0f;
-      v[i] += b1;                       // z1
-      tnh[i] = tanhf(tnh[i] + b2);      // t
-    }
+    for (int i = 0; i < kChunk; ++i) v[i] += a[i];                      // z1
+    load_row<kChunk>(p.b2, p.vec_dt, (size_t)gcol, ncols, p.bias_vec != 0, a);
+#pragma unroll
+    for (int i = 0; i < kChunk; ++i) tnh[i] = fast_tanh(tnh[i] + a[i]);  // t
     float mk[kChunk];
     load_row<kChunk>(p.mask, p.full_dt, off, nvalid, vec, mk);
     load_row<kChunk>(p.y, p.full_dt, off, nvalid, vec, a);
