@@ -139,6 +139,7 @@ class WorkloadC2:
     launches_per_step = 2
     work_per_step = C2A_BYTES + C2B_BYTES
     work_scale = 1e9
+    e2e_note = "three streams, two device buffer sets: upload of step i+1, kernels of step i, download of step i-1 overlap"
 
     def __init__(self, ctx, dev, world, rank, peaks, reducer):
         import torch
@@ -161,6 +162,17 @@ class WorkloadC2:
         self.q_pin = torch.empty((8, 4096, 4096), dtype=torch.float32).pin_memory()
         self.h2d = self.x_pin.numel() * 2 + self.p_pin.numel() * 4 + 2 * 256 * 4
         self.d2h = self.y_pin.numel() * 2 + self.q_pin.numel() * 4
+        # end-to-end leg: two sets of device buffers and three streams, so that the upload of step i+1,
+        # the kernels of step i and the download of step i-1 overlap (PCIe is full duplex); this is the
+        # host-to-device pipelining helium's executor does per stream (helium/src/cuda.rs:192-222)
+        self.bufs = [dict(x=self.x_d, s=self.s_d, b=self.b_d, p=self.p_d, y=self.y_d, q=self.q_d),
+                     dict(x=torch.empty_like(self.x_d), s=torch.empty_like(self.s_d), b=torch.empty_like(self.b_d),
+                          p=torch.empty_like(self.p_d), y=torch.empty_like(self.y_d), q=torch.empty_like(self.q_d))]
+        self.st_up, self.st_run, self.st_down = (torch.cuda.Stream(device=dev) for _ in range(3))
+        self.ev_up = [torch.cuda.Event() for _ in range(2)]
+        self.ev_run = [torch.cuda.Event() for _ in range(2)]
+        self.ev_down = [torch.cuda.Event() for _ in range(2)]
+        self.e2e_i = 0
         self.dominant = {"permute_c2b": ("permute_tile_vec<4> on [4096,4096,8] f32", C2B_BYTES, "hbm", peaks["hbm_gbs"], "GB/s"),
                          "pointwise_c2a": ("affine+relu+NCHW->NHWC tile kernel on bf16 [64,256,56,56]", C2A_BYTES, "hbm", peaks["hbm_gbs"], "GB/s")}
         self.dominant_key = "permute_c2b"
@@ -178,15 +190,32 @@ class WorkloadC2:
         record.append(("pointwise_c2a", a0, a1)); record.append(("permute_c2b", b0, b1))
 
     def step_e2e(self):
+        """One step fed from pinned host memory, results read back to pinned host memory.  Steps are
+        software-pipelined over two buffer sets; the caller synchronises the device after the last one."""
         torch = self.torch
-        self.x_d.view(torch.int16).copy_(self.x_pin, non_blocking=True)
-        self.s_d.copy_(self.s_pin, non_blocking=True); self.b_d.copy_(self.b_pin, non_blocking=True)
-        self.p_d.copy_(self.p_pin, non_blocking=True)
-        self.plan_a.launch([self.x_d, self.s_d, self.b_d], [self.y_d])
-        self.plan_b.launch([self.p_d], [self.q_d])
-        self.y_pin.copy_(self.y_d.view(torch.int16), non_blocking=True)
-        self.q_pin.copy_(self.q_d, non_blocking=True)
-        torch.cuda.current_stream().synchronize()
+        k = self.e2e_i & 1
+        first_use = self.e2e_i < 2
+        self.e2e_i += 1
+        B = self.bufs[k]
+        with torch.cuda.stream(self.st_up):
+            if not first_use:
+                self.st_up.wait_event(self.ev_run[k])      # the kernels that last read this input set are done
+            B["x"].view(torch.int16).copy_(self.x_pin, non_blocking=True)
+            B["s"].copy_(self.s_pin, non_blocking=True); B["b"].copy_(self.b_pin, non_blocking=True)
+            B["p"].copy_(self.p_pin, non_blocking=True)
+            self.ev_up[k].record(self.st_up)
+        with torch.cuda.stream(self.st_run):
+            self.st_run.wait_event(self.ev_up[k])
+            if not first_use:
+                self.st_run.wait_event(self.ev_down[k])   # the previous results of this set have left the device
+            self.plan_a.launch([B["x"], B["s"], B["b"]], [B["y"]])
+            self.plan_b.launch([B["p"]], [B["q"]])
+            self.ev_run[k].record(self.st_run)
+        with torch.cuda.stream(self.st_down):
+            self.st_down.wait_event(self.ev_run[k])
+            self.y_pin.copy_(B["y"].view(torch.int16), non_blocking=True)
+            self.q_pin.copy_(B["q"], non_blocking=True)
+            self.ev_down[k].record(self.st_down)
 
     @staticmethod
     def cpu_sample(max_steps=3):
@@ -610,7 +639,7 @@ def main():
     ctx.poll()
 
     # ---- end-to-end leg: host buffers in, host buffers out, copies inside the timed region ----------
-    e2e_steps = max(3, min(args.steps, 10)) if args.workload != "c1" else min(args.steps, 500)
+    e2e_steps = {"c1": min(args.steps, 500), "c2": max(3, min(args.steps, 40))}.get(args.workload, max(3, min(args.steps, 10)))
     if args.brief:
         e2e_steps = 0
     for _ in range(2 if e2e_steps else 0):
@@ -653,7 +682,8 @@ def main():
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": wl.dtype, "data": "synthetic", "config": config, "roofline": roofline,
             "e2e": None if args.brief else {"value": to_value(e2e_sec), "unit": wl.unit, "h2d_bytes_per_step": wl.h2d,
-                                            "d2h_bytes_per_step": wl.d2h, "ms_per_step": e2e_sec * 1e3},
+                                            "d2h_bytes_per_step": wl.d2h, "ms_per_step": e2e_sec * 1e3, "steps": e2e_steps,
+                                            "pipelining": getattr(wl, "e2e_note", "one stream: upload, kernels, download in order")},
             "gpu_launches": wl.launches_per_step * args.steps,
             "clocks": clocks,
         }
