@@ -129,6 +129,44 @@ def _events(torch):
     return torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
 
 
+class _E2EPipeline:
+    """End-to-end leg: two sets of device buffers and three streams, so that the upload of step i+1, the
+    kernels of step i and the download of step i-1 overlap (PCIe is full duplex).  This is the
+    host-to-device pipelining helium's executor does per stream (helium/src/cuda.rs:192-222).
+    `upload(k)`, `run(k)`, `download(k)` enqueue the work of one step on buffer set k; the caller
+    synchronises the device after the last step."""
+    note = "three streams, two device buffer sets: upload of step i+1, kernels of step i, download of step i-1 overlap"
+
+    def __init__(self, torch, dev):
+        self.torch = torch
+        self.st_up, self.st_run, self.st_down = (torch.cuda.Stream(device=dev) for _ in range(3))
+        self.ev_up = [torch.cuda.Event() for _ in range(2)]
+        self.ev_run = [torch.cuda.Event() for _ in range(2)]
+        self.ev_down = [torch.cuda.Event() for _ in range(2)]
+        self.i = 0
+
+    def step(self, upload, run, download):
+        torch = self.torch
+        k = self.i & 1
+        first_use = self.i < 2
+        self.i += 1
+        with torch.cuda.stream(self.st_up):
+            if not first_use:
+                self.st_up.wait_event(self.ev_run[k])      # the kernels that last read this input set are done
+            upload(k)
+            self.ev_up[k].record(self.st_up)
+        with torch.cuda.stream(self.st_run):
+            self.st_run.wait_event(self.ev_up[k])
+            if not first_use:
+                self.st_run.wait_event(self.ev_down[k])   # the previous results of this set have left the device
+            run(k)
+            self.ev_run[k].record(self.st_run)
+        with torch.cuda.stream(self.st_down):
+            self.st_down.wait_event(self.ev_run[k])
+            download(k)
+            self.ev_down[k].record(self.st_down)
+
+
 class WorkloadC2:
     key = "c2"
     metric, unit = "pointwise_permute_hbm_gbs", "GB/s"
@@ -139,7 +177,7 @@ class WorkloadC2:
     launches_per_step = 2
     work_per_step = C2A_BYTES + C2B_BYTES
     work_scale = 1e9
-    e2e_note = "three streams, two device buffer sets: upload of step i+1, kernels of step i, download of step i-1 overlap"
+    e2e_note = _E2EPipeline.note
 
     def __init__(self, ctx, dev, world, rank, peaks, reducer):
         import torch
@@ -162,17 +200,10 @@ class WorkloadC2:
         self.q_pin = torch.empty((8, 4096, 4096), dtype=torch.float32).pin_memory()
         self.h2d = self.x_pin.numel() * 2 + self.p_pin.numel() * 4 + 2 * 256 * 4
         self.d2h = self.y_pin.numel() * 2 + self.q_pin.numel() * 4
-        # end-to-end leg: two sets of device buffers and three streams, so that the upload of step i+1,
-        # the kernels of step i and the download of step i-1 overlap (PCIe is full duplex); this is the
-        # host-to-device pipelining helium's executor does per stream (helium/src/cuda.rs:192-222)
         self.bufs = [dict(x=self.x_d, s=self.s_d, b=self.b_d, p=self.p_d, y=self.y_d, q=self.q_d),
                      dict(x=torch.empty_like(self.x_d), s=torch.empty_like(self.s_d), b=torch.empty_like(self.b_d),
                           p=torch.empty_like(self.p_d), y=torch.empty_like(self.y_d), q=torch.empty_like(self.q_d))]
-        self.st_up, self.st_run, self.st_down = (torch.cuda.Stream(device=dev) for _ in range(3))
-        self.ev_up = [torch.cuda.Event() for _ in range(2)]
-        self.ev_run = [torch.cuda.Event() for _ in range(2)]
-        self.ev_down = [torch.cuda.Event() for _ in range(2)]
-        self.e2e_i = 0
+        self.pipe = _E2EPipeline(torch, dev)
         self.dominant = {"permute_c2b": ("permute_tile_vec<4> on [4096,4096,8] f32", C2B_BYTES, "hbm", peaks["hbm_gbs"], "GB/s"),
                          "pointwise_c2a": ("affine+relu+NCHW->NHWC tile kernel on bf16 [64,256,56,56]", C2A_BYTES, "hbm", peaks["hbm_gbs"], "GB/s")}
         self.dominant_key = "permute_c2b"
@@ -190,32 +221,25 @@ class WorkloadC2:
         record.append(("pointwise_c2a", a0, a1)); record.append(("permute_c2b", b0, b1))
 
     def step_e2e(self):
-        """One step fed from pinned host memory, results read back to pinned host memory.  Steps are
-        software-pipelined over two buffer sets; the caller synchronises the device after the last one."""
         torch = self.torch
-        k = self.e2e_i & 1
-        first_use = self.e2e_i < 2
-        self.e2e_i += 1
-        B = self.bufs[k]
-        with torch.cuda.stream(self.st_up):
-            if not first_use:
-                self.st_up.wait_event(self.ev_run[k])      # the kernels that last read this input set are done
+
+        def upload(k):
+            B = self.bufs[k]
             B["x"].view(torch.int16).copy_(self.x_pin, non_blocking=True)
             B["s"].copy_(self.s_pin, non_blocking=True); B["b"].copy_(self.b_pin, non_blocking=True)
             B["p"].copy_(self.p_pin, non_blocking=True)
-            self.ev_up[k].record(self.st_up)
-        with torch.cuda.stream(self.st_run):
-            self.st_run.wait_event(self.ev_up[k])
-            if not first_use:
-                self.st_run.wait_event(self.ev_down[k])   # the previous results of this set have left the device
+
+        def run(k):
+            B = self.bufs[k]
             self.plan_a.launch([B["x"], B["s"], B["b"]], [B["y"]])
             self.plan_b.launch([B["p"]], [B["q"]])
-            self.ev_run[k].record(self.st_run)
-        with torch.cuda.stream(self.st_down):
-            self.st_down.wait_event(self.ev_run[k])
+
+        def download(k):
+            B = self.bufs[k]
             self.y_pin.copy_(B["y"].view(torch.int16), non_blocking=True)
             self.q_pin.copy_(B["q"], non_blocking=True)
-            self.ev_down[k].record(self.st_down)
+
+        self.pipe.step(upload, run, download)
 
     @staticmethod
     def cpu_sample(max_steps=3):
@@ -279,6 +303,8 @@ class WorkloadGemm(_GemmBase):
         self.outs_d = self.plan.alloc_outputs(dev)
         self.out_pin = torch.empty((m, n), dtype=torch.bfloat16).pin_memory()
         self.flush = self._flush_buffer(dev)
+        self.sets = [(self.a_d, self.b_d, self.outs_d), (torch.empty_like(self.a_d), torch.empty_like(self.b_d), self.plan.alloc_outputs(dev))]
+        self.pipe = _E2EPipeline(torch, dev)
         self.h2d, self.d2h = 2 * m * k * 2, m * n * 2
         self.dominant = {"gemm_plain": (self.plan.description, self.work_per_step, "tensor", peaks["bf16_tflops"], "TFLOP/s")}
         self.dominant_key = "gemm_plain"
@@ -293,11 +319,19 @@ class WorkloadGemm(_GemmBase):
         e0.record(st); self.plan.launch([self.a_d, self.b_d], self.outs_d); e1.record(st)
         record.append(("gemm_plain", e0, e1))
 
+    e2e_note = _E2EPipeline.note
+
     def step_e2e(self):
-        self.a_d.copy_(self.a_pin, non_blocking=True); self.b_d.copy_(self.b_pin, non_blocking=True)
-        self.plan.launch([self.a_d, self.b_d], self.outs_d)
-        self.out_pin.copy_(self.outs_d[0], non_blocking=True)
-        self.torch.cuda.current_stream().synchronize()
+        def upload(k):
+            self.sets[k][0].copy_(self.a_pin, non_blocking=True); self.sets[k][1].copy_(self.b_pin, non_blocking=True)
+
+        def run(k):
+            self.plan.launch([self.sets[k][0], self.sets[k][1]], self.sets[k][2])
+
+        def download(k):
+            self.out_pin.copy_(self.sets[k][2][0], non_blocking=True)
+
+        self.pipe.step(upload, run, download)
 
     @staticmethod
     def cpu_sample(max_steps=1):
@@ -329,6 +363,10 @@ class WorkloadC3(_GemmBase):
         self.outs_pin = [torch.empty(o.shape, dtype=torch.int16 if o.dtype == torch.bfloat16 else torch.float32).pin_memory()
                          for o in self.outs_d]
         self.flush = self._flush_buffer(dev)
+        ins2 = [torch.empty_like(t) for t in self.ins_d]
+        ins2[5] = ins2[1]
+        self.sets = [(self.ins_d, self.outs_d), (ins2, self.plan.alloc_outputs(dev))]
+        self.pipe = _E2EPipeline(torch, dev)
         self.h2d = sum(p.numel() * 2 for i, p in enumerate(self.pins) if i != 5)
         self.d2h = sum(p.numel() * p.element_size() for p in self.outs_pin)
         self.plan.launch(self.ins_d, self.outs_d)
@@ -346,15 +384,24 @@ class WorkloadC3(_GemmBase):
         e0.record(st); self.plan.launch(self.ins_d, self.outs_d); e1.record(st)
         record.append(("gemm_c3", e0, e1))
 
+    e2e_note = _E2EPipeline.note
+
     def step_e2e(self):
         torch = self.torch
-        for i, (d, p) in enumerate(zip(self.ins_d, self.pins)):
-            if i != 5:
-                d.view(torch.int16).copy_(p, non_blocking=True)
-        self.plan.launch(self.ins_d, self.outs_d)
-        for o, p in zip(self.outs_d, self.outs_pin):
-            p.copy_(o.view(torch.int16) if o.dtype == torch.bfloat16 else o, non_blocking=True)
-        torch.cuda.current_stream().synchronize()
+
+        def upload(k):
+            for i, (d, p) in enumerate(zip(self.sets[k][0], self.pins)):
+                if i != 5:
+                    d.view(torch.int16).copy_(p, non_blocking=True)
+
+        def run(k):
+            self.plan.launch(self.sets[k][0], self.sets[k][1])
+
+        def download(k):
+            for o, p in zip(self.sets[k][1], self.outs_pin):
+                p.copy_(o.view(torch.int16) if o.dtype == torch.bfloat16 else o, non_blocking=True)
+
+        self.pipe.step(upload, run, download)
 
     @staticmethod
     def cpu_sample(max_steps=1):
@@ -390,6 +437,10 @@ class WorkloadC4(_GemmBase):
         self.db_pin = torch.empty(ff + d, dtype=torch.float32).pin_memory()
         self.h2d = 2 * T * d * 2
         self.d2h = T * d * 2 + (ff + d) * 4
+        blk = self.blk
+        self.io = [(blk.X, blk.dO, blk.dX, blk.db_flat),
+                   (torch.empty_like(blk.X), torch.empty_like(blk.dO), torch.empty_like(blk.dX), torch.empty_like(blk.db_flat))]
+        self.pipe = _E2EPipeline(torch, dev)
         self.blk.step(self.reducer)
         self.launches_per_step = self.blk.launch_count()
         peak = peaks.get("bf16_tflops_sustained") or peaks["bf16_tflops"]
@@ -426,15 +477,30 @@ class WorkloadC4(_GemmBase):
             red.reduce_bucket([blk.db_flat])
             red.finish()
 
+    e2e_note = _E2EPipeline.note + "; the gradient all-reduce runs on its own stream behind the kernels of the same step"
+
+    def _bind_io(self, k):
+        blk = self.blk
+        blk.X, blk.dO, blk.dX, blk.db_flat = self.io[k]
+        blk.db1 = blk.db_flat[:blk.ff].view(1, blk.ff)
+        blk.db2 = blk.db_flat[blk.ff:].view(1, blk.d)
+
     def step_e2e(self):
         torch = self.torch
-        blk = self.blk
-        blk.X.view(torch.int16).copy_(self.x_pin, non_blocking=True)
-        blk.dO.view(torch.int16).copy_(self.do_pin, non_blocking=True)
-        blk.step(self.reducer)
-        self.dx_pin.copy_(blk.dX.view(torch.int16), non_blocking=True)
-        self.db_pin.copy_(blk.db_flat, non_blocking=True)
-        torch.cuda.current_stream().synchronize()
+
+        def upload(k):
+            self.io[k][0].view(torch.int16).copy_(self.x_pin, non_blocking=True)
+            self.io[k][1].view(torch.int16).copy_(self.do_pin, non_blocking=True)
+
+        def run(k):
+            self._bind_io(k)
+            self.blk.step(self.reducer)
+
+        def download(k):
+            self.dx_pin.copy_(self.io[k][2].view(torch.int16), non_blocking=True)
+            self.db_pin.copy_(self.io[k][3], non_blocking=True)
+
+        self.pipe.step(upload, run, download)
 
     @staticmethod
     def cpu_sample(max_steps=1):
