@@ -104,7 +104,9 @@ struct TileParams {
   int lg_chunks_x;       // log2 of 16-byte chunks per tile row
   int lg_y_blocks;       // log2(TY / 32)
   unsigned tiles_x, tiles_y;
+  int xt;                // consecutive X tiles one CTA of the vector kernel walks (amortises its prologue)
   FastDiv fd_tiles_x, fd_tiles_y, fd_b[kMaxBatchDims];   // 32-bit magic division for the CTA prologue
+                                                         // (fd_tiles_x divides by the number of X tile groups)
   // affine functor
   int f_mode, f_batch, relu, has_scale, has_bias, s_dt, b_dt;
   const void* scale;
@@ -191,12 +193,11 @@ __global__ void __launch_bounds__(kThreads) permute_tile_vec(const __grid_consta
   const BatchOffsets bo = decode_block(p, tx, ty);
   const int TX = kFixed ? TXW_C * EPW : p.TX, TY = kFixed ? TY_C : p.TY;
   const int P = kFixed ? (TXW_C > 8 ? TXW_C : 8) + 1 : p.P;
-  const long long x0 = (long long)tx * TX, y0 = (long long)ty * TY;
-  // rows / columns of this tile that exist (tiles at the border are partial)
-  const unsigned nx = (unsigned)min((long long)TX, p.X - x0), ny = (unsigned)min((long long)TY, p.Y - y0);
-  const char* in_tile = reinterpret_cast<const char*>(p.in) + (bo.in_base + y0 * p.in_sY + x0) * EB;
-  char* out_tile = reinterpret_cast<char*>(p.out) + (bo.out_base + x0 * p.out_sX + y0) * EB;
+  const long long y0 = (long long)ty * TY;
+  const unsigned ny = (unsigned)min((long long)TY, p.Y - y0);   // rows of this tile that exist
   const unsigned in_sY = (unsigned)p.in_sY, out_sX = (unsigned)p.out_sX;
+  const unsigned tx_first = tx * (unsigned)p.xt;
+  long long x0 = (long long)tx_first * TX;
 
   // ---- fused-affine parameters: one (scale, bias) pair per row / column / CTA, staged in smem ----
   float* par = reinterpret_cast<float*>(sm + TY * P);
@@ -212,6 +213,15 @@ __global__ void __launch_bounds__(kThreads) permute_tile_vec(const __grid_consta
     __syncthreads();
   }
 
+  // A CTA walks p.xt consecutive X tiles of the same (Y tile, batch): block decode and parameter
+  // staging above are paid once (with parameters along X the host keeps p.xt at 1).
+#pragma unroll 1
+  for (int xs = 0; xs < p.xt; ++xs, x0 += TX) {
+  if (tx_first + xs >= p.tiles_x) break;
+  if (xs > 0) __syncthreads();   // the previous tile's transposed reads are done
+  const unsigned nx = (unsigned)min((long long)TX, p.X - x0);   // columns of this tile that exist
+  const char* in_tile = reinterpret_cast<const char*>(p.in) + (bo.in_base + y0 * p.in_sY + x0) * EB;
+  char* out_tile = reinterpret_cast<char*>(p.out) + (bo.out_base + x0 * p.out_sX + y0) * EB;
   // ---- phase 1: global (vector along X) -> shared [y][xw] -------------------------------------
   {
     const int lg_cx = kFixed ? ilog2_c(TXW_C / 4) : p.lg_chunks_x;   // chunks (16 B) per tile row = 1 << lg_cx
@@ -308,6 +318,7 @@ __global__ void __launch_bounds__(kThreads) permute_tile_vec(const __grid_consta
       }
     }
   }
+  }  // X tiles of this CTA
 }
 
 // Scalar fallback: classic 32x32 tile, one element per thread per pass.
@@ -643,13 +654,23 @@ int32_t make_permute_plan(he_ctx* ctx, int rank, const int64_t* in_shape, const 
     delete plan;
     HE_FAIL(HE_ERR_UNSUPPORTED, "permute: too many tiles");
   }
-  tp.fd_tiles_x = FastDiv(tp.tiles_x);
+  // X tiles per CTA: as many (1, 2 or 4) as still leave at least four full waves of CTAs
+  tp.xt = 1;
+  if (vec && tp.f_mode != F_AXIS_X) {
+    const size_t smem_c = (size_t)tp.TY * tp.P * 4 + 1024;
+    const long long per_wave = (long long)ctx_sm_count(ctx) *
+                               (long long)std::max<size_t>(1, std::min<size_t>(2048 / kThreads, (size_t)(220 * 1024) / smem_c));
+    while (tp.xt < 4 && (long long)tp.tiles_x >= 2 * tp.xt && g64 / (2 * tp.xt) >= 4 * per_wave) tp.xt *= 2;
+  }
+  const unsigned tiles_xg = (tp.tiles_x + tp.xt - 1) / tp.xt;
+  g64 = (long long)tiles_xg * tp.tiles_y * batch;
+  tp.fd_tiles_x = FastDiv(tiles_xg);
   tp.fd_tiles_y = FastDiv(tp.tiles_y);
   for (int k = 0; k < tp.nb; ++k) tp.fd_b[k] = FastDiv((uint32_t)tp.b_ext[k]);
   plan->grid = g64;
   plan->smem = (size_t)tp.TY * tp.P * 4 + (fn ? (size_t)std::max(tp.TX, tp.TY) * 8 : 0);
-  snprintf(desc, sizeof desc, "permute: tile %dx%d (%d-byte elems, pitch %d words, %s%s), grid %lld",
-           tp.TX, tp.TY, eb, tp.P, vec ? "16-byte vectors" : "scalar fallback", fn ? ", fused affine" : "", g64);
+  snprintf(desc, sizeof desc, "permute: tile %dx%d (%d-byte elems, pitch %d words, %s%s), %d X tile(s) per CTA, grid %lld",
+           tp.TX, tp.TY, eb, tp.P, vec ? "16-byte vectors" : "scalar fallback", fn ? ", fused affine" : "", tp.xt, g64);
   plan->description = desc;
   *out = plan;
   return HE_OK;
