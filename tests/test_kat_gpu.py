@@ -61,3 +61,32 @@ def test_matmul_vectors(ctx, case):
     torch.cuda.synchronize()
     got = c.float().cpu().numpy().reshape(-1)
     assert np.allclose(got, expected[0], rtol=0, atol=tol * max(1.0, np.abs(expected[0]).max())), f"{name} ({where})"
+
+
+from test_oracle_golden import compare_with_golden, golden_cases  # noqa: E402
+
+
+@pytest.mark.parametrize("case", golden_cases(), ids=lambda c: c[0])
+def test_golden_fixtures_on_device(ctx, case):
+    """The committed golden outputs (tests/golden) through the C ABI: pointwise / permute cases as
+    pointwise plans, matmul cases as fused matmul plans, the training step through the host runtime."""
+    import torch
+    name, g, ins, want = case
+    tin = [storage_to_torch(a, g.nodes[i].dtype) for a, i in zip(ins, g.inputs)]
+    if name == "mlp_train_step":
+        touts = [torch.zeros(g.nodes[o].shape, dtype=torch.float32, device="cuda") for o in g.outputs]
+        ex = hb.Executor(ctx, hb.HostGraph(g), tin, touts, capture=True)
+        ex.run(); ex.run()
+    elif any(n.kind == ir.OP_MATMUL for n in g.nodes):
+        touts = hb.Plan.fused_matmul(ctx, g).launch(tin)
+    else:
+        touts = hb.Plan.pointwise(ctx, g).launch(tin)
+    torch.cuda.synchronize()
+    ctx.poll()
+    got = [torch_to_storage(t, g.nodes[o].dtype) for t, o in zip(touts, g.outputs)]
+    if name == "affine_relu_nhwc":
+        # one f32 fma then one rounding vs the f64 oracle: double-rounding ties may differ by one ulp
+        a, b = np.asarray(got[0]).reshape(-1).astype(np.int64), np.asarray(want[0]).reshape(-1).astype(np.int64)
+        assert np.abs(a - b).max() <= 1 and np.mean(a != b) < 1e-3
+    else:
+        compare_with_golden(g, got, want, exact_moves=name.startswith("permute"))

@@ -193,3 +193,57 @@ def test_mlp_block_forward_backward(ctx):
         want = O.evaluate(g, [dev[k] for k in ins])
         _compare(g, [dev[k] for k in outs], want, f"{name}: {blk.plans[name].description}")
     assert blk.launch_count() >= 6
+
+
+def test_mlp_block_full_size_sampled(ctx):
+    """configs[3] at its benchmark size (8192 tokens, d 4096, ff 16384).  The numpy oracle would take
+    hours, so 32 sampled output rows of every GEMM go through the C oracle's bf16 GEMM (f32
+    accumulate) with the epilogue restated in f64, and the bias gradients are checked as checksums."""
+    import torch
+    from math import sqrt
+    from scipy.special import erf
+    from oracle import oracle_c as OC
+    from helium_b200.mlp_block import MlpBlock, mlp_block_inputs
+    T, d, ff = 8192, 4096, 16384
+    blk = MlpBlock(ctx, T, d, ff)
+    host = mlp_block_inputs(T, d, ff)
+    blk.load(host)
+    blk.step()
+    torch.cuda.synchronize()
+    ctx.poll()
+    bits = lambda t: t.contiguous().view(torch.int16).cpu().numpy().view(np.uint16)
+    dec = lambda b: (np.asarray(b, dtype=np.uint16).astype(np.uint32) << 16).view(np.float32).astype(np.float64)
+    dev = {k: bits(getattr(blk, k)) for k in ("H", "Z", "O", "dZ", "dX", "dW1", "dW2")}
+    r = rng(31)
+    rows_t = np.sort(r.choice(T, 32, replace=False))
+    close = lambda got, want, what: (O.rel_l2(got, want) <= 1e-2) or pytest.fail(f"{what}: rel-L2 {O.rel_l2(got, want):.3e}")
+    gelu = lambda z: 0.5 * z * (1 + erf(z / sqrt(2)))
+    dgelu = lambda z: 0.5 * (1 + erf(z / sqrt(2))) + z * np.exp(-0.5 * z * z) / sqrt(2 * np.pi)
+    X, W1, W2, dO = host["X"], host["W1"], host["W2"], host["dO"]
+    b1, b2 = dec(host["b1"]), dec(host["b2"])
+    # H = gelu(X W1 + b1), Z kept
+    z = OC.gemm_bf16(X[rows_t], W1).astype(np.float64) + b1
+    close(dec(dev["Z"][rows_t]), z, "Z")
+    close(dec(dev["H"][rows_t]), gelu(z), "H")
+    # O = H W2 + b2 + X   (H as the kernel stored it)
+    o = OC.gemm_bf16(dev["H"][rows_t], W2).astype(np.float64) + b2 + dec(X[rows_t])
+    close(dec(dev["O"][rows_t]), o, "O")
+    # dZ = (dO W2^T) * gelu'(Z)
+    w2t = np.ascontiguousarray(W2.T)
+    dz = OC.gemm_bf16(dO[rows_t], w2t).astype(np.float64) * dgelu(dec(dev["Z"][rows_t]))
+    close(dec(dev["dZ"][rows_t]), dz, "dZ")
+    # dX = dZ W1^T + dO
+    w1t = np.ascontiguousarray(W1.T)
+    dx = OC.gemm_bf16(dev["dZ"][rows_t], w1t).astype(np.float64) + dec(dO[rows_t])
+    close(dec(dev["dX"][rows_t]), dx, "dX")
+    # dW1 = X^T dZ (rows of dW1 are columns of X), dW2 = H^T dO
+    rows_d = np.sort(r.choice(d, 32, replace=False))
+    close(dec(dev["dW1"][rows_d]), OC.gemm_bf16(np.ascontiguousarray(X[:, rows_d].T), dev["dZ"]).astype(np.float64), "dW1")
+    rows_f = np.sort(r.choice(ff, 32, replace=False))
+    close(dec(dev["dW2"][rows_f]), OC.gemm_bf16(np.ascontiguousarray(dev["H"][:, rows_f].T), dO).astype(np.float64), "dW2")
+    # bias gradients: db2 = colsum(dO) from the inputs (f32 tolerance); db1 = colsum(dZ) against the
+    # column sums of the stored (bf16-rounded) dZ, which bounds it to the rounding of 8192 terms
+    db2 = blk.db2.cpu().numpy().reshape(-1).astype(np.float64)
+    assert O.rel_l2(db2, dec(dO).sum(0)) <= 1e-5
+    db1 = blk.db1.cpu().numpy().reshape(-1).astype(np.float64)
+    assert O.rel_l2(db1, dec(dev["dZ"]).sum(0)) <= 2e-3
