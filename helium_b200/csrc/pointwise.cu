@@ -379,14 +379,18 @@ int32_t plan_pointwise(he_ctx* ctx, const Graph& g, he_plan** out, int* tier_onl
         L.red_out_slot[s] = (int)o;
         ++s;
       }
-    if (P.group_size <= 2048) {
+    // Small problems (a few launches' worth of latency, not bandwidth) are spread as widely as they
+    // go: a thread that walks 8-16 elements of a fused prologue serially pays a dependent memory
+    // latency per element, which made 2560-element reductions take 30 us.
+    const bool small = (uint64_t)L.num_groups * P.group_size <= (1u << 21);
+    if (P.group_size <= (small ? 32u : 2048u)) {
       L.warp_mode = 1;
       L.blocks_per_group = 1;
       L.chunk = P.group_size;
     } else {
       L.warp_mode = 0;
-      // ~16 elements per thread per CTA, but never more CTAs than ~8 waves' worth of the GPU
-      uint32_t chunk = kPwThreads * 16;
+      // ~16 elements per thread per CTA (one for small problems), but never more CTAs than ~8 waves' worth of the GPU
+      uint32_t chunk = kPwThreads * (small ? 1 : 16);
       uint32_t bpg = (P.group_size + chunk - 1) / chunk;
       uint64_t max_ctas = (uint64_t)ctx_sm_count(ctx) * 64;
       if ((uint64_t)bpg * L.num_groups > max_ctas) {
