@@ -27,6 +27,7 @@ SOURCES = [
     "permute.cu",
     "pointwise_compile.cu",
     "pointwise.cu",
+    "pointwise_dense.cu",
     "gemm_plan.cu",
     "gemm_kernels_flex.cu",
     "gemm_kernels_c3.cu",

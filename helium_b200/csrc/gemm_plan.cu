@@ -13,6 +13,7 @@
 #include <mutex>
 
 #include "gemm_plan.cuh"
+#include "pointwise_dense.cuh"
 
 namespace he {
 namespace {
@@ -379,6 +380,12 @@ struct MatmulPlan : he_plan {
   int s_bias = -1, s_act = 0, s_in_dt = HE_F32, s_out_dt = HE_F32, s_bias_dt = HE_F32;
   // workspace layout (floats)
   size_t ws_col_off[2] = {0, 0}, ws_scalar_off = 0;
+  // Mainloop fusion by materialisation: relu(A) * mask is written once to the workspace by the dense
+  // elementwise kernel and the GEMM runs its plain mainloop on it.  Chosen at plan time when the
+  // in-kernel rewrite (repeated for every N tile, at about half the plain mainloop's rate) would
+  // cost more than one extra pass over A and the mask.
+  bool materialise_a = false;
+  size_t ws_aprime_off = 0;   // bytes
 
   int32_t launch(const void* const* inputs, void* const* outputs, void* workspace, cudaStream_t stream) override {
     for (int i = 0; i < n_inputs; ++i)
@@ -393,11 +400,26 @@ struct MatmulPlan : he_plan {
       return HE_OK;
     }
     float* ws = reinterpret_cast<float*>(workspace);
+    if (workspace_bytes > 0 && !workspace) HE_FAIL(HE_ERR_WORKSPACE, "fused matmul launch: this plan needs a %zu-byte workspace", workspace_bytes);
     CUtensorMap ta, tb, tm;
     memset(&tm, 0, sizeof tm);
-    HE_TRY(make_operand_tmap(&ta, inputs[a_slot], core.ab_format, cfg.a_mn, core.M, core.K, core.batch, kBM));
+    const void* a_ptr = inputs[a_slot];
+    GemmLaunchCfg cfg = this->cfg;
+    int extra_launches = 0;
+    if (materialise_a) {
+      void* a_prime = reinterpret_cast<char*>(workspace) + ws_aprime_off;
+      const void* ew_in[3] = {inputs[mask_slot], inputs[a_slot], nullptr};   // a * relu(b): mask * relu(A)
+      if ((reinterpret_cast<uintptr_t>(ew_in[0]) | reinterpret_cast<uintptr_t>(ew_in[1])) & 15)
+        HE_FAIL(HE_ERR_UNSUPPORTED, "fused matmul: operand pointer is not 16-byte aligned");
+      HE_TRY(launch_dense_elementwise(EW_MUL_RELU, core.ab_format == 1 ? HE_BF16 : HE_F16, ew_in, a_prime,
+                                      (unsigned long long)core.batch * core.M * core.K, 0.0f, ctx_sm_count(ctx), stream));
+      a_ptr = a_prime;
+      cfg.ml = ML_NONE;
+      extra_launches = 1;
+    }
+    HE_TRY(make_operand_tmap(&ta, a_ptr, core.ab_format, cfg.a_mn, core.M, core.K, core.batch, kBM));
     HE_TRY(make_operand_tmap(&tb, inputs[b_slot], core.ab_format, cfg.b_mn, core.N, core.K, core.batch, cfg.two_cta ? 128 : cfg.bn));
-    if (mask_slot >= 0) HE_TRY(make_operand_tmap(&tm, inputs[mask_slot], core.ab_format, cfg.a_mn, core.M, core.K, core.batch, kBM));
+    if (mask_slot >= 0 && !materialise_a) HE_TRY(make_operand_tmap(&tm, inputs[mask_slot], core.ab_format, cfg.a_mn, core.M, core.K, core.batch, kBM));
     GemmCore c = core;
     c.status = ctx ? ctx->d_status : nullptr;
     if (kind == EpiKind::Flex) {
@@ -417,7 +439,7 @@ struct MatmulPlan : he_plan {
       p.epi.vec_ok = vec ? 1 : 0;
       p.epi.bias_vec = (c.N % 8 == 0 && (uintptr_t)p.epi.bias % 16 == 0) ? 1 : 0;
       HE_TRY(launch_gemm_flex(cfg, p, stream));
-      last_launches = 1;
+      last_launches = 1 + extra_launches;
       if (flex.colsum_src != 0) {
         HE_TRY(launch_colsum_finalize(ws + ws_col_off[0], (float*)outputs[f_colsum], c.batch, c.tiles_m, c.N, stream));
         ++last_launches;
@@ -449,7 +471,7 @@ struct MatmulPlan : he_plan {
       HE_TRY(launch_colsum_finalize(ws + ws_col_off[0], (float*)outputs[r3.db2], c.batch, c.tiles_m, c.N, stream));
       HE_TRY(launch_colsum_finalize(ws + ws_col_off[1], (float*)outputs[r3.db1], c.batch, c.tiles_m, c.N, stream));
       HE_TRY(launch_scalar_finalize(ws + ws_scalar_off, (float*)outputs[r3.loss], c.num_tiles, stream));
-      last_launches = 4;
+      last_launches = 4 + extra_launches;
       return HE_OK;
     }
     GemmParams<EpiProgramParams> p;
@@ -459,7 +481,7 @@ struct MatmulPlan : he_plan {
     for (int i = 0; i < n_inputs; ++i) p.epi.prog.in[i] = inputs[i];
     for (int i = 0; i < n_outputs; ++i) p.epi.prog.out[i] = outputs[i];
     HE_TRY(launch_gemm_program(cfg, p, stream));
-    last_launches = 1;
+    last_launches = 1 + extra_launches;
     return HE_OK;
   }
 };
@@ -586,6 +608,23 @@ int32_t plan_fused_matmul(he_ctx* ctx, const Graph& g, he_plan** out, int* tier_
     }
     if (const char* gm = getenv("HE_GEMM_GROUP_M")) c.group_m = std::max(1, atoi(gm));
   };
+  // Decide how a mainloop fusion is executed (after the epilogue's own workspace is laid out).
+  // Cost model from measurements on B200: the in-kernel rewrite runs the mainloop at about half the
+  // plain rate (1316 -> 680-770 TFLOP/s at 4096^3), i.e. it adds ~0.7 x the plain GEMM time; the
+  // pre-pass reads A and the mask and writes A' once at ~4.5 TB/s plus a launch.
+  auto choose_mainloop = [&]() -> std::string {
+    if (plan->cfg.ml == ML_NONE) return "";
+    const double gemm_us = 2.0 * c.batch * c.M * (double)c.N * c.K / 1.3e9;
+    const double bytes = 3.0 * c.batch * c.M * (double)c.K * 2.0;
+    const double prepass_us = bytes / 4.5e6 + 5.0;
+    bool mat = 0.7 * gemm_us > prepass_us;
+    if (const char* e = getenv("HE_GEMM_MAINLOOP")) mat = e[0] == 'm' ? true : e[0] == 'f' ? false : mat;   // "materialise" / "fused"
+    if (!mat) return ", mainloop rewrite in shared memory";
+    plan->materialise_a = true;
+    plan->ws_aprime_off = (plan->workspace_bytes + 255) / 256 * 256;
+    plan->workspace_bytes = plan->ws_aprime_off + (size_t)c.batch * c.M * c.K * 2;
+    return ", mainloop operand materialised by a pre-pass";
+  };
   auto out_dt = [&](int out_idx) { return g.nodes[g.outputs[out_idx]].dtype; };
   auto in_dt = [&](int slot) { return g.nodes[g.inputs[slot]].dtype; };
   char desc[320];
@@ -634,7 +673,7 @@ int32_t plan_fused_matmul(he_ctx* ctx, const Graph& g, he_plan** out, int* tier_
              "fused matmul tier 2: tcgen05 %sx%dx64, %s-major A, %s-major B, mainloop %d, epilogue flex(bias=%d resid=%d act=%d gate=%d z=%d colsum=%d), grid %d",
              plan->cfg.two_cta ? "2-CTA 256" : "128", plan->cfg.bn, plan->cfg.a_mn ? "M" : "K", plan->cfg.b_mn ? "N" : "K", plan->cfg.ml, plan->f_bias >= 0, plan->f_resid >= 0,
              f.act, f.gate, plan->f_z >= 0, f.colsum_src, plan->cfg.grid);
-    plan->description = desc;
+    plan->description = std::string(desc) + choose_mainloop();
     *out = guard.release();
     return HE_OK;
   }
@@ -688,7 +727,7 @@ int32_t plan_fused_matmul(he_ctx* ctx, const Graph& g, he_plan** out, int* tier_
       snprintf(desc, sizeof desc,
                "fused matmul tier 2: tcgen05 %sx256x64, %s-major A, %s-major B, mainloop %d, epilogue README graph (loss + 2 column sums + 2 tiles%s), grid %d",
                plan->cfg.two_cta ? "2-CTA 256" : "128", plan->cfg.a_mn ? "M" : "K", plan->cfg.b_mn ? "N" : "K", plan->cfg.ml, with_e ? ", E1/E2" : "", plan->cfg.grid);
-      plan->description = desc;
+      plan->description = std::string(desc) + choose_mainloop();
       *out = guard.release();
       return HE_OK;
     }
@@ -710,7 +749,7 @@ int32_t plan_fused_matmul(he_ctx* ctx, const Graph& g, he_plan** out, int* tier_
     snprintf(desc, sizeof desc,
              "fused matmul tier 1: tcgen05 %sx256x64, %s-major A, %s-major B, mainloop %d, interpreted epilogue (%d instr), grid %d",
              plan->cfg.two_cta ? "2-CTA 256" : "128", plan->cfg.a_mn ? "M" : "K", plan->cfg.b_mn ? "N" : "K", plan->cfg.ml, plan->prog.prog.n_instr, plan->cfg.grid);
-    plan->description = desc;
+    plan->description = std::string(desc) + choose_mainloop();
     *out = guard.release();
     return HE_OK;
   }

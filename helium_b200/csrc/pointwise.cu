@@ -15,6 +15,7 @@
 // folds them in index order (the reference's float atomics are order-dependent).
 #include "permute.cuh"
 #include "pointwise_interp.cuh"
+#include "pointwise_dense.cuh"
 
 #include <algorithm>
 
@@ -118,6 +119,12 @@ namespace {
 
 struct PointwisePlan : he_plan {
   PwCompiled c;
+  // dense elementwise tier-2 kernel (when the program is in its catalogue); ew_slot[k] = caller input
+  // slot of canonical input k.  The interpreter program stays as the fallback for pointers or sizes
+  // off the 16-byte rules.
+  EwMatch ew;
+  int ew_slot[3] = {-1, -1, -1};
+  int ew_dtype = HE_F32;
   bool reduce = false;
   PwReduceLaunch rl{};
   int n_inputs = 0, n_outputs = 0;
@@ -132,6 +139,20 @@ struct PointwisePlan : he_plan {
     for (int i = 0; i < n_outputs; ++i) {
       if (!outputs || !outputs[i]) HE_FAIL(HE_ERR_INVALID, "pointwise launch: output %d is null", i);
       P.out[i] = outputs[i];
+    }
+    if (!reduce && ew.kind >= 0) {
+      const unsigned ve = ew_dtype == HE_F32 ? 4 : 8;
+      const void* in[3] = {nullptr, nullptr, nullptr};
+      bool ok = P.n_elems % ve == 0 && (reinterpret_cast<uintptr_t>(outputs[0]) & 15) == 0;
+      for (int k = 0; k < ew.n_in; ++k) {
+        in[k] = inputs[ew_slot[k]];
+        ok = ok && (reinterpret_cast<uintptr_t>(in[k]) & 15) == 0;
+      }
+      if (ok) {
+        HE_TRY(launch_dense_elementwise(ew.kind, ew_dtype, in, outputs[0], P.n_elems, ew.k, ctx_sm_count(ctx), stream));
+        last_launches = 1;
+        return HE_OK;
+      }
     }
     if (!reduce) {
       if (c.has_bool_io) {
@@ -358,8 +379,33 @@ int32_t plan_pointwise(he_ctx* ctx, const Graph& g, he_plan** out, int* tier_onl
       set_error("%s", saved.c_str());
     }
   }
+  // tier 2, dense elementwise: one output, every load a dense identity load, one dtype throughout
+  {
+    const PwProgram& P0 = plan->c.prog;
+    bool dense = P0.n_outputs == 1 && P0.n_reductions == 0 && !plan->c.has_bool_io && !plan->c.loads.empty() &&
+                 plan->c.loads.size() <= 3 && g.inputs.size() == plan->c.loads.size();
+    const int dt = g.nodes[g.outputs[0]].dtype;
+    dense = dense && (dt == HE_F32 || dt == HE_BF16 || dt == HE_F16);
+    for (const PwLoadInfo& li : plan->c.loads)
+      dense = dense && li.identity && g.nodes[li.node].dtype == dt && num_elements(g.nodes[li.node]) == (int64_t)P0.n_elems;
+    if (dense) {
+      PwCompileOptions opt;
+      opt.fuse_fma = false;
+      PwCompiled plain;
+      PwCanon canon;
+      std::string saved = he_last_error_string();
+      if (compile_pointwise(g, opt, &plain) == HE_OK && canonicalize_program(g, plain, -1, -1, &canon) == HE_OK &&
+          match_dense_elementwise(canon.text, &plan->ew) && (int)canon.slot_order.size() == plan->ew.n_in) {
+        for (int k = 0; k < plan->ew.n_in; ++k) plan->ew_slot[k] = canon.slot_order[k];
+        plan->ew_dtype = dt;
+      } else {
+        plan->ew.kind = -1;
+        set_error("%s", saved.c_str());
+      }
+    }
+  }
   if (tier_only) {
-    *tier_only = 1;
+    *tier_only = plan->ew.kind >= 0 ? 2 : 1;
     delete plan;
     return HE_OK;
   }
@@ -405,6 +451,9 @@ int32_t plan_pointwise(he_ctx* ctx, const Graph& g, he_plan** out, int* tier_onl
     }
     snprintf(desc, sizeof desc, "pointwise tier 1 (interpreter, %d instr, %d regs), reduce: %u groups of %u, %s, %u CTAs/group",
              P.n_instr, plan->c.n_regs, L.num_groups, P.group_size, L.warp_mode ? "warp per group" : "CTA slices", L.blocks_per_group);
+  } else if (plan->ew.kind >= 0) {
+    snprintf(desc, sizeof desc, "pointwise tier 2 (dense elementwise kernel %s, 16-byte vectors; interpreter fallback for unaligned tensors)",
+             plan->ew.name);
   } else {
     snprintf(desc, sizeof desc, "pointwise tier 1 (interpreter, %d instr, %d regs, %d elems/thread)", P.n_instr,
              plan->c.n_regs, plan->c.has_bool_io ? 1 : 4);

@@ -1,0 +1,192 @@
+// Tier-2 pointwise kernels for dense, same-shape, same-dtype elementwise programs.
+//
+// The interpreter tier spends ~100 machine instructions per program instruction per 8 elements,
+// which caps it at 1.8 (bf16) to 3.8 (f32) TB/s.  The short programs that dominate helium graphs
+// once matmul epilogues are fused away -- relu, add, mul, relu(a) * m, relu(a + b), a * b + c, the
+// SGD update w - lr * g (helium/src/optimizer/sgd.rs:48), gelu -- are compiled here as straight-line
+// functors instead: 16-byte loads, two vectors per tensor in flight per thread, f32 arithmetic, one
+// rounding at the store, exactly the operation order the interpreter uses (separately rounded mul
+// and add unless the program's mul feeds only an add, which both tiers contract to one fma like
+// the reference's NVRTC build does).
+//
+// A program qualifies when every load is a full-tensor identity load (canonical form `I<n>:F`), all
+// tensors share one dtype of {bf16, f16, f32}, and its canonical text is in the table below.
+#include "pointwise_dense.cuh"
+
+#include <cstring>
+
+namespace he {
+namespace {
+
+constexpr int kEwThreads = 256;
+constexpr int kEwUnroll = 2;   // 16-byte vectors per tensor per thread per iteration
+
+struct EwParams {
+  const void* in[3];
+  void* out;
+  unsigned long long n_vec;   // 16-byte vectors per tensor
+  float k;                    // the program's constant, when it has one
+};
+
+template <typename T> struct EwVec;
+template <> struct EwVec<float> {
+  static constexpr int kElems = 4;
+  __device__ static void unpack(const uint4& q, float* o) {
+    o[0] = __uint_as_float(q.x); o[1] = __uint_as_float(q.y); o[2] = __uint_as_float(q.z); o[3] = __uint_as_float(q.w);
+  }
+  __device__ static uint4 pack(const float* v) {
+    return make_uint4(__float_as_uint(v[0]), __float_as_uint(v[1]), __float_as_uint(v[2]), __float_as_uint(v[3]));
+  }
+};
+template <> struct EwVec<__nv_bfloat16> {
+  static constexpr int kElems = 8;
+  __device__ static void unpack(const uint4& q, float* o) {
+    const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) { o[2 * j] = __uint_as_float(w[j] << 16); o[2 * j + 1] = __uint_as_float(w[j] & 0xffff0000u); }
+  }
+  __device__ static uint4 pack(const float* v) {
+    return make_uint4(f32x2_to_bf16x2(v[0], v[1]), f32x2_to_bf16x2(v[2], v[3]), f32x2_to_bf16x2(v[4], v[5]), f32x2_to_bf16x2(v[6], v[7]));
+  }
+};
+template <> struct EwVec<__half> {
+  static constexpr int kElems = 8;
+  __device__ static void unpack(const uint4& q, float* o) {
+    const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) { o[2 * j] = f16_bits_to_f32(w[j] & 0xffffu); o[2 * j + 1] = f16_bits_to_f32(w[j] >> 16); }
+  }
+  __device__ static uint4 pack(const float* v) {
+    uint32_t w[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) w[j] = f32_to_f16_bits(v[2 * j]) | (f32_to_f16_bits(v[2 * j + 1]) << 16);
+    return make_uint4(w[0], w[1], w[2], w[3]);
+  }
+};
+
+// Functors: NIN inputs -> one value.  __fmul_rn / __fadd_rn keep separately rounded operations
+// separate (the compiler would otherwise contract them, the interpreter cannot).
+struct FRelu { static constexpr int kIn = 1; __device__ static float f(float a, float, float, float) { return fmaxf(a, 0.0f); } };
+struct FGelu {
+  static constexpr int kIn = 1;
+  __device__ static float f(float a, float, float, float) { return 0.5f * a * (1.0f + erff(a * 0.70710678118654752440f)); }
+};
+struct FAdd { static constexpr int kIn = 2; __device__ static float f(float a, float b, float, float) { return __fadd_rn(a, b); } };
+struct FMul { static constexpr int kIn = 2; __device__ static float f(float a, float b, float, float) { return __fmul_rn(a, b); } };
+struct FAddRelu { static constexpr int kIn = 2; __device__ static float f(float a, float b, float, float) { return fmaxf(__fadd_rn(a, b), 0.0f); } };
+// canonical `prod(I0, relu(I1))`
+struct FMulRelu { static constexpr int kIn = 2; __device__ static float f(float a, float b, float, float) { return __fmul_rn(a, fmaxf(b, 0.0f)); } };
+// canonical `sum(I0, prod(I1, I2))`: the mul feeds only the add, so it is one fma in both tiers
+struct FFma { static constexpr int kIn = 3; __device__ static float f(float a, float b, float c, float) { return fmaf(b, c, a); } };
+// canonical `sum(I0, neg(prod(I1, K)))`: mul, neg, add are three separately rounded steps
+struct FAxmy { static constexpr int kIn = 2; __device__ static float f(float a, float b, float, float k) { return __fadd_rn(a, -__fmul_rn(b, k)); } };
+
+template <class F, typename T>
+__global__ void __launch_bounds__(kEwThreads) ew_dense_kernel(const __grid_constant__ EwParams p) {
+  using V = EwVec<T>;
+  const unsigned long long stride = (unsigned long long)gridDim.x * kEwThreads * kEwUnroll;
+  for (unsigned long long base = (unsigned long long)blockIdx.x * kEwThreads * kEwUnroll + threadIdx.x; base < p.n_vec; base += stride) {
+    uint4 q[3][kEwUnroll];
+#pragma unroll
+    for (int u = 0; u < kEwUnroll; ++u) {
+      const unsigned long long i = base + (unsigned long long)u * kEwThreads;
+      if (i < p.n_vec) {
+#pragma unroll
+        for (int t = 0; t < F::kIn; ++t) q[t][u] = __ldcs(reinterpret_cast<const uint4*>(p.in[t]) + i);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < kEwUnroll; ++u) {
+      const unsigned long long i = base + (unsigned long long)u * kEwThreads;
+      if (i >= p.n_vec) break;
+      float a[V::kElems], b[V::kElems], c[V::kElems], r[V::kElems];
+      V::unpack(q[0][u], a);
+      if (F::kIn > 1) V::unpack(q[1][u], b);
+      if (F::kIn > 2) V::unpack(q[2][u], c);
+#pragma unroll
+      for (int e = 0; e < V::kElems; ++e) r[e] = F::f(a[e], F::kIn > 1 ? b[e] : 0.0f, F::kIn > 2 ? c[e] : 0.0f, p.k);
+      __stcs(reinterpret_cast<uint4*>(p.out) + i, V::pack(r));
+    }
+  }
+}
+
+template <class F>
+int32_t launch_for_dtype(int dt, const EwParams& p, unsigned grid, cudaStream_t stream) {
+  if (dt == HE_F32) ew_dense_kernel<F, float><<<grid, kEwThreads, 0, stream>>>(p);
+  else if (dt == HE_BF16) ew_dense_kernel<F, __nv_bfloat16><<<grid, kEwThreads, 0, stream>>>(p);
+  else ew_dense_kernel<F, __half><<<grid, kEwThreads, 0, stream>>>(p);
+  HE_CUDA(cudaGetLastError());
+  return HE_OK;
+}
+
+struct Entry {
+  const char* text;   // canonical text with the constant blanked to K*
+  int kind;
+  int n_in;
+  const char* name;
+};
+const Entry kTable[] = {
+    {"store(u8(I0:F));", EW_RELU, 1, "relu(a)"},
+    {"store(u16(I0:F));", EW_GELU, 1, "gelu(a)"},
+    {"store(sum(I0:F,I1:F));", EW_ADD, 2, "a + b"},
+    {"store(prod(I0:F,I1:F));", EW_MUL, 2, "a * b"},
+    {"store(u8(sum(I0:F,I1:F)));", EW_ADD_RELU, 2, "relu(a + b)"},
+    {"store(prod(I0:F,u8(I1:F)));", EW_MUL_RELU, 2, "a * relu(b)"},
+    {"store(sum(I0:F,prod(I1:F,I2:F)));", EW_FMA, 3, "a + b * c"},
+    {"store(sum(I0:F,u1(prod(I1:F,K*))));", EW_AXMY, 2, "a - k * b"},
+};
+
+}  // namespace
+
+bool match_dense_elementwise(const std::string& canon_text, EwMatch* m) {
+  // blank the (single) constant, remembering its bits
+  std::string t = canon_text;
+  uint32_t kbits = 0;
+  int n_const = 0;
+  for (size_t i = 0; i + 9 <= t.size(); ++i) {
+    if (t[i] != 'K') continue;
+    bool hex = true;
+    for (int j = 1; j <= 8; ++j) hex = hex && isxdigit((unsigned char)t[i + j]);
+    if (!hex) continue;
+    kbits = (uint32_t)strtoul(t.substr(i + 1, 8).c_str(), nullptr, 16);
+    t.replace(i + 1, 8, "*");
+    ++n_const;
+  }
+  if (n_const > 1) return false;
+  for (const Entry& e : kTable)
+    if (t == e.text) {
+      m->kind = e.kind;
+      m->n_in = e.n_in;
+      m->name = e.name;
+      memcpy(&m->k, &kbits, 4);
+      return true;
+    }
+  return false;
+}
+
+int32_t launch_dense_elementwise(int kind, int dtype, const void* const* in, void* out, unsigned long long n_elems, float k,
+                                 int sm_count, cudaStream_t stream) {
+  const int ve = dtype == HE_F32 ? 4 : 8;
+  EwParams p{};
+  for (int t = 0; t < 3; ++t) p.in[t] = in[t];
+  p.out = out;
+  p.n_vec = n_elems / ve;
+  p.k = k;
+  const unsigned long long per_cta = (unsigned long long)kEwThreads * kEwUnroll;
+  // enough CTAs for every vector, capped at 32 per SM's worth (the loop strides over the rest)
+  const unsigned grid = (unsigned)std::max<unsigned long long>(1, std::min<unsigned long long>((p.n_vec + per_cta - 1) / per_cta,
+                                                                                             (unsigned long long)sm_count * 32));
+  switch (kind) {
+    case EW_RELU: return launch_for_dtype<FRelu>(dtype, p, grid, stream);
+    case EW_GELU: return launch_for_dtype<FGelu>(dtype, p, grid, stream);
+    case EW_ADD: return launch_for_dtype<FAdd>(dtype, p, grid, stream);
+    case EW_MUL: return launch_for_dtype<FMul>(dtype, p, grid, stream);
+    case EW_ADD_RELU: return launch_for_dtype<FAddRelu>(dtype, p, grid, stream);
+    case EW_MUL_RELU: return launch_for_dtype<FMulRelu>(dtype, p, grid, stream);
+    case EW_FMA: return launch_for_dtype<FFma>(dtype, p, grid, stream);
+    case EW_AXMY: return launch_for_dtype<FAxmy>(dtype, p, grid, stream);
+    default: HE_FAIL(HE_ERR_INVALID, "dense elementwise: unknown kernel %d", kind);
+  }
+}
+
+}  // namespace he

@@ -1,0 +1,28 @@
+// Dense elementwise tier-2 kernels (pointwise_dense.cu): catalogue lookup and launch.
+#pragma once
+#include <string>
+
+#include "device_utils.cuh"
+#include "he_internal.h"
+
+namespace he {
+
+enum EwKind : int { EW_RELU = 0, EW_GELU, EW_ADD, EW_MUL, EW_ADD_RELU, EW_MUL_RELU, EW_FMA, EW_AXMY };
+
+struct EwMatch {
+  int kind = -1;
+  int n_in = 0;
+  float k = 0.0f;          // the program's constant (EW_AXMY)
+  const char* name = "";
+};
+
+// True when `canon_text` (canonicalize_program of a program compiled without FMA fusion) is one of
+// the catalogued dense programs.  The caller still has to check that every tensor is dense, of one
+// dtype, 16-byte aligned and a whole number of 16-byte vectors long.
+bool match_dense_elementwise(const std::string& canon_text, EwMatch* m);
+
+// in[0..n_in) follow the canonical input order (PwCanon::slot_order).
+int32_t launch_dense_elementwise(int kind, int dtype, const void* const* in, void* out, unsigned long long n_elems, float k,
+                                 int sm_count, cudaStream_t stream);
+
+}  // namespace he

@@ -217,3 +217,23 @@ def test_mlp_block_plans_at_full_size():
     assert "K-major B" in hb.Plan.fused_matmul(None, graphs["dZ"]).description
     assert "M-major A" in hb.Plan.fused_matmul(None, graphs["dW1"]).description
     assert flops_per_token(4096, 16384) * 8192 == 6 * 2 * 8192 * 4096 * 16384
+
+
+def test_dense_elementwise_programs_are_tier_2():
+    """Short dense programs hit the hand-written elementwise kernels; anything else stays on the interpreter."""
+    import helium_b200 as hb
+    def tier(build, dts, shape=(64, 128)):
+        g = ir.Graph()
+        ins = [g.new_input(list(shape), d) for d in dts]
+        g.new_output(build(g, ins))
+        return hb.plan_supported(g, 0)
+    assert tier(lambda g, i: g.unary(ir.UN_RELU, i[0]), [ir.BF16]) == 2
+    assert tier(lambda g, i: g.binary(ir.BIN_MUL, g.unary(ir.UN_RELU, i[0]), i[1]), [ir.BF16, ir.BF16]) == 2
+    assert tier(lambda g, i: g.binary(ir.BIN_ADD, i[0], g.unary(ir.UN_NEG, g.binary(ir.BIN_MUL, i[1], g.constant(0.01, [64, 128])))), [ir.F32, ir.F32]) == 2
+    # mixed dtypes, a broadcast operand, or an op outside the catalogue: interpreter tier
+    assert tier(lambda g, i: g.binary(ir.BIN_ADD, i[0], i[1]), [ir.BF16, ir.F32]) == 1
+    assert tier(lambda g, i: g.unary(ir.UN_EXP, i[0]), [ir.F32]) == 1
+    g = ir.Graph()
+    x = g.new_input([64, 128], ir.F32); b = g.new_input([128], ir.F32)
+    g.new_output(g.binary(ir.BIN_ADD, x, g.broadcast_to(b, [64, 128])))
+    assert hb.plan_supported(g, 0) == 1
