@@ -598,11 +598,27 @@ int32_t plan_fused_matmul(he_ctx* ctx, const Graph& g, he_plan** out, int* tier_
     if (plan->cfg.two_cta) {
       const int tiles_m2 = (c.M + 255) / 256;
       c.tiles_m = 2 * tiles_m2;                       // partial-sum rows: the odd CTA of the last pair may be empty
-      c.num_tiles = c.tiles_m * c.tiles_n * c.batch;  // one scalar partial per CTA tile
-      plan->cfg.grid = 2 * std::max(1, std::min(tiles_m2 * c.tiles_n * c.batch, ctx_sm_count(ctx) / 2));
+      const int pair_tiles = tiles_m2 * c.tiles_n * c.batch;
+      const int pairs = std::max(1, std::min(pair_tiles, ctx_sm_count(ctx) / 2));
+      plan->cfg.grid = 2 * pairs;
+      // Tail balancing: when the last round of the static schedule would leave more than half of
+      // the pairs idle, its tiles are issued as two half-width tiles each (the tile list grows by
+      // `rest` entries and the last round keeps 2 * rest pairs busy for about half a tile time).
+      const int rest = pair_tiles % pairs;
+      const char* no_split = getenv("HE_GEMM_NO_SPLIT");
+      if (pair_tiles > pairs && rest > 0 && 2 * rest <= pairs && !(no_split && no_split[0] == '1')) {
+        c.split_from = pair_tiles - rest;
+        c.split_count = rest;
+      } else {
+        c.split_from = pair_tiles;
+        c.split_count = 0;
+      }
+      c.num_tiles = 2 * (pair_tiles + c.split_count);  // one scalar partial per CTA tile of the list
       c.group_m = 8;    // 2048 rows of A per group
     } else {
       c.group_m = 16;
+      c.split_from = 0;
+      c.split_count = 0;
       c.num_tiles = c.tiles_m * c.tiles_n * c.batch;
       plan->cfg.grid = std::max(1, std::min(c.num_tiles, ctx_sm_count(ctx)));
     }

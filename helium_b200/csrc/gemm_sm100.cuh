@@ -34,12 +34,16 @@ struct GemmCore {
   int tiles_m, tiles_n, num_tiles, k_blocks;
   int ab_format;  // 0 = f16, 1 = bf16
   int group_m;    // tile rasterisation: row tiles per group (see decode_tile)
+  // Pair-tile kernel only: tiles [split_from, split_from + split_count) of the tile list are walked
+  // as two half-width tiles each, by different CTA pairs (see finish_tiles in gemm_plan.cu).
+  int split_from, split_count;
   int debug;      // timing experiments only (HE_GEMM_DEBUG): bit 0 skips the mainloop rewrite, bit 1 its proxy fence
   DeviceStatus* status;
 };
 
 struct TileInfo {
   int m0, n0, b, tile_m, tile_n, tile_idx;
+  int bn;   // columns of this tile (the kernel's BN, or half of it for the split tiles of the last round)
 };
 
 // ---- row-segment load / store helpers (one thread owns CH consecutive columns of one row) -------
@@ -159,7 +163,7 @@ struct EpiEnv {
 __device__ __forceinline__ void col_partials_flush(const EpiEnv& env, const TileInfo& t, int nred, float* const* partials) {
   ptx::named_barrier_sync(1, env.n_epi_threads);
   const GemmCore& c = *env.core;
-  for (int col = env.epi_tid; col < env.bn; col += env.n_epi_threads) {
+  for (int col = env.epi_tid; col < t.bn; col += env.n_epi_threads) {
     const int gc = t.n0 + col;
     if (gc < c.N) {
       for (int r = 0; r < nred; ++r) {
@@ -548,6 +552,7 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmParams<typename Epi::Params> p) 
     t.tile_m = first_m + (w - t.tile_n * gm);
     t.m0 = t.tile_m * kBM;
     t.n0 = t.tile_n * BN;
+    t.bn = BN;
     return t;
   };
 

@@ -114,7 +114,10 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ GemmParams<typename Epi::Params
   const bool leader = rank == 0;
   const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
   const int tiles_m2 = (c.M + 255) / 256;
-  const int pair_tiles = tiles_m2 * c.tiles_n * c.batch;
+  // The tile list: every 256 x 256 pair tile once, except that the last `split_count` of them
+  // appear as two 256 x 128 halves.  With 256 tiles on 74 pairs the fourth round would keep 34 pairs
+  // busy and 40 idle; as 68 half tiles it keeps 68 busy for about half as long.
+  const int pair_tiles = tiles_m2 * c.tiles_n * c.batch + c.split_count;
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
@@ -146,8 +149,14 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ GemmParams<typename Epi::Params
   const uint32_t tmem_base = *tmem_holder;
 
   // pair tile -> (batch, m2, n); this CTA's rows start at m2 * 256 + rank * 128
-  auto decode_tile = [&](int tile) {
+  auto decode_tile = [&](int list_idx) {
     TileInfo t;
+    int tile = list_idx, half = -1;
+    if (list_idx >= c.split_from && c.split_count > 0) {
+      const int h = list_idx - c.split_from;
+      tile = c.split_from + (h >> 1);
+      half = h & 1;
+    }
     const int per_batch = tiles_m2 * c.tiles_n;
     t.b = tile / per_batch;
     const int r = tile - t.b * per_batch;
@@ -160,8 +169,9 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ GemmParams<typename Epi::Params
     const int m2 = first_m + (w - t.tile_n * gm);
     t.tile_m = m2 * 2 + (int)rank;
     t.m0 = t.tile_m * kBM;
-    t.n0 = t.tile_n * BN;
-    t.tile_idx = tile * 2 + (int)rank;
+    t.n0 = t.tile_n * BN + (half > 0 ? BN / 2 : 0);
+    t.bn = half >= 0 ? BN / 2 : BN;
+    t.tile_idx = list_idx * 2 + (int)rank;
     return t;
   };
 
@@ -180,7 +190,10 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ GemmParams<typename Epi::Params
         for (int kb = 0; kb < c.k_blocks; ++kb) {
           if (!ptx::mbar_wait(bar_empty(stage), phase ^ 1u, abort_flag, c.status, 1, stage)) { alive = false; break; }
           const uint32_t leader_full = ptx::mapa(bar_full_b(stage), 0);
-          if (leader) ptx::mbar_arrive_expect_tx(bar_full_b(stage), kLeaderBytes);
+          // a half-width tile needs 64 columns of B per CTA: with N-major B that is one of the two
+          // 64-column boxes; with K-major B the full 128-row box is fetched and half of it ignored
+          const bool half_b = t.bn < BN && B_MN;
+          if (leader) ptx::mbar_arrive_expect_tx(bar_full_b(stage), kLeaderBytes - (half_b ? kBHalfBytes : 0));
           if (kFused) ptx::mbar_arrive_expect_tx(bar_full_a(stage), kABytes);
           const int k0 = kb * kBK;
           const uint32_t a_dst = smem_base + SM::off_a + stage * kATileBytes;
@@ -211,10 +224,10 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ GemmParams<typename Epi::Params
             }
           }
           // B: this CTA's 128 columns of the 256-wide tile
-          const int nb0 = t.n0 + 128 * (int)rank;
+          const int nb0 = t.n0 + (t.bn / 2) * (int)rank;
           if (B_MN) {
-#pragma unroll
-            for (int j = 0; j < 2; ++j) ptx::tma_load_3d_2cta(b_dst + j * (kBK * 128), &p.tma_b, leader_full, nb0 + 64 * j, k0, t.b);
+            ptx::tma_load_3d_2cta(b_dst, &p.tma_b, leader_full, nb0, k0, t.b);
+            if (!half_b) ptx::tma_load_3d_2cta(b_dst + kBK * 128, &p.tma_b, leader_full, nb0 + 64, k0, t.b);
           } else {
             ptx::tma_load_3d_2cta(b_dst, &p.tma_b, leader_full, k0, nb0, t.b);
           }
@@ -225,7 +238,8 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ GemmParams<typename Epi::Params
   } else if (warp == 1) {
     // ===================== MMA issuer (leader CTA only) =====================
     if (lane == 0 && leader) {
-      const uint32_t idesc = ptx::make_idesc_f16(c.ab_format, A_MN ? 1 : 0, B_MN ? 1 : 0, 256, BN);
+      const uint32_t idesc_full = ptx::make_idesc_f16(c.ab_format, A_MN ? 1 : 0, B_MN ? 1 : 0, 256, BN);
+      const uint32_t idesc_half = ptx::make_idesc_f16(c.ab_format, A_MN ? 1 : 0, B_MN ? 1 : 0, 256, BN / 2);
       constexpr uint32_t a_lbo = A_MN ? kBK * 128 : 16, b_lbo = B_MN ? kBK * 128 : 16;
       constexpr uint32_t a_kadv = A_MN ? 2048 : 32, b_kadv = B_MN ? 2048 : 32;
       int stage = 0;
@@ -238,6 +252,7 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ GemmParams<typename Epi::Params
         if (!ptx::mbar_wait(bar_tmem_empty(acc), acc_phase ^ 1u, abort_flag, c.status, 2, acc)) { alive = false; break; }
         ptx::tcgen05_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
+        const uint32_t idesc = (c.split_count > 0 && tile >= c.split_from) ? idesc_half : idesc_full;
         for (int kb = 0; kb < c.k_blocks; ++kb) {
           if (!ptx::mbar_wait(bar_full_b(stage), phase, abort_flag, c.status, 3, stage)) { alive = false; break; }
           if (kFused && !ptx::mbar_wait(bar_xform(stage), phase, abort_flag, c.status, 6, stage)) { alive = false; break; }
@@ -271,14 +286,14 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ GemmParams<typename Epi::Params
     env.epi_warp = warp - 2;
     env.epi_tid = env.epi_warp * 32 + lane;
     env.quadrant = warp & 3;
-    constexpr int kColsPerWarp = BN / (NE_WARPS / 4);
-    const int col_begin = (env.epi_warp / 4) * kColsPerWarp;
     int it = 0;
     bool dead = false;
     for (int tile = pair; tile < pair_tiles; tile += n_pairs, ++it) {
       const int acc = it & 1;
       const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
       const TileInfo t = decode_tile(tile);
+      const int kColsPerWarp = t.bn / (NE_WARPS / 4);
+      const int col_begin = (env.epi_warp / 4) * kColsPerWarp;
       if (!dead && !ptx::mbar_wait(bar_tmem_full(acc), acc_phase, abort_flag, c.status, 4, acc)) dead = true;
       dead = __any_sync(0xffffffffu, dead);   // the warp decides together (it shares a __syncwarp below)
       typename Epi::State st;

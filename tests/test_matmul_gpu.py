@@ -247,3 +247,20 @@ def test_mlp_block_full_size_sampled(ctx):
     assert O.rel_l2(db2, dec(dO).sum(0)) <= 1e-5
     db1 = blk.db1.cpu().numpy().reshape(-1).astype(np.float64)
     assert O.rel_l2(db1, dec(dev["dZ"]).sum(0)) <= 2e-3
+
+
+@pytest.mark.parametrize("kw", [
+    dict(bias=False),                                              # N-major B: half tiles load one 64-column box
+    dict(bias=False, b_t=True),                                    # K-major B: half tiles use half of the 128-row box
+    dict(bias=True, act=ir.UN_RELU, resid=True, colsum="resid"),   # column sums across full and half tiles
+    dict(bias=False, a_t=True, b_t=True, out_dtype=ir.F32),
+])
+def test_tail_split_tiles(ctx, kw):
+    """256 pair tiles on 74 SM pairs: the last 34 tiles run as 68 half-width tiles.  Every output
+    element and every column sum must come out as if the tiles were whole."""
+    m, n, k = 4096, 4096, 192
+    g = graph_linear(m, n, k, **kw)
+    ins = _gen(g, 41, {1: 1.0 / np.sqrt(k)})
+    got, plan = _run(ctx, g, ins)
+    assert "2-CTA" in plan.description
+    _compare(g, got, O.evaluate(g, ins), plan.description)
