@@ -373,8 +373,11 @@ struct MatmulPlan : he_plan {
   // C3
   EpiC3Params c3{};
   C3Roles r3;
-  // Program
+  // Program (interpreted epilogue) and its reductions: kind 0 columns, 1 rows, 2 scalar
   PwCompiled prog;
+  int pr_n_red = 0, pr_kind[4] = {0, 0, 0, 0}, pr_out[4] = {-1, -1, -1, -1}, pr_fold_batch[4] = {0, 0, 0, 0};
+  size_t pr_off[4] = {0, 0, 0, 0};   // workspace offsets in floats
+  int pr_n_col = 0, pr_col_slot[2] = {0, 0}, pr_row_slots = 0;
   int n_inputs = 0, n_outputs = 0;
   // Sgemm
   int s_bias = -1, s_act = 0, s_in_dt = HE_F32, s_out_dt = HE_F32, s_bias_dt = HE_F32;
@@ -480,8 +483,30 @@ struct MatmulPlan : he_plan {
     p.epi.prog = prog.prog;
     for (int i = 0; i < n_inputs; ++i) p.epi.prog.in[i] = inputs[i];
     for (int i = 0; i < n_outputs; ++i) p.epi.prog.out[i] = outputs[i];
+    p.epi.n_red = pr_n_red;
+    p.epi.n_col = pr_n_col;
+    p.epi.col_slot[0] = pr_col_slot[0];
+    p.epi.col_slot[1] = pr_col_slot[1];
+    p.epi.rows_total = c.batch * c.M;
+    for (int s = 0; s < 4; ++s) {
+      p.epi.red_kind[s] = pr_kind[s];
+      p.epi.red_partials[s] = s < pr_n_red ? ws + pr_off[s] : nullptr;
+    }
     HE_TRY(launch_gemm_program(cfg, p, stream));
     last_launches = 1 + extra_launches;
+    for (int s = 0; s < pr_n_red; ++s) {
+      float* dst = reinterpret_cast<float*>(outputs[pr_out[s]]);
+      if (pr_kind[s] == 0) {
+        // [batch][tile_m][N] partials; folding the batch in just lengthens the tile axis
+        if (pr_fold_batch[s]) HE_TRY(launch_colsum_finalize(ws + pr_off[s], dst, 1, c.batch * c.tiles_m, c.N, stream));
+        else HE_TRY(launch_colsum_finalize(ws + pr_off[s], dst, c.batch, c.tiles_m, c.N, stream));
+      } else if (pr_kind[s] == 1) {
+        HE_TRY(launch_colsum_finalize(ws + pr_off[s], dst, 1, pr_row_slots, c.batch * c.M, stream));   // [slot][batch * M]
+      } else {
+        HE_TRY(launch_scalar_finalize(ws + pr_off[s], dst, c.num_tiles, stream));
+      }
+      ++last_launches;
+    }
     return HE_OK;
   }
 };
@@ -756,15 +781,57 @@ int32_t plan_fused_matmul(he_ctx* ctx, const Graph& g, he_plan** out, int* tier_
     opt.fuse_fma = true;
     opt.epilogue = true;
     HE_TRY(compile_pointwise(g, opt, &plan->prog));
-    if (plan->prog.prog.n_reductions > 0)
-      HE_FAIL(HE_ERR_UNSUPPORTED, "fused matmul: this epilogue contains a reduction that matches no hand-written kernel");
     if (plan->prog.has_bool_io) HE_FAIL(HE_ERR_UNSUPPORTED, "fused matmul: bool tensors in the epilogue are not supported");
+    // reductions of the interpreted epilogue: Sum over rows, over columns, or over the whole tile
+    const PwProgram& EP = plan->prog.prog;
+    if (EP.n_reductions > 4) HE_FAIL(HE_ERR_UNSUPPORTED, "fused matmul: more than 4 reductions in one epilogue");
+    for (int i = 0; i < EP.n_instr; ++i) {
+      const PwInstr& in = EP.instr[i];
+      if (in.op != PW_REDUCE) continue;
+      if (in.sub != HE_RED_SUM)
+        HE_FAIL(HE_ERR_UNSUPPORTED, "fused matmul: the generic epilogue reduces with Sum only (the playground's ReductionOp)");
+      const int s = in.slot2;
+      const uint32_t m = in.imm;
+      int kind;
+      if ((m & 3u) == 3u) {
+        if (!(m & 4u) && c.batch != 1)
+          HE_FAIL(HE_ERR_UNSUPPORTED, "fused matmul: a per-item scalar reduction needs batch 1 in the generic epilogue");
+        kind = 2;
+      } else if ((m & 3u) == 2u) {
+        kind = 0;
+        plan->pr_fold_batch[s] = (m & 4u) ? 1 : 0;
+      } else if (m == 1u) {
+        kind = 1;
+      } else {
+        HE_FAIL(HE_ERR_UNSUPPORTED, "fused matmul: reduction axes mask %u is not one of rows / columns / item / batch", m);
+      }
+      plan->pr_kind[s] = kind;
+      plan->pr_out[s] = in.slot;
+      if (kind == 0) {
+        if (plan->pr_n_col == 2) HE_FAIL(HE_ERR_UNSUPPORTED, "fused matmul: at most two column reductions in the generic epilogue");
+        plan->pr_col_slot[plan->pr_n_col++] = s;
+      }
+      plan->pr_n_red = std::max(plan->pr_n_red, s + 1);
+    }
     if (tier_only) { *tier_only = 1; return HE_OK; }
     plan->kind = EpiKind::Program;
     finish_tiles();
+    {
+      size_t off = 0;
+      plan->pr_row_slots = c.tiles_n * (plan->cfg.bn / 64);
+      for (int s = 0; s < plan->pr_n_red; ++s) {
+        plan->pr_off[s] = off;
+        const size_t n = plan->pr_kind[s] == 0 ? (size_t)c.batch * c.tiles_m * c.N
+                         : plan->pr_kind[s] == 1 ? (size_t)plan->pr_row_slots * c.batch * c.M
+                                                 : (size_t)c.num_tiles;
+        off += (n + 63) / 64 * 64;
+      }
+      plan->workspace_bytes = off * sizeof(float);
+    }
     snprintf(desc, sizeof desc,
-             "fused matmul tier 1: tcgen05 %sx256x64, %s-major A, %s-major B, mainloop %d, interpreted epilogue (%d instr), grid %d",
-             plan->cfg.two_cta ? "2-CTA 256" : "128", plan->cfg.a_mn ? "M" : "K", plan->cfg.b_mn ? "N" : "K", plan->cfg.ml, plan->prog.prog.n_instr, plan->cfg.grid);
+             "fused matmul tier 1: tcgen05 %sx256x64, %s-major A, %s-major B, mainloop %d, interpreted epilogue (%d instr, %d reductions), grid %d",
+             plan->cfg.two_cta ? "2-CTA 256" : "128", plan->cfg.a_mn ? "M" : "K", plan->cfg.b_mn ? "N" : "K", plan->cfg.ml, plan->prog.prog.n_instr,
+             plan->pr_n_red, plan->cfg.grid);
     plan->description = std::string(desc) + choose_mainloop();
     *out = guard.release();
     return HE_OK;

@@ -411,34 +411,136 @@ struct EpiC3 {
 };
 
 // ---- EpiProgram: generic tier, the pointwise interpreter fed with accumulator values -------------
+// Any legal pointwise epilogue, plus up to four Sum reductions of pointwise expressions of the tile
+// (the playground's Reduction{Sum, depth}, helium-playground/src/opgraph.rs:397-413):
+//   kind 0  over rows (Columns, -> [b,1,N], or [1,1,N] when the batch is folded in): values are
+//           summed over the warp's 32 rows, the four row quadrants meet in shared memory, one partial
+//           per (M tile, column);
+//   kind 1  over columns (Rows, -> [b,M,1]): a thread owns a row, so it keeps a running sum over
+//           the chunks it walks and writes one partial per 64-column slot of the row;
+//   kind 2  over the whole tile (Item with batch 1, Batch, -> one scalar): running sum per thread,
+//           shuffle tree, one partial per CTA tile.
+// Fixed-order folds of the partials (gemm_colsum_finalize / gemm_scalar_finalize) finish the job,
+// so results repeat bit for bit.
 struct EpiProgramParams {
   PwProgram prog;  // by value: lives in the kernel parameter block (constant bank)
+  int n_red;             // reductions of the program (PwInstr::slot2 numbers them)
+  int red_kind[4];       // per reduction slot: 0 columns, 1 rows, 2 scalar
+  float* red_partials[4];
+  int n_col;             // kind-0 reductions (at most kColReductions)
+  int col_slot[2];       // their reduction slots
+  int rows_total;        // batch * M
 };
 struct EpiProgram {
   using Params = EpiProgramParams;
-  static constexpr int kColReductions = 0;
+  static constexpr int kColReductions = 2;
   static constexpr int kChunk = 32;
-  struct State {};
-  __device__ static void tile_begin(State&) {}
-  __device__ static void chunk(const Params& p, const EpiEnv& env, const TileInfo& t, State&, int row, int col, float (&v)[kChunk]) {
+  struct State { float red[4]; };
+  __device__ static void tile_begin(State& s) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) s.red[i] = 0.0f;
+  }
+  __device__ static void chunk(const Params& p, const EpiEnv& env, const TileInfo& t, State& st, int row, int col, float (&v)[kChunk]) {
     const GemmCore& c = *env.core;
     const int grow = t.m0 + row, gcol = t.n0 + col;
-    if (grow >= c.M) return;
-    const uint32_t base = (uint32_t)(((size_t)t.b * c.M + grow) * c.N + gcol);
-    const bool row_aligned = (c.N & 3) == 0;
+    float cbuf[kColReductions][kChunk];
+    if (p.n_col > 0) {
+#pragma unroll
+      for (int r = 0; r < kColReductions; ++r)
+#pragma unroll
+        for (int i = 0; i < kChunk; ++i) cbuf[r][i] = 0.0f;
+    }
+    if (grow < c.M) {
+      const uint32_t base = (uint32_t)(((size_t)t.b * c.M + grow) * c.N + gcol);
+      const bool row_aligned = (c.N & 3) == 0;
+      // rolled on purpose: the interpreter body is large, eight inlined copies would not fit the
+      // instruction cache (cbuf then lives in local memory, which only programs with column sums touch)
 #pragma unroll 1
-    for (int i = 0; i < kChunk; i += 4) {
-      const int nv = max(0, min(4, c.N - (gcol + i)));
-      if (nv == 0) break;
-      const float acc4[4] = {v[i], v[i + 1], v[i + 2], v[i + 3]};
-      if (row_aligned) {
-        pw_run<4>(p.prog, base + i, nv, acc4, nullptr);
-      } else {
-        for (int j = 0; j < nv; ++j) pw_run<1>(p.prog, base + i + j, 1, acc4 + j, nullptr);
+      for (int i = 0; i < kChunk; i += 4) {
+        const int nv = max(0, min(4, c.N - (gcol + i)));
+        if (nv > 0) {
+          const float acc4[4] = {v[i], v[i + 1], v[i + 2], v[i + 3]};
+          float cv[4][4];
+          if (row_aligned) {
+            pw_run<4>(p.prog, base + i, nv, acc4, st.red, p.n_col > 0 ? cv : nullptr);
+          } else {
+            for (int j = 0; j < nv; ++j) {
+              float cv1[4][1];
+              pw_run<1>(p.prog, base + i + j, 1, acc4 + j, st.red, p.n_col > 0 ? cv1 : nullptr);
+#pragma unroll
+              for (int s = 0; s < 4; ++s) cv[s][j] = cv1[s][0];
+            }
+            for (int j = nv; j < 4; ++j)
+#pragma unroll
+              for (int s = 0; s < 4; ++s) cv[s][j] = 0.0f;
+          }
+          if (p.n_col > 0) {
+#pragma unroll
+            for (int r = 0; r < kColReductions; ++r) {
+              const int s = p.col_slot[r];
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const float x = s == 0 ? cv[0][j] : s == 1 ? cv[1][j] : s == 2 ? cv[2][j] : cv[3][j];
+                cbuf[r][i + j] = r < p.n_col ? x : 0.0f;
+              }
+            }
+          }
+        }
       }
     }
+    // every lane of the warp takes part in the shuffles, rows beyond M contribute zeros
+#pragma unroll
+    for (int r = 0; r < kColReductions; ++r)
+      if (r < p.n_col) warp_colsum_store<kChunk>(cbuf[r], env.scratch + (r * 4 + env.quadrant) * env.bn + col);
   }
-  __device__ static void tile_end(const Params&, const EpiEnv&, const TileInfo&, State&) {}
+  __device__ static void tile_end(const Params& p, const EpiEnv& env, const TileInfo& t, State& st) {
+    if (p.n_red == 0) return;
+    const GemmCore& c = *env.core;
+    const int lane = threadIdx.x & 31;
+    float* scal = env.scratch + (size_t)kColReductions * 4 * env.bn;   // [reduction][epilogue warp]
+    const int n_warps = env.n_epi_threads / 32;
+    bool any_scalar = false;
+#pragma unroll
+    for (int s = 0; s < 4; ++s) {
+      if (s >= p.n_red) break;
+      if (p.red_kind[s] == 1) {
+        // one partial per 64-column slot of the row; a warp that covers more than one slot puts its
+        // sum into the first and zeros into the rest, so that the fold may read every slot
+        const int cols_per_warp = t.bn / (n_warps / 4);
+        const int col_begin = (env.epi_warp / 4) * cols_per_warp;
+        const int grow = t.m0 + env.quadrant * 32 + lane;
+        if (grow < c.M) {
+          const int slot0 = (t.n0 + col_begin) / 64;
+          const size_t r = (size_t)t.b * c.M + grow;
+          for (int k = 0; k < cols_per_warp / 64; ++k)
+            p.red_partials[s][(size_t)(slot0 + k) * p.rows_total + r] = k == 0 ? st.red[s] : 0.0f;
+        }
+      } else if (p.red_kind[s] == 2) {
+        float l = st.red[s];
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) l += __shfl_down_sync(0xffffffffu, l, off);
+        if (lane == 0) scal[s * n_warps + env.epi_warp] = l;
+        any_scalar = true;
+      }
+    }
+    if (p.n_col > 0) {
+      float* parts[kColReductions] = {p.red_partials[p.col_slot[0]], p.red_partials[p.col_slot[p.n_col > 1 ? 1 : 0]]};
+      col_partials_flush(env, t, p.n_col, parts);   // its first barrier also publishes scal[]
+    } else if (any_scalar) {
+      ptx::named_barrier_sync(1, env.n_epi_threads);
+    }
+    if (any_scalar) {
+      if (env.epi_tid == 0) {
+        for (int s = 0; s < p.n_red; ++s)
+          if (p.red_kind[s] == 2) {
+            float tot = 0.0f;
+            for (int w = 0; w < n_warps; ++w) tot += scal[s * n_warps + w];
+            p.red_partials[s][t.tile_idx] = tot;
+          }
+      }
+      ptx::named_barrier_sync(1, env.n_epi_threads);   // scal[] may be rewritten for the next tile
+    }
+  }
 };
 
 // =================================================================================================
@@ -459,7 +561,7 @@ struct GemmSmem {
   static constexpr int off_b = off_a + STAGES * kATileBytes;
   static constexpr int off_mask = off_b + STAGES * kBTileBytes;
   static constexpr int off_scratch = off_mask + (kHasMask ? STAGES * kATileBytes : 0);
-  static constexpr int scratch_bytes = (N_COLRED * 4 * BN + 16) * 4;
+  static constexpr int scratch_bytes = (N_COLRED * 4 * BN + 64) * 4;
   static constexpr int off_bar = off_scratch + scratch_bytes;
   static constexpr int n_bars = 3 * STAGES + 4;
   static constexpr int off_misc = off_bar + n_bars * 8;

@@ -75,7 +75,7 @@ struct GemmSmem2 {
   static constexpr int off_b = off_a + STAGES * kATileBytes;
   static constexpr int off_mask = off_b + STAGES * kBHalfBytes;
   static constexpr int off_scratch = off_mask + (kHasMask ? STAGES * kATileBytes : 0);
-  static constexpr int scratch_bytes = (N_COLRED * 4 * kBN2 + 16) * 4;
+  static constexpr int scratch_bytes = (N_COLRED * 4 * kBN2 + 64) * 4;
   static constexpr int off_bar = off_scratch + scratch_bytes;
   // full_b[S] (leader), full_a[S] (local, mainloop fusion only), empty[S] (local), xform[S] (leader),
   // tmem_full[2] (local), tmem_empty[2] (leader)

@@ -120,9 +120,13 @@ __device__ __forceinline__ float pw_reduce_identity(int op) {
 //   red[s]      : running reduction values, updated with every valid element
 //   STORE_BOOL_BALLOT: bool outputs are written one word per warp with __ballot_sync (V == 1 and
 //                      idx0 = 32 * k + lane); all lanes of the warp must call with the same program.
+//   colv[s][j] : fused-matmul epilogues only.  A reduction over the rows of the output tile (axes mask
+//                 2 or 6: "Columns" sums) cannot be folded into a per-thread scalar, because a thread
+//                 owns one row; the values of its V elements are handed back per reduction slot and
+//                 the caller sums them across the warp's rows.  Invalid elements yield 0.
 template <int V>
 __device__ __forceinline__ void pw_run(const PwProgram& P, uint32_t idx0, int nvalid, const float* acc,
-                                       float* red) {
+                                       float* red, float (*colv)[V] = nullptr) {
   uint32_t R[kPwMaxRegs][V];
 #pragma unroll 1
   for (int pc = 0; pc < P.n_instr; ++pc) {
@@ -256,9 +260,14 @@ __device__ __forceinline__ void pw_run(const PwProgram& P, uint32_t idx0, int nv
         break;
       }
       case PW_REDUCE:
+        if (colv && (in.imm & 3u) == 2u) {
 #pragma unroll
-        for (int j = 0; j < V; ++j)
-          if (j < nvalid) red[in.slot2] = pw_reduce_combine(in.sub, red[in.slot2], __uint_as_float(R[in.a][j]));
+          for (int j = 0; j < V; ++j) colv[in.slot2 & 3][j] = j < nvalid ? __uint_as_float(R[in.a][j]) : 0.0f;
+        } else {
+#pragma unroll
+          for (int j = 0; j < V; ++j)
+            if (j < nvalid) red[in.slot2] = pw_reduce_combine(in.sub, red[in.slot2], __uint_as_float(R[in.a][j]));
+        }
         break;
       default: break;
     }

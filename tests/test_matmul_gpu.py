@@ -264,3 +264,56 @@ def test_tail_split_tiles(ctx, kw):
     got, plan = _run(ctx, g, ins)
     assert "2-CTA" in plan.description
     _compare(g, got, O.evaluate(g, ins), plan.description)
+
+
+def _generic_reduction_graph(m, n, k, batch=None, which=("cols", "rows", "all")):
+    """tanh(A B + bias) stored, plus Sum reductions of pointwise expressions of it that match no
+    hand-written epilogue: over rows (Columns), over columns (Rows), over everything."""
+    g = ir.Graph()
+    lead = [] if batch is None else [batch]
+    a = g.new_input(lead + [m, k], ir.BF16)
+    b = g.new_input(lead + [k, n], ir.BF16)
+    bias = g.new_input([n], ir.BF16)
+    w = g.new_input(lead + [m, n], ir.BF16)
+    t = g.binary(ir.BIN_ADD, g.matmul(a, b, ir.PREC_BF16_F32), g.broadcast_to(bias, lead + [m, n]))
+    y = g.unary(ir.UN_TANH, t)
+    g.new_output(g.cast(y, ir.BF16))
+    r = len(lead) + 2
+    e = g.binary(ir.BIN_MUL, y, w)
+    if "cols" in which:
+        g.new_output(g.reduce_axes(ir.RED_SUM, e, [r - 2]))                       # [.., 1, n]
+    if "rows" in which:
+        g.new_output(g.reduce_axes(ir.RED_SUM, g.binary(ir.BIN_MUL, y, y), [r - 1]))   # [.., m, 1]
+    if "all" in which:
+        g.new_output(g.reduce_axes(ir.RED_SUM, e, list(range(r))))                # [1, .., 1]
+    if "cols_batch" in which:
+        g.new_output(g.reduce_axes(ir.RED_SUM, y, [0, r - 2]))                    # [1, 1, n]: batch folded in
+    return g
+
+
+@pytest.mark.parametrize("m,n,k,batch,which", [
+    (256, 512, 128, None, ("cols", "rows", "all")),
+    (200, 264, 72, None, ("cols", "rows", "all")),        # ragged tiles, one-CTA kernel for the last rows
+    (640, 768, 64, None, ("rows",)),
+    (128, 128, 64, None, ("cols", "all")),                 # single-CTA kernel
+    (256, 256, 64, 3, ("cols", "rows", "cols_batch")),
+    (4096, 4096, 64, None, ("cols", "rows", "all")),       # tail-split half tiles
+])
+def test_generic_epilogue_reductions(ctx, m, n, k, batch, which):
+    g = _generic_reduction_graph(m, n, k, batch, which)
+    ins = _gen(g, 51, {1: 1.0 / np.sqrt(k), 2: 0.1})
+    got, plan = _run(ctx, g, ins)
+    assert "tier 1" in plan.description and "reductions" in plan.description
+    _compare(g, got, O.evaluate(g, ins), plan.description)
+    got2, _ = _run(ctx, g, ins)
+    for x, y in zip(got, got2):
+        assert np.array_equal(x, y), "reductions must be bit-stable across launches"
+
+
+def test_generic_epilogue_reduction_limits(ctx):
+    g = ir.Graph()
+    a = g.new_input([256, 64], ir.BF16); b = g.new_input([64, 256], ir.BF16)
+    y = g.unary(ir.UN_EXP, g.matmul(a, b, ir.PREC_BF16_F32))
+    g.new_output(g.reduce_axes(ir.RED_MAX, y, [0]))
+    with pytest.raises(hb.HeliumError, match="Sum only"):
+        hb.Plan.fused_matmul(ctx, g)
