@@ -92,3 +92,14 @@ def test_matmul_epilogue_and_mainloop_fuse_through_the_planner():
     g.new_output(g.cast(t, ir.BF16))
     ins = _instrs(hb.HostGraph(g).plan_text())
     assert len(ins) == 1 and ins[0]["kind"] == "FusedMatmul" and ins[0]["tier"] == 2
+
+
+def test_readme_graph_fuses_into_one_matmul_instruction():
+    """Greedy pairwise fusion (plan_generation.rs:243-256) folds the README graph, op by op, into a
+    single FusedMatmul instruction that the kernel catalogue serves at tier 2; the intermediate
+    merges are legal because the interpreted epilogue accepts Sum reductions."""
+    import helium_b200 as hb
+    from helium_b200.configs import graph_c3
+    text = hb.HostGraph(graph_c3(1024, 1024, 1024)).plan_text()
+    steps = [ln for ln in text.splitlines() if "FusedMatmul" in ln or "Pointwise" in ln or "Permute" in ln]
+    assert len(steps) == 1 and "FusedMatmul tier=2" in steps[0], text

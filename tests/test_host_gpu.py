@@ -69,3 +69,17 @@ def test_transformer_mlp_forward_graph(ctx):
     want = O.evaluate(g, ins, round_nodes=[h_node])
     got, _ = _run_graph(ctx, g, ins, capture=False)
     assert O.rel_l2(O.decode(got[0], ir.BF16, (T, d)), O.decode(want[0], ir.BF16, (T, d))) <= 1e-2
+
+
+def test_readme_graph_through_the_host_runtime(ctx):
+    """The whole README graph handed to the planner as an op graph: one fused instruction, same numbers."""
+    m, n, k = 256, 512, 128
+    g = configs.graph_c3(m, n, k, False)
+    ins = configs.c3_inputs(m, n, k, False)
+    got, ex = _run_graph(ctx, g, ins, capture=False)
+    want = O.evaluate(g, ins)
+    assert ex.stats()["instrs"] == 1
+    for o, a, b in zip(g.outputs, got, want):
+        node = g.nodes[o]
+        tol = 1e-5 if node.dtype == ir.F32 else 1e-2
+        assert O.rel_l2(O.decode(a, node.dtype, node.shape), O.decode(b, node.dtype, node.shape)) <= tol
