@@ -155,6 +155,12 @@ int32_t he_permute_output_strides(int32_t rank, const int64_t* in_shape, int32_t
  * (op.rs:272-282); a SWAP_DIMS of the last two dims feeding an operand selects the transposed
  * shared-memory descriptor instead of moving data. */
 int32_t he_plan_fused_matmul(he_ctx* ctx, const he_graph_desc* desc, he_plan** out);
+/* Environment switches read at plan time (benchmarks and comparisons only):
+ *   HE_GEMM_ONE_CTA=1         one CTA per 128 x 256 tile instead of CTA pairs on 256 x 256 tiles
+ *   HE_GEMM_GROUP_M=<n>       row tiles per rasterisation group
+ *   HE_GEMM_NO_SPLIT=1        never run the tiles of an under-filled last round as half-width tiles
+ *   HE_GEMM_MAINLOOP=fused|materialise   force how a mainloop fusion is executed
+ *   HE_GEMM_DEBUG=<bits>      timing experiments: 1 skips the mainloop rewrite (wrong results), 2 its proxy fence */
 
 /* Backs Instruction::can_fuse_with (helium/src/backend.rs:85-95): 0 = cannot run as one kernel,
  * 1 = runs through the generic interpreter tier, 2 = matches a hand-written fast kernel.
@@ -162,7 +168,9 @@ int32_t he_plan_fused_matmul(he_ctx* ctx, const he_graph_desc* desc, he_plan** o
 int32_t he_plan_supported(he_ctx* ctx, const he_graph_desc* desc, int32_t kind);
 
 /* Scratch the launch needs (caller-allocated from its stream allocator with 256-byte alignment,
- * like the cuDNN workspace in helium/src/cuda/instr/cudnn_graph.rs:75-92). */
+ * like the cuDNN workspace in helium/src/cuda/instr/cudnn_graph.rs:75-92).  It holds the per-tile
+ * partials of fused reductions and, when a mainloop fusion is executed by a pre-pass, the
+ * materialised A operand (batch * M * K elements); contents are undefined between launches. */
 int32_t he_plan_workspace_bytes(const he_plan* plan, size_t* out);
 
 /* Replaces {PointwiseGraph,PermuteDims,CudnnGraph}::execute (pointwise.rs:57-86,
