@@ -513,7 +513,148 @@ struct MatmulPlan : he_plan {
 
 }  // namespace
 
+namespace {
+int32_t plan_fused_matmul_core(he_ctx* ctx, const Graph& g, he_plan** out, int* tier_only);
+
+// Pointwise sub-DAG that computes `node`, as a graph of its own: ancestors keep their order, input
+// slots are the caller's slots that the sub-DAG reads (`slots`), the single output is `node`.
+int32_t extract_operand_graph(const Graph& g, int node, Graph* sub, std::vector<int>* slots) {
+  std::vector<char> used(g.nodes.size(), 0);
+  std::vector<int> stack{node};
+  while (!stack.empty()) {
+    const int i = stack.back();
+    stack.pop_back();
+    if (used[i]) continue;
+    used[i] = 1;
+    const he_node& n = g.nodes[i];
+    if (n.kind == HE_OP_MATMUL) HE_FAIL(HE_ERR_UNSUPPORTED, "fused matmul: a matmul operand depends on another matmul");
+    if (n.kind == HE_OP_REDUCE) HE_FAIL(HE_ERR_UNSUPPORTED, "fused matmul: a reduction on the operand side cannot be fused");
+    for (int k = 0; k < 3; ++k)
+      if (n.in[k] >= 0) stack.push_back(n.in[k]);
+  }
+  std::vector<int> remap(g.nodes.size(), -1);
+  for (size_t i = 0; i < g.nodes.size(); ++i) {
+    if (!used[i]) continue;
+    he_node n = g.nodes[i];
+    for (int k = 0; k < 3; ++k)
+      if (n.in[k] >= 0) n.in[k] = remap[n.in[k]];
+    remap[i] = (int)sub->nodes.size();
+    sub->nodes.push_back(n);
+  }
+  for (size_t k = 0; k < g.inputs.size(); ++k)
+    if (used[g.inputs[k]]) {
+      sub->inputs.push_back(remap[g.inputs[k]]);
+      slots->push_back((int)k);
+    }
+  sub->outputs.push_back(remap[node]);
+  return HE_OK;
+}
+
+// A fused matmul whose A and / or B operand is a pointwise expression beyond what the kernels apply
+// in their mainloop (helium-kernel-generator accepts Constant / Unary / Binary / ChangeDataType /
+// Reshape / SwapDims chains there, generators/matmul.rs:234-264).  The expression is evaluated once
+// by a pointwise plan into the workspace and the inner plan sees it as one more input.
+struct PrologueMatmulPlan : he_plan {
+  std::unique_ptr<he_plan> inner;
+  int n_caller_inputs = 0;
+  struct Pro {
+    std::unique_ptr<he_plan> plan;
+    std::vector<int> slots;   // caller input slots, in the pointwise plan's input order
+    size_t off = 0;           // bytes into the workspace
+  };
+  std::vector<Pro> pros;      // in the order their results were appended to the inner plan's inputs
+
+  int32_t launch(const void* const* inputs, void* const* outputs, void* workspace, cudaStream_t stream) override {
+    if (!workspace) HE_FAIL(HE_ERR_WORKSPACE, "fused matmul launch: this plan needs a %zu-byte workspace", workspace_bytes);
+    std::vector<const void*> ext(inputs, inputs + n_caller_inputs);
+    last_launches = 0;
+    for (Pro& pr : pros) {
+      std::vector<const void*> pin;
+      for (int sl : pr.slots) {
+        if (!inputs[sl]) HE_FAIL(HE_ERR_INVALID, "fused matmul launch: input %d is null", sl);
+        pin.push_back(inputs[sl]);
+      }
+      void* dst = reinterpret_cast<char*>(workspace) + pr.off;
+      void* pout[1] = {dst};
+      HE_TRY(pr.plan->launch(pin.data(), pout, nullptr, stream));
+      last_launches += pr.plan->last_launches;
+      ext.push_back(dst);
+    }
+    HE_TRY(inner->launch(ext.data(), outputs, inner->workspace_bytes ? workspace : nullptr, stream));
+    last_launches += inner->last_launches;
+    return HE_OK;
+  }
+};
+}  // namespace
+
 int32_t plan_fused_matmul(he_ctx* ctx, const Graph& g, he_plan** out, int* tier_only) {
+  int mm = -1;
+  for (int i = 0; i < (int)g.nodes.size(); ++i)
+    if (g.nodes[i].kind == HE_OP_MATMUL && mm < 0) mm = i;
+  if (mm < 0) return plan_fused_matmul_core(ctx, g, out, tier_only);   // reports the error
+  const OperandInfo A = trace_operand(g, g.nodes[mm].in[0], false), B = trace_operand(g, g.nodes[mm].in[1], false);
+  // The kernels apply exactly relu(A) * mask on bf16 tiles in their mainloop (or in the dense pre-pass);
+  // every other operand expression, and that one on shapes / dtypes the tensor-core path does not
+  // take, goes through a pointwise pre-pass.
+  bool fusable_a = A.ok;
+  if (A.ok && !A.pure()) {
+    const he_node& M0 = g.nodes[mm];
+    const int64_t Md = M0.shape[M0.rank - 2], Kd = g.nodes[M0.in[0]].shape[M0.rank - 1], Nd = M0.shape[M0.rank - 1];
+    fusable_a = A.relu && A.mask >= 0 && g.nodes[A.root].dtype == HE_BF16 && g.nodes[A.mask].dtype == HE_BF16 && B.ok && B.pure() &&
+                g.nodes[B.root].dtype == HE_BF16 && (A.transposed ? Md : Kd) % 8 == 0 && (B.transposed ? Kd : Nd) % 8 == 0;
+  }
+  const bool pro_a = !fusable_a, pro_b = !B.ok || !B.pure();
+  if (!pro_a && !pro_b) return plan_fused_matmul_core(ctx, g, out, tier_only);
+
+  // replace each such operand by a virtual input (same node index, so the list stays topological)
+  Graph g2 = g;
+  auto plan = std::make_unique<PrologueMatmulPlan>();
+  plan->ctx = ctx;
+  plan->n_caller_inputs = (int)g.inputs.size();
+  std::string note;
+  size_t extra = 0;
+  for (int side = 0; side < 2; ++side) {
+    if (!(side == 0 ? pro_a : pro_b)) continue;
+    const int node = g.nodes[mm].in[side];
+    const he_node& on = g.nodes[node];
+    PrologueMatmulPlan::Pro pr;
+    Graph sub;
+    HE_TRY(extract_operand_graph(g, node, &sub, &pr.slots));
+    he_plan* pp = nullptr;
+    int tier = 0;
+    HE_TRY(plan_pointwise(ctx, sub, tier_only ? nullptr : &pp, tier_only ? &tier : nullptr));
+    pr.plan.reset(pp);
+    pr.off = extra;   // relative to the end of the inner workspace, fixed up below
+    extra += ((size_t)num_elements(on) * (on.dtype == HE_F32 ? 4 : 2) + 255) / 256 * 256;
+    he_node in{};
+    in.kind = HE_OP_INPUT;
+    in.dtype = on.dtype;
+    in.rank = on.rank;
+    for (int k = 0; k < on.rank; ++k) in.shape[k] = on.shape[k];
+    in.in[0] = in.in[1] = in.in[2] = -1;
+    g2.nodes[node] = in;
+    g2.inputs.push_back(node);
+    if (pp) note += std::string(", operand ") + (side == 0 ? "A" : "B") + " evaluated by a pre-pass (" + pp->description + ")";
+    plan->pros.push_back(std::move(pr));
+  }
+  he_plan* inner = nullptr;
+  int inner_tier = 0;
+  HE_TRY(plan_fused_matmul_core(ctx, g2, tier_only ? nullptr : &inner, tier_only ? &inner_tier : nullptr));
+  if (tier_only) {
+    *tier_only = inner_tier > 0 ? 1 : 0;   // runs, but the operand side is not fused into the mainloop
+    return HE_OK;
+  }
+  plan->inner.reset(inner);
+  const size_t base = (inner->workspace_bytes + 255) / 256 * 256;
+  for (auto& pr : plan->pros) pr.off += base;
+  plan->workspace_bytes = base + extra;
+  plan->description = inner->description + note;
+  *out = plan.release();
+  return HE_OK;
+}
+
+namespace {
+int32_t plan_fused_matmul_core(he_ctx* ctx, const Graph& g, he_plan** out, int* tier_only) {
   int mm = -1;
   for (int i = 0; i < (int)g.nodes.size(); ++i)
     if (g.nodes[i].kind == HE_OP_MATMUL) {
@@ -837,5 +978,7 @@ int32_t plan_fused_matmul(he_ctx* ctx, const Graph& g, he_plan** out, int* tier_
     return HE_OK;
   }
 }
+
+}  // namespace
 
 }  // namespace he

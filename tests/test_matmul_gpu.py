@@ -317,3 +317,33 @@ def test_generic_epilogue_reduction_limits(ctx):
     g.new_output(g.reduce_axes(ir.RED_MAX, y, [0]))
     with pytest.raises(hb.HeliumError, match="Sum only"):
         hb.Plan.fused_matmul(ctx, g)
+
+
+def test_operand_side_pointwise_prologues(ctx):
+    """Operand expressions beyond relu * mask (any Constant / Unary / Binary / cast / reshape / swap
+    chain, generators/matmul.rs:234-264) are evaluated once into the workspace by a pointwise plan;
+    the oracle rounds the operand where the pre-pass materialises it."""
+    m, n, k = 256, 384, 128
+    g = ir.Graph()
+    x = g.new_input([m, k], ir.BF16); s = g.new_input([k], ir.BF16); y = g.new_input([m, k], ir.BF16)
+    w = g.new_input([n, k], ir.BF16); bias = g.new_input([n], ir.BF16)
+    a = g.binary(ir.BIN_ADD, g.binary(ir.BIN_MUL, x, g.broadcast_to(s, [m, k])), g.unary(ir.UN_TANH, y))     # A = x * s + tanh(y)
+    b = g.unary(ir.UN_MUL_CONST, g.unary(ir.UN_SIGMOID, g.transpose(w)), 0.5)                                  # B = 0.5 * sigmoid(w^T)
+    t = g.binary(ir.BIN_ADD, g.matmul(a, b, ir.PREC_BF16_F32), g.broadcast_to(bias, [m, n]))
+    g.new_output(g.cast(g.unary(ir.UN_RELU, t), ir.BF16))
+    ins = _gen(g, 61, {1: 0.5, 3: 1.0})
+    plan = hb.Plan.fused_matmul(ctx, g)
+    assert "operand A evaluated by a pre-pass" in plan.description and "operand B evaluated by a pre-pass" in plan.description
+    assert hb.plan_supported(g, 2) == 1
+    got, _ = _run(ctx, g, ins)
+    mm = [i for i, nd in enumerate(g.nodes) if nd.kind == ir.OP_MATMUL][0]
+    want = O.evaluate(g, ins, round_nodes=list(g.nodes[mm].inputs[:2]))
+    _compare(g, got, want, plan.description)
+    # f32 operands take the SIMT GEMM; the prologue works the same way
+    g = ir.Graph()
+    a = g.new_input([96, 40], ir.F32); b = g.new_input([40, 24], ir.F32)
+    g.new_output(g.matmul(g.binary(ir.BIN_MUL, a, a), g.unary(ir.UN_EXP, b), ir.PREC_TF32_F32))
+    ins = _gen(g, 62, {1: 0.3})
+    got, plan = _run(ctx, g, ins)
+    assert "SIMT" in plan.description and "pre-pass" in plan.description
+    _compare(g, got, O.evaluate(g, ins), plan.description)

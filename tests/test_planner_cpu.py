@@ -181,10 +181,16 @@ def test_matmul_refusals():
     with pytest.raises(HeliumError) as e:
         hb.Plan.fused_matmul(None, g)
     assert "multiples of 8" in str(e.value)
-    # unsupported mainloop op
+    # an operand expression the kernels do not apply in their mainloop is evaluated by a pre-pass (tier 1)
     g = ir.Graph()
     a = g.new_input([128, 64], ir.BF16); b = g.new_input([64, 256], ir.BF16)
     g.new_output(g.matmul(g.unary(ir.UN_EXP, a), b))
+    assert hb.plan_supported(g, 2) == 1
+    assert "operand A evaluated by a pre-pass" in hb.Plan.fused_matmul(None, g).description
+    # ... unless it hides a reduction or another matmul
+    g = ir.Graph()
+    a = g.new_input([128, 64], ir.BF16); b = g.new_input([64, 256], ir.BF16)
+    g.new_output(g.matmul(g.broadcast_to(g.reduce(ir.RED_SUM, a, 1), [128, 64]), b))
     assert hb.plan_supported(g, 2) == 0
     # f32 operands use the SIMT kernel
     g = ir.Graph()
