@@ -587,7 +587,39 @@ struct PrologueMatmulPlan : he_plan {
 };
 }  // namespace
 
-int32_t plan_fused_matmul(he_ctx* ctx, const Graph& g, he_plan** out, int* tier_only) {
+// helium's front end spells a reduction over the rows of y as swap_dims(y) -> Reduce{depth 1}
+// (-> reshape): "move the axis last, reduce trailing dims" (helium/src/tensor.rs:83-142).  The GEMM
+// epilogue walks y in its own layout, so those leaves are rewritten to the equivalent reduction
+// over y's row axis; the output bytes are the same ([.., N, 1] and [.., 1, N] are both N contiguous
+// values per batch).
+Graph normalise_reduction_leaves(const Graph& g) {
+  Graph o = g;
+  for (int& leaf : o.outputs) {
+    if (o.nodes[leaf].kind == HE_OP_RESHAPE) {
+      const int src = o.nodes[leaf].in[0];
+      if (src >= 0 && o.nodes[src].kind == HE_OP_REDUCE && num_elements(o.nodes[src]) == num_elements(o.nodes[leaf])) leaf = src;
+    }
+    he_node& R = o.nodes[leaf];
+    if (R.kind != HE_OP_REDUCE || R.in[0] < 0) continue;
+    const he_node& S = o.nodes[R.in[0]];
+    if (S.kind != HE_OP_SWAP_DIMS || S.rank < 2) continue;
+    const int lo = std::min(S.axis_a, S.axis_b), hi = std::max(S.axis_a, S.axis_b);
+    if (lo != S.rank - 2 || hi != S.rank - 1) continue;
+    const he_node& V = o.nodes[S.in[0]];
+    const uint32_t b_lo = 1u << lo, b_hi = 1u << hi;
+    uint32_t axes = R.axes & ~(b_lo | b_hi);
+    if (R.axes & b_lo) axes |= b_hi;
+    if (R.axes & b_hi) axes |= b_lo;
+    R.in[0] = S.in[0];
+    R.axes = axes;
+    R.rank = V.rank;
+    for (int k = 0; k < V.rank; ++k) R.shape[k] = ((axes >> k) & 1u) ? 1 : V.shape[k];
+  }
+  return o;
+}
+
+int32_t plan_fused_matmul(he_ctx* ctx, const Graph& g_in, he_plan** out, int* tier_only) {
+  const Graph g = normalise_reduction_leaves(g_in);
   int mm = -1;
   for (int i = 0; i < (int)g.nodes.size(); ++i)
     if (g.nodes[i].kind == HE_OP_MATMUL && mm < 0) mm = i;

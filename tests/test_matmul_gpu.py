@@ -347,3 +347,22 @@ def test_operand_side_pointwise_prologues(ctx):
     got, plan = _run(ctx, g, ins)
     assert "SIMT" in plan.description and "pre-pass" in plan.description
     _compare(g, got, O.evaluate(g, ins), plan.description)
+
+
+def test_helium_style_bias_gradient_fuses(ctx):
+    """helium's front end writes a bias gradient as swap_dims -> Reduce{depth 1} -> reshape
+    (tensor.rs:83-142); the planner rewrites that leaf to a reduction over the rows of the epilogue
+    value, so it lands in the same hand-written column-sum epilogue as the playground spelling."""
+    m, n, k = 384, 512, 128
+    g = ir.Graph()
+    do = g.new_input([m, k], ir.BF16); w = g.new_input([n, k], ir.BF16); z = g.new_input([m, n], ir.BF16)
+    dz = g.binary(ir.BIN_MUL, g.matmul(do, g.transpose(w), ir.PREC_BF16_F32), g.unary(ir.UN_DGELU, z))
+    g.new_output(g.cast(dz, ir.BF16))
+    g.new_output(g.reshape(g.reduce(ir.RED_SUM, g.transpose(dz), 1), [n]))
+    ins = _gen(g, 71, {1: 1.0 / np.sqrt(k)})
+    got, plan = _run(ctx, g, ins)
+    assert "tier 2" in plan.description and "colsum=2" in plan.description
+    _compare(g, got, O.evaluate(g, ins), plan.description)
+    # through the host runtime the three ops (matmul, gate, bias-gradient chain) become one instruction
+    text = hb.HostGraph(g).plan_text()
+    assert sum("FusedMatmul" in ln for ln in text.splitlines()) == 1 and "Pointwise" not in text and "Permute" not in text, text
