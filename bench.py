@@ -10,7 +10,7 @@ on synthetic seeded inputs; the metric is algorithmic HBM bytes moved per second
 Other workloads: c1 = configs[0] (MLP training step, steps/s, whole graph through the C++ host
 runtime as one CUDA graph), c3 = configs[2] (fused 4096^3 GEMM, TFLOP/s), c4 = configs[3]
 (transformer MLP block forward+backward, 8192 tokens per GPU, weight gradients all-reduced over
-NCCL), gemm = a plain 8192^3 bf16 matmul.
+NCCL), c4g = the same block as one op graph through the host runtime, gemm = a plain 8192^3 bf16 matmul.
 
 Rank 0 prints exactly one JSON line.  With N > 1 (launched under torch.distributed.run) c1-c3 run
 an independent replica per rank (those configurations have no cross-GPU dependency); c4 shards
@@ -512,6 +512,70 @@ class WorkloadC4(_GemmBase):
              "(epilogues not included)"), dt
 
 
+class WorkloadC4Graph(_GemmBase):
+    """configs[3] again, but handed to the C++ host runtime as ONE helium-style op graph (casts after every
+    matmul, explicit transposes, swap_dims -> reduce -> reshape bias gradients) instead of six hand-built
+    subgraphs: what the drop-in path behind helium's planner produces.  Single GPU (no gradient exchange)."""
+    key = "c4g"
+    metric, unit = "fused_gemm_tflops", "TFLOP/s"
+    dtype = "bf16 x bf16 -> f32 accumulate, f32 epilogue"
+    TOKENS, D, FF = 8192, 4096, 16384
+    description = ("configs[3] as one op graph through the host runtime: transformer MLP block forward+backward, 8192 tokens, d=4096, "
+                   "ff=16384, bf16; the planner fuses it into six matmul instructions and one column-sum kernel, replayed as a CUDA graph")
+    l2_note = "every GEMM streams operands larger than L2; no flush needed"
+    work_per_step = 6 * 2.0 * 8192 * 4096 * 16384
+
+    def __init__(self, ctx, dev, world, rank, peaks, reducer):
+        import torch
+        import helium_b200 as hb
+        from helium_b200 import configs
+        from helium_b200.mlp_block import mlp_block_inputs
+        self.torch = torch
+        T, d, ff = self.TOKENS, self.D, self.FF
+        g = configs.graph_mlp_block_train(T, d, ff)
+        host = mlp_block_inputs(T, d, ff, seed=3, shard=rank)
+        as_pin = lambda v: torch.from_numpy(np.ascontiguousarray(v).view(np.int16)).pin_memory()
+        order = ("X", "W1", "b1", "W2", "b2", "dO")
+        self.pins = {k: as_pin(host[k]) for k in order}
+        self.ins = [self.pins[k].to(dev).view(torch.bfloat16) for k in order]
+        bf, f32 = torch.bfloat16, torch.float32
+        self.outs = [torch.empty((T, d), dtype=bf, device=dev), torch.empty((T, d), dtype=bf, device=dev),
+                     torch.empty((d, ff), dtype=bf, device=dev), torch.empty(ff, dtype=f32, device=dev),
+                     torch.empty((ff, d), dtype=bf, device=dev), torch.empty(d, dtype=f32, device=dev)]
+        hg = hb.HostGraph(g)
+        self.ex = hb.Executor(ctx, hg, self.ins, self.outs, capture=True)
+        self._keep = hg
+        st = self.ex.stats()
+        self.launches_per_step = st["launches"]
+        self.dx_pin = torch.empty((T, d), dtype=torch.int16).pin_memory()
+        self.h2d = 2 * T * d * 2
+        self.d2h = T * d * 2
+        peak = peaks.get("bf16_tflops_sustained") or peaks["bf16_tflops"]
+        self.dominant = {"mlp_block_graph": (f"CUDA graph of {st['launches']} kernels ({st['instrs']} fused instructions, {st['steps']} plan steps)",
+                                             self.work_per_step, "tensor", peak, "TFLOP/s")}
+        self.dominant_key = "mlp_block_graph"
+        self.peak_note = "sustained cuBLAS bf16 figure (multi-millisecond step under the power cap)"
+
+    def step(self, record=None):
+        if record is None:
+            self.ex.run()
+            return
+        st = self.torch.cuda.current_stream()
+        e0, e1 = _events(self.torch)
+        e0.record(st); self.ex.run(); e1.record(st)
+        record.append(("mlp_block_graph", e0, e1))
+
+    def step_e2e(self):
+        torch = self.torch
+        self.ins[0].view(torch.int16).copy_(self.pins["X"], non_blocking=True)
+        self.ins[5].view(torch.int16).copy_(self.pins["dO"], non_blocking=True)
+        self.ex.run()
+        self.dx_pin.copy_(self.outs[1].view(torch.int16), non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    cpu_sample = staticmethod(lambda max_steps=1: WorkloadC4.cpu_sample(max_steps))
+
+
 class WorkloadC1:
     key = "c1"
     metric, unit = "train_steps_per_s", "step/s"
@@ -588,7 +652,7 @@ class WorkloadC1:
         return 1.0 / dt, cores, f"{max_steps} steps of the numpy f64 restatement (oracle/oracle.py) of the same op graph; the reference's CPU backend is a stub", dt
 
 
-WORKLOADS = {w.key: w for w in (WorkloadC1, WorkloadC2, WorkloadC3, WorkloadC4, WorkloadGemm)}
+WORKLOADS = {w.key: w for w in (WorkloadC1, WorkloadC2, WorkloadC3, WorkloadC4, WorkloadC4Graph, WorkloadGemm)}
 
 
 def _use_all_host_threads():
@@ -630,7 +694,7 @@ def main():
                          "(the printed line is then not a bench value)")
     args = ap.parse_args()
     if args.steps is None:
-        args.steps = {"c1": 2000, "c2": 200, "c3": 200, "c4": 30, "gemm": 100}[args.workload]
+        args.steps = {"c1": 2000, "c2": 200, "c3": 200, "c4": 30, "c4g": 30, "gemm": 100}[args.workload]
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))

@@ -239,3 +239,35 @@ def mlp_inputs(batch: int = 256, d_in: int = 784, d_hidden: int = 512, d_out: in
     w1 = (r.standard_normal((d_in, d_hidden), dtype=np.float32) / np.float32(np.sqrt(d_hidden))).astype(np.float32)
     w2 = (r.standard_normal((d_hidden, d_out), dtype=np.float32) / np.float32(np.sqrt(d_out))).astype(np.float32)
     return [x, t, w1, np.zeros(d_hidden, np.float32), w2, np.zeros(d_out, np.float32)]
+
+
+def graph_mlp_block_train(tokens: int, d: int, ff: int, dtype=ir.BF16, return_nodes: bool = False):
+    """configs[3] as ONE op graph, recorded the way helium's front end would record a transformer MLP
+    block and its backward pass: every matmul result is cast back to the operand dtype
+    (raw_tensor.rs:225-229), gradients use explicit transposes (tensor.rs:437-450) and bias
+    gradients are swap_dims -> reduce_sum -> reshape (tensor.rs:83-142).
+
+    Inputs: X [T,d], W1 [d,ff], b1 [ff], W2 [ff,d], b2 [d], dO [T,d].
+    Outputs: O, dX, dW1, db1, dW2, db2.  With return_nodes the node ids of z, h and dz are returned
+    too: a plan with one kernel per matmul materialises exactly those three between kernels."""
+    g = ir.Graph()
+    T = tokens
+    x = g.new_input([T, d], dtype)
+    w1 = g.new_input([d, ff], dtype)
+    b1 = g.new_input([ff], dtype)
+    w2 = g.new_input([ff, d], dtype)
+    b2 = g.new_input([d], dtype)
+    do = g.new_input([T, d], dtype)
+    mm = lambda a, b: g.cast(g.matmul(a, b, ir.PREC_BF16_F32), dtype)
+    z = g.binary(ir.BIN_ADD, mm(x, w1), g.broadcast_to(b1, [T, ff]))
+    h = g.unary(ir.UN_GELU, z)
+    o = g.binary(ir.BIN_ADD, g.binary(ir.BIN_ADD, mm(h, w2), g.broadcast_to(b2, [T, d])), x)
+    dz = g.binary(ir.BIN_MUL, mm(do, g.transpose(w2)), g.unary(ir.UN_DGELU, z))
+    dw2 = mm(g.transpose(h), do)
+    db2 = g.reshape(g.reduce(ir.RED_SUM, g.transpose(do), 1), [d])
+    dw1 = mm(g.transpose(x), dz)
+    db1 = g.reshape(g.reduce(ir.RED_SUM, g.transpose(dz), 1), [ff])
+    dx = g.binary(ir.BIN_ADD, mm(dz, g.transpose(w1)), do)
+    for t in (o, dx, dw1, db1, dw2, db2):
+        g.new_output(t)
+    return (g, {"z": z, "h": h, "dz": dz}) if return_nodes else g

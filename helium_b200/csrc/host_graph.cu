@@ -160,7 +160,14 @@ struct Instr {
     if (!fused_kind(next, &k)) return false;
     Instr merged{k, sub.merge_with(next.sub)};
     const int t = merged.tier(ctx);
-    if (kind != next.kind && k == InstrKind::PointwiseGraph) return t == 2;
+    if (kind != next.kind && k == InstrKind::PointwiseGraph) {
+      // a permutation folds into a pointwise kernel when a single-pass kernel exists for the pair
+      // (tier 2), or when it only feeds reductions: those read through the swapped view in column
+      // mode, coalesced, and no permuted copy is ever written
+      bool only_reductions = true;
+      for (NodeId l : merged.sub.leafs) only_reductions = only_reductions && sub.graph->nodes[l].kind == HE_OP_REDUCE;
+      return t == 2 || (t > 0 && only_reductions);
+    }
     // Greedy pairwise fusion passes through partial subgraphs that only the interpreter tier
     // serves on the way to one that a hand-written kernel serves, so tier 1 is accepted here.
     return t > 0;

@@ -36,7 +36,8 @@ struct PwReduceLaunch {
   uint32_t num_groups;
   uint32_t blocks_per_group;   // CTAs per group (block mode) -- 1 in warp mode
   uint32_t chunk;              // elements of a group handled by one CTA
-  int warp_mode;               // 1: one warp per group, 8 groups per CTA
+  int warp_mode;               // 0: CTA slices of one group; 1: one warp per group, 8 groups per CTA;
+                               // 2: column mode, a lane per group, 32 groups x one slice per CTA
   int red_ops[4];
   int red_out_slot[4];
   float* partials;             // [n_red][num_groups][blocks_per_group] when blocks_per_group > 1
@@ -51,7 +52,7 @@ __global__ void __launch_bounds__(kPwThreads) pw_reduce_kernel(const __grid_cons
 #pragma unroll
   for (int s = 0; s < 4; ++s) red[s] = s < P.n_reductions ? pw_reduce_identity(L.red_ops[s]) : 0.0f;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  if (L.warp_mode) {
+  if (L.warp_mode == 1) {
     const uint32_t group = blockIdx.x * (kPwThreads / 32) + warp;
     if (group >= L.num_groups) return;  // whole warp leaves together
     const uint32_t base = group * P.group_size;
@@ -66,6 +67,33 @@ __global__ void __launch_bounds__(kPwThreads) pw_reduce_kernel(const __grid_cons
 #pragma unroll
       for (int off = 16; off > 0; off >>= 1) red[s] = pw_reduce_combine(L.red_ops[s], red[s], __shfl_down_sync(0xffffffffu, red[s], off));
       if (lane == 0) reinterpret_cast<float*>(P.out[L.red_out_slot[s]])[group] = red[s];
+    }
+    return;
+  }
+  if (L.warp_mode == 2) {
+    // Column mode, for reductions read through a transposing view (helium's bias gradients:
+    // swap_dims -> reduce): consecutive GROUPS are contiguous in memory, consecutive elements of one
+    // group are a row pitch apart.  Lanes therefore own 32 consecutive groups, so that every load of
+    // the warp is one contiguous run, and the 8 warps of the CTA split this CTA's slice of the group.
+    __shared__ float scol[4][kPwThreads / 32][32];
+    const uint32_t gblocks = (L.num_groups + 31) / 32;
+    const uint32_t blk = blockIdx.x / gblocks, gb = blockIdx.x - blk * gblocks;
+    const uint32_t group = gb * 32 + lane;
+    const bool gvalid = group < L.num_groups;
+    const uint32_t start = blk * L.chunk, end = min(start + L.chunk, P.group_size);
+    const uint32_t base = gvalid ? group * P.group_size : 0u;
+    for (uint32_t e = start + warp; e < end; e += kPwThreads / 32) pw_run<1>(P, base + e, gvalid ? 1 : 0, nullptr, red);
+#pragma unroll
+    for (int s = 0; s < 4; ++s)
+      if (s < P.n_reductions) scol[s][warp][lane] = red[s];
+    __syncthreads();
+    if (warp == 0 && gvalid) {
+      for (int s = 0; s < P.n_reductions; ++s) {
+        float v = scol[s][0][lane];
+        for (int w = 1; w < kPwThreads / 32; ++w) v = pw_reduce_combine(L.red_ops[s], v, scol[s][w][lane]);
+        if (L.blocks_per_group == 1) reinterpret_cast<float*>(P.out[L.red_out_slot[s]])[group] = v;
+        else L.partials[((size_t)s * L.num_groups + group) * L.blocks_per_group + blk] = v;
+      }
     }
     return;
   }
@@ -122,6 +150,10 @@ struct PointwisePlan : he_plan {
   // dense elementwise tier-2 kernel (when the program is in its catalogue); ew_slot[k] = caller input
   // slot of canonical input k.  The interpreter program stays as the fallback for pointers or sizes
   // off the 16-byte rules.
+  // dense column sum (reduce over rows of a plain tensor read through a swap): hand-written kernel
+  bool cs_dense = false;
+  unsigned cs_batch = 1, cs_M = 0, cs_N = 0, cs_slices = 1;
+  int cs_dtype = HE_F32, cs_slot = 0;
   EwMatch ew;
   int ew_slot[3] = {-1, -1, -1};
   int ew_dtype = HE_F32;
@@ -168,11 +200,32 @@ struct PointwisePlan : he_plan {
     }
     PwReduceLaunch L = rl;
     L.partials = reinterpret_cast<float*>(workspace);
-    unsigned grid = L.warp_mode ? (L.num_groups + 7) / 8 : L.num_groups * L.blocks_per_group;
+    if (cs_dense && (reinterpret_cast<uintptr_t>(inputs[cs_slot]) & 15) == 0) {
+      if (cs_slices > 1 && !workspace) HE_FAIL(HE_ERR_WORKSPACE, "pointwise launch: this plan needs a %zu-byte workspace", workspace_bytes);
+      float* dst = cs_slices > 1 ? L.partials : reinterpret_cast<float*>(outputs[L.red_out_slot[0]]);
+      HE_TRY(launch_colsum_dense(cs_dtype, inputs[cs_slot], dst, cs_batch, cs_M, cs_N, cs_slices, 256, stream));
+      last_launches = 1;
+      if (cs_slices > 1) {
+        PwFinalize F{};
+        F.num_groups = cs_batch * cs_N;
+        F.blocks_per_group = cs_slices;
+        F.n_red = 1;
+        F.red_ops[0] = HE_RED_SUM;
+        F.out[0] = reinterpret_cast<float*>(outputs[L.red_out_slot[0]]);
+        F.partials = L.partials;
+        pw_reduce_finalize_kernel<<<(F.num_groups + kPwThreads - 1) / kPwThreads, kPwThreads, 0, stream>>>(F);
+        HE_CUDA(cudaGetLastError());
+        last_launches = 2;
+      }
+      return HE_OK;
+    }
+    unsigned grid = L.warp_mode == 1 ? (L.num_groups + 7) / 8
+                    : L.warp_mode == 2 ? (L.num_groups + 31) / 32 * L.blocks_per_group
+                                       : L.num_groups * L.blocks_per_group;
     pw_reduce_kernel<<<grid, kPwThreads, 0, stream>>>(P, L);
     HE_CUDA(cudaGetLastError());
     last_launches = 1;
-    if (!L.warp_mode && L.blocks_per_group > 1) {
+    if (L.warp_mode != 1 && L.blocks_per_group > 1) {
       PwFinalize F{};
       F.num_groups = L.num_groups;
       F.blocks_per_group = L.blocks_per_group;
@@ -347,7 +400,21 @@ bool match_affine_permute(const Graph& g, const PwCompiled& c, AffineFunctor* f,
 
 }  // namespace
 
-int32_t plan_pointwise(he_ctx* ctx, const Graph& g, he_plan** out, int* tier_only) {
+// A reshape of a reduction result as a leaf (helium's bias gradient ends in `.reshape([n])`,
+// tensor.rs:139) writes the same bytes as the reduction itself: the leaf becomes the reduction.
+static Graph peel_reshaped_reduction_leaves(const Graph& g) {
+  Graph o = g;
+  for (int& leaf : o.outputs) {
+    const he_node& L = o.nodes[leaf];
+    if (L.kind != HE_OP_RESHAPE || L.in[0] < 0) continue;
+    const he_node& R = o.nodes[L.in[0]];
+    if (R.kind == HE_OP_REDUCE && num_elements(R) == num_elements(L)) leaf = L.in[0];
+  }
+  return o;
+}
+
+int32_t plan_pointwise(he_ctx* ctx, const Graph& g_in, he_plan** out, int* tier_only) {
+  const Graph g = peel_reshaped_reduction_leaves(g_in);
   for (const he_node& n : g.nodes)
     if (n.kind == HE_OP_MATMUL) HE_FAIL(HE_ERR_UNSUPPORTED, "pointwise: subgraph contains a matmul");
   PointwisePlan* plan = new PointwisePlan();
@@ -429,7 +496,62 @@ int32_t plan_pointwise(he_ctx* ctx, const Graph& g, he_plan** out, int* tier_onl
     // go: a thread that walks 8-16 elements of a fused prologue serially pays a dependent memory
     // latency per element, which made 2560-element reductions take 30 us.
     const bool small = (uint64_t)L.num_groups * P.group_size <= (1u << 21);
-    if (P.group_size <= (small ? 32u : 2048u)) {
+    // Does the largest tensor walk memory contiguously along the GROUPS rather than along the
+    // elements of a group?  (the reduce input is a transposing view of it)
+    bool column = false;
+    {
+      const PwLoadInfo* big = nullptr;
+      for (const PwLoadInfo& li : plan->c.loads)
+        if (!big || num_elements(g.nodes[li.node]) > num_elements(g.nodes[big->node])) big = &li;
+      int gdim = plan->c.iter_rank - 1;   // last dim that indexes groups
+      int64_t prod = 1;
+      while (gdim >= 0 && prod < (int64_t)P.group_size) prod *= plan->c.iter_shape[gdim--];
+      while (gdim > 0 && plan->c.iter_shape[gdim] == 1) --gdim;
+      if (big && big->single_view && !big->identity && gdim >= 0 && prod == (int64_t)P.group_size && P.group_size > 1 &&
+          L.num_groups >= 32 && big->iter_stride[gdim] == 1 && big->iter_stride[plan->c.iter_rank - 1] > 1)
+        column = true;
+    }
+    if (column) {
+      L.warp_mode = 2;
+      uint32_t chunk = small ? 64 : 256;   // elements of a group per CTA: 8 / 32 per lane
+      chunk = std::min<uint32_t>(chunk, (P.group_size + 7) / 8 * 8);
+      uint32_t bpg = (P.group_size + chunk - 1) / chunk;
+      const uint64_t gblocks = (L.num_groups + 31) / 32, max_ctas = (uint64_t)ctx_sm_count(ctx) * 64;
+      if (bpg * gblocks > max_ctas) {
+        bpg = (uint32_t)std::max<uint64_t>(1, max_ctas / gblocks);
+        chunk = (P.group_size + bpg - 1) / bpg;
+        chunk = (chunk + 7) / 8 * 8;
+        bpg = (P.group_size + chunk - 1) / chunk;
+      }
+      L.blocks_per_group = bpg;
+      L.chunk = chunk;
+      if (bpg > 1) plan->workspace_bytes = (size_t)P.n_reductions * L.num_groups * bpg * sizeof(float);
+      // the plain case -- one tensor, no prologue, Sum over its rows -- has a kernel of its own
+      const PwLoadInfo& li = plan->c.loads[0];
+      const he_node& xn = g.nodes[li.node];
+      const int rk = plan->c.iter_rank;
+      if (plan->c.loads.size() == 1 && P.n_instr == 2 && P.n_reductions == 1 && L.red_ops[0] == HE_RED_SUM && rk >= 2 &&
+          (xn.dtype == HE_F32 || xn.dtype == HE_BF16 || xn.dtype == HE_F16) && num_elements(xn) == (int64_t)P.n_elems) {
+        const int64_t N = plan->c.iter_shape[rk - 2], M = plan->c.iter_shape[rk - 1];
+        bool ok = (int64_t)P.group_size == M && li.iter_stride[rk - 1] == N && li.iter_stride[rk - 2] == 1 &&
+                  N % (xn.dtype == HE_F32 ? 4 : 8) == 0;
+        int64_t expect = M * N, batch = 1;
+        for (int k = rk - 3; k >= 0; --k) {
+          if (plan->c.iter_shape[k] != 1 && li.iter_stride[k] != expect) ok = false;
+          expect *= plan->c.iter_shape[k];
+          batch *= plan->c.iter_shape[k];
+        }
+        if (ok && batch <= 65535) {
+          plan->cs_dense = true;
+          plan->cs_batch = (unsigned)batch; plan->cs_M = (unsigned)M; plan->cs_N = (unsigned)N;
+          plan->cs_slices = (unsigned)((M + 255) / 256);
+          plan->cs_dtype = xn.dtype;
+          plan->cs_slot = li.input_slot;
+          if (plan->cs_slices > 1)
+            plan->workspace_bytes = std::max(plan->workspace_bytes, (size_t)batch * N * plan->cs_slices * sizeof(float));
+        }
+      }
+    } else if (P.group_size <= (small ? 32u : 2048u)) {
       L.warp_mode = 1;
       L.blocks_per_group = 1;
       L.chunk = P.group_size;
@@ -449,8 +571,12 @@ int32_t plan_pointwise(he_ctx* ctx, const Graph& g, he_plan** out, int* tier_onl
       L.chunk = chunk;
       if (bpg > 1) plan->workspace_bytes = (size_t)P.n_reductions * L.num_groups * bpg * sizeof(float);
     }
+    if (plan->cs_dense)
+      snprintf(desc, sizeof desc, "pointwise tier 2 (dense column-sum kernel, [%u x %u x %u], %u row slices; column-mode interpreter for unaligned tensors)",
+               plan->cs_batch, plan->cs_M, plan->cs_N, plan->cs_slices);
+    else
     snprintf(desc, sizeof desc, "pointwise tier 1 (interpreter, %d instr, %d regs), reduce: %u groups of %u, %s, %u CTAs/group",
-             P.n_instr, plan->c.n_regs, L.num_groups, P.group_size, L.warp_mode ? "warp per group" : "CTA slices", L.blocks_per_group);
+             P.n_instr, plan->c.n_regs, L.num_groups, P.group_size, L.warp_mode == 1 ? "warp per group" : L.warp_mode == 2 ? "column mode (lane per group)" : "CTA slices", L.blocks_per_group);
   } else if (plan->ew.kind >= 0) {
     snprintf(desc, sizeof desc, "pointwise tier 2 (dense elementwise kernel %s, 16-byte vectors; interpreter fallback for unaligned tensors)",
              plan->ew.name);

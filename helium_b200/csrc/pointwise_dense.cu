@@ -164,6 +164,68 @@ bool match_dense_elementwise(const std::string& canon_text, EwMatch* m) {
   return false;
 }
 
+namespace {
+// Column sums of a dense [batch, M, N] tensor: out[b, n] = sum_m x[b, m, n] -- what helium's bias
+// gradient (swap_dims -> reduce_sum -> reshape, tensor.rs:83-142) computes when its operand is a
+// plain tensor.  A thread owns 16 bytes of consecutive columns and walks rows ty, ty + 8, ... of its
+// slice, so every warp load is one contiguous 512-byte run; the eight row lanes meet in shared
+// memory; one partial per (column, slice), folded by the generic finalize kernel in slice order.
+struct ColsumParams {
+  const void* x;
+  float* out;        // [batch * N] when slices == 1, else partials [(b * N + n) * slices + slice]
+  unsigned M, N, batch, rows_per_slice, slices;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(256) colsum_dense_kernel(const __grid_constant__ ColsumParams p) {
+  using V = EwVec<T>;
+  constexpr int VE = V::kElems;
+  __shared__ float part[8][32][VE + 1];
+  const unsigned tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const unsigned col0 = (blockIdx.x * 32 + tx) * VE, slice = blockIdx.y, b = blockIdx.z;
+  float acc[VE];
+#pragma unroll
+  for (int e = 0; e < VE; ++e) acc[e] = 0.0f;
+  if (col0 < p.N) {
+    const unsigned r_end = min(p.M, (slice + 1) * p.rows_per_slice);
+    const T* base = reinterpret_cast<const T*>(p.x) + ((size_t)b * p.M) * p.N + col0;
+    for (unsigned r = slice * p.rows_per_slice + ty; r < r_end; r += 8) {
+      float v[VE];
+      V::unpack(__ldcs(reinterpret_cast<const uint4*>(base + (size_t)r * p.N)), v);
+#pragma unroll
+      for (int e = 0; e < VE; ++e) acc[e] += v[e];
+    }
+  }
+#pragma unroll
+  for (int e = 0; e < VE; ++e) part[ty][tx][e] = acc[e];
+  __syncthreads();
+  if (ty == 0 && col0 < p.N) {
+#pragma unroll
+    for (int e = 0; e < VE; ++e) {
+      float v = part[0][tx][e];
+#pragma unroll
+      for (int w = 1; w < 8; ++w) v += part[w][tx][e];
+      const size_t group = (size_t)b * p.N + col0 + e;
+      if (p.slices == 1) p.out[group] = v;
+      else p.out[group * p.slices + slice] = v;
+    }
+  }
+}
+}  // namespace
+
+int32_t launch_colsum_dense(int dtype, const void* x, float* out_or_partials, unsigned batch, unsigned M, unsigned N,
+                            unsigned slices, unsigned rows_per_slice, cudaStream_t stream) {
+  const unsigned ve = dtype == HE_F32 ? 4 : 8;
+  ColsumParams p{x, out_or_partials, M, N, batch, rows_per_slice, slices};
+  dim3 grid((N / ve + 31) / 32, slices, batch);
+  if (grid.y > 65535 || grid.z > 65535) HE_FAIL(HE_ERR_UNSUPPORTED, "dense column sum: shape too large");
+  if (dtype == HE_F32) colsum_dense_kernel<float><<<grid, 256, 0, stream>>>(p);
+  else if (dtype == HE_BF16) colsum_dense_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(p);
+  else colsum_dense_kernel<__half><<<grid, 256, 0, stream>>>(p);
+  HE_CUDA(cudaGetLastError());
+  return HE_OK;
+}
+
 int32_t launch_dense_elementwise(int kind, int dtype, const void* const* in, void* out, unsigned long long n_elems, float k,
                                  int sm_count, cudaStream_t stream) {
   const int ve = dtype == HE_F32 ? 4 : 8;

@@ -25,4 +25,9 @@ bool match_dense_elementwise(const std::string& canon_text, EwMatch* m);
 int32_t launch_dense_elementwise(int kind, int dtype, const void* const* in, void* out, unsigned long long n_elems, float k,
                                  int sm_count, cudaStream_t stream);
 
+// out[b, n] = sum_m x[b, m, n] for a dense tensor (N a multiple of the 16-byte vector width, x
+// 16-byte aligned).  With slices > 1 the kernel writes partials [(b * N + n) * slices + slice].
+int32_t launch_colsum_dense(int dtype, const void* x, float* out_or_partials, unsigned batch, unsigned M, unsigned N,
+                            unsigned slices, unsigned rows_per_slice, cudaStream_t stream);
+
 }  // namespace he

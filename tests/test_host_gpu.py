@@ -83,3 +83,29 @@ def test_readme_graph_through_the_host_runtime(ctx):
         node = g.nodes[o]
         tol = 1e-5 if node.dtype == ir.F32 else 1e-2
         assert O.rel_l2(O.decode(a, node.dtype, node.shape), O.decode(b, node.dtype, node.shape)) <= tol
+
+
+def test_mlp_block_training_graph_through_the_host_runtime(ctx):
+    """configs[3] recorded helium-style as ONE op graph (casts after every matmul, explicit transposes,
+    swap_dims -> reduce -> reshape bias gradients): the planner must arrive at six fused matmuls
+    (bias gradient of the first layer inside its GEMM) plus one column-mode reduction, and the
+    numbers must match the oracle with the three materialised activations rounded to bf16."""
+    # at the benchmark size (planning only): transposes above 10^6 elements would be PermuteDims
+    # instructions (cuda.rs:38) if they did not fold into the GEMMs and the reduction
+    text = hb.HostGraph(configs.graph_mlp_block_train(8192, 4096, 16384)).plan_text()
+    lines = [ln for ln in text.splitlines() if "tier=" in ln]
+    assert sum("FusedMatmul tier=2" in ln for ln in lines) == 6 and len(lines) == 7, text
+    assert not any("PermuteDims" in ln for ln in lines), text
+    # executed at a small size (below the threshold the planner may group the pointwise ops differently)
+    T, d, ff = 256, 128, 256
+    g, nodes = configs.graph_mlp_block_train(T, d, ff, return_nodes=True)
+    lines = [ln for ln in hb.HostGraph(g).plan_text().splitlines() if "tier=" in ln]
+    assert sum("FusedMatmul tier=2" in ln for ln in lines) == 6
+    r = configs.rng(5)
+    ins = [configs.bf16_normal(r, (T, d)), configs.bf16_normal(r, (d, ff), 0.05), configs.bf16_normal(r, (ff,), 0.05),
+           configs.bf16_normal(r, (ff, d), 0.05), configs.bf16_normal(r, (d,), 0.05), configs.bf16_normal(r, (T, d))]
+    want = O.evaluate(g, ins, round_nodes=list(nodes.values()))
+    got, ex = _run_graph(ctx, g, ins, capture=True, repeats=2)
+    for o, a, b in zip(g.outputs, got, want):
+        node = g.nodes[o]
+        assert O.rel_l2(O.decode(a, node.dtype, node.shape), O.decode(b, node.dtype, node.shape)) <= 1e-2, o
