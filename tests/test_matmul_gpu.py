@@ -366,3 +366,39 @@ def test_helium_style_bias_gradient_fuses(ctx):
     # through the host runtime the three ops (matmul, gate, bias-gradient chain) become one instruction
     text = hb.HostGraph(g).plan_text()
     assert sum("FusedMatmul" in ln for ln in text.splitlines()) == 1 and "Pointwise" not in text and "Permute" not in text, text
+
+
+def _random_linear_case(r):
+    """One random fused-linear configuration within what graph_linear can express."""
+    pick = lambda xs: xs[int(r.integers(0, len(xs)))]
+    m = int(pick([8, 72, 128, 200, 256, 392, 520, 1024, 2304]))
+    n = int(pick([8, 40, 128, 264, 512, 776, 1280]))
+    k = int(pick([8, 64, 136, 320, 1024]))
+    kw = dict(bias=bool(r.integers(0, 2)), a_t=bool(r.integers(0, 2)), b_t=bool(r.integers(0, 2)))
+    kw["act"] = pick([None, ir.UN_RELU, ir.UN_GELU, ir.UN_TANH])
+    kw["resid"] = bool(r.integers(0, 2))
+    kw["gate"] = pick([None, None, "mul", "dgelu", "drelu"])
+    kw["store_z"] = bool(r.integers(0, 2)) and kw["act"] is not None
+    kw["colsum"] = pick([None, None, "y", "resid" if kw["resid"] else None])
+    kw["batch"] = pick([None, None, 2, 3])
+    kw["dtype"] = pick([ir.BF16, ir.BF16, ir.F16])
+    kw["out_dtype"] = pick([None, ir.F32])
+    return m, n, k, kw
+
+
+@pytest.mark.parametrize("seed", range(24))
+def test_random_fused_linear_configurations(ctx, seed):
+    """Seeded sweep over shapes (ragged, batched, tiny), operand majors, dtypes and epilogue pieces:
+    whatever tier the planner picks, the numbers must be the oracle's."""
+    r = rng(1000 + seed)
+    m, n, k, kw = _random_linear_case(r)
+    g = graph_linear(m, n, k, **kw)
+    ins = _gen(g, 2000 + seed, {1: 1.0 / np.sqrt(k)})
+    try:
+        plan = hb.Plan.fused_matmul(ctx, g)
+    except hb.HeliumError as e:
+        # the only legitimate refusals: shapes off the TMA pitch rules with an epilogue beyond the SIMT kernel
+        assert "multiples of 8" in str(e) or "SIMT" in str(e), str(e)
+        pytest.skip(f"refused as documented: {e}")
+    got, plan = _run(ctx, g, ins)
+    _compare(g, got, O.evaluate(g, ins), f"{(m, n, k, kw)}: {plan.description}")

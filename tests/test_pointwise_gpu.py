@@ -223,3 +223,57 @@ def test_dense_column_sum_kernel(ctx, shape, dtype):
     plan.launch_ptrs([shifted.data_ptr()], [out2.data_ptr()], (ws.data_ptr() + 255) // 256 * 256)
     torch.cuda.synchronize()
     assert O.rel_l2(out2.cpu().numpy().reshape(-1).astype(np.float64), want) <= 1e-5
+
+
+def _random_pointwise_graph(r):
+    """A random pointwise DAG over a 3-D iteration space: broadcasts of lower-rank inputs, swaps, casts,
+    unary / binary / compare / select nodes, then either a store or a trailing reduction."""
+    pick = lambda xs: xs[int(r.integers(0, len(xs)))]
+    shape = [int(pick([1, 2, 3, 5, 8, 16, 33])) for _ in range(3)]
+    g = ir.Graph()
+    dts = [ir.F32, ir.BF16, ir.F16]
+    vals = []
+    for _ in range(int(r.integers(1, 4))):
+        form = int(r.integers(0, 4))
+        dt = pick(dts)
+        if form == 0:
+            vals.append(g.new_input(shape, dt))
+        elif form == 1:      # row vector broadcast over the leading dims
+            vals.append(g.broadcast_to(g.new_input([shape[2]], dt), shape))
+        elif form == 2:      # tensor stored with its last two dims swapped
+            vals.append(g.swap_dims(g.new_input([shape[0], shape[2], shape[1]], dt), 1, 2))
+        else:                # column vector [s1, 1] broadcast along the last dim
+            vals.append(g.broadcast_to(g.new_input([shape[1], 1], dt), shape))
+    for _ in range(int(r.integers(2, 9))):
+        kind = int(r.integers(0, 6))
+        a = pick(vals)
+        if kind <= 1:
+            vals.append(g.unary(pick([ir.UN_RELU, ir.UN_NEG, ir.UN_TANH, ir.UN_SIGMOID, ir.UN_SIN, ir.UN_COS]), a))
+        elif kind <= 3:
+            vals.append(g.binary(pick([ir.BIN_ADD, ir.BIN_MUL, ir.BIN_MIN, ir.BIN_MAX, ir.BIN_SUB]), a, pick(vals)))
+        elif kind == 4:
+            vals.append(g.cast(a, pick(dts)))
+        else:
+            c = g.compare(pick([ir.CMP_LT, ir.CMP_GE, ir.CMP_NE]), a, pick(vals))
+            vals.append(g.select(a, pick(vals), c))
+    out = vals[-1]
+    tail = int(r.integers(0, 4))
+    if tail == 0:
+        out = g.reduce(pick([ir.RED_SUM, ir.RED_MAX, ir.RED_MIN, ir.RED_MEAN]), out, int(r.integers(1, 4)))
+    elif tail == 1:
+        out = g.swap_dims(out, 0, 2)
+    g.new_output(out)
+    return g
+
+
+@pytest.mark.parametrize("seed", range(40))
+def test_random_pointwise_graphs(ctx, seed):
+    r = rng(3000 + seed)
+    g = _random_pointwise_graph(r)
+    ins = [O.encode(r.standard_normal(g.nodes[i].shape), g.nodes[i].dtype) for i in g.inputs]
+    got, plan = _run(ctx, g, ins)
+    want = O.evaluate(g, ins)
+    node = g.nodes[g.outputs[0]]
+    a, b = O.decode(got[0], node.dtype, node.shape).reshape(-1), O.decode(want[0], node.dtype, node.shape).reshape(-1)
+    tol = 1e-5 if node.dtype == ir.F32 else 1e-2
+    assert np.allclose(a, b, rtol=tol, atol=tol), (float(np.abs(a - b).max()), plan.description)
