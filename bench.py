@@ -627,11 +627,14 @@ class WorkloadC1:
         e0.record(st); ex.run(); e1.record(st)
         record.append(("mlp_step_graph", e0, e1))
 
+    e2e_note = "one stream, no host synchronisation between steps: batch upload, graph replay and loss download are queued back to back"
+
     def step_e2e(self):
+        # every step uploads its batch and downloads its loss; the host does not wait in between
+        # (a training loop reads the loss of step i while step i+1 is already queued)
         self.x_d.copy_(self.x_pin, non_blocking=True); self.t_d.copy_(self.t_pin, non_blocking=True)
         self.step()
         self.loss_pin.copy_(self.loss_d, non_blocking=True)
-        self.torch.cuda.current_stream().synchronize()
 
     @staticmethod
     def cpu_sample(max_steps=20):
