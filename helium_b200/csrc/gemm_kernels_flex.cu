@@ -5,27 +5,31 @@ namespace he {
 
 // ---- reduction finalisers (fixed summation order => bit-stable results) --------------------------
 // out[b][n] = sum_{tm} partials[b][tm][n]
-__global__ void gemm_colsum_finalize(const float* __restrict__ partials, float* __restrict__ out, int batch, int tiles_m, int N) {
+// op: 0 sum, 1 max, 2 min; the folded value is multiplied by `scale` (1 / count for a mean)
+__device__ __forceinline__ float fold_op(int op, float a, float b) { return op == 1 ? fmaxf(a, b) : op == 2 ? fminf(a, b) : a + b; }
+__global__ void gemm_colsum_finalize(const float* __restrict__ partials, float* __restrict__ out, int batch, int tiles_m, int N, int op,
+                                     float scale) {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= batch * N) return;
   const int b = i / N, n = i - b * N;
   const float* p = partials + (size_t)b * tiles_m * N + n;
-  float s = 0.0f;
-  for (int t = 0; t < tiles_m; ++t) s += p[(size_t)t * N];
-  out[i] = s;
+  float s = p[0];
+  for (int t = 1; t < tiles_m; ++t) s = fold_op(op, s, p[(size_t)t * N]);
+  out[i] = s * scale;
 }
 // out[0] = sum_t partials[t], one CTA, tree in a fixed order
-__global__ void gemm_scalar_finalize(const float* __restrict__ partials, float* __restrict__ out, int n) {
+__global__ void gemm_scalar_finalize(const float* __restrict__ partials, float* __restrict__ out, int n, int op, float scale) {
   __shared__ float s[256];
-  float v = 0.0f;
-  for (int i = threadIdx.x; i < n; i += 256) v += partials[i];
+  const float ident = op == 1 ? -INFINITY : op == 2 ? INFINITY : 0.0f;
+  float v = ident;
+  for (int i = threadIdx.x; i < n; i += 256) v = fold_op(op, v, partials[i]);
   s[threadIdx.x] = v;
   __syncthreads();
   for (int off = 128; off > 0; off >>= 1) {
-    if ((int)threadIdx.x < off) s[threadIdx.x] += s[threadIdx.x + off];
+    if ((int)threadIdx.x < off) s[threadIdx.x] = fold_op(op, s[threadIdx.x], s[threadIdx.x + off]);
     __syncthreads();
   }
-  if (threadIdx.x == 0) out[0] = s[0];
+  if (threadIdx.x == 0) out[0] = s[0] * scale;
 }
 
 int32_t launch_gemm_flex(const GemmLaunchCfg& cfg, const GemmParams<EpiFlexParams>& p, cudaStream_t stream) {
@@ -42,15 +46,15 @@ int32_t launch_gemm_flex(const GemmLaunchCfg& cfg, const GemmParams<EpiFlexParam
   HE_FAIL(HE_ERR_UNSUPPORTED, "fused matmul: no kernel compiled for bn=%d mainloop=%d with this epilogue", cfg.bn, cfg.ml);
 }
 
-int32_t launch_colsum_finalize(const float* partials, float* out, int batch, int tiles_m, int N, cudaStream_t stream) {
+int32_t launch_colsum_finalize(const float* partials, float* out, int batch, int tiles_m, int N, cudaStream_t stream, int op, float scale) {
   const int n = batch * N;
-  gemm_colsum_finalize<<<(n + 255) / 256, 256, 0, stream>>>(partials, out, batch, tiles_m, N);
+  gemm_colsum_finalize<<<(n + 255) / 256, 256, 0, stream>>>(partials, out, batch, tiles_m, N, op, scale);
   HE_CUDA(cudaGetLastError());
   return HE_OK;
 }
 
-int32_t launch_scalar_finalize(const float* partials, float* out, int n, cudaStream_t stream) {
-  gemm_scalar_finalize<<<1, 256, 0, stream>>>(partials, out, n);
+int32_t launch_scalar_finalize(const float* partials, float* out, int n, cudaStream_t stream, int op, float scale) {
+  gemm_scalar_finalize<<<1, 256, 0, stream>>>(partials, out, n, op, scale);
   HE_CUDA(cudaGetLastError());
   return HE_OK;
 }

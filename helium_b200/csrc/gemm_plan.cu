@@ -376,6 +376,8 @@ struct MatmulPlan : he_plan {
   // Program (interpreted epilogue) and its reductions: kind 0 columns, 1 rows, 2 scalar
   PwCompiled prog;
   int pr_n_red = 0, pr_kind[4] = {0, 0, 0, 0}, pr_out[4] = {-1, -1, -1, -1}, pr_fold_batch[4] = {0, 0, 0, 0};
+  int pr_op[4] = {0, 0, 0, 0};               // 0 sum, 1 max, 2 min
+  float pr_scale[4] = {1.f, 1.f, 1.f, 1.f};  // 1 / count for a mean
   size_t pr_off[4] = {0, 0, 0, 0};   // workspace offsets in floats
   int pr_n_col = 0, pr_col_slot[2] = {0, 0}, pr_row_slots = 0;
   int n_inputs = 0, n_outputs = 0;
@@ -490,6 +492,7 @@ struct MatmulPlan : he_plan {
     p.epi.rows_total = c.batch * c.M;
     for (int s = 0; s < 4; ++s) {
       p.epi.red_kind[s] = pr_kind[s];
+      p.epi.red_op[s] = pr_op[s];
       p.epi.red_partials[s] = s < pr_n_red ? ws + pr_off[s] : nullptr;
     }
     HE_TRY(launch_gemm_program(cfg, p, stream));
@@ -498,12 +501,12 @@ struct MatmulPlan : he_plan {
       float* dst = reinterpret_cast<float*>(outputs[pr_out[s]]);
       if (pr_kind[s] == 0) {
         // [batch][tile_m][N] partials; folding the batch in just lengthens the tile axis
-        if (pr_fold_batch[s]) HE_TRY(launch_colsum_finalize(ws + pr_off[s], dst, 1, c.batch * c.tiles_m, c.N, stream));
-        else HE_TRY(launch_colsum_finalize(ws + pr_off[s], dst, c.batch, c.tiles_m, c.N, stream));
+        if (pr_fold_batch[s]) HE_TRY(launch_colsum_finalize(ws + pr_off[s], dst, 1, c.batch * c.tiles_m, c.N, stream, pr_op[s], pr_scale[s]));
+        else HE_TRY(launch_colsum_finalize(ws + pr_off[s], dst, c.batch, c.tiles_m, c.N, stream, pr_op[s], pr_scale[s]));
       } else if (pr_kind[s] == 1) {
-        HE_TRY(launch_colsum_finalize(ws + pr_off[s], dst, 1, pr_row_slots, c.batch * c.M, stream));   // [slot][batch * M]
+        HE_TRY(launch_colsum_finalize(ws + pr_off[s], dst, 1, pr_row_slots, c.batch * c.M, stream, pr_op[s], pr_scale[s]));   // [slot][batch * M]
       } else {
-        HE_TRY(launch_scalar_finalize(ws + pr_off[s], dst, c.num_tiles, stream));
+        HE_TRY(launch_scalar_finalize(ws + pr_off[s], dst, c.num_tiles, stream, pr_op[s], pr_scale[s]));
       }
       ++last_launches;
     }
@@ -961,8 +964,6 @@ int32_t plan_fused_matmul_core(he_ctx* ctx, const Graph& g, he_plan** out, int* 
     for (int i = 0; i < EP.n_instr; ++i) {
       const PwInstr& in = EP.instr[i];
       if (in.op != PW_REDUCE) continue;
-      if (in.sub != HE_RED_SUM)
-        HE_FAIL(HE_ERR_UNSUPPORTED, "fused matmul: the generic epilogue reduces with Sum only (the playground's ReductionOp)");
       const int s = in.slot2;
       const uint32_t m = in.imm;
       int kind;
@@ -980,6 +981,16 @@ int32_t plan_fused_matmul_core(he_ctx* ctx, const Graph& g, he_plan** out, int* 
       }
       plan->pr_kind[s] = kind;
       plan->pr_out[s] = in.slot;
+      plan->pr_op[s] = in.sub == HE_RED_MAX ? 1 : in.sub == HE_RED_MIN ? 2 : 0;
+      if (plan->pr_op[s] != 0 && kind == 0)
+        HE_FAIL(HE_ERR_UNSUPPORTED, "fused matmul: Max / Min over the rows of the tile are not implemented in the generic epilogue (Sum and Mean are)");
+      if (in.sub == HE_RED_MEAN) {
+        double count = 1.0;
+        if (m & 1u) count *= c.N;
+        if (m & 2u) count *= c.M;
+        if (m & 4u) count *= c.batch;
+        plan->pr_scale[s] = (float)(1.0 / count);
+      }
       if (kind == 0) {
         if (plan->pr_n_col == 2) HE_FAIL(HE_ERR_UNSUPPORTED, "fused matmul: at most two column reductions in the generic epilogue");
         plan->pr_col_slot[plan->pr_n_col++] = s;

@@ -18,8 +18,9 @@ struct GemmLaunchCfg {
 int32_t launch_gemm_flex(const GemmLaunchCfg& cfg, const GemmParams<EpiFlexParams>& p, cudaStream_t stream);
 int32_t launch_gemm_c3(const GemmLaunchCfg& cfg, const GemmParams<EpiC3Params>& p, cudaStream_t stream);
 int32_t launch_gemm_program(const GemmLaunchCfg& cfg, const GemmParams<EpiProgramParams>& p, cudaStream_t stream);
-int32_t launch_colsum_finalize(const float* partials, float* out, int batch, int tiles_m, int N, cudaStream_t stream);
-int32_t launch_scalar_finalize(const float* partials, float* out, int n, cudaStream_t stream);
+int32_t launch_colsum_finalize(const float* partials, float* out, int batch, int tiles_m, int N, cudaStream_t stream, int op = 0,
+                               float scale = 1.0f);
+int32_t launch_scalar_finalize(const float* partials, float* out, int n, cudaStream_t stream, int op = 0, float scale = 1.0f);
 // SIMT matmul: f32 operands, or 2-byte operands whose shapes break the TMA alignment rules
 int32_t launch_sgemm(const void* a, const void* b, void* c, int in_dt, int out_dt, int batch, int M, int N, int K,
                      bool a_mn, bool b_mn, const void* bias, int bias_dt, int act, cudaStream_t stream);

@@ -217,7 +217,7 @@ struct EpiFlex {
   static constexpr int kColReductions = 1;
   static constexpr int kChunk = 32;
   struct State {};
-  __device__ static void tile_begin(State&) {}
+  __device__ static void tile_begin(const Params&, State&) {}
   // The op selectors are uniform per launch: switch once per chunk, not once per element.
   __device__ static void activate(int act, float (&v)[kChunk]) {
     switch (act) {
@@ -317,7 +317,7 @@ struct EpiC3 {
   static constexpr int kColReductions = 2;
   static constexpr int kChunk = 16;
   struct State { float loss; };
-  __device__ static void tile_begin(State& s) { s.loss = 0.0f; }
+  __device__ static void tile_begin(const Params&, State& s) { s.loss = 0.0f; }
   __device__ static void chunk(const Params& p, const EpiEnv& env, const TileInfo& t, State& st, int row, int col, float (&v)[kChunk]) {
     const GemmCore& c = *env.core;
     const int grow = t.m0 + row, gcol = t.n0 + col;
@@ -426,6 +426,7 @@ struct EpiProgramParams {
   PwProgram prog;  // by value: lives in the kernel parameter block (constant bank)
   int n_red;             // reductions of the program (PwInstr::slot2 numbers them)
   int red_kind[4];       // per reduction slot: 0 columns, 1 rows, 2 scalar
+  int red_op[4];         // 0 sum (also mean: scaled by the fold), 1 max, 2 min (kinds 1 and 2 only)
   float* red_partials[4];
   int n_col;             // kind-0 reductions (at most kColReductions)
   int col_slot[2];       // their reduction slots
@@ -436,9 +437,9 @@ struct EpiProgram {
   static constexpr int kColReductions = 2;
   static constexpr int kChunk = 32;
   struct State { float red[4]; };
-  __device__ static void tile_begin(State& s) {
+  __device__ static void tile_begin(const Params& p, State& s) {
 #pragma unroll
-    for (int i = 0; i < 4; ++i) s.red[i] = 0.0f;
+    for (int i = 0; i < 4; ++i) s.red[i] = p.red_op[i] == 1 ? -INFINITY : p.red_op[i] == 2 ? INFINITY : 0.0f;
   }
   __device__ static void chunk(const Params& p, const EpiEnv& env, const TileInfo& t, State& st, int row, int col, float (&v)[kChunk]) {
     const GemmCore& c = *env.core;
@@ -513,12 +514,17 @@ struct EpiProgram {
           const int slot0 = (t.n0 + col_begin) / 64;
           const size_t r = (size_t)t.b * c.M + grow;
           for (int k = 0; k < cols_per_warp / 64; ++k)
-            p.red_partials[s][(size_t)(slot0 + k) * p.rows_total + r] = k == 0 ? st.red[s] : 0.0f;
+            p.red_partials[s][(size_t)(slot0 + k) * p.rows_total + r] =
+                k == 0 ? st.red[s] : (p.red_op[s] == 1 ? -INFINITY : p.red_op[s] == 2 ? INFINITY : 0.0f);
         }
       } else if (p.red_kind[s] == 2) {
         float l = st.red[s];
+        const int op = p.red_op[s];
 #pragma unroll
-        for (int off = 16; off > 0; off >>= 1) l += __shfl_down_sync(0xffffffffu, l, off);
+        for (int off = 16; off > 0; off >>= 1) {
+          const float o = __shfl_down_sync(0xffffffffu, l, off);
+          l = op == 1 ? fmaxf(l, o) : op == 2 ? fminf(l, o) : l + o;
+        }
         if (lane == 0) scal[s * n_warps + env.epi_warp] = l;
         any_scalar = true;
       }
@@ -533,8 +539,12 @@ struct EpiProgram {
       if (env.epi_tid == 0) {
         for (int s = 0; s < p.n_red; ++s)
           if (p.red_kind[s] == 2) {
-            float tot = 0.0f;
-            for (int w = 0; w < n_warps; ++w) tot += scal[s * n_warps + w];
+            const int op = p.red_op[s];
+            float tot = scal[s * n_warps];
+            for (int w = 1; w < n_warps; ++w) {
+              const float o = scal[s * n_warps + w];
+              tot = op == 1 ? fmaxf(tot, o) : op == 2 ? fminf(tot, o) : tot + o;
+            }
             p.red_partials[s][t.tile_idx] = tot;
           }
       }
@@ -761,7 +771,7 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmParams<typename Epi::Params> p) 
       if (!dead && !ptx::mbar_wait(bar_tmem_full(acc), acc_phase, abort_flag, c.status, 4, acc)) dead = true;
       dead = __any_sync(0xffffffffu, dead);   // the warp decides together (it shares a __syncwarp below)
       typename Epi::State st;
-      Epi::tile_begin(st);
+      Epi::tile_begin(p.epi, st);
       if (!dead) {
         ptx::tcgen05_fence_after();
         const int row = env.quadrant * 32 + lane;

@@ -297,7 +297,7 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ GemmParams<typename Epi::Params
       if (!dead && !ptx::mbar_wait(bar_tmem_full(acc), acc_phase, abort_flag, c.status, 4, acc)) dead = true;
       dead = __any_sync(0xffffffffu, dead);   // the warp decides together (it shares a __syncwarp below)
       typename Epi::State st;
-      Epi::tile_begin(st);
+      Epi::tile_begin(p.epi, st);
       if (!dead) {
         ptx::tcgen05_fence_after();
         const int row = env.quadrant * 32 + lane;

@@ -398,7 +398,7 @@ int32_t compile_pointwise(const Graph& g, const PwCompileOptions& opt, PwCompile
     if (L.kind == HE_OP_REDUCE) {
       int v = c.eval(L.in[0], ident);
       if (c.status != HE_OK) return c.status;
-      if (L.sub_op == HE_RED_MEAN) {
+      if (L.sub_op == HE_RED_MEAN && !opt.epilogue) {   // a fused-matmul epilogue scales when it folds its partials
         PwInstr ms{};
         ms.op = PW_MEAN_SCALE;
         v = c.emit(ms, v);

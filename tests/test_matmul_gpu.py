@@ -315,8 +315,30 @@ def test_generic_epilogue_reduction_limits(ctx):
     a = g.new_input([256, 64], ir.BF16); b = g.new_input([64, 256], ir.BF16)
     y = g.unary(ir.UN_EXP, g.matmul(a, b, ir.PREC_BF16_F32))
     g.new_output(g.reduce_axes(ir.RED_MAX, y, [0]))
-    with pytest.raises(hb.HeliumError, match="Sum only"):
+    with pytest.raises(hb.HeliumError, match="Max / Min over the rows"):
         hb.Plan.fused_matmul(ctx, g)
+
+
+@pytest.mark.parametrize("m,n,k", [(256, 512, 128), (200, 264, 72), (4096, 4096, 64)])
+def test_generic_epilogue_mean_max_min(ctx, m, n, k):
+    """Mean over rows / columns / everything (Sum scaled when the partials are folded) and Max / Min over
+    columns and over everything (running extrema per thread, op-aware folds)."""
+    g = ir.Graph()
+    a = g.new_input([m, k], ir.BF16); b = g.new_input([k, n], ir.BF16)
+    y = g.unary(ir.UN_TANH, g.matmul(a, b, ir.PREC_BF16_F32))
+    g.new_output(g.reduce_axes(ir.RED_MEAN, y, [0]))          # [1, n]
+    g.new_output(g.reduce_axes(ir.RED_MAX, y, [1]))           # [m, 1]
+    g.new_output(g.reduce_axes(ir.RED_MIN, y, [0, 1]))        # [1, 1]
+    g.new_output(g.reduce_axes(ir.RED_MEAN, g.binary(ir.BIN_MUL, y, y), [0, 1]))
+    ins = _gen(g, 81, {1: 1.0 / np.sqrt(k)})
+    got, plan = _run(ctx, g, ins)
+    assert "4 reductions" in plan.description
+    want = O.evaluate(g, ins)
+    for o, x, w in zip(g.outputs, got, want):
+        node = g.nodes[o]
+        x, w = np.asarray(x, dtype=np.float64).reshape(-1), np.asarray(w, dtype=np.float64).reshape(-1)
+        # extrema of a bf16-operand matmul are exact picks of values that carry the GEMM's rounding: 1e-5 relative to their scale
+        assert np.allclose(x, w, rtol=2e-5, atol=2e-5), (node.shape, float(np.abs(x - w).max()))
 
 
 def test_operand_side_pointwise_prologues(ctx):
