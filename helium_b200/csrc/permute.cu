@@ -215,6 +215,25 @@ __global__ void __launch_bounds__(kThreads) permute_tile_vec(const __grid_consta
 
   // A CTA walks p.xt consecutive X tiles of the same (Y tile, batch): block decode and parameter
   // staging above are paid once (with parameters along X the host keeps p.xt at 1).
+  // With a compile-time tile shape the input vectors of the NEXT X tile are fetched into registers
+  // before the current tile's transposed stores start, so a CTA always has loads in flight.
+  // (2-byte instantiations only: they carry 2-4 vectors per thread; the 4-byte ones would pay 16
+  // more registers, which costs the streaming permutations more occupancy than the overlap returns)
+  constexpr bool kPrefetch = kFixed && EB == 2;
+  constexpr int NV = kPrefetch ? (TY_C * (TXW_C / 4)) / kThreads : 1;   // 16-byte vectors per thread per tile
+  constexpr int kLgCx = kFixed ? ilog2_c(TXW_C / 4) : 0;
+  uint4 pre[NV];
+  auto fetch_tile = [&](long long xa) {
+    const unsigned nxa = (unsigned)min((long long)TX, p.X - xa);
+    const char* src = reinterpret_cast<const char*>(p.in) + (bo.in_base + y0 * p.in_sY + xa) * EB;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int q = threadIdx.x + i * kThreads;
+      const unsigned cx = q & ((1u << kLgCx) - 1u), y = (unsigned)q >> kLgCx;
+      if (cx * VE < nxa && y < ny) pre[i] = __ldcs(reinterpret_cast<const uint4*>(src + (size_t)(y * in_sY + cx * VE) * EB));
+    }
+  };
+  if constexpr (kPrefetch) fetch_tile(x0);
 #pragma unroll 1
   for (int xs = 0; xs < p.xt; ++xs, x0 += TX) {
   if (tx_first + xs >= p.tiles_x) break;
@@ -228,11 +247,13 @@ __global__ void __launch_bounds__(kThreads) permute_tile_vec(const __grid_consta
     const int total = TY << lg_cx;
     const float floor_v = p.relu ? 0.0f : -INFINITY;
 #pragma unroll
-    for (int q = threadIdx.x; q < total; q += kThreads) {
+    for (int q = threadIdx.x, qi = 0; q < total; q += kThreads, ++qi) {
       const unsigned cx = q & ((1u << lg_cx) - 1u), y = (unsigned)q >> lg_cx;
       const unsigned x = cx * VE;
       if (x < nx && y < ny) {
-        uint4 v = __ldcs(reinterpret_cast<const uint4*>(in_tile + (size_t)(y * in_sY + x) * EB));
+        uint4 v;
+        if constexpr (kPrefetch) v = pre[qi < NV ? qi : 0];
+        else v = __ldcs(reinterpret_cast<const uint4*>(in_tile + (size_t)(y * in_sY + x) * EB));
         if constexpr (XDT >= 0) {
           uint32_t w[4] = {v.x, v.y, v.z, v.w};
           if (p.f_mode == F_AXIS_X) {
@@ -273,6 +294,9 @@ __global__ void __launch_bounds__(kThreads) permute_tile_vec(const __grid_consta
         dst[0] = v.x; dst[1] = v.y; dst[2] = v.z; dst[3] = v.w;
       }
     }
+  }
+  if constexpr (kPrefetch) {
+    if (xs + 1 < p.xt && tx_first + xs + 1 < p.tiles_x) fetch_tile(x0 + TX);
   }
   __syncthreads();
   // ---- phase 2: shared (transposed read) -> global (vector along Y) ---------------------------
@@ -654,13 +678,14 @@ int32_t make_permute_plan(he_ctx* ctx, int rank, const int64_t* in_shape, const 
     delete plan;
     HE_FAIL(HE_ERR_UNSUPPORTED, "permute: too many tiles");
   }
-  // X tiles per CTA: as many (1, 2 or 4) as still leave at least four full waves of CTAs
+  // X tiles per CTA: as many (1, 2 or 4) as still leave at least two full waves of CTAs; beyond
+  // the first tile a CTA's loads overlap its stores
   tp.xt = 1;
   if (vec && tp.f_mode != F_AXIS_X) {
     const size_t smem_c = (size_t)tp.TY * tp.P * 4 + 1024;
     const long long per_wave = (long long)ctx_sm_count(ctx) *
                                (long long)std::max<size_t>(1, std::min<size_t>(2048 / kThreads, (size_t)(220 * 1024) / smem_c));
-    while (tp.xt < 4 && (long long)tp.tiles_x >= 2 * tp.xt && g64 / (2 * tp.xt) >= 4 * per_wave) tp.xt *= 2;
+    while (tp.xt < 4 && (long long)tp.tiles_x >= 2 * tp.xt && g64 / (2 * tp.xt) >= 2 * per_wave) tp.xt *= 2;
   }
   const unsigned tiles_xg = (tp.tiles_x + tp.xt - 1) / tp.xt;
   g64 = (long long)tiles_xg * tp.tiles_y * batch;
