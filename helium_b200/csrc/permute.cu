@@ -184,7 +184,7 @@ constexpr int ilog2_c(int v) { return v <= 1 ? 0 : 1 + ilog2_c(v / 2); }
 // TXW_C / TY_C > 0 fix the tile shape at compile time (the common shapes), which unrolls both
 // loops and folds every shift, mask and pitch; 0 keeps them as kernel parameters.
 template <int EB, int XDT, int TXW_C = 0, int TY_C = 0>
-__global__ void __launch_bounds__(kThreads) permute_tile_vec(const __grid_constant__ TileParams p) {
+__global__ void __launch_bounds__(kThreads, (EB == 2 && TXW_C > 0) ? 8 : 1) permute_tile_vec(const __grid_constant__ TileParams p) {
   extern __shared__ uint32_t sm[];
   constexpr int EPW = 4 / EB;            // elements per 32-bit word
   constexpr int VE = 16 / EB;            // elements per 16-byte vector
