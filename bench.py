@@ -10,7 +10,8 @@ on synthetic seeded inputs; the metric is algorithmic HBM bytes moved per second
 Other workloads: c1 = configs[0] (MLP training step, steps/s, whole graph through the C++ host
 runtime as one CUDA graph), c3 = configs[2] (fused 4096^3 GEMM, TFLOP/s), c4 = configs[3]
 (transformer MLP block forward+backward, 8192 tokens per GPU, weight gradients all-reduced over
-NCCL), c4g = the same block as one op graph through the host runtime, gemm = a plain 8192^3 bf16 matmul.
+NCCL), c4g = the same block as one op graph through the host runtime, gemm = a plain 8192^3 bf16 matmul,
+pw = stand-alone pointwise programs on 64 Mi-element tensors.
 
 Rank 0 prints exactly one JSON line.  With N > 1 (launched under torch.distributed.run) c1-c3 run
 an independent replica per rank (those configurations have no cross-GPU dependency); c4 shards
@@ -576,6 +577,87 @@ class WorkloadC4Graph(_GemmBase):
     cpu_sample = staticmethod(lambda max_steps=1: WorkloadC4.cpu_sample(max_steps))
 
 
+class WorkloadPointwise:
+    """Stand-alone pointwise programs on tensors larger than L2 (the P1 row of the hot path): three short dense
+    programs served by hand-written kernels and one longer program served by the register-program interpreter."""
+    key = "pw"
+    metric, unit = "pointwise_hbm_gbs", "GB/s"
+    dtype = "bf16 / f32 storage, f32 arithmetic"
+    N = 8192 * 8192
+    description = ("stand-alone pointwise programs on 64 Mi-element tensors: relu(a)*m (bf16), a+b (f32), w-0.01*g (f32) on the dense "
+                   "elementwise kernels; gelu(a+b)*c (bf16) on the interpreter")
+    l2_note = "every tensor is 128 MiB (bf16) or 256 MiB (f32): larger than L2"
+    work_scale = 1e9
+
+    def __init__(self, ctx, dev, world, rank, peaks, reducer):
+        import torch
+        import helium_b200 as hb
+        from helium_b200 import ir
+        self.torch = torch
+        n = self.N
+        td = {ir.BF16: torch.bfloat16, ir.F32: torch.float32}
+        gen = torch.Generator(device=dev).manual_seed(6)
+
+        def case(name, dts, build):
+            g = ir.Graph()
+            ins = [g.new_input([n], d) for d in dts]
+            g.new_output(build(g, ins))
+            plan = hb.Plan.pointwise(ctx, g)
+            tin = [torch.randn(n, generator=gen, device=dev).to(td[d]) for d in dts]
+            tout = plan.alloc_outputs(dev)
+            nbytes = sum(t.numel() * t.element_size() for t in tin + tout)
+            return name, plan, tin, tout, nbytes
+
+        self.cases = [
+            case("relu_mul_bf16", [ir.BF16, ir.BF16], lambda g, i: g.binary(ir.BIN_MUL, g.unary(ir.UN_RELU, i[0]), i[1])),
+            case("add_f32", [ir.F32, ir.F32], lambda g, i: g.binary(ir.BIN_ADD, i[0], i[1])),
+            case("sgd_f32", [ir.F32, ir.F32], lambda g, i: g.binary(ir.BIN_ADD, i[0], g.unary(ir.UN_NEG, g.binary(ir.BIN_MUL, i[1], g.constant(0.01, [n]))))),
+            case("gelu_add_mul_bf16_interpreter", [ir.BF16, ir.BF16, ir.BF16],
+                 lambda g, i: g.binary(ir.BIN_MUL, g.unary(ir.UN_GELU, g.binary(ir.BIN_ADD, i[0], i[1])), i[2])),
+        ]
+        self.work_per_step = float(sum(c[4] for c in self.cases))
+        self.launches_per_step = len(self.cases)
+        self.dominant = {c[0]: (c[1].description, c[4], "hbm", peaks["hbm_gbs"], "GB/s") for c in self.cases}
+        self.dominant_key = "relu_mul_bf16"
+        self.e2e_work_per_step = float(self.cases[0][4])   # the end-to-end leg runs the first program only
+        self.pin_in = self.cases[0][2][0].cpu().pin_memory(); self.pin_m = self.cases[0][2][1].cpu().pin_memory()
+        self.pin_out = torch.empty_like(self.pin_in).pin_memory()
+        self.h2d = 2 * self.pin_in.numel() * 2
+        self.d2h = self.pin_in.numel() * 2
+
+    def step(self, record=None):
+        st = self.torch.cuda.current_stream()
+        for name, plan, tin, tout, _ in self.cases:
+            if record is None:
+                plan.launch(tin, tout)
+            else:
+                e0, e1 = _events(self.torch)
+                e0.record(st); plan.launch(tin, tout); e1.record(st)
+                record.append((name, e0, e1))
+
+    def step_e2e(self):
+        # the first program only, fed from and read back to pinned host memory
+        name, plan, tin, tout, _ = self.cases[0]
+        tin[0].copy_(self.pin_in, non_blocking=True); tin[1].copy_(self.pin_m, non_blocking=True)
+        plan.launch(tin, tout)
+        self.pin_out.copy_(tout[0], non_blocking=True)
+        self.torch.cuda.current_stream().synchronize()
+
+    @staticmethod
+    def cpu_sample(max_steps=1):
+        from helium_b200.configs import bf16_normal, rng
+        from oracle import oracle as O
+        from helium_b200 import ir
+        n = 1 << 22
+        r = rng(6)
+        a, m = bf16_normal(r, (n,)), bf16_normal(r, (n,))
+        t0 = time.perf_counter()
+        x = np.maximum(O.decode(a, ir.BF16, (n,)), 0) * O.decode(m, ir.BF16, (n,))
+        O.encode(x, ir.BF16)
+        dt = time.perf_counter() - t0
+        return 3 * n * 2 / dt / 1e9, 1, f"relu(a)*m on {n} bf16 elements with the numpy oracle (single thread)", dt
+
+
 class WorkloadC1:
     key = "c1"
     metric, unit = "train_steps_per_s", "step/s"
@@ -655,7 +737,7 @@ class WorkloadC1:
         return 1.0 / dt, cores, f"{max_steps} steps of the numpy f64 restatement (oracle/oracle.py) of the same op graph; the reference's CPU backend is a stub", dt
 
 
-WORKLOADS = {w.key: w for w in (WorkloadC1, WorkloadC2, WorkloadC3, WorkloadC4, WorkloadC4Graph, WorkloadGemm)}
+WORKLOADS = {w.key: w for w in (WorkloadC1, WorkloadC2, WorkloadC3, WorkloadC4, WorkloadC4Graph, WorkloadGemm, WorkloadPointwise)}
 
 
 def _use_all_host_threads():
@@ -697,7 +779,7 @@ def main():
                          "(the printed line is then not a bench value)")
     args = ap.parse_args()
     if args.steps is None:
-        args.steps = {"c1": 2000, "c2": 200, "c3": 200, "c4": 30, "c4g": 30, "gemm": 100}[args.workload]
+        args.steps = {"c1": 2000, "c2": 200, "c3": 200, "c4": 30, "c4g": 30, "gemm": 100, "pw": 50}[args.workload]
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -814,7 +896,8 @@ def main():
             "metric": wl.metric, "value": to_value(ms_per_step * 1e-3), "unit": wl.unit, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": wl.dtype, "data": "synthetic", "config": config, "roofline": roofline,
-            "e2e": None if args.brief else {"value": to_value(e2e_sec), "unit": wl.unit, "h2d_bytes_per_step": wl.h2d,
+            "e2e": None if args.brief else {"value": getattr(wl, "e2e_work_per_step", wl.work_per_step) * world / e2e_sec / wl.work_scale,
+                                            "unit": wl.unit, "h2d_bytes_per_step": wl.h2d,
                                             "d2h_bytes_per_step": wl.d2h, "ms_per_step": e2e_sec * 1e3, "steps": e2e_steps,
                                             "pipelining": getattr(wl, "e2e_note", "one stream: upload, kernels, download in order")},
             "gpu_launches": wl.launches_per_step * args.steps,
