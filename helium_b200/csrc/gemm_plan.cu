@@ -383,6 +383,10 @@ struct MatmulPlan : he_plan {
   int n_inputs = 0, n_outputs = 0;
   // Sgemm
   int s_bias = -1, s_act = 0, s_in_dt = HE_F32, s_out_dt = HE_F32, s_bias_dt = HE_F32;
+  // SIMT scale/accumulate epilogue: out = [resid +] [-] (acc * (s_alpha | mul input))
+  bool s_axpy = false;
+  int s_resid = -1, s_resid_dt = HE_F32, s_mul = -1, s_mul_dt = HE_F32, s_negate = 0;
+  float s_alpha = 1.0f;
   // workspace layout (floats)
   size_t ws_col_off[2] = {0, 0}, ws_scalar_off = 0;
   // Mainloop fusion by materialisation: relu(A) * mask is written once to the workspace by the dense
@@ -399,8 +403,14 @@ struct MatmulPlan : he_plan {
       if (!outputs || !outputs[i]) HE_FAIL(HE_ERR_INVALID, "fused matmul launch: output %d is null", i);
     if (core.M == 0 || core.N == 0 || core.batch == 0) return HE_OK;
     if (kind == EpiKind::Sgemm) {
+      SgemmAxpy axpy;
+      if (s_axpy) {
+        axpy.enabled = 1; axpy.alpha = s_alpha; axpy.negate = s_negate;
+        if (s_resid >= 0) { axpy.resid = inputs[s_resid]; axpy.resid_dt = s_resid_dt; }
+        if (s_mul >= 0) { axpy.mul = inputs[s_mul]; axpy.mul_dt = s_mul_dt; }
+      }
       HE_TRY(launch_sgemm(inputs[a_slot], inputs[b_slot], outputs[0], s_in_dt, s_out_dt, core.batch, core.M, core.N, core.K,
-                          cfg.a_mn, cfg.b_mn, s_bias >= 0 ? inputs[s_bias] : nullptr, s_bias_dt, s_act, stream));
+                          cfg.a_mn, cfg.b_mn, s_bias >= 0 ? inputs[s_bias] : nullptr, s_bias_dt, s_act, axpy, stream));
       last_launches = 1;
       return HE_OK;
     }
@@ -738,15 +748,61 @@ int32_t plan_fused_matmul_core(he_ctx* ctx, const Graph& g, he_plan** out, int* 
     PwCompiled pc;
     PwCanon canon;
     HE_TRY(canon_of(g, mm, &pc, &canon));
-    int bias_slot = -1, act = 0;
+    int bias_slot = -1, act = 0, axpy_slot = -1, mul_slot = -1, axpy_neg = 0;
+    float axpy_alpha = 1.0f;
+    bool has_axpy = false;
     bool ok = false;
     if (canon.text == "store(A);") ok = true;
     else if (canon.text == "store(sum(A,I0:R));") { ok = true; bias_slot = canon.slot_order[0]; }
     else if (canon.text == "store(u8(sum(A,I0:R)));") { ok = true; bias_slot = canon.slot_order[0]; act = 1; }
     else if (canon.text == "store(u8(A));") { ok = true; act = 1; }
+    else {
+      // scaled / negated / accumulated forms: [I:F +] [-] (A * (K | I:F)) -- the SGD update of a weight
+      // gradient, w + (-(g * lr)) (helium/src/optimizer/sgd.rs), and every partial subgraph that greedy
+      // pairwise fusion passes through on the way there.  A constant is spelled K<8 hex digits>.
+      std::string t = canon.text;
+      auto eat = [&](const char* lit) {
+        const size_t n = strlen(lit);
+        if (t.compare(0, n, lit) != 0) return false;
+        t.erase(0, n);
+        return true;
+      };
+      auto eat_full_input = [&](int* slot) {   // I<k>:F
+        if (t.size() < 4 || t[0] != 'I') return false;
+        size_t q = 1;
+        int k = 0;
+        while (q < t.size() && t[q] >= '0' && t[q] <= '9') k = k * 10 + (t[q++] - '0');
+        if (q == 1 || t.compare(q, 2, ":F") != 0 || k >= (int)canon.slot_order.size()) return false;
+        *slot = canon.slot_order[k];
+        t.erase(0, q + 2);
+        return true;
+      };
+      bool good = eat("store(");
+      const bool has_sum = good && eat("sum(");
+      if (has_sum) good = eat_full_input(&axpy_slot) && eat(",");
+      const bool neg = good && eat("u1(");
+      good = good && eat("prod(A,");
+      if (good) {
+        if (t.size() >= 9 && t[0] == 'K') {
+          char* end = nullptr;
+          const std::string hex = t.substr(1, 8);
+          const uint32_t b32 = (uint32_t)strtoul(hex.c_str(), &end, 16);
+          good = end == hex.c_str() + 8;
+          memcpy(&axpy_alpha, &b32, 4);
+          t.erase(0, 9);
+        } else {
+          good = eat_full_input(&mul_slot);
+        }
+      }
+      good = good && eat(")") && (!neg || eat(")")) && (!has_sum || eat(")")) && eat(");") && t.empty();
+      if (good) { ok = true; axpy_neg = neg; has_axpy = true; }
+      else { axpy_slot = mul_slot = -1; }
+    }
     const int odt = g.nodes[g.outputs[0]].dtype;
+    for (int sl : {axpy_slot, mul_slot})
+      if (ok && sl >= 0 && dclass(g.nodes[g.inputs[sl]].dtype) != DClass::Float) ok = false;
     if (!ok || dclass(odt) != DClass::Float || (bias_slot >= 0 && dclass(g.nodes[g.inputs[bias_slot]].dtype) != DClass::Float))
-      HE_FAIL(HE_ERR_UNSUPPORTED, "fused matmul: the SIMT path (%s) supports only store / +bias / relu epilogues", why);
+      HE_FAIL(HE_ERR_UNSUPPORTED, "fused matmul: the SIMT path (%s) supports only store / +bias / relu / axpy epilogues", why);
     if (tier_only) { *tier_only = 2; return HE_OK; }
     plan->kind = EpiKind::Sgemm;
     plan->s_bias = bias_slot;
@@ -754,7 +810,14 @@ int32_t plan_fused_matmul_core(he_ctx* ctx, const Graph& g, he_plan** out, int* 
     plan->s_in_dt = An.dtype;
     plan->s_out_dt = odt;
     plan->s_bias_dt = bias_slot >= 0 ? g.nodes[g.inputs[bias_slot]].dtype : HE_F32;
-    plan->description = std::string("fused matmul: SIMT FFMA kernel, 64x64 tiles (") + why + ")";
+    plan->s_axpy = has_axpy;
+    plan->s_resid = axpy_slot;
+    plan->s_resid_dt = axpy_slot >= 0 ? g.nodes[g.inputs[axpy_slot]].dtype : HE_F32;
+    plan->s_mul = mul_slot;
+    plan->s_mul_dt = mul_slot >= 0 ? g.nodes[g.inputs[mul_slot]].dtype : HE_F32;
+    plan->s_alpha = axpy_alpha;
+    plan->s_negate = axpy_neg;
+    plan->description = std::string("fused matmul: SIMT FFMA kernel, 64x64 tiles (") + why + (has_axpy ? ", scale/accumulate epilogue)" : ")");
     *out = guard.release();
     return HE_OK;
   };

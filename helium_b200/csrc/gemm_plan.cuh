@@ -22,7 +22,17 @@ int32_t launch_colsum_finalize(const float* partials, float* out, int batch, int
                                float scale = 1.0f);
 int32_t launch_scalar_finalize(const float* partials, float* out, int n, cudaStream_t stream, int op = 0, float scale = 1.0f);
 // SIMT matmul: f32 operands, or 2-byte operands whose shapes break the TMA alignment rules
+// `axpy`: optional epilogue out = [resid +] [-] (acc * (mul ? mul[i] : alpha)); resid and mul have the
+// output's shape, every step rounds separately like the unfused graph
+struct SgemmAxpy {
+  int enabled = 0;
+  const void* resid = nullptr;
+  const void* mul = nullptr;
+  int resid_dt = HE_F32, mul_dt = HE_F32;
+  float alpha = 1.0f;
+  int negate = 0;
+};
 int32_t launch_sgemm(const void* a, const void* b, void* c, int in_dt, int out_dt, int batch, int M, int N, int K,
-                     bool a_mn, bool b_mn, const void* bias, int bias_dt, int act, cudaStream_t stream);
+                     bool a_mn, bool b_mn, const void* bias, int bias_dt, int act, const SgemmAxpy& axpy, cudaStream_t stream);
 
 }  // namespace he

@@ -21,7 +21,11 @@ namespace he {
 
 struct SgemmParams {
   const void* a; const void* b; void* c; const void* bias;
-  int in_dt, out_dt, bias_dt;
+  // scale / accumulate epilogue (the SGD update of a weight gradient, w + (-(g * lr))):
+  // out = [resid +] [-] (acc * (mul ? mul[i] : alpha)), resid and mul of the output's shape
+  const void* resid; const void* mul;
+  float alpha; int axpy, alpha_neg;
+  int in_dt, out_dt, bias_dt, resid_dt, mul_dt;
   int M, N, K, batch;
   long long sam, sak, sbk, sbn;  // element strides of A(m, k) and B(k, n)
   int act;
@@ -39,6 +43,12 @@ constexpr int kSgPitch = 64 + 4;
 
 __device__ __forceinline__ void sg_store(const SgemmParams& p, size_t o, int gn, float v) {
   if (p.bias) v += sg_load(p.bias, p.bias_dt, gn);
+  if (p.axpy) {
+    // separately rounded product and sum, like the unfused graph
+    float s = __fmul_rn(v, p.mul ? sg_load(p.mul, p.mul_dt, (long long)o) : p.alpha);
+    if (p.alpha_neg) s = -s;
+    v = p.resid ? __fadd_rn(sg_load(p.resid, p.resid_dt, (long long)o), s) : s;
+  }
   if (p.act == 1) v = fmaxf(v, 0.0f);
   if (p.out_dt == HE_F32) reinterpret_cast<float*>(p.c)[o] = v;
   else reinterpret_cast<unsigned short*>(p.c)[o] = (unsigned short)(p.out_dt == HE_BF16 ? f32_to_bf16_bits(v) : f32_to_f16_bits(v));
@@ -130,9 +140,11 @@ __global__ void __launch_bounds__(256) sgemm_64x64_kernel(const __grid_constant_
 }
 
 int32_t launch_sgemm(const void* a, const void* b, void* c, int in_dt, int out_dt, int batch, int M, int N, int K,
-                     bool a_mn, bool b_mn, const void* bias, int bias_dt, int act, cudaStream_t stream) {
+                     bool a_mn, bool b_mn, const void* bias, int bias_dt, int act, const SgemmAxpy& axpy, cudaStream_t stream) {
   SgemmParams p{};
   p.a = a; p.b = b; p.c = c; p.bias = bias;
+  p.axpy = axpy.enabled; p.resid = axpy.resid; p.resid_dt = axpy.resid_dt; p.mul = axpy.mul; p.mul_dt = axpy.mul_dt;
+  p.alpha = axpy.alpha; p.alpha_neg = axpy.negate;
   p.in_dt = in_dt; p.out_dt = out_dt; p.bias_dt = bias_dt;
   p.M = M; p.N = N; p.K = K; p.batch = batch;
   // a_mn: A stored [K, M]; b_mn: B stored [K, N] (the helium layout), else [N, K]

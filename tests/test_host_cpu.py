@@ -47,8 +47,11 @@ def test_mlp_step_plan_structure():
     ins = _instrs(text)
     mm = [i for i in ins if i["kind"] == "FusedMatmul"]
     assert len(mm) == 5
-    # the explicit transposes of the backward matmuls fold into the matmul instructions
-    assert sum(1 for i in mm if len(i["nodes"]) == 2) >= 2
+    # explicit transposes of the backward matmuls fold into the matmul instructions, and both weight
+    # gradients carry their SGD update (const, mul, neg, add) in the epilogue
+    assert sum(1 for i in mm if len(i["nodes"]) >= 2) >= 3
+    assert sum(1 for i in mm if len(i["nodes"]) >= 5) == 2
+    assert len(ins) == 14
     # every node is planned exactly once and in dependency order
     seen = set(g.inputs)
     for i in ins:

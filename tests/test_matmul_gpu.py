@@ -169,6 +169,28 @@ def test_simt_paths(ctx):
         _compare(g, got, O.evaluate(g, ins), plan.description)
 
 
+def test_simt_scale_accumulate_epilogues(ctx):
+    """The SGD update of a weight gradient, w + (-(g * lr)) (helium/src/optimizer/sgd.rs), and the
+    partial forms greedy fusion passes through, as epilogues of the f32 SIMT kernel (with and without
+    the cluster split of K)."""
+    for (m, n, k) in [(784, 512, 256), (512, 10, 256), (70, 33, 19)]:
+        for form in range(5):
+            g = ir.Graph()
+            a = g.new_input([k, m], ir.F32); b = g.new_input([k, n], ir.F32)
+            w = g.new_input([m, n], ir.F32); s = g.new_input([m, n], ir.F32)
+            t = g.matmul(g.transpose(a), b, ir.PREC_TF32_F32)
+            t = g.binary(ir.BIN_MUL, t, s if form == 0 else g.constant(0.01, [m, n]))
+            if form in (2, 3):
+                t = g.unary(ir.UN_NEG, t)
+            if form in (3, 4):
+                t = g.binary(ir.BIN_ADD, w, t)
+            g.new_output(t)
+            ins = _gen(g, 61 + form, {1: 1.0 / np.sqrt(k)})
+            got, plan = _run(ctx, g, ins)
+            assert "SIMT" in plan.description and "scale/accumulate" in plan.description
+            _compare(g, got, O.evaluate(g, ins), plan.description)
+
+
 def test_mlp_block_forward_backward(ctx):
     """configs[3] at a small size: every one of the six fused GEMMs against the oracle evaluated on
     the operands that GEMM actually read (so an upstream rounding does not hide a downstream error)."""
