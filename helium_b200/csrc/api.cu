@@ -163,7 +163,16 @@ int32_t parse_graph(const he_graph_desc* desc, Graph* out) {
             HE_FAIL(HE_ERR_INVALID, "node %d: matmul batch dims mismatch", i);
         if (n.shape[r - 2] != a->shape[r - 2] || n.shape[r - 1] != b->shape[r - 1])
           HE_FAIL(HE_ERR_INVALID, "node %d: matmul output shape wrong", i);
-        if (n.dtype != HE_F32) HE_FAIL(HE_ERR_INVALID, "node %d: matmul output is the f32 accumulator type", i);
+        {
+          // the node's dtype is the accumulator type of its precision (precision.rs:84-96)
+          const int kind = HE_PREC_KIND(n.sub_op);
+          if (kind < HE_PREC_F32_F32 || kind > HE_PREC_F8_F16) HE_FAIL(HE_ERR_INVALID, "node %d: unknown matmul precision %d", i, kind);
+          const bool f8 = kind == HE_PREC_F8_F32 || kind == HE_PREC_F8_F16;
+          if ((n.sub_op & ~0xff) != 0 && (!f8 || (n.sub_op & ~0x11ff) != 0))
+            HE_FAIL(HE_ERR_INVALID, "node %d: malformed matmul precision 0x%x", i, n.sub_op);
+          const int acc = (kind == HE_PREC_F16_F16 || kind == HE_PREC_F8_F16) ? HE_F16 : HE_F32;
+          if (n.dtype != acc) HE_FAIL(HE_ERR_INVALID, "node %d: matmul output must be the accumulator type of its precision (%s)", i, dtype_name(acc));
+        }
         if (dclass(a->dtype) != DClass::Float || dclass(b->dtype) != DClass::Float)
           HE_FAIL(HE_ERR_INVALID, "node %d: matmul of non-float", i);
         break;

@@ -26,7 +26,15 @@ BIN_ADD, BIN_MUL, BIN_POW, BIN_MIN, BIN_MAX, BIN_AND, BIN_OR, BIN_XOR = range(8)
 BIN_SUB, BIN_DIV, BIN_DRELU = 16, 17, 18
 CMP_EQ, CMP_NE, CMP_LT, CMP_LE, CMP_GT, CMP_GE = range(6)
 RED_SUM, RED_MEAN, RED_MAX, RED_MIN = range(4)
-PREC_F32_F32, PREC_TF32_F32, PREC_BF16_F32, PREC_F16_F32 = range(4)
+PREC_F32_F32, PREC_TF32_F32, PREC_BF16_F32, PREC_F16_F32, PREC_F16_F16, PREC_F8_F32, PREC_F8_F16 = range(7)
+F8_E4M3, F8_E5M2 = 0, 1
+
+
+def prec_f8(kind: int, mode_a: int = F8_E4M3, mode_b: int = F8_E4M3) -> int:
+    """MulF8Accum* { mode_a, mode_b } (helium-ir/src/opgraph/op/precision.rs:60-81) packed the way the
+    C ABI's `sub_op` carries it."""
+    assert kind in (PREC_F8_F32, PREC_F8_F16)
+    return kind | (mode_a << 8) | (mode_b << 12)
 
 
 def _is_float(dt: int) -> bool:
@@ -171,7 +179,9 @@ class Graph:
     def matmul(self, a: int, b: int, precision: int = PREC_BF16_F32) -> int:
         na, nb = self.nodes[a], self.nodes[b]
         shape = tuple(na.shape[:-1]) + (nb.shape[-1],)
-        return self._add(Node(OP_MATMUL, F32, shape, sub_op=precision, inputs=(a, b)))
+        # the node's dtype is the accumulator type (precision.rs:84-96)
+        acc = F16 if (precision & 0xff) in (PREC_F16_F16, PREC_F8_F16) else F32
+        return self._add(Node(OP_MATMUL, acc, shape, sub_op=precision, inputs=(a, b)))
 
     # -- queries ---------------------------------------------------------------------------------
     @property

@@ -81,8 +81,20 @@ typedef enum he_precision {
   HE_PREC_F32_F32 = 0,   /* MulF32AccumF32  */
   HE_PREC_TF32_F32 = 1,  /* MulTf32AccumF32 (a minimum: served with full f32 products here)        */
   HE_PREC_BF16_F32 = 2,  /* MulBf16AccumF32 */
-  HE_PREC_F16_F32 = 3    /* MulF16AccumF32  */
+  HE_PREC_F16_F32 = 3,   /* MulF16AccumF32  */
+  HE_PREC_F16_F16 = 4,   /* MulF16AccumF16: the node's dtype is F16 (accumulator_type, precision.rs:84-96) */
+  HE_PREC_F8_F32 = 5,    /* MulF8AccumF32 { mode_a, mode_b }: see HE_PREC_F8 */
+  HE_PREC_F8_F16 = 6     /* MulF8AccumF16 { mode_a, mode_b }: node dtype F16 */
 } he_precision;
+/* F8Mode (precision.rs:100-108) of each operand rides in the upper bits of `sub_op`:
+ * sub_op = HE_PREC_F8(HE_PREC_F8_F32, HE_F8_E4M3, HE_F8_E5M2).
+ * The reference documents the setting as a MINIMUM (precision.rs:3-9).  This library multiplies at
+ * the precision of the operand tensors (bf16 / f16 on tcgen05 with f32 accumulation, f32 on FFMA) and
+ * never narrower, so the F8 and F16-accumulate requests are served above their minimum; the output
+ * is rounded once to the node's dtype. */
+typedef enum he_f8_mode { HE_F8_E4M3 = 0, HE_F8_E5M2 = 1 } he_f8_mode;
+#define HE_PREC_KIND(sub_op) ((sub_op) & 0xff)
+#define HE_PREC_F8(kind, mode_a, mode_b) ((kind) | ((mode_a) << 8) | ((mode_b) << 12))
 
 /* One node of a subgraph, in topological order (every `in[i]` is a smaller index, or -1).
  * `shape`/`rank`/`dtype` describe the node's OUTPUT (the reference's `Descriptor`,

@@ -41,7 +41,8 @@ BIN_ADD, BIN_MUL, BIN_POW, BIN_MIN, BIN_MAX, BIN_AND, BIN_OR, BIN_XOR = range(8)
 BIN_SUB, BIN_DIV, BIN_DRELU = 16, 17, 18
 CMP_EQ, CMP_NE, CMP_LT, CMP_LE, CMP_GT, CMP_GE = range(6)
 RED_SUM, RED_MEAN, RED_MAX, RED_MIN = range(4)
-PREC_F32_F32, PREC_TF32_F32, PREC_BF16_F32, PREC_F16_F32 = range(4)
+PREC_F32_F32, PREC_TF32_F32, PREC_BF16_F32, PREC_F16_F32, PREC_F16_F16, PREC_F8_F32, PREC_F8_F16 = range(7)
+F8_E4M3, F8_E5M2 = 0, 1
 
 try:  # scipy is present in the image; math.erf keeps the oracle usable without it
     from scipy.special import erf as _erf
@@ -110,6 +111,21 @@ def round_to(value: np.ndarray, dtype: int) -> np.ndarray:
     return value
 
 
+def round_to_f8(value: np.ndarray, mode: int) -> np.ndarray:
+    """Nearest-even rounding to the 8-bit float of F8Mode (helium-ir/src/opgraph/op/precision.rs:100-108),
+    saturating at the largest finite value: E4M3 (bias 7, max 448) or E5M2 (bias 15, max 57344).  Only
+    used to draw the error envelope of the reference's 8-bit multiplication; the library multiplies at
+    the operand dtype, which the precision contract allows (precision.rs:3-9)."""
+    man, emin, vmax = (3, -6, 448.0) if mode == F8_E4M3 else (2, -14, 57344.0)
+    x = np.asarray(value, dtype=np.float64)
+    mag = np.abs(x)
+    with np.errstate(divide="ignore"):
+        e = np.floor(np.log2(np.where(mag > 0, mag, 1.0)))
+    quantum = np.exp2(np.maximum(e, emin) - man)
+    q = np.rint(mag / quantum) * quantum
+    return np.sign(x) * np.minimum(q, vmax)
+
+
 def _const_value(bits: int, dtype: int):
     if dtype == F32:
         return float(np.array([bits], dtype=np.uint32).view(np.float32)[0])
@@ -173,7 +189,8 @@ _CMP = {CMP_EQ: np.equal, CMP_NE: np.not_equal, CMP_LT: np.less, CMP_LE: np.less
         CMP_GT: np.greater, CMP_GE: np.greater_equal}
 
 
-def evaluate(graph, inputs: Sequence[np.ndarray], round_nodes: Iterable[int] = (), return_all: bool = False):
+def evaluate(graph, inputs: Sequence[np.ndarray], round_nodes: Iterable[int] = (), return_all: bool = False,
+             f8_quantise: bool = False):
     """Evaluates a graph (any object with `.nodes` / `.outputs` shaped like helium_b200.ir.Graph).
 
     `inputs[i]` is the storage array of the i-th OP_INPUT node (uint16 bits for bf16, float16,
@@ -238,10 +255,16 @@ def evaluate(graph, inputs: Sequence[np.ndarray], round_nodes: Iterable[int] = (
             v = np.where(vals[n.inputs[2]].reshape(a.shape), vals[n.inputs[1]].reshape(a.shape), a)
         elif k == OP_MATMUL:
             a, b = vals[n.inputs[0]], vals[n.inputs[1]]
-            if n.sub_op == PREC_BF16_F32:
+            # Precision is a minimum (precision.rs:3-9): bf16 / f16 requests multiply operands rounded to
+            # that type; the 8-bit requests multiply at the operand dtype unless `f8_quantise` asks for
+            # the reference's narrowest legal reading (operands rounded to their F8Mode)
+            kind = n.sub_op & 0xff
+            if kind == PREC_BF16_F32:
                 a, b = round_to(a, BF16), round_to(b, BF16)
-            elif n.sub_op == PREC_F16_F32:
+            elif kind in (PREC_F16_F32, PREC_F16_F16):
                 a, b = round_to(a, F16), round_to(b, F16)
+            elif kind in (PREC_F8_F32, PREC_F8_F16) and f8_quantise:
+                a, b = round_to_f8(a, (n.sub_op >> 8) & 1), round_to_f8(b, (n.sub_op >> 12) & 1)
             v = np.matmul(a, b)
         else:
             raise ValueError(f"unknown op kind {k}")

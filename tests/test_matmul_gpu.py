@@ -191,6 +191,34 @@ def test_simt_scale_accumulate_epilogues(ctx):
             _compare(g, got, O.evaluate(g, ins), plan.description)
 
 
+def test_low_precision_requests_are_served_at_or_above_their_minimum(ctx):
+    """MulF16AccumF16 and MulF8Accum{F32,F16} (helium-ir/src/opgraph/op/precision.rs:56-81).  The setting
+    is a minimum (precision.rs:3-9): the product is taken at the operand dtype with f32 accumulation, so
+    the result must match the operand-precision oracle to the usual tolerance, and must be closer to it
+    than the narrowest legal reading (operands rounded to their F8Mode) is."""
+    for dt, prec, epi in [(ir.F16, ir.PREC_F16_F16, False), (ir.F16, ir.PREC_F16_F16, True),
+                          (ir.BF16, ir.prec_f8(ir.PREC_F8_F32, ir.F8_E4M3, ir.F8_E5M2), False),
+                          (ir.BF16, ir.prec_f8(ir.PREC_F8_F32, ir.F8_E4M3, ir.F8_E4M3), True),
+                          (ir.F16, ir.prec_f8(ir.PREC_F8_F16, ir.F8_E5M2, ir.F8_E4M3), False),
+                          (ir.F32, ir.prec_f8(ir.PREC_F8_F32), False)]:
+        m, n, k = 264, 392, 520
+        g = ir.Graph()
+        a = g.new_input([m, k], dt); b = g.new_input([k, n], dt); bias = g.new_input([n], ir.F32)
+        t = g.matmul(a, b, prec)
+        if epi:
+            t = g.cast(g.unary(ir.UN_RELU, g.binary(ir.BIN_ADD, t, g.broadcast_to(bias, [m, n]))), dt)
+        g.new_output(t)
+        ins = _gen(g, 71, {1: 1.0 / np.sqrt(k)})
+        got, plan = _run(ctx, g, ins)
+        want = O.evaluate(g, ins)
+        _compare(g, got, want, plan.description)
+        if (prec & 0xff) in (ir.PREC_F8_F32, ir.PREC_F8_F16):
+            node = g.nodes[g.outputs[0]]
+            dec = lambda x: O.decode(x, node.dtype, node.shape)
+            narrow = O.evaluate(g, ins, f8_quantise=True)
+            assert O.rel_l2(dec(got[0]), dec(want[0])) < 0.1 * O.rel_l2(dec(narrow[0]), dec(want[0])), plan.description
+
+
 def test_mlp_block_forward_backward(ctx):
     """configs[3] at a small size: every one of the six fused GEMMs against the oracle evaluated on
     the operands that GEMM actually read (so an upstream rounding does not hide a downstream error)."""

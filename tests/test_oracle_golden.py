@@ -298,3 +298,21 @@ def test_golden_fixtures(case):
     name, g, ins, want = case
     got = O.evaluate(g, ins)
     compare_with_golden(g, got, want, f32_tol=1e-6, half_tol=2e-3, exact_moves=name.startswith("permute"))
+
+
+def test_f8_rounding_known_answers():
+    """E4M3 (bias 7, 3 mantissa bits, largest finite 448) and E5M2 (bias 15, 2 mantissa bits, largest
+    finite 57344), helium-ir/src/opgraph/op/precision.rs:100-108: nearest-even, ties, subnormals,
+    saturation."""
+    from oracle import oracle as O
+    x = np.array([0.0, 1.0, 1.0625, 1.1875, 17.0, 448.0, 500.0, -1000.0, 2.0 ** -9, 2.0 ** -10, 0.3, 3.7])
+    e4 = np.array([0.0, 1.0, 1.0, 1.25, 16.0, 448.0, 448.0, -448.0, 2.0 ** -9, 0.0, 0.3125, 3.75])
+    e5 = np.array([0.0, 1.0, 1.0, 1.25, 16.0, 448.0, 512.0, -1024.0, 2.0 ** -9, 2.0 ** -10, 0.3125, 3.5])
+    assert np.array_equal(O.round_to_f8(x, O.F8_E4M3), e4)
+    assert np.array_equal(O.round_to_f8(x, O.F8_E5M2), e5)
+    assert np.array_equal(O.round_to_f8(np.array([6.0e4, 1.0e6, 2.0 ** -16, 2.0 ** -17]), O.F8_E5M2), np.array([57344.0, 57344.0, 2.0 ** -16, 0.0]))
+    # every value of either format is a fixed point
+    for mode in (O.F8_E4M3, O.F8_E5M2):
+        g = O.round_to_f8(np.linspace(-500, 500, 20001), mode)
+        assert np.array_equal(O.round_to_f8(g, mode), g)
+        assert len(np.unique(g)) <= 256

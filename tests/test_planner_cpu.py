@@ -243,3 +243,32 @@ def test_dense_elementwise_programs_are_tier_2():
     x = g.new_input([64, 128], ir.F32); b = g.new_input([128], ir.F32)
     g.new_output(g.binary(ir.BIN_ADD, x, g.broadcast_to(b, [64, 128])))
     assert hb.plan_supported(g, 0) == 1
+
+
+def test_every_precision_setting_is_accepted_at_or_above_its_minimum():
+    """helium-ir/src/opgraph/op/precision.rs:36-96: seven settings; the node's dtype is the accumulator
+    type; the setting is a minimum, so the 8-bit and f16-accumulate requests plan onto the same kernels
+    as the operand dtype's own setting."""
+    cases = [(ir.F32, ir.PREC_F32_F32), (ir.F32, ir.PREC_TF32_F32), (ir.BF16, ir.PREC_BF16_F32), (ir.F16, ir.PREC_F16_F32),
+             (ir.F16, ir.PREC_F16_F16), (ir.BF16, ir.prec_f8(ir.PREC_F8_F32, ir.F8_E4M3, ir.F8_E5M2)),
+             (ir.F16, ir.prec_f8(ir.PREC_F8_F16, ir.F8_E5M2, ir.F8_E5M2)), (ir.F32, ir.prec_f8(ir.PREC_F8_F32))]
+    for dt, prec in cases:
+        g = ir.Graph()
+        a = g.new_input([256, 512], dt); b = g.new_input([512, 384], dt)
+        t = g.matmul(a, b, prec)
+        assert g.nodes[t].dtype == (ir.F16 if (prec & 0xff) in (ir.PREC_F16_F16, ir.PREC_F8_F16) else ir.F32)
+        g.new_output(t)
+        assert hb.plan_supported(g, 2) == 2, hex(prec)
+        d = hb.Plan.fused_matmul(None, g).description
+        assert ("SIMT" in d) == (dt == ir.F32), d
+    # accumulator type and mode bits are validated
+    for bad_dtype, prec in [(ir.F32, ir.PREC_F16_F16), (ir.F16, ir.PREC_BF16_F32), (ir.F32, 7), (ir.F32, ir.PREC_BF16_F32 | (1 << 8)),
+                            (ir.F32, ir.PREC_F8_F32 | (2 << 8))]:
+        g = ir.Graph()
+        a = g.new_input([64, 64], ir.F16); b = g.new_input([64, 64], ir.F16)
+        t = g.matmul(a, b, ir.PREC_F16_F32)
+        g.nodes[t].sub_op = prec
+        g.nodes[t].dtype = bad_dtype
+        g.new_output(t)
+        with pytest.raises(HeliumError):
+            hb.Plan.fused_matmul(None, g)
