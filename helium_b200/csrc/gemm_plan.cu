@@ -1045,8 +1045,6 @@ int32_t plan_fused_matmul_core(he_ctx* ctx, const Graph& g, he_plan** out, int* 
       plan->pr_kind[s] = kind;
       plan->pr_out[s] = in.slot;
       plan->pr_op[s] = in.sub == HE_RED_MAX ? 1 : in.sub == HE_RED_MIN ? 2 : 0;
-      if (plan->pr_op[s] != 0 && kind == 0)
-        HE_FAIL(HE_ERR_UNSUPPORTED, "fused matmul: Max / Min over the rows of the tile are not implemented in the generic epilogue (Sum and Mean are)");
       if (in.sub == HE_RED_MEAN) {
         double count = 1.0;
         if (m & 1u) count *= c.N;

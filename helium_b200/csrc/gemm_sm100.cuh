@@ -141,6 +141,30 @@ __device__ __forceinline__ void warp_colsum_store(float (&v)[CH], float* dst) {
   if ((lane & ((1 << (5 - kLog)) - 1)) == 0) dst[lane >> (5 - kLog)] = v[0];
 }
 
+// The same exchange pattern for Sum (0), Max (1) or Min (2), chosen at run time (interpreted epilogue).
+__device__ __forceinline__ float red_combine(float a, float b, int op) { return op == 1 ? fmaxf(a, b) : op == 2 ? fminf(a, b) : a + b; }
+__device__ __forceinline__ float red_identity(int op) { return op == 1 ? -INFINITY : op == 2 ? INFINITY : 0.0f; }
+template <int CH>
+__device__ __forceinline__ void warp_colreduce_store(float (&v)[CH], float* dst, int op) {
+  const int lane = threadIdx.x & 31;
+  constexpr int kLog = CH == 32 ? 5 : CH == 16 ? 4 : 3;
+  int bit = 16;
+#pragma unroll
+  for (int s = CH / 2; s >= 1; s >>= 1) {
+    const bool upper = (lane & bit) != 0;
+#pragma unroll
+    for (int i = 0; i < s; ++i) {
+      const float send = upper ? v[i] : v[i + s];
+      const float keep = upper ? v[i + s] : v[i];
+      v[i] = red_combine(keep, __shfl_xor_sync(0xffffffffu, send, bit), op);
+    }
+    bit >>= 1;
+  }
+#pragma unroll
+  for (int b = (1 << (5 - kLog)) >> 1; b >= 1; b >>= 1) v[0] = red_combine(v[0], __shfl_xor_sync(0xffffffffu, v[0], b), op);
+  if ((lane & ((1 << (5 - kLog)) - 1)) == 0) dst[lane >> (5 - kLog)] = v[0];
+}
+
 // =================================================================================================
 // Epilogue functors.  Interface:
 //   Params                      POD passed by value inside the kernel parameter block
@@ -160,7 +184,8 @@ struct EpiEnv {
   int epi_warp;
 };
 
-__device__ __forceinline__ void col_partials_flush(const EpiEnv& env, const TileInfo& t, int nred, float* const* partials) {
+__device__ __forceinline__ void col_partials_flush(const EpiEnv& env, const TileInfo& t, int nred, float* const* partials,
+                                                   const int* ops = nullptr) {
   ptx::named_barrier_sync(1, env.n_epi_threads);
   const GemmCore& c = *env.core;
   for (int col = env.epi_tid; col < t.bn; col += env.n_epi_threads) {
@@ -168,7 +193,8 @@ __device__ __forceinline__ void col_partials_flush(const EpiEnv& env, const Tile
     if (gc < c.N) {
       for (int r = 0; r < nred; ++r) {
         const float* s = env.scratch + (size_t)r * 4 * env.bn;
-        const float v = ((s[col] + s[env.bn + col]) + s[2 * env.bn + col]) + s[3 * env.bn + col];
+        const int op = ops ? ops[r] : 0;
+        const float v = red_combine(red_combine(red_combine(s[col], s[env.bn + col], op), s[2 * env.bn + col], op), s[3 * env.bn + col], op);
         partials[r][((size_t)t.b * c.tiles_m + t.tile_m) * c.N + gc] = v;
       }
     }
@@ -426,7 +452,7 @@ struct EpiProgramParams {
   PwProgram prog;  // by value: lives in the kernel parameter block (constant bank)
   int n_red;             // reductions of the program (PwInstr::slot2 numbers them)
   int red_kind[4];       // per reduction slot: 0 columns, 1 rows, 2 scalar
-  int red_op[4];         // 0 sum (also mean: scaled by the fold), 1 max, 2 min (kinds 1 and 2 only)
+  int red_op[4];         // 0 sum (also mean: scaled by the fold), 1 max, 2 min
   float* red_partials[4];
   int n_col;             // kind-0 reductions (at most kColReductions)
   int col_slot[2];       // their reduction slots
@@ -445,11 +471,14 @@ struct EpiProgram {
     const GemmCore& c = *env.core;
     const int grow = t.m0 + row, gcol = t.n0 + col;
     float cbuf[kColReductions][kChunk];
+    int col_op[kColReductions];
+#pragma unroll
+    for (int r = 0; r < kColReductions; ++r) col_op[r] = r < p.n_col ? p.red_op[p.col_slot[r]] : 0;
     if (p.n_col > 0) {
 #pragma unroll
       for (int r = 0; r < kColReductions; ++r)
 #pragma unroll
-        for (int i = 0; i < kChunk; ++i) cbuf[r][i] = 0.0f;
+        for (int i = 0; i < kChunk; ++i) cbuf[r][i] = red_identity(col_op[r]);
     }
     if (grow < c.M) {
       const uint32_t base = (uint32_t)(((size_t)t.b * c.M + grow) * c.N + gcol);
@@ -482,17 +511,17 @@ struct EpiProgram {
 #pragma unroll
               for (int j = 0; j < 4; ++j) {
                 const float x = s == 0 ? cv[0][j] : s == 1 ? cv[1][j] : s == 2 ? cv[2][j] : cv[3][j];
-                cbuf[r][i + j] = r < p.n_col ? x : 0.0f;
+                if (r < p.n_col && j < nv) cbuf[r][i + j] = x;
               }
             }
           }
         }
       }
     }
-    // every lane of the warp takes part in the shuffles, rows beyond M contribute zeros
+    // every lane of the warp takes part in the shuffles, rows beyond M contribute the identity
 #pragma unroll
     for (int r = 0; r < kColReductions; ++r)
-      if (r < p.n_col) warp_colsum_store<kChunk>(cbuf[r], env.scratch + (r * 4 + env.quadrant) * env.bn + col);
+      if (r < p.n_col) warp_colreduce_store<kChunk>(cbuf[r], env.scratch + (r * 4 + env.quadrant) * env.bn + col, col_op[r]);
   }
   __device__ static void tile_end(const Params& p, const EpiEnv& env, const TileInfo& t, State& st) {
     if (p.n_red == 0) return;
@@ -531,7 +560,8 @@ struct EpiProgram {
     }
     if (p.n_col > 0) {
       float* parts[kColReductions] = {p.red_partials[p.col_slot[0]], p.red_partials[p.col_slot[p.n_col > 1 ? 1 : 0]]};
-      col_partials_flush(env, t, p.n_col, parts);   // its first barrier also publishes scal[]
+      const int ops[kColReductions] = {p.red_op[p.col_slot[0]], p.red_op[p.col_slot[p.n_col > 1 ? 1 : 0]]};
+      col_partials_flush(env, t, p.n_col, parts, ops);   // its first barrier also publishes scal[]
     } else if (any_scalar) {
       ptx::named_barrier_sync(1, env.n_epi_threads);
     }

@@ -364,9 +364,31 @@ def test_generic_epilogue_reduction_limits(ctx):
     g = ir.Graph()
     a = g.new_input([256, 64], ir.BF16); b = g.new_input([64, 256], ir.BF16)
     y = g.unary(ir.UN_EXP, g.matmul(a, b, ir.PREC_BF16_F32))
-    g.new_output(g.reduce_axes(ir.RED_MAX, y, [0]))
-    with pytest.raises(hb.HeliumError, match="Max / Min over the rows"):
+    for _ in range(3):
+        g.new_output(g.reduce_axes(ir.RED_MAX, y, [0]))
+    with pytest.raises(hb.HeliumError, match="at most two column reductions"):
         hb.Plan.fused_matmul(ctx, g)
+
+
+@pytest.mark.parametrize("m,n,k,batch", [(256, 512, 128, None), (200, 264, 72, None), (136, 72, 40, 3), (4096, 4096, 64, None)])
+def test_generic_epilogue_column_extrema(ctx, m, n, k, batch):
+    """Max and Min over the rows of the output (one value per column), with ragged tiles whose rows
+    beyond M must contribute the identity, not zero."""
+    lead = [] if batch is None else [batch]
+    g = ir.Graph()
+    a = g.new_input(lead + [m, k], ir.BF16); b = g.new_input(lead + [k, n], ir.BF16)
+    y = g.unary(ir.UN_ADD_CONST, g.unary(ir.UN_TANH, g.matmul(a, b, ir.PREC_BF16_F32)), const=3.0)   # all positive: zero would win a Min
+    r = len(lead)
+    g.new_output(g.reduce_axes(ir.RED_MIN, y, [r]))
+    g.new_output(g.reduce_axes(ir.RED_MAX, g.unary(ir.UN_NEG, y), [r]))   # all negative: zero would win a Max
+    g.new_output(g.reduce_axes(ir.RED_SUM, y, [r + 1]))
+    ins = _gen(g, 83, {1: 1.0 / np.sqrt(k)})
+    got, plan = _run(ctx, g, ins)
+    assert "3 reductions" in plan.description
+    want = O.evaluate(g, ins)
+    for o, x, w in zip(g.outputs, got, want):
+        x, w = np.asarray(x, dtype=np.float64).reshape(-1), np.asarray(w, dtype=np.float64).reshape(-1)
+        assert np.allclose(x, w, rtol=2e-5, atol=2e-5), (g.nodes[o].shape, float(np.abs(x - w).max()))
 
 
 @pytest.mark.parametrize("m,n,k", [(256, 512, 128), (200, 264, 72), (4096, 4096, 64)])
