@@ -479,8 +479,12 @@ struct MatmulPlan : he_plan {
       p.epi.loss_partials = ws + ws_scalar_off;
       bool vec = c.N % 8 == 0;
       const void* ptrs[] = {p.epi.mask, p.epi.y, p.epi.e1, p.epi.e2, p.epi.out_gt, p.epi.out_gz1};
-      for (const void* q : ptrs) vec = vec && ((uintptr_t)q % 16 == 0);
-      p.epi.vec_ok = vec ? 1 : 0;
+      bool vec32 = c.N % 16 == 0;
+      for (const void* q : ptrs) {
+        vec = vec && ((uintptr_t)q % 16 == 0);
+        vec32 = vec32 && ((uintptr_t)q % 32 == 0);
+      }
+      p.epi.vec_ok = vec ? (vec32 ? 2 : 1) : 0;
       p.epi.bias_vec = (c.N % 8 == 0 && (uintptr_t)p.epi.b1 % 16 == 0 && (uintptr_t)p.epi.b2 % 16 == 0) ? 1 : 0;
       HE_TRY(launch_gemm_c3(cfg, p, stream));
       HE_TRY(launch_colsum_finalize(ws + ws_col_off[0], (float*)outputs[r3.db2], c.batch, c.tiles_m, c.N, stream));

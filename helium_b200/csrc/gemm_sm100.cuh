@@ -334,7 +334,7 @@ struct EpiC3Params {
   float inv_n;       // MulConstant operand of README node 38 / 45
   int full_dt;       // dtype of mask / y / e1 / e2 / gt / gz1
   int vec_dt;        // dtype of b1 / b2
-  int vec_ok;
+  int vec_ok;        // 1: 16-byte row segments are aligned; 2: 32-byte ones are too
   int bias_vec;      // b1 / b2 pointers and N allow 16-byte loads
 };
 
@@ -372,8 +372,22 @@ struct EpiC3 {
 #pragma unroll
     for (int i = 0; i < kChunk; ++i) tnh[i] = fast_tanh(tnh[i] + a[i]);  // t
     float mk[kChunk];
-    load_row<kChunk>(p.mask, p.full_dt, off, nvalid, vec, mk);
-    load_row<kChunk>(p.y, p.full_dt, off, nvalid, vec, a);
+    // 16 bf16 columns are one 32-byte segment per lane: one 256-bit access instead of two 128-bit ones
+    // halves the load/store-unit work of a warp whose lanes sit on 32 different rows
+    const bool wide = p.vec_ok == 2 && nvalid == kChunk && p.full_dt == HE_BF16;
+    if (wide) {
+      uint32_t qm[8], qy[8];
+      ptx::ld_global_nc_256(reinterpret_cast<const unsigned short*>(p.mask) + off, qm);
+      ptx::ld_global_nc_256(reinterpret_cast<const unsigned short*>(p.y) + off, qy);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        mk[2 * j] = __uint_as_float(qm[j] << 16); mk[2 * j + 1] = __uint_as_float(qm[j] & 0xffff0000u);
+        a[2 * j] = __uint_as_float(qy[j] << 16); a[2 * j + 1] = __uint_as_float(qy[j] & 0xffff0000u);
+      }
+    } else {
+      load_row<kChunk>(p.mask, p.full_dt, off, nvalid, vec, mk);
+      load_row<kChunk>(p.y, p.full_dt, off, nvalid, vec, a);
+    }
     // The graph's op order is relaxed where it only moves roundings (all intermediates are f32, the
     // outputs are bf16 tiles and f32 sums checked to 1e-2 / 1e-5): h = m + u (t - m) instead of
     // (1 - u) m + u t, g (t - m) instead of g t - g m, and the loss is summed as d^2 and scaled by
@@ -412,7 +426,16 @@ struct EpiC3 {
       }
     }
     st.loss += loss;
-    if (nvalid > 0) {
+    if (wide) {
+      uint32_t w0[8], w1[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        w0[j] = f32x2_to_bf16x2(v[2 * j], v[2 * j + 1]);
+        w1[j] = f32x2_to_bf16x2(tnh[2 * j], tnh[2 * j + 1]);
+      }
+      ptx::st_global_256(reinterpret_cast<unsigned short*>(p.out_gt) + off, w0);
+      ptx::st_global_256(reinterpret_cast<unsigned short*>(p.out_gz1) + off, w1);
+    } else if (nvalid > 0) {
       store_row<kChunk>(p.out_gt, p.full_dt, off, nvalid, vec, v);
       store_row<kChunk>(p.out_gz1, p.full_dt, off, nvalid, vec, tnh);
     }
