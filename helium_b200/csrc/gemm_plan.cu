@@ -450,8 +450,12 @@ struct MatmulPlan : he_plan {
       p.epi.colsum_partials = ws ? ws + ws_col_off[0] : nullptr;
       bool vec = c.N % 8 == 0;
       const void* ptrs[] = {p.epi.out, p.epi.out_z, p.epi.resid, p.epi.gate_in};
-      for (const void* q : ptrs) vec = vec && ((uintptr_t)q % 16 == 0);
-      p.epi.vec_ok = vec ? 1 : 0;
+      bool vec32 = c.N % 16 == 0;
+      for (const void* q : ptrs) {
+        vec = vec && ((uintptr_t)q % 16 == 0);
+        vec32 = vec32 && ((uintptr_t)q % 32 == 0);
+      }
+      p.epi.vec_ok = vec ? (vec32 ? 2 : 1) : 0;
       p.epi.bias_vec = (c.N % 8 == 0 && (uintptr_t)p.epi.bias % 16 == 0) ? 1 : 0;
       HE_TRY(launch_gemm_flex(cfg, p, stream));
       last_launches = 1 + extra_launches;
