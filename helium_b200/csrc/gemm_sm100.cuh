@@ -282,6 +282,7 @@ struct EpiFlex {
   static constexpr int kChunk = 32;
   struct State {};
   __device__ static void tile_begin(const Params&, State&) {}
+  __device__ static void tile_prepare(const Params&, const EpiEnv&, const TileInfo&) {}
   // The op selectors are uniform per launch: switch once per chunk, not once per element.
   __device__ static void activate(int act, float (&v)[kChunk]) {
     switch (act) {
@@ -378,10 +379,27 @@ struct EpiC3Params {
 
 struct EpiC3 {
   using Params = EpiC3Params;
-  static constexpr int kColReductions = 2;
+  // two column-sum scratch blocks and a third block of the same size whose first 2 * BN floats hold the
+  // tile's b1 and b2 values (see tile_prepare)
+  static constexpr int kColReductions = 3;
   static constexpr int kChunk = 16;
   struct State { float loss; };
   __device__ static void tile_begin(const Params&, State& s) { s.loss = 0.0f; }
+  // Called by every epilogue thread once per tile, before the accumulator is awaited (so it overlaps
+  // the tile's mainloop): the tile's slice of both bias vectors goes to shared memory as f32.  Reading
+  // them from global memory in every chunk put two L2 round trips on each chunk's dependent chain (L1
+  // keeps next to nothing beside 200 KB of pipeline stages).  The previous tile's readers are behind
+  // the barriers of its tile_end.
+  __device__ static void tile_prepare(const Params& p, const EpiEnv& env, const TileInfo& t) {
+    float* bs = env.scratch + 2 * 4 * env.bn;
+    const int n = env.core->N;
+    for (int i = env.epi_tid; i < 2 * env.bn; i += env.n_epi_threads) {
+      const int which = i >= env.bn ? 1 : 0;
+      const int gc = t.n0 + (i - which * env.bn);
+      bs[i] = gc < n ? load_param_as_f32(which ? p.b2 : p.b1, p.vec_dt, gc) : 0.0f;
+    }
+    ptx::named_barrier_sync(1, env.n_epi_threads);
+  }
   __device__ static void chunk(const Params& p, const EpiEnv& env, const TileInfo& t, State& st, int row, int col, float (&v)[kChunk]) {
     const GemmCore& c = *env.core;
     const int grow = t.m0 + row, gcol = t.n0 + col;
@@ -402,13 +420,17 @@ struct EpiC3 {
 #pragma unroll
       for (int i = 0; i < kChunk; ++i) v[i] += a[i];
     }
-    const int ncols = max(0, min(kChunk, c.N - gcol));
-    load_row<kChunk>(p.b1, p.vec_dt, (size_t)gcol, ncols, p.bias_vec != 0, a);
+    {
+      const float4* s1 = reinterpret_cast<const float4*>(env.scratch + 2 * 4 * env.bn + col);
+      const float4* s2 = reinterpret_cast<const float4*>(env.scratch + 2 * 4 * env.bn + env.bn + col);
 #pragma unroll
-    for (int i = 0; i < kChunk; ++i) v[i] += a[i];                      // z1
-    load_row<kChunk>(p.b2, p.vec_dt, (size_t)gcol, ncols, p.bias_vec != 0, a);
-#pragma unroll
-    for (int i = 0; i < kChunk; ++i) tnh[i] = fast_tanh(tnh[i] + a[i]);  // t
+      for (int i = 0; i < kChunk / 4; ++i) {
+        const float4 x = s1[i], y = s2[i];
+        v[4 * i] += x.x; v[4 * i + 1] += x.y; v[4 * i + 2] += x.z; v[4 * i + 3] += x.w;   // z1
+        tnh[4 * i] = fast_tanh(tnh[4 * i] + y.x); tnh[4 * i + 1] = fast_tanh(tnh[4 * i + 1] + y.y);
+        tnh[4 * i + 2] = fast_tanh(tnh[4 * i + 2] + y.z); tnh[4 * i + 3] = fast_tanh(tnh[4 * i + 3] + y.w);   // t
+      }
+    }
     float mk[kChunk];
     // 16 bf16 columns are one 32-byte segment per lane.  Both 256-bit loads are issued before either is
     // unpacked, and both stores after both tiles are packed: measured 3.5 % faster on the 4096^3 README
@@ -529,6 +551,7 @@ struct EpiProgram {
 #pragma unroll
     for (int i = 0; i < 4; ++i) s.red[i] = p.red_op[i] == 1 ? -INFINITY : p.red_op[i] == 2 ? INFINITY : 0.0f;
   }
+  __device__ static void tile_prepare(const Params&, const EpiEnv&, const TileInfo&) {}
   __device__ static void chunk(const Params& p, const EpiEnv& env, const TileInfo& t, State& st, int row, int col, float (&v)[kChunk]) {
     const GemmCore& c = *env.core;
     const int grow = t.m0 + row, gcol = t.n0 + col;
@@ -860,6 +883,7 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmParams<typename Epi::Params> p) 
       const TileInfo t = decode_tile(tile);
       // After an abandoned wait the thread keeps walking the tile list without touching TMEM so
       // that the named barriers inside tile_end() still see every epilogue thread.
+      Epi::tile_prepare(p.epi, env, t);   // per-tile staging that does not need the accumulator
       if (!dead && !ptx::mbar_wait(bar_tmem_full(acc), acc_phase, abort_flag, c.status, 4, acc)) dead = true;
       dead = __any_sync(0xffffffffu, dead);   // the warp decides together (it shares a __syncwarp below)
       typename Epi::State st;

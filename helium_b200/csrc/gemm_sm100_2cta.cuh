@@ -294,6 +294,7 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ GemmParams<typename Epi::Params
       const TileInfo t = decode_tile(tile);
       const int kColsPerWarp = t.bn / (NE_WARPS / 4);
       const int col_begin = (env.epi_warp / 4) * kColsPerWarp;
+      Epi::tile_prepare(p.epi, env, t);   // per-tile staging that does not need the accumulator
       if (!dead && !ptx::mbar_wait(bar_tmem_full(acc), acc_phase, abort_flag, c.status, 4, acc)) dead = true;
       dead = __any_sync(0xffffffffu, dead);   // the warp decides together (it shares a __syncwarp below)
       typename Epi::State st;
