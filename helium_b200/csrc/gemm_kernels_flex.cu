@@ -32,6 +32,43 @@ __global__ void gemm_scalar_finalize(const float* __restrict__ partials, float* 
   if (threadIdx.x == 0) out[0] = s[0] * scale;
 }
 
+// The three folds of the README graph in one launch: blocks [0, nb) fold the first column-sum
+// partials, [nb, 2 nb) the second, the last block the scalar.  Same fixed orders as the kernels above.
+__global__ void gemm_readme_finalize(const float* __restrict__ col_a, float* __restrict__ out_a, const float* __restrict__ col_b,
+                                     float* __restrict__ out_b, int batch, int tiles_m, int N, const float* __restrict__ scal,
+                                     float* __restrict__ out_scal, int n_scal) {
+  const int nb = (batch * N + 255) / 256;
+  if ((int)blockIdx.x < 2 * nb) {
+    const bool second = (int)blockIdx.x >= nb;
+    const int i = ((int)blockIdx.x - (second ? nb : 0)) * 256 + threadIdx.x;
+    if (i >= batch * N) return;
+    const int b = i / N, n = i - b * N;
+    const float* p = (second ? col_b : col_a) + (size_t)b * tiles_m * N + n;
+    float s = p[0];
+    for (int t = 1; t < tiles_m; ++t) s += p[(size_t)t * N];
+    (second ? out_b : out_a)[i] = s;
+    return;
+  }
+  __shared__ float sh[256];
+  float v = 0.0f;
+  for (int i = threadIdx.x; i < n_scal; i += 256) v += scal[i];
+  sh[threadIdx.x] = v;
+  __syncthreads();
+  for (int off = 128; off > 0; off >>= 1) {
+    if ((int)threadIdx.x < off) sh[threadIdx.x] += sh[threadIdx.x + off];
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) out_scal[0] = sh[0];
+}
+
+int32_t launch_readme_finalize(const float* col_a, float* out_a, const float* col_b, float* out_b, int batch, int tiles_m, int N,
+                               const float* scal, float* out_scal, int n_scal, cudaStream_t stream) {
+  const int nb = (batch * N + 255) / 256;
+  gemm_readme_finalize<<<2 * nb + 1, 256, 0, stream>>>(col_a, out_a, col_b, out_b, batch, tiles_m, N, scal, out_scal, n_scal);
+  HE_CUDA(cudaGetLastError());
+  return HE_OK;
+}
+
 int32_t launch_gemm_flex(const GemmLaunchCfg& cfg, const GemmParams<EpiFlexParams>& p, cudaStream_t stream) {
   if (cfg.two_cta && cfg.bn == 256) {
     if (cfg.ml == ML_NONE) return launch_majors_2cta<6, ML_NONE, 8, EpiFlex>(cfg, p, stream);

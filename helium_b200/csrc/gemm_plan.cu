@@ -491,10 +491,9 @@ struct MatmulPlan : he_plan {
       p.epi.vec_ok = vec ? (vec32 ? 2 : 1) : 0;
       p.epi.bias_vec = (c.N % 8 == 0 && (uintptr_t)p.epi.b1 % 16 == 0 && (uintptr_t)p.epi.b2 % 16 == 0) ? 1 : 0;
       HE_TRY(launch_gemm_c3(cfg, p, stream));
-      HE_TRY(launch_colsum_finalize(ws + ws_col_off[0], (float*)outputs[r3.db2], c.batch, c.tiles_m, c.N, stream));
-      HE_TRY(launch_colsum_finalize(ws + ws_col_off[1], (float*)outputs[r3.db1], c.batch, c.tiles_m, c.N, stream));
-      HE_TRY(launch_scalar_finalize(ws + ws_scalar_off, (float*)outputs[r3.loss], c.num_tiles, stream));
-      last_launches = 4 + extra_launches;
+      HE_TRY(launch_readme_finalize(ws + ws_col_off[0], (float*)outputs[r3.db2], ws + ws_col_off[1], (float*)outputs[r3.db1], c.batch, c.tiles_m,
+                                    c.N, ws + ws_scalar_off, (float*)outputs[r3.loss], c.num_tiles, stream));
+      last_launches = 2 + extra_launches;
       return HE_OK;
     }
     GemmParams<EpiProgramParams> p;

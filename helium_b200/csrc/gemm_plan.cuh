@@ -20,6 +20,8 @@ int32_t launch_gemm_c3(const GemmLaunchCfg& cfg, const GemmParams<EpiC3Params>& 
 int32_t launch_gemm_program(const GemmLaunchCfg& cfg, const GemmParams<EpiProgramParams>& p, cudaStream_t stream);
 int32_t launch_colsum_finalize(const float* partials, float* out, int batch, int tiles_m, int N, cudaStream_t stream, int op = 0,
                                float scale = 1.0f);
+int32_t launch_readme_finalize(const float* col_a, float* out_a, const float* col_b, float* out_b, int batch, int tiles_m, int N,
+                               const float* scal, float* out_scal, int n_scal, cudaStream_t stream);
 int32_t launch_scalar_finalize(const float* partials, float* out, int n, cudaStream_t stream, int op = 0, float scale = 1.0f);
 // SIMT matmul: f32 operands, or 2-byte operands whose shapes break the TMA alignment rules
 // `axpy`: optional epilogue out = [resid +] [-] (acc * (mul ? mul[i] : alpha)); resid and mul have the
