@@ -269,6 +269,11 @@ __device__ __forceinline__ float fast_erf(float x) {
 // tanh x = 1 - 2 / (1 + e^(2x)) on the exp2 / reciprocal units: absolute error ~2e-7 (libm's tanhf
 // costs ~30 instructions per element, which made the README epilogue outlast its mainloop).
 // Saturates correctly: e = inf gives 1, e = 0 gives -1.
+__device__ __forceinline__ float exp2f_approx(float x) {
+  float r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+  return r;
+}
 __device__ __forceinline__ float fast_tanh(float x) { return 1.0f - __fdividef(2.0f, 1.0f + __expf(2.0f * x)); }
 __device__ __forceinline__ float fast_gelu(float x) { return 0.5f * x * (1.0f + fast_erf(x * 0.70710678118654752440f)); }
 __device__ __forceinline__ float fast_dgelu(float x) {
@@ -423,12 +428,29 @@ struct EpiC3 {
     {
       const float4* s1 = reinterpret_cast<const float4*>(env.scratch + 2 * 4 * env.bn + col);
       const float4* s2 = reinterpret_cast<const float4*>(env.scratch + 2 * 4 * env.bn + env.bn + col);
+      // z1 = c + b1 and t = tanh(c + b2) = 1 - 2 / (1 + e^(2 z2)) on column pairs: the adds, the scaling
+      // of the exponent and the final 1 - q are packed f32x2 operations with the roundings of fast_tanh
+      using u64 = unsigned long long;
+      const u64 one2 = ptx::f2_pack(1.0f, 1.0f), neg1b = ptx::f2_pack(-1.0f, -1.0f);
+      const u64 l2e2 = ptx::f2_pack(2.0f * 1.4426950408889634f, 2.0f * 1.4426950408889634f);
 #pragma unroll
       for (int i = 0; i < kChunk / 4; ++i) {
         const float4 x = s1[i], y = s2[i];
-        v[4 * i] += x.x; v[4 * i + 1] += x.y; v[4 * i + 2] += x.z; v[4 * i + 3] += x.w;   // z1
-        tnh[4 * i] = fast_tanh(tnh[4 * i] + y.x); tnh[4 * i + 1] = fast_tanh(tnh[4 * i + 1] + y.y);
-        tnh[4 * i + 2] = fast_tanh(tnh[4 * i + 2] + y.z); tnh[4 * i + 3] = fast_tanh(tnh[4 * i + 3] + y.w);   // t
+        const float bx[4] = {x.x, x.y, x.z, x.w}, by[4] = {y.x, y.y, y.z, y.w};
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const int k = 4 * i + 2 * h;
+          const u64 z1 = ptx::f2_fma(ptx::f2_pack(bx[2 * h], bx[2 * h + 1]), one2, ptx::f2_pack(v[k], v[k + 1]));
+          ptx::f2_unpack(z1, v[k], v[k + 1]);
+          const u64 z2 = ptx::f2_fma(ptx::f2_pack(by[2 * h], by[2 * h + 1]), one2, ptx::f2_pack(tnh[k], tnh[k + 1]));
+          float ea, eb;
+          ptx::f2_unpack(ptx::f2_mul(z2, l2e2), ea, eb);
+          const u64 s = ptx::f2_fma(ptx::f2_pack(exp2f_approx(ea), exp2f_approx(eb)), one2, one2);
+          float sa, sb;
+          ptx::f2_unpack(s, sa, sb);
+          const u64 q = ptx::f2_pack(__fdividef(2.0f, sa), __fdividef(2.0f, sb));
+          ptx::f2_unpack(ptx::f2_fma(q, neg1b, one2), tnh[k], tnh[k + 1]);
+        }
       }
     }
     float mk[kChunk];
@@ -466,15 +488,36 @@ struct EpiC3 {
       gz1 = z1 > 0.0f ? g * tm : 0.0f;
       dd = d;
     };
-    if (nvalid == kChunk) {   // interior chunk: no per-element predicates
+    if (nvalid == kChunk) {
+      // interior chunk: no per-element predicates, and the arithmetic runs on pairs of columns with the
+      // packed f32x2 instructions.  Every packed lane is the same IEEE operation as in `element`
+      // (t - m as fma(m, -1, t); (u * -g) * (t^2 - 1) for (u * g) * (1 - t^2): negation commutes with
+      // rounding), so both paths give the same bits; only the loss is summed as two interleaved chains.
+      using u64 = unsigned long long;
+      const u64 neg1 = ptx::f2_pack(-1.0f, -1.0f), gs2 = ptx::f2_pack(g_scale, g_scale), ngs2 = ptx::f2_pack(-g_scale, -g_scale);
+      u64 loss2 = ptx::f2_pack(0.0f, 0.0f);
 #pragma unroll
-      for (int i = 0; i < kChunk; ++i) {
-        float gt, gz1, d;
-        element(i, gt, gz1, d);
-        loss = fmaf(d, d, loss);
-        v[i] = gt;
-        tnh[i] = gz1;
+      for (int j = 0; j < kChunk / 2; ++j) {
+        const float z1a = v[2 * j], z1b = v[2 * j + 1];
+        const u64 u = ptx::f2_pack(fmaxf(z1a, 0.0f), fmaxf(z1b, 0.0f));
+        const u64 tt = ptx::f2_pack(tnh[2 * j], tnh[2 * j + 1]);
+        const u64 m = ptx::f2_pack(mk[2 * j], mk[2 * j + 1]);
+        const u64 y = ptx::f2_pack(a[2 * j], a[2 * j + 1]);
+        const u64 tm = ptx::f2_fma(m, neg1, tt);
+        const u64 d = ptx::f2_fma(y, neg1, ptx::f2_fma(u, tm, m));
+        const u64 g = ptx::f2_mul(d, gs2), ng = ptx::f2_mul(d, ngs2);
+        const u64 gt = ptx::f2_mul(ptx::f2_mul(u, ng), ptx::f2_fma(tt, tt, neg1));
+        const u64 gm = ptx::f2_mul(g, tm);
+        loss2 = ptx::f2_fma(d, d, loss2);
+        ptx::f2_unpack(gt, v[2 * j], v[2 * j + 1]);
+        float ga, gb;
+        ptx::f2_unpack(gm, ga, gb);
+        tnh[2 * j] = z1a > 0.0f ? ga : 0.0f;
+        tnh[2 * j + 1] = z1b > 0.0f ? gb : 0.0f;
       }
+      float la, lb;
+      ptx::f2_unpack(loss2, la, lb);
+      loss = la + lb;
     } else {
 #pragma unroll
       for (int i = 0; i < kChunk; ++i) {
