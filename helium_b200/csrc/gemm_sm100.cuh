@@ -274,6 +274,11 @@ __device__ __forceinline__ float exp2f_approx(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
   return r;
 }
+__device__ __forceinline__ float rcp_approx(float x) {
+  float r;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+  return r;
+}
 __device__ __forceinline__ float fast_tanh(float x) { return 1.0f - __fdividef(2.0f, 1.0f + __expf(2.0f * x)); }
 __device__ __forceinline__ float fast_gelu(float x) { return 0.5f * x * (1.0f + fast_erf(x * 0.70710678118654752440f)); }
 __device__ __forceinline__ float fast_dgelu(float x) {
@@ -431,7 +436,7 @@ struct EpiC3 {
       // z1 = c + b1 and t = tanh(c + b2) = 1 - 2 / (1 + e^(2 z2)) on column pairs: the adds, the scaling
       // of the exponent and the final 1 - q are packed f32x2 operations with the roundings of fast_tanh
       using u64 = unsigned long long;
-      const u64 one2 = ptx::f2_pack(1.0f, 1.0f), neg1b = ptx::f2_pack(-1.0f, -1.0f);
+      const u64 one2 = ptx::f2_pack(1.0f, 1.0f), neg2b = ptx::f2_pack(-2.0f, -2.0f);
       const u64 l2e2 = ptx::f2_pack(2.0f * 1.4426950408889634f, 2.0f * 1.4426950408889634f);
 #pragma unroll
       for (int i = 0; i < kChunk / 4; ++i) {
@@ -448,8 +453,9 @@ struct EpiC3 {
           const u64 s = ptx::f2_fma(ptx::f2_pack(exp2f_approx(ea), exp2f_approx(eb)), one2, one2);
           float sa, sb;
           ptx::f2_unpack(s, sa, sb);
-          const u64 q = ptx::f2_pack(__fdividef(2.0f, sa), __fdividef(2.0f, sb));
-          ptx::f2_unpack(ptx::f2_fma(q, neg1b, one2), tnh[k], tnh[k + 1]);
+          // 1 + e >= 1, so the bare reciprocal needs none of the range handling of an approximate divide
+          const u64 r = ptx::f2_pack(rcp_approx(sa), rcp_approx(sb));
+          ptx::f2_unpack(ptx::f2_fma(r, neg2b, one2), tnh[k], tnh[k + 1]);
         }
       }
     }
