@@ -286,13 +286,66 @@ __device__ __forceinline__ float fast_dgelu(float x) {
   return fmaf(x * 0.39894228040143267794f, __expf(-0.5f * x * x), cdf);
 }
 
+// ---- GELU / GELU' on column pairs -----------------------------------------------------------------
+// The same approximations as fast_erf / fast_gelu / fast_dgelu with the polynomial, the scalings and the
+// final combinations as packed f32x2 operations (two IEEE-rounded f32 results per instruction); only the
+// reciprocal and the exponential stay scalar.  1 + 0.3275911 |x| >= 1, so the bare reciprocal is safe.
+__device__ __forceinline__ unsigned long long erf_pair(unsigned long long x2) {
+  using u64 = unsigned long long;
+  const u64 ax = x2 & 0x7fffffff7fffffffull;
+  float da, db;
+  ptx::f2_unpack(ptx::f2_fma(ax, ptx::f2_pack(0.3275911f, 0.3275911f), ptx::f2_pack(1.0f, 1.0f)), da, db);
+  const u64 t = ptx::f2_pack(rcp_approx(da), rcp_approx(db));
+  u64 poly = ptx::f2_fma(ptx::f2_pack(1.061405429f, 1.061405429f), t, ptx::f2_pack(-1.453152027f, -1.453152027f));
+  poly = ptx::f2_fma(poly, t, ptx::f2_pack(1.421413741f, 1.421413741f));
+  poly = ptx::f2_fma(poly, t, ptx::f2_pack(-0.284496736f, -0.284496736f));
+  poly = ptx::f2_fma(poly, t, ptx::f2_pack(0.254829592f, 0.254829592f));
+  float ea, eb;
+  ptx::f2_unpack(ptx::f2_mul(ptx::f2_mul(ax, ax), ptx::f2_pack(-1.4426950408889634f, -1.4426950408889634f)), ea, eb);
+  const u64 e = ptx::f2_pack(exp2f_approx(ea), exp2f_approx(eb));
+  const u64 y = ptx::f2_fma(ptx::f2_mul(ptx::f2_mul(poly, t), e), ptx::f2_pack(-1.0f, -1.0f), ptx::f2_pack(1.0f, 1.0f));
+  return y | (x2 & 0x8000000080000000ull);   // y is in [0, 1]: or-ing the sign of x is copysign
+}
+__device__ __forceinline__ void gelu_pair(float& a, float& b) {
+  const unsigned long long x2 = ptx::f2_pack(a, b);
+  const unsigned long long e2 = erf_pair(ptx::f2_mul(x2, ptx::f2_pack(0.70710678118654752440f, 0.70710678118654752440f)));
+  const unsigned long long hx = ptx::f2_mul(x2, ptx::f2_pack(0.5f, 0.5f));
+  ptx::f2_unpack(ptx::f2_fma(hx, e2, hx), a, b);   // 0.5 x (1 + erf)
+}
+// (va, vb) *= gelu'(xa, xb)
+__device__ __forceinline__ void dgelu_mul_pair(float& va, float& vb, float xa, float xb) {
+  using u64 = unsigned long long;
+  const u64 x2 = ptx::f2_pack(xa, xb);
+  const u64 e2 = erf_pair(ptx::f2_mul(x2, ptx::f2_pack(0.70710678118654752440f, 0.70710678118654752440f)));
+  const u64 cdf = ptx::f2_fma(e2, ptx::f2_pack(0.5f, 0.5f), ptx::f2_pack(0.5f, 0.5f));
+  float pa, pb;
+  ptx::f2_unpack(ptx::f2_mul(ptx::f2_mul(x2, x2), ptx::f2_pack(-0.5f * 1.4426950408889634f, -0.5f * 1.4426950408889634f)), pa, pb);
+  const u64 pdf = ptx::f2_pack(exp2f_approx(pa), exp2f_approx(pb));
+  const u64 d = ptx::f2_fma(ptx::f2_mul(x2, ptx::f2_pack(0.39894228040143267794f, 0.39894228040143267794f)), pdf, cdf);
+  ptx::f2_unpack(ptx::f2_mul(ptx::f2_pack(va, vb), d), va, vb);
+}
+
 struct EpiFlex {
   using Params = EpiFlexParams;
-  static constexpr int kColReductions = 1;
+  // block 0: column-sum scratch; block 1: the tile's bias slice as f32 (tile_prepare)
+  static constexpr int kColReductions = 2;
   static constexpr int kChunk = 32;
   struct State {};
   __device__ static void tile_begin(const Params&, State&) {}
-  __device__ static void tile_prepare(const Params&, const EpiEnv&, const TileInfo&) {}
+  // Every epilogue thread, once per tile, before the accumulator is awaited: the tile's bias slice goes
+  // to shared memory as f32, so that the chunks do not put an L2 round trip on their dependent chain.
+  // The previous tile's readers are behind this barrier pair and the barriers of tile_end.
+  __device__ static void tile_prepare(const Params& p, const EpiEnv& env, const TileInfo& t) {
+    if (!p.bias) return;
+    ptx::named_barrier_sync(1, env.n_epi_threads);   // the previous tile's chunks are done with the slice
+    float* bs = env.scratch + 4 * env.bn;
+    const int n = env.core->N;
+    for (int i = env.epi_tid; i < env.bn; i += env.n_epi_threads) {
+      const int gc = t.n0 + i;
+      bs[i] = gc < n ? load_param_as_f32(p.bias, p.bias_dt, gc) : 0.0f;
+    }
+    ptx::named_barrier_sync(1, env.n_epi_threads);
+  }
   // The op selectors are uniform per launch: switch once per chunk, not once per element.
   __device__ static void activate(int act, float (&v)[kChunk]) {
     switch (act) {
@@ -302,7 +355,7 @@ struct EpiFlex {
         break;
       case ACT_GELU:
 #pragma unroll
-        for (int i = 0; i < kChunk; ++i) v[i] = fast_gelu(v[i]);
+        for (int i = 0; i < kChunk; i += 2) gelu_pair(v[i], v[i + 1]);
         break;
       case ACT_TANH:
 #pragma unroll
@@ -315,7 +368,7 @@ struct EpiFlex {
     switch (g) {
       case GATE_DGELU:
 #pragma unroll
-        for (int i = 0; i < kChunk; ++i) v[i] *= fast_dgelu(x[i]);
+        for (int i = 0; i < kChunk; i += 2) dgelu_mul_pair(v[i], v[i + 1], x[i], x[i + 1]);
         break;
       case GATE_DRELU:
 #pragma unroll
@@ -339,10 +392,12 @@ struct EpiFlex {
     const int vec = p.vec_ok;
     float aux[kChunk];
     if (p.bias) {
-      // every lane of the warp reads the same kChunk bias values: vector loads that hit L1
-      load_row<kChunk>(p.bias, p.bias_dt, (size_t)gcol, max(0, min(kChunk, c.N - gcol)), p.bias_vec != 0, aux);
+      const float4* bs = reinterpret_cast<const float4*>(env.scratch + 4 * env.bn + col);   // staged by tile_prepare
 #pragma unroll
-      for (int i = 0; i < kChunk; ++i) v[i] += aux[i];
+      for (int i = 0; i < kChunk / 4; ++i) {
+        const float4 b = bs[i];
+        v[4 * i] += b.x; v[4 * i + 1] += b.y; v[4 * i + 2] += b.z; v[4 * i + 3] += b.w;
+      }
     }
     if (p.resid) {
       load_row<kChunk>(p.resid, p.resid_dt, off, nvalid, vec, aux);
