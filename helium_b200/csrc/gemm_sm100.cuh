@@ -290,7 +290,7 @@ __device__ __forceinline__ float fast_dgelu(float x) {
 // The same approximations as fast_erf / fast_gelu / fast_dgelu with the polynomial, the scalings and the
 // final combinations as packed f32x2 operations (two IEEE-rounded f32 results per instruction); only the
 // reciprocal and the exponential stay scalar.  1 + 0.3275911 |x| >= 1, so the bare reciprocal is safe.
-__device__ __forceinline__ unsigned long long erf_pair(unsigned long long x2) {
+__device__ __forceinline__ unsigned long long erf_pair(unsigned long long x2, unsigned long long* exp_neg_sq = nullptr) {
   using u64 = unsigned long long;
   const u64 ax = x2 & 0x7fffffff7fffffffull;
   float da, db;
@@ -303,6 +303,7 @@ __device__ __forceinline__ unsigned long long erf_pair(unsigned long long x2) {
   float ea, eb;
   ptx::f2_unpack(ptx::f2_mul(ptx::f2_mul(ax, ax), ptx::f2_pack(-1.4426950408889634f, -1.4426950408889634f)), ea, eb);
   const u64 e = ptx::f2_pack(exp2f_approx(ea), exp2f_approx(eb));
+  if (exp_neg_sq) *exp_neg_sq = e;   // exp(-x^2) of the argument, for callers that need it as well
   const u64 y = ptx::f2_fma(ptx::f2_mul(ptx::f2_mul(poly, t), e), ptx::f2_pack(-1.0f, -1.0f), ptx::f2_pack(1.0f, 1.0f));
   return y | (x2 & 0x8000000080000000ull);   // y is in [0, 1]: or-ing the sign of x is copysign
 }
@@ -316,11 +317,10 @@ __device__ __forceinline__ void gelu_pair(float& a, float& b) {
 __device__ __forceinline__ void dgelu_mul_pair(float& va, float& vb, float xa, float xb) {
   using u64 = unsigned long long;
   const u64 x2 = ptx::f2_pack(xa, xb);
-  const u64 e2 = erf_pair(ptx::f2_mul(x2, ptx::f2_pack(0.70710678118654752440f, 0.70710678118654752440f)));
+  // erf is taken at x / sqrt 2, whose exp(-(.)^2) is the exp(-x^2 / 2) of the density term
+  u64 pdf;
+  const u64 e2 = erf_pair(ptx::f2_mul(x2, ptx::f2_pack(0.70710678118654752440f, 0.70710678118654752440f)), &pdf);
   const u64 cdf = ptx::f2_fma(e2, ptx::f2_pack(0.5f, 0.5f), ptx::f2_pack(0.5f, 0.5f));
-  float pa, pb;
-  ptx::f2_unpack(ptx::f2_mul(ptx::f2_mul(x2, x2), ptx::f2_pack(-0.5f * 1.4426950408889634f, -0.5f * 1.4426950408889634f)), pa, pb);
-  const u64 pdf = ptx::f2_pack(exp2f_approx(pa), exp2f_approx(pb));
   const u64 d = ptx::f2_fma(ptx::f2_mul(x2, ptx::f2_pack(0.39894228040143267794f, 0.39894228040143267794f)), pdf, cdf);
   ptx::f2_unpack(ptx::f2_mul(ptx::f2_pack(va, vb), d), va, vb);
 }
