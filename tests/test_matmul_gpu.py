@@ -219,6 +219,41 @@ def test_low_precision_requests_are_served_at_or_above_their_minimum(ctx):
             assert O.rel_l2(dec(got[0]), dec(want[0])) < 0.1 * O.rel_l2(dec(narrow[0]), dec(want[0])), plan.description
 
 
+def test_gelu_epilogues_at_extreme_arguments(ctx):
+    """GELU and gelu' in the GEMM epilogue at arguments far from the random-normal range: the product is
+    zero (A = 0), so the outputs are gelu(bias[col]) and gelu'(G[row, col]) of hand-picked values --
+    zeros of both signs, tiny, the bulk, the tails where erf saturates, and infinities -- checked
+    element by element (f32 outputs, absolute error: the polynomial erf is good to 1.5e-7)."""
+    m, n, k = 128, 256, 64
+    vals = np.array([0.0, -0.0, 1e-30, -1e-30, 1e-4, -1e-4, 0.5, -0.5, 1.0, -1.0, 2.5, -2.5, 4.0, -4.0, 6.0, -6.0,
+                     9.0, -9.0, 13.0, -13.0, 40.0, -40.0, 300.0, -300.0, 3.0e4, -3.0e4, np.inf, 0.25, -0.25, 3.0, -3.0, 1.5], dtype=np.float64)
+    # forward: gelu(0 + bias)
+    g = graph_linear(m, n, k, bias=True, act=ir.UN_GELU, dtype=ir.BF16, out_dtype=ir.F32)
+    ins = _gen(g, 91)
+    ins[0] = O.encode(np.zeros((m, k)), ir.BF16)
+    ins[2] = O.encode(np.resize(vals, n), ir.BF16)
+    got, plan = _run(ctx, g, ins)
+    want = O.evaluate(g, ins)
+    a = O.decode(got[0], ir.F32, (m, n)); b = O.decode(want[0], ir.F32, (m, n))
+    fin = np.isfinite(b)
+    assert np.array_equal(np.isfinite(a), fin), plan.description
+    assert np.allclose(a[fin], b[fin], rtol=2e-6, atol=2e-6), float(np.abs(a[fin] - b[fin]).max())
+    assert np.array_equal(a[~fin], b[~fin])
+    # backward: (1 + 0) * gelu'(G), with the column sum
+    g = graph_linear(m, n, k, bias=True, gate="dgelu", colsum="y", dtype=ir.BF16, out_dtype=ir.F32)
+    ins = _gen(g, 92)
+    ins[0] = O.encode(np.zeros((m, k)), ir.BF16)
+    ins[2] = O.encode(np.ones(n), ir.BF16)
+    gv = np.resize(vals[np.isfinite(vals)], (m, n))
+    ins[3] = O.encode(gv, ir.BF16)
+    got, plan = _run(ctx, g, ins)
+    want = O.evaluate(g, ins)
+    a = O.decode(got[0], ir.F32, (m, n)); b = O.decode(want[0], ir.F32, (m, n))
+    assert np.allclose(a, b, rtol=2e-6, atol=2e-6), (plan.description, float(np.abs(a - b).max()))
+    cs_a = np.asarray(got[1], dtype=np.float64).reshape(-1); cs_b = np.asarray(want[1], dtype=np.float64).reshape(-1)
+    assert np.allclose(cs_a, cs_b, rtol=1e-5, atol=1e-4)
+
+
 def test_mlp_block_forward_backward(ctx):
     """configs[3] at a small size: every one of the six fused GEMMs against the oracle evaluated on
     the operands that GEMM actually read (so an upstream rounding does not hide a downstream error)."""
