@@ -118,6 +118,23 @@ def test_readme_graph(ctx, m, n, k, with_e):
         assert np.array_equal(x, y), "reductions must be bit-stable across launches"
 
 
+def test_readme_graph_with_saturating_biases(ctx):
+    """The README epilogue where tanh saturates and relu switches: the product is zero (A = 0) and b1 / b2
+    carry zeros of both signs, tiny values, the bulk and +-3 ... +-200, so z1 = b1 and t = tanh(b2) exactly
+    as the oracle sees them."""
+    m, n, k = 256, 512, 128
+    g = graph_c3(m, n, k, False)
+    ins = _c3_inputs(m, n, k, False)
+    vals = np.array([0.0, -0.0, 1e-20, -1e-20, 0.01, -0.01, 0.5, -0.5, 1.0, -1.0, 3.0, -3.0, 8.0, -8.0, 12.0, -12.0,
+                     45.0, -45.0, 90.0, -90.0, 200.0, -200.0, 0.25, -0.25], dtype=np.float64)
+    ins[0] = O.encode(np.zeros((1, m, k)), ir.BF16)
+    ins[3] = O.encode(np.resize(vals, (1, 1, n)), ir.BF16)
+    ins[4] = O.encode(np.resize(np.roll(vals, 5), (1, 1, n)), ir.BF16)
+    got, plan = _run(ctx, g, ins)
+    assert "README graph" in plan.description
+    _compare(g, got, O.evaluate(g, ins), plan.description)
+
+
 def test_readme_graph_full_size_against_c_oracle(ctx):
     """BASELINE config 3 at 4096^3.  The numpy oracle would take minutes, so: 256 sampled rows go
     through the C oracle (bit-identical semantics, f32), and the reductions are cross-checked
