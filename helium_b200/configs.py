@@ -32,7 +32,7 @@ def bf16_bernoulli(g: np.random.Generator, shape, p: float = 0.5) -> np.ndarray:
 
 
 def graph_affine_relu_permute(n, c, h, w, x_dtype=ir.BF16, p_dtype=ir.F32) -> ir.Graph:
-    """BASELINE config 2a: relu(x * s_c + b_c) on NCHW, written NHWC (swap_dims(1,2).swap_dims(2,3))."""
+    """The fused affine + relu + layout change benchmark graph: relu(x * s_c + b_c) on NCHW, written NHWC (swap_dims(1,2).swap_dims(2,3))."""
     g = ir.Graph()
     x = g.new_input([n, c, h, w], x_dtype)
     s = g.new_input([c], p_dtype)

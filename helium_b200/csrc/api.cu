@@ -203,7 +203,8 @@ int32_t he_ctx_create(int32_t device_ordinal, he_ctx** out) {
             e == cudaSuccess ? "device count is 0" : cudaGetErrorString(e));
   if (device_ordinal < 0 || device_ordinal >= count)
     HE_FAIL(HE_ERR_INVALID, "device ordinal %d out of range (0..%d)", device_ordinal, count - 1);
-  HE_CUDA(cudaSetDevice(device_ordinal));
+  DeviceGuard guard(device_ordinal);
+  HE_TRY(guard.status());
   cudaDeviceProp prop;
   HE_CUDA(cudaGetDeviceProperties(&prop, device_ordinal));
   if (prop.major != 10)
@@ -337,9 +338,8 @@ int32_t he_launch(he_plan* plan, const void* const* inputs, void* const* outputs
     if (!workspace) HE_FAIL(HE_ERR_WORKSPACE, "plan needs %zu workspace bytes but workspace is null", plan->workspace_bytes);
     if ((uintptr_t)workspace % 256 != 0) HE_FAIL(HE_ERR_WORKSPACE, "workspace must be 256-byte aligned");
   }
-  int dev = -1;
-  HE_CUDA(cudaGetDevice(&dev));
-  if (dev != plan->ctx->device) HE_CUDA(cudaSetDevice(plan->ctx->device));
+  DeviceGuard guard(plan->ctx->device);   // restores the caller's current device on return
+  HE_TRY(guard.status());
   plan->last_launches = 0;
   return plan->launch(inputs, outputs, workspace, (cudaStream_t)cu_stream);
 }
@@ -383,6 +383,11 @@ int32_t he_debug_canonical_text(const he_graph_desc* desc, char* buf, size_t cap
   if (!buf || cap < canon.text.size() + 1) HE_FAIL(HE_ERR_INVALID, "he_debug_canonical_text: buffer too small (need %zu)", canon.text.size() + 1);
   memcpy(buf, canon.text.c_str(), canon.text.size() + 1);
   return HE_OK;
+}
+
+int32_t he_debug_plan_fault_injection(he_plan* plan, uint32_t wait_limit_us, int32_t withhold_loads) {
+  if (!plan) HE_FAIL(HE_ERR_INVALID, "he_debug_plan_fault_injection: plan is null");
+  return plan->set_fault_injection(wait_limit_us, withhold_loads);
 }
 
 int32_t he_plan_last_launch_count(const he_plan* plan) { return plan ? plan->last_launches : 0; }

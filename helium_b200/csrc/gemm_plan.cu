@@ -396,6 +396,13 @@ struct MatmulPlan : he_plan {
   bool materialise_a = false;
   size_t ws_aprime_off = 0;   // bytes
 
+  int32_t set_fault_injection(uint32_t wait_limit_us, int32_t withhold_loads) override {
+    if (kind == EpiKind::Sgemm) HE_FAIL(HE_ERR_UNSUPPORTED, "the SIMT matmul has no device-side waits to bound");
+    core.wait_limit_us = wait_limit_us ? wait_limit_us : ptx::kDefaultWaitLimitUs;
+    core.withhold_loads = withhold_loads ? 1 : 0;
+    return HE_OK;
+  }
+
   int32_t launch(const void* const* inputs, void* const* outputs, void* workspace, cudaStream_t stream) override {
     for (int i = 0; i < n_inputs; ++i)
       if (!inputs || !inputs[i]) HE_FAIL(HE_ERR_INVALID, "fused matmul launch: input %d is null", i);
@@ -583,6 +590,10 @@ struct PrologueMatmulPlan : he_plan {
     size_t off = 0;           // bytes into the workspace
   };
   std::vector<Pro> pros;      // in the order their results were appended to the inner plan's inputs
+
+  int32_t set_fault_injection(uint32_t wait_limit_us, int32_t withhold_loads) override {
+    return inner->set_fault_injection(wait_limit_us, withhold_loads);
+  }
 
   int32_t launch(const void* const* inputs, void* const* outputs, void* workspace, cudaStream_t stream) override {
     if (!workspace) HE_FAIL(HE_ERR_WORKSPACE, "fused matmul launch: this plan needs a %zu-byte workspace", workspace_bytes);
@@ -832,11 +843,9 @@ int32_t plan_fused_matmul_core(he_ctx* ctx, const Graph& g, he_plan** out, int* 
   if (!((An.dtype == HE_BF16 && Bn.dtype == HE_BF16) || (An.dtype == HE_F16 && Bn.dtype == HE_F16)))
     HE_FAIL(HE_ERR_UNSUPPORTED, "fused matmul: operands must both be bf16, both f16 or both f32 (got %s x %s)", dtype_name(An.dtype), dtype_name(Bn.dtype));
   c.ab_format = An.dtype == HE_BF16 ? 1 : 0;
-  {
-    const char* dbg = getenv("HE_GEMM_DEBUG");
-    c.debug = dbg ? atoi(dbg) : 0;
-    c.group_m = 1;
-  }
+  c.group_m = 1;
+  c.wait_limit_us = ptx::kDefaultWaitLimitUs;
+  c.withhold_loads = 0;
   if (plan->cfg.ml != ML_NONE && plan->cfg.ml != ML_RELU_MASK)
     HE_FAIL(HE_ERR_UNSUPPORTED, "fused matmul: only the relu(A) * mask mainloop fusion is compiled in");
   if (plan->cfg.ml != ML_NONE && (An.dtype != HE_BF16 || g.nodes[A.mask].dtype != HE_BF16))

@@ -37,7 +37,12 @@ struct GemmCore {
   // Pair-tile kernel only: tiles [split_from, split_from + split_count) of the tile list are walked
   // as two half-width tiles each, by different CTA pairs (see finish_tiles in gemm_plan.cu).
   int split_from, split_count;
-  int debug;      // timing experiments only (HE_GEMM_DEBUG): bit 0 skips the mainloop rewrite, bit 1 its proxy fence
+  // Bound of every device-side wait in microseconds (2 s by default).  `withhold_loads` is the host-side
+  // fault injection of the tests: the TMA producers issue nothing, so the first wait on a full barrier
+  // runs into the limit and the kernel leaves through its abort path (results are then undefined and
+  // he_ctx_poll_device_status reports HE_ERR_DEVICE_TIMEOUT).  Set only by he_debug_plan_fault_injection.
+  unsigned wait_limit_us;
+  int withhold_loads;
   DeviceStatus* status;
 };
 
@@ -894,10 +899,10 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmParams<typename Epi::Params> p) 
       int stage = 0;
       uint32_t phase = 0;
       bool alive = true;
-      for (int tile = blockIdx.x; alive && tile < c.num_tiles; tile += gridDim.x) {
+      for (int tile = blockIdx.x; alive && !c.withhold_loads && tile < c.num_tiles; tile += gridDim.x) {
         const TileInfo t = decode_tile(tile);
         for (int kb = 0; kb < c.k_blocks; ++kb) {
-          if (!ptx::mbar_wait(bar_empty(stage), phase ^ 1u, abort_flag, c.status, 1, stage)) { alive = false; break; }
+          if (!ptx::mbar_wait(bar_empty(stage), phase ^ 1u, abort_flag, c.status, 1, stage, c.wait_limit_us)) { alive = false; break; }
           ptx::mbar_arrive_expect_tx(bar_full(stage), kStageBytes);
           const int k0 = kb * kBK;
           const uint32_t a_dst = smem_base + SM::off_a + stage * kATileBytes;
@@ -946,12 +951,12 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmParams<typename Epi::Params> p) 
       for (int tile = blockIdx.x; alive && tile < c.num_tiles; tile += gridDim.x, ++it) {
         const int acc = it & 1;
         const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
-        if (!ptx::mbar_wait(bar_tmem_empty(acc), acc_phase ^ 1u, abort_flag, c.status, 2, acc)) { alive = false; break; }
+        if (!ptx::mbar_wait(bar_tmem_empty(acc), acc_phase ^ 1u, abort_flag, c.status, 2, acc, c.wait_limit_us)) { alive = false; break; }
         ptx::tcgen05_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
         for (int kb = 0; kb < c.k_blocks; ++kb) {
           const uint32_t ready = (ML != ML_NONE) ? bar_xform(stage) : bar_full(stage);
-          if (!ptx::mbar_wait(ready, phase, abort_flag, c.status, 3, stage)) { alive = false; break; }
+          if (!ptx::mbar_wait(ready, phase, abort_flag, c.status, 3, stage, c.wait_limit_us)) { alive = false; break; }
           ptx::tcgen05_fence_after();
           const uint32_t a_addr = smem_base + SM::off_a + stage * kATileBytes;
           const uint32_t b_addr = smem_base + SM::off_b + stage * SM::kBTileBytes;
@@ -988,7 +993,7 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmParams<typename Epi::Params> p) 
       // After an abandoned wait the thread keeps walking the tile list without touching TMEM so
       // that the named barriers inside tile_end() still see every epilogue thread.
       Epi::tile_prepare(p.epi, env, t);   // per-tile staging that does not need the accumulator
-      if (!dead && !ptx::mbar_wait(bar_tmem_full(acc), acc_phase, abort_flag, c.status, 4, acc)) dead = true;
+      if (!dead && !ptx::mbar_wait(bar_tmem_full(acc), acc_phase, abort_flag, c.status, 4, acc, c.wait_limit_us)) dead = true;
       dead = __any_sync(0xffffffffu, dead);   // the warp decides together (it shares a __syncwarp below)
       typename Epi::State st;
       Epi::tile_begin(p.epi, st);
@@ -1018,13 +1023,12 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmParams<typename Epi::Params> p) 
       bool alive = true;
       for (int tile = blockIdx.x; alive && tile < c.num_tiles; tile += gridDim.x) {
         for (int kb = 0; kb < c.k_blocks; ++kb) {
-          const bool ok = ptx::mbar_wait(bar_full(stage), phase, abort_flag, c.status, 5, stage);
+          const bool ok = ptx::mbar_wait(bar_full(stage), phase, abort_flag, c.status, 5, stage, c.wait_limit_us);
           if (!__all_sync(0xffffffffu, ok)) { alive = false; break; }
           uint4* a = reinterpret_cast<uint4*>(smem + SM::off_a + stage * kATileBytes);
           const uint4* mk = reinterpret_cast<const uint4*>(smem + SM::off_mask + stage * kATileBytes);
           // A and the mask were loaded with the same box and swizzle, so equal smem offsets hold
           // the same (row, k) element: the rewrite is position-wise.
-          if (!(c.debug & 1))
 #pragma unroll
           for (int i = 0; i < kATileBytes / 16 / 128; ++i) {
             const int idx = tt + i * 128;
@@ -1043,7 +1047,7 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmParams<typename Epi::Params> p) 
             }
             a[idx] = va;
           }
-          if (!(c.debug & 2)) ptx::fence_proxy_async_smem();   // every writer publishes its own stores to the async proxy
+          ptx::fence_proxy_async_smem();   // every writer publishes its own stores to the async proxy
           __syncwarp();
           if (lane == 0) ptx::mbar_arrive(bar_xform(stage));
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }

@@ -185,10 +185,10 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ GemmParams<typename Epi::Params
       int stage = 0;
       uint32_t phase = 0;
       bool alive = true;
-      for (int tile = pair; alive && tile < pair_tiles; tile += n_pairs) {
+      for (int tile = pair; alive && !c.withhold_loads && tile < pair_tiles; tile += n_pairs) {
         const TileInfo t = decode_tile(tile);
         for (int kb = 0; kb < c.k_blocks; ++kb) {
-          if (!ptx::mbar_wait(bar_empty(stage), phase ^ 1u, abort_flag, c.status, 1, stage)) { alive = false; break; }
+          if (!ptx::mbar_wait(bar_empty(stage), phase ^ 1u, abort_flag, c.status, 1, stage, c.wait_limit_us)) { alive = false; break; }
           const uint32_t leader_full = ptx::mapa(bar_full_b(stage), 0);
           // a half-width tile needs 64 columns of B per CTA: with N-major B that is one of the two
           // 64-column boxes; with K-major B the full 128-row box is fetched and half of it ignored
@@ -249,13 +249,13 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ GemmParams<typename Epi::Params
       for (int tile = pair; alive && tile < pair_tiles; tile += n_pairs, ++it) {
         const int acc = it & 1;
         const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
-        if (!ptx::mbar_wait(bar_tmem_empty(acc), acc_phase ^ 1u, abort_flag, c.status, 2, acc)) { alive = false; break; }
+        if (!ptx::mbar_wait(bar_tmem_empty(acc), acc_phase ^ 1u, abort_flag, c.status, 2, acc, c.wait_limit_us)) { alive = false; break; }
         ptx::tcgen05_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
         const uint32_t idesc = (c.split_count > 0 && tile >= c.split_from) ? idesc_half : idesc_full;
         for (int kb = 0; kb < c.k_blocks; ++kb) {
-          if (!ptx::mbar_wait(bar_full_b(stage), phase, abort_flag, c.status, 3, stage)) { alive = false; break; }
-          if (kFused && !ptx::mbar_wait(bar_xform(stage), phase, abort_flag, c.status, 6, stage)) { alive = false; break; }
+          if (!ptx::mbar_wait(bar_full_b(stage), phase, abort_flag, c.status, 3, stage, c.wait_limit_us)) { alive = false; break; }
+          if (kFused && !ptx::mbar_wait(bar_xform(stage), phase, abort_flag, c.status, 6, stage, c.wait_limit_us)) { alive = false; break; }
           ptx::tcgen05_fence_after();
           const uint32_t a_addr = smem_base + SM::off_a + stage * kATileBytes;
           const uint32_t b_addr = smem_base + SM::off_b + stage * kBHalfBytes;
@@ -295,7 +295,7 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ GemmParams<typename Epi::Params
       const int kColsPerWarp = t.bn / (NE_WARPS / 4);
       const int col_begin = (env.epi_warp / 4) * kColsPerWarp;
       Epi::tile_prepare(p.epi, env, t);   // per-tile staging that does not need the accumulator
-      if (!dead && !ptx::mbar_wait(bar_tmem_full(acc), acc_phase, abort_flag, c.status, 4, acc)) dead = true;
+      if (!dead && !ptx::mbar_wait(bar_tmem_full(acc), acc_phase, abort_flag, c.status, 4, acc, c.wait_limit_us)) dead = true;
       dead = __any_sync(0xffffffffu, dead);   // the warp decides together (it shares a __syncwarp below)
       typename Epi::State st;
       Epi::tile_begin(p.epi, st);
@@ -325,11 +325,10 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ GemmParams<typename Epi::Params
       bool alive = true;
       for (int tile = pair; alive && tile < pair_tiles; tile += n_pairs) {
         for (int kb = 0; kb < c.k_blocks; ++kb) {
-          const bool ok = ptx::mbar_wait(bar_full_a(stage), phase, abort_flag, c.status, 5, stage);
+          const bool ok = ptx::mbar_wait(bar_full_a(stage), phase, abort_flag, c.status, 5, stage, c.wait_limit_us);
           if (!__all_sync(0xffffffffu, ok)) { alive = false; break; }
           uint4* a = reinterpret_cast<uint4*>(smem + SM::off_a + stage * kATileBytes);
           const uint4* mk = reinterpret_cast<const uint4*>(smem + SM::off_mask + stage * kATileBytes);
-          if (!(c.debug & 1))
 #pragma unroll
           for (int i = 0; i < kATileBytes / 16 / 128; ++i) {
             const int idx = tt + i * 128;
@@ -348,7 +347,7 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ GemmParams<typename Epi::Params
             }
             a[idx] = va;
           }
-          if (!(c.debug & 2)) ptx::fence_proxy_async_smem();
+          ptx::fence_proxy_async_smem();
           __syncwarp();
           if (lane == 0) ptx::mbar_arrive_cluster(ptx::mapa(bar_xform(stage), 0));
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }

@@ -88,9 +88,38 @@ struct he_plan {
   virtual ~he_plan() {}
   virtual int32_t launch(const void* const* inputs, void* const* outputs, void* workspace,
                          cudaStream_t stream) = 0;
+  // he_debug_plan_fault_injection: only plans whose kernels contain bounded waits implement it
+  virtual int32_t set_fault_injection(uint32_t /*wait_limit_us*/, int32_t /*withhold_loads*/) {
+    he::set_error("this plan's kernels have no device-side waits to bound");
+    return HE_ERR_UNSUPPORTED;
+  }
 };
 
 namespace he {
+
+// Makes `device` current for a scope and restores the caller's device afterwards, so that a host
+// thread driving several GPUs does not find its current device changed by a library call.
+class DeviceGuard {
+ public:
+  explicit DeviceGuard(int device) {
+    if (cudaGetDevice(&prev_) != cudaSuccess) { prev_ = -1; failed_ = true; return; }
+    if (prev_ != device) {
+      if (cudaSetDevice(device) != cudaSuccess) failed_ = true;
+      else switched_ = true;
+    }
+  }
+  ~DeviceGuard() {
+    if (switched_) cudaSetDevice(prev_);
+  }
+  int32_t status() const {
+    if (!failed_) return HE_OK;
+    set_error("could not make the plan's device current: %s", cudaGetErrorString(cudaGetLastError()));
+    return HE_ERR_CUDA;
+  }
+ private:
+  int prev_ = -1;
+  bool switched_ = false, failed_ = false;
+};
 
 // ---- validated subgraph -----------------------------------------------------------------------
 struct Graph {

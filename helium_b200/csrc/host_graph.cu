@@ -504,7 +504,8 @@ int32_t heh_exec_create(he_ctx* ctx, heh_graph* g, const void* const* inputs, vo
   std::unique_ptr<heh_exec> e(new heh_exec());
   e->ctx = ctx;
   e->plan = generate_plan(G, ctx);
-  HE_CUDA(cudaSetDevice(ctx->device));
+  DeviceGuard device_guard(ctx->device);   // the caller's current device is restored on return
+  HE_TRY(device_guard.status());
 
   // tensor table: caller buffers for inputs / outputs, owned buffers for the rest
   std::map<NodeId, void*> tensors;
@@ -515,13 +516,18 @@ int32_t heh_exec_create(he_ctx* ctx, heh_graph* g, const void* const* inputs, vo
   for (size_t j = 0; j < G.outputs.size(); ++j) {
     if (!outputs || !outputs[j]) HE_FAIL(HE_ERR_INVALID, "heh_exec_create: output %zu is null", j);
     if (G.nodes[G.outputs[j]].kind == HE_OP_INPUT) HE_FAIL(HE_ERR_UNSUPPORTED, "an input marked as output needs no execution");
-    if (!tensors.count(G.outputs[j])) tensors[G.outputs[j]] = outputs[j];
+    // one node bound to two caller buffers would need a device copy appended to the plan
+    if (tensors.count(G.outputs[j]))
+      HE_FAIL(HE_ERR_UNSUPPORTED, "heh_exec_create: node %d is listed as an output more than once (output %zu)", (int)G.outputs[j], j);
+    tensors[G.outputs[j]] = outputs[j];
   }
   int step_idx = 0;
   for (const Step& st : e->plan.steps) {
     for (const Instr& in : st.instrs) {
       ++e->n_instrs;
-      heh_exec::Bound b;
+      // owned by the executor from here on, so that every error return below releases the plan
+      e->launches.emplace_back();
+      heh_exec::Bound& b = e->launches.back();
       b.step = step_idx;
       OpSubgraph::Flat f = in.sub.flatten();
       he_graph_desc d = f.desc();
@@ -563,13 +569,11 @@ int32_t heh_exec_create(he_ctx* ctx, heh_graph* g, const void* const* inputs, vo
         HE_CUDA(cudaMalloc(&b.workspace, ws));
         e->owned.push_back(b.workspace);
       }
-      e->launches.push_back(std::move(b));
     }
     ++step_idx;
   }
   e->n_steps = step_idx;
-  // an output that is also consumed internally was bound to the caller's buffer above; outputs that
-  // alias an earlier output node share the buffer and need a copy -- not supported, and rare
+  // an output that is also consumed internally was bound to the caller's buffer above
   size_t widest = 1;
   for (const Step& st : e->plan.steps) widest = std::max(widest, st.instrs.size());
   const int ns = (int)std::min<size_t>(4, widest);
@@ -584,12 +588,39 @@ int32_t heh_exec_create(he_ctx* ctx, heh_graph* g, const void* const* inputs, vo
   HE_CUDA(cudaEventCreateWithFlags(&e->fork_event, cudaEventDisableTiming));
 
   if (capture_cuda_graph) {
-    // one eager pass first: lazy one-time initialisation (function attributes, driver entry
-    // points) must not happen inside a capture
+    // One eager pass first: lazy one-time initialisation (module loading, function attributes,
+    // driver entry points) must not happen inside a capture.  The pass writes to scratch copies
+    // of the caller's output buffers, never to the buffers themselves: an output may alias live
+    // state (a weight updated in place), and creating an executor must not advance it.
     cudaStream_t cap;
     HE_CUDA(cudaStreamCreateWithFlags(&cap, cudaStreamNonBlocking));
-    int32_t rc = e->issue(cap);
-    if (rc == HE_OK && cudaStreamSynchronize(cap) != cudaSuccess) rc = HE_ERR_CUDA;
+    std::vector<void*> scratch(G.outputs.size(), nullptr);
+    auto free_scratch = [&]() {
+      for (void* p : scratch)
+        if (p) cudaFree(p);
+    };
+    int32_t rc = HE_OK;
+    for (size_t j = 0; j < G.outputs.size() && rc == HE_OK; ++j) {
+      const he_node& n = G.nodes[G.outputs[j]];
+      if (cudaMalloc(&scratch[j], std::max<size_t>(256, storage_bytes(n.dtype, num_elements(n)))) != cudaSuccess) {
+        cudaGetLastError();
+        set_error("heh_exec_create: no memory for the warm-up copies of the outputs");
+        rc = HE_ERR_CUDA;
+      }
+    }
+    auto swap_outputs = [&](bool to_scratch) {
+      for (heh_exec::Bound& b : e->launches)
+        for (void*& o : b.outs)
+          for (size_t j = 0; j < G.outputs.size(); ++j)
+            if (o == (to_scratch ? outputs[j] : scratch[j])) { o = to_scratch ? scratch[j] : outputs[j]; break; }
+    };
+    if (rc == HE_OK) {
+      swap_outputs(true);
+      rc = e->issue(cap);
+      if (rc == HE_OK && cudaStreamSynchronize(cap) != cudaSuccess) rc = HE_ERR_CUDA;
+      swap_outputs(false);
+    }
+    free_scratch();
     if (rc != HE_OK) {
       cudaStreamDestroy(cap);
       return rc;

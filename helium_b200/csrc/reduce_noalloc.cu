@@ -82,7 +82,8 @@ extern "C" int32_t he_reduce_sum_f32_noalloc(const float* in, float* out, int64_
   if (!in || !out) HE_FAIL(HE_ERR_INVALID, "he_reduce_sum_f32_noalloc: null tensor pointer");
   if (num_groups < 0 || group_size < 0) HE_FAIL(HE_ERR_INVALID, "he_reduce_sum_f32_noalloc: negative extent");
   if (num_groups == 0) return HE_OK;
-  if (group_size == 0 || num_groups * group_size >= (1ll << 31))
+  // compared by division: the product of two hostile 64-bit extents can wrap past the bound
+  if (group_size == 0 || group_size > ((1ll << 31) - 1) / num_groups)
     HE_FAIL(HE_ERR_UNSUPPORTED, "he_reduce_sum_f32_noalloc: needs 0 < num_groups * group_size < 2^31 (got %lld x %lld)",
             (long long)num_groups, (long long)group_size);
   int dev = -1;
@@ -111,7 +112,11 @@ extern "C" int32_t he_reduce_sum_f32_noalloc(const float* in, float* out, int64_
             (long long)num_groups, spg, n_partials, (int)HE_NOALLOC_MAX_PARTIALS);
   cudaStream_t stream = (cudaStream_t)cu_stream;
   float* partials = g_partials_addr[dev];
-  noalloc_sum_slices<<<(unsigned)(num_groups * spg), kThreads, 0, stream>>>(in, partials, out, (unsigned)group_size, spg, slice);
+  // num_groups * group_size < 2^31 and spg <= ceil(group_size / 4096), so the grid fits 31 bits; checked anyway
+  const unsigned long long grid = (unsigned long long)num_groups * spg;
+  if (grid == 0 || grid > 0x7fffffffull)
+    HE_FAIL(HE_ERR_UNSUPPORTED, "he_reduce_sum_f32_noalloc: grid of %llu CTAs is out of range", grid);
+  noalloc_sum_slices<<<(unsigned)grid, kThreads, 0, stream>>>(in, partials, out, (unsigned)group_size, spg, slice);
   HE_CUDA(cudaGetLastError());
   if (spg > 1) {
     noalloc_fold_partials<<<(unsigned)num_groups, kThreads, 0, stream>>>(partials, out, spg);

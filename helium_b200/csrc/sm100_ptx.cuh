@@ -43,18 +43,20 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
 }
 
 // Bounded wait.  Returns false when the wait was abandoned: either another role of this CTA
-// already raised `*abort_flag`, or ~2 s passed; in the latter case the first CTA to give up
-// records (site, detail) in the device status block.  Callers leave their loops on false.
-constexpr uint64_t kWaitLimitNs = 2000000000ull;
+// already raised `*abort_flag`, or `limit_us` microseconds passed (2 s unless the plan says
+// otherwise); in the latter case the first CTA to give up records (site, detail) in the device
+// status block.  Callers leave their loops on false.
+constexpr uint32_t kDefaultWaitLimitUs = 2000000u;
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                          DeviceStatus* status, uint32_t site, uint32_t detail) {
+                                          DeviceStatus* status, uint32_t site, uint32_t detail,
+                                          uint32_t limit_us = kDefaultWaitLimitUs) {
   if (mbar_try_wait(bar, parity)) return true;
   const uint64_t t0 = globaltimer_ns();
   uint32_t spins = 0;
   while (!mbar_try_wait(bar, parity)) {
     if ((++spins & 255u) == 0u) {
       if (*abort_flag) return false;
-      if (globaltimer_ns() - t0 > kWaitLimitNs) {
+      if (globaltimer_ns() - t0 > (uint64_t)limit_us * 1000ull) {
         *abort_flag = 1;
         if (status && atomicCAS(&status->code, 0u, (site << 16) | (detail & 0xffffu)) == 0u) {
           status->block = blockIdx.x;

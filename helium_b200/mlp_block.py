@@ -1,4 +1,5 @@
-"""Transformer MLP block, forward + backward, as six fused matmul plans (BASELINE configs[3]).
+"""Transformer MLP block, forward + backward, as six fused matmul plans (the token-sharded benchmark workload:
+d -> ff with bias + GELU, ff -> d with bias + residual, and their backward GEMMs).
 
     forward :  Z = X W1 + b1,  H = gelu(Z)            one GEMM, bias + GELU epilogue, Z kept for backward
                O = H W2 + b2 + X                      one GEMM, bias + residual epilogue

@@ -124,6 +124,11 @@ class Plan:
     def last_launch_count(self) -> int:
         return lib.he_plan_last_launch_count(self._h)
 
+    def fault_injection(self, wait_limit_us: int = 0, withhold_loads: bool = False) -> None:
+        """he_debug_plan_fault_injection: bound of the kernels' device-side waits (0 = default 2 s) and
+        whether the TMA producers stay silent, which makes the first operand wait run out."""
+        check(lib.he_debug_plan_fault_injection(self._h, wait_limit_us, 1 if withhold_loads else 0))
+
     # -- launching ---------------------------------------------------------------------------------
     def alloc_outputs(self, device: str = "cuda"):
         torch = _torch()

@@ -172,7 +172,7 @@ int32_t he_plan_fused_matmul(he_ctx* ctx, const he_graph_desc* desc, he_plan** o
  *   HE_GEMM_GROUP_M=<n>       row tiles per rasterisation group
  *   HE_GEMM_NO_SPLIT=1        never run the tiles of an under-filled last round as half-width tiles
  *   HE_GEMM_MAINLOOP=fused|materialise   force how a mainloop fusion is executed
- *   HE_GEMM_DEBUG=<bits>      timing experiments: 1 skips the mainloop rewrite (wrong results), 2 its proxy fence */
+ * None of them changes results. */
 
 /* Backs Instruction::can_fuse_with (helium/src/backend.rs:85-95): 0 = cannot run as one kernel,
  * 1 = runs through the generic interpreter tier, 2 = matches a hand-written fast kernel.
@@ -231,7 +231,12 @@ int32_t heh_graph_plan_text(he_ctx* ctx, heh_graph* g, char* buf, size_t cap);
 /* Prepares an execution: plans, creates every he_plan, allocates intermediates and workspaces
  * once, binds the caller's device buffers (`inputs[i]` for the i-th new_input, `outputs[j]` for the
  * j-th new_output) and, if `capture_cuda_graph` != 0, records the whole plan into a CUDA graph.
- * heh_exec_run enqueues one evaluation on `cu_stream`. */
+ * Before recording, the plan runs once eagerly (one-time kernel set-up must not happen inside a
+ * capture): that pass READS the caller's input buffers, which must therefore hold readable memory
+ * already, and writes to temporary copies of the output buffers, so creating an executor never
+ * changes the caller's outputs -- an output may alias live state such as a weight updated in place.
+ * A node listed twice as an output is refused (HE_ERR_UNSUPPORTED).  The calling thread's current
+ * device is left as it was.  heh_exec_run enqueues one evaluation on `cu_stream`. */
 int32_t heh_exec_create(he_ctx* ctx, heh_graph* g, const void* const* inputs, void* const* outputs,
                         int32_t capture_cuda_graph, heh_exec** out);
 int32_t heh_exec_run(heh_exec* e, void* cu_stream);
@@ -248,6 +253,17 @@ void heh_exec_destroy(heh_exec* e);
 int32_t he_debug_dump_program(const he_graph_desc* desc, int32_t epilogue, void* buf, size_t cap,
                               size_t* size_out);
 int32_t he_debug_canonical_text(const he_graph_desc* desc, char* buf, size_t cap);
+
+/* Host-side fault injection for the bounded device waits of the tensor-core matmul kernels (no
+ * counterpart in the reference, whose kernels have no such waits).  Every mbarrier wait in those
+ * kernels gives up after `wait_limit_us` microseconds (0 restores the default of 2 s), records the wait
+ * site in the context's status block and lets the kernel finish through its normal teardown; with
+ * `withhold_loads` != 0 the kernel's TMA producers issue nothing, so the first wait for operands is
+ * certain to run into the limit.  A launch of such a plan returns HE_OK (the failure happens on the
+ * device), writes undefined results, and the next he_ctx_poll_device_status returns
+ * HE_ERR_DEVICE_TIMEOUT; the context stays usable.  Plans without device-side waits (pointwise,
+ * permute, SIMT matmul) return HE_ERR_UNSUPPORTED. */
+int32_t he_debug_plan_fault_injection(he_plan* plan, uint32_t wait_limit_us, int32_t withhold_loads);
 
 /* Sum over the trailing dims of an f32 tensor viewed as [num_groups, group_size], written to
  * out[num_groups], with no workspace argument and no device allocation by anyone.

@@ -327,7 +327,7 @@ def permute(x: np.ndarray, out_strides: Sequence[int]) -> np.ndarray:
 
 # ---- config-level helpers ---------------------------------------------------------------------------
 def affine_relu_nchw_to_nhwc(x_bits: np.ndarray, scale: np.ndarray, bias: np.ndarray) -> np.ndarray:
-    """BASELINE config 2a: y = relu(x * s_c + b_c) on bf16 [N,C,H,W], written as [N,H,W,C] bf16 bits.
+    """Fused affine + relu + NCHW -> NHWC benchmark case: y = relu(x * s_c + b_c) on bf16 [N,C,H,W], written as [N,H,W,C] bf16 bits.
 
     One fused multiply-add in f32 (f64 product and sum are exact enough to round identically except
     for double-rounding ties), then max with 0, then one rounding to bf16.

@@ -7,7 +7,7 @@
  * helium/src/raw_tensor.rs:100,156,1073), so this file follows the semantics of its CUDA kernels:
  *   oc_permute                  helium/src/cuda/instr/permute_dims/jit.rs:15-117
  *   oc_affine_relu_nchw_nhwc    helium/src/cuda/instr/pointwise/jit.rs:300-340,532-561 fused with the
- *                               swap_dims chain of permute_dims.rs:112-172 (BASELINE config 2a)
+ *                               swap_dims chain of permute_dims.rs:112-172 (the bf16 [64,256,56,56] benchmark case)
  *   oc_gemm_bf16                helium-ir/src/opgraph/op.rs:272-282 (row-major [M,K] x [K,N], bf16
  *                               products, f32 accumulation) with the relu(A) * mask mainloop fusion of
  *                               README.md:36-39

@@ -28,7 +28,7 @@ def _run_graph(ctx, g, ins, capture, repeats=1):
 
 @pytest.mark.parametrize("capture", [False, True])
 def test_mlp_training_step(ctx, capture):
-    """BASELINE config 1: 784 -> 512 -> 10 MLP, batch 256, f32, one SGD step; tolerance rel-L2 <= 1e-5."""
+    """The f32 MLP training-step workload: 784 -> 512 -> 10 MLP, batch 256, f32, one SGD step; tolerance rel-L2 <= 1e-5."""
     g = configs.graph_mlp_train_step()
     ins = configs.mlp_inputs()
     want = O.evaluate(g, ins)

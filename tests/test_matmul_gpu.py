@@ -136,7 +136,7 @@ def test_readme_graph_with_saturating_biases(ctx):
 
 
 def test_readme_graph_full_size_against_c_oracle(ctx):
-    """BASELINE config 3 at 4096^3.  The numpy oracle would take minutes, so: 256 sampled rows go
+    """The README fused matmul at its benchmark size, 4096^3.  The numpy oracle would take minutes, so: 256 sampled rows go
     through the C oracle (bit-identical semantics, f32), and the reductions are cross-checked
     against sums of the kernel's own tile outputs."""
     from oracle import oracle_c as OC

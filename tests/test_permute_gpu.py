@@ -87,7 +87,7 @@ def test_reference_stride_convention(ctx):
 
 
 @pytest.mark.parametrize("shape,swaps,dtype", [
-    ((4096, 4096, 8), [(1, 2), (0, 1)], ir.F32),        # BASELINE config 2b
+    ((4096, 4096, 8), [(1, 2), (0, 1)], ir.F32),        # the f32 benchmark permutation
     ((64, 256, 56, 56), [(1, 2), (2, 3)], ir.BF16),     # the permute half of config 2a
     ((2048, 128, 128, 32), [(0, 3)], ir.F32),           # helium/examples/permute_dim_benchmark.rs:13-38
 ])

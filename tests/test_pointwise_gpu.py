@@ -54,7 +54,7 @@ def test_affine_relu_permute_tier2(ctx, shape, x_dtype, p_dtype):
 
 
 def test_config_2a_full_size(ctx):
-    """BASELINE config 2a at full size: [64,256,56,56] bf16; checked against the numpy oracle."""
+    """The fused affine + relu + layout change at its benchmark size: [64,256,56,56] bf16; checked against the numpy oracle."""
     g = graph_affine_relu_permute(64, 256, 56, 56)
     r = rng(1)
     x = O.f32_to_bf16_bits(r.standard_normal((64, 256, 56, 56), dtype=np.float32))
