@@ -72,6 +72,14 @@ SIGNATURES = {
     "heh_exec_destroy": (None, [C.c_void_p]),
     "he_debug_dump_program": (C.c_int32, [C.POINTER(HeGraphDesc), C.c_int32, C.c_void_p, C.c_size_t, C.POINTER(C.c_size_t)]),
     "he_debug_canonical_text": (C.c_int32, [C.POINTER(HeGraphDesc), C.c_char_p, C.c_size_t]),
+    "he_comm_unique_id": (C.c_int32, [C.c_void_p]),
+    "he_comm_create": (C.c_int32, [C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_int32, C.c_int32, C.POINTER(C.c_void_p)]),
+    "he_comm_info": (C.c_int32, [C.c_void_p, C.POINTER(C.c_int32), C.POINTER(C.c_int32), C.POINTER(C.c_int32)]),
+    "he_allreduce_grads": (C.c_int32, [C.c_void_p, C.POINTER(C.c_void_p), C.POINTER(C.c_size_t), C.c_int32, C.c_int32, C.c_int32,
+                                       C.c_void_p]),
+    "he_comm_poll": (C.c_int32, [C.c_void_p]),
+    "he_comm_abort": (C.c_int32, [C.c_void_p]),
+    "he_comm_destroy": (None, [C.c_void_p]),
     "he_debug_plan_fault_injection": (C.c_int32, [C.c_void_p, C.c_uint32, C.c_int32]),
     "he_last_error_string": (C.c_char_p, []),
     "he_reduce_sum_f32_noalloc": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_void_p]),

@@ -35,6 +35,7 @@ SOURCES = [
     "sgemm.cu",
     "host_graph.cu",
     "reduce_noalloc.cu",
+    "comm.cu",
 ]
 
 NVCC_FLAGS = [
@@ -101,7 +102,7 @@ def build(force: bool = False, verbose: bool = False, ptxas_v: bool = False) -> 
     need_link = bool(jobs) or not os.path.exists(LIB_PATH)
     if need_link:
         cmd = [nvcc, "-shared", "-o", LIB_PATH, *objs, "-gencode", "arch=compute_100a,code=sm_100a",
-               "-Xcompiler", "-fPIC"]
+               "-Xcompiler", "-fPIC", "-ldl"]
         res = subprocess.run(cmd, capture_output=True, text=True)
         if res.returncode != 0:
             raise RuntimeError(f"link failed:\n{res.stdout}\n{res.stderr}")

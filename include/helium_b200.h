@@ -30,7 +30,9 @@ typedef enum he_status {
   HE_ERR_UNSUPPORTED = -2,  /* well-formed but outside what the kernels implement             */
   HE_ERR_CUDA = -3,         /* a CUDA runtime / driver call failed (message has the detail)    */
   HE_ERR_WORKSPACE = -4,    /* workspace pointer missing or too small                          */
-  HE_ERR_DEVICE_TIMEOUT = -5 /* a bounded device-side wait gave up (see he_ctx_poll_device_status) */
+  HE_ERR_DEVICE_TIMEOUT = -5, /* a bounded device-side wait gave up (see he_ctx_poll_device_status) */
+  HE_ERR_COMM = -6,          /* NCCL is missing or reported an error; the communicator may have been aborted */
+  HE_ERR_COMM_TIMEOUT = -7   /* a communicator call did not complete by its deadline; the communicator was aborted */
 } he_status;
 
 /* Mirrors helium_ir::data_type::DataType (helium-ir/src/data_type.rs:9-24).
@@ -253,6 +255,44 @@ void heh_exec_destroy(heh_exec* e);
 int32_t he_debug_dump_program(const he_graph_desc* desc, int32_t epilogue, void* buf, size_t cap,
                               size_t* size_out);
 int32_t he_debug_canonical_text(const he_graph_desc* desc, char* buf, size_t cap);
+
+/* ------------------------------------------------------------------------------------------------
+ * Data-parallel gradient exchange.  No counterpart in the reference, which runs on one GPU: its
+ * optimiser consumes whatever gradient tensors it is handed (helium/src/optimizer/sgd.rs:35-62).  A
+ * data-parallel host calls he_allreduce_grads between `backward()` and `Optimizer::step`, once per
+ * bucket of gradients, on a stream of its choice so that the exchange overlaps the remaining backward
+ * kernels.  One process (or thread) per GPU; NCCL is loaded at run time (dlopen of the copy already in
+ * the process, else libnccl.so.2; HE_NCCL_LIBRARY overrides the name).
+ *
+ * Failure handling is on the host: the communicator is non-blocking, every call below polls
+ * ncclCommGetAsyncError against a deadline, and a call that misses its deadline (a peer that never
+ * joined) or meets an NCCL error aborts the communicator (ncclCommAbort) and returns HE_ERR_COMM_TIMEOUT
+ * / HE_ERR_COMM; afterwards only he_comm_destroy is valid.  Nothing here can wait for ever.
+ * ------------------------------------------------------------------------------------------------ */
+typedef struct he_comm he_comm;
+#define HE_COMM_UNIQUE_ID_BYTES 128
+/* Rank 0 calls this and hands the 128 bytes to every rank by any channel it has (a file, a socket, an
+ * existing process group). */
+int32_t he_comm_unique_id(void* id_out);
+/* `ctx` selects the device (NULL: the calling thread's current device).  `max_ctas` > 0 caps the CTAs a
+ * collective may occupy (ncclConfig_t::maxCTAs) so that a persistent GEMM launched next to it can be given
+ * the remaining SMs; 0 leaves NCCL's default.  `timeout_ms` bounds this call and becomes the default
+ * deadline of the later ones (0: 30 s). */
+int32_t he_comm_create(he_ctx* ctx, int32_t rank, int32_t world, const void* unique_id, int32_t max_ctas,
+                       int32_t timeout_ms, he_comm** out);
+int32_t he_comm_info(const he_comm* comm, int32_t* rank, int32_t* world, int32_t* max_ctas);
+/* In-place sum (mean != 0: mean) over ranks of n device buffers of `dtype` (F16 / BF16 / F32), enqueued on
+ * `cu_stream` as one NCCL group.  The first call with a given layout (n, counts, dtype, mean) checks that
+ * every rank passed the same layout -- a 16-byte collective whose result is read back before anything
+ * else is enqueued; a mismatch returns HE_ERR_INVALID on the ranks that differ from the others and no
+ * gradient is touched.  Later calls with that layout enqueue and return. */
+int32_t he_allreduce_grads(he_comm* comm, void* const* bufs, const size_t* counts, int32_t n, int32_t dtype,
+                           int32_t mean, void* cu_stream);
+/* HE_OK while the communicator is healthy (idle or busy), HE_ERR_COMM once NCCL has reported an
+ * asynchronous error or the communicator was aborted.  Cheap; meant to be called once per step. */
+int32_t he_comm_poll(he_comm* comm);
+int32_t he_comm_abort(he_comm* comm);
+void he_comm_destroy(he_comm* comm);
 
 /* Host-side fault injection for the bounded device waits of the tensor-core matmul kernels (no
  * counterpart in the reference, whose kernels have no such waits).  Every mbarrier wait in those

@@ -135,30 +135,89 @@ def test_readme_graph_with_saturating_biases(ctx):
     _compare(g, got, O.evaluate(g, ins), plan.description)
 
 
-def test_readme_graph_full_size_against_c_oracle(ctx):
-    """The README fused matmul at its benchmark size, 4096^3.  The numpy oracle would take minutes, so: 256 sampled rows go
-    through the C oracle (bit-identical semantics, f32), and the reductions are cross-checked
-    against sums of the kernel's own tile outputs."""
+def _readme_oracle_full(ins, m, n):
+    """Every row of the README graph through the C oracle (bf16 products, f32 accumulate, the epilogue in
+    f32 as the graph spells it, sums in f64): (loss, db2, db1, gt bits, gz1 bits, z1)."""
     from oracle import oracle_c as OC
+    a, mk_ml, b, b1, b2, mk, y = [x.reshape(x.shape[-2], x.shape[-1]) for x in ins]
+    acc = OC.gemm_bf16(a, b, mk_ml, 0, m)
+    out = OC.c3_epilogue(acc, mk, y, b1.reshape(-1), b2.reshape(-1), 1.0 / n, 0, m)
+    acc += O.bf16_bits_to_f32(b1.reshape(1, -1))     # z1 = C + b1, the argument of the relu switch
+    return out + (acc,)
+
+
+def _check_readme_outputs(got, ref, ins, m, n, what):
+    loss, db2, db1, gt, gz1 = got
+    l_ref, db2_ref, db1_ref, gt_ref, gz_ref, z1 = ref
+    dec = lambda bits: O.bf16_bits_to_f32(np.asarray(bits).reshape(m, n)).astype(np.float64)
+    for name, mine, want in (("gt", gt, gt_ref), ("gz1", gz1, gz_ref)):
+        err = O.rel_l2(dec(mine), dec(want))
+        assert err <= 1e-2, f"{what}: {name} rel-L2 {err:.3e}"
+    # DB1 sums gz1 = (z1 > 0 ? gu : 0), which jumps at z1 = 0.  Two f32 accumulations of the same 4096-term dot
+    # product differ by ~1e-6, so among 16.7 M elements a handful with |z1| below that may legally switch the
+    # other way, each moving one column sum by a whole element (~3e-4 of the vector's norm).  Those elements
+    # are identified from the oracle's z1; for them the kernel's stored value must be one of the two legal
+    # outcomes (0, or the oracle's value had the switch been on), and the reference sum takes the kernel's
+    # choice.  Everything else is compared as is.
+    amb = np.argwhere(np.abs(z1) <= 4e-6 * max(1.0, float(np.abs(z1).max())))
+    assert len(amb) <= max(64, int(1e-4 * m * n)), f"{what}: {len(amb)} elements next to the relu switch"
+    db1_ref = np.array(db1_ref, dtype=np.float64)
+    gz_mine, gz_want = dec(gz1), dec(gz_ref)
+    b1v, b2v = [O.bf16_bits_to_f32(ins[k].reshape(-1)).astype(np.float64) for k in (3, 4)]
+    mkv, yv = [O.bf16_bits_to_f32(ins[k].reshape(m, n)) for k in (5, 6)]
+    for i, j in amb:
+        # u ~ 0 here, so d = mask - y and the switched-on value is g * (t - mask)
+        t = np.tanh(float(z1[i, j]) - b1v[j] + b2v[j])
+        on = (float(mkv[i, j]) - float(yv[i, j])) * 2.0 / n * (t - float(mkv[i, j]))
+        assert gz_mine[i, j] == 0.0 or abs(gz_mine[i, j] - on) <= 1e-2 * abs(on) + 1e-12, (what, i, j, gz_mine[i, j], on)
+        db1_ref[j] += gz_mine[i, j] - gz_want[i, j]
+    # the three reductions against the oracle's own f64 sums, at the f32 tolerance
+    for name, mine, want in (("DB2", db2, db2_ref), ("DB1", db1, db1_ref), ("LOSS", loss, np.array([l_ref]))):
+        err = O.rel_l2(np.asarray(mine, dtype=np.float64).reshape(-1), np.asarray(want, dtype=np.float64).reshape(-1))
+        assert err <= 1e-5, f"{what}: {name} rel-L2 {err:.3e} ({len(amb)} elements next to the relu switch)"
+
+
+def test_readme_graph_full_size_against_c_oracle(ctx):
+    """The README fused matmul at its benchmark size, 4096^3: ALL rows go through the C oracle (the numpy
+    oracle would take minutes); both stored tiles are compared over the whole matrix at 1e-2, and LOSS, DB1,
+    DB2 against the oracle's f64 sums at 1e-5."""
     m = n = k = 4096
     g = graph_c3(m, n, k, False)
     ins = _c3_inputs(m, n, k, False)
     got, plan = _run(ctx, g, ins)
-    loss, db2, db1, gt, gz1 = got
-    a, mk_ml, b, b1, b2, mk, y = [x.reshape(x.shape[-2], x.shape[-1]) for x in ins]
-    for m0 in (0, 1920, 3968):
-        acc = OC.gemm_bf16(a, b, mk_ml, m0, m0 + 128)
-        l, d2, d1, gt_ref, gz_ref = OC.c3_epilogue(acc, mk, y, b1.reshape(-1), b2.reshape(-1), 1.0 / n, m0, m)
-        for name, mine, ref in (("gt", gt, gt_ref), ("gz1", gz1, gz_ref)):
-            mine_v = O.bf16_bits_to_f32(mine.reshape(m, n)[m0:m0 + 128]).astype(np.float64)
-            err = O.rel_l2(mine_v, O.bf16_bits_to_f32(ref).astype(np.float64))
-            assert err <= 1e-2, (name, m0, err)
-    # column sums / loss agree with sums over the kernel's own bf16 tiles up to bf16 rounding of the tiles
-    gt_v = O.bf16_bits_to_f32(gt.reshape(m, n)).astype(np.float64)
-    gz_v = O.bf16_bits_to_f32(gz1.reshape(m, n)).astype(np.float64)
-    assert O.rel_l2(db2.reshape(-1), gt_v.sum(0)) <= 1e-2
-    assert O.rel_l2(db1.reshape(-1), gz_v.sum(0)) <= 1e-2
-    assert np.isfinite(loss).all() and loss.reshape(-1)[0] > 0
+    _check_readme_outputs(got, _readme_oracle_full(ins, m, n), ins, m, n, plan.description)
+
+
+@pytest.mark.parametrize("m,n,k,repeats", [(4096, 4096, 4096, 50), (8192, 512, 4096, 20)])
+def test_in_kernel_mainloop_fusion_at_scale(ctx, monkeypatch, m, n, k, repeats):
+    """The in-kernel mainloop rewrite (transform warps of both CTAs of a pair hand their tiles to the leader's
+    MMA thread through a cluster-remote mbarrier arrive) forced on at sizes where the planner would
+    materialise instead: parity against the C oracle on every row, then repeated launches that must give
+    the same bits every time -- a lost or early hand-off would show up as a changed tile."""
+    import torch
+    monkeypatch.setenv("HE_GEMM_MAINLOOP", "fused")   # read at plan time
+    g = graph_c3(m, n, k, False)
+    ins = _c3_inputs(m, n, k, False)
+    plan = hb.Plan.fused_matmul(ctx, g)
+    assert "mainloop rewrite in shared memory" in plan.description, plan.description
+    t_ins = [storage_to_torch(a, g.nodes[i].dtype) for a, i in zip(ins, g.inputs)]
+    outs = plan.launch(t_ins)
+    torch.cuda.synchronize()
+    ctx.poll()
+    first = [t.clone() for t in outs]
+    got = [torch_to_storage(t, g.nodes[o].dtype) for t, o in zip(outs, g.outputs)]
+    _check_readme_outputs(got, _readme_oracle_full(ins, m, n), ins, m, n, plan.description)
+    for it in range(repeats):
+        plan.launch(t_ins, outs)
+        if it % 10 == 9:
+            for a, b in zip(first, outs):
+                assert torch.equal(a.view(torch.int32) if a.dtype == torch.float32 else a.view(torch.int16),
+                                   b.view(torch.int32) if b.dtype == torch.float32 else b.view(torch.int16)), f"launch {it + 1} changed a result"
+    torch.cuda.synchronize()
+    ctx.poll()
+    for a, b in zip(first, outs):
+        assert torch.equal(a.view(torch.int32) if a.dtype == torch.float32 else a.view(torch.int16),
+                           b.view(torch.int32) if b.dtype == torch.float32 else b.view(torch.int16))
 
 
 def test_interpreted_epilogue(ctx):
@@ -343,12 +402,17 @@ def test_mlp_block_full_size_sampled(ctx):
     close(dec(dev["dW1"][rows_d]), OC.gemm_bf16(np.ascontiguousarray(X[:, rows_d].T), dev["dZ"]).astype(np.float64), "dW1")
     rows_f = np.sort(r.choice(ff, 32, replace=False))
     close(dec(dev["dW2"][rows_f]), OC.gemm_bf16(np.ascontiguousarray(dev["H"][:, rows_f].T), dO).astype(np.float64), "dW2")
-    # bias gradients: db2 = colsum(dO) from the inputs (f32 tolerance); db1 = colsum(dZ) against the
-    # column sums of the stored (bf16-rounded) dZ, which bounds it to the rounding of 8192 terms
+    # bias gradients against the oracle at the f32 tolerance: db2 = colsum(dO) from the inputs; db1 =
+    # colsum(dZ) over ALL 8192 rows of the oracle's own dZ (C-oracle GEMM, gelu' in f64 on the Z that the dZ
+    # GEMM read, summed in f64 before any rounding) for 64 sampled columns
     db2 = blk.db2.cpu().numpy().reshape(-1).astype(np.float64)
     assert O.rel_l2(db2, dec(dO).sum(0)) <= 1e-5
     db1 = blk.db1.cpu().numpy().reshape(-1).astype(np.float64)
-    assert O.rel_l2(db1, dec(dev["dZ"]).sum(0)) <= 2e-3
+    cols = np.sort(r.choice(ff, 64, replace=False))
+    dh_cols = OC.gemm_bf16(dO, np.ascontiguousarray(W2[cols].T)).astype(np.float64)        # [T, 64] = dO W2^T[:, cols]
+    dz_cols = dh_cols * dgelu(dec(dev["Z"][:, cols]))
+    err = O.rel_l2(db1[cols], dz_cols.sum(0))
+    assert err <= 1e-5, f"db1 against the oracle's column sums: rel-L2 {err:.3e}"
 
 
 @pytest.mark.parametrize("kw", [
