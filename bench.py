@@ -1,21 +1,22 @@
 #!/usr/bin/env python
 """Benchmark of the fused-kernel hot path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c1|c2|c3|c4|gemm] [--impl ours|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c4|c3|c3f|c2|c1|c4g|gemm|pw] [--impl ours|reference]
 
-Default workload = BASELINE.json configs[1] ("c2"): one step is
-  (a) y = relu(x * s_c + b_c) on bf16 [64,256,56,56] NCHW written as NHWC, one fused kernel, and
-  (b) the f32 permutation [4096,4096,8] -> axes (2,0,1),
-on synthetic seeded inputs; the metric is algorithmic HBM bytes moved per second.
-Other workloads: c1 = configs[0] (MLP training step, steps/s, whole graph through the C++ host
-runtime as one CUDA graph), c3 = configs[2] (fused 4096^3 GEMM, TFLOP/s), c4 = configs[3]
-(transformer MLP block forward+backward, 8192 tokens per GPU, weight gradients all-reduced over
-NCCL), c4g = the same block as one op graph through the host runtime, gemm = a plain 8192^3 bf16 matmul,
-pw = stand-alone pointwise programs on 64 Mi-element tensors.
+Default workload "c4": the transformer MLP block forward + backward, bf16, 8192 tokens per GPU, d 4096,
+ff 16384 -- six fused GEMMs per step, metric fused-GEMM TFLOP/s.  With N > 1 (launched under
+torch.distributed.run, one process per GPU) tokens are sharded over the ranks and the weight / bias
+gradients are averaged with NCCL through the library's own communicator (he_allreduce_grads), overlapped
+with the remaining backward GEMMs; the value is N x per-GPU work / max-over-ranks device time.
+At N = 1 the default run also times the other single-GPU configurations in the same process and reports
+them under "configs": the README fused matmul 4096^3 as planned ("c3") and with the in-kernel mainloop
+rewrite forced ("c3f"), the fused affine + layout change and the f32 permutation ("c2"), the f32 MLP
+training step ("c1").  Other workloads: c4g = the MLP block as one op graph through the host runtime,
+gemm = a plain 8192^3 bf16 matmul, pw = stand-alone pointwise programs on 64 Mi-element tensors.
 
-Rank 0 prints exactly one JSON line.  With N > 1 (launched under torch.distributed.run) c1-c3 run
-an independent replica per rank (those configurations have no cross-GPU dependency); c4 shards
-tokens over ranks and exchanges gradients.  The whole-job value is N x work / max-over-ranks time.
+Rank 0 prints exactly one JSON line.  c1-c3 have no cross-GPU dependency: with N > 1 they run an independent
+replica per rank.  `--impl reference` times the CPU restatement of the same work (oracle/) on the host
+cores; it loads neither the CUDA library nor the package initialiser.
 """
 from __future__ import annotations
 
@@ -33,12 +34,29 @@ import numpy as np
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
+
+
+def host_configs():
+    """helium_b200/configs.py (graphs + seeded inputs, pure numpy) WITHOUT running the package initialiser, so
+    that the CPU legs -- above all `--impl reference` -- never map libhelium_b200.so: the modules are imported
+    under a stand-in package whose path is the package directory."""
+    import importlib
+    import types
+    name = "helium_b200_hostonly"
+    if name not in sys.modules:
+        pkg = types.ModuleType(name)
+        pkg.__path__ = [os.path.join(ROOT, "helium_b200")]
+        sys.modules[name] = pkg
+    return importlib.import_module(name + ".configs")
+
+
 C2A_SHAPE = (64, 256, 56, 56)
 C2B_SHAPE = (4096, 4096, 8)
 C2A_BYTES = 2 * 64 * 256 * 56 * 56 * 2 + 2 * 256 * 4      # x in + y out (bf16) + s, b (f32)
 C2B_BYTES = 2 * 4096 * 4096 * 8 * 4                       # in + out (f32)
 C3_MNK = (4096, 4096, 4096)
 C3_FLOPS = 2 * 4096 ** 3
+NCCL_CTAS_DEFAULT = 0
 
 
 def load_peaks():
@@ -50,9 +68,13 @@ def load_peaks():
     return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
 
 
+TRAFFIC_SOURCE = "profiles/dram_traffic.txt (ncu capture of this kernel and shape, committed; not measured by this run)"
+
+
 def load_traffic(name: str):
     """Per-launch DRAM traffic (bytes) of the dominant kernel, read from the committed ncu summary
-    profiles/dram_traffic.txt (lines `key bytes  # comment`), or None when the kernel has no capture."""
+    profiles/dram_traffic.txt (lines `key bytes  # comment`), or None when the kernel has no capture.  The
+    JSON line labels it with `traffic_source`: it is a recorded figure, not a measurement of the run."""
     path = os.path.join(ROOT, "profiles", "dram_traffic.txt")
     if not os.path.exists(path):
         return None
@@ -243,19 +265,21 @@ class WorkloadC2:
         self.pipe.step(upload, run, download)
 
     @staticmethod
-    def cpu_sample(max_steps=3):
-        from helium_b200.configs import c2_inputs
+    def cpu_sample(steps=3, warmup=1):
+        """Every timed step is one full pass of both kernels' work on the host cores."""
+        cfg = host_configs()
         from oracle import oracle_c as OC
-        x, s, b, p = c2_inputs(1)
+        x, s, b, p = cfg.c2_inputs(1)
         st = [4096, 1, 4096 * 4096]
-        OC.affine_relu_nchw_nhwc(x, s, b); OC.permute(p, st)      # first call also builds / loads the C object
+        for _ in range(max(1, warmup)):                           # the first call also builds / loads the C object
+            OC.affine_relu_nchw_nhwc(x, s, b); OC.permute(p, st)
         t0 = time.perf_counter()
-        for _ in range(max_steps):
+        for _ in range(steps):
             OC.affine_relu_nchw_nhwc(x, s, b)
             OC.permute(p, st)
-        dt = (time.perf_counter() - t0) / max_steps
+        dt = (time.perf_counter() - t0) / steps
         return (C2A_BYTES + C2B_BYTES) / dt / 1e9, OC.num_threads(), \
-            f"{max_steps} full configs[1] steps of the C+OpenMP restatement (oracle/oracle_c.c); the reference has no CPU path", dt
+            f"{steps} full steps (both kernels' work) of the C+OpenMP restatement (oracle/oracle_c.c); the reference has no CPU path", dt
 
 
 class _GemmBase:
@@ -267,17 +291,20 @@ class _GemmBase:
         return self.torch.empty(256 << 20, dtype=self.torch.uint8, device=dev)
 
     @staticmethod
-    def _cpu_gemm_sample(m, n, k, rows, masked, seed):
-        """`rows` output rows of an [m,k]x[k,n] bf16 GEMM on the host cores, scaled linearly to m rows."""
-        from helium_b200.configs import bf16_bernoulli, bf16_normal, rng
+    def _cpu_gemm_sample(m, n, k, rows, masked, seed, steps=1, warmup=1):
+        """`rows` output rows of an [m,k]x[k,n] bf16 GEMM on the host cores per timed step, scaled linearly to m
+        rows; returns (seconds per full GEMM, threads)."""
+        cfg = host_configs()
         from oracle import oracle_c as OC
-        r = rng(seed)
-        a = bf16_normal(r, (rows, k)); b = bf16_normal(r, (k, n), 1.0 / np.sqrt(k))
-        mk = bf16_bernoulli(r, (rows, k)) if masked else None
-        OC.gemm_bf16(a[:8], b, None if mk is None else mk[:8], 0, 8)   # builds / loads the C object, warms the caches
+        r = cfg.rng(seed)
+        a = cfg.bf16_normal(r, (rows, k)); b = cfg.bf16_normal(r, (k, n), 1.0 / np.sqrt(k))
+        mk = cfg.bf16_bernoulli(r, (rows, k)) if masked else None
+        for _ in range(max(1, warmup)):                           # builds / loads the C object, warms the caches
+            OC.gemm_bf16(a[:8], b, None if mk is None else mk[:8], 0, 8)
         t0 = time.perf_counter()
-        OC.gemm_bf16(a, b, mk, 0, rows)
-        dt = (time.perf_counter() - t0) * (m / rows)
+        for _ in range(steps):
+            OC.gemm_bf16(a, b, mk, 0, rows)
+        dt = (time.perf_counter() - t0) / steps * (m / rows)
         return dt, OC.num_threads()
 
 
@@ -335,10 +362,11 @@ class WorkloadGemm(_GemmBase):
         self.pipe.step(upload, run, download)
 
     @staticmethod
-    def cpu_sample(max_steps=1):
-        rows = 4096
-        dt, cores = _GemmBase._cpu_gemm_sample(8192, 8192, 8192, rows, False, 2)
-        return 2.0 * 8192 ** 3 / dt / 1e12, cores, f"{rows} of 8192 output rows, C+OpenMP restatement (oracle/oracle_c.c), scaled linearly", dt
+    def cpu_sample(steps=1, warmup=1):
+        rows = 256
+        dt, cores = _GemmBase._cpu_gemm_sample(8192, 8192, 8192, rows, False, 2, steps, warmup)
+        return 2.0 * 8192 ** 3 / dt / 1e12, cores, \
+            f"{steps} timed steps of {rows} of 8192 output rows each, C+OpenMP restatement (oracle/oracle_c.c), scaled linearly", dt
 
 
 class WorkloadC3(_GemmBase):
@@ -405,11 +433,12 @@ class WorkloadC3(_GemmBase):
         self.pipe.step(upload, run, download)
 
     @staticmethod
-    def cpu_sample(max_steps=1):
-        rows = 4096
-        dt, cores = _GemmBase._cpu_gemm_sample(4096, 4096, 4096, rows, True, 2)
+    def cpu_sample(steps=1, warmup=1):
+        rows = 1024
+        dt, cores = _GemmBase._cpu_gemm_sample(4096, 4096, 4096, rows, True, 2, steps, warmup)
         return C3_FLOPS / dt / 1e12, cores, \
-            f"{rows} of 4096 output rows of the mainloop-fused GEMM (epilogue not included), C+OpenMP restatement, scaled linearly", dt
+            (f"{steps} timed steps of {rows} of 4096 output rows each of the mainloop-fused GEMM (epilogue not included), "
+             "C+OpenMP restatement (oracle/oracle_c.c), scaled linearly"), dt
 
 
 class WorkloadC4(_GemmBase):
@@ -423,13 +452,13 @@ class WorkloadC4(_GemmBase):
     l2_note = "every GEMM streams operands larger than L2 (W1/W2/H/Z are 128-256 MiB each); no flush needed"
     work_per_step = 6 * 2.0 * 8192 * 4096 * 16384
 
-    def __init__(self, ctx, dev, world, rank, peaks, reducer):
+    def __init__(self, ctx, dev, world, rank, peaks, reducer, overlap_sms=0):
         import torch
         from helium_b200.mlp_block import MlpBlock, mlp_block_inputs
         self.torch = torch
         self.reducer = reducer
         T, d, ff = self.TOKENS, self.D, self.FF
-        self.blk = MlpBlock(ctx, T, d, ff, dev)
+        self.blk = MlpBlock(ctx, T, d, ff, dev, overlap_sms=overlap_sms)
         host = mlp_block_inputs(T, d, ff, seed=3, shard=rank)       # same weights on every rank, a different token shard each
         self.blk.load(host)
         as_pin = lambda v: torch.from_numpy(np.ascontiguousarray(v).view(np.int16)).pin_memory()
@@ -504,13 +533,13 @@ class WorkloadC4(_GemmBase):
         self.pipe.step(upload, run, download)
 
     @staticmethod
-    def cpu_sample(max_steps=1):
-        rows = 2048
-        dt, cores = _GemmBase._cpu_gemm_sample(8192, 16384, 4096, rows, False, 3)
+    def cpu_sample(steps=1, warmup=1):
+        rows = 256
+        dt, cores = _GemmBase._cpu_gemm_sample(8192, 16384, 4096, rows, False, 3, steps, warmup)
         dt *= 6     # six GEMMs of equal flop count per step
         return WorkloadC4.work_per_step / dt / 1e12, cores, \
-            (f"{rows} of 8192 rows of the X*W1 GEMM, C+OpenMP restatement, scaled linearly to the six equal-sized GEMMs of a step "
-             "(epilogues not included)"), dt
+            (f"{steps} timed steps of {rows} of 8192 rows of the X*W1 GEMM each, C+OpenMP restatement (oracle/oracle_c.c), scaled "
+             "linearly to the six equal-sized GEMMs of a step (epilogues not included)"), dt
 
 
 class WorkloadC4Graph(_GemmBase):
@@ -574,7 +603,7 @@ class WorkloadC4Graph(_GemmBase):
         self.dx_pin.copy_(self.outs[1].view(torch.int16), non_blocking=True)
         torch.cuda.current_stream().synchronize()
 
-    cpu_sample = staticmethod(lambda max_steps=1: WorkloadC4.cpu_sample(max_steps))
+    cpu_sample = staticmethod(lambda steps=1, warmup=1: WorkloadC4.cpu_sample(steps, warmup))
 
 
 class WorkloadPointwise:
@@ -644,18 +673,20 @@ class WorkloadPointwise:
         self.torch.cuda.current_stream().synchronize()
 
     @staticmethod
-    def cpu_sample(max_steps=1):
-        from helium_b200.configs import bf16_normal, rng
+    def cpu_sample(steps=1, warmup=1):
+        cfg = host_configs()
         from oracle import oracle as O
-        from helium_b200 import ir
         n = 1 << 22
-        r = rng(6)
-        a, m = bf16_normal(r, (n,)), bf16_normal(r, (n,))
+        r = cfg.rng(6)
+        a, m = cfg.bf16_normal(r, (n,)), cfg.bf16_normal(r, (n,))
+        run = lambda: O.encode(np.maximum(O.decode(a, O.BF16, (n,)), 0) * O.decode(m, O.BF16, (n,)), O.BF16)
+        for _ in range(warmup):
+            run()
         t0 = time.perf_counter()
-        x = np.maximum(O.decode(a, ir.BF16, (n,)), 0) * O.decode(m, ir.BF16, (n,))
-        O.encode(x, ir.BF16)
-        dt = time.perf_counter() - t0
-        return 3 * n * 2 / dt / 1e9, 1, f"relu(a)*m on {n} bf16 elements with the numpy oracle (single thread)", dt
+        for _ in range(steps):
+            run()
+        dt = (time.perf_counter() - t0) / steps
+        return 3 * n * 2 / dt / 1e9, 1, f"{steps} timed steps of relu(a)*m on {n} bf16 elements with the numpy oracle (single thread)", dt
 
 
 class WorkloadC1:
@@ -719,25 +750,65 @@ class WorkloadC1:
         self.loss_pin.copy_(self.loss_d, non_blocking=True)
 
     @staticmethod
-    def cpu_sample(max_steps=20):
-        from helium_b200 import configs
+    def cpu_sample(steps=20, warmup=1):
+        cfg = host_configs()
         from oracle import oracle as O
-        g = configs.graph_mlp_train_step()
-        ins = configs.mlp_inputs()
-        O.evaluate(g, ins)
-        t0 = time.perf_counter()
-        for _ in range(max_steps):
+        g = cfg.graph_mlp_train_step()
+        ins = cfg.mlp_inputs()
+        for _ in range(max(1, warmup)):
             O.evaluate(g, ins)
-        dt = (time.perf_counter() - t0) / max_steps
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            O.evaluate(g, ins)
+        dt = (time.perf_counter() - t0) / steps
         try:
             from threadpoolctl import threadpool_info
             cores = max([i.get("num_threads", 1) for i in threadpool_info()] or [1])
         except Exception:
             cores = 1
-        return 1.0 / dt, cores, f"{max_steps} steps of the numpy f64 restatement (oracle/oracle.py) of the same op graph; the reference's CPU backend is a stub", dt
+        return 1.0 / dt, cores, f"{steps} timed steps of the numpy f64 restatement (oracle/oracle.py) of the same op graph; the reference's CPU backend is a stub", dt
 
 
-WORKLOADS = {w.key: w for w in (WorkloadC1, WorkloadC2, WorkloadC3, WorkloadC4, WorkloadC4Graph, WorkloadGemm, WorkloadPointwise)}
+class WorkloadC3Fused(WorkloadC3):
+    """configs[2] with the relu(A) * M rewrite forced into the GEMM's mainloop (one kernel plus the fold of its
+    reductions), where the planner on its own materialises the operand first at this size."""
+    key = "c3f"
+    description = WorkloadC3.description + "; in-kernel mainloop rewrite forced (HE_GEMM_MAINLOOP=fused)"
+
+    def __init__(self, *a, **kw):
+        prev = os.environ.get("HE_GEMM_MAINLOOP")
+        os.environ["HE_GEMM_MAINLOOP"] = "fused"      # read at plan time
+        try:
+            super().__init__(*a, **kw)
+        finally:
+            if prev is None:
+                os.environ.pop("HE_GEMM_MAINLOOP", None)
+            else:
+                os.environ["HE_GEMM_MAINLOOP"] = prev
+
+
+WORKLOADS = {w.key: w for w in (WorkloadC1, WorkloadC2, WorkloadC3, WorkloadC3Fused, WorkloadC4, WorkloadC4Graph, WorkloadGemm,
+                                WorkloadPointwise)}
+DEFAULT_STEPS = {"c1": 2000, "c2": 200, "c3": 200, "c3f": 200, "c4": 30, "c4g": 30, "gemm": 100, "pw": 50}
+# what the default N = 1 run times beside its own workload, and the steps each gets
+SUB_RECORDS = (("configs[2] fused matmul 4096^3 (as planned)", "c3", 100), ("configs[2] with the in-kernel mainloop rewrite", "c3f", 100),
+               ("configs[1] pointwise + permute", "c2", 100), ("configs[0] MLP training step f32", "c1", 1000))
+
+
+def config_for(key: str, world: int) -> dict:
+    """The `config` object of the JSON line: a function of the workload and the rank count only, so that the
+    product arm and `--impl reference` print the same one."""
+    wl = WORKLOADS[key]
+    config = {"workload": wl.description, "l2": wl.l2_note}
+    if key == "c4":
+        n_grads = 2 * wl.D * wl.FF * 2 + (wl.FF + wl.D) * 4
+        config.update({"tokens_per_gpu": wl.TOKENS, "sharding": "tokens",
+                       "grad_allreduce": "NCCL mean through he_allreduce_grads, 3 buckets (dW1, dW2, biases), overlapped with the "
+                                         "remaining backward GEMMs" if world > 1 else "none (1 rank)",
+                       "allreduce_bytes_per_step": n_grads if world > 1 else 0})
+    else:
+        config["replicas"] = world
+    return config
 
 
 def _use_all_host_threads():
@@ -753,17 +824,96 @@ def _use_all_host_threads():
 def run_reference_arm(args):
     """`--impl reference`: the reference is Rust + run-time generated CUDA, has no CPU implementation of
     this path and cannot be built in this image, so the arm times the CPU restatement of the same work
-    (oracle/) on all host cores, on a bounded sample of the workload."""
+    (oracle/) on all host cores.  Every one of the `--steps` timed steps (after `--warmup` untimed ones) is a
+    bounded sample of the workload (the `sample` text says which), scaled to a full step.  Neither the CUDA
+    library nor the package initialiser is loaded."""
     _use_all_host_threads()
     wl = WORKLOADS[args.workload]
-    n = {"c2": min(args.steps, 3), "c1": min(args.steps, 20)}.get(args.workload, 1)
-    value, cores, sample, dt = wl.cpu_sample(max(1, n))
+    value, cores, sample, dt = wl.cpu_sample(max(1, args.steps), max(0, args.warmup))
     line = {"impl": "reference", "metric": wl.metric, "value": value, "unit": wl.unit, "n_gpus": args.gpus,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic", "config": {"workload": wl.description},
+            "steps": max(1, args.steps), "warmup": max(0, args.warmup), "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic", "config": config_for(args.workload, args.gpus),
             "cpu_baseline": {"value": value, "unit": wl.unit, "cores": cores, "kind": "port", "sample": sample},
             "e2e": {"value": value, "unit": wl.unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    assert not any("libhelium_b200" in ln for ln in open("/proc/self/maps")), "the reference arm must not map the CUDA library"
     print(json.dumps(line))
+
+
+def measure(wl, key, steps, warmup, world, dev, barrier, brief, peaks, busy_s=0.6):
+    """Times one workload: `warmup` untimed steps, a short busy loop (so that clock samples cover the timed
+    region), `steps` timed steps between CUDA events bracketed by barrier + synchronize, then the end-to-end
+    leg from pinned host buffers.  Returns the fields of a JSON record (without clocks / cpu_baseline)."""
+    import torch
+    import torch.distributed as dist
+    for _ in range(warmup):
+        wl.step()
+    barrier()
+    t_busy = time.perf_counter()
+    while not brief and time.perf_counter() - t_busy < busy_s:
+        wl.step()
+        torch.cuda.synchronize()
+    records = []
+    t_start = torch.cuda.Event(enable_timing=True); t_end = torch.cuda.Event(enable_timing=True)
+    barrier()
+    t_start.record()
+    for _ in range(steps):
+        wl.step(records)
+    t_end.record()
+    barrier()
+    elapsed_ms = t_start.elapsed_time(t_end)
+    if world > 1:
+        t = torch.tensor([elapsed_ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        elapsed_ms = float(t.item())
+    ms_per_step = elapsed_ms / steps
+    per_kernel = {}
+    for name, a, b in records:
+        per_kernel.setdefault(name, []).append(a.elapsed_time(b))
+    kernel_ms = {k: statistics.mean(v) for k, v in per_kernel.items()}
+
+    # ---- end-to-end leg: host buffers in, host buffers out, copies inside the timed region ----------
+    e2e_steps = {"c1": min(steps, 500), "c2": max(3, min(steps, 40))}.get(key, max(3, min(steps, 10)))
+    if brief:
+        e2e_steps = 0
+    for _ in range(2 if e2e_steps else 0):
+        wl.step_e2e()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        wl.step_e2e()
+    barrier()
+    e2e_sec = (time.perf_counter() - t0) / e2e_steps if e2e_steps else float("nan")
+    if world > 1:
+        t = torch.tensor([e2e_sec], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_sec = float(t.item())
+
+    to_value = lambda sec: wl.work_per_step * world / sec / wl.work_scale
+    dom_key = wl.dominant_key or max(kernel_ms, key=kernel_ms.get)
+    name, work, bound, peak, punit = wl.dominant[dom_key]
+    k_ms = kernel_ms[dom_key]
+    achieved = work / (k_ms * 1e-3) / (1e9 if bound == "hbm" else 1e12)
+    traffic = load_traffic(dom_key)
+    roofline = {"bound": bound, "kernel": name, "achieved": achieved, "peak": peak, "unit": punit, "frac": achieved / peak,
+                "peak_source": peaks["source"] + (": " + wl.peak_note if hasattr(wl, "peak_note") else ""),
+                "kernel_ms": k_ms, "traffic": traffic, "traffic_source": TRAFFIC_SOURCE if traffic is not None else None}
+    if len(kernel_ms) > 1:
+        roofline["kernels"] = {}
+        for k, ms in kernel_ms.items():
+            _, w_k, b_k, p_k, _ = wl.dominant[k]
+            a_k = w_k / (ms * 1e-3) / (1e9 if b_k == "hbm" else 1e12)
+            roofline["kernels"][k] = {"ms": ms, "achieved": a_k, "frac": a_k / p_k, "share_of_step": ms / ms_per_step}
+    rec = {
+        "metric": wl.metric, "value": to_value(ms_per_step * 1e-3), "unit": wl.unit, "n_gpus": world, "steps": steps,
+        "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": wl.dtype, "data": "synthetic", "config": config_for(key, world), "roofline": roofline,
+        "e2e": None if brief else {"value": getattr(wl, "e2e_work_per_step", wl.work_per_step) * world / e2e_sec / wl.work_scale,
+                                   "unit": wl.unit, "h2d_bytes_per_step": wl.h2d,
+                                   "d2h_bytes_per_step": wl.d2h, "ms_per_step": e2e_sec * 1e3, "steps": e2e_steps,
+                                   "pipelining": getattr(wl, "e2e_note", "one stream: upload, kernels, download in order")},
+        "gpu_launches": wl.launches_per_step * steps,
+    }
+    return rec
 
 
 def main():
@@ -772,14 +922,20 @@ def main():
     ap.add_argument("--steps", type=int, default=None)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="c4", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-sub", action="store_true", help="default workload at N = 1: do not time the other configurations as well")
+    ap.add_argument("--reducer", default="comm", choices=["comm", "torch"],
+                    help="gradient exchange of c4 at N > 1: the library's communicator (he_allreduce_grads) or torch.distributed")
+    ap.add_argument("--nccl-ctas", type=int, default=NCCL_CTAS_DEFAULT,
+                    help="c4 at N > 1: CTAs the gradient all-reduce may occupy (ncclConfig maxCTAs); the two GEMMs it overlaps are "
+                         "planned for that many fewer SMs.  0 = NCCL's default and full-device GEMM grids")
     ap.add_argument("--brief", action="store_true",
                     help="profiler captures only: no busy loop before the timed region, no end-to-end leg, no CPU baseline "
                          "(the printed line is then not a bench value)")
     args = ap.parse_args()
     if args.steps is None:
-        args.steps = {"c1": 2000, "c2": 200, "c3": 200, "c4": 30, "c4g": 30, "gemm": 100, "pw": 50}[args.workload]
+        args.steps = DEFAULT_STEPS[args.workload] if args.impl == "ours" else 20
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -795,7 +951,7 @@ def main():
     import torch.distributed as dist
 
     import helium_b200 as hb
-    from helium_b200.grad_sync import GradReducer
+    from helium_b200.grad_sync import CommReducer, GradReducer
 
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: helium_b200 has no CPU path")
@@ -811,106 +967,71 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
-    reducer = GradReducer() if (world > 1 and args.workload == "c4") else None
-    wl = WORKLOADS[args.workload](ctx, dev, world, rank, peaks, reducer)
-    step, step_e2e = wl.step, wl.step_e2e
+    reducer, comm = None, None
+    if world > 1 and args.workload == "c4":
+        if args.reducer == "comm":
+            def exchange(b: bytes) -> bytes:
+                t = torch.tensor(list(b), dtype=torch.uint8, device=dev)
+                dist.broadcast(t, src=0)
+                return bytes(t.cpu().tolist())
+            comm = hb.Comm(ctx, rank, world, exchange, max_ctas=args.nccl_ctas)
+            reducer = CommReducer(comm)
+        else:
+            reducer = GradReducer()
+    wl_kwargs = {"overlap_sms": args.nccl_ctas} if (world > 1 and args.workload == "c4") else {}
+    wl = WORKLOADS[args.workload](ctx, dev, world, rank, peaks, reducer, **wl_kwargs)
 
-    # ---- warm-up, then the timed region ------------------------------------------------------------
     try:
         gpu_id = "GPU-" + str(torch.cuda.get_device_properties(local_rank).uuid)
     except Exception:
         gpu_id = str(local_rank)
     # nvidia-smi needs ~0.2 s to deliver its first sample, so it is started before the warm-up and
-    # read until the end-to-end leg finishes; only samples taken while the GPU was busy are used
+    # read until the last leg finishes; only samples taken while the GPU was busy are used
     sampler = ClockSampler(gpu_id)
     if rank == 0:
         sampler.start()
-    for _ in range(args.warmup):
-        step()
-    barrier()
-    # keep the device busy long enough for the clock record to cover the measurement
-    t_busy = time.perf_counter()
-    while not args.brief and time.perf_counter() - t_busy < 0.6:
-        step()
-        torch.cuda.synchronize()
-    records = []
-    t_start = torch.cuda.Event(enable_timing=True); t_end = torch.cuda.Event(enable_timing=True)
-    barrier()
-    t_start.record()
-    for _ in range(args.steps):
-        step(records)
-    t_end.record()
-    barrier()
-    elapsed_ms = t_start.elapsed_time(t_end)
-    if world > 1:
-        t = torch.tensor([elapsed_ms], device=dev, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        elapsed_ms = float(t.item())
-    ms_per_step = elapsed_ms / args.steps
-    per_kernel = {}
-    for name, a, b in records:
-        per_kernel.setdefault(name, []).append(a.elapsed_time(b))
-    kernel_ms = {k: statistics.mean(v) for k, v in per_kernel.items()}
+    line = measure(wl, args.workload, args.steps, args.warmup, world, dev, barrier, args.brief, peaks)
     ctx.poll()
+    if comm is not None:
+        comm.poll()
+        line["config"]["nccl_max_ctas"] = args.nccl_ctas
+        line["config"]["gemm_sms_reserved_under_allreduce"] = args.nccl_ctas
+    elif reducer is not None:
+        line["config"]["grad_allreduce"] = "NCCL mean through torch.distributed, 3 buckets, overlapped"
+    if rank == 0 and not args.no_cpu_baseline and not args.brief and world == 1:
+        value, cores, sample, _ = WORKLOADS[args.workload].cpu_sample(3, 1)
+        line["cpu_baseline"] = {"value": value, "unit": wl.unit, "cores": cores, "kind": "port", "sample": sample}
 
-    # ---- end-to-end leg: host buffers in, host buffers out, copies inside the timed region ----------
-    e2e_steps = {"c1": min(args.steps, 500), "c2": max(3, min(args.steps, 40))}.get(args.workload, max(3, min(args.steps, 10)))
-    if args.brief:
-        e2e_steps = 0
-    for _ in range(2 if e2e_steps else 0):
-        step_e2e()
-    barrier()
-    t0 = time.perf_counter()
-    for _ in range(e2e_steps):
-        step_e2e()
-    barrier()
-    e2e_sec = (time.perf_counter() - t0) / e2e_steps if e2e_steps else float("nan")
-    if world > 1:
-        t = torch.tensor([e2e_sec], device=dev, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_sec = float(t.item())
+    # ---- the other single-GPU configurations, timed in the same run ---------------------------------
+    if world == 1 and args.workload == "c4" and not args.no_sub and not args.brief:
+        del wl
+        torch.cuda.empty_cache()
+        subs = {}
+        for label, key, sub_steps in SUB_RECORDS:
+            sub = WORKLOADS[key](ctx, dev, 1, 0, peaks, None)
+            rec = measure(sub, key, sub_steps, max(3, args.warmup), 1, dev, barrier, False, peaks, busy_s=0.3)
+            ctx.poll()
+            keep = {k: rec[k] for k in ("metric", "value", "unit", "steps", "ms_per_step", "dtype", "roofline", "e2e", "gpu_launches")}
+            keep["workload"] = rec["config"]["workload"]
+            if not args.no_cpu_baseline:
+                value, cores, sample, _ = WORKLOADS[key].cpu_sample(2, 1)
+                keep["cpu_baseline"] = {"value": value, "unit": rec["unit"], "cores": cores, "kind": "port", "sample": sample}
+            subs[label] = keep
+            line["gpu_launches"] += rec["gpu_launches"]
+            del sub
+            torch.cuda.empty_cache()
+        line["configs"] = subs
 
     clocks = sampler.stop() if rank == 0 else None
     if rank == 0:
-        to_value = lambda sec: wl.work_per_step * world / sec / wl.work_scale
-        dom_key = wl.dominant_key or max(kernel_ms, key=kernel_ms.get)
-        name, work, bound, peak, punit = wl.dominant[dom_key]
-        k_ms = kernel_ms[dom_key]
-        achieved = work / (k_ms * 1e-3) / (1e9 if bound == "hbm" else 1e12)
-        roofline = {"bound": bound, "kernel": name, "achieved": achieved, "peak": peak, "unit": punit, "frac": achieved / peak,
-                    "peak_source": peaks["source"] + (": " + wl.peak_note if hasattr(wl, "peak_note") else ""),
-                    "kernel_ms": k_ms, "traffic": load_traffic(dom_key)}
-        if len(kernel_ms) > 1:
-            roofline["kernels"] = {}
-            for k, ms in kernel_ms.items():
-                _, w_k, b_k, p_k, _ = wl.dominant[k]
-                a_k = w_k / (ms * 1e-3) / (1e9 if b_k == "hbm" else 1e12)
-                roofline["kernels"][k] = {"ms": ms, "achieved": a_k, "frac": a_k / p_k, "share_of_step": ms / ms_per_step}
-        config = {"workload": wl.description, "l2": wl.l2_note}
-        if args.workload == "c4":
-            config.update({"tokens_per_gpu": wl.TOKENS, "sharding": "tokens", "grad_allreduce": "nccl avg, 3 buckets" if world > 1 else "none (1 rank)"})
-            config["allreduce_bytes_per_step"] = (wl.blk.dW_flat.numel() * 2 + wl.blk.db_flat.numel() * 4) if world > 1 else 0
-        else:
-            config["replicas"] = world
-        line = {
-            "metric": wl.metric, "value": to_value(ms_per_step * 1e-3), "unit": wl.unit, "n_gpus": world, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": wl.dtype, "data": "synthetic", "config": config, "roofline": roofline,
-            "e2e": None if args.brief else {"value": getattr(wl, "e2e_work_per_step", wl.work_per_step) * world / e2e_sec / wl.work_scale,
-                                            "unit": wl.unit, "h2d_bytes_per_step": wl.h2d,
-                                            "d2h_bytes_per_step": wl.d2h, "ms_per_step": e2e_sec * 1e3, "steps": e2e_steps,
-                                            "pipelining": getattr(wl, "e2e_note", "one stream: upload, kernels, download in order")},
-            "gpu_launches": wl.launches_per_step * args.steps,
-            "clocks": clocks,
-        }
+        line["clocks"] = clocks
         if args.brief:
             line["note"] = "--brief run for a profiler capture: not a bench value"
-        if not args.no_cpu_baseline and not args.brief and world == 1:
-            value, cores, sample, _ = wl.cpu_sample()
-            line["cpu_baseline"] = {"value": value, "unit": wl.unit, "cores": cores, "kind": "port", "sample": sample}
         print(json.dumps(line))
     if world > 1:
         dist.barrier()
+        if comm is not None:
+            comm.close()
         dist.destroy_process_group()
     return 0
 

@@ -8,6 +8,6 @@ Importing it requires the built library; there is no fallback path.
 from . import configs, ir
 from ._lib import LIB_PATH, HeliumError, lib
 from .host import Executor, HostGraph
-from .runtime import Context, Plan, permute_output_strides, plan_supported
+from .runtime import Comm, Context, Plan, permute_output_strides, plan_supported
 
-__all__ = ["ir", "configs", "HostGraph", "Executor", "lib", "LIB_PATH", "HeliumError", "Context", "Plan", "permute_output_strides", "plan_supported"]
+__all__ = ["ir", "configs", "HostGraph", "Executor", "lib", "LIB_PATH", "HeliumError", "Context", "Plan", "Comm", "permute_output_strides", "plan_supported"]

@@ -8,83 +8,10 @@ from __future__ import annotations
 import ctypes as C
 import os
 
-HE_MAX_RANK = 8
+from ._abi import HE_MAX_RANK, SIGNATURES, HeGraphDesc, HeNode  # noqa: F401  (re-exported)
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "lib", "libhelium_b200.so")
-
-
-class HeNode(C.Structure):
-    """struct he_node of include/helium_b200.h."""
-
-    _fields_ = [
-        ("kind", C.c_int32),
-        ("sub_op", C.c_int32),
-        ("inp", C.c_int32 * 3),
-        ("dtype", C.c_int32),
-        ("rank", C.c_int32),
-        ("shape", C.c_int64 * HE_MAX_RANK),
-        ("const_bits", C.c_uint32),
-        ("axis_a", C.c_int32),
-        ("axis_b", C.c_int32),
-        ("axes", C.c_uint32),
-    ]
-
-
-class HeGraphDesc(C.Structure):
-    """struct he_graph_desc of include/helium_b200.h."""
-
-    _fields_ = [
-        ("num_nodes", C.c_int32),
-        ("nodes", C.POINTER(HeNode)),
-        ("num_outputs", C.c_int32),
-        ("outputs", C.POINTER(C.c_int32)),
-    ]
-
-
-#: every symbol include/helium_b200.h declares: name -> (restype, argtypes)
-SIGNATURES = {
-    "he_ctx_create": (C.c_int32, [C.c_int32, C.POINTER(C.c_void_p)]),
-    "he_ctx_destroy": (None, [C.c_void_p]),
-    "he_ctx_poll_device_status": (C.c_int32, [C.c_void_p, C.c_void_p]),
-    "he_plan_pointwise": (C.c_int32, [C.c_void_p, C.POINTER(HeGraphDesc), C.POINTER(C.c_void_p)]),
-    "he_plan_permute": (C.c_int32, [C.c_void_p, C.c_int32, C.POINTER(C.c_int64), C.POINTER(C.c_int64), C.c_int32,
-                                    C.POINTER(C.c_void_p)]),
-    "he_permute_output_strides": (C.c_int32, [C.c_int32, C.POINTER(C.c_int64), C.c_int32, C.POINTER(C.c_int32),
-                                              C.c_int32, C.POINTER(C.c_int64)]),
-    "he_plan_fused_matmul": (C.c_int32, [C.c_void_p, C.POINTER(HeGraphDesc), C.POINTER(C.c_void_p)]),
-    "he_plan_supported": (C.c_int32, [C.c_void_p, C.POINTER(HeGraphDesc), C.c_int32]),
-    "he_plan_workspace_bytes": (C.c_int32, [C.c_void_p, C.POINTER(C.c_size_t)]),
-    "he_launch": (C.c_int32, [C.c_void_p, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.c_void_p, C.c_void_p]),
-    "he_plan_last_launch_count": (C.c_int32, [C.c_void_p]),
-    "he_plan_describe": (C.c_char_p, [C.c_void_p]),
-    "he_plan_destroy": (None, [C.c_void_p]),
-    "heh_graph_create": (C.c_int32, [C.POINTER(C.c_void_p)]),
-    "heh_graph_destroy": (None, [C.c_void_p]),
-    "heh_graph_new_input": (C.c_int32, [C.c_void_p, C.c_int32, C.c_int32, C.POINTER(C.c_int64), C.POINTER(C.c_int32)]),
-    "heh_graph_new_op": (C.c_int32, [C.c_void_p, C.POINTER(HeNode), C.POINTER(C.c_int32)]),
-    "heh_graph_new_output": (C.c_int32, [C.c_void_p, C.c_int32]),
-    "heh_graph_plan_text": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_char_p, C.c_size_t]),
-    "heh_exec_create": (C.c_int32, [C.c_void_p, C.c_void_p, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.c_int32,
-                                    C.POINTER(C.c_void_p)]),
-    "heh_exec_run": (C.c_int32, [C.c_void_p, C.c_void_p]),
-    "heh_exec_stats": (C.c_int32, [C.c_void_p, C.POINTER(C.c_int32), C.POINTER(C.c_int32), C.POINTER(C.c_int32)]),
-    "heh_exec_destroy": (None, [C.c_void_p]),
-    "he_debug_dump_program": (C.c_int32, [C.POINTER(HeGraphDesc), C.c_int32, C.c_void_p, C.c_size_t, C.POINTER(C.c_size_t)]),
-    "he_debug_canonical_text": (C.c_int32, [C.POINTER(HeGraphDesc), C.c_char_p, C.c_size_t]),
-    "he_comm_unique_id": (C.c_int32, [C.c_void_p]),
-    "he_comm_create": (C.c_int32, [C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_int32, C.c_int32, C.POINTER(C.c_void_p)]),
-    "he_comm_info": (C.c_int32, [C.c_void_p, C.POINTER(C.c_int32), C.POINTER(C.c_int32), C.POINTER(C.c_int32)]),
-    "he_allreduce_grads": (C.c_int32, [C.c_void_p, C.POINTER(C.c_void_p), C.POINTER(C.c_size_t), C.c_int32, C.c_int32, C.c_int32,
-                                       C.c_void_p]),
-    "he_comm_poll": (C.c_int32, [C.c_void_p]),
-    "he_comm_abort": (C.c_int32, [C.c_void_p]),
-    "he_comm_destroy": (None, [C.c_void_p]),
-    "he_debug_plan_fault_injection": (C.c_int32, [C.c_void_p, C.c_uint32, C.c_int32]),
-    "he_last_error_string": (C.c_char_p, []),
-    "he_reduce_sum_f32_noalloc": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_void_p]),
-    "he_version": (C.c_char_p, []),
-}
 
 
 class HeliumError(RuntimeError):

@@ -224,6 +224,13 @@ int32_t he_ctx_create(int32_t device_ordinal, he_ctx** out) {
   return HE_OK;
 }
 
+int32_t he_ctx_reserve_sms(he_ctx* ctx, int32_t sms) {
+  if (!ctx) HE_FAIL(HE_ERR_INVALID, "he_ctx_reserve_sms: ctx is null");
+  if (sms < 0 || sms > ctx->sm_count - 2) HE_FAIL(HE_ERR_INVALID, "he_ctx_reserve_sms: %d is not in [0, %d]", sms, ctx->sm_count - 2);
+  ctx->sm_reserved = sms;
+  return HE_OK;
+}
+
 void he_ctx_destroy(he_ctx* ctx) {
   if (!ctx) return;
   if (ctx->d_status) cudaFree(ctx->d_status);

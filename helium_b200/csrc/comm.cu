@@ -53,7 +53,8 @@ NcclApi* nccl_api() {
       if (n == forced) break;   // an explicit choice that fails is an error, not a reason to fall through
     }
     if (!api.handle) {
-      api.error = std::string("could not load NCCL: ") + (dlerror() ? dlerror() : "libnccl.so.2 not found");
+      const char* why = dlerror();   // a second call would return NULL: the message is consumed by the first
+      api.error = std::string("could not load NCCL: ") + (why ? why : "libnccl.so.2 not found");
       return;
     }
     auto sym = [&](const char* name) -> void* {

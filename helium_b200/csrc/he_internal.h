@@ -71,13 +71,14 @@ struct DeviceStatus {
 struct he_ctx {
   int device = 0;
   int sm_count = 0;
+  int sm_reserved = 0;   // he_ctx_reserve_sms: SMs that plans created from now on leave to other work
   int max_smem_optin = 0;
   he::DeviceStatus* d_status = nullptr;  // device memory
 };
 
 // A plan may be created with a null context ("planning only": tier, tile shape and workspace can
 // be inspected, launching is refused); such plans assume the SM count of a B200.
-inline int ctx_sm_count(const he_ctx* c) { return c ? c->sm_count : 148; }
+inline int ctx_sm_count(const he_ctx* c) { return c ? (c->sm_count - c->sm_reserved > 2 ? c->sm_count - c->sm_reserved : 2) : 148; }
 
 // Base of every plan.  Immutable after creation except for the launch counter.
 struct he_plan {

@@ -88,6 +88,50 @@ class GradReducer:
             torch.cuda.current_stream().wait_stream(self._stream)
 
 
+class CommReducer:
+    """The same bucket / finish interface over the library's own communicator (he_comm, NCCL behind the C
+    ABI) instead of torch.distributed: each bucket is one he_allreduce_grads call on a side stream, ordered
+    after the producer kernel by an event.  This is the path a non-Python host takes."""
+
+    def __init__(self, comm, mean: bool = True):
+        self.comm = comm
+        self.world = comm.world
+        self.enabled = comm.world > 1
+        self.mean = mean
+        self._stream = None
+        self._dirty = False
+        self.bytes_reduced = 0
+        self.collectives = 0
+
+    def reduce_bucket(self, tensors: Sequence, after_event=None) -> None:
+        import torch
+
+        if not tensors:
+            return
+        for t in tensors:
+            self.bytes_reduced += t.numel() * t.element_size()
+        if not self.enabled:
+            return
+        if self._stream is None:
+            self._stream = torch.cuda.Stream(device=tensors[0].device)
+        ev = after_event
+        if ev is None:
+            ev = torch.cuda.Event()
+            ev.record(torch.cuda.current_stream())
+        self._stream.wait_event(ev)
+        self.comm.allreduce(list(tensors), mean=self.mean, stream=self._stream)
+        self.collectives += len(tensors)
+        self._dirty = True
+
+    def finish(self) -> None:
+        import torch
+
+        if self._dirty:
+            torch.cuda.current_stream().wait_stream(self._stream)
+            self._dirty = False
+        self.comm.poll()   # an asynchronous NCCL error surfaces here, once per step
+
+
 def shard_rows(total_rows: int, world: int, rank: int) -> range:
     """Rows of a batch-sharded tensor owned by `rank`: contiguous blocks, the first `total % world`
     ranks one row longer."""
@@ -114,4 +158,4 @@ def bucket_by_bytes(sizes_bytes: Sequence[int], cap_bytes: int) -> List[List[int
     return buckets
 
 
-__all__ = ["GradReducer", "shard_rows", "bucket_by_bytes"]
+__all__ = ["GradReducer", "CommReducer", "shard_rows", "bucket_by_bytes"]

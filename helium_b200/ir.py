@@ -11,7 +11,7 @@ import struct
 from dataclasses import dataclass, field
 from typing import List, Sequence, Tuple
 
-from ._lib import HE_MAX_RANK, HeGraphDesc, HeNode
+from ._abi import HE_MAX_RANK, HeGraphDesc, HeNode
 
 # ---- enums (values = include/helium_b200.h) ------------------------------------------------------
 F16, BF16, F32, U32, BOOL = 0, 1, 2, 3, 4

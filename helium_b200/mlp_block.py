@@ -64,12 +64,23 @@ def flops_per_token(d: int, ff: int) -> int:
 class MlpBlock:
     """Plans + device buffers for one rank's shard of tokens."""
 
-    def __init__(self, ctx: Context, tokens: int, d: int, ff: int, device=None):
+    def __init__(self, ctx: Context, tokens: int, d: int, ff: int, device=None, overlap_sms: int = 0):
+        """`overlap_sms` > 0: the two GEMMs that run while a weight-gradient all-reduce is in flight (dW2
+        and dX) are planned for that many fewer SMs, so their persistent grids and the collective's CTAs
+        do not queue behind each other."""
         import torch
 
         self.tokens, self.d, self.ff = tokens, d, ff
         self.graphs = mlp_block_graphs(tokens, d, ff)
-        self.plans = {k: Plan.fused_matmul(ctx, g) for k, g in self.graphs.items()}
+        self.plans = {}
+        for k, g in self.graphs.items():
+            if overlap_sms and k in ("dW2", "dX"):
+                ctx.reserve_sms(overlap_sms)
+            try:
+                self.plans[k] = Plan.fused_matmul(ctx, g)
+            finally:
+                if overlap_sms:
+                    ctx.reserve_sms(0)
         dev = device if device is not None else torch.device("cuda", ctx.device)
         bf = torch.bfloat16
         e = lambda *s: torch.empty(s, dtype=bf, device=dev)

@@ -41,6 +41,10 @@ class Context:
         self._h = h
         self.device = device
 
+    def reserve_sms(self, sms: int) -> None:
+        """he_ctx_reserve_sms: plans created afterwards leave `sms` SMs to concurrent work."""
+        check(lib.he_ctx_reserve_sms(self._h, sms))
+
     def poll(self, stream=None) -> None:
         check(lib.he_ctx_poll_device_status(self._h, C.c_void_p(_stream_ptr(stream))))
 
@@ -178,6 +182,50 @@ class Plan:
             pass
 
 
+class Comm:
+    """he_comm: NCCL communicator behind the C ABI (one per process / GPU).  The 128-byte unique id is made
+    on rank 0 and handed out through `exchange`, a callable bytes -> bytes that broadcasts rank 0's value
+    (a torch.distributed broadcast in bench.py and the tests; any other channel works)."""
+
+    def __init__(self, ctx: Optional[Context], rank: int, world: int, exchange, max_ctas: int = 0, timeout_ms: int = 60000):
+        uid = C.create_string_buffer(128)
+        if rank == 0:
+            check(lib.he_comm_unique_id(uid))
+        uid = C.create_string_buffer(exchange(bytes(uid.raw)), 128)
+        h = C.c_void_p()
+        check(lib.he_comm_create(ctx._h if ctx else None, rank, world, uid, max_ctas, timeout_ms, C.byref(h)))
+        self._h = h
+        self.rank, self.world, self.max_ctas = rank, world, max_ctas
+
+    def allreduce(self, tensors: Sequence, mean: bool = True, stream=None) -> None:
+        """In-place sum / mean over ranks of same-dtype CUDA tensors, one NCCL group on `stream`."""
+        torch = _torch()
+        if not tensors:
+            return
+        dt = {torch.float16: ir.F16, torch.bfloat16: ir.BF16, torch.float32: ir.F32}[tensors[0].dtype]
+        n = len(tensors)
+        bufs = (C.c_void_p * n)(*[t.data_ptr() for t in tensors])
+        counts = (C.c_size_t * n)(*[t.numel() for t in tensors])
+        check(lib.he_allreduce_grads(self._h, bufs, counts, n, dt, 1 if mean else 0, C.c_void_p(_stream_ptr(stream))))
+
+    def poll(self) -> None:
+        check(lib.he_comm_poll(self._h))
+
+    def abort(self) -> None:
+        check(lib.he_comm_abort(self._h))
+
+    def close(self) -> None:
+        if self._h:
+            lib.he_comm_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
 def plan_supported(graph: ir.Graph, kind: int, ctx: Optional[Context] = None) -> int:
     """he_plan_supported: 0 unsupported, 1 interpreter tier, 2 hand-written kernel."""
     desc, keep = graph.to_desc()
@@ -196,4 +244,4 @@ def permute_output_strides(in_shape: Sequence[int], swaps: Sequence[tuple], refe
     return list(out)
 
 
-__all__ = ["Context", "Plan", "HeliumError", "plan_supported", "permute_output_strides", "storage_elems"]
+__all__ = ["Context", "Plan", "Comm", "HeliumError", "plan_supported", "permute_output_strides", "storage_elems"]

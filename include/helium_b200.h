@@ -135,6 +135,12 @@ typedef struct he_plan he_plan;
  * allocates one 64-byte device status block used by bounded device-side waits. */
 int32_t he_ctx_create(int32_t device_ordinal, he_ctx** out);
 void he_ctx_destroy(he_ctx* ctx);
+/* Plans created after this call size their persistent grids for (SM count - sms) SMs.  For a kernel that
+ * is meant to run beside other work on the same GPU -- the GEMM that overlaps a gradient all-reduce whose
+ * communicator was created with `max_ctas` = sms: a persistent grid that claims every SM would have
+ * some of its CTAs wait for the collective's to retire.  0 restores the full device.  Existing plans keep
+ * the grid they were planned with.  No counterpart in the reference (one stream, one kernel at a time). */
+int32_t he_ctx_reserve_sms(he_ctx* ctx, int32_t sms);
 /* Reads (synchronously, after syncing `cu_stream`) and clears the device status word.
  * Returns HE_OK or HE_ERR_DEVICE_TIMEOUT; detail in he_last_error_string(). */
 int32_t he_ctx_poll_device_status(he_ctx* ctx, void* cu_stream);
