@@ -39,20 +39,23 @@ EncodeTiledFn get_encode_fn() {
 }
 
 // Operand tensor [batch, R, K] (K-major) or [batch, K, R] (MN-major), 2-byte elements.
+// `pitch` = elements between consecutive rows of the stored matrix (0: dense, i.e. K or R).
 int32_t make_operand_tmap(CUtensorMap* out, const void* ptr, int ab_format, bool mn_major, int64_t R, int64_t K,
-                          int64_t batch, int box_rows) {
+                          int64_t batch, int box_rows, int64_t pitch = 0) {
   EncodeTiledFn fn = get_encode_fn();
   if (!fn) HE_FAIL(HE_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
   if ((uintptr_t)ptr % 16 != 0) HE_FAIL(HE_ERR_UNSUPPORTED, "fused matmul: operand pointer is not 16-byte aligned");
   cuuint64_t dims[3], strides[2];
   cuuint32_t box[3], estr[3] = {1, 1, 1};
   if (!mn_major) {
+    const cuuint64_t ld = (cuuint64_t)(pitch ? pitch : K);
     dims[0] = (cuuint64_t)K; dims[1] = (cuuint64_t)R; dims[2] = (cuuint64_t)batch;
-    strides[0] = (cuuint64_t)K * 2; strides[1] = (cuuint64_t)R * K * 2;
+    strides[0] = ld * 2; strides[1] = (cuuint64_t)R * ld * 2;
     box[0] = kBK; box[1] = (cuuint32_t)box_rows; box[2] = 1;
   } else {
+    const cuuint64_t ld = (cuuint64_t)(pitch ? pitch : R);
     dims[0] = (cuuint64_t)R; dims[1] = (cuuint64_t)K; dims[2] = (cuuint64_t)batch;
-    strides[0] = (cuuint64_t)R * 2; strides[1] = (cuuint64_t)R * K * 2;
+    strides[0] = ld * 2; strides[1] = (cuuint64_t)K * ld * 2;
     box[0] = 64; box[1] = kBK; box[2] = 1;
   }
   if (strides[0] % 16 != 0) HE_FAIL(HE_ERR_UNSUPPORTED, "fused matmul: operand row pitch %llu B is not a multiple of 16", (unsigned long long)strides[0]);
@@ -395,6 +398,13 @@ struct MatmulPlan : he_plan {
   // cost more than one extra pass over A and the mask.
   bool materialise_a = false;
   size_t ws_aprime_off = 0;   // bytes
+  // Operands whose row pitch is not a multiple of 16 bytes cannot be described to TMA.  They are copied
+  // once per launch into the workspace with the pitch rounded up to 8 elements (`pad_pitch`), and the
+  // tensor map reads that copy with the true extent, so the ragged edge is zero-filled by TMA as usual.
+  // The reference's generator serves such shapes with predicated mma.sync tiles
+  // (helium-kernel-generator/src/generators/matmul/sm80.rs:470-526); here they stay on tcgen05.
+  int64_t pad_pitch[2] = {0, 0};   // A, B
+  size_t ws_pad_off[2] = {0, 0};   // bytes
 
   int32_t set_fault_injection(uint32_t wait_limit_us, int32_t withhold_loads) override {
     if (kind == EpiKind::Sgemm) HE_FAIL(HE_ERR_UNSUPPORTED, "the SIMT matmul has no device-side waits to bound");
@@ -439,8 +449,20 @@ struct MatmulPlan : he_plan {
       cfg.ml = ML_NONE;
       extra_launches = 1;
     }
-    HE_TRY(make_operand_tmap(&ta, a_ptr, core.ab_format, cfg.a_mn, core.M, core.K, core.batch, kBM));
-    HE_TRY(make_operand_tmap(&tb, inputs[b_slot], core.ab_format, cfg.b_mn, core.N, core.K, core.batch, cfg.two_cta ? 128 : cfg.bn));
+    const void* b_ptr = inputs[b_slot];
+    for (int side = 0; side < 2; ++side) {
+      if (!pad_pitch[side]) continue;
+      // stored matrix: rows x cols with cols contiguous
+      const bool mn = side == 0 ? cfg.a_mn : cfg.b_mn;
+      const int64_t R = side == 0 ? core.M : core.N;
+      const int64_t rows = (mn ? core.K : R) * core.batch, cols = mn ? R : core.K;
+      void* dst = reinterpret_cast<char*>(workspace) + ws_pad_off[side];
+      HE_TRY(launch_pad_rows(side == 0 ? a_ptr : b_ptr, dst, rows, cols, pad_pitch[side], stream));
+      (side == 0 ? a_ptr : b_ptr) = dst;
+      ++extra_launches;
+    }
+    HE_TRY(make_operand_tmap(&ta, a_ptr, core.ab_format, cfg.a_mn, core.M, core.K, core.batch, kBM, pad_pitch[0]));
+    HE_TRY(make_operand_tmap(&tb, b_ptr, core.ab_format, cfg.b_mn, core.N, core.K, core.batch, cfg.two_cta ? 128 : cfg.bn, pad_pitch[1]));
     if (mask_slot >= 0 && !materialise_a) HE_TRY(make_operand_tmap(&tm, inputs[mask_slot], core.ab_format, cfg.a_mn, core.M, core.K, core.batch, kBM));
     GemmCore c = core;
     c.status = ctx ? ctx->d_status : nullptr;
@@ -846,16 +868,29 @@ int32_t plan_fused_matmul_core(he_ctx* ctx, const Graph& g, he_plan** out, int* 
   c.group_m = 1;
   c.wait_limit_us = ptx::kDefaultWaitLimitUs;
   c.withhold_loads = 0;
+  {
+    const char* e = getenv("HE_GEMM_K_SERPENTINE");
+    c.k_serpentine = e ? (e[0] == '1') : 1;
+  }
   if (plan->cfg.ml != ML_NONE && plan->cfg.ml != ML_RELU_MASK)
     HE_FAIL(HE_ERR_UNSUPPORTED, "fused matmul: only the relu(A) * mask mainloop fusion is compiled in");
   if (plan->cfg.ml != ML_NONE && (An.dtype != HE_BF16 || g.nodes[A.mask].dtype != HE_BF16))
     HE_FAIL(HE_ERR_UNSUPPORTED, "fused matmul: mainloop fusion needs bf16 A and mask");
-  // TMA pitch rules (16-byte multiples)
-  if ((plan->cfg.a_mn ? c.M : c.K) % 8 != 0 || (plan->cfg.b_mn ? c.N : c.K) % 8 != 0) {
-    const int32_t st = try_simt("operand rows are not multiples of 8 elements, TMA needs 16-byte pitches");
-    if (st != HE_OK)
-      HE_FAIL(HE_ERR_UNSUPPORTED, "fused matmul: operand row lengths must be multiples of 8 elements for TMA (M=%d N=%d K=%d) and the epilogue is beyond the SIMT path", c.M, c.N, c.K);
-    return st;
+  // TMA pitch rules (16-byte multiples).  Small problems off the rules run on the SIMT kernel when its
+  // epilogues cover the graph; everything else gets a pitch-padded copy of the offending operand.
+  const int64_t a_cols = plan->cfg.a_mn ? c.M : c.K, b_cols = plan->cfg.b_mn ? c.N : c.K;
+  std::string pad_note;
+  if (a_cols % 8 != 0 || b_cols % 8 != 0) {
+    const double flop = 2.0 * c.batch * c.M * (double)c.N * c.K;
+    if (flop < 268435456.0 && plan->cfg.ml == ML_NONE) {
+      set_error("");
+      const int32_t st = try_simt("operand rows are not multiples of 8 elements, TMA needs 16-byte pitches");
+      if (st == HE_OK) return st;
+    }
+    if (plan->cfg.ml != ML_NONE)
+      HE_FAIL(HE_ERR_UNSUPPORTED, "fused matmul: in-kernel mainloop fusion needs operand rows that are multiples of 8 elements (M=%d N=%d K=%d)", c.M, c.N, c.K);
+    if (a_cols % 8 != 0) { plan->pad_pitch[0] = (a_cols + 7) / 8 * 8; pad_note += ", A copied to a 16-byte pitch"; }
+    if (b_cols % 8 != 0) { plan->pad_pitch[1] = (b_cols + 7) / 8 * 8; pad_note += ", B copied to a 16-byte pitch"; }
   }
 
   // ---- epilogue
@@ -909,7 +944,15 @@ int32_t plan_fused_matmul_core(he_ctx* ctx, const Graph& g, he_plan** out, int* 
   // plain rate (1316 -> 680-770 TFLOP/s at 4096^3), i.e. it adds ~0.7 x the plain GEMM time; the
   // pre-pass reads A and the mask and writes A' once at ~4.5 TB/s plus a launch.
   auto choose_mainloop = [&]() -> std::string {
-    if (plan->cfg.ml == ML_NONE) return "";
+    // pitch-padded operand copies live behind the epilogue's own workspace
+    for (int side = 0; side < 2; ++side) {
+      if (!plan->pad_pitch[side]) continue;
+      const bool mn = side == 0 ? plan->cfg.a_mn : plan->cfg.b_mn;
+      const int64_t rows = (mn ? c.K : (side == 0 ? c.M : c.N)) * (int64_t)c.batch;
+      plan->ws_pad_off[side] = (plan->workspace_bytes + 255) / 256 * 256;
+      plan->workspace_bytes = plan->ws_pad_off[side] + (size_t)rows * plan->pad_pitch[side] * 2;
+    }
+    if (plan->cfg.ml == ML_NONE) return pad_note;
     const double gemm_us = 2.0 * c.batch * c.M * (double)c.N * c.K / 1.3e9;
     const double bytes = 3.0 * c.batch * c.M * (double)c.K * 2.0;
     const double prepass_us = bytes / 4.5e6 + 5.0;

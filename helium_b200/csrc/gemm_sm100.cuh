@@ -43,6 +43,7 @@ struct GemmCore {
   // he_ctx_poll_device_status reports HE_ERR_DEVICE_TIMEOUT).  Set only by he_debug_plan_fault_injection.
   unsigned wait_limit_us;
   int withhold_loads;
+  int k_serpentine;   // pair kernel: odd tiles of a CTA walk K from the end (L2 reuse between waves)
   DeviceStatus* status;
 };
 
@@ -821,6 +822,31 @@ __device__ __forceinline__ void tmem_ld_chunk(uint32_t taddr, float (&v)[CH]) {
   }
 }
 
+// Issue of a chunk load without its wait, and the walk over a warp's column chunks with the load of chunk
+// i + 1 in flight while chunk i is computed: the TMEM read latency leaves the per-chunk dependent chain.
+template <int CH>
+__device__ __forceinline__ void tmem_ld_issue(uint32_t taddr, uint32_t (&r)[CH]) {
+  if constexpr (CH == 32) ptx::tmem_ld_32x32(taddr, r);
+  else ptx::tmem_ld_32x16(taddr, r);
+}
+template <class Epi, class State>
+__device__ __forceinline__ void epilogue_walk_chunks(const typename Epi::Params& ep, const EpiEnv& env, const TileInfo& t, State& st,
+                                                     uint32_t taddr0, int row, int col_begin, int col_end) {
+  constexpr int CH = Epi::kChunk;
+  uint32_t nxt[CH];
+  if (col_begin < col_end) tmem_ld_issue<CH>(taddr0 + (uint32_t)col_begin, nxt);
+#pragma unroll 1
+  for (int col = col_begin; col < col_end; col += CH) {
+    float v[CH];
+    ptx::tmem_ld_wait_regs(nxt);
+#pragma unroll
+    for (int i = 0; i < CH; ++i) v[i] = __uint_as_float(nxt[i]);
+    if (col + CH < col_end) tmem_ld_issue<CH>(taddr0 + (uint32_t)(col + CH), nxt);
+    Epi::chunk(ep, env, t, st, row, col, v);
+  }
+  ptx::tmem_ld_wait();   // nothing of this warp is left in flight when the accumulator is handed back
+}
+
 template <int BN, int STAGES, bool A_MN, bool B_MN, int ML, int NE_WARPS, class Epi>
 __global__ void __launch_bounds__(32 * (2 + NE_WARPS + (ML != ML_NONE ? 4 : 0)), 1)
 gemm_tcgen05_kernel(const __grid_constant__ GemmParams<typename Epi::Params> p) {
@@ -1000,14 +1026,10 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmParams<typename Epi::Params> p) 
       if (!dead) {
         ptx::tcgen05_fence_after();
         const int row = env.quadrant * 32 + lane;
-#pragma unroll 1
-        for (int col = col_begin; col < col_begin + kColsPerWarp; col += CH) {
-          if (t.n0 + col >= c.N) break;
-          float v[CH];
-          const uint32_t taddr = tmem_base + ((uint32_t)(env.quadrant * 32) << 16) + (uint32_t)(acc * BN + col);
-          tmem_ld_chunk<CH>(taddr, v);
-          Epi::chunk(p.epi, env, t, st, row, col, v);
-        }
+        const uint32_t taddr0 = tmem_base + ((uint32_t)(env.quadrant * 32) << 16) + (uint32_t)(acc * BN);
+        // chunks that start at or beyond N are skipped (a ragged last chunk is handled inside the functor)
+        const int col_end = min(col_begin + kColsPerWarp, ((c.N - t.n0 + CH - 1) / CH) * CH);
+        epilogue_walk_chunks<Epi>(p.epi, env, t, st, taddr0, row, col_begin, col_end);
         ptx::tcgen05_fence_before();
         __syncwarp();
         if (lane == 0) ptx::mbar_arrive(bar_tmem_empty(acc));   // 128+ arrivals on one word would serialise

@@ -185,7 +185,8 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ GemmParams<typename Epi::Params
       int stage = 0;
       uint32_t phase = 0;
       bool alive = true;
-      for (int tile = pair; alive && !c.withhold_loads && tile < pair_tiles; tile += n_pairs) {
+      int it = 0;
+      for (int tile = pair; alive && !c.withhold_loads && tile < pair_tiles; tile += n_pairs, ++it) {
         const TileInfo t = decode_tile(tile);
         for (int kb = 0; kb < c.k_blocks; ++kb) {
           if (!ptx::mbar_wait(bar_empty(stage), phase ^ 1u, abort_flag, c.status, 1, stage, c.wait_limit_us)) { alive = false; break; }
@@ -195,7 +196,11 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ GemmParams<typename Epi::Params
           const bool half_b = t.bn < BN && B_MN;
           if (leader) ptx::mbar_arrive_expect_tx(bar_full_b(stage), kLeaderBytes - (half_b ? kBHalfBytes : 0));
           if (kFused) ptx::mbar_arrive_expect_tx(bar_full_a(stage), kABytes);
-          const int k0 = kb * kBK;
+          // Every other tile of a CTA walks K backwards.  All pairs are on the same tile count at about the
+          // same time, so a wave that starts where the previous one stopped finds the tail of the operand
+          // panels it shares with that wave still in L2 (the sum order within a tile changes, the result
+          // stays a fixed function of the inputs).
+          const int k0 = ((c.k_serpentine && (it & 1)) ? c.k_blocks - 1 - kb : kb) * kBK;
           const uint32_t a_dst = smem_base + SM::off_a + stage * kATileBytes;
           const uint32_t b_dst = smem_base + SM::off_b + stage * kBHalfBytes;
           // A (and the mask): this CTA's 128 rows
@@ -302,14 +307,9 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ GemmParams<typename Epi::Params
       if (!dead) {
         ptx::tcgen05_fence_after();
         const int row = env.quadrant * 32 + lane;
-#pragma unroll 1
-        for (int col = col_begin; col < col_begin + kColsPerWarp; col += CH) {
-          if (t.n0 + col >= c.N) break;
-          float v[CH];
-          const uint32_t taddr = tmem_base + ((uint32_t)(env.quadrant * 32) << 16) + (uint32_t)(acc * BN + col);
-          tmem_ld_chunk<CH>(taddr, v);
-          Epi::chunk(p.epi, env, t, st, row, col, v);
-        }
+        const uint32_t taddr0 = tmem_base + ((uint32_t)(env.quadrant * 32) << 16) + (uint32_t)(acc * BN);
+        const int col_end = min(col_begin + kColsPerWarp, ((c.N - t.n0 + CH - 1) / CH) * CH);
+        epilogue_walk_chunks<Epi>(p.epi, env, t, st, taddr0, row, col_begin, col_end);
         ptx::tcgen05_fence_before();
         __syncwarp();
         if (lane == 0) ptx::mbar_arrive_cluster(ptx::mapa(bar_tmem_empty(acc), 0));

@@ -251,4 +251,30 @@ int32_t launch_dense_elementwise(int kind, int dtype, const void* const* in, voi
   }
 }
 
+// Row re-pitching copy for matmul operands whose row length breaks the 16-byte rule of TMA.  A warp walks a
+// row in 64-byte steps of 2-byte loads (source rows of odd length start on odd 2-byte addresses) and
+// writes the 16-byte-aligned destination row the same way; HBM-bound in spite of the narrow accesses
+// because every byte of every sector that is touched is used.
+__global__ void __launch_bounds__(256) pad_rows_kernel(const unsigned short* __restrict__ src, unsigned short* __restrict__ dst,
+                                                       long long rows, long long cols, long long dst_pitch) {
+  const int lane = threadIdx.x & 31;
+  const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const long long n_warps = ((long long)gridDim.x * blockDim.x) >> 5;
+  for (long long r = warp; r < rows; r += n_warps) {
+    const unsigned short* s = src + r * cols;
+    unsigned short* d = dst + r * dst_pitch;
+    for (long long c = lane; c < cols; c += 32) d[c] = __ldg(s + c);
+  }
+}
+
+int32_t launch_pad_rows(const void* src, void* dst, long long rows, long long cols, long long dst_pitch, cudaStream_t stream) {
+  if (rows <= 0 || cols <= 0) return HE_OK;
+  const long long warps = std::min<long long>(rows, 148ll * 64);
+  const unsigned grid = (unsigned)((warps * 32 + 255) / 256);
+  pad_rows_kernel<<<grid, 256, 0, stream>>>(reinterpret_cast<const unsigned short*>(src), reinterpret_cast<unsigned short*>(dst), rows,
+                                            cols, dst_pitch);
+  HE_CUDA(cudaGetLastError());
+  return HE_OK;
+}
+
 }  // namespace he

@@ -30,4 +30,9 @@ int32_t launch_dense_elementwise(int kind, int dtype, const void* const* in, voi
 int32_t launch_colsum_dense(int dtype, const void* x, float* out_or_partials, unsigned batch, unsigned M, unsigned N,
                             unsigned slices, unsigned rows_per_slice, cudaStream_t stream);
 
+// Copies a dense [rows, cols] matrix of 2-byte elements to a matrix with row pitch `dst_pitch` elements
+// (dst_pitch >= cols); the padding columns are not written.  Source rows may start at any 2-byte
+// address (cols odd), so reads are 2-byte accesses, coalesced along the row.
+int32_t launch_pad_rows(const void* src, void* dst, long long rows, long long cols, long long dst_pitch, cudaStream_t stream);
+
 }  // namespace he

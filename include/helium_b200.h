@@ -180,6 +180,7 @@ int32_t he_plan_fused_matmul(he_ctx* ctx, const he_graph_desc* desc, he_plan** o
  *   HE_GEMM_GROUP_M=<n>       row tiles per rasterisation group
  *   HE_GEMM_NO_SPLIT=1        never run the tiles of an under-filled last round as half-width tiles
  *   HE_GEMM_MAINLOOP=fused|materialise   force how a mainloop fusion is executed
+ *   HE_GEMM_K_SERPENTINE=0    every tile walks K forwards (default: every other tile of a CTA pair backwards)
  * None of them changes results. */
 
 /* Backs Instruction::can_fuse_with (helium/src/backend.rs:85-95): 0 = cannot run as one kernel,
