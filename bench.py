@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the fused-kernel hot path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c4|c3|c3f|c2|c1|c4g|gemm|pw] [--impl ours|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c4|c5|c3|c3f|c2|c1|c4g|gemm|pw] [--impl ours|reference]
 
 Default workload "c4": the transformer MLP block forward + backward, bf16, 8192 tokens per GPU, d 4096,
 ff 16384 -- six fused GEMMs per step, metric fused-GEMM TFLOP/s.  With N > 1 (launched under
@@ -769,6 +769,102 @@ class WorkloadC1:
         return 1.0 / dt, cores, f"{steps} timed steps of the numpy f64 restatement (oracle/oracle.py) of the same op graph; the reference's CPU backend is a stub", dt
 
 
+class WorkloadC5:
+    """configs[4]: one training step of the convolutional network of resnet-train (the model the reference trains on
+    ImageNet; BASELINE calls it ResNet-50, the reference contains no 50-layer network), batch 128 per GPU of synthetic
+    3 x 224 x 224 images, 1000 classes, bf16 activations / f32 master weights, SGD with helium's momentum 0.9."""
+    key = "c5"
+    metric, unit = "train_steps_per_s", "step/s"
+    dtype = "bf16 x bf16 -> f32 accumulate (implicit-GEMM convolutions), f32 master weights"
+    BATCH, HW, CLASSES = 128, 224, 1000
+    description = ("configs[4]: resnet-train network (7x7/2 head, 4 x (downsample block + basic block), bn/relu, 1x1 to 1000 classes), "
+                   "training step forward + backward + SGD momentum 0.9, batch 128 per GPU of synthetic 3x224x224 images, bf16 compute, f32 "
+                   "master weights; implicit-GEMM convolutions with bias / residual / batch-statistics epilogues")
+    l2_note = "activations of one step (several GB) exceed L2; every step re-reads them"
+    work_per_step = 1.0
+    work_scale = 1.0
+
+    def __init__(self, ctx, dev, world, rank, peaks, reducer):
+        import torch
+        from helium_b200 import convnet
+        self.torch, self.reducer = torch, reducer
+        self.net = convnet.ConvNet(ctx, self.BATCH, self.HW, self.CLASSES, dev)
+        self.net.load_params(convnet.init_params(4, self.CLASSES))
+        bits, labels = convnet.synthetic_batch(self.BATCH, self.HW, self.CLASSES, seed=4, shard=rank)
+        self.x_pin = torch.from_numpy(bits.view(np.int16)).pin_memory()
+        self.l_pin = torch.from_numpy(labels).pin_memory()
+        self.loss_pin = torch.zeros(self.BATCH, dtype=torch.float32).pin_memory()
+        self.net.acts["x0"].view(torch.int16).copy_(self.x_pin)
+        self.net.labels.copy_(self.l_pin)
+        self.h2d = self.x_pin.numel() * 2 + self.l_pin.numel() * 4
+        self.d2h = self.BATCH * 4
+        self.net.step(0.01, self.reducer)
+        self.launches_per_step = self.net.launches
+        flops = 3.0 * convnet.flops_per_image(self.HW, self.CLASSES) * self.BATCH
+        peak = peaks.get("bf16_tflops_sustained") or peaks["bf16_tflops"]
+        self.dominant = {"step": (f"whole step: {self.launches_per_step} launches, {flops / 1e12:.3f} TFLOP of convolution math "
+                                  "(forward + data and filter gradients)", flops, "tensor", peak, "TFLOP/s"),
+                         "forward": ("forward pass", flops / 3, "tensor", peak, "TFLOP/s"),
+                         "backward": ("backward pass", 2 * flops / 3, "tensor", peak, "TFLOP/s")}
+        self.dominant_key = "step"
+        self.peak_note = "sustained cuBLAS bf16 figure; the step is a mix of tensor-core and HBM-bound kernels, so the fraction is informational"
+
+    def step(self, record=None):
+        net, torch = self.net, self.torch
+        if record is None:
+            net.step(0.01, self.reducer)
+            return
+        st = torch.cuda.current_stream()
+        e = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+        net.launches = 0
+        net.g_vec2.zero_()
+        e[0].record(st); net.forward(); e[1].record(st); net.backward(); e[2].record(st)
+        if self.reducer is not None:
+            self.reducer.reduce_bucket([net.g_conv]); self.reducer.reduce_bucket([net.g_vec, net.g_vec2]); self.reducer.finish()
+        net.optimizer_step(0.01); e[3].record(st)
+        record.append(("forward", e[0], e[1])); record.append(("backward", e[1], e[2])); record.append(("step", e[0], e[3]))
+
+    e2e_note = "one stream: image upload, step, loss download queued back to back without host synchronisation"
+
+    def step_e2e(self):
+        torch = self.torch
+        self.net.acts["x0"].view(torch.int16).copy_(self.x_pin, non_blocking=True)
+        self.net.labels.copy_(self.l_pin, non_blocking=True)
+        self.net.step(0.01, self.reducer)
+        self.loss_pin.copy_(self.net.loss, non_blocking=True)
+
+    @staticmethod
+    def cpu_sample(steps=1, warmup=0):
+        """The float64 torch restatement of the same step on 2 images per timed step, scaled linearly to 128."""
+        import torch
+        from oracle import convnet_torch as CT
+        # parameters / images without the package (its initialiser would load the CUDA library)
+        r = np.random.Generator(np.random.Philox(4))
+        names = CT.parameter_shapes(WorkloadC5.CLASSES)
+        params = {}
+        for n, shape in names:
+            if n.endswith(".w"):
+                params[n] = (r.standard_normal(shape, dtype=np.float32) / np.float32(np.sqrt(shape[0] * shape[1] * shape[2]))).astype(np.float32)
+            elif n.endswith(".g"):
+                params[n] = np.ones(shape, dtype=np.float32)
+            else:
+                params[n] = np.zeros(shape, dtype=np.float32)
+        n_img = 2
+        img = np.zeros((n_img, WorkloadC5.HW, WorkloadC5.HW, 8), dtype=np.float32)
+        img[..., :3] = r.standard_normal((n_img, WorkloadC5.HW, WorkloadC5.HW, 3), dtype=np.float32)
+        bits = (img.view(np.uint32) >> 16).astype(np.uint16)
+        labels = r.integers(0, WorkloadC5.CLASSES, size=n_img).astype(np.int32)
+        for _ in range(warmup):
+            CT.training_step(params, bits, labels, WorkloadC5.CLASSES, 0.01, 0.9, None)
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            CT.training_step(params, bits, labels, WorkloadC5.CLASSES, 0.01, 0.9, None)
+        dt = (time.perf_counter() - t0) / steps * (WorkloadC5.BATCH / n_img)
+        return 1.0 / dt, torch.get_num_threads(), \
+            (f"{steps} timed steps of the float64 torch restatement (oracle/convnet_torch.py) on {n_img} images each, scaled linearly to "
+             "a batch of 128; the reference's CPU backend is a stub"), dt
+
+
 class WorkloadC3Fused(WorkloadC3):
     """configs[2] with the relu(A) * M rewrite forced into the GEMM's mainloop (one kernel plus the fold of its
     reductions), where the planner on its own materialises the operand first at this size."""
@@ -787,12 +883,13 @@ class WorkloadC3Fused(WorkloadC3):
                 os.environ["HE_GEMM_MAINLOOP"] = prev
 
 
-WORKLOADS = {w.key: w for w in (WorkloadC1, WorkloadC2, WorkloadC3, WorkloadC3Fused, WorkloadC4, WorkloadC4Graph, WorkloadGemm,
+WORKLOADS = {w.key: w for w in (WorkloadC1, WorkloadC2, WorkloadC3, WorkloadC3Fused, WorkloadC4, WorkloadC4Graph, WorkloadC5, WorkloadGemm,
                                 WorkloadPointwise)}
-DEFAULT_STEPS = {"c1": 2000, "c2": 200, "c3": 200, "c3f": 200, "c4": 30, "c4g": 30, "gemm": 100, "pw": 50}
+DEFAULT_STEPS = {"c1": 2000, "c2": 200, "c3": 200, "c3f": 200, "c4": 30, "c4g": 30, "c5": 10, "gemm": 100, "pw": 50}
 # what the default N = 1 run times beside its own workload, and the steps each gets
 SUB_RECORDS = (("configs[2] fused matmul 4096^3 (as planned)", "c3", 100), ("configs[2] with the in-kernel mainloop rewrite", "c3f", 100),
-               ("configs[1] pointwise + permute", "c2", 100), ("configs[0] MLP training step f32", "c1", 1000))
+               ("configs[1] pointwise + permute", "c2", 100), ("configs[0] MLP training step f32", "c1", 1000),
+               ("configs[4] conv-net training step", "c5", 10))
 
 
 def config_for(key: str, world: int) -> dict:
@@ -800,7 +897,11 @@ def config_for(key: str, world: int) -> dict:
     product arm and `--impl reference` print the same one."""
     wl = WORKLOADS[key]
     config = {"workload": wl.description, "l2": wl.l2_note}
-    if key == "c4":
+    if key == "c5":
+        config.update({"images_per_gpu": wl.BATCH, "sharding": "batch",
+                       "grad_allreduce": "NCCL mean through he_allreduce_grads, 2 buckets (filters bf16, vectors f32) after the backward pass; "
+                                         "batch-norm statistics stay per GPU" if world > 1 else "none (1 rank)"})
+    elif key == "c4":
         n_grads = 2 * wl.D * wl.FF * 2 + (wl.FF + wl.D) * 4
         config.update({"tokens_per_gpu": wl.TOKENS, "sharding": "tokens",
                        "grad_allreduce": "NCCL mean through he_allreduce_grads, 3 buckets (dW1, dW2, biases), overlapped with the "
@@ -845,13 +946,24 @@ def measure(wl, key, steps, warmup, world, dev, barrier, brief, peaks, busy_s=0.
     leg from pinned host buffers.  Returns the fields of a JSON record (without clocks / cpu_baseline)."""
     import torch
     import torch.distributed as dist
+    barrier()
+    t_warm = time.perf_counter()
     for _ in range(warmup):
         wl.step()
     barrier()
-    t_busy = time.perf_counter()
-    while not brief and time.perf_counter() - t_busy < busy_s:
+    # Keep the device busy for ~busy_s more, so that the clock samples cover the timed region.  The number of
+    # steps must be the SAME on every rank (a step of a sharded workload contains collectives: a rank that ran one
+    # step more than its peer would wait for ever), so it is derived from the slowest rank's warm-up time and
+    # agreed on before the loop, not from each rank's own clock inside it.
+    per_step = (time.perf_counter() - t_warm) / max(1, warmup)
+    if world > 1:
+        t = torch.tensor([per_step], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        per_step = float(t.item())
+    n_busy = 0 if brief else int(min(200, max(1, busy_s / max(per_step, 1e-6))))
+    for _ in range(n_busy):
         wl.step()
-        torch.cuda.synchronize()
+    torch.cuda.synchronize()
     records = []
     t_start = torch.cuda.Event(enable_timing=True); t_end = torch.cuda.Event(enable_timing=True)
     barrier()
@@ -957,7 +1069,9 @@ def main():
         raise SystemExit("bench.py needs a CUDA device: helium_b200 has no CPU path")
     torch.cuda.set_device(local_rank)
     if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        import datetime
+        # a short collective timeout: a rank that falls out of step must end the run in minutes, not hold the GPUs
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank), timeout=datetime.timedelta(seconds=90))
     ctx = hb.Context(local_rank)
     peaks = load_peaks()
     dev = torch.device("cuda", local_rank)
@@ -968,7 +1082,7 @@ def main():
         torch.cuda.synchronize()
 
     reducer, comm = None, None
-    if world > 1 and args.workload == "c4":
+    if world > 1 and args.workload in ("c4", "c5"):
         if args.reducer == "comm":
             def exchange(b: bytes) -> bytes:
                 t = torch.tensor(list(b), dtype=torch.uint8, device=dev)

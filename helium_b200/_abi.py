@@ -35,6 +35,19 @@ class HeGraphDesc(C.Structure):
     ]
 
 
+class HeConv2dParams(C.Structure):
+    """struct he_conv2d_params of include/helium_b200.h."""
+
+    _fields_ = [(n, C.c_int32) for n in ("in_channels", "out_channels", "kernel_h", "kernel_w", "stride_h", "stride_w",
+                                         "dilation_h", "dilation_w", "padding_mode")]
+
+
+class HeConv2dFusion(C.Structure):
+    """struct he_conv2d_fusion of include/helium_b200.h."""
+
+    _fields_ = [(n, C.c_int32) for n in ("out_dtype", "has_bias", "bias_dtype", "has_resid", "has_gate", "want_stats")]
+
+
 #: every symbol include/helium_b200.h declares: name -> (restype, argtypes)
 SIGNATURES = {
     "he_ctx_create": (C.c_int32, [C.c_int32, C.POINTER(C.c_void_p)]),
@@ -47,6 +60,19 @@ SIGNATURES = {
     "he_permute_output_strides": (C.c_int32, [C.c_int32, C.POINTER(C.c_int64), C.c_int32, C.POINTER(C.c_int32),
                                               C.c_int32, C.POINTER(C.c_int64)]),
     "he_plan_fused_matmul": (C.c_int32, [C.c_void_p, C.POINTER(HeGraphDesc), C.POINTER(C.c_void_p)]),
+    "he_plan_conv2d": (C.c_int32, [C.c_void_p, C.c_int32, C.POINTER(HeConv2dParams), C.c_int32, C.c_int32, C.c_int32, C.c_int32,
+                                   C.POINTER(HeConv2dFusion), C.POINTER(C.c_void_p)]),
+    "he_bn_finalize": (C.c_int32, [C.c_void_p, C.c_int64] + [C.c_void_p] * 8 + [C.c_int32, C.c_void_p]),
+    "he_bn_workspace_bytes": (C.c_size_t, [C.c_int64, C.c_int32]),
+    "he_bn_apply": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p,
+                                C.c_void_p]),
+    "he_bn_backward_coeffs": (C.c_int32, [C.c_void_p, C.c_int64] + [C.c_void_p] * 6 + [C.c_int32, C.c_void_p]),
+    "he_bn_backward_apply": (C.c_int32, [C.c_void_p] * 10 + [C.c_int64, C.c_int32, C.c_void_p]),
+    "he_add_bf16": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p]),
+    "he_colsum_bf16": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_void_p]),
+    "he_sgd_momentum": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p, C.c_int64, C.c_float, C.c_float, C.c_int32,
+                                    C.c_void_p]),
+    "he_pool_softmax_ce": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_void_p]),
     "he_plan_supported": (C.c_int32, [C.c_void_p, C.POINTER(HeGraphDesc), C.c_int32]),
     "he_plan_workspace_bytes": (C.c_int32, [C.c_void_p, C.POINTER(C.c_size_t)]),
     "he_launch": (C.c_int32, [C.c_void_p, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.c_void_p, C.c_void_p]),

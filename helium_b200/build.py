@@ -36,6 +36,8 @@ SOURCES = [
     "host_graph.cu",
     "reduce_noalloc.cu",
     "comm.cu",
+    "conv.cu",
+    "train_ops.cu",
 ]
 
 NVCC_FLAGS = [

@@ -1,0 +1,494 @@
+// Implicit-GEMM 2-D convolution kernels for sm_100a on the tcgen05 / TMEM / TMA core.
+//
+// What they replace: the three cuDNN graphs the reference builds for Op::Conv, Op::ConvBackwardData and
+// Op::ConvBackwardFilter (helium/src/cuda/instr/cudnn_graph.rs:182-228; geometry from
+// helium-ir/src/opgraph/op/conv.rs:51-95; layouts NHWC for images and KRSC for filters,
+// helium/src/raw_tensor.rs:232-240).  No im2col buffer exists anywhere: the "A" operand of the GEMM is
+// fetched straight from the NHWC tensor, one filter tap and 64 channels at a time, by a 4-D TMA box whose
+// pixel extent is a small patch of the output grid (tw x th pixels of tn images).  The tap's shift is an
+// offset of the box's start coordinate, padding is the zero fill TMA gives out-of-range coordinates, and a
+// stride of two is served by four tensor maps over the parity classes of the input (even / odd rows x
+// even / odd columns), so that every load is a plain dense box.
+//
+//   conv_fprop_kernel   y[pix, ko]  = sum_{tap, c}  x[pix + tap, c] * w[ko, tap, c]           (forward)
+//                       dx[pix, c]  = sum_{tap, ko} dy[pix - tap, ko] * w[ko, tap, c]          (data gradient:
+//                       the same kernel with the filter read N-major and mirrored taps; a stride of two
+//                       runs it once per parity class of the input grid)
+//   conv_wgrad_kernel   dw[ko, tap, c] = sum_pix dy[pix, ko] * x[pix + tap, c]                 (filter gradient:
+//                       both operands MN-major, the pixel axis is the contraction and is split over CTAs;
+//                       f32 partial tiles go to the workspace and are folded in a fixed order)
+//
+// Roles, barriers, bounded waits and the abort path are those of gemm_tcgen05_kernel (gemm_sm100.cuh).
+#pragma once
+#include "gemm_sm100.cuh"
+
+namespace he {
+
+constexpr int kConvMaxTaps = 49;   // up to 7 x 7
+
+struct ConvTap {
+  short dh, dw;    // start-coordinate offset of the activation box for this tap, in the tensor map's pixel units
+  short map;       // which of the (up to four) activation tensor maps
+  short tap;       // filter tap index r * S + s (coordinate 1 of the filter map)
+};
+
+// Pixel patch of one M tile (forward / data gradient) or one K block (filter gradient): tn images x th rows
+// x tw columns of the patch grid, all powers of two.  Patches may hang over the grid's edge; those pixels
+// read zeros (TMA fill) and are never written.
+struct ConvGeom {
+  int tw, th, tn;
+  int GP, GQ, GN;               // patch grid: rows, columns, images
+  int tiles_q, tiles_p, tiles_nb;
+  // where patch-grid pixel (n, p, q) lives in the OUTPUT tensor: ((n * OH + p * os + oh0) * OW + q * os + ow0)
+  int OH, OW, os, oh0, ow0;
+  int n_taps, c_blocks;         // k-blocks per tile = n_taps * c_blocks (64 channels each)
+  int tile_m_base;              // first M-tile number of this pass (rows of the statistics partials)
+  ConvTap taps[kConvMaxTaps];
+};
+
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* m, uint32_t bar, int c0, int c1, int c2, int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+
+// ---- epilogue of the forward / data-gradient kernel ------------------------------------------------
+//   t = acc (+ bias[col]) (+ resid[pix, col]);
+//   gate (backward through relu(x * s[col] + b[col])):  t = (gx[pix, col] * s[col] + b[col] > 0) ? t : 0;
+//   out[pix, col] = t;   stats: S0[col] = sum_pix t,  S1[col] = sum_pix t * (gate ? gx : t)
+// Forward use: bias, residual add, and the batch statistics (sum, sum of squares) of the tensor the next
+// batch norm normalises (helium/src/modules/batch_norm.rs:38-65).  Backward use: the gradient arriving at a
+// batch-normalised, rectified activation, masked by the rectifier, with the two sums batch norm's backward
+// needs (sum g and sum g x).
+struct EpiConvParams {
+  void* out;
+  const void* bias; const void* resid; const void* gate_x;
+  const float* gate_scale; const float* gate_shift;
+  float* stat0_partials; float* stat1_partials;
+  int out_dt, bias_dt, resid_dt, gate_dt;
+  int vec_ok;
+};
+
+struct EpiConv {
+  using Params = EpiConvParams;
+  // blocks 0, 1: the two column-sum scratch areas; block 2: bias / gate scale / gate shift slices of the tile
+  static constexpr int kColReductions = 3;
+  static constexpr int kChunk = 32;
+  struct State {};
+  __device__ static void tile_begin(const Params&, State&) {}
+  __device__ static void tile_prepare(const Params& p, const EpiEnv& env, const TileInfo& t) {
+    if (!p.bias && !p.gate_x) return;
+    ptx::named_barrier_sync(1, env.n_epi_threads);   // the previous tile's chunks are done with the slices
+    float* bs = env.scratch + 2 * 4 * env.bn;
+    const int n = env.core->N;
+    for (int i = env.epi_tid; i < env.bn; i += env.n_epi_threads) {
+      const int gc = t.n0 + i;
+      const bool ok = gc < n;
+      bs[i] = (ok && p.bias) ? load_param_as_f32(p.bias, p.bias_dt, gc) : 0.0f;
+      bs[env.bn + i] = (ok && p.gate_x) ? __ldg(p.gate_scale + gc) : 0.0f;
+      bs[2 * env.bn + i] = (ok && p.gate_x) ? __ldg(p.gate_shift + gc) : 0.0f;
+    }
+    ptx::named_barrier_sync(1, env.n_epi_threads);
+  }
+  // `row` is the output pixel's linear index (or core->M for a patch pixel outside the grid)
+  __device__ static void chunk(const Params& p, const EpiEnv& env, const TileInfo& t, State&, int row, int col, float (&v)[kChunk]) {
+    const GemmCore& c = *env.core;
+    const int gcol = t.n0 + col;
+    const int nvalid = row < c.M ? max(0, min(kChunk, c.N - gcol)) : 0;
+    const size_t off = (size_t)row * c.N + gcol;
+    const int vec = p.vec_ok;
+    const float* bs = env.scratch + 2 * 4 * env.bn;
+    float aux[kChunk];
+    if (p.bias) {
+#pragma unroll
+      for (int i = 0; i < kChunk; ++i) v[i] += bs[col + i];
+    }
+    if (p.resid) {
+      load_row<kChunk>(p.resid, p.resid_dt, off, nvalid, vec, aux);
+#pragma unroll
+      for (int i = 0; i < kChunk; ++i) v[i] += aux[i];
+    }
+    if (p.gate_x) {
+      load_row<kChunk>(p.gate_x, p.gate_dt, off, nvalid, vec, aux);
+#pragma unroll
+      for (int i = 0; i < kChunk; ++i) v[i] = fmaf(aux[i], bs[env.bn + col + i], bs[2 * env.bn + col + i]) > 0.0f ? v[i] : 0.0f;
+    }
+#pragma unroll
+    for (int i = 0; i < kChunk; ++i) v[i] = i < nvalid ? v[i] : 0.0f;
+    if (nvalid > 0) store_row<kChunk>(p.out, p.out_dt, off, nvalid, vec, v);
+    if (p.stat0_partials) {
+      float s1[kChunk];
+#pragma unroll
+      for (int i = 0; i < kChunk; ++i) s1[i] = v[i] * (p.gate_x ? aux[i] : v[i]);   // aux is 0 where nvalid cuts
+      warp_colsum_store<kChunk>(v, env.scratch + env.quadrant * env.bn + col);
+      warp_colsum_store<kChunk>(s1, env.scratch + (4 + env.quadrant) * env.bn + col);
+    }
+  }
+  __device__ static void tile_end(const Params& p, const EpiEnv& env, const TileInfo& t, State&) {
+    if (p.stat0_partials) {
+      float* parts[2] = {p.stat0_partials, p.stat1_partials};
+      col_partials_flush(env, t, 2, parts);
+    }
+  }
+};
+
+struct alignas(64) ConvParams {
+  CUtensorMap tma_x[4];   // activation (forward: image, data gradient: flow), one per input parity class
+  CUtensorMap tma_w;      // filter as (C, R*S, K)
+  GemmCore core;          // M = output pixels (all images), N = output columns, K unused, tiles_m = M tiles
+  ConvGeom geom;
+  EpiConvParams epi;
+};
+
+template <int BN, int STAGES>
+struct ConvSmem {
+  static constexpr int kBTileBytes = BN * kBK * 2;
+  static constexpr int off_a = 0;
+  static constexpr int off_b = off_a + STAGES * kATileBytes;
+  static constexpr int off_scratch = off_b + STAGES * kBTileBytes;
+  static constexpr int scratch_bytes = (EpiConv::kColReductions * 4 * BN + 64) * 4;
+  static constexpr int off_bar = off_scratch + scratch_bytes;
+  static constexpr int n_bars = 2 * STAGES + 4;
+  static constexpr int off_misc = off_bar + n_bars * 8;
+  static constexpr int total = off_misc + 16;
+  static constexpr int dynamic_bytes = total + 1024;
+};
+
+// B_MN = false: filter tiles are K-major ([ko rows][64 c], forward); true: N-major ([64 ko rows][c], data gradient).
+template <int BN, int STAGES, bool B_MN>
+__global__ void __launch_bounds__(32 * 10, 1) conv_fprop_kernel(const __grid_constant__ ConvParams p) {
+  using SM = ConvSmem<BN, STAGES>;
+  constexpr int NE_WARPS = 8;
+  constexpr int kTmemCols = 2 * BN <= 128 ? 128 : 256;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  const uint32_t smem_base = ptx::smem_u32(smem);
+  const uint32_t bar0 = smem_base + SM::off_bar;
+  auto bar_full = [&](int s) { return bar0 + 8u * s; };
+  auto bar_empty = [&](int s) { return bar0 + 8u * (STAGES + s); };
+  auto bar_tmem_full = [&](int a) { return bar0 + 8u * (2 * STAGES + a); };
+  auto bar_tmem_empty = [&](int a) { return bar0 + 8u * (2 * STAGES + 2 + a); };
+  volatile uint32_t* tmem_holder = reinterpret_cast<volatile uint32_t*>(smem + SM::off_misc);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + SM::off_misc + 4);
+  float* scratch = reinterpret_cast<float*>(smem + SM::off_scratch);
+
+  const GemmCore& c = p.core;
+  const ConvGeom& g = p.geom;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int k_blocks = g.n_taps * g.c_blocks;
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    for (int s = 0; s < STAGES; ++s) {
+      ptx::mbar_init(bar_full(s), 1);
+      ptx::mbar_init(bar_empty(s), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      ptx::mbar_init(bar_tmem_full(a), 1);
+      ptx::mbar_init(bar_tmem_empty(a), NE_WARPS);
+    }
+    ptx::fence_mbar_init();
+  }
+  if (warp == 0 && lane == 0) {
+    for (int i = 0; i < 4; ++i) ptx::prefetch_tmap(&p.tma_x[i]);
+    ptx::prefetch_tmap(&p.tma_w);
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc(ptx::smem_u32(const_cast<uint32_t*>(tmem_holder)), kTmemCols);
+    ptx::tmem_relinquish();
+  }
+  ptx::tcgen05_fence_before();
+  __syncthreads();
+  ptx::tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+
+  // tile -> (column tile, patch origin); column tiles fastest so that neighbouring CTAs share the patch
+  struct Origin { int n0, p0, q0, nb0, tile_m; };
+  auto decode = [&](int tile) {
+    Origin o;
+    const int tn_ = tile % c.tiles_n;
+    int m = tile / c.tiles_n;
+    o.tile_m = m + g.tile_m_base;
+    o.n0 = tn_ * BN;
+    const int qi = m % g.tiles_q; m /= g.tiles_q;
+    const int pi = m % g.tiles_p; m /= g.tiles_p;
+    o.q0 = qi * g.tw; o.p0 = pi * g.th; o.nb0 = m * g.tn;
+    return o;
+  };
+
+  if (warp == 0) {
+    if (lane == 0) {
+      constexpr uint32_t kStageBytes = kATileBytes + SM::kBTileBytes;
+      int stage = 0;
+      uint32_t phase = 0;
+      bool alive = true;
+      for (int tile = blockIdx.x; alive && !c.withhold_loads && tile < c.num_tiles; tile += gridDim.x) {
+        const Origin o = decode(tile);
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!ptx::mbar_wait(bar_empty(stage), phase ^ 1u, abort_flag, c.status, 1, stage, c.wait_limit_us)) { alive = false; break; }
+          ptx::mbar_arrive_expect_tx(bar_full(stage), kStageBytes);
+          const int ti = kb / g.c_blocks, cb = kb - ti * g.c_blocks;
+          const ConvTap tp = g.taps[ti];
+          const uint32_t a_dst = smem_base + SM::off_a + stage * kATileBytes;
+          const uint32_t b_dst = smem_base + SM::off_b + stage * SM::kBTileBytes;
+          // activation: 64 channels x (tw x th x tn) pixels, shifted by the tap
+          tma_load_4d(a_dst, &p.tma_x[tp.map], bar_full(stage), cb * kBK, o.q0 + tp.dw, o.p0 + tp.dh, o.nb0);
+          if (B_MN) {
+            // rows = 64 contraction channels (ko), columns = output channels c: boxes of 64 columns
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j)
+              ptx::tma_load_3d(b_dst + j * (kBK * 128), &p.tma_w, bar_full(stage), o.n0 + 64 * j, tp.tap, cb * kBK);
+          } else {
+            // rows = BN output channels (ko), columns = 64 contraction channels c
+            ptx::tma_load_3d(b_dst, &p.tma_w, bar_full(stage), cb * kBK, tp.tap, o.n0);
+          }
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc = ptx::make_idesc_f16(c.ab_format, 0, B_MN ? 1 : 0, kBM, BN);
+      constexpr uint32_t b_lbo = B_MN ? kBK * 128 : 16;
+      constexpr uint32_t b_kadv = B_MN ? 2048 : 32;
+      int stage = 0;
+      uint32_t phase = 0;
+      int it = 0;
+      bool alive = true;
+      for (int tile = blockIdx.x; alive && tile < c.num_tiles; tile += gridDim.x, ++it) {
+        const int acc = it & 1;
+        const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
+        if (!ptx::mbar_wait(bar_tmem_empty(acc), acc_phase ^ 1u, abort_flag, c.status, 2, acc, c.wait_limit_us)) { alive = false; break; }
+        ptx::tcgen05_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!ptx::mbar_wait(bar_full(stage), phase, abort_flag, c.status, 3, stage, c.wait_limit_us)) { alive = false; break; }
+          ptx::tcgen05_fence_after();
+          const uint32_t a_addr = smem_base + SM::off_a + stage * kATileBytes;
+          const uint32_t b_addr = smem_base + SM::off_b + stage * SM::kBTileBytes;
+#pragma unroll
+          for (int k = 0; k < kBK / kUmmaK; ++k) {
+            const uint64_t adesc = ptx::make_smem_desc_sw128(a_addr + k * 32, 16, 1024);
+            const uint64_t bdesc = ptx::make_smem_desc_sw128(b_addr + k * b_kadv, b_lbo, 1024);
+            ptx::umma_f16(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          ptx::umma_commit(bar_empty(stage));
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+        if (alive) ptx::umma_commit(bar_tmem_full(acc));
+      }
+    }
+  } else {
+    EpiEnv env;
+    env.core = &c;
+    env.scratch = scratch;
+    env.bn = BN;
+    env.n_epi_threads = NE_WARPS * 32;
+    env.epi_warp = warp - 2;
+    env.epi_tid = env.epi_warp * 32 + lane;
+    env.quadrant = warp & 3;
+    constexpr int kColsPerWarp = BN / (NE_WARPS / 4);
+    const int col_begin = (env.epi_warp / 4) * kColsPerWarp;
+    // this thread's pixel within the patch: row = (in * th + ih) * tw + iw
+    const int prow = env.quadrant * 32 + lane;
+    const int iw = prow & (g.tw - 1);
+    const int ih = (prow / g.tw) & (g.th - 1);
+    const int in = prow / (g.tw * g.th);
+    int it = 0;
+    bool dead = false;
+    for (int tile = blockIdx.x; tile < c.num_tiles; tile += gridDim.x, ++it) {
+      const int acc = it & 1;
+      const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
+      const Origin o = decode(tile);
+      TileInfo t;
+      t.m0 = 0; t.n0 = o.n0; t.b = 0; t.tile_m = o.tile_m; t.tile_n = o.n0 / BN; t.tile_idx = tile; t.bn = BN;
+      const int n = o.nb0 + in, pp = o.p0 + ih, qq = o.q0 + iw;
+      const bool inside = n < g.GN && pp < g.GP && qq < g.GQ && in < g.tn;
+      const int pix = inside ? ((n * g.OH + pp * g.os + g.oh0) * g.OW + qq * g.os + g.ow0) : c.M;
+      EpiConv::tile_prepare(p.epi, env, t);
+      if (!dead && !ptx::mbar_wait(bar_tmem_full(acc), acc_phase, abort_flag, c.status, 4, acc, c.wait_limit_us)) dead = true;
+      dead = __any_sync(0xffffffffu, dead);
+      EpiConv::State st;
+      EpiConv::tile_begin(p.epi, st);
+      if (!dead) {
+        ptx::tcgen05_fence_after();
+        const uint32_t taddr0 = tmem_base + ((uint32_t)(env.quadrant * 32) << 16) + (uint32_t)(acc * BN);
+        const int col_end = min(col_begin + kColsPerWarp, ((c.N - t.n0 + 31) / 32) * 32);
+        epilogue_walk_chunks<EpiConv>(p.epi, env, t, st, taddr0, pix, col_begin, col_end);
+        ptx::tcgen05_fence_before();
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(bar_tmem_empty(acc));
+      }
+      EpiConv::tile_end(p.epi, env, t, st);
+    }
+  }
+
+  ptx::tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    ptx::tcgen05_fence_after();
+    ptx::tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// ---- filter gradient -----------------------------------------------------------------------------------
+struct alignas(64) ConvWgradParams {
+  CUtensorMap tma_dy;     // flow as (K, Q, P, N), box 64 x patch
+  CUtensorMap tma_x[4];   // image parity classes as (C, W', H', N), box 64 x patch
+  GemmCore core;          // M = K (output channels), N = C (input channels); tiles_m / tiles_n over them
+  ConvGeom geom;          // patch = one K block of 64 pixels; taps = all filter taps
+  float* partials;        // [splits][K][R*S][C] f32
+  int splits, k_tiles;    // pixel tiles in all, and how many CTAs share them
+  int rs;                 // R * S
+};
+
+template <int BN, int STAGES>
+struct ConvWgradSmem {
+  static constexpr int kBTileBytes = BN * kBK * 2;
+  static constexpr int off_a = 0;
+  static constexpr int off_b = off_a + STAGES * kATileBytes;
+  static constexpr int off_bar = off_b + STAGES * kBTileBytes;
+  static constexpr int n_bars = 2 * STAGES + 1;
+  static constexpr int off_misc = off_bar + n_bars * 8;
+  static constexpr int total = off_misc + 16;
+  static constexpr int dynamic_bytes = total + 1024;
+};
+
+// One CTA = one (output tile, tap, split): it contracts its share of the pixel tiles and writes one f32 tile.
+template <int BN, int STAGES>
+__global__ void __launch_bounds__(32 * 6, 1) conv_wgrad_kernel(const __grid_constant__ ConvWgradParams p) {
+  using SM = ConvWgradSmem<BN, STAGES>;
+  constexpr int kTmemCols = BN <= 64 ? 64 : 128;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  const uint32_t smem_base = ptx::smem_u32(smem);
+  const uint32_t bar0 = smem_base + SM::off_bar;
+  auto bar_full = [&](int s) { return bar0 + 8u * s; };
+  auto bar_empty = [&](int s) { return bar0 + 8u * (STAGES + s); };
+  const uint32_t bar_done = bar0 + 8u * (2 * STAGES);
+  volatile uint32_t* tmem_holder = reinterpret_cast<volatile uint32_t*>(smem + SM::off_misc);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + SM::off_misc + 4);
+
+  const GemmCore& c = p.core;
+  const ConvGeom& g = p.geom;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  // work item
+  int item = blockIdx.x;
+  const int split = item % p.splits; item /= p.splits;
+  const int ti = item % g.n_taps; item /= g.n_taps;
+  const int tile_n = item % c.tiles_n;
+  const int tile_m = item / c.tiles_n;
+  const int m0 = tile_m * kBM, n0 = tile_n * BN;
+  const int kt_begin = (int)(((long long)p.k_tiles * split) / p.splits);
+  const int kt_end = (int)(((long long)p.k_tiles * (split + 1)) / p.splits);
+  const ConvTap tp = g.taps[ti];
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    for (int s = 0; s < STAGES; ++s) {
+      ptx::mbar_init(bar_full(s), 1);
+      ptx::mbar_init(bar_empty(s), 1);
+    }
+    ptx::mbar_init(bar_done, 1);
+    ptx::fence_mbar_init();
+  }
+  if (warp == 0 && lane == 0) {
+    ptx::prefetch_tmap(&p.tma_dy);
+    ptx::prefetch_tmap(&p.tma_x[tp.map]);
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc(ptx::smem_u32(const_cast<uint32_t*>(tmem_holder)), kTmemCols);
+    ptx::tmem_relinquish();
+  }
+  ptx::tcgen05_fence_before();
+  __syncthreads();
+  ptx::tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+
+  if (warp == 0) {
+    if (lane == 0 && !c.withhold_loads) {
+      constexpr uint32_t kStageBytes = kATileBytes + SM::kBTileBytes;
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int kt = kt_begin; kt < kt_end; ++kt) {
+        if (!ptx::mbar_wait(bar_empty(stage), phase ^ 1u, abort_flag, c.status, 1, stage, c.wait_limit_us)) break;
+        ptx::mbar_arrive_expect_tx(bar_full(stage), kStageBytes);
+        int m = kt;
+        const int qi = m % g.tiles_q; m /= g.tiles_q;
+        const int pi = m % g.tiles_p; m /= g.tiles_p;
+        const int q0 = qi * g.tw, p0 = pi * g.th, nb0 = m * g.tn;
+        const uint32_t a_dst = smem_base + SM::off_a + stage * kATileBytes;
+        const uint32_t b_dst = smem_base + SM::off_b + stage * SM::kBTileBytes;
+        // A = flow^T: 64 pixels (contraction) x 128 output channels, as two boxes of 64 channels
+#pragma unroll
+        for (int j = 0; j < kBM / 64; ++j) tma_load_4d(a_dst + j * (kBK * 128), &p.tma_dy, bar_full(stage), m0 + 64 * j, q0, p0, nb0);
+        // B = image shifted by the tap: 64 pixels x BN input channels
+#pragma unroll
+        for (int j = 0; j < BN / 64; ++j)
+          tma_load_4d(b_dst + j * (kBK * 128), &p.tma_x[tp.map], bar_full(stage), n0 + 64 * j, q0 + tp.dw, p0 + tp.dh, nb0);
+        if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc = ptx::make_idesc_f16(c.ab_format, 1, 1, kBM, BN);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool alive = true;
+      for (int kt = kt_begin; kt < kt_end; ++kt) {
+        if (!ptx::mbar_wait(bar_full(stage), phase, abort_flag, c.status, 3, stage, c.wait_limit_us)) { alive = false; break; }
+        ptx::tcgen05_fence_after();
+        const uint32_t a_addr = smem_base + SM::off_a + stage * kATileBytes;
+        const uint32_t b_addr = smem_base + SM::off_b + stage * SM::kBTileBytes;
+#pragma unroll
+        for (int k = 0; k < kBK / kUmmaK; ++k) {
+          const uint64_t adesc = ptx::make_smem_desc_sw128(a_addr + k * 2048, kBK * 128, 1024);
+          const uint64_t bdesc = ptx::make_smem_desc_sw128(b_addr + k * 2048, kBK * 128, 1024);
+          ptx::umma_f16(tmem_base, adesc, bdesc, idesc, (kt > kt_begin || k != 0) ? 1u : 0u);
+        }
+        ptx::umma_commit(bar_empty(stage));
+        if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+      }
+      if (alive) ptx::umma_commit(bar_done);
+    }
+  } else {
+    // four epilogue warps: rows = output channels of the filter, columns = input channels
+    const int quadrant = warp & 3;
+    const int row = quadrant * 32 + lane;
+    const int ko = m0 + row;
+    bool ok = kt_end > kt_begin;
+    if (ok) ok = ptx::mbar_wait(bar_done, 0, abort_flag, c.status, 4, 0, c.wait_limit_us);
+    ok = __all_sync(0xffffffffu, ok);
+    ptx::tcgen05_fence_after();
+    float* dst = p.partials + (((size_t)split * c.M + ko) * p.rs + tp.tap) * c.N + n0;
+#pragma unroll 1
+    for (int col = 0; col < BN; col += 32) {
+      if (n0 + col >= c.N) break;
+      float v[32];
+      if (ok) {
+        tmem_ld_chunk<32>(tmem_base + ((uint32_t)(quadrant * 32) << 16) + (uint32_t)col, v);
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = 0.0f;   // an empty share of the pixel tiles contributes zeros
+      }
+      if (ko < c.M) {
+        const int nvalid = min(32, c.N - (n0 + col));
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+          if (i < nvalid) dst[col + i] = v[i];
+      }
+    }
+    ptx::tcgen05_fence_before();
+  }
+
+  ptx::tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    ptx::tcgen05_fence_after();
+    ptx::tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+}  // namespace he

@@ -12,6 +12,7 @@ from typing import List, Optional, Sequence
 import numpy as np
 
 from . import ir
+from ._abi import HeConv2dFusion, HeConv2dParams
 from ._lib import HeliumError, check, lib
 
 _TORCH_DTYPES = None
@@ -112,6 +113,37 @@ class Plan:
             order = sorted(range(rank), key=lambda i: -out_strides[i])
             out_shape = [in_shape[i] for i in order]
         return Plan(h, [tuple(out_shape)], [dtype], 1, ctx)
+
+    @staticmethod
+    def conv2d(ctx: Optional[Context], kind: str, batch: int, in_hw, in_channels: int, out_channels: int, kernel, stride: int = 1,
+               dilation: int = 1, padding_mode: int = 0, dtype: int = ir.BF16, out_dtype: Optional[int] = None, bias: bool = False,
+               bias_dtype: int = ir.F32, resid: bool = False, gate: bool = False, stats: bool = False) -> "Plan":
+        """he_plan_conv2d.  kind: "fwd" (inputs image, filter[, bias][, resid]), "bwd_data" (flow, filter[, resid]
+        [, gate_x, gate_scale, gate_shift]) or "bwd_filter" (flow, image).  `in_hw` is the image's size."""
+        k = {"fwd": 0, "bwd_data": 1, "bwd_filter": 2}[kind]
+        prm = HeConv2dParams(in_channels, out_channels, kernel[0], kernel[1], stride, stride, dilation, dilation, padding_mode)
+        od = dtype if out_dtype is None else out_dtype
+        fus = HeConv2dFusion(od, int(bias), bias_dtype, int(resid), int(gate), int(stats))
+        h = C.c_void_p()
+        check(lib.he_plan_conv2d(ctx._h if ctx else None, k, C.byref(prm), batch, in_hw[0], in_hw[1], dtype, C.byref(fus), C.byref(h)))
+        size = list(in_hw)
+        for i in range(2):
+            if padding_mode == 2:
+                size[i] += kernel[i] // 2
+            elif padding_mode == 1:
+                size[i] = max(0, size[i] - kernel[i] // 2)
+            size[i] //= stride
+        if k == 0:
+            shapes, n_in = [(batch, size[0], size[1], out_channels)], 2 + int(bias) + int(resid)
+        elif k == 1:
+            shapes, n_in = [(batch, in_hw[0], in_hw[1], in_channels)], 2 + int(resid) + 3 * int(gate)
+        else:
+            shapes, n_in = [(out_channels, kernel[0], kernel[1], in_channels)], 2
+        dtypes = [od]
+        if stats:
+            shapes.append((2, shapes[0][3]))
+            dtypes.append(ir.F32)
+        return Plan(h, shapes, dtypes, n_in, ctx)
 
     # -- queries -----------------------------------------------------------------------------------
     @property

@@ -264,6 +264,97 @@ int32_t he_debug_dump_program(const he_graph_desc* desc, int32_t epilogue, void*
 int32_t he_debug_canonical_text(const he_graph_desc* desc, char* buf, size_t cap);
 
 /* ------------------------------------------------------------------------------------------------
+ * 2-D convolution as implicit GEMM on the tcgen05 core.  Replaces the cuDNN graphs the reference builds
+ * for Op::Conv, Op::ConvBackwardData and Op::ConvBackwardFilter (helium/src/cuda/instr/cudnn_graph.rs:
+ * 182-228).  Images are NHWC, filters KRSC (helium/src/raw_tensor.rs:232-240); geometry follows
+ * Conv2dParams (helium-ir/src/opgraph/op/conv.rs:5-95): output size = input size adjusted by the padding
+ * mode and divided by the stride, zero padding k/2 (Same), 0 (Valid), k-1 (Full) on both sides.
+ * Implemented: bf16 / f16 tensors with f32 accumulation, dilation 1, strides 1x1 and 2x2, up to 49 taps,
+ * channel counts that are multiples of 8 (a 16-byte pixel pitch; pad narrower images, e.g. RGB to 8).
+ *
+ * he_launch operands, in order:
+ *   HE_CONV_FWD         inputs  image [N,H,W,C], filter [K,R,S,C] (, bias [K]) (, resid [N,P,Q,K])
+ *                       outputs y [N,P,Q,K] (, stats f32 [2,K])
+ *   HE_CONV_BWD_DATA    inputs  flow [N,P,Q,K], filter [K,R,S,C] (, resid [N,H,W,C])
+ *                               (, gate_x [N,H,W,C], gate_scale f32 [C], gate_shift f32 [C])
+ *                       outputs dx [N,H,W,C] (, stats f32 [2,C])
+ *   HE_CONV_BWD_FILTER  inputs  flow [N,P,Q,K], image [N,H,W,C];  output dw [K,R,S,C]
+ * Fused epilogue of the first two (he_conv2d_fusion): t = acc + bias[col] + resid[pix, col]; with a gate,
+ * t = (gate_x[pix, col] * gate_scale[col] + gate_shift[col] > 0) ? t : 0 -- the backward of a rectified
+ * batch-norm output; out = t; stats = per-column sums over all pixels of t and of t * t (or of
+ * t * gate_x with a gate): the batch statistics of helium's BatchNorm2d (helium/src/modules/batch_norm.rs:
+ * 38-65) in the forward direction, and the two sums its backward needs in the other.
+ * ------------------------------------------------------------------------------------------------ */
+typedef enum he_conv_kind { HE_CONV_FWD = 0, HE_CONV_BWD_DATA = 1, HE_CONV_BWD_FILTER = 2 } he_conv_kind;
+typedef enum he_padding_mode { HE_PAD_SAME = 0, HE_PAD_VALID = 1, HE_PAD_FULL = 2 } he_padding_mode;   /* conv.rs:77-83 */
+typedef struct he_conv2d_params {   /* Conv2dParams, conv.rs:5-12 */
+  int32_t in_channels, out_channels;
+  int32_t kernel_h, kernel_w;
+  int32_t stride_h, stride_w;
+  int32_t dilation_h, dilation_w;
+  int32_t padding_mode;
+} he_conv2d_params;
+typedef struct he_conv2d_fusion {
+  int32_t out_dtype;     /* dtype of the output tensor (F16 / BF16 / F32) */
+  int32_t has_bias;      /* bias vector over output channels */
+  int32_t bias_dtype;
+  int32_t has_resid;     /* tensor of the output's shape and the operands' dtype, added */
+  int32_t has_gate;      /* rectifier mask recomputed from gate_x, gate_scale, gate_shift */
+  int32_t want_stats;    /* second output: f32 [2, columns] */
+} he_conv2d_fusion;
+/* `in_h`, `in_w`: spatial size of the IMAGE (for the gradients too); `fusion` may be NULL (plain store in
+ * `dtype`).  A strided data gradient whose filter leaves some input pixels untouched (1x1 with stride 2)
+ * zero-fills the output first and accepts no fusion. */
+int32_t he_plan_conv2d(he_ctx* ctx, int32_t kind, const he_conv2d_params* params, int32_t batch, int32_t in_h,
+                       int32_t in_w, int32_t dtype, const he_conv2d_fusion* fusion, he_plan** out);
+
+/* ------------------------------------------------------------------------------------------------
+ * Hand-written kernels for the pointwise / reduction chains of a convolutional training step.  In the
+ * reference each is a chain of generic pointwise and reduce instructions over broadcast views of
+ * channels-last tensors; here each remaining pass over an activation is one HBM-bound kernel.  All tensors
+ * are bf16 [pixels, channels] (NHWC flattened) with channels a multiple of 8, 16-byte aligned; per-channel
+ * vectors are f32.  Everything is enqueued on `cu_stream`; sums are folded in a fixed order.
+ * ------------------------------------------------------------------------------------------------ */
+/* BatchNorm2d::forward in train mode (helium/src/modules/batch_norm.rs:38-65) from the sums a convolution's
+ * epilogue (or he_bn_apply) produced: stats = [sum x, sum x^2] per channel over `count` values.  Writes
+ * scale = gamma * rstd, shift = beta - mean * scale, mean and rstd = 1 / sqrt(E[x^2] - mean^2 + 1e-3), and
+ * updates the running statistics in place (x 0.9 + 0.1 x new; either may be NULL). */
+int32_t he_bn_finalize(const float* stats, int64_t count, const float* gamma, const float* beta, float* running_mean,
+                       float* running_var, float* scale, float* shift, float* mean, float* rstd, int32_t channels,
+                       void* cu_stream);
+/* y = x * scale[c] + shift[c], rectified when `relu` != 0 (batch_norm.rs:60-70 followed by tensor.rs:374-387).
+ * With `stats_out` (f32 [2, channels]) the sums of y and y^2 as stored are produced as well, for a second
+ * normalisation of the same tensor; that needs he_bn_workspace_bytes(pixels, channels) of workspace. */
+size_t he_bn_workspace_bytes(int64_t pixels, int32_t channels);
+int32_t he_bn_apply(const void* x, void* y, const float* scale, const float* shift, int64_t pixels, int32_t channels,
+                    int32_t relu, float* stats_out, void* workspace, void* cu_stream);
+/* Backward of the normalisation.  stats = [sum g, sum g x] per channel, with g the gradient at the normalised
+ * (and rectifier-masked) output and x the normalised tensor -- the second output of an HE_CONV_BWD_DATA plan with
+ * a gate.  Writes dgamma, dbeta and coef = [A, B, K] (f32 [3, channels]) such that dx = A g + B x + K. */
+int32_t he_bn_backward_coeffs(const float* stats, int64_t count, const float* gamma, const float* mean, const float* rstd,
+                              float* coef, float* dgamma, float* dbeta, int32_t channels, void* cu_stream);
+/* out = coef.A[c] g + coef.B[c] x + coef.K[c] (+ addend).  With `mask_x` the result is zeroed where
+ * mask_x * mask_scale[c] + mask_shift[c] <= 0 (a rectified normalisation in front of this one) and
+ * stats_out = [sum out, sum out * mask_x] is produced (workspace as for he_bn_apply). */
+int32_t he_bn_backward_apply(const void* g, const void* x, const void* addend, void* out, const float* coef,
+                             const void* mask_x, const float* mask_scale, const float* mask_shift, float* stats_out,
+                             void* workspace, int64_t pixels, int32_t channels, void* cu_stream);
+/* out = a + b on bf16 tensors of n elements (gradient branches meeting at a fork). */
+int32_t he_add_bf16(const void* a, const void* b, void* out, int64_t n, void* cu_stream);
+/* out[c] = sum over pixels of x[pixel, c]: the gradient of a convolution's bias (workspace as for he_bn_apply). */
+int32_t he_colsum_bf16(const void* x, float* out, void* workspace, int64_t pixels, int32_t channels, void* cu_stream);
+/* Sgd::step with momentum (helium/src/optimizer/sgd.rs:47-62): avg = first_step ? g : g (1 - m) + avg m;
+ * w -= lr * avg; `w_bf16` (may be NULL) receives the updated weights rounded to bf16, the copy the next
+ * step's convolutions read (helium/src/modules/conv.rs:63).  `avg` may be NULL for plain SGD (momentum 0). */
+int32_t he_sgd_momentum(float* w, float* avg, const void* grad, int32_t grad_dtype, void* w_bf16, int64_t n, float lr,
+                        float momentum, int32_t first_step, void* cu_stream);
+/* Global average pooling + cross entropy (resnet-train/src/model.rs:77-82, helium/src/loss.rs:5-8): logits =
+ * mean over `positions` of y[n, position, :], loss[n] = -log_softmax(logits)[labels[n]] / batch, and dy = the
+ * gradient of sum(loss) at y (bf16, same shape). */
+int32_t he_pool_softmax_ce(const void* y, const int32_t* labels, float* loss, void* dy, int32_t batch, int32_t positions,
+                           int32_t classes, void* cu_stream);
+
+/* ------------------------------------------------------------------------------------------------
  * Data-parallel gradient exchange.  No counterpart in the reference, which runs on one GPU: its
  * optimiser consumes whatever gradient tensors it is handed (helium/src/optimizer/sgd.rs:35-62).  A
  * data-parallel host calls he_allreduce_grads between `backward()` and `Optimizer::step`, once per

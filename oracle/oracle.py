@@ -17,6 +17,10 @@ What each function follows:
                           helium-playground/src/kernel_generator.rs:363-414 and
                           helium-playground/src/torch_synthesizer.rs:31-87 (playground op meanings),
                           helium-ir/src/opgraph/op.rs:272-282 (matmul contract)
+  * conv2d*()             helium-ir/src/opgraph/op/conv.rs:51-95 (geometry), helium/src/raw_tensor.rs:232-330
+                          (NHWC / KRSC operands), helium/src/cuda/instr/cudnn_graph.rs:182-228 (the three
+                          cuDNN operations: cross-correlation, its data and filter gradients); pinned on the
+                          reference's one vector, helium/tests/tensor_ops.rs:379-397
   * permute()             helium/src/cuda/instr/permute_dims/jit.rs:15-117 (out[sum s_i c_i] = in[c])
   * output_strides_*()    helium/src/cuda/instr/permute_dims.rs:158-172
   * bit-packed bools      helium/src/cuda/instr/pointwise/jit.rs:107-114, 234-237
@@ -323,6 +327,82 @@ def permute(x: np.ndarray, out_strides: Sequence[int]) -> np.ndarray:
             raise ValueError("out_strides do not form a dense permutation")
         expect *= x.shape[i]
     return np.ascontiguousarray(np.transpose(x, order)).reshape(-1)
+
+
+# ---- convolution -------------------------------------------------------------------------------------
+PAD_SAME, PAD_VALID, PAD_FULL = 0, 1, 2
+
+
+def conv_geometry(in_hw, kernel, stride, padding_mode=PAD_SAME):
+    """(output size, padding) of Conv2dParams (helium-ir/src/opgraph/op/conv.rs:51-74, 86-94): the input size is
+    adjusted by the padding mode (Full: + k/2, Valid: - k/2, Same: unchanged) and divided by the stride
+    (integer division); the zero padding on both sides is k/2 (Same), 0 (Valid) or k-1 (Full)."""
+    size = list(in_hw)
+    for i in range(2):
+        if padding_mode == PAD_FULL:
+            size[i] += kernel[i] // 2
+        elif padding_mode == PAD_VALID:
+            size[i] = max(0, size[i] - kernel[i] // 2)
+        size[i] //= stride[i]
+    pad = {PAD_SAME: [kernel[0] // 2, kernel[1] // 2], PAD_VALID: [0, 0], PAD_FULL: [kernel[0] - 1, kernel[1] - 1]}[padding_mode]
+    return size, pad
+
+
+def _padded(x, pad, P, Q, R, S, stride):
+    """x [N,H,W,C] zero-padded so that every tap of every output pixel is addressable."""
+    n, h, w, c = x.shape
+    hh = max(h + 2 * pad[0], (P - 1) * stride[0] + R)
+    ww = max(w + 2 * pad[1], (Q - 1) * stride[1] + S)
+    xp = np.zeros((n, hh, ww, c), dtype=np.float64)
+    xp[:, pad[0]:pad[0] + h, pad[1]:pad[1] + w, :] = x
+    return xp
+
+
+def conv2d(x, w, stride=(1, 1), padding_mode=PAD_SAME):
+    """Op::Conv (helium/src/raw_tensor.rs:232-287; cuDNN cross-correlation, cudnn_graph.rs:196-207):
+    y[n,p,q,k] = sum_{r,s,c} x[n, p*sh + r - pad_h, q*sw + s - pad_w, c] * w[k,r,s,c], zeros outside the image.
+    x NHWC, w KRSC, float64."""
+    x = np.asarray(x, dtype=np.float64); w = np.asarray(w, dtype=np.float64)
+    K, R, S, C = w.shape
+    (P, Q), pad = conv_geometry(x.shape[1:3], (R, S), stride, padding_mode)
+    xp = _padded(x, pad, P, Q, R, S, stride)
+    y = np.zeros((x.shape[0], P, Q, K))
+    for r in range(R):
+        for s in range(S):
+            patch = xp[:, r:r + (P - 1) * stride[0] + 1:stride[0], s:s + (Q - 1) * stride[1] + 1:stride[1], :]
+            y += patch @ w[:, r, s, :].T
+    return y
+
+
+def conv2d_backward_data(dy, w, in_hw, stride=(1, 1), padding_mode=PAD_SAME):
+    """Op::ConvBackwardData: the gradient of conv2d with respect to the image, shape [N, in_h, in_w, C]."""
+    dy = np.asarray(dy, dtype=np.float64); w = np.asarray(w, dtype=np.float64)
+    K, R, S, C = w.shape
+    (P, Q), pad = conv_geometry(in_hw, (R, S), stride, padding_mode)
+    n = dy.shape[0]
+    hh = max(in_hw[0] + 2 * pad[0], (P - 1) * stride[0] + R)
+    ww = max(in_hw[1] + 2 * pad[1], (Q - 1) * stride[1] + S)
+    dxp = np.zeros((n, hh, ww, C))
+    for r in range(R):
+        for s in range(S):
+            dxp[:, r:r + (P - 1) * stride[0] + 1:stride[0], s:s + (Q - 1) * stride[1] + 1:stride[1], :] += dy @ w[:, r, s, :]
+    return dxp[:, pad[0]:pad[0] + in_hw[0], pad[1]:pad[1] + in_hw[1], :]
+
+
+def conv2d_backward_filter(dy, x, kernel, stride=(1, 1), padding_mode=PAD_SAME):
+    """Op::ConvBackwardFilter: the gradient of conv2d with respect to the filter, shape [K, R, S, C]."""
+    dy = np.asarray(dy, dtype=np.float64); x = np.asarray(x, dtype=np.float64)
+    R, S = kernel
+    (P, Q), pad = conv_geometry(x.shape[1:3], (R, S), stride, padding_mode)
+    xp = _padded(x, pad, P, Q, R, S, stride)
+    K, C = dy.shape[3], x.shape[3]
+    dw = np.zeros((K, R, S, C))
+    flow = dy.reshape(-1, K)
+    for r in range(R):
+        for s in range(S):
+            patch = xp[:, r:r + (P - 1) * stride[0] + 1:stride[0], s:s + (Q - 1) * stride[1] + 1:stride[1], :]
+            dw[:, r, s, :] = flow.T @ patch.reshape(-1, C)
+    return dw
 
 
 # ---- config-level helpers ---------------------------------------------------------------------------
