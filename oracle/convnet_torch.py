@@ -40,18 +40,37 @@ def _bf16(t: torch.Tensor) -> torch.Tensor:
     return t.to(torch.float32).to(torch.bfloat16).to(torch.float64)
 
 
+class _RoundBf16(torch.autograd.Function):
+    """Identity that rounds to bf16 in both directions: a tensor that is stored as bf16 between two kernels."""
+
+    @staticmethod
+    def forward(ctx, x):
+        return _bf16(x)
+
+    @staticmethod
+    def backward(ctx, g):
+        return _bf16(g)
+
+
+_EMULATE_BF16 = False
+
+
+def _store(x):
+    return _RoundBf16.apply(x) if _EMULATE_BF16 else x
+
+
 def _conv(x, w, b, stride):
     """x NHWC, w KRSC (f64 holding bf16 values), 'Same' padding k/2, output size in/stride."""
     k = w.shape[1]
     y = F.conv2d(x.permute(0, 3, 1, 2), w.permute(0, 3, 1, 2), stride=stride, padding=k // 2)
     p, q = x.shape[1] // stride, x.shape[2] // stride
-    return y[:, :, :p, :q].permute(0, 2, 3, 1) + b
+    return _store(y[:, :, :p, :q].permute(0, 2, 3, 1) + b)
 
 
 def _bn(x, gamma, beta):
     mean = x.mean(dim=(0, 1, 2))
     var = (x * x).mean(dim=(0, 1, 2)) - mean * mean
-    return (x - mean) / torch.sqrt(var + 1e-3) * gamma + beta
+    return _store((x - mean) / torch.sqrt(var + 1e-3) * gamma + beta)
 
 
 def forward(params: dict, images: torch.Tensor, labels: np.ndarray, classes: int):
@@ -81,8 +100,20 @@ def forward(params: dict, images: torch.Tensor, labels: np.ndarray, classes: int
 
 
 def training_step(params_f32: dict, image_bits: np.ndarray, labels: np.ndarray, classes: int, lr: float, momentum: float,
-                  averages: dict | None):
-    """One step on f32 master parameters (numpy).  Returns (loss, grads, new_params, new_averages)."""
+                  averages: dict | None, emulate_bf16: bool = False):
+    """One step on f32 master parameters (numpy).  Returns (loss, grads, new_params, new_averages).
+    With `emulate_bf16` every convolution and batch-norm output (and the gradient flowing back through it) is
+    rounded to bf16, which is where a bf16 run stores tensors: the distance of that run's gradients from the
+    exact ones is the noise floor any bf16 implementation of this step has."""
+    global _EMULATE_BF16
+    _EMULATE_BF16 = bool(emulate_bf16)
+    try:
+        return _training_step(params_f32, image_bits, labels, classes, lr, momentum, averages)
+    finally:
+        _EMULATE_BF16 = False
+
+
+def _training_step(params_f32, image_bits, labels, classes, lr, momentum, averages):
     bits = np.ascontiguousarray(image_bits, dtype=np.uint16)
     img = torch.from_numpy((bits.astype(np.uint32) << 16).view(np.float32).astype(np.float64))
     P = {}

@@ -14,12 +14,11 @@ from helpers import O
 pytestmark = pytest.mark.gpu
 
 
-def _run_steps(ctx, batch, hw, classes, steps, lr):
+def _setup(ctx, batch, hw, classes):
     import torch
-    from oracle import convnet_torch as CT
     net = convnet.ConvNet(ctx, batch, image_hw=hw, classes=classes)
     params = convnet.init_params(4, classes)
-    # non-trivial biases / gammas so that their gradients matter
+    # non-trivial biases / gammas / betas so that their gradients matter
     r = np.random.default_rng(9)
     for n, k, shape in net.spec:
         if k == "bias":
@@ -32,38 +31,79 @@ def _run_steps(ctx, batch, hw, classes, steps, lr):
     bits, labels = convnet.synthetic_batch(batch, hw, classes)
     net.acts["x0"].view(torch.int16).copy_(torch.from_numpy(bits.view(np.int16)))
     net.labels.copy_(torch.from_numpy(labels))
-    ref_params, ref_avg = {k: v.copy() for k, v in params.items()}, None
-    out = []
-    for _ in range(steps):
-        net.step(lr)
-        torch.cuda.synchronize()
-        ctx.poll()
-        loss = float(net.loss.sum().item())
-        grads = {}
-        for n, k, shape in net.spec:
-            src = net.GW[n] if k == "conv" else net.GV[n]
-            grads[n] = src.float().cpu().numpy().astype(np.float64)
-        ref_loss, ref_grads, ref_params, ref_avg = CT.training_step(ref_params, bits, labels, classes, lr, 0.9, ref_avg)
-        out.append((loss, grads, net.params_to_host(), ref_loss, ref_grads, {k: v.copy() for k, v in ref_params.items()}))
-    return net, out
+    return net, params, bits, labels
+
+
+def _device_grads(net):
+    out = {}
+    for n, k, shape in net.spec:
+        src = net.GW[n] if k == "conv" else net.GV[n]
+        out[n] = src.float().cpu().numpy().astype(np.float64)
+    return out
 
 
 def test_training_step_matches_the_reference_model(ctx):
-    batch, hw, classes = 8, 64, 40
-    net, out = _run_steps(ctx, batch, hw, classes, 2, 0.05)
-    assert net.launches > 100
-    for step, (loss, grads, new_p, ref_loss, ref_grads, ref_p) in enumerate(out):
-        assert abs(loss - ref_loss) <= 1e-2 * abs(ref_loss), (step, loss, ref_loss)
-        worst = ("", 0.0)
+    """Loss, gradients and updated parameters of two steps.  The yardstick for the gradients is the reference itself
+    run with bf16 storage emulated (oracle/convnet_torch.py): its distance from the exact float64 gradients is the
+    noise floor of any bf16 run of this network (batch statistics over a few hundred values amplify the 0.4 %
+    rounding of the activations to tens of percent in the first layers).  The GPU must stay within 1.5 x that
+    floor plus 1 % for every tensor.  Convolution biases in front of a batch norm have a gradient of exactly zero
+    (the norm removes the mean); for those the device value must be small against the filter gradient's scale."""
+    import torch
+    from oracle import convnet_torch as CT
+    batch, hw, classes, lr = 16, 96, 40, 0.05
+    net, params, bits, labels = _setup(ctx, batch, hw, classes)
+    def averages_to_host():
+        out = {}
         for n, k, shape in net.spec:
-            g, rg = grads[n], ref_grads[n]
-            if n == "head.w":
-                g, rg = g[..., :3], rg[..., :3]       # the padded input channels carry no information
-            err = O.rel_l2(g, rg)
-            if err > worst[1]:
-                worst = (n, err)
-            tol = 2e-2 if n.startswith("tail") else 5e-2
-            assert err <= tol, (step, n, err)
+            flat = net.avg_conv if k == "conv" else net.avg_vec
+            out[n] = flat[net.offs[n]: net.offs[n] + int(np.prod(shape))].view(shape).cpu().numpy().astype(np.float64)
+        return out
+
+    for step in range(2):
+        # the reference starts every step from the device's own state, so that one step is compared at a time
+        old_p = net.params_to_host()
+        old_avg = None if step == 0 else averages_to_host()
+        net.step(lr)
+        torch.cuda.synchronize()
+        ctx.poll()
+        assert net.launches > 100
+        loss = float(net.loss.sum().item())
+        grads = _device_grads(net)
+        new_p = net.params_to_host()
+        _, noisy, _, _ = CT.training_step(old_p, bits, labels, classes, lr, 0.9, old_avg, emulate_bf16=True)
+        ref_loss, exact, ref_p, _ = CT.training_step(old_p, bits, labels, classes, lr, 0.9, old_avg)
+        assert abs(loss - ref_loss) <= 5e-3 * abs(ref_loss), (step, loss, ref_loss)
+        report = []
         for n, k, shape in net.spec:
-            assert O.rel_l2(new_p[n], ref_p[n]) <= 2e-3, (step, n, O.rel_l2(new_p[n], ref_p[n]))
-        print("step", step, "loss", loss, ref_loss, "worst gradient", worst)
+            g, rg, ng = grads[n], exact[n], noisy[n]
+            cut = (lambda a: a[..., :3]) if n == "head.w" else (lambda a: a)   # the padded input channels carry no information
+            upd_dev, upd_ref = cut(old_p[n].astype(np.float64) - new_p[n]), cut(old_p[n].astype(np.float64) - ref_p[n])
+            if k == "bias" and n != "tail.b":
+                wref = exact[n[:-1] + "w"]
+                bound = 0.05 * np.abs(wref).max() * np.prod(wref.shape[1:])
+                assert np.abs(g).max() <= bound and np.abs(upd_dev).max() <= lr * bound, (step, n)
+                continue
+            err, floor = O.rel_l2(cut(g), cut(rg)), O.rel_l2(cut(ng), cut(rg))
+            report.append((n, err, floor))
+            assert err <= 1.5 * floor + 1e-2, (step, n, err, floor)
+            # the optimiser step (the second one exercises the exponential average): same yardstick on the update
+            uerr = O.rel_l2(upd_dev, upd_ref)
+            assert uerr <= 1.5 * floor + 2e-2, (step, n, uerr, floor)
+        print(f"step {step}: loss {loss:.5f} vs {ref_loss:.5f}; gradient error / bf16 floor: " +
+              " ".join(f"{n}={e:.3f}/{f:.3f}" for n, e, f in report))
+
+
+def test_step_is_bit_stable(ctx):
+    """Two nets fed the same bytes produce the same loss and gradient bits: every reduction has a fixed order."""
+    import torch
+    outs = []
+    for _ in range(2):
+        net, _, _, _ = _setup(ctx, 8, 64, 24)
+        net.step(0.01)
+        torch.cuda.synchronize()
+        ctx.poll()
+        outs.append((net.loss.clone(), net.g_conv.clone(), net.g_vec.clone()))
+    for a, b in zip(outs[0], outs[1]):
+        assert torch.equal(a.view(torch.int32) if a.dtype == torch.float32 else a.view(torch.int16),
+                           b.view(torch.int32) if b.dtype == torch.float32 else b.view(torch.int16))
