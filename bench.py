@@ -850,8 +850,7 @@ class WorkloadC5:
             else:
                 params[n] = np.zeros(shape, dtype=np.float32)
         n_img = 2
-        img = np.zeros((n_img, WorkloadC5.HW, WorkloadC5.HW, 8), dtype=np.float32)
-        img[..., :3] = r.standard_normal((n_img, WorkloadC5.HW, WorkloadC5.HW, 3), dtype=np.float32)
+        img = r.standard_normal((n_img, WorkloadC5.HW, WorkloadC5.HW, 3), dtype=np.float32)
         bits = (img.view(np.uint32) >> 16).astype(np.uint16)
         labels = r.integers(0, WorkloadC5.CLASSES, size=n_img).astype(np.int32)
         for _ in range(warmup):

@@ -72,6 +72,7 @@ SIGNATURES = {
     "he_colsum_bf16": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_void_p]),
     "he_sgd_momentum": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p, C.c_int64, C.c_float, C.c_float, C.c_int32,
                                     C.c_void_p]),
+    "he_im2col_nhwc": (C.c_int32, [C.c_void_p, C.c_void_p] + [C.c_int32] * 8 + [C.c_void_p]),
     "he_pool_softmax_ce": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_void_p]),
     "he_plan_supported": (C.c_int32, [C.c_void_p, C.POINTER(HeGraphDesc), C.c_int32]),
     "he_plan_workspace_bytes": (C.c_int32, [C.c_void_p, C.POINTER(C.c_size_t)]),

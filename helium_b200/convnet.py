@@ -16,8 +16,10 @@ What is fused where:
   * bias and the block's residual add ride in the convolution epilogue;
   * in the backward pass the rectifier mask and the two sums batch norm's backward needs ride in the epilogue
     of the data-gradient convolution, so bn backward is one affine pass dx = A g + B x + K.
-RGB images are padded to 8 channels (a 16-byte pixel pitch) and so is the head's filter; the extra channels are
-zero and receive zero gradients.
+The stem is the one convolution that does not read its image through TMA: three channels are a 6-byte pixel, below
+the 16-byte pitch a tensor map needs and far below the 64-channel slices the tensor core consumes.  Its patch
+matrix [N, 112, 112, 152] is written once per step by he_im2col_nhwc and serves both the forward pass and the
+filter gradient as the input of a 1 x 1 convolution; every other convolution is implicit.
 """
 from __future__ import annotations
 
@@ -31,12 +33,24 @@ from ._lib import check, lib
 from .runtime import Context, Plan, _stream_ptr
 
 HEAD_CHANNELS = 32
-IMG_CHANNELS = 8      # RGB padded
+IMG_CHANNELS = 3
+HEAD_K = 152          # 7 * 7 * 3 = 147 patch columns, padded to a multiple of 8
+
+
+def filter_to_head(w: np.ndarray) -> np.ndarray:
+    """[32, 7, 7, 3] stem filter -> the [32, 1, 1, 152] filter of the 1 x 1 convolution over the patch matrix."""
+    out = np.zeros((w.shape[0], 1, 1, HEAD_K), dtype=w.dtype)
+    out[:, 0, 0, :147] = w.reshape(w.shape[0], 147)
+    return out
+
+
+def head_to_filter(w: np.ndarray) -> np.ndarray:
+    return np.ascontiguousarray(w.reshape(w.shape[0], HEAD_K)[:, :147]).reshape(w.shape[0], 7, 7, 3)
 
 
 def model_spec(classes: int = 1000):
     """Convolutions and batch norms in parameter order: (name, kind, shape)."""
-    spec = [("head.w", "conv", (HEAD_CHANNELS, 7, 7, IMG_CHANNELS)), ("head.b", "bias", (HEAD_CHANNELS,))]
+    spec = [("head.w", "conv", (HEAD_CHANNELS, 1, 1, HEAD_K)), ("head.b", "bias", (HEAD_CHANNELS,))]
     c = HEAD_CHANNELS
     for s in range(4):
         o = 2 * c
@@ -58,16 +72,17 @@ def model_spec(classes: int = 1000):
 
 def init_params(seed: int = 4, classes: int = 1000) -> Dict[str, np.ndarray]:
     """f32 master parameters: filters ~ N(0, 1/sqrt(R S K)) (helium's "KaimingNormal", initializer.rs:29-36,48-52),
-    biases 0, gamma 1, beta 0.  The head's filter is zero in the padded input channels."""
+    biases 0, gamma 1, beta 0.  The stem's [32, 7, 7, 3] filter is stored as the [32, 1, 1, 152] filter of a 1 x 1
+    convolution over the patch matrix (filter_to_head)."""
     r = np.random.Generator(np.random.Philox(seed))
     out = {}
     for name, kind, shape in model_spec(classes):
-        if kind == "conv":
+        if name == "head.w":
+            w = (r.standard_normal((HEAD_CHANNELS, 7, 7, 3), dtype=np.float32) / np.float32(np.sqrt(7 * 7 * HEAD_CHANNELS))).astype(np.float32)
+            out[name] = filter_to_head(w)
+        elif kind == "conv":
             k, rr, ss, cc = shape
-            w = (r.standard_normal(shape, dtype=np.float32) / np.float32(np.sqrt(rr * ss * k))).astype(np.float32)
-            if name == "head.w":
-                w[..., 3:] = 0.0
-            out[name] = w
+            out[name] = (r.standard_normal(shape, dtype=np.float32) / np.float32(np.sqrt(rr * ss * k))).astype(np.float32)
         elif kind == "gamma":
             out[name] = np.ones(shape, dtype=np.float32)
         else:
@@ -77,7 +92,7 @@ def init_params(seed: int = 4, classes: int = 1000) -> Dict[str, np.ndarray]:
 
 def flops_per_image(hw: int = 224, classes: int = 1000) -> float:
     """Multiply-adds x 2 of the forward convolutions (RGB counted as 3 channels); backward costs twice that."""
-    f = (hw // 2) ** 2 * 7 * 7 * 3 * HEAD_CHANNELS
+    f = (hw // 2) ** 2 * 7 * 7 * IMG_CHANNELS * HEAD_CHANNELS
     c, s = HEAD_CHANNELS, hw // 2
     for _ in range(4):
         o, s2 = 2 * c, s // 2
@@ -175,7 +190,8 @@ class ConvNet:
         N, hw = self.N, self.hw
         self._act("x0", (N, hw, hw, IMG_CHANNELS))
         s = hw // 2
-        self._conv_plans("head", hw, IMG_CHANNELS, HEAD_CHANNELS, 7, 2, dict(stats=True))
+        self._act("cols", (N, s, s, HEAD_K))
+        self._conv_plans("head", s, HEAD_K, HEAD_CHANNELS, 1, 1, dict(stats=True))
         self._act("h", (N, s, s, HEAD_CHANNELS))
         c = HEAD_CHANNELS
         self.blocks = []
@@ -279,7 +295,9 @@ class ConvNet:
     def forward(self) -> None:
         A, W, V, B = self.acts, self.W16, self.V, self.bns
         N = self.N
-        self._launch("head.fwd", [A["x0"], W["head.w"], V["head.b"]], [A["h"], B["seg0.down.bn1"].stats])
+        check(lib.he_im2col_nhwc(A["x0"].data_ptr(), A["cols"].data_ptr(), N, self.hw, self.hw, IMG_CHANNELS, 7, 7, 2, HEAD_K, self._st()))
+        self.launches += 1
+        self._launch("head.fwd", [A["cols"], W["head.w"], V["head.b"]], [A["h"], B["seg0.down.bn1"].stats])
         x = A["h"]
         for (i, c, o, s, s2) in self.blocks:
             p, q = f"seg{i}.down", f"seg{i}.basic"
@@ -372,7 +390,7 @@ class ConvNet:
             else:
                 self._bn_backward(p + ".bn1", A[p + ".gx"], xprev, A[p + ".ga"], p + ".bn1")
                 dout = A[p + ".ga"]
-        self._launch("head.wgrad", [dout, A["x0"]], [GW["head.w"]])
+        self._launch("head.wgrad", [dout, A["cols"]], [GW["head.w"]])
         self._colsum(dout, GV["head.b"])
 
     def torch_copy(self, dst, src):
@@ -404,10 +422,9 @@ class ConvNet:
 
 
 def synthetic_batch(batch: int, hw: int = 224, classes: int = 1000, seed: int = 4, shard: int = 0):
-    """Images ~ N(0,1) as bf16 bits [N, hw, hw, 8] (channels 3..7 zero) and labels uniform over the classes."""
+    """Images ~ N(0,1) as bf16 bits [N, hw, hw, 3] and labels uniform over the classes."""
     r = np.random.Generator(np.random.Philox(seed + 7919 * (shard + 1)))
-    img = np.zeros((batch, hw, hw, IMG_CHANNELS), dtype=np.float32)
-    img[..., :3] = r.standard_normal((batch, hw, hw, 3), dtype=np.float32)
+    img = r.standard_normal((batch, hw, hw, IMG_CHANNELS), dtype=np.float32)
     b = img.view(np.uint32).astype(np.uint64)
     bits = ((b + 0x7FFF + ((b >> 16) & 1)) >> 16).astype(np.uint16)
     labels = r.integers(0, classes, size=batch).astype(np.int32)

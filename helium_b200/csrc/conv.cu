@@ -188,6 +188,7 @@ struct ConvPlan : he_plan {
     const int OHt = fwd ? P : H, OWt = fwd ? Q : W; // output tensor grid
     if (memset_out) HE_CUDA(cudaMemsetAsync(outputs[0], 0, (size_t)NB * OHt * OWt * Nout * (fus.out_dtype == HE_F32 ? 4 : 2), stream));
     float* ws = reinterpret_cast<float*>(workspace);
+    if (fus.want_stats) HE_CUDA(cudaMemsetAsync(workspace, 0, workspace_bytes, stream));   // CTAs add into their partial rows
     for (const Pass& ps : passes) {
       ConvParams p;
       memset(&p, 0, sizeof p);
@@ -378,10 +379,10 @@ int32_t plan_conv2d(he_ctx* ctx, int32_t kind, const he_conv2d_params* prm, int3
       choose_patch(kBM, g.GQ, g.GP, batch, &g.tw, &g.th, &g.tn);
       g.tiles_q = (g.GQ + g.tw - 1) / g.tw; g.tiles_p = (g.GP + g.th - 1) / g.th; g.tiles_nb = (batch + g.tn - 1) / g.tn;
       const int tiles_m = g.tiles_q * g.tiles_p * g.tiles_nb;
-      ps.tile_m_base = tile_m_base;
-      tile_m_base += tiles_m;
       ps.num_tiles = tiles_m * c.tiles_n;
       ps.grid = std::max(1, std::min(ps.num_tiles, sms));
+      ps.tile_m_base = tile_m_base;     // statistics partials: one row per CTA of every pass
+      tile_m_base += ps.grid;
       plan->passes.push_back(ps);
     }
   if (plan->passes.empty()) HE_FAIL(HE_ERR_INVALID, "conv2d: nothing to compute");

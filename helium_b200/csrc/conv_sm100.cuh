@@ -42,7 +42,7 @@ struct ConvGeom {
   // where patch-grid pixel (n, p, q) lives in the OUTPUT tensor: ((n * OH + p * os + oh0) * OW + q * os + ow0)
   int OH, OW, os, oh0, ow0;
   int n_taps, c_blocks;         // k-blocks per tile = n_taps * c_blocks (64 channels each)
-  int tile_m_base;              // first M-tile number of this pass (rows of the statistics partials)
+  int tile_m_base;              // first statistics-partial row of this pass; CTA b of the pass owns row tile_m_base + b
   ConvTap taps[kConvMaxTaps];
 };
 
@@ -125,11 +125,28 @@ struct EpiConv {
       warp_colsum_store<kChunk>(s1, env.scratch + (4 + env.quadrant) * env.bn + col);
     }
   }
+  // The two column sums go to ONE partial row per CTA (row = t.tile_m, which the kernel sets to the CTA's row):
+  // a CTA adds every tile it processes into its own row, in its fixed tile order, so the fold that follows
+  // reads at most one row per CTA instead of one per tile, and the result is still a fixed function of the
+  // inputs.  The rows are zeroed by the host before the launch.
   __device__ static void tile_end(const Params& p, const EpiEnv& env, const TileInfo& t, State&) {
-    if (p.stat0_partials) {
-      float* parts[2] = {p.stat0_partials, p.stat1_partials};
-      col_partials_flush(env, t, 2, parts);
+    if (!p.stat0_partials) return;
+    ptx::named_barrier_sync(1, env.n_epi_threads);
+    const GemmCore& c = *env.core;
+    for (int col = env.epi_tid; col < t.bn; col += env.n_epi_threads) {
+      const int gc = t.n0 + col;
+      if (gc < c.N) {
+        float* parts[2] = {p.stat0_partials, p.stat1_partials};
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+          const float* s = env.scratch + (size_t)r * 4 * env.bn;
+          const float v = ((s[col] + s[env.bn + col]) + s[2 * env.bn + col]) + s[3 * env.bn + col];
+          float* dst = parts[r] + (size_t)t.tile_m * c.N + gc;
+          *dst += v;   // only this thread of this CTA ever touches this word
+        }
+      }
     }
+    ptx::named_barrier_sync(1, env.n_epi_threads);
   }
 };
 
@@ -209,7 +226,7 @@ __global__ void __launch_bounds__(32 * 10, 1) conv_fprop_kernel(const __grid_con
     Origin o;
     const int tn_ = tile % c.tiles_n;
     int m = tile / c.tiles_n;
-    o.tile_m = m + g.tile_m_base;
+    o.tile_m = g.tile_m_base + (int)blockIdx.x;
     o.n0 = tn_ * BN;
     const int qi = m % g.tiles_q; m /= g.tiles_q;
     const int pi = m % g.tiles_p; m /= g.tiles_p;

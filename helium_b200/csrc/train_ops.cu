@@ -320,10 +320,44 @@ __global__ void __launch_bounds__(256) pool_softmax_ce_kernel(const unsigned sho
   }
 }
 
+// cols[n, p, q, k] = x[n, p * st + r - pad_h, q * st + s - pad_w, c] for k = (r * S + s) * C + c < R * S * C, zero
+// elsewhere (outside the image, and the padding columns up to `pitch`).  One thread writes 8 consecutive k of
+// one output pixel as a 16-byte store; the source elements are 2-byte loads that hit L1 / L2 (every input pixel
+// is read by R * S / st^2 outputs).  Used for convolutions whose channel count is too small to feed the tensor
+// core from the NHWC tensor directly (an RGB stem): the explicit patch matrix then goes through the same
+// convolution kernels as a 1 x 1 convolution over `pitch` channels.
+__global__ void __launch_bounds__(256) im2col_kernel(const unsigned short* __restrict__ x, uint4* __restrict__ cols, int NB, int H, int W,
+                                                     int C, int R, int S, int st, int pad_h, int pad_w, int P, int Q, int pitch) {
+  const int vec_per_pix = pitch >> 3;
+  const long long total = (long long)NB * P * Q * vec_per_pix;
+  const int rsc = R * S * C, sc = S * C;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int v = (int)(i % vec_per_pix);
+    long long pix = i / vec_per_pix;
+    const int q = (int)(pix % Q); pix /= Q;
+    const int p = (int)(pix % P);
+    const int n = (int)(pix / P);
+    uint32_t e[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int k = v * 8 + j;
+      uint32_t val = 0;
+      if (k < rsc) {
+        const int r = k / sc, rem = k - r * sc;
+        const int s_ = rem / C, c = rem - s_ * C;
+        const int h = p * st + r - pad_h, w = q * st + s_ - pad_w;
+        if (h >= 0 && h < H && w >= 0 && w < W) val = __ldg(x + (((size_t)n * H + h) * W + w) * C + c);
+      }
+      e[j] = val;
+    }
+    __stcs(cols + i, make_uint4(e[0] | (e[1] << 16), e[2] | (e[3] << 16), e[4] | (e[5] << 16), e[6] | (e[7] << 16)));
+  }
+}
+
 int ctas_for(long long pixels, int C) {
   const int lanes = 256 / (C >> 3);
   const long long want = (pixels + (long long)lanes * 8 - 1) / ((long long)lanes * 8);
-  return (int)std::max<long long>(1, std::min<long long>(want, 148 * 8));
+  return (int)std::max<long long>(1, std::min<long long>(want, 148 * 2));
 }
 
 int32_t check_channels(const char* who, long long pixels, int C) {
@@ -452,6 +486,21 @@ int32_t he_sgd_momentum(float* w, float* avg, const void* grad, int32_t grad_dty
   else
     sgd_momentum_kernel<unsigned short><<<grid, 256, 0, st>>>(w, avg, reinterpret_cast<const unsigned short*>(grad),
                                                               reinterpret_cast<unsigned short*>(w_bf16), n, lr, momentum, first_step);
+  HE_CUDA(cudaGetLastError());
+  return HE_OK;
+}
+
+int32_t he_im2col_nhwc(const void* x, void* cols, int32_t batch, int32_t in_h, int32_t in_w, int32_t channels, int32_t kernel_h,
+                       int32_t kernel_w, int32_t stride, int32_t pitch, void* cu_stream) {
+  if (!x || !cols || batch <= 0 || in_h <= 0 || in_w <= 0 || channels <= 0 || kernel_h <= 0 || kernel_w <= 0 || stride <= 0)
+    HE_FAIL(HE_ERR_INVALID, "he_im2col_nhwc: bad argument");
+  if (pitch % 8 != 0 || pitch < kernel_h * kernel_w * channels) HE_FAIL(HE_ERR_INVALID, "he_im2col_nhwc: pitch must be a multiple of 8 and at least R*S*C = %d", kernel_h * kernel_w * channels);
+  if ((uintptr_t)cols & 15) HE_FAIL(HE_ERR_UNSUPPORTED, "he_im2col_nhwc: the patch matrix must be 16-byte aligned");
+  const int P = in_h / stride, Q = in_w / stride;   // 'Same' geometry: helium-ir/src/opgraph/op/conv.rs:51-74
+  const long long total = (long long)batch * P * Q * (pitch / 8);
+  const unsigned grid = (unsigned)std::min<long long>((total + 255) / 256, 148 * 32);
+  im2col_kernel<<<grid, 256, 0, (cudaStream_t)cu_stream>>>(reinterpret_cast<const unsigned short*>(x), reinterpret_cast<uint4*>(cols), batch,
+                                                          in_h, in_w, channels, kernel_h, kernel_w, stride, kernel_h / 2, kernel_w / 2, P, Q, pitch);
   HE_CUDA(cudaGetLastError());
   return HE_OK;
 }

@@ -348,6 +348,13 @@ int32_t he_colsum_bf16(const void* x, float* out, void* workspace, int64_t pixel
  * step's convolutions read (helium/src/modules/conv.rs:63).  `avg` may be NULL for plain SGD (momentum 0). */
 int32_t he_sgd_momentum(float* w, float* avg, const void* grad, int32_t grad_dtype, void* w_bf16, int64_t n, float lr,
                         float momentum, int32_t first_step, void* cu_stream);
+/* Patch matrix of a 'Same'-padded convolution over a thin NHWC tensor (any channel count, e.g. RGB):
+ * cols[n, p, q, (r * S + s) * C + c] = x[n, p * stride + r - R/2, q * stride + s - S/2, c], zero outside the image and
+ * in the padding columns up to `pitch` (a multiple of 8).  The result, seen as an NHWC tensor with `pitch` channels,
+ * goes through he_plan_conv2d as a 1 x 1 convolution whose filter is the original one reshaped to [K, 1, 1, pitch]:
+ * the route for a stem whose 3 input channels cannot feed the tensor core from the image directly. */
+int32_t he_im2col_nhwc(const void* x, void* cols, int32_t batch, int32_t in_h, int32_t in_w, int32_t channels, int32_t kernel_h,
+                       int32_t kernel_w, int32_t stride, int32_t pitch, void* cu_stream);
 /* Global average pooling + cross entropy (resnet-train/src/model.rs:77-82, helium/src/loss.rs:5-8): logits =
  * mean over `positions` of y[n, position, :], loss[n] = -log_softmax(logits)[labels[n]] / batch, and dy = the
  * gradient of sum(loss) at y (bf16, same shape). */

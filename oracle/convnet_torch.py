@@ -21,7 +21,7 @@ import torch.nn.functional as F
 def parameter_shapes(classes: int = 1000):
     """(name, shape) of every parameter, in the model's order (the same list as helium_b200.convnet.model_spec,
     restated here so that the CPU legs need not import the package)."""
-    out = [("head.w", (32, 7, 7, 8)), ("head.b", (32,))]
+    out = [("head.w", (32, 7, 7, 3)), ("head.b", (32,))]
     c = 32
     for s in range(4):
         o = 2 * c
