@@ -644,9 +644,16 @@ class WorkloadPointwise:
             case("gelu_add_mul_bf16_interpreter", [ir.BF16, ir.BF16, ir.BF16],
                  lambda g, i: g.binary(ir.BIN_MUL, g.unary(ir.UN_GELU, g.binary(ir.BIN_ADD, i[0], i[1])), i[2])),
         ]
-        self.work_per_step = float(sum(c[4] for c in self.cases))
-        self.launches_per_step = len(self.cases)
+        # the allocation-free trailing-dims Sum (he_reduce_sum_f32_noalloc): 16 groups of 4 Mi f32 elements
+        from helium_b200._lib import check, lib as _lib
+        self._lib, self._check = _lib, check
+        self.red_in = torch.randn(16 * (1 << 22), generator=gen, device=dev)
+        self.red_out = torch.empty(16, dtype=torch.float32, device=dev)
+        self.red_bytes = self.red_in.numel() * 4
+        self.work_per_step = float(sum(c[4] for c in self.cases)) + self.red_bytes
+        self.launches_per_step = len(self.cases) + 2
         self.dominant = {c[0]: (c[1].description, c[4], "hbm", peaks["hbm_gbs"], "GB/s") for c in self.cases}
+        self.dominant["reduce_sum_noalloc_f32"] = ("he_reduce_sum_f32_noalloc on [16, 4 Mi] f32", self.red_bytes, "hbm", peaks["hbm_gbs"], "GB/s")
         self.dominant_key = "relu_mul_bf16"
         self.e2e_work_per_step = float(self.cases[0][4])   # the end-to-end leg runs the first program only
         self.pin_in = self.cases[0][2][0].cpu().pin_memory(); self.pin_m = self.cases[0][2][1].cpu().pin_memory()
@@ -663,6 +670,15 @@ class WorkloadPointwise:
                 e0, e1 = _events(self.torch)
                 e0.record(st); plan.launch(tin, tout); e1.record(st)
                 record.append((name, e0, e1))
+        import ctypes as C
+        call = lambda: self._check(self._lib.he_reduce_sum_f32_noalloc(self.red_in.data_ptr(), self.red_out.data_ptr(), 16, 1 << 22,
+                                                                        C.c_void_p(st.cuda_stream)))
+        if record is None:
+            call()
+        else:
+            e0, e1 = _events(self.torch)
+            e0.record(st); call(); e1.record(st)
+            record.append(("reduce_sum_noalloc_f32", e0, e1))
 
     def step_e2e(self):
         # the first program only, fed from and read back to pinned host memory

@@ -96,6 +96,20 @@ __global__ void conv_wgrad_fold(const float* __restrict__ partials, void* __rest
   else reinterpret_cast<unsigned short*>(out)[i] = (unsigned short)(out_dt == HE_BF16 ? f32_to_bf16_bits(s) : f32_to_f16_bits(s));
 }
 
+// out[2][N] = column sums of the two statistics partial blocks [rows][N], rows folded in order (bit-stable)
+__global__ void conv_stats_fold(const float* __restrict__ p0, const float* __restrict__ p1, float* __restrict__ out, int rows, int N) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= 2 * N) return;
+  const float* p = (i < N ? p0 : p1) + (i < N ? i : i - N);
+  float s0 = 0.0f, s1 = 0.0f, s2 = 0.0f, s3 = 0.0f;   // four interleaved chains: fixed order, shorter dependency chain
+  int r = 0;
+  for (; r + 4 <= rows; r += 4) {
+    s0 += p[(size_t)r * N]; s1 += p[(size_t)(r + 1) * N]; s2 += p[(size_t)(r + 2) * N]; s3 += p[(size_t)(r + 3) * N];
+  }
+  for (; r < rows; ++r) s0 += p[(size_t)r * N];
+  out[i] = (s0 + s1) + (s2 + s3);
+}
+
 template <int BN, bool B_MN>
 int32_t launch_fprop(const ConvParams& p, int grid, cudaStream_t stream) {
   constexpr int STAGES = BN == 128 ? 6 : 8;
@@ -229,9 +243,9 @@ struct ConvPlan : he_plan {
     }
     if (fus.want_stats) {
       float* st = reinterpret_cast<float*>(outputs[1]);
-      HE_TRY(launch_colsum_finalize(ws + ws_stat_off[0], st, 1, total_tiles_m, Nout, stream));
-      HE_TRY(launch_colsum_finalize(ws + ws_stat_off[1], st + Nout, 1, total_tiles_m, Nout, stream));
-      last_launches += 2;
+      conv_stats_fold<<<(2 * Nout + 63) / 64, 64, 0, stream>>>(ws + ws_stat_off[0], ws + ws_stat_off[1], st, total_tiles_m, Nout);
+      HE_CUDA(cudaGetLastError());
+      ++last_launches;
     }
     return HE_OK;
   }

@@ -41,7 +41,25 @@ __global__ void __launch_bounds__(kThreads) noalloc_sum_slices(const float* __re
   const unsigned end = min(start + slice, group_size);
   const float* src = in + (size_t)group * group_size;
   float acc = 0.0f;
-  for (unsigned e = start + threadIdx.x; e < end; e += kThreads) acc += __ldg(src + e);
+  // A full slice on a 16-byte boundary is read as four float4 per thread (the slice is 256 threads x 16
+  // elements); the per-thread order of additions is the same as in the scalar walk below, element e of the slice
+  // goes to thread e % 256 in both, so the result does not depend on which walk ran.
+  if (end - start == kThreads * 16 && ((reinterpret_cast<uintptr_t>(src + start) & 15) == 0)) {
+    const float* base = src + start;
+    // thread t owns elements t, t + 256, ...; the four elements of a 16-byte vector belong to four different threads,
+    // so the CTA moves the slice to shared memory with 16-byte loads and every thread then reads its own elements
+    __shared__ float stage[kThreads * 16];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float4 v = __ldg(reinterpret_cast<const float4*>(base) + i * kThreads + threadIdx.x);
+      reinterpret_cast<float4*>(stage)[i * kThreads + threadIdx.x] = v;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < 16; ++i) acc += stage[i * kThreads + threadIdx.x];
+  } else {
+    for (unsigned e = start + threadIdx.x; e < end; e += kThreads) acc += __ldg(src + e);
+  }
 #pragma unroll
   for (int off = 16; off > 0; off >>= 1) acc += __shfl_down_sync(0xffffffffu, acc, off);
   if ((threadIdx.x & 31) == 0) warp_sums[threadIdx.x >> 5] = acc;

@@ -326,31 +326,46 @@ __global__ void __launch_bounds__(256) pool_softmax_ce_kernel(const unsigned sho
 // is read by R * S / st^2 outputs).  Used for convolutions whose channel count is too small to feed the tensor
 // core from the NHWC tensor directly (an RGB stem): the explicit patch matrix then goes through the same
 // convolution kernels as a 1 x 1 convolution over `pitch` channels.
+// A CTA produces the patch rows of `kImQ` consecutive output pixels of one output row: the R source rows they read
+// are staged in shared memory with coalesced loads, then every thread assembles 16-byte output vectors from
+// 2-byte shared-memory reads and stores them coalesced.
+constexpr int kImQ = 32;
 __global__ void __launch_bounds__(256) im2col_kernel(const unsigned short* __restrict__ x, uint4* __restrict__ cols, int NB, int H, int W,
                                                      int C, int R, int S, int st, int pad_h, int pad_w, int P, int Q, int pitch) {
+  extern __shared__ unsigned short srow[];   // [R][span * C], span = (kImQ - 1) * st + S source pixels
+  const int span = (kImQ - 1) * st + S;
+  const int q_tiles = (Q + kImQ - 1) / kImQ;
   const int vec_per_pix = pitch >> 3;
-  const long long total = (long long)NB * P * Q * vec_per_pix;
   const int rsc = R * S * C, sc = S * C;
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
-    const int v = (int)(i % vec_per_pix);
-    long long pix = i / vec_per_pix;
-    const int q = (int)(pix % Q); pix /= Q;
-    const int p = (int)(pix % P);
-    const int n = (int)(pix / P);
-    uint32_t e[8];
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const int k = v * 8 + j;
-      uint32_t val = 0;
-      if (k < rsc) {
-        const int r = k / sc, rem = k - r * sc;
-        const int s_ = rem / C, c = rem - s_ * C;
-        const int h = p * st + r - pad_h, w = q * st + s_ - pad_w;
-        if (h >= 0 && h < H && w >= 0 && w < W) val = __ldg(x + (((size_t)n * H + h) * W + w) * C + c);
-      }
-      e[j] = val;
+  for (long long tile = blockIdx.x; tile < (long long)NB * P * q_tiles; tile += gridDim.x) {
+    const int qt = (int)(tile % q_tiles);
+    const long long np = tile / q_tiles;
+    const int p = (int)(np % P), n = (int)(np / P);
+    const int q0 = qt * kImQ, w0 = q0 * st - pad_w;
+    __syncthreads();   // the previous tile's readers are done
+    for (int i = threadIdx.x; i < R * span * C; i += 256) {
+      const int r = i / (span * C), rem = i - r * (span * C);
+      const int w = w0 + rem / C, h = p * st + r - pad_h;
+      srow[i] = (h >= 0 && h < H && w >= 0 && w < W) ? __ldg(x + (((long long)n * H + h) * W + w0) * C + rem) : (unsigned short)0;
     }
-    __stcs(cols + i, make_uint4(e[0] | (e[1] << 16), e[2] | (e[3] << 16), e[4] | (e[5] << 16), e[6] | (e[7] << 16)));
+    __syncthreads();
+    const int nq = min(kImQ, Q - q0);
+    for (int i = threadIdx.x; i < nq * vec_per_pix; i += 256) {
+      const int ql = i / vec_per_pix, v = i - ql * vec_per_pix;
+      uint32_t e[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int k = v * 8 + j;
+        uint32_t val = 0;
+        if (k < rsc) {
+          const int r = k / sc, kk = k - r * sc;           // kk = s * C + c: contiguous in the source row
+          val = srow[r * span * C + ql * st * C + kk];
+        }
+        e[j] = val;
+      }
+      cols[(((size_t)n * P + p) * Q + q0 + ql) * vec_per_pix + v] =
+          make_uint4(e[0] | (e[1] << 16), e[2] | (e[3] << 16), e[4] | (e[5] << 16), e[6] | (e[7] << 16));
+    }
   }
 }
 
@@ -497,9 +512,11 @@ int32_t he_im2col_nhwc(const void* x, void* cols, int32_t batch, int32_t in_h, i
   if (pitch % 8 != 0 || pitch < kernel_h * kernel_w * channels) HE_FAIL(HE_ERR_INVALID, "he_im2col_nhwc: pitch must be a multiple of 8 and at least R*S*C = %d", kernel_h * kernel_w * channels);
   if ((uintptr_t)cols & 15) HE_FAIL(HE_ERR_UNSUPPORTED, "he_im2col_nhwc: the patch matrix must be 16-byte aligned");
   const int P = in_h / stride, Q = in_w / stride;   // 'Same' geometry: helium-ir/src/opgraph/op/conv.rs:51-74
-  const long long total = (long long)batch * P * Q * (pitch / 8);
-  const unsigned grid = (unsigned)std::min<long long>((total + 255) / 256, 148 * 32);
-  im2col_kernel<<<grid, 256, 0, (cudaStream_t)cu_stream>>>(reinterpret_cast<const unsigned short*>(x), reinterpret_cast<uint4*>(cols), batch,
+  const long long tiles = (long long)batch * P * ((Q + kImQ - 1) / kImQ);
+  const unsigned grid = (unsigned)std::min<long long>(tiles, 148 * 16);
+  const size_t smem = (size_t)kernel_h * ((kImQ - 1) * stride + kernel_w) * channels * sizeof(unsigned short);
+  if (smem > 48 * 1024) HE_FAIL(HE_ERR_UNSUPPORTED, "he_im2col_nhwc: %zu bytes of staging exceed 48 KB (channel count too large for this route)", smem);
+  im2col_kernel<<<grid, 256, smem, (cudaStream_t)cu_stream>>>(reinterpret_cast<const unsigned short*>(x), reinterpret_cast<uint4*>(cols), batch,
                                                           in_h, in_w, channels, kernel_h, kernel_w, stride, kernel_h / 2, kernel_w / 2, P, Q, pitch);
   HE_CUDA(cudaGetLastError());
   return HE_OK;
