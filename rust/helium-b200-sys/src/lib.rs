@@ -37,7 +37,6 @@ pub const HE_OP_SWAP_DIMS: i32 = 8;
 pub const HE_OP_COMPARE: i32 = 9;
 pub const HE_OP_SELECT: i32 = 10;
 pub const HE_OP_MATMUL: i32 = 11;
-pub const HE_OP_CONV2D: i32 = 12;
 
 // he_precision (helium_ir::opgraph::op::precision::Precision)
 pub const HE_PREC_F32_F32: i32 = 0;
@@ -63,6 +62,26 @@ pub struct he_node {
     pub axis_b: i32,
     pub axes: u32,
 }
+
+#[repr(C)]
+#[derive(Copy, Clone)]
+pub struct he_conv2d_params {
+    pub in_channels: i32, pub out_channels: i32,
+    pub kernel_h: i32, pub kernel_w: i32,
+    pub stride_h: i32, pub stride_w: i32,
+    pub dilation_h: i32, pub dilation_w: i32,
+    pub padding_mode: i32,
+}
+
+#[repr(C)]
+#[derive(Copy, Clone)]
+pub struct he_conv2d_fusion {
+    pub out_dtype: i32, pub has_bias: i32, pub bias_dtype: i32, pub has_resid: i32, pub has_gate: i32, pub want_stats: i32,
+}
+
+pub const HE_CONV_FWD: i32 = 0;
+pub const HE_CONV_BWD_DATA: i32 = 1;
+pub const HE_CONV_BWD_FILTER: i32 = 2;
 
 #[repr(C)]
 pub struct he_graph_desc {
@@ -100,6 +119,29 @@ extern "C" {
     pub fn he_plan_last_launch_count(plan: *const he_plan) -> i32;
     pub fn he_plan_describe(plan: *const he_plan) -> *const c_char;
     pub fn he_plan_destroy(plan: *mut he_plan);
+
+    pub fn he_plan_conv2d(ctx: *mut he_ctx, kind: i32, params: *const he_conv2d_params, batch: i32, in_h: i32, in_w: i32,
+                          dtype: i32, fusion: *const he_conv2d_fusion, out: *mut *mut he_plan) -> i32;
+    pub fn he_bn_finalize(stats: *const f32, count: i64, gamma: *const f32, beta: *const f32, running_mean: *mut f32,
+                          running_var: *mut f32, scale: *mut f32, shift: *mut f32, mean: *mut f32, rstd: *mut f32, channels: i32,
+                          cu_stream: *mut c_void) -> i32;
+    pub fn he_bn_workspace_bytes(pixels: i64, channels: i32) -> usize;
+    pub fn he_bn_apply(x: *const c_void, y: *mut c_void, scale: *const f32, shift: *const f32, pixels: i64, channels: i32,
+                       relu: i32, stats_out: *mut f32, workspace: *mut c_void, cu_stream: *mut c_void) -> i32;
+    pub fn he_bn_backward_coeffs(stats: *const f32, count: i64, gamma: *const f32, mean: *const f32, rstd: *const f32,
+                                 coef: *mut f32, dgamma: *mut f32, dbeta: *mut f32, channels: i32, cu_stream: *mut c_void) -> i32;
+    pub fn he_bn_backward_apply(g: *const c_void, x: *const c_void, addend: *const c_void, out: *mut c_void, coef: *const f32,
+                                mask_x: *const c_void, mask_scale: *const f32, mask_shift: *const f32, stats_out: *mut f32,
+                                workspace: *mut c_void, pixels: i64, channels: i32, cu_stream: *mut c_void) -> i32;
+    pub fn he_add_bf16(a: *const c_void, b: *const c_void, out: *mut c_void, n: i64, cu_stream: *mut c_void) -> i32;
+    pub fn he_colsum_bf16(x: *const c_void, out: *mut f32, workspace: *mut c_void, pixels: i64, channels: i32,
+                          cu_stream: *mut c_void) -> i32;
+    pub fn he_sgd_momentum(w: *mut f32, avg: *mut f32, grad: *const c_void, grad_dtype: i32, w_bf16: *mut c_void, n: i64, lr: f32,
+                           momentum: f32, first_step: i32, cu_stream: *mut c_void) -> i32;
+    pub fn he_im2col_nhwc(x: *const c_void, cols: *mut c_void, batch: i32, in_h: i32, in_w: i32, channels: i32, kernel_h: i32,
+                          kernel_w: i32, stride: i32, pitch: i32, cu_stream: *mut c_void) -> i32;
+    pub fn he_pool_softmax_ce(y: *const c_void, labels: *const i32, loss: *mut f32, dy: *mut c_void, batch: i32, positions: i32,
+                              classes: i32, cu_stream: *mut c_void) -> i32;
 
     pub fn he_comm_unique_id(id_out: *mut c_void) -> i32;
     pub fn he_comm_create(ctx: *mut he_ctx, rank: i32, world: i32, unique_id: *const c_void, max_ctas: i32,

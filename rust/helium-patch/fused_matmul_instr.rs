@@ -12,7 +12,7 @@ pub enum Instr {
     PointwiseGraph(PointwiseGraph),
     PermuteDims(PermuteDims),
     FusedMatmul(FusedMatmul), // new: Op::Matmul (cuda.rs:55-58 builds it instead of CudnnGraph)
-    CudnnGraph(CudnnGraph),   // convolutions keep their path until HE_OP_CONV2D is wired in
+    Conv2d(Conv2d),           // new: Op::Conv / ConvBackwardData / ConvBackwardFilter through he_plan_conv2d (see below)
 }
 
 pub struct FusedMatmul {
@@ -96,7 +96,6 @@ fn record_for(op: &Op, d: &Descriptor) -> sys::he_node {
         Op::Compare(c) => { let mut n = blank(sys::HE_OP_COMPARE, d); n.sub_op = c.op as i32; n }
         Op::Select(_) => blank(sys::HE_OP_SELECT, d), // in = {lhs, rhs, selector}
         Op::Matmul(m) => { let mut n = blank(sys::HE_OP_MATMUL, d); n.sub_op = precision_code(m.precision); n }
-        Op::Conv2d(c) => conv_record(c, d),          // HE_OP_CONV2D: geometry in const_bits / axis_a / axis_b / axes
         _ => unreachable!("op is not served by helium_b200"),
     }
 }
@@ -174,6 +173,40 @@ impl Instruction<Cuda> for Instr {
                                         num_outputs: outputs.len() as i32, outputs: outputs.as_ptr() };
         // 2 = hand-written kernel, 1 = interpreter tier, 0 = cannot run as one kernel
         unsafe { sys::he_plan_supported(CudaContext::current().he_ctx(), &desc, kind) > 0 }
+    }
+}
+
+/// Convolutions do not travel as graph records: one plan per (kind, Conv2dParams, image size, fusion).
+pub struct Conv2d {
+    kind: i32, // sys::HE_CONV_FWD / HE_CONV_BWD_DATA / HE_CONV_BWD_FILTER
+    params: sys::he_conv2d_params,
+    fusion: sys::he_conv2d_fusion,
+    batch: i32,
+    in_h: i32,
+    in_w: i32,
+    dtype: i32,
+    input_order: Vec<NodeId>, // operand order of include/helium_b200.h for `kind`
+    leaf_order: Vec<NodeId>,
+}
+
+fn conv_params(p: &Conv2dParams) -> sys::he_conv2d_params {
+    sys::he_conv2d_params {
+        in_channels: p.in_channels as i32, out_channels: p.out_channels as i32,
+        kernel_h: p.kernel_size[0] as i32, kernel_w: p.kernel_size[1] as i32,
+        stride_h: p.stride[0] as i32, stride_w: p.stride[1] as i32,
+        dilation_h: p.dilation[0] as i32, dilation_w: p.dilation[1] as i32,
+        padding_mode: match p.padding_mode { PaddingMode::Same => 0, PaddingMode::Valid => 1, PaddingMode::Full => 2 },
+    }
+}
+
+impl Conv2d {
+    fn plan(&self, cx: &CudaContext) -> *mut sys::he_plan {
+        let mut plan = std::ptr::null_mut();
+        let st = unsafe {
+            sys::he_plan_conv2d(cx.he_ctx(), self.kind, &self.params, self.batch, self.in_h, self.in_w, self.dtype, &self.fusion, &mut plan)
+        };
+        assert_eq!(st, sys::HE_OK, "{}", sys::last_error());
+        plan // cached per Conv2d like the plans above; launched exactly like FusedMatmul::execute
     }
 }
 
