@@ -73,10 +73,14 @@ int32_t launch_gemm_flex(const GemmLaunchCfg& cfg, const GemmParams<EpiFlexParam
   if (cfg.two_cta && cfg.bn == 256) {
     if (cfg.ml == ML_NONE) return launch_majors_2cta<6, ML_NONE, 8, EpiFlex>(cfg, p, stream);
     if (cfg.ml == ML_RELU_MASK) return launch_majors_2cta<4, ML_RELU_MASK, 8, EpiFlex>(cfg, p, stream);
+    if (cfg.ml == ML_GENERIC) return launch_majors_2cta<6, ML_GENERIC, 8, EpiFlex>(cfg, p, stream);
+    if (cfg.ml == ML_GENERIC_MASK) return launch_majors_2cta<4, ML_GENERIC_MASK, 8, EpiFlex>(cfg, p, stream);
   }
   if (cfg.bn == 256) {
     if (cfg.ml == ML_NONE) return launch_majors<256, 4, ML_NONE, 8, EpiFlex>(cfg, p, stream);
     if (cfg.ml == ML_RELU_MASK) return launch_majors<256, 3, ML_RELU_MASK, 8, EpiFlex>(cfg, p, stream);
+    if (cfg.ml == ML_GENERIC) return launch_majors<256, 4, ML_GENERIC, 8, EpiFlex>(cfg, p, stream);
+    if (cfg.ml == ML_GENERIC_MASK) return launch_majors<256, 3, ML_GENERIC_MASK, 8, EpiFlex>(cfg, p, stream);
   } else if (cfg.bn == 128) {
     if (cfg.ml == ML_NONE) return launch_majors<128, 6, ML_NONE, 4, EpiFlex>(cfg, p, stream);
   }

@@ -7,10 +7,14 @@ int32_t launch_gemm_program(const GemmLaunchCfg& cfg, const GemmParams<EpiProgra
   if (cfg.two_cta && cfg.bn == 256) {
     if (cfg.ml == ML_NONE) return launch_majors_2cta<6, ML_NONE, 8, EpiProgram>(cfg, p, stream);
     if (cfg.ml == ML_RELU_MASK) return launch_majors_2cta<4, ML_RELU_MASK, 8, EpiProgram>(cfg, p, stream);
+    if (cfg.ml == ML_GENERIC) return launch_majors_2cta<6, ML_GENERIC, 8, EpiProgram>(cfg, p, stream);
+    if (cfg.ml == ML_GENERIC_MASK) return launch_majors_2cta<4, ML_GENERIC_MASK, 8, EpiProgram>(cfg, p, stream);
   }
   if (cfg.bn == 256) {
     if (cfg.ml == ML_NONE) return launch_majors<256, 4, ML_NONE, 8, EpiProgram>(cfg, p, stream);
     if (cfg.ml == ML_RELU_MASK) return launch_majors<256, 3, ML_RELU_MASK, 8, EpiProgram>(cfg, p, stream);
+    if (cfg.ml == ML_GENERIC) return launch_majors<256, 4, ML_GENERIC, 8, EpiProgram>(cfg, p, stream);
+    if (cfg.ml == ML_GENERIC_MASK) return launch_majors<256, 3, ML_GENERIC_MASK, 8, EpiProgram>(cfg, p, stream);
   }
   HE_FAIL(HE_ERR_UNSUPPORTED, "fused matmul: no kernel compiled for bn=%d mainloop=%d with this epilogue", cfg.bn, cfg.ml);
 }

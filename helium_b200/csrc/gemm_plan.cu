@@ -71,12 +71,36 @@ int32_t make_operand_tmap(CUtensorMap* out, const void* ptr, int ab_format, bool
 // ------------------------------------------------------------------------------------------------
 struct OperandInfo {
   int root = -1;      // graph node of the tensor that feeds the MMA
-  int mask = -1;      // second tensor multiplied in (relu(A) * M)
-  bool relu = false;
+  int mask = -1;      // second tensor combined elementwise (relu(A) * M, A + E, ...)
+  bool relu = false;  // the chain is exactly relu(root) (* mask): the hand-written rewrite applies
   bool transposed = false;  // root is stored with its last two dims swapped w.r.t. what matmul sees
   bool ok = true;
-  bool pure() const { return ok && mask < 0 && !relu; }
+  std::vector<MlStep> steps;   // the chain in evaluation order (unary steps, at most one multiply / add by `mask`)
+  bool pure() const { return ok && steps.empty(); }
+  bool relu_mask() const { return ok && relu && mask >= 0 && steps.size() == 2; }
 };
+
+MlStep ml_unary(int op, uint32_t imm) {
+  MlStep s{};
+  s.kind = 0;
+  s.op = (unsigned char)op;
+  s.imm = imm;
+  return s;
+}
+
+// Value of a node that is a constant broadcast to any shape (Constant, or Broadcast / Reshape / same-class Cast of one).
+bool constant_value(const Graph& g, int node, float* out) {
+  const he_node& n = g.nodes[node];
+  if (n.kind == HE_OP_CONSTANT && dclass(n.dtype) == DClass::Float) {
+    if (n.dtype == HE_F32) memcpy(out, &n.const_bits, 4);
+    else if (n.dtype == HE_BF16) { const uint32_t b = n.const_bits << 16; memcpy(out, &b, 4); }
+    else return false;
+    return true;
+  }
+  if ((n.kind == HE_OP_BROADCAST || n.kind == HE_OP_RESHAPE || (n.kind == HE_OP_CAST && dclass(n.dtype) == DClass::Float)) && n.in[0] >= 0)
+    return constant_value(g, n.in[0], out);
+  return false;
+}
 
 OperandInfo trace_operand(const Graph& g, int node, bool transposed) {
   const he_node& n = g.nodes[node];
@@ -87,7 +111,12 @@ OperandInfo trace_operand(const Graph& g, int node, bool transposed) {
       r.transposed = transposed;
       return r;
     case HE_OP_CAST:
-      if (n.dtype == g.nodes[n.in[0]].dtype) return trace_operand(g, n.in[0], transposed);
+      // a cast between float types only changes where the value is rounded; the chain is evaluated in f32 and
+      // rounded once to the operand type
+      if (dclass(n.dtype) == DClass::Float && dclass(g.nodes[n.in[0]].dtype) == DClass::Float) {
+        r = trace_operand(g, n.in[0], transposed);
+        if (r.ok && (n.dtype == g.nodes[n.in[0]].dtype || !r.steps.empty() || g.nodes[r.root].dtype == n.dtype)) return r;
+      }
       break;
     case HE_OP_RESHAPE: {
       const he_node& a = g.nodes[n.in[0]];
@@ -102,22 +131,39 @@ OperandInfo trace_operand(const Graph& g, int node, bool transposed) {
       if (lo == n.rank - 2 && hi == n.rank - 1) return trace_operand(g, n.in[0], !transposed);
       break;
     }
-    case HE_OP_UNARY:
-      if (n.sub_op == HE_UN_RELU) {
-        r = trace_operand(g, n.in[0], transposed);
-        if (r.pure()) {
-          r.relu = true;
-          return r;
-        }
-      }
-      break;
+    case HE_OP_UNARY: {
+      r = trace_operand(g, n.in[0], transposed);
+      if (!r.ok) break;
+      if (n.sub_op == HE_UN_RELU && r.pure()) r.relu = true;
+      else if (!r.steps.empty()) r.relu = false;
+      r.steps.push_back(ml_unary(n.sub_op, n.const_bits));
+      return r;
+    }
     case HE_OP_BINARY:
-      if (n.sub_op == HE_BIN_MUL) {
+      if (n.sub_op == HE_BIN_MUL || n.sub_op == HE_BIN_ADD) {
+        // x (op) constant becomes a unary step
+        for (int side = 0; side < 2; ++side) {
+          float cv;
+          if (constant_value(g, n.in[1 - side], &cv)) {
+            r = trace_operand(g, n.in[side], transposed);
+            if (!r.ok) break;
+            uint32_t bits;
+            memcpy(&bits, &cv, 4);
+            r.relu = false;
+            r.steps.push_back(ml_unary(n.sub_op == HE_BIN_MUL ? HE_UN_MUL_CONST : HE_UN_ADD_CONST, bits));
+            return r;
+          }
+        }
         OperandInfo l = trace_operand(g, n.in[0], transposed), rr = trace_operand(g, n.in[1], transposed);
         if (l.ok && rr.ok) {
           if (!rr.pure() && l.pure()) std::swap(l, rr);
-          if (rr.pure() && l.mask < 0 && l.transposed == rr.transposed) {
+          if (rr.pure() && l.mask < 0 && l.transposed == rr.transposed &&
+              num_elements(g.nodes[rr.root]) == num_elements(g.nodes[l.root])) {
             l.mask = rr.root;
+            MlStep st{};
+            st.kind = n.sub_op == HE_BIN_MUL ? 1 : 2;
+            l.steps.push_back(st);
+            if (!(l.relu && l.steps.size() == 2 && st.kind == 1)) l.relu = false;
             return l;
           }
         }
@@ -397,6 +443,7 @@ struct MatmulPlan : he_plan {
   // in-kernel rewrite (repeated for every N tile, at about half the plain mainloop's rate) would
   // cost more than one extra pass over A and the mask.
   bool materialise_a = false;
+  bool ml_b = false;          // generic mainloop program on the B operand (single-CTA kernel only)
   size_t ws_aprime_off = 0;   // bytes
   // Operands whose row pitch is not a multiple of 16 bytes cannot be described to TMA.  They are copied
   // once per launch into the workspace with the pitch rounded up to 8 elements (`pad_pitch`), and the
@@ -678,18 +725,50 @@ int32_t plan_fused_matmul(he_ctx* ctx, const Graph& g_in, he_plan** out, int* ti
     if (g.nodes[i].kind == HE_OP_MATMUL && mm < 0) mm = i;
   if (mm < 0) return plan_fused_matmul_core(ctx, g, out, tier_only);   // reports the error
   const OperandInfo A = trace_operand(g, g.nodes[mm].in[0], false), B = trace_operand(g, g.nodes[mm].in[1], false);
-  // The kernels apply exactly relu(A) * mask on bf16 tiles in their mainloop (or in the dense pre-pass);
-  // every other operand expression, and that one on shapes / dtypes the tensor-core path does not
-  // take, goes through a pointwise pre-pass.
+  // Operand-side expressions run either inside the kernel's mainloop (transform warps rewrite the tile in
+  // shared memory: the hand-written relu(A) * mask rewrite, or a generic program of unary steps with at most
+  // one elementwise multiply / add by a second tensor) or as a pointwise pre-pass that writes the operand once.
+  // The in-kernel rewrite is repeated for every tile across the other dimension and slows the mainloop, so
+  // it is chosen when that repetition is short (same cost rule as for relu * mask, see choose_mainloop), when
+  // HE_GEMM_MAINLOOP=fused forces it, and never for shapes / dtypes the tensor-core path does not take.
+  const he_node& M0 = g.nodes[mm];
+  const int64_t Md = M0.shape[M0.rank - 2], Kd = g.nodes[M0.in[0]].shape[M0.rank - 1], Nd = M0.shape[M0.rank - 1];
+  int64_t batch0 = 1;
+  for (int k = 0; k < M0.rank - 2; ++k) batch0 *= M0.shape[k];
+  const char* ml_env = getenv("HE_GEMM_MAINLOOP");
+  auto in_kernel_ok = [&](const OperandInfo& X, bool is_a) {
+    if (!X.ok || X.pure() || !A.ok || !B.ok) return false;
+    const int dt = g.nodes[X.root].dtype;
+    if ((dt != HE_BF16 && dt != HE_F16) || g.nodes[A.root].dtype != g.nodes[B.root].dtype) return false;
+    if (X.mask >= 0 && (g.nodes[X.mask].dtype != dt || !is_a)) return false;
+    if ((int)X.steps.size() > kMlMaxSteps) return false;
+    if ((A.transposed ? Md : Kd) % 8 != 0 || (B.transposed ? Kd : Nd) % 8 != 0) return false;
+    return true;
+  };
+  auto prefers_kernel = [&](bool is_a) {
+    if (ml_env) return ml_env[0] == 'f';
+    // repetition count of the rewrite = tiles across the other dimension; the pre-pass costs one more pass over the operand
+    const double gemm_us = 2.0 * batch0 * Md * (double)Nd * Kd / 1.3e9;
+    const double bytes = 3.0 * batch0 * (is_a ? Md : Nd) * (double)Kd * 2.0;
+    return 0.7 * gemm_us <= bytes / 4.5e6 + 5.0;
+  };
   bool fusable_a = A.ok;
   if (A.ok && !A.pure()) {
-    const he_node& M0 = g.nodes[mm];
-    const int64_t Md = M0.shape[M0.rank - 2], Kd = g.nodes[M0.in[0]].shape[M0.rank - 1], Nd = M0.shape[M0.rank - 1];
-    fusable_a = A.relu && A.mask >= 0 && g.nodes[A.root].dtype == HE_BF16 && g.nodes[A.mask].dtype == HE_BF16 && B.ok && B.pure() &&
-                g.nodes[B.root].dtype == HE_BF16 && (A.transposed ? Md : Kd) % 8 == 0 && (B.transposed ? Kd : Nd) % 8 == 0;
+    if (A.relu_mask()) fusable_a = in_kernel_ok(A, true) && g.nodes[A.root].dtype == HE_BF16 && B.pure();   // materialise-or-fuse is decided in the core planner
+    else fusable_a = in_kernel_ok(A, true) && prefers_kernel(true);
   }
-  const bool pro_a = !fusable_a, pro_b = !B.ok || !B.pure();
-  if (!pro_a && !pro_b) return plan_fused_matmul_core(ctx, g, out, tier_only);
+  bool fusable_b = B.ok;
+  if (B.ok && !B.pure()) fusable_b = in_kernel_ok(B, false) && prefers_kernel(false) && !(A.ok && A.relu_mask());
+  bool pro_a = !fusable_a, pro_b = !fusable_b;
+  if (!pro_a && !pro_b) {
+    const int32_t st = plan_fused_matmul_core(ctx, g, out, tier_only);
+    const bool generic = (A.ok && !A.pure() && !A.relu_mask()) || (B.ok && !B.pure());
+    if (st == HE_OK || !generic) return st;
+    // the generic in-kernel rewrite is not compiled for this epilogue family: evaluate the operands by a pre-pass
+    set_error("");
+    pro_a = !A.pure();
+    pro_b = !B.pure();
+  }
 
   // replace each such operand by a virtual input (same node index, so the list stays topological)
   Graph g2 = g;
@@ -751,8 +830,8 @@ int32_t plan_fused_matmul_core(he_ctx* ctx, const Graph& g, he_plan** out, int* 
   const int r = M.rank;
   const OperandInfo A = trace_operand(g, M.in[0], false), B = trace_operand(g, M.in[1], false);
   if (!A.ok || !B.ok)
-    HE_FAIL(HE_ERR_UNSUPPORTED, "fused matmul: operand side uses ops outside {cast, reshape, transpose, relu, elementwise mask}");
-  if (!B.pure()) HE_FAIL(HE_ERR_UNSUPPORTED, "fused matmul: mainloop fusion on the B operand is not implemented");
+    HE_FAIL(HE_ERR_UNSUPPORTED, "fused matmul: operand side uses ops outside {cast, reshape, transpose, unary, multiply / add by one tensor or a constant}");
+  if (B.mask >= 0) HE_FAIL(HE_ERR_UNSUPPORTED, "fused matmul: a second tensor on the B operand side is not implemented in the mainloop");
   const he_node& An = g.nodes[A.root];
   const he_node& Bn = g.nodes[B.root];
 
@@ -779,7 +858,19 @@ int32_t plan_fused_matmul_core(he_ctx* ctx, const Graph& g, he_plan** out, int* 
   plan->n_outputs = (int)g.outputs.size();
   plan->cfg.a_mn = A.transposed;
   plan->cfg.b_mn = !B.transposed;  // helium stores B as [K, N] row-major = N-major
-  plan->cfg.ml = (A.relu ? ML_RELU : 0) | (A.mask >= 0 ? ML_MASK : 0);
+  if (A.pure() && B.pure()) plan->cfg.ml = ML_NONE;
+  else if (A.relu_mask() && B.pure()) plan->cfg.ml = ML_RELU_MASK;
+  else plan->cfg.ml = ML_GENERIC | (A.mask >= 0 ? ML_MASK : 0);
+  auto fill_prog = [](const OperandInfo& X, MlProg* P) -> bool {
+    memset(P, 0, sizeof *P);
+    if ((int)X.steps.size() > kMlMaxSteps) return false;
+    P->n = (int)X.steps.size();
+    for (int i = 0; i < P->n; ++i) P->s[i] = X.steps[i];
+    return true;
+  };
+  if (!fill_prog(A, &c.ml_a) || !fill_prog(B, &c.ml_b))
+    HE_FAIL(HE_ERR_UNSUPPORTED, "fused matmul: operand-side chains of more than %d steps are not fused into the mainloop", kMlMaxSteps);
+  plan->ml_b = !B.pure();
 
   // ---- SIMT path: f32 operands (exact f32 products; the precision setting is a minimum,
   // precision.rs:3-9) and 2-byte operands that break the TMA pitch rules
@@ -872,10 +963,10 @@ int32_t plan_fused_matmul_core(he_ctx* ctx, const Graph& g, he_plan** out, int* 
     const char* e = getenv("HE_GEMM_K_SERPENTINE");
     c.k_serpentine = e ? (e[0] == '1') : 1;
   }
-  if (plan->cfg.ml != ML_NONE && plan->cfg.ml != ML_RELU_MASK)
-    HE_FAIL(HE_ERR_UNSUPPORTED, "fused matmul: only the relu(A) * mask mainloop fusion is compiled in");
-  if (plan->cfg.ml != ML_NONE && (An.dtype != HE_BF16 || g.nodes[A.mask].dtype != HE_BF16))
-    HE_FAIL(HE_ERR_UNSUPPORTED, "fused matmul: mainloop fusion needs bf16 A and mask");
+  if (plan->cfg.ml == ML_RELU_MASK && (An.dtype != HE_BF16 || g.nodes[A.mask].dtype != HE_BF16))
+    HE_FAIL(HE_ERR_UNSUPPORTED, "fused matmul: the relu * mask mainloop rewrite needs bf16 A and mask");
+  if (A.mask >= 0 && g.nodes[A.mask].dtype != An.dtype)
+    HE_FAIL(HE_ERR_UNSUPPORTED, "fused matmul: the second tensor of a mainloop fusion must have the operand's dtype");
   // TMA pitch rules (16-byte multiples).  Small problems off the rules run on the SIMT kernel when its
   // epilogues cover the graph; everything else gets a pitch-padded copy of the offending operand.
   const int64_t a_cols = plan->cfg.a_mn ? c.M : c.K, b_cols = plan->cfg.b_mn ? c.N : c.K;
@@ -909,7 +1000,7 @@ int32_t plan_fused_matmul_core(he_ctx* ctx, const Graph& g, he_plan** out, int* 
     // Two SMs per 256 x 256 tile whenever there are at least two row tiles to pair up; the
     // environment switch keeps the single-CTA kernel reachable for comparisons.
     const char* force1 = getenv("HE_GEMM_ONE_CTA");
-    plan->cfg.two_cta = plan->cfg.bn == 256 && c.tiles_m >= 2 && !(force1 && force1[0] == '1');
+    plan->cfg.two_cta = plan->cfg.bn == 256 && c.tiles_m >= 2 && !(force1 && force1[0] == '1') && !plan->ml_b;   // the B rewrite lives in the single-CTA kernel
     if (plan->cfg.two_cta) {
       const int tiles_m2 = (c.M + 255) / 256;
       c.tiles_m = 2 * tiles_m2;                       // partial-sum rows: the odd CTA of the last pair may be empty
@@ -953,6 +1044,7 @@ int32_t plan_fused_matmul_core(he_ctx* ctx, const Graph& g, he_plan** out, int* 
       plan->workspace_bytes = plan->ws_pad_off[side] + (size_t)rows * plan->pad_pitch[side] * 2;
     }
     if (plan->cfg.ml == ML_NONE) return pad_note;
+    if (plan->cfg.ml & ML_GENERIC) return ", generic mainloop rewrite in shared memory";
     const double gemm_us = 2.0 * c.batch * c.M * (double)c.N * c.K / 1.3e9;
     const double bytes = 3.0 * c.batch * c.M * (double)c.K * 2.0;
     const double prepass_us = bytes / 4.5e6 + 5.0;
@@ -1051,6 +1143,7 @@ int32_t plan_fused_matmul_core(he_ctx* ctx, const Graph& g, he_plan** out, int* 
                    in_dt(rr.b1) == in_dt(rr.b2) && dclass(full_dt) == DClass::Float && dclass(in_dt(rr.b1)) == DClass::Float;
       if (rr.e1 >= 0) dt_ok = dt_ok && in_dt(rr.e1) == full_dt && in_dt(rr.e2) == full_dt;
       if (!dt_ok) continue;  // falls through to the interpreter tier
+      if (plan->cfg.ml & ML_GENERIC) HE_FAIL(HE_ERR_UNSUPPORTED, "fused matmul: the README epilogue is compiled with the relu * mask mainloop only");
       if (tier_only) { *tier_only = 2; return HE_OK; }
       plan->kind = EpiKind::C3;
       plan->r3 = rr;

@@ -25,7 +25,21 @@ constexpr int kBK = 64;                       // 64 bf16 = one 128-byte swizzle 
 constexpr int kATileBytes = kBM * kBK * 2;    // 16 KiB
 constexpr int kUmmaK = 16;
 
-enum MainloopKind : int { ML_NONE = 0, ML_RELU = 1, ML_MASK = 2, ML_RELU_MASK = 3 };
+// ML_RELU | ML_MASK is the hand-written relu(A) * mask rewrite on packed bf16 pairs.  ML_GENERIC runs a short
+// program of unary steps and at most one elementwise multiply / add with a second tensor (staged like the mask,
+// ML_MASK then says that tensor exists) on the A tile, and a unary-only program on the B tile (single-CTA kernel).
+enum MainloopKind : int { ML_NONE = 0, ML_RELU = 1, ML_MASK = 2, ML_RELU_MASK = 3, ML_GENERIC = 4, ML_GENERIC_MASK = 6 };
+constexpr int kMlMaxSteps = 6;
+struct MlStep {
+  unsigned char kind;   // 0 unary (op = he_unary_op, imm = constant bits), 1 multiply by the second tensor, 2 add it
+  unsigned char op;
+  unsigned short pad;
+  unsigned imm;
+};
+struct MlProg {
+  int n;
+  MlStep s[kMlMaxSteps];
+};
 enum ActKind : int { ACT_NONE = 0, ACT_RELU = 1, ACT_GELU = 2, ACT_TANH = 3 };
 enum GateKind : int { GATE_NONE = 0, GATE_MUL = 1, GATE_DGELU = 2, GATE_DRELU = 3, GATE_DTANH = 4 };
 
@@ -44,6 +58,7 @@ struct GemmCore {
   unsigned wait_limit_us;
   int withhold_loads;
   int k_serpentine;   // pair kernel: odd tiles of a CTA walk K from the end (L2 reuse between waves)
+  MlProg ml_a, ml_b;  // ML_GENERIC: operand-side programs (ml_b: unary steps only)
   DeviceStatus* status;
 };
 
@@ -207,6 +222,43 @@ __device__ __forceinline__ void warp_colreduce_store(float (&v)[CH], float* dst,
 #pragma unroll
   for (int b = (1 << (5 - kLog)) >> 1; b >= 1; b >>= 1) v[0] = red_combine(v[0], __shfl_xor_sync(0xffffffffu, v[0], b), op);
   if ((lane & ((1 << (5 - kLog)) - 1)) == 0) dst[lane >> (5 - kLog)] = v[0];
+}
+
+// ---- generic mainloop rewrite of one 16-byte vector (8 operand elements) -----------------------------
+// The reference's generator applies the operand-side pointwise chain to register fragments in f32 and casts
+// to the MMA type (helium-kernel-generator/src/generators/matmul/sm80.rs:396-439); here the chain runs on the
+// tile in shared memory between TMA arrival and MMA issue: unpack to f32, steps in order, one rounding back.
+__device__ __forceinline__ void ml_unpack8(const uint4& v, int fmt, float (&x)[8]) {
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    if (fmt == 1) { x[2 * j] = __uint_as_float(w[j] << 16); x[2 * j + 1] = __uint_as_float(w[j] & 0xffff0000u); }
+    else { x[2 * j] = f16_bits_to_f32(w[j] & 0xffffu); x[2 * j + 1] = f16_bits_to_f32(w[j] >> 16); }
+  }
+}
+__device__ __forceinline__ uint4 ml_pack8(const float (&x)[8], int fmt) {
+  uint32_t w[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j)
+    w[j] = fmt == 1 ? f32x2_to_bf16x2(x[2 * j], x[2 * j + 1]) : (f32_to_f16_bits(x[2 * j]) | (f32_to_f16_bits(x[2 * j + 1]) << 16));
+  return make_uint4(w[0], w[1], w[2], w[3]);
+}
+__device__ __forceinline__ void ml_apply8(const MlProg& P, int fmt, uint4& va, const uint4* second) {
+  float x[8], m[8];
+  ml_unpack8(va, fmt, x);
+  if (second) ml_unpack8(*second, fmt, m);
+#pragma unroll 1
+  for (int i = 0; i < P.n; ++i) {
+    const MlStep st = P.s[i];
+    if (st.kind == 0) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) x[j] = pw_unary(st.op, x[j], st.imm);
+    } else if (second) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) x[j] = st.kind == 1 ? x[j] * m[j] : x[j] + m[j];
+    }
+  }
+  va = ml_pack8(x, fmt);
 }
 
 // =================================================================================================
@@ -1051,6 +1103,27 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmParams<typename Epi::Params> p) 
           const uint4* mk = reinterpret_cast<const uint4*>(smem + SM::off_mask + stage * kATileBytes);
           // A and the mask were loaded with the same box and swizzle, so equal smem offsets hold
           // the same (row, k) element: the rewrite is position-wise.
+          if constexpr ((ML & ML_GENERIC) != 0) {
+#pragma unroll 1
+            for (int i = 0; i < kATileBytes / 16 / 128; ++i) {
+              const int idx = tt + i * 128;
+              uint4 va = a[idx];
+              uint4 vm;
+              if (ML & ML_MASK) vm = mk[idx];
+              ml_apply8(c.ml_a, c.ab_format, va, (ML & ML_MASK) ? &vm : nullptr);
+              a[idx] = va;
+            }
+            if (c.ml_b.n > 0) {
+              uint4* b = reinterpret_cast<uint4*>(smem + SM::off_b + stage * SM::kBTileBytes);
+#pragma unroll 1
+              for (int i = 0; i < SM::kBTileBytes / 16 / 128; ++i) {
+                const int idx = tt + i * 128;
+                uint4 vb = b[idx];
+                ml_apply8(c.ml_b, c.ab_format, vb, nullptr);
+                b[idx] = vb;
+              }
+            }
+          } else
 #pragma unroll
           for (int i = 0; i < kATileBytes / 16 / 128; ++i) {
             const int idx = tt + i * 128;

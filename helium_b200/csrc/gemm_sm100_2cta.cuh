@@ -329,6 +329,17 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ GemmParams<typename Epi::Params
           if (!__all_sync(0xffffffffu, ok)) { alive = false; break; }
           uint4* a = reinterpret_cast<uint4*>(smem + SM::off_a + stage * kATileBytes);
           const uint4* mk = reinterpret_cast<const uint4*>(smem + SM::off_mask + stage * kATileBytes);
+          if constexpr ((ML & ML_GENERIC) != 0) {
+#pragma unroll 1
+            for (int i = 0; i < kATileBytes / 16 / 128; ++i) {
+              const int idx = tt + i * 128;
+              uint4 va = a[idx];
+              uint4 vm;
+              if (ML & ML_MASK) vm = mk[idx];
+              ml_apply8(c.ml_a, c.ab_format, va, (ML & ML_MASK) ? &vm : nullptr);
+              a[idx] = va;
+            }
+          } else
 #pragma unroll
           for (int i = 0; i < kATileBytes / 16 / 128; ++i) {
             const int idx = tt + i * 128;

@@ -569,9 +569,10 @@ def test_generic_epilogue_mean_max_min(ctx, m, n, k):
 
 
 def test_operand_side_pointwise_prologues(ctx):
-    """Operand expressions beyond relu * mask (any Constant / Unary / Binary / cast / reshape / swap
-    chain, generators/matmul.rs:234-264) are evaluated once into the workspace by a pointwise plan;
-    the oracle rounds the operand where the pre-pass materialises it."""
+    """Operand expressions the mainloop rewrite does not cover (here: a broadcast vector inside A's expression;
+    any Constant / Unary / Binary / cast / reshape / swap chain is legal, generators/matmul.rs:234-264) are
+    evaluated once into the workspace by a pointwise plan, while B's unary chain is applied in the kernel;
+    the oracle rounds each operand once, where the plan does."""
     m, n, k = 256, 384, 128
     g = ir.Graph()
     x = g.new_input([m, k], ir.BF16); s = g.new_input([k], ir.BF16); y = g.new_input([m, k], ir.BF16)
@@ -582,7 +583,7 @@ def test_operand_side_pointwise_prologues(ctx):
     g.new_output(g.cast(g.unary(ir.UN_RELU, t), ir.BF16))
     ins = _gen(g, 61, {1: 0.5, 3: 1.0})
     plan = hb.Plan.fused_matmul(ctx, g)
-    assert "operand A evaluated by a pre-pass" in plan.description and "operand B evaluated by a pre-pass" in plan.description
+    assert "operand A evaluated by a pre-pass" in plan.description and "generic mainloop rewrite" in plan.description, plan.description
     assert hb.plan_supported(g, 2) == 1
     got, _ = _run(ctx, g, ins)
     mm = [i for i, nd in enumerate(g.nodes) if nd.kind == ir.OP_MATMUL][0]
@@ -596,6 +597,53 @@ def test_operand_side_pointwise_prologues(ctx):
     got, plan = _run(ctx, g, ins)
     assert "SIMT" in plan.description and "pre-pass" in plan.description
     _compare(g, got, O.evaluate(g, ins), plan.description)
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 256, 64), (256, 264, 200), (512, 384, 1024), (1024, 512, 512)])
+def test_generic_mainloop_fusion(ctx, monkeypatch, m, n, k):
+    """Operand-side chains beyond relu * mask applied inside the kernel (the transform warps rewrite the tile in
+    shared memory): unary chains with constants on A, a chain with a second tensor, a chain on B, transposed
+    operands, f16.  The oracle rounds the operand once, where the kernel does."""
+    monkeypatch.setenv("HE_GEMM_MAINLOOP", "fused")
+    cases = []
+    # A = tanh(x) * 0.5 + 0.25
+    g = ir.Graph()
+    x = g.new_input([m, k], ir.BF16); w = g.new_input([k, n], ir.BF16)
+    a = g.unary(ir.UN_ADD_CONST, g.unary(ir.UN_MUL_CONST, g.unary(ir.UN_TANH, x), 0.5), 0.25)
+    g.new_output(g.cast(g.matmul(a, w), ir.BF16))
+    cases.append(("unary chain on A", g))
+    # A = sigmoid(x) + e   (second tensor added), bias + relu epilogue
+    g = ir.Graph()
+    x = g.new_input([m, k], ir.BF16); e = g.new_input([m, k], ir.BF16); w = g.new_input([k, n], ir.BF16); bias = g.new_input([n], ir.BF16)
+    a = g.binary(ir.BIN_ADD, g.unary(ir.UN_SIGMOID, x), e)
+    t = g.binary(ir.BIN_ADD, g.matmul(a, w), g.broadcast_to(bias, [m, n]))
+    g.new_output(g.cast(g.unary(ir.UN_RELU, t), ir.BF16))
+    cases.append(("second tensor on A", g))
+    # A = neg(x) * mk with A stored transposed; B = gelu(w) stored [n, k]
+    g = ir.Graph()
+    x = g.new_input([k, m], ir.BF16); mk = g.new_input([k, m], ir.BF16); w = g.new_input([n, k], ir.BF16)
+    a = g.transpose(g.binary(ir.BIN_MUL, g.unary(ir.UN_NEG, x), mk))
+    b = g.transpose(g.unary(ir.UN_GELU, w))
+    g.new_output(g.matmul(a, b))
+    cases.append(("A and B chains, transposed", g))
+    # f16, B = exp(w * 0.1)
+    g = ir.Graph()
+    x = g.new_input([m, k], ir.F16); w = g.new_input([k, n], ir.F16)
+    b = g.unary(ir.UN_EXP, g.unary(ir.UN_MUL_CONST, w, 0.1))
+    g.new_output(g.cast(g.matmul(x, b, ir.PREC_F16_F32), ir.F16))
+    cases.append(("f16 chain on B", g))
+    for what, g in cases:
+        ins = _gen(g, 33, {i: 0.5 for i in range(4)})
+        plan = hb.Plan.fused_matmul(ctx, g)
+        assert "generic mainloop rewrite" in plan.description and "pre-pass" not in plan.description, (what, plan.description)
+        assert hb.plan_supported(g, 2) == 2
+        got, _ = _run(ctx, g, ins)
+        mm = [i for i, nd in enumerate(g.nodes) if nd.kind == ir.OP_MATMUL][0]
+        want = O.evaluate(g, ins, round_nodes=list(g.nodes[mm].inputs[:2]))
+        _compare(g, got, want, f"{what}: {plan.description}")
+        got2, _ = _run(ctx, g, ins)
+        for p_, q_ in zip(got, got2):
+            assert np.array_equal(p_, q_), what
 
 
 def test_helium_style_bias_gradient_fuses(ctx):

@@ -181,9 +181,15 @@ def test_matmul_refusals():
     plan = hb.Plan.fused_matmul(None, g)
     assert "tcgen05" in plan.description and "A copied to a 16-byte pitch" in plan.description and "B copied" not in plan.description
     assert plan.workspace_bytes >= 128 * 104 * 2
-    # an operand expression the kernels do not apply in their mainloop is evaluated by a pre-pass (tier 1)
+    # an operand expression runs in the kernel's mainloop when its repetition is short (small N here) ...
     g = ir.Graph()
     a = g.new_input([128, 64], ir.BF16); b = g.new_input([64, 256], ir.BF16)
+    g.new_output(g.matmul(g.unary(ir.UN_EXP, a), b))
+    assert hb.plan_supported(g, 2) == 2
+    assert "generic mainloop rewrite" in hb.Plan.fused_matmul(None, g).description
+    # ... and as a pre-pass that writes the operand once when the GEMM is long (tier 1)
+    g = ir.Graph()
+    a = g.new_input([4096, 4096], ir.BF16); b = g.new_input([4096, 4096], ir.BF16)
     g.new_output(g.matmul(g.unary(ir.UN_EXP, a), b))
     assert hb.plan_supported(g, 2) == 1
     assert "operand A evaluated by a pre-pass" in hb.Plan.fused_matmul(None, g).description
