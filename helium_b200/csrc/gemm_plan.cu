@@ -737,9 +737,10 @@ int32_t plan_fused_matmul(he_ctx* ctx, const Graph& g_in, he_plan** out, int* ti
   for (int k = 0; k < M0.rank - 2; ++k) batch0 *= M0.shape[k];
   const char* ml_env = getenv("HE_GEMM_MAINLOOP");
   auto in_kernel_ok = [&](const OperandInfo& X, bool is_a) {
-    if (!X.ok || X.pure() || !A.ok || !B.ok) return false;
+    if (!X.ok || X.pure()) return false;
     const int dt = g.nodes[X.root].dtype;
-    if ((dt != HE_BF16 && dt != HE_F16) || g.nodes[A.root].dtype != g.nodes[B.root].dtype) return false;
+    // both MMA operands must have the stored tensor's 2-byte type (the other one may come out of a pre-pass)
+    if ((dt != HE_BF16 && dt != HE_F16) || g.nodes[M0.in[0]].dtype != dt || g.nodes[M0.in[1]].dtype != dt) return false;
     if (X.mask >= 0 && (g.nodes[X.mask].dtype != dt || !is_a)) return false;
     if ((int)X.steps.size() > kMlMaxSteps) return false;
     if ((A.transposed ? Md : Kd) % 8 != 0 || (B.transposed ? Kd : Nd) % 8 != 0) return false;
