@@ -73,6 +73,10 @@ int32_t make_filter_tmap(CUtensorMap* out, const void* ptr, int ab_format, int K
 // (tw, th, tn) with tw * th * tn = total that cover the grid with the least padding; ties prefer wide rows
 // (longer contiguous runs in memory).
 void choose_patch(int total, int GQ, int GP, int GN, int* tw, int* th, int* tn) {
+  if (const char* e = getenv("HE_CONV_PATCH_TMP")) {
+    int a, b, cc;
+    if (sscanf(e, "%d,%d,%d", &a, &b, &cc) == 3 && a * b * cc == total) { *tw = a; *th = b; *tn = cc; return; }
+  }
   long long best = -1;
   for (int a = total; a >= 1; a >>= 1)          // tw
     for (int b = total / a; b >= 1; b >>= 1) {  // th
@@ -136,11 +140,13 @@ int32_t launch_fprop(const ConvParams& p, int grid, cudaStream_t stream) {
   return HE_OK;
 }
 
-template <int BN>
+template <int BN, int T>
 int32_t launch_wgrad(const ConvWgradParams& p, int grid, cudaStream_t stream) {
-  constexpr int STAGES = 6;
-  using SM = ConvWgradSmem<BN, STAGES>;
-  auto kernel = conv_wgrad_kernel<BN, STAGES>;
+  // stages: as many as fit beside 1 KB of alignment slack (16 KB flow tile + T image tiles per stage)
+  constexpr int STAGES = T == 1 ? 6 : (BN == 64 ? 5 : 3);
+  using SM = ConvWgradSmem<BN, STAGES, T>;
+  static_assert(SM::dynamic_bytes <= 232448, "shared memory budget of sm_100 exceeded");
+  auto kernel = conv_wgrad_kernel<BN, STAGES, T>;
   static bool configured = false;
   if (!configured) {
     HE_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SM::dynamic_bytes));
@@ -172,7 +178,7 @@ struct ConvPlan : he_plan {
   size_t ws_stat_off[2] = {0, 0};
   // filter gradient
   ConvGeom wgeom{};
-  int splits = 1, k_tiles = 0, wgrid = 0;
+  int splits = 1, k_tiles = 0, wgrid = 0, taps_per_cta = 1;
 
   int32_t launch(const void* const* inputs, void* const* outputs, void* workspace, cudaStream_t stream) override {
     for (int i = 0; i < n_in; ++i)
@@ -198,7 +204,9 @@ struct ConvPlan : he_plan {
       p.splits = splits;
       p.k_tiles = k_tiles;
       p.rs = RS;
-      HE_TRY(bn == 64 ? launch_wgrad<64>(p, wgrid, stream) : launch_wgrad<128>(p, wgrid, stream));
+      p.tap_groups = (RS + taps_per_cta - 1) / taps_per_cta;
+      if (taps_per_cta == 3) HE_TRY(bn == 64 ? (launch_wgrad<64, 3>(p, wgrid, stream)) : (launch_wgrad<128, 3>(p, wgrid, stream)));
+      else HE_TRY(bn == 64 ? (launch_wgrad<64, 1>(p, wgrid, stream)) : (launch_wgrad<128, 1>(p, wgrid, stream)));
       const long long n = (long long)Kout * RS * Cin;
       conv_wgrad_fold<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(p.partials, outputs[0], fus.out_dtype, n, splits);
       HE_CUDA(cudaGetLastError());
@@ -337,16 +345,21 @@ int32_t plan_conv2d(he_ctx* ctx, int32_t kind, const he_conv2d_params* prm, int3
         t.tap = (short)(r * S + q);
       }
     plan->k_tiles = g.tiles_q * g.tiles_p * g.tiles_nb;
-    const int items = c.tiles_m * c.tiles_n * g.n_taps;
-    // enough CTAs for two waves, at least 8 pixel tiles each
-    int splits = std::max(1, (2 * sms + items - 1) / items);
+    // up to three taps share a CTA's flow tiles (three image tiles of 128 columns fill the 512 TMEM columns)
+    plan->taps_per_cta = g.n_taps >= 3 ? 3 : 1;
+    const int tap_groups = (g.n_taps + plan->taps_per_cta - 1) / plan->taps_per_cta;
+    const int items = c.tiles_m * c.tiles_n * tap_groups;
+    // one wave of CTAs (one per SM: a CTA's set-up, its f32 tile stores and the fold's reads grow with the
+    // split count), at least 8 pixel tiles each
+    int splits = std::max(1, sms / items);
     splits = std::min(splits, std::max(1, plan->k_tiles / 8));
+    if (const char* e = getenv("HE_CONV_SPLITS_TMP")) splits = atoi(e);
     plan->splits = splits;
     plan->wgrid = items * splits;
     plan->workspace_bytes = (size_t)splits * c.M * R * S * c.N * sizeof(float);
     snprintf(desc, sizeof desc,
-             "conv2d filter gradient: tcgen05 implicit GEMM 128x%dx64, K = %d x %d x %d pixels in patches %dx%dx%d, %d taps x %d splits, grid %d",
-             plan->bn, batch, P, Q, g.tn, g.th, g.tw, g.n_taps, splits, plan->wgrid);
+             "conv2d filter gradient: tcgen05 implicit GEMM 128x%dx64, K = %d x %d x %d pixels in patches %dx%dx%d, %d taps (%d per CTA) x %d splits, grid %d",
+             plan->bn, batch, P, Q, g.tn, g.th, g.tw, g.n_taps, plan->taps_per_cta, splits, plan->wgrid);
     plan->description = desc;
     *out = plan.release();
     return HE_OK;

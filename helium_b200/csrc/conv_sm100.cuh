@@ -15,7 +15,8 @@
 //                       the same kernel with the filter read N-major and mirrored taps; a stride of two
 //                       runs it once per parity class of the input grid)
 //   conv_wgrad_kernel   dw[ko, tap, c] = sum_pix dy[pix, ko] * x[pix + tap, c]                 (filter gradient:
-//                       both operands MN-major, the pixel axis is the contraction and is split over CTAs;
+//                       both operands MN-major, the pixel axis is the contraction and is split over CTAs,
+//                       a CTA multiplies one flow tile with the image tiles of up to three taps;
 //                       f32 partial tiles go to the workspace and are folded in a fixed order)
 //
 // Roles, barriers, bounded waits and the abort path are those of gemm_tcgen05_kernel (gemm_sm100.cuh).
@@ -357,12 +358,14 @@ struct alignas(64) ConvWgradParams {
   ConvGeom geom;          // patch = one K block of 64 pixels; taps = all filter taps
   float* partials;        // [splits][K][R*S][C] f32
   int splits, k_tiles;    // pixel tiles in all, and how many CTAs share them
+  int tap_groups;         // ceil(taps / T): a CTA owns the taps [g * T, g * T + T)
   int rs;                 // R * S
 };
 
-template <int BN, int STAGES>
+template <int BN, int STAGES, int T>
 struct ConvWgradSmem {
-  static constexpr int kBTileBytes = BN * kBK * 2;
+  static constexpr int kBTapBytes = BN * kBK * 2;          // one tap's image tile
+  static constexpr int kBTileBytes = T * kBTapBytes;
   static constexpr int off_a = 0;
   static constexpr int off_b = off_a + STAGES * kATileBytes;
   static constexpr int off_bar = off_b + STAGES * kBTileBytes;
@@ -372,11 +375,15 @@ struct ConvWgradSmem {
   static constexpr int dynamic_bytes = total + 1024;
 };
 
-// One CTA = one (output tile, tap, split): it contracts its share of the pixel tiles and writes one f32 tile.
-template <int BN, int STAGES>
+// One CTA = one (output tile, group of T taps, split): it contracts its share of the pixel tiles and writes
+// one f32 tile per tap.  The flow tile of a pixel block is fetched once and multiplied with the T shifted image
+// tiles of the group, each tap into its own TMEM columns: what bounds these kernels is the rate at which TMA
+// fills shared memory, and sharing the flow tile cuts the bytes per tap from (128 + BN) to (128 / T + BN) rows.
+template <int BN, int STAGES, int T>
 __global__ void __launch_bounds__(32 * 6, 1) conv_wgrad_kernel(const __grid_constant__ ConvWgradParams p) {
-  using SM = ConvWgradSmem<BN, STAGES>;
-  constexpr int kTmemCols = BN <= 64 ? 64 : 128;
+  using SM = ConvWgradSmem<BN, STAGES, T>;
+  constexpr int kTmemCols = T * BN <= 64 ? 64 : T * BN <= 128 ? 128 : T * BN <= 256 ? 256 : 512;
+  static_assert(T * BN <= 512, "the taps of a group share the 512 TMEM columns");
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   const uint32_t smem_base = ptx::smem_u32(smem);
@@ -394,13 +401,14 @@ __global__ void __launch_bounds__(32 * 6, 1) conv_wgrad_kernel(const __grid_cons
   // work item
   int item = blockIdx.x;
   const int split = item % p.splits; item /= p.splits;
-  const int ti = item % g.n_taps; item /= g.n_taps;
+  const int tg = item % p.tap_groups; item /= p.tap_groups;
   const int tile_n = item % c.tiles_n;
   const int tile_m = item / c.tiles_n;
   const int m0 = tile_m * kBM, n0 = tile_n * BN;
   const int kt_begin = (int)(((long long)p.k_tiles * split) / p.splits);
   const int kt_end = (int)(((long long)p.k_tiles * (split + 1)) / p.splits);
-  const ConvTap tp = g.taps[ti];
+  const int tap0 = tg * T;
+  const int nt = min(T, g.n_taps - tap0);   // taps of this group (the last group may be short)
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
@@ -413,7 +421,7 @@ __global__ void __launch_bounds__(32 * 6, 1) conv_wgrad_kernel(const __grid_cons
   }
   if (warp == 0 && lane == 0) {
     ptx::prefetch_tmap(&p.tma_dy);
-    ptx::prefetch_tmap(&p.tma_x[tp.map]);
+    for (int t = 0; t < nt; ++t) ptx::prefetch_tmap(&p.tma_x[g.taps[tap0 + t].map]);
   }
   if (warp == 1) {
     ptx::tmem_alloc(ptx::smem_u32(const_cast<uint32_t*>(tmem_holder)), kTmemCols);
@@ -426,12 +434,12 @@ __global__ void __launch_bounds__(32 * 6, 1) conv_wgrad_kernel(const __grid_cons
 
   if (warp == 0) {
     if (lane == 0 && !c.withhold_loads) {
-      constexpr uint32_t kStageBytes = kATileBytes + SM::kBTileBytes;
+      const uint32_t stage_bytes = kATileBytes + (uint32_t)nt * SM::kBTapBytes;
       int stage = 0;
       uint32_t phase = 0;
       for (int kt = kt_begin; kt < kt_end; ++kt) {
         if (!ptx::mbar_wait(bar_empty(stage), phase ^ 1u, abort_flag, c.status, 1, stage, c.wait_limit_us)) break;
-        ptx::mbar_arrive_expect_tx(bar_full(stage), kStageBytes);
+        ptx::mbar_arrive_expect_tx(bar_full(stage), stage_bytes);
         int m = kt;
         const int qi = m % g.tiles_q; m /= g.tiles_q;
         const int pi = m % g.tiles_p; m /= g.tiles_p;
@@ -441,10 +449,14 @@ __global__ void __launch_bounds__(32 * 6, 1) conv_wgrad_kernel(const __grid_cons
         // A = flow^T: 64 pixels (contraction) x 128 output channels, as two boxes of 64 channels
 #pragma unroll
         for (int j = 0; j < kBM / 64; ++j) tma_load_4d(a_dst + j * (kBK * 128), &p.tma_dy, bar_full(stage), m0 + 64 * j, q0, p0, nb0);
-        // B = image shifted by the tap: 64 pixels x BN input channels
+        // B = the image shifted by each tap of the group: 64 pixels x BN input channels per tap
+        for (int t = 0; t < nt; ++t) {
+          const ConvTap tp = g.taps[tap0 + t];
 #pragma unroll
-        for (int j = 0; j < BN / 64; ++j)
-          tma_load_4d(b_dst + j * (kBK * 128), &p.tma_x[tp.map], bar_full(stage), n0 + 64 * j, q0 + tp.dw, p0 + tp.dh, nb0);
+          for (int j = 0; j < BN / 64; ++j)
+            tma_load_4d(b_dst + t * SM::kBTapBytes + j * (kBK * 128), &p.tma_x[tp.map], bar_full(stage), n0 + 64 * j, q0 + tp.dw,
+                        p0 + tp.dh, nb0);
+        }
         if (++stage == STAGES) { stage = 0; phase ^= 1u; }
       }
     }
@@ -459,11 +471,13 @@ __global__ void __launch_bounds__(32 * 6, 1) conv_wgrad_kernel(const __grid_cons
         ptx::tcgen05_fence_after();
         const uint32_t a_addr = smem_base + SM::off_a + stage * kATileBytes;
         const uint32_t b_addr = smem_base + SM::off_b + stage * SM::kBTileBytes;
+        for (int t = 0; t < nt; ++t) {
 #pragma unroll
-        for (int k = 0; k < kBK / kUmmaK; ++k) {
-          const uint64_t adesc = ptx::make_smem_desc_sw128(a_addr + k * 2048, kBK * 128, 1024);
-          const uint64_t bdesc = ptx::make_smem_desc_sw128(b_addr + k * 2048, kBK * 128, 1024);
-          ptx::umma_f16(tmem_base, adesc, bdesc, idesc, (kt > kt_begin || k != 0) ? 1u : 0u);
+          for (int k = 0; k < kBK / kUmmaK; ++k) {
+            const uint64_t adesc = ptx::make_smem_desc_sw128(a_addr + k * 2048, kBK * 128, 1024);
+            const uint64_t bdesc = ptx::make_smem_desc_sw128(b_addr + t * SM::kBTapBytes + k * 2048, kBK * 128, 1024);
+            ptx::umma_f16(tmem_base + (uint32_t)(t * BN), adesc, bdesc, idesc, (kt > kt_begin || k != 0) ? 1u : 0u);
+          }
         }
         ptx::umma_commit(bar_empty(stage));
         if (++stage == STAGES) { stage = 0; phase ^= 1u; }
@@ -471,7 +485,7 @@ __global__ void __launch_bounds__(32 * 6, 1) conv_wgrad_kernel(const __grid_cons
       if (alive) ptx::umma_commit(bar_done);
     }
   } else {
-    // four epilogue warps: rows = output channels of the filter, columns = input channels
+    // four epilogue warps: rows = output channels of the filter, columns = input channels of one tap
     const int quadrant = warp & 3;
     const int row = quadrant * 32 + lane;
     const int ko = m0 + row;
@@ -479,22 +493,30 @@ __global__ void __launch_bounds__(32 * 6, 1) conv_wgrad_kernel(const __grid_cons
     if (ok) ok = ptx::mbar_wait(bar_done, 0, abort_flag, c.status, 4, 0, c.wait_limit_us);
     ok = __all_sync(0xffffffffu, ok);
     ptx::tcgen05_fence_after();
-    float* dst = p.partials + (((size_t)split * c.M + ko) * p.rs + tp.tap) * c.N + n0;
+    const bool vec = (c.N & 3) == 0;   // a lane's 32 columns are then eight aligned 16-byte words
+    for (int t = 0; t < nt; ++t) {
+      float* dst = p.partials + (((size_t)split * c.M + ko) * p.rs + g.taps[tap0 + t].tap) * c.N + n0;
 #pragma unroll 1
-    for (int col = 0; col < BN; col += 32) {
-      if (n0 + col >= c.N) break;
-      float v[32];
-      if (ok) {
-        tmem_ld_chunk<32>(tmem_base + ((uint32_t)(quadrant * 32) << 16) + (uint32_t)col, v);
-      } else {
+      for (int col = 0; col < BN; col += 32) {
+        if (n0 + col >= c.N) break;
+        float v[32];
+        if (ok) {
+          tmem_ld_chunk<32>(tmem_base + ((uint32_t)(quadrant * 32) << 16) + (uint32_t)(t * BN + col), v);
+        } else {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) v[i] = 0.0f;   // an empty share of the pixel tiles contributes zeros
-      }
-      if (ko < c.M) {
-        const int nvalid = min(32, c.N - (n0 + col));
+          for (int i = 0; i < 32; ++i) v[i] = 0.0f;   // an empty share of the pixel tiles contributes zeros
+        }
+        if (ko < c.M) {
+          const int nvalid = min(32, c.N - (n0 + col));
+          if (vec && nvalid == 32) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i)
-          if (i < nvalid) dst[col + i] = v[i];
+            for (int i = 0; i < 32; i += 4) *reinterpret_cast<float4*>(dst + col + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (i < nvalid) dst[col + i] = v[i];
+          }
+        }
       }
     }
     ptx::tcgen05_fence_before();
