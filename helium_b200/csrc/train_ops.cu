@@ -338,45 +338,55 @@ __global__ void __launch_bounds__(256) pool_softmax_ce_kernel(const unsigned sho
 // is read by R * S / st^2 outputs).  Used for convolutions whose channel count is too small to feed the tensor
 // core from the NHWC tensor directly (an RGB stem): the explicit patch matrix then goes through the same
 // convolution kernels as a 1 x 1 convolution over `pitch` channels.
-// A CTA produces the patch rows of `kImQ` consecutive output pixels of one output row: the R source rows they read
-// are staged in shared memory with coalesced loads, then every thread assembles 16-byte output vectors from
-// 2-byte shared-memory reads and stores them coalesced.
-constexpr int kImQ = 32;
+// A CTA produces the patch rows of `imq` consecutive output pixels of one output row: the R source rows they read
+// are staged in shared memory with coalesced loads; then thread (group g, vector v) assembles vector v of pixels
+// g, g + groups, ... from eight 2-byte shared-memory reads whose offsets inside the staged rows it computed once
+// for the whole kernel (they depend on v only; a pixel step is a constant shift), and stores 16 bytes.  A warp's
+// stores cover consecutive vectors of consecutive pixels, i.e. one contiguous stretch of the patch matrix.
 __global__ void __launch_bounds__(256) im2col_kernel(const unsigned short* __restrict__ x, uint4* __restrict__ cols, int NB, int H, int W,
-                                                     int C, int R, int S, int st, int pad_h, int pad_w, int P, int Q, int pitch) {
-  extern __shared__ unsigned short srow[];   // [R][span * C], span = (kImQ - 1) * st + S source pixels
-  const int span = (kImQ - 1) * st + S;
-  const int q_tiles = (Q + kImQ - 1) / kImQ;
+                                                     int C, int R, int S, int st, int pad_h, int pad_w, int P, int Q, int pitch, int imq) {
+  extern __shared__ unsigned short srow[];   // [R][span * C], span = (imq - 1) * st + S source pixels
+  const int span = (imq - 1) * st + S;
+  const int row_pitch = span * C;
+  const int q_tiles = (Q + imq - 1) / imq;
   const int vec_per_pix = pitch >> 3;
+  const int groups = 256 / vec_per_pix;
+  const int v = threadIdx.x % vec_per_pix, grp = threadIdx.x / vec_per_pix;
   const int rsc = R * S * C, sc = S * C;
+  int off[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const int k = v * 8 + j;
+    const int r = k / sc;                         // k - r * sc = s * C + c: contiguous in the source row
+    off[j] = k < rsc ? r * row_pitch + (k - r * sc) : -1;
+  }
+  const int pix_step = st * C;
   for (long long tile = blockIdx.x; tile < (long long)NB * P * q_tiles; tile += gridDim.x) {
     const int qt = (int)(tile % q_tiles);
     const long long np = tile / q_tiles;
     const int p = (int)(np % P), n = (int)(np / P);
-    const int q0 = qt * kImQ, w0 = q0 * st - pad_w;
+    const int q0 = qt * imq, w0 = q0 * st - pad_w;
     __syncthreads();   // the previous tile's readers are done
-    for (int i = threadIdx.x; i < R * span * C; i += 256) {
-      const int r = i / (span * C), rem = i - r * (span * C);
-      const int w = w0 + rem / C, h = p * st + r - pad_h;
-      srow[i] = (h >= 0 && h < H && w >= 0 && w < W) ? __ldg(x + (((long long)n * H + h) * W + w0) * C + rem) : (unsigned short)0;
+    for (int r = 0; r < R; ++r) {
+      const int h = p * st + r - pad_h;
+      const bool row_ok = h >= 0 && h < H;
+      const unsigned short* src = x + (((long long)n * H + h) * W + w0) * C;
+      for (int e = threadIdx.x; e < row_pitch; e += 256) {
+        const int w = w0 + e / C;
+        srow[r * row_pitch + e] = (row_ok && w >= 0 && w < W) ? __ldg(src + e) : (unsigned short)0;
+      }
     }
     __syncthreads();
-    const int nq = min(kImQ, Q - q0);
-    for (int i = threadIdx.x; i < nq * vec_per_pix; i += 256) {
-      const int ql = i / vec_per_pix, v = i - ql * vec_per_pix;
-      uint32_t e[8];
+    const int nq = min(imq, Q - q0);
+    if (grp < groups) {
+      uint4* dst = cols + (((size_t)n * P + p) * Q + q0) * vec_per_pix + v;
+      for (int ql = grp; ql < nq; ql += groups) {
+        const unsigned short* sp = srow + ql * pix_step;
+        uint32_t e[8];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const int k = v * 8 + j;
-        uint32_t val = 0;
-        if (k < rsc) {
-          const int r = k / sc, kk = k - r * sc;           // kk = s * C + c: contiguous in the source row
-          val = srow[r * span * C + ql * st * C + kk];
-        }
-        e[j] = val;
+        for (int j = 0; j < 8; ++j) e[j] = off[j] >= 0 ? (uint32_t)sp[off[j]] : 0u;
+        dst[(size_t)ql * vec_per_pix] = make_uint4(e[0] | (e[1] << 16), e[2] | (e[3] << 16), e[4] | (e[5] << 16), e[6] | (e[7] << 16));
       }
-      cols[(((size_t)n * P + p) * Q + q0 + ql) * vec_per_pix + v] =
-          make_uint4(e[0] | (e[1] << 16), e[2] | (e[3] << 16), e[4] | (e[5] << 16), e[6] | (e[7] << 16));
     }
   }
 }
@@ -524,12 +534,17 @@ int32_t he_im2col_nhwc(const void* x, void* cols, int32_t batch, int32_t in_h, i
   if (pitch % 8 != 0 || pitch < kernel_h * kernel_w * channels) HE_FAIL(HE_ERR_INVALID, "he_im2col_nhwc: pitch must be a multiple of 8 and at least R*S*C = %d", kernel_h * kernel_w * channels);
   if ((uintptr_t)cols & 15) HE_FAIL(HE_ERR_UNSUPPORTED, "he_im2col_nhwc: the patch matrix must be 16-byte aligned");
   const int P = in_h / stride, Q = in_w / stride;   // 'Same' geometry: helium-ir/src/opgraph/op/conv.rs:51-74
-  const long long tiles = (long long)batch * P * ((Q + kImQ - 1) / kImQ);
-  const unsigned grid = (unsigned)std::min<long long>(tiles, 148 * 16);
-  const size_t smem = (size_t)kernel_h * ((kImQ - 1) * stride + kernel_w) * channels * sizeof(unsigned short);
+  if (pitch > 2048) HE_FAIL(HE_ERR_UNSUPPORTED, "he_im2col_nhwc: pitch above 2048 columns");
+  // pixels per CTA tile: a whole output row if its source rows fit 48 KB of staging, else the largest power of two
+  auto staging = [&](int q) { return (size_t)kernel_h * ((q - 1) * stride + kernel_w) * channels * sizeof(unsigned short); };
+  int imq = 128;
+  while (imq > 1 && (imq / 2 >= Q || staging(imq) > 48 * 1024)) imq >>= 1;
+  const size_t smem = staging(imq);
   if (smem > 48 * 1024) HE_FAIL(HE_ERR_UNSUPPORTED, "he_im2col_nhwc: %zu bytes of staging exceed 48 KB (channel count too large for this route)", smem);
+  const long long tiles = (long long)batch * P * ((Q + imq - 1) / imq);
+  const unsigned grid = (unsigned)std::min<long long>(tiles, 148 * 8);
   im2col_kernel<<<grid, 256, smem, (cudaStream_t)cu_stream>>>(reinterpret_cast<const unsigned short*>(x), reinterpret_cast<uint4*>(cols), batch,
-                                                          in_h, in_w, channels, kernel_h, kernel_w, stride, kernel_h / 2, kernel_w / 2, P, Q, pitch);
+                                                          in_h, in_w, channels, kernel_h, kernel_w, stride, kernel_h / 2, kernel_w / 2, P, Q, pitch, imq);
   HE_CUDA(cudaGetLastError());
   return HE_OK;
 }
