@@ -73,10 +73,6 @@ int32_t make_filter_tmap(CUtensorMap* out, const void* ptr, int ab_format, int K
 // (tw, th, tn) with tw * th * tn = total that cover the grid with the least padding; ties prefer wide rows
 // (longer contiguous runs in memory).
 void choose_patch(int total, int GQ, int GP, int GN, int* tw, int* th, int* tn) {
-  if (const char* e = getenv("HE_CONV_PATCH_TMP")) {
-    int a, b, cc;
-    if (sscanf(e, "%d,%d,%d", &a, &b, &cc) == 3 && a * b * cc == total) { *tw = a; *th = b; *tn = cc; return; }
-  }
   long long best = -1;
   for (int a = total; a >= 1; a >>= 1)          // tw
     for (int b = total / a; b >= 1; b >>= 1) {  // th
@@ -353,7 +349,6 @@ int32_t plan_conv2d(he_ctx* ctx, int32_t kind, const he_conv2d_params* prm, int3
     // split count), at least 8 pixel tiles each
     int splits = std::max(1, sms / items);
     splits = std::min(splits, std::max(1, plan->k_tiles / 8));
-    if (const char* e = getenv("HE_CONV_SPLITS_TMP")) splits = atoi(e);
     plan->splits = splits;
     plan->wgrid = items * splits;
     plan->workspace_bytes = (size_t)splits * c.M * R * S * c.N * sizeof(float);
