@@ -608,13 +608,15 @@ class WorkloadC4Graph(_GemmBase):
 
 class WorkloadPointwise:
     """Stand-alone pointwise programs on tensors larger than L2 (the P1 row of the hot path): three short dense
-    programs served by hand-written kernels and one longer program served by the register-program interpreter."""
+    programs served by hand-written kernels, two longer programs served by kernels specialised at plan time (one
+    with a row-vector broadcast), and the first of those again on the register-program interpreter."""
     key = "pw"
     metric, unit = "pointwise_hbm_gbs", "GB/s"
     dtype = "bf16 / f32 storage, f32 arithmetic"
     N = 8192 * 8192
     description = ("stand-alone pointwise programs on 64 Mi-element tensors: relu(a)*m (bf16), a+b (f32), w-0.01*g (f32) on the dense "
-                   "elementwise kernels; gelu(a+b)*c (bf16) on the interpreter")
+                   "elementwise kernels; gelu(a+b)*c (bf16) and tanh(x+bias[col]) (f32, [8192,8192]) on plan-time specialised kernels; "
+                   "gelu(a+b)*c once more on the interpreter")
     l2_note = "every tensor is 128 MiB (bf16) or 256 MiB (f32): larger than L2"
     work_scale = 1e9
 
@@ -627,12 +629,23 @@ class WorkloadPointwise:
         td = {ir.BF16: torch.bfloat16, ir.F32: torch.float32}
         gen = torch.Generator(device=dev).manual_seed(6)
 
-        def case(name, dts, build):
+        def case(name, dts, build, shapes=None, interpreter=False):
             g = ir.Graph()
-            ins = [g.new_input([n], d) for d in dts]
+            shapes = shapes or [[n]] * len(dts)
+            ins = [g.new_input(list(sh), d) for sh, d in zip(shapes, dts)]
             g.new_output(build(g, ins))
-            plan = hb.Plan.pointwise(ctx, g)
-            tin = [torch.randn(n, generator=gen, device=dev).to(td[d]) for d in dts]
+            saved = os.environ.get("HE_PW_JIT")
+            if interpreter:
+                os.environ["HE_PW_JIT"] = "0"     # read when the plan is made
+            try:
+                plan = hb.Plan.pointwise(ctx, g)
+            finally:
+                if interpreter:
+                    if saved is None:
+                        del os.environ["HE_PW_JIT"]
+                    else:
+                        os.environ["HE_PW_JIT"] = saved
+            tin = [torch.randn(*sh, generator=gen, device=dev).to(td[d]) for sh, d in zip(shapes, dts)]
             tout = plan.alloc_outputs(dev)
             nbytes = sum(t.numel() * t.element_size() for t in tin + tout)
             return name, plan, tin, tout, nbytes
@@ -641,8 +654,12 @@ class WorkloadPointwise:
             case("relu_mul_bf16", [ir.BF16, ir.BF16], lambda g, i: g.binary(ir.BIN_MUL, g.unary(ir.UN_RELU, i[0]), i[1])),
             case("add_f32", [ir.F32, ir.F32], lambda g, i: g.binary(ir.BIN_ADD, i[0], i[1])),
             case("sgd_f32", [ir.F32, ir.F32], lambda g, i: g.binary(ir.BIN_ADD, i[0], g.unary(ir.UN_NEG, g.binary(ir.BIN_MUL, i[1], g.constant(0.01, [n]))))),
-            case("gelu_add_mul_bf16_interpreter", [ir.BF16, ir.BF16, ir.BF16],
+            case("gelu_add_mul_bf16_specialised", [ir.BF16, ir.BF16, ir.BF16],
                  lambda g, i: g.binary(ir.BIN_MUL, g.unary(ir.UN_GELU, g.binary(ir.BIN_ADD, i[0], i[1])), i[2])),
+            case("bias_tanh_f32_specialised", [ir.F32, ir.F32],
+                 lambda g, i: g.unary(ir.UN_TANH, g.binary(ir.BIN_ADD, i[0], g.broadcast_to(i[1], [8192, 8192]))), shapes=[[8192, 8192], [8192]]),
+            case("gelu_add_mul_bf16_interpreter", [ir.BF16, ir.BF16, ir.BF16],
+                 lambda g, i: g.binary(ir.BIN_MUL, g.unary(ir.UN_GELU, g.binary(ir.BIN_ADD, i[0], i[1])), i[2]), interpreter=True),
         ]
         # the allocation-free trailing-dims Sum (he_reduce_sum_f32_noalloc): 16 groups of 4 Mi f32 elements
         from helium_b200._lib import check, lib as _lib

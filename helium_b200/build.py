@@ -27,7 +27,7 @@ SOURCES = [
     "permute.cu",
     "pointwise_compile.cu",
     "pointwise.cu",
-    "pointwise_dense.cu",
+    "pointwise_dense.cu", "pointwise_jit.cu",
     "gemm_plan.cu",
     "gemm_kernels_flex.cu",
     "gemm_kernels_c3.cu",

@@ -265,9 +265,10 @@ class ConvNet:
                               stats_out.data_ptr() if stats_out is not None else None, self._ws_ptr(), self._st()))
         self.launches += 1 + (1 if stats_out is not None else 0)
 
-    def _bn_backward(self, name, g, x, out, gamma_name, second=False, addend=None, mask=None):
+    def _bn_backward(self, name, g, x, out, gamma_name, second=False, addend=None, mask=None, colsum_to=None):
         """dx = A g + B x + K (+ addend) from the sums in bns[name].bstats; writes dgamma / dbeta into the gradient
-        buffers (the second application of a shared norm goes to the second buffer)."""
+        buffers (the second application of a shared norm goes to the second buffer).  `colsum_to` receives the
+        column sums of `out`: the bias gradient of the convolution that `out` flows into next."""
         b = self.bns[name]
         c = x.shape[-1]
         pixels = x.numel() // c
@@ -277,8 +278,9 @@ class ConvNet:
                                         GV[gamma_name + ".g"].data_ptr(), GV[gamma_name + ".b"].data_ptr(), c, self._st()))
         if mask is None:
             check(lib.he_bn_backward_apply(g.data_ptr(), x.data_ptr(), addend.data_ptr() if addend is not None else None, out.data_ptr(),
-                                           b.coef.data_ptr(), None, None, None, None, None, pixels, c, self._st()))
-            self.launches += 2
+                                           b.coef.data_ptr(), None, None, None, colsum_to.data_ptr() if colsum_to is not None else None,
+                                           self._ws_ptr() if colsum_to is not None else None, pixels, c, self._st()))
+            self.launches += 2 + (1 if colsum_to is not None else 0)
         else:
             mx, mb = mask   # (tensor, _Bn whose scale / shift define the rectifier) ; statistics go to that norm's bstats
             check(lib.he_bn_backward_apply(g.data_ptr(), x.data_ptr(), addend.data_ptr() if addend is not None else None, out.data_ptr(),
@@ -339,37 +341,34 @@ class ConvNet:
         self._colsum(A["dy"], GV["tail.b"])
         tb = B["tail_bn"]
         self._launch("tail.dgrad", [A["dy"], W["tail.w"], x, tb.scale, tb.shift], [A["tail.g"], tb.bstats])
-        self._bn_backward("tail_bn", A["tail.g"], x, A["dlast"], "tail_bn")
+        self._bn_backward("tail_bn", A["tail.g"], x, A["dlast"], "tail_bn", colsum_to=GV[f"seg{self.blocks[-1][0]}.basic.conv2.b"])
         dout = A["dlast"]
         for (i, c, o, s, s2) in reversed(self.blocks):
             p, q = f"seg{i}.down", f"seg{i}.basic"
             xin = A[p + ".out"]
             # ---- basic block: out = conv2(relu(bn2(conv1(relu(bn1(xin)))))) + xin
+            # (the bias gradients, column sums of each flow, come out of the pass that produced the flow)
             self._launch(q + ".conv2.wgrad", [dout, A[q + ".a2"]], [GW[q + ".conv2.w"]])
-            self._colsum(dout, GV[q + ".conv2.b"])
             b2 = B[q + ".bn2"]
             self._launch(q + ".conv2.dgrad", [dout, W[q + ".conv2.w"], A[q + ".c1"], b2.scale, b2.shift], [A[q + ".g"], b2.bstats])
-            self._bn_backward(q + ".bn2", A[q + ".g"], A[q + ".c1"], A[q + ".gx"], q + ".bn2")        # gradient at c1
+            self._bn_backward(q + ".bn2", A[q + ".g"], A[q + ".c1"], A[q + ".gx"], q + ".bn2", colsum_to=GV[q + ".conv1.b"])   # gradient at c1
             dc1 = A[q + ".gx"]
             self._launch(q + ".conv1.wgrad", [dc1, A[q + ".a"]], [GW[q + ".conv1.w"]])
-            self._colsum(dc1, GV[q + ".conv1.b"])
             b1 = B[q + ".bn1"]
             self._launch(q + ".conv1.dgrad", [dc1, W[q + ".conv1.w"], xin, b1.scale, b1.shift], [A[q + ".g"], b1.bstats])
-            self._bn_backward(q + ".bn1", A[q + ".g"], xin, A[p + ".g"], q + ".bn1", addend=dout)       # gradient at xin (+ the skip)
+            self._bn_backward(q + ".bn1", A[q + ".g"], xin, A[p + ".g"], q + ".bn1", addend=dout, colsum_to=GV[p + ".conv2.b"])   # gradient at xin (+ the skip)
             dout = A[p + ".g"]
             # ---- downsample block: out = conv2(relu(bn2(conv1(relu(bn1(a)))))) + sc(a),  a = relu(bn1(x))
             xprev = A["h"] if i == 0 else A[f"seg{i - 1}.basic.out"]
             self._launch(p + ".conv2.wgrad", [dout, A[p + ".a3"]], [GW[p + ".conv2.w"]])
-            self._colsum(dout, GV[p + ".conv2.b"])
             self.torch_copy(GV[p + ".sc.b"], GV[p + ".conv2.b"])       # both biases see the same flow
             self._launch(p + ".sc.wgrad", [dout, A[p + ".a"]], [GW[p + ".sc.w"]])
             self._launch(p + ".sc.dgrad", [dout, W[p + ".sc.w"]], [A[p + ".dsc"]])
             b2 = B[p + ".bn2"]
             self._launch(p + ".conv2.dgrad", [dout, W[p + ".conv2.w"], A[p + ".c1"], b2.scale, b2.shift], [A[q + ".g"], b2.bstats])
-            self._bn_backward(p + ".bn2", A[q + ".g"], A[p + ".c1"], A[q + ".gx"], p + ".bn2")        # gradient at c1
+            self._bn_backward(p + ".bn2", A[q + ".g"], A[p + ".c1"], A[q + ".gx"], p + ".bn2", colsum_to=GV[p + ".conv1.b"])   # gradient at c1
             dc1 = A[q + ".gx"]
             self._launch(p + ".conv1.wgrad", [dc1, A[p + ".a2"]], [GW[p + ".conv1.w"]])
-            self._colsum(dc1, GV[p + ".conv1.b"])
             b12, b11 = B[p + ".bn1#2"], B[p + ".bn1"]
             self._launch(p + ".conv1.dgrad", [dc1, W[p + ".conv1.w"], A[p + ".a"], b12.scale, b12.shift], [A[p + ".ga"], b12.bstats])
             # second application of bn1 (on a), plus the shortcut's gradient, masked by the first rectifier
@@ -384,14 +383,13 @@ class ConvNet:
                 self.launches += 1
                 # the head still needs the gradient at its output
                 check(lib.he_bn_backward_apply(A[p + ".gx"].data_ptr(), xprev.data_ptr(), None, A[p + ".ga"].data_ptr(), b.coef.data_ptr(),
-                                               None, None, None, None, None, xprev.numel() // c, c, self._st()))
-                self.launches += 1
+                                               None, None, None, GV["head.b"].data_ptr(), self._ws_ptr(), xprev.numel() // c, c, self._st()))
+                self.launches += 2
                 dout = A[p + ".ga"]
             else:
-                self._bn_backward(p + ".bn1", A[p + ".gx"], xprev, A[p + ".ga"], p + ".bn1")
+                self._bn_backward(p + ".bn1", A[p + ".gx"], xprev, A[p + ".ga"], p + ".bn1", colsum_to=GV[f"seg{i - 1}.basic.conv2.b"])
                 dout = A[p + ".ga"]
         self._launch("head.wgrad", [dout, A["cols"]], [GW["head.w"]])
-        self._colsum(dout, GV["head.b"])
 
     def torch_copy(self, dst, src):
         """Device-to-device copy of a small parameter-gradient vector (a cudaMemcpyAsync on the current stream)."""

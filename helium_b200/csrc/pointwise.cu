@@ -15,6 +15,7 @@
 // folds them in index order (the reference's float atomics are order-dependent).
 #include "permute.cuh"
 #include "pointwise_interp.cuh"
+#include "pointwise_jit.h"
 #include "pointwise_dense.cuh"
 
 #include <algorithm>
@@ -144,6 +145,14 @@ __global__ void __launch_bounds__(kPwThreads) pw_reduce_finalize_kernel(const __
 }
 
 namespace {
+// HE_PW_JIT=0 keeps every program outside the catalogue on the interpreter (A/B measurements, parity tests)
+bool jit_enabled() {
+  const char* e = getenv("HE_PW_JIT");
+  return !(e && e[0] == '0');
+}
+}  // namespace
+
+namespace {
 
 struct PointwisePlan : he_plan {
   PwCompiled c;
@@ -160,6 +169,8 @@ struct PointwisePlan : he_plan {
   bool reduce = false;
   PwReduceLaunch rl{};
   int n_inputs = 0, n_outputs = 0;
+  // elementwise programs outside the catalogue: the program printed as CUDA C and compiled at plan time
+  std::shared_ptr<PwJitModule> jit;
 
   int32_t launch(const void* const* inputs, void* const* outputs, void* workspace, cudaStream_t stream) override {
     PwProgram P = c.prog;
@@ -185,6 +196,11 @@ struct PointwisePlan : he_plan {
         last_launches = 1;
         return HE_OK;
       }
+    }
+    if (!reduce && jit && pw_jit_pointers_ok(c, P)) {
+      HE_TRY(pw_jit_launch(*jit, P, ctx_sm_count(ctx), stream));
+      last_launches = 1;
+      return HE_OK;
     }
     if (!reduce) {
       if (c.has_bool_io) {
@@ -580,6 +596,14 @@ int32_t plan_pointwise(he_ctx* ctx, const Graph& g_in, he_plan** out, int* tier_
   } else if (plan->ew.kind >= 0) {
     snprintf(desc, sizeof desc, "pointwise tier 2 (dense elementwise kernel %s, 16-byte vectors; interpreter fallback for unaligned tensors)",
              plan->ew.name);
+  } else if (jit_enabled() && !plan->c.has_bool_io && [&] {
+               const std::string saved = he_last_error_string();
+               const bool ok = pw_jit_compile(plan->c, &plan->jit) == HE_OK;
+               if (!ok) set_error("%s", saved.c_str());
+               return ok;
+             }()) {
+    snprintf(desc, sizeof desc, "pointwise tier 1 (program of %d instr specialised at plan time with NVRTC, 8 elems/thread, 16-byte vectors; "
+             "interpreter fallback for unaligned tensors)", P.n_instr);
   } else {
     snprintf(desc, sizeof desc, "pointwise tier 1 (interpreter, %d instr, %d regs, %d elems/thread)", P.n_instr,
              plan->c.n_regs, plan->c.has_bool_io ? 1 : 4);

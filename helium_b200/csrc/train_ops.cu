@@ -146,7 +146,7 @@ __global__ void bn_backward_coeffs_kernel(const float* __restrict__ stats, float
 // out = A[c] g + B[c] x + K[c] (+ e) on [pixels, C] bf16; with MASK the result is additionally zeroed where
 // mx * ms[c] + mb[c] <= 0 (the rectifier in front of an enclosing normalisation) and the sums of out and
 // out * mx per channel are produced like in bn_apply_kernel.
-template <bool ADD, bool MASK>
+template <bool ADD, bool MASK, bool SUM = false>
 __global__ void __launch_bounds__(256) bn_backward_apply_kernel(const uint4* __restrict__ g, const uint4* __restrict__ x,
                                                                 const uint4* __restrict__ e, uint4* __restrict__ out,
                                                                 const float* __restrict__ coef, const uint4* __restrict__ mx,
@@ -195,6 +195,10 @@ __global__ void __launch_bounds__(256) bn_backward_apply_kernel(const uint4* __r
           r[h] = t;
         }
         o[j] = f32x2_to_bf16x2(r[0], r[1]);
+        if (SUM) {   // column sums of the tensor as stored: what a reduction over the bf16 flow would add up
+          s0[2 * j] += __uint_as_float(o[j] << 16);
+          s0[2 * j + 1] += __uint_as_float(o[j] & 0xffff0000u);
+        }
       }
       __stcs(out + idx, make_uint4(o[0], o[1], o[2], o[3]));
     }
@@ -215,6 +219,18 @@ __global__ void __launch_bounds__(256) bn_backward_apply_kernel(const uint4* __r
         }
         partials[((size_t)blockIdx.x * 2 + 0) * C + grp * 8 + i] = a;
         partials[((size_t)blockIdx.x * 2 + 1) * C + grp * 8 + i] = b;
+      }
+    }
+  }
+  if (SUM && !MASK) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) sh[threadIdx.x * 8 + i] = s0[i];
+    __syncthreads();
+    if (lane == 0) {
+      for (int i = 0; i < 8; ++i) {
+        float a = 0.0f;
+        for (int l = 0; l < lanes; ++l) a += sh[(l * groups + grp) * 8 + i];
+        partials[(size_t)blockIdx.x * C + grp * 8 + i] = a;
       }
     }
   }
@@ -479,6 +495,14 @@ int32_t he_bn_backward_apply(const void* g, const void* x, const void* addend, v
     else bn_backward_apply_kernel<false, true><<<grid, 256, 256 * 16 * 4, st>>>(G, X, E, O, coef, MX, mask_scale, mask_shift, pixels, channels, parts);
     HE_CUDA(cudaGetLastError());
     bn_fold_partials<<<(2 * channels + 31) / 32, dim3(32, 8), 0, st>>>(parts, stats_out, grid, 2 * channels);
+  } else if (stats_out) {
+    // no mask: the statistics output is [C] column sums of `out` as stored (the bias gradient of the convolution
+    // this flow enters next), folded from per-CTA partials in CTA order
+    if (!workspace) HE_FAIL(HE_ERR_WORKSPACE, "he_bn_backward_apply: column sums need he_bn_workspace_bytes() of workspace");
+    if (addend) bn_backward_apply_kernel<true, false, true><<<grid, 256, 256 * 8 * 4, st>>>(G, X, E, O, coef, nullptr, nullptr, nullptr, pixels, channels, parts);
+    else bn_backward_apply_kernel<false, false, true><<<grid, 256, 256 * 8 * 4, st>>>(G, X, E, O, coef, nullptr, nullptr, nullptr, pixels, channels, parts);
+    HE_CUDA(cudaGetLastError());
+    bn_fold_partials<<<(channels + 31) / 32, dim3(32, 8), 0, st>>>(parts, stats_out, grid, channels);
   } else {
     if (addend) bn_backward_apply_kernel<true, false><<<grid, 256, 0, st>>>(G, X, E, O, coef, nullptr, nullptr, nullptr, pixels, channels, nullptr);
     else bn_backward_apply_kernel<false, false><<<grid, 256, 0, st>>>(G, X, E, O, coef, nullptr, nullptr, nullptr, pixels, channels, nullptr);

@@ -335,7 +335,9 @@ int32_t he_bn_backward_coeffs(const float* stats, int64_t count, const float* ga
                               float* coef, float* dgamma, float* dbeta, int32_t channels, void* cu_stream);
 /* out = coef.A[c] g + coef.B[c] x + coef.K[c] (+ addend).  With `mask_x` the result is zeroed where
  * mask_x * mask_scale[c] + mask_shift[c] <= 0 (a rectified normalisation in front of this one) and
- * stats_out = [sum out, sum out * mask_x] is produced (workspace as for he_bn_apply). */
+ * stats_out = [sum out, sum out * mask_x] is produced (workspace as for he_bn_apply).  Without a mask, a non-null
+ * stats_out receives f32 [channels] column sums of `out` as stored -- the bias gradient of the convolution that
+ * `out` enters next, which the reference computes with a separate reduction -- and needs the same workspace. */
 int32_t he_bn_backward_apply(const void* g, const void* x, const void* addend, void* out, const float* coef,
                              const void* mask_x, const float* mask_scale, const float* mask_shift, float* stats_out,
                              void* workspace, int64_t pixels, int32_t channels, void* cu_stream);
