@@ -56,7 +56,7 @@ C2A_BYTES = 2 * 64 * 256 * 56 * 56 * 2 + 2 * 256 * 4      # x in + y out (bf16) 
 C2B_BYTES = 2 * 4096 * 4096 * 8 * 4                       # in + out (f32)
 C3_MNK = (4096, 4096, 4096)
 C3_FLOPS = 2 * 4096 ** 3
-NCCL_CTAS_DEFAULT = 0
+NCCL_CTAS_DEFAULT = 32
 
 
 def load_peaks():
