@@ -812,7 +812,8 @@ class WorkloadC5:
     BATCH, HW, CLASSES = 128, 224, 1000
     description = ("configs[4]: resnet-train network (7x7/2 head, 4 x (downsample block + basic block), bn/relu, 1x1 to 1000 classes), "
                    "training step forward + backward + SGD momentum 0.9, batch 128 per GPU of synthetic 3x224x224 images, bf16 compute, f32 "
-                   "master weights; implicit-GEMM convolutions with bias / residual / batch-statistics epilogues")
+                   "master weights; implicit-GEMM convolutions with bias / residual / batch-statistics epilogues; the step's launches are "
+                   "replayed from three CUDA graphs (forward, backward, optimiser)")
     l2_note = "activations of one step (several GB) exceed L2; every step re-reads them"
     work_per_step = 1.0
     work_scale = 1.0
@@ -845,17 +846,16 @@ class WorkloadC5:
     def step(self, record=None):
         net, torch = self.net, self.torch
         if record is None:
-            net.step(0.01, self.reducer)
+            net.step(0.01, self.reducer, graph=True)   # replayed from CUDA graphs after the first (eager) step
             return
         st = torch.cuda.current_stream()
-        e = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
-        net.launches = 0
-        net.g_vec2.zero_()
-        e[0].record(st); net.forward(); e[1].record(st); net.backward(); e[2].record(st)
-        if self.reducer is not None:
-            self.reducer.reduce_bucket([net.g_conv]); self.reducer.reduce_bucket([net.g_vec, net.g_vec2]); self.reducer.finish()
-        net.optimizer_step(0.01); e[3].record(st)
-        record.append(("forward", e[0], e[1])); record.append(("backward", e[1], e[2])); record.append(("step", e[0], e[3]))
+        e = {}
+        def mark(tag):
+            e[tag] = torch.cuda.Event(enable_timing=True)
+            e[tag].record(st)
+        net.step(0.01, self.reducer, graph=True, mark=mark)
+        record.append(("forward", e["start"], e["forward"])); record.append(("backward", e["forward"], e["backward"]))
+        record.append(("step", e["start"], e["end"]))
 
     e2e_note = "one stream: image upload, step, loss download queued back to back without host synchronisation"
 
@@ -863,7 +863,7 @@ class WorkloadC5:
         torch = self.torch
         self.net.acts["x0"].view(torch.int16).copy_(self.x_pin, non_blocking=True)
         self.net.labels.copy_(self.l_pin, non_blocking=True)
-        self.net.step(0.01, self.reducer)
+        self.net.step(0.01, self.reducer, graph=True)
         self.loss_pin.copy_(self.net.loss, non_blocking=True)
 
     @staticmethod

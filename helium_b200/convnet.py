@@ -161,6 +161,7 @@ class ConvNet:
         self.labels = torch.zeros(batch, dtype=torch.int32, device=dev)
         self.loss = torch.zeros(batch, dtype=torch.float32, device=dev)
         self.launches = 0
+        self._graphs = None       # (lr, forward+backward graph, optimiser graph, launches) once captured
 
     # -- construction -----------------------------------------------------------------------------------
     def _act(self, name, shape):
@@ -406,17 +407,55 @@ class ConvNet:
         self.first_step = False
         self.launches += 3
 
-    def step(self, lr: float = 0.01, reducer=None) -> None:
-        """Forward, backward, (gradient mean over ranks,) optimiser.  Images are in acts["x0"], labels in self.labels."""
-        self.launches = 0
-        self.g_vec2.zero_()
-        self.forward()
-        self.backward()
+    def step(self, lr: float = 0.01, reducer=None, graph: bool = False, mark=None) -> None:
+        """Forward, backward, (gradient mean over ranks,) optimiser.  Images are in acts["x0"], labels in self.labels.
+        With `graph` the ~270 launches are replayed from three CUDA graphs (forward, backward, optimiser) captured
+        on the second call with this learning rate; the gradient exchange stays an ordinary call between them.
+        `mark(tag)` is called on the host at the phase boundaries ("start", "forward", "backward", "end"), e.g. to
+        record events on the stream."""
+        mark = mark or (lambda tag: None)
+        use_graphs = graph and not self.first_step
+        if use_graphs and (self._graphs is None or self._graphs[0] != lr):
+            self._capture(lr)
+        mark("start")
+        if use_graphs:
+            self._graphs[1].replay()
+        else:
+            self.launches = 0
+            self.g_vec2.zero_()
+            self.forward()
+        mark("forward")
+        if use_graphs:
+            self._graphs[2].replay()
+        else:
+            self.backward()
+        mark("backward")
         if reducer is not None:
             reducer.reduce_bucket([self.g_conv])
             reducer.reduce_bucket([self.g_vec, self.g_vec2])
             reducer.finish()
-        self.optimizer_step(lr)
+        if use_graphs:
+            self._graphs[3].replay()
+            self.launches = self._graphs[4]
+        else:
+            self.optimizer_step(lr)
+        mark("end")
+
+    def _capture(self, lr):
+        torch = self.torch
+        torch.cuda.synchronize(self.dev)
+        self.ctx.poll()
+        gf, gb, go = torch.cuda.CUDAGraph(), torch.cuda.CUDAGraph(), torch.cuda.CUDAGraph()
+        # the step's own buffers are all allocated; capture records the launches without running them
+        self.launches = 0
+        with torch.cuda.graph(gf):
+            self.g_vec2.zero_()
+            self.forward()
+        with torch.cuda.graph(gb):
+            self.backward()
+        with torch.cuda.graph(go):
+            self.optimizer_step(lr)
+        self._graphs = (lr, gf, gb, go, self.launches)
 
 
 def synthetic_batch(batch: int, hw: int = 224, classes: int = 1000, seed: int = 4, shard: int = 0):

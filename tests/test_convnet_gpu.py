@@ -115,3 +115,22 @@ def test_step_is_bit_stable(ctx):
     for a, b in zip(outs[0], outs[1]):
         assert torch.equal(a.view(torch.int32) if a.dtype == torch.float32 else a.view(torch.int16),
                            b.view(torch.int32) if b.dtype == torch.float32 else b.view(torch.int16))
+
+
+def test_graph_replay_gives_the_eager_step(ctx):
+    """Three steps replayed from the captured CUDA graphs leave the same weights, gradients and loss bits as three
+    eager steps from the same start (the graphs hold the same launches, nothing else)."""
+    import torch
+    res = []
+    for use_graph in (False, True):
+        net, _, _, _ = _setup(ctx, 8, 64, 24)
+        for _ in range(4):                     # first step eager either way, then three eager / replayed
+            net.step(0.01, graph=use_graph)
+        torch.cuda.synchronize()
+        ctx.poll()
+        assert (net._graphs is not None) == use_graph
+        res.append((net.loss.clone(), net.g_conv.clone(), net.g_vec.clone(), net.w_conv.clone(), net.w_vec.clone(), net.launches))
+    bits = lambda t: t.view(torch.int32) if t.dtype == torch.float32 else t.view(torch.int16)
+    for a, b in zip(res[0][:5], res[1][:5]):
+        assert torch.equal(bits(a), bits(b))
+    assert res[0][5] == res[1][5] > 200
