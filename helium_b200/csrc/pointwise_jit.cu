@@ -229,9 +229,41 @@ bool emit_instr(Src& o, const PwProgram& P, const PwInstr& in, bool vec, std::st
                 "__float_as_uint(h2f(w[t] >> 16)); } }\n", in.dst, in.dst);
         }
       } else {
-        o.f("      %s{\n", loop);
-        emit_views(o, P, in.view0, in.nviews, "(idx0 + j)", "vi");
-        o.f("      %s = %s(p.in[%d], vi); }\n", R.u(in.dst).c_str(), elem_loader(in.dt), in.slot);
+        // A single view whose innermost extent is a multiple of 8: the thread's 8 elements share every outer
+        // coordinate, so the chain runs once for idx0.  Innermost stride 1 (a row vector along the last dim, a
+        // sliced or permuted outer dim): 8 consecutive source elements, one or two 16-byte loads when every outer
+        // stride keeps them aligned.  Innermost stride 0 (a column vector or a scalar): one load, replicated.
+        const PwView& vw = P.views[in.view0];
+        const bool run8 = vec && in.nviews == 1 && vw.nd >= 1 && vw.fd[0].d % 8 == 0 && (vw.stride[0] == 1 || vw.stride[0] == 0);
+        if (run8) {
+          const uint32_t per16 = (in.dt == HE_F32 || in.dt == HE_U32) ? 4 : 8;
+          bool aligned = vw.stride[0] == 1;
+          for (int k = 1; k < vw.nd; ++k) aligned = aligned && vw.stride[k] % per16 == 0;
+          o.f("      {\n");
+          emit_views(o, P, in.view0, 1, "idx0", "v0");
+          if (vw.stride[0] == 0) {
+            o.f("        const u32 x = %s(p.in[%d], v0);\n#pragma unroll\n        for (int j = 0; j < 8; ++j) R%d[j] = x; }\n", elem_loader(in.dt),
+                in.slot, in.dst);
+          } else if (!aligned) {
+            o.f("#pragma unroll\n        for (int j = 0; j < 8; ++j) R%d[j] = %s(p.in[%d], v0 + j); }\n", in.dst, elem_loader(in.dt), in.slot);
+          } else if (per16 == 4) {
+            o.f("        const uint4 a = __ldg((const uint4*)((const char*)p.in[%d] + (size_t)v0 * 4)), b = __ldg((const uint4*)((const char*)p.in[%d] + "
+                "(size_t)v0 * 4) + 1);\n", in.slot, in.slot);
+            o.f("        R%d[0] = a.x; R%d[1] = a.y; R%d[2] = a.z; R%d[3] = a.w; R%d[4] = b.x; R%d[5] = b.y; R%d[6] = b.z; R%d[7] = b.w; }\n",
+                in.dst, in.dst, in.dst, in.dst, in.dst, in.dst, in.dst, in.dst);
+          } else {
+            o.f("        const uint4 a = __ldg((const uint4*)((const char*)p.in[%d] + (size_t)v0 * 2)); const u32 w[4] = {a.x, a.y, a.z, a.w};\n", in.slot);
+            if (in.dt == HE_BF16)
+              o.f("#pragma unroll\n        for (int t = 0; t < 4; ++t) { R%d[2 * t] = w[t] << 16; R%d[2 * t + 1] = w[t] & 0xffff0000u; } }\n", in.dst, in.dst);
+            else
+              o.f("#pragma unroll\n        for (int t = 0; t < 4; ++t) { R%d[2 * t] = __float_as_uint(h2f(w[t] & 0xffffu)); R%d[2 * t + 1] = "
+                  "__float_as_uint(h2f(w[t] >> 16)); } }\n", in.dst, in.dst);
+          }
+        } else {
+          o.f("      %s{\n", loop);
+          emit_views(o, P, in.view0, in.nviews, "(idx0 + j)", "vi");
+          o.f("      %s = %s(p.in[%d], vi); }\n", R.u(in.dst).c_str(), elem_loader(in.dt), in.slot);
+        }
       }
       return true;
     }
@@ -391,11 +423,11 @@ int32_t pw_jit_compile(const PwCompiled& c, std::shared_ptr<PwJitModule>* out) {
 }
 
 bool pw_jit_pointers_ok(const PwCompiled& c, const PwProgram& P) {
-  for (int i = 0; i < P.n_instr; ++i) {
-    const PwInstr& in = P.instr[i];
-    if (in.op == PW_LOAD && in.nviews == 0 && (reinterpret_cast<uintptr_t>(P.in[in.slot]) & 15)) return false;
-    if (in.op == PW_STORE && (reinterpret_cast<uintptr_t>(P.out[in.slot]) & 15)) return false;
-  }
+  // identity-mapped tensors and the contiguous runs of viewed ones move as 16-byte vectors
+  for (int i = 0; i < P.n_inputs; ++i)
+    if (reinterpret_cast<uintptr_t>(P.in[i]) & 15) return false;
+  for (int i = 0; i < P.n_outputs; ++i)
+    if (reinterpret_cast<uintptr_t>(P.out[i]) & 15) return false;
   (void)c;
   return true;
 }

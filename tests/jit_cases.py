@@ -49,6 +49,12 @@ def cases(shape=(37, 24)):
         y = g.new_input([m, n], ir.F16)
         return g.unary(ir.UN_GELU, g.binary(ir.BIN_ADD, i[0], g.swap_dims(y, 0, 1)))
     out.append(("transposed_operand", _graph(shape, [ir.BF16], transposed), False))
+    def outer_swap(g, i):
+        # [4, 6, 16] read through a swap of its two outer dims plus a row vector: runs of 8 along the last dim
+        x = g.new_input([6, 4, 16], ir.BF16); row = g.new_input([16], ir.F32); colv = g.new_input([4, 1, 1], ir.F16)
+        t = g.binary(ir.BIN_ADD, g.swap_dims(x, 0, 1), g.broadcast_to(row, [4, 6, 16]))
+        return g.unary(ir.UN_TANH, g.binary(ir.BIN_MUL, t, g.broadcast_to(colv, [4, 6, 16])))
+    out.append(("outer_swap_runs", _graph(shape, [], outer_swap), False))
     # compare / select / conversions through bool and u32 values held in registers (no bool tensors in memory)
     def select(g, i):
         c = g.compare(ir.CMP_GT, i[0], i[1])
