@@ -323,7 +323,7 @@ class WorkloadGemm(_GemmBase):
         from helium_b200.configs import graph_linear
         self.torch = torch
         m, n, k = self.M, self.N, self.K
-        self.plan = hb.Plan.fused_matmul(ctx, graph_linear(m, n, k, bias=False))
+        self.plan = hb.Plan.fused_matmul(ctx, graph_linear(m, n, k, bias=False, precision=self.precision()))
         gen = torch.Generator(device=dev).manual_seed(2)
         self.a_d = torch.randn((m, k), generator=gen, device=dev).to(torch.bfloat16)
         self.b_d = (torch.randn((k, n), generator=gen, device=dev) / 90.0).to(torch.bfloat16)
@@ -334,8 +334,14 @@ class WorkloadGemm(_GemmBase):
         self.sets = [(self.a_d, self.b_d, self.outs_d), (torch.empty_like(self.a_d), torch.empty_like(self.b_d), self.plan.alloc_outputs(dev))]
         self.pipe = _E2EPipeline(torch, dev)
         self.h2d, self.d2h = 2 * m * k * 2, m * n * 2
-        self.dominant = {"gemm_plain": (self.plan.description, self.work_per_step, "tensor", peaks["bf16_tflops"], "TFLOP/s")}
+        self.dominant = {"gemm_plain": (self.plan.description, self.work_per_step, "tensor", peaks["bf16_tflops"] * self.peak_factor, "TFLOP/s")}
         self.dominant_key = "gemm_plain"
+
+    peak_factor = 1.0
+
+    @staticmethod
+    def precision():
+        return None
 
     def step(self, record=None):
         self.flush.zero_()
@@ -604,6 +610,22 @@ class WorkloadC4Graph(_GemmBase):
         torch.cuda.current_stream().synchronize()
 
     cpu_sample = staticmethod(lambda steps=1, warmup=1: WorkloadC4.cpu_sample(steps, warmup))
+
+
+class WorkloadGemmF8(WorkloadGemm):
+    """The same product requested as MulF8AccumF32 (E4M3 x E4M3): bf16 operands in HBM, rounded once per launch into
+    8-bit copies (two extra launches inside the timed step), tcgen05 kind::f8f6f4."""
+    key = "gemm8"
+    dtype = "e4m3 x e4m3 -> f32 accumulate (bf16 operands rounded to 8 bits inside the step)"
+    description = "plain matmul 8192^3, bf16 operands, MulF8AccumF32 { E4M3, E4M3 }, bf16 output"
+    launches_per_step = 3
+    peak_factor = 2.0
+    peak_note = "no measured 8-bit peak on this pool: twice the measured bf16 burst figure (the nominal ratio)"
+
+    @staticmethod
+    def precision():
+        from helium_b200 import ir
+        return ir.prec_f8(ir.PREC_F8_F32, ir.F8_E4M3, ir.F8_E4M3)
 
 
 class WorkloadPointwise:
@@ -916,8 +938,8 @@ class WorkloadC3Fused(WorkloadC3):
 
 
 WORKLOADS = {w.key: w for w in (WorkloadC1, WorkloadC2, WorkloadC3, WorkloadC3Fused, WorkloadC4, WorkloadC4Graph, WorkloadC5, WorkloadGemm,
-                                WorkloadPointwise)}
-DEFAULT_STEPS = {"c1": 2000, "c2": 200, "c3": 200, "c3f": 200, "c4": 30, "c4g": 30, "c5": 10, "gemm": 100, "pw": 50}
+                                WorkloadGemmF8, WorkloadPointwise)}
+DEFAULT_STEPS = {"c1": 2000, "c2": 200, "c3": 200, "c3f": 200, "c4": 30, "c4g": 30, "c5": 10, "gemm": 100, "gemm8": 100, "pw": 50}
 # what the default N = 1 run times beside its own workload, and the steps each gets
 SUB_RECORDS = (("configs[2] fused matmul 4096^3 (as planned)", "c3", 100), ("configs[2] with the in-kernel mainloop rewrite", "c3f", 100),
                ("configs[1] pointwise + permute", "c2", 100), ("configs[0] MLP training step f32", "c1", 1000),

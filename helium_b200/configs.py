@@ -106,7 +106,7 @@ def graph_c3(m: int, n: int, k: int, with_e: bool = False, dtype=ir.BF16):
 
 
 def graph_linear(m, n, k, bias=True, act=None, resid=False, store_z=False, a_t=False, b_t=False, dtype=ir.BF16,
-                 out_dtype=None, gate=None, colsum=None, batch=None):
+                 out_dtype=None, gate=None, colsum=None, batch=None, precision=None):
     """act(A @ B + bias (+ resid)) (* gate(G)) with optional transposed operand storage.
 
     a_t: A is stored [k, m] and transposed in the graph; b_t: B stored [n, k] and transposed.
@@ -117,7 +117,7 @@ def graph_linear(m, n, k, bias=True, act=None, resid=False, store_z=False, a_t=F
     b = g.new_input(lead + ([n, k] if b_t else [k, n]), dtype)
     am = g.transpose(a) if a_t else a
     bm = g.transpose(b) if b_t else b
-    prec = {ir.BF16: ir.PREC_BF16_F32, ir.F16: ir.PREC_F16_F32, ir.F32: ir.PREC_TF32_F32}[dtype]
+    prec = {ir.BF16: ir.PREC_BF16_F32, ir.F16: ir.PREC_F16_F32, ir.F32: ir.PREC_TF32_F32}[dtype] if precision is None else precision
     t = g.matmul(am, bm, prec)
     rnk = len(lead) + 2
     r_in = None

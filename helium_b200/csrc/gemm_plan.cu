@@ -66,6 +66,19 @@ int32_t make_operand_tmap(CUtensorMap* out, const void* ptr, int ab_format, bool
   return HE_OK;
 }
 
+// 8-bit operand copy [batch, R, k_pitch] bytes, K-major: box = 128 bytes of K x box_rows rows.
+int32_t make_f8_tmap(CUtensorMap* out, const void* ptr, int64_t R, int64_t K, int64_t k_pitch, int64_t batch, int box_rows) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) HE_FAIL(HE_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  cuuint64_t dims[3] = {(cuuint64_t)K, (cuuint64_t)R, (cuuint64_t)batch};
+  cuuint64_t strides[2] = {(cuuint64_t)k_pitch, (cuuint64_t)R * k_pitch};
+  cuuint32_t box[3] = {128u, (cuuint32_t)box_rows, 1u}, estr[3] = {1, 1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) HE_FAIL(HE_ERR_CUDA, "cuTensorMapEncodeTiled (8-bit operand) failed with CUresult %d", (int)r);
+  return HE_OK;
+}
+
 // ------------------------------------------------------------------------------------------------
 // operand (mainloop) side
 // ------------------------------------------------------------------------------------------------
@@ -452,6 +465,13 @@ struct MatmulPlan : he_plan {
   // (helium-kernel-generator/src/generators/matmul/sm80.rs:470-526); here they stay on tcgen05.
   int64_t pad_pitch[2] = {0, 0};   // A, B
   size_t ws_pad_off[2] = {0, 0};   // bytes
+  // 8-bit multiplication (MulF8Accum*): both operands are rounded once per launch into K-major 8-bit copies in the
+  // workspace (the reference converts fragments in registers, sm80.rs:317-333) and the kernels run
+  // tcgen05.mma kind::f8f6f4 on them: twice the math per byte staged in shared memory.
+  int f8 = 0;                      // GemmCore::f8
+  bool f8_src_mn[2] = {false, false};
+  int f8_src_dt[2] = {HE_BF16, HE_BF16};
+  size_t ws_f8_off[2] = {0, 0};    // bytes
 
   int32_t set_fault_injection(uint32_t wait_limit_us, int32_t withhold_loads) override {
     if (kind == EpiKind::Sgemm) HE_FAIL(HE_ERR_UNSUPPORTED, "the SIMT matmul has no device-side waits to bound");
@@ -508,8 +528,19 @@ struct MatmulPlan : he_plan {
       (side == 0 ? a_ptr : b_ptr) = dst;
       ++extra_launches;
     }
+    if (f8) {
+      const int64_t kp = (core.K + 15) / 16 * 16;
+      void* a8 = reinterpret_cast<char*>(workspace) + ws_f8_off[0];
+      void* b8 = reinterpret_cast<char*>(workspace) + ws_f8_off[1];
+      HE_TRY(launch_to_f8(a_ptr, f8_src_dt[0], f8_src_mn[0], a8, core.batch, core.M, core.K, kp, f8 & 2, stream));
+      HE_TRY(launch_to_f8(b_ptr, f8_src_dt[1], f8_src_mn[1], b8, core.batch, core.N, core.K, kp, f8 & 4, stream));
+      extra_launches += 2;
+      HE_TRY(make_f8_tmap(&ta, a8, core.M, core.K, kp, core.batch, kBM));
+      HE_TRY(make_f8_tmap(&tb, b8, core.N, core.K, kp, core.batch, cfg.two_cta ? 128 : cfg.bn));
+    } else {
     HE_TRY(make_operand_tmap(&ta, a_ptr, core.ab_format, cfg.a_mn, core.M, core.K, core.batch, kBM, pad_pitch[0]));
     HE_TRY(make_operand_tmap(&tb, b_ptr, core.ab_format, cfg.b_mn, core.N, core.K, core.batch, cfg.two_cta ? 128 : cfg.bn, pad_pitch[1]));
+    }
     if (mask_slot >= 0 && !materialise_a) HE_TRY(make_operand_tmap(&tm, inputs[mask_slot], core.ab_format, cfg.a_mn, core.M, core.K, core.batch, kBM));
     GemmCore c = core;
     c.status = ctx ? ctx->d_status : nullptr;
@@ -953,8 +984,26 @@ int32_t plan_fused_matmul_core(he_ctx* ctx, const Graph& g, he_plan** out, int* 
     *out = guard.release();
     return HE_OK;
   };
-  if (An.dtype == HE_F32 && Bn.dtype == HE_F32) return try_simt("f32 operands");
-  if (!((An.dtype == HE_BF16 && Bn.dtype == HE_BF16) || (An.dtype == HE_F16 && Bn.dtype == HE_F16)))
+  // 8-bit multiplication: the setting is a minimum (precision.rs:3-9), so small products stay at the operand
+  // precision; from ~4 GFLOP on the two conversion passes are cheap against a mainloop that does twice the math
+  // per byte.  HE_GEMM_F8=native|operand forces either.
+  {
+    const int pk = HE_PREC_KIND(M.sub_op);
+    const bool same = An.dtype == Bn.dtype && (An.dtype == HE_BF16 || An.dtype == HE_F16 || An.dtype == HE_F32);
+    bool native = (pk == HE_PREC_F8_F32 || pk == HE_PREC_F8_F16) && same && plan->cfg.ml == ML_NONE &&
+                  2.0 * c.batch * c.M * (double)c.N * c.K >= 4294967296.0;
+    if (const char* e = getenv("HE_GEMM_F8"))
+      native = (pk == HE_PREC_F8_F32 || pk == HE_PREC_F8_F16) && same && plan->cfg.ml == ML_NONE && (e[0] == 'n' ? true : e[0] == 'o' ? false : native);
+    if (native) {
+      plan->f8 = 1 | (((M.sub_op >> 8) & 1) << 1) | (((M.sub_op >> 12) & 1) << 2);
+      plan->f8_src_mn[0] = plan->cfg.a_mn; plan->f8_src_mn[1] = plan->cfg.b_mn;
+      plan->f8_src_dt[0] = An.dtype; plan->f8_src_dt[1] = Bn.dtype;
+      plan->cfg.a_mn = plan->cfg.b_mn = false;   // the copies are K-major
+      c.f8 = plan->f8;
+    }
+  }
+  if (!plan->f8 && An.dtype == HE_F32 && Bn.dtype == HE_F32) return try_simt("f32 operands");
+  if (!plan->f8 && !((An.dtype == HE_BF16 && Bn.dtype == HE_BF16) || (An.dtype == HE_F16 && Bn.dtype == HE_F16)))
     HE_FAIL(HE_ERR_UNSUPPORTED, "fused matmul: operands must both be bf16, both f16 or both f32 (got %s x %s)", dtype_name(An.dtype), dtype_name(Bn.dtype));
   c.ab_format = An.dtype == HE_BF16 ? 1 : 0;
   c.group_m = 1;
@@ -972,7 +1021,7 @@ int32_t plan_fused_matmul_core(he_ctx* ctx, const Graph& g, he_plan** out, int* 
   // epilogues cover the graph; everything else gets a pitch-padded copy of the offending operand.
   const int64_t a_cols = plan->cfg.a_mn ? c.M : c.K, b_cols = plan->cfg.b_mn ? c.N : c.K;
   std::string pad_note;
-  if (a_cols % 8 != 0 || b_cols % 8 != 0) {
+  if (!plan->f8 && (a_cols % 8 != 0 || b_cols % 8 != 0)) {
     const double flop = 2.0 * c.batch * c.M * (double)c.N * c.K;
     if (flop < 268435456.0 && plan->cfg.ml == ML_NONE) {
       set_error("");
@@ -997,7 +1046,7 @@ int32_t plan_fused_matmul_core(he_ctx* ctx, const Graph& g, he_plan** out, int* 
   auto finish_tiles = [&]() {
     c.tiles_m = (c.M + kBM - 1) / kBM;
     c.tiles_n = (c.N + plan->cfg.bn - 1) / plan->cfg.bn;
-    c.k_blocks = (c.K + kBK - 1) / kBK;
+    c.k_blocks = plan->f8 ? (c.K + 2 * kBK - 1) / (2 * kBK) : (c.K + kBK - 1) / kBK;   // 128 bytes of K per block
     // Two SMs per 256 x 256 tile whenever there are at least two row tiles to pair up; the
     // environment switch keeps the single-CTA kernel reachable for comparisons.
     const char* force1 = getenv("HE_GEMM_ONE_CTA");
@@ -1043,6 +1092,14 @@ int32_t plan_fused_matmul_core(he_ctx* ctx, const Graph& g, he_plan** out, int* 
       const int64_t rows = (mn ? c.K : (side == 0 ? c.M : c.N)) * (int64_t)c.batch;
       plan->ws_pad_off[side] = (plan->workspace_bytes + 255) / 256 * 256;
       plan->workspace_bytes = plan->ws_pad_off[side] + (size_t)rows * plan->pad_pitch[side] * 2;
+    }
+    if (plan->f8) {
+      const size_t kp = (size_t)(c.K + 15) / 16 * 16;
+      plan->ws_f8_off[0] = (plan->workspace_bytes + 255) / 256 * 256;
+      plan->ws_f8_off[1] = (plan->ws_f8_off[0] + (size_t)c.batch * c.M * kp + 255) / 256 * 256;
+      plan->workspace_bytes = plan->ws_f8_off[1] + (size_t)c.batch * c.N * kp;
+      return std::string(", 8-bit multiplication (A ") + (plan->f8 & 2 ? "E5M2" : "E4M3") + ", B " + (plan->f8 & 4 ? "E5M2" : "E4M3") +
+             ": operands rounded once per launch into K-major copies, tcgen05 kind::f8f6f4)";
     }
     if (plan->cfg.ml == ML_NONE) return pad_note;
     if (plan->cfg.ml & ML_GENERIC) return ", generic mainloop rewrite in shared memory";

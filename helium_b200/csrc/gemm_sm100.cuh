@@ -47,6 +47,9 @@ struct GemmCore {
   int M, N, K, batch;
   int tiles_m, tiles_n, num_tiles, k_blocks;
   int ab_format;  // 0 = f16, 1 = bf16
+  // 8-bit multiplication (MulF8Accum*, helium-ir/src/opgraph/op/precision.rs:60-81): bit 0 set = the operand tiles
+  // are 8-bit floats (K-major, 128 elements of K per 128-byte row), bit 1 = A is E5M2, bit 2 = B is E5M2 (else E4M3)
+  int f8;
   int group_m;    // tile rasterisation: row tiles per group (see decode_tile)
   // Pair-tile kernel only: tiles [split_from, split_from + split_count) of the tile list are walked
   // as two half-width tiles each, by different CTA pairs (see finish_tiles in gemm_plan.cu).
@@ -982,7 +985,7 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmParams<typename Epi::Params> p) 
         for (int kb = 0; kb < c.k_blocks; ++kb) {
           if (!ptx::mbar_wait(bar_empty(stage), phase ^ 1u, abort_flag, c.status, 1, stage, c.wait_limit_us)) { alive = false; break; }
           ptx::mbar_arrive_expect_tx(bar_full(stage), kStageBytes);
-          const int k0 = kb * kBK;
+          const int k0 = kb * (c.f8 ? 2 * kBK : kBK);   // 128 bytes of K per block
           const uint32_t a_dst = smem_base + SM::off_a + stage * kATileBytes;
           const uint32_t b_dst = smem_base + SM::off_b + stage * SM::kBTileBytes;
           if (A_MN) {
@@ -1016,7 +1019,8 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmParams<typename Epi::Params> p) 
   } else if (warp == 1) {
     // ===================== MMA issuer =====================
     if (lane == 0) {
-      const uint32_t idesc = ptx::make_idesc_f16(c.ab_format, A_MN ? 1 : 0, B_MN ? 1 : 0, kBM, BN);
+      const uint32_t idesc = c.f8 ? ptx::make_idesc_f8(c.f8 & 2 ? 1 : 0, c.f8 & 4 ? 1 : 0, kBM, BN)
+                                  : ptx::make_idesc_f16(c.ab_format, A_MN ? 1 : 0, B_MN ? 1 : 0, kBM, BN);
       // K-major: 8-row groups 1024 B apart (SBO), K advances 32 B inside the swizzle row.
       // MN-major: 64-element blocks kBK*128 B apart (LBO), 8-k groups 1024 B apart (SBO),
       //           K advances two k-groups = 2048 B per MMA.
@@ -1042,7 +1046,8 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmParams<typename Epi::Params> p) 
           for (int k = 0; k < kBK / kUmmaK; ++k) {
             const uint64_t adesc = ptx::make_smem_desc_sw128(a_addr + k * a_kadv, a_lbo, 1024);
             const uint64_t bdesc = ptx::make_smem_desc_sw128(b_addr + k * b_kadv, b_lbo, 1024);
-            ptx::umma_f16(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+            if (c.f8) ptx::umma_f8(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+            else ptx::umma_f16(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
           }
           ptx::umma_commit(bar_empty(stage));   // frees the smem stage when these MMAs retire
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }

@@ -277,4 +277,94 @@ int32_t launch_pad_rows(const void* src, void* dst, long long rows, long long co
   return HE_OK;
 }
 
+
+// ---- 8-bit operand copies --------------------------------------------------------------------------------
+namespace {
+__device__ __forceinline__ unsigned f8x2(float lo, float hi, int e5m2) {
+  unsigned short r;
+  if (e5m2) asm("cvt.rn.satfinite.e5m2x2.f32 %0, %1, %2;" : "=h"(r) : "f"(hi), "f"(lo));
+  else asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+__device__ __forceinline__ float load_as_f32(const void* p, int dt, long long i) {
+  if (dt == HE_F32) return __ldg(reinterpret_cast<const float*>(p) + i);
+  const unsigned h = __ldg(reinterpret_cast<const unsigned short*>(p) + i);
+  return dt == HE_BF16 ? bf16_bits_to_f32(h) : f16_bits_to_f32(h);
+}
+
+// rows of k elements, k contiguous: a thread converts 16 consecutive elements into one 16-byte store
+__global__ void __launch_bounds__(256) to_f8_rows_kernel(const void* __restrict__ src, int dt, unsigned char* __restrict__ dst, long long rows,
+                                                         long long k, long long k_pitch, int e5m2) {
+  const long long vec_per_row = (k + 15) / 16;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < rows * vec_per_row; i += (long long)gridDim.x * blockDim.x) {
+    const long long r = i / vec_per_row, c0 = (i - r * vec_per_row) * 16;
+    const long long base = r * k + c0;
+    float v[16];
+    if (c0 + 16 <= k && dt != HE_F32 && ((base * 2 + reinterpret_cast<uintptr_t>(src)) & 15) == 0) {
+      const uint4 a = __ldcs(reinterpret_cast<const uint4*>(reinterpret_cast<const unsigned short*>(src) + base));
+      const uint4 b = __ldcs(reinterpret_cast<const uint4*>(reinterpret_cast<const unsigned short*>(src) + base) + 1);
+      const unsigned w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        v[2 * j] = dt == HE_BF16 ? __uint_as_float(w[j] << 16) : f16_bits_to_f32(w[j] & 0xffffu);
+        v[2 * j + 1] = dt == HE_BF16 ? __uint_as_float(w[j] & 0xffff0000u) : f16_bits_to_f32(w[j] >> 16);
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 16; ++j) v[j] = c0 + j < k ? load_as_f32(src, dt, base + j) : 0.0f;
+    }
+    unsigned o[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) o[j] = f8x2(v[4 * j], v[4 * j + 1], e5m2) | (f8x2(v[4 * j + 2], v[4 * j + 3], e5m2) << 16);
+    unsigned char* d = dst + r * k_pitch + c0;
+    if (c0 + 16 <= k_pitch) {
+      *reinterpret_cast<uint4*>(d) = make_uint4(o[0], o[1], o[2], o[3]);   // k_pitch is a multiple of 16: the store stays inside the row
+    }
+  }
+}
+
+// [batch, k, rows] -> [batch, rows, k_pitch]: 64 x 64 tiles through shared memory (reads coalesced along rows,
+// writes along k)
+__global__ void __launch_bounds__(256) to_f8_transpose_kernel(const void* __restrict__ src, int dt, unsigned char* __restrict__ dst, long long rows,
+                                                              long long k, long long k_pitch, int e5m2) {
+  __shared__ float tile[64][65];
+  const long long b = blockIdx.z;
+  const long long r0 = (long long)blockIdx.x * 64, k0 = (long long)blockIdx.y * 64;
+  const int tx = threadIdx.x & 63, ty = threadIdx.x >> 6;   // 64 x 4
+  for (int kk = ty; kk < 64; kk += 4) {
+    const long long kq = k0 + kk, r = r0 + tx;
+    tile[kk][tx] = (kq < k && r < rows) ? load_as_f32(src, dt, (b * k + kq) * rows + r) : 0.0f;
+  }
+  __syncthreads();
+  // a thread writes 16 consecutive k of one row: 4 threads per row, 64 rows
+  const int row = threadIdx.x >> 2, seg = threadIdx.x & 3;
+  const long long r = r0 + row, kq = k0 + seg * 16;
+  if (r < rows && kq < k_pitch) {
+    unsigned o[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      o[j] = f8x2(tile[seg * 16 + 4 * j][row], tile[seg * 16 + 4 * j + 1][row], e5m2) |
+             (f8x2(tile[seg * 16 + 4 * j + 2][row], tile[seg * 16 + 4 * j + 3][row], e5m2) << 16);
+    *reinterpret_cast<uint4*>(dst + (b * rows + r) * k_pitch + kq) = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+}
+}  // namespace
+
+int32_t launch_to_f8(const void* src, int src_dtype, bool transposed, void* dst, long long batch, long long rows, long long k,
+                     long long k_pitch, int e5m2, cudaStream_t stream) {
+  if (!src || !dst || batch <= 0 || rows <= 0 || k <= 0) HE_FAIL(HE_ERR_INVALID, "8-bit operand copy: bad argument");
+  if (k_pitch % 16 != 0 || k_pitch < k || (reinterpret_cast<uintptr_t>(dst) & 15)) HE_FAIL(HE_ERR_INVALID, "8-bit operand copy: pitch / alignment");
+  if (!transposed) {
+    const long long n = batch * rows * ((k + 15) / 16);
+    const unsigned grid = (unsigned)std::max<long long>(1, std::min<long long>((n + 255) / 256, 148 * 16));
+    to_f8_rows_kernel<<<grid, 256, 0, stream>>>(src, src_dtype, reinterpret_cast<unsigned char*>(dst), batch * rows, k, k_pitch, e5m2);
+  } else {
+    if (batch > 65535 || (k + 63) / 64 > 65535) HE_FAIL(HE_ERR_UNSUPPORTED, "8-bit operand copy: grid too large");
+    dim3 grid((unsigned)((rows + 63) / 64), (unsigned)((k + 63) / 64), (unsigned)batch);
+    to_f8_transpose_kernel<<<grid, 256, 0, stream>>>(src, src_dtype, reinterpret_cast<unsigned char*>(dst), rows, k, k_pitch, e5m2);
+  }
+  HE_CUDA(cudaGetLastError());
+  return HE_OK;
+}
+
 }  // namespace he

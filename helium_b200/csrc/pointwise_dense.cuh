@@ -35,4 +35,12 @@ int32_t launch_colsum_dense(int dtype, const void* x, float* out_or_partials, un
 // address (cols odd), so reads are 2-byte accesses, coalesced along the row.
 int32_t launch_pad_rows(const void* src, void* dst, long long rows, long long cols, long long dst_pitch, cudaStream_t stream);
 
+// 8-bit copies of a matmul operand for MulF8Accum* (helium-ir/src/opgraph/op/precision.rs:60-81; the reference's
+// generator converts the fragments in registers, helium-kernel-generator/src/generators/matmul/sm80.rs:317-333).
+// src is [batch, rows, k] (`transposed` = false) or [batch, k, rows] (true) of f16 / bf16 / f32; dst is
+// [batch, rows, k_pitch] bytes with k contiguous, each value rounded to nearest even and saturated to the
+// format's largest finite value (`e5m2` != 0: E5M2, else E4M3).  The padding bytes k .. k_pitch are not written.
+int32_t launch_to_f8(const void* src, int src_dtype, bool transposed, void* dst, long long batch, long long rows, long long k,
+                     long long k_pitch, int e5m2, cudaStream_t stream);
+
 }  // namespace he

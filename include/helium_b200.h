@@ -181,7 +181,10 @@ int32_t he_plan_fused_matmul(he_ctx* ctx, const he_graph_desc* desc, he_plan** o
  *   HE_GEMM_NO_SPLIT=1        never run the tiles of an under-filled last round as half-width tiles
  *   HE_GEMM_MAINLOOP=fused|materialise   force how a mainloop fusion is executed
  *   HE_GEMM_K_SERPENTINE=0    every tile walks K forwards (default: every other tile of a CTA pair backwards)
- * None of them changes results. */
+ * None of them changes results.
+ *   HE_GEMM_F8=native|operand  MulF8Accum* requests: always / never multiply 8-bit copies of the operands with
+ *                             tcgen05 kind::f8f6f4 (default: from 4 GFLOP per launch).  This one does change results,
+ *                             within what the precision contract allows (precision.rs:3-9). */
 
 /* Backs Instruction::can_fuse_with (helium/src/backend.rs:85-95): 0 = cannot run as one kernel,
  * 1 = runs through a generic tier (pointwise: a kernel specialised at plan time with NVRTC when the program is

@@ -334,6 +334,41 @@ def test_low_precision_requests_are_served_at_or_above_their_minimum(ctx):
             assert O.rel_l2(dec(got[0]), dec(want[0])) < 0.1 * O.rel_l2(dec(narrow[0]), dec(want[0])), plan.description
 
 
+@pytest.mark.parametrize("dt", [ir.BF16, ir.F16, ir.F32])
+@pytest.mark.parametrize("ta,tb", [(False, False), (True, False), (False, True), (True, True)])
+def test_native_8bit_multiplication(ctx, monkeypatch, dt, ta, tb):
+    """MulF8AccumF32 served by tcgen05 kind::f8f6f4 (forced at a test size): both operands are rounded to their
+    F8Mode once, products of 8-bit floats are exact in f32, so the result must match the oracle's narrowest legal
+    reading (operands rounded to E4M3 / E5M2, f64 accumulation) to f32 accumulation error -- and it must NOT match
+    the operand-precision reading.  All four operand layouts, a batch, K off every vector rule, saturating values,
+    a fused bias + relu epilogue."""
+    monkeypatch.setenv("HE_GEMM_F8", "native")
+    bt, m, n, k = 2, 264, 392, 1000 + (1 if dt == ir.F32 else 0)
+    for ma, mb, epi in [(ir.F8_E4M3, ir.F8_E4M3, False), (ir.F8_E5M2, ir.F8_E4M3, True), (ir.F8_E4M3, ir.F8_E5M2, False)]:
+        g = ir.Graph()
+        a = g.new_input([bt, k, m] if ta else [bt, m, k], dt)
+        b = g.new_input([bt, n, k] if tb else [bt, k, n], dt)
+        bias = g.new_input([n], ir.F32)
+        t = g.matmul(g.swap_dims(a, 1, 2) if ta else a, g.swap_dims(b, 1, 2) if tb else b, ir.prec_f8(ir.PREC_F8_F32, ma, mb))
+        if epi:
+            t = g.unary(ir.UN_RELU, g.binary(ir.BIN_ADD, t, g.broadcast_to(bias, [bt, m, n])))
+        g.new_output(t)
+        ins = _gen(g, 91, {})
+        # a few values beyond both formats' ranges and below their subnormals
+        av = O.decode(ins[0], dt, g.nodes[g.inputs[0]].shape).copy()
+        av.reshape(-1)[:6] = [500.0, -6.0e4, 6.2e4, 2.0 ** -10, -2.0 ** -17, 0.0]
+        ins[0] = O.encode(av, dt)
+        got, plan = _run(ctx, g, ins)
+        assert "kind::f8f6f4" in plan.description, plan.description
+        node = g.nodes[g.outputs[0]]
+        dec = lambda x: O.decode(x, node.dtype, node.shape)
+        narrow = O.evaluate(g, ins, f8_quantise=True)
+        wide = O.evaluate(g, ins)
+        err = O.rel_l2(dec(got[0]), dec(narrow[0]))
+        assert err <= 2e-6, (err, plan.description)
+        assert O.rel_l2(dec(got[0]), dec(wide[0])) > 1e-3
+
+
 def test_gelu_epilogues_at_extreme_arguments(ctx):
     """GELU and gelu' in the GEMM epilogue at arguments far from the random-normal range: the product is
     zero (A = 0), so the outputs are gelu(bias[col]) and gelu'(G[row, col]) of hand-picked values --

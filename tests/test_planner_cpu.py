@@ -278,3 +278,24 @@ def test_every_precision_setting_is_accepted_at_or_above_its_minimum():
         g.new_output(t)
         with pytest.raises(HeliumError):
             hb.Plan.fused_matmul(None, g)
+
+
+def test_8bit_multiplication_goes_native_from_4_gflop(monkeypatch):
+    """MulF8Accum* requests: small products stay at the operand precision (the setting is a minimum), large ones
+    run tcgen05 kind::f8f6f4 on 8-bit copies of the operands; the environment switch forces either."""
+    def plan(m, n, k, dt=ir.BF16, prec=None):
+        g = ir.Graph()
+        a = g.new_input([m, k], dt); b = g.new_input([k, n], dt)
+        g.new_output(g.matmul(a, b, prec if prec is not None else ir.prec_f8(ir.PREC_F8_F32, ir.F8_E4M3, ir.F8_E5M2)))
+        return hb.Plan.fused_matmul(None, g)
+    monkeypatch.delenv("HE_GEMM_F8", raising=False)
+    big = plan(4096, 4096, 4096)
+    assert "kind::f8f6f4" in big.description and "A E4M3, B E5M2" in big.description
+    assert big.workspace_bytes >= 2 * 4096 * 4096
+    assert "f8f6f4" not in plan(256, 256, 256).description
+    assert "f8f6f4" not in plan(4096, 4096, 4096, prec=ir.PREC_BF16_F32).description
+    assert "kind::f8f6f4" in plan(4096, 4096, 4096, dt=ir.F32).description
+    monkeypatch.setenv("HE_GEMM_F8", "operand")
+    assert "f8f6f4" not in plan(4096, 4096, 4096).description
+    monkeypatch.setenv("HE_GEMM_F8", "native")
+    assert "kind::f8f6f4" in plan(256, 264, 1001).description
