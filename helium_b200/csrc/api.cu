@@ -1,8 +1,27 @@
 // C ABI entry points: context, descriptor validation, plan dispatch, launch.
+#include <nvtx3/nvToolsExt.h>
 #include "he_internal.h"
 #include "pointwise_program.h"
 
 #include <mutex>
+
+namespace he {
+namespace {
+bool nvtx_enabled() {
+  static const bool on = [] {
+    const char* e = getenv("HE_NVTX");
+    return !(e && e[0] == '0');
+  }();
+  return on;
+}
+}  // namespace
+TraceRange::TraceRange(const char* name) : on_(nvtx_enabled()) {
+  if (on_) nvtxRangePushA(name ? name : "helium_b200");
+}
+TraceRange::~TraceRange() {
+  if (on_) nvtxRangePop();
+}
+}  // namespace he
 
 namespace he {
 
@@ -348,6 +367,7 @@ int32_t he_launch(he_plan* plan, const void* const* inputs, void* const* outputs
   DeviceGuard guard(plan->ctx->device);   // restores the caller's current device on return
   HE_TRY(guard.status());
   plan->last_launches = 0;
+  TraceRange range(plan->description.c_str());
   return plan->launch(inputs, outputs, workspace, (cudaStream_t)cu_stream);
 }
 

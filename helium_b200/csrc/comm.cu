@@ -197,6 +197,7 @@ int32_t he_comm_info(const he_comm* comm, int32_t* rank, int32_t* world, int32_t
 int32_t he_allreduce_grads(he_comm* comm, void* const* bufs, const size_t* counts, int32_t n, int32_t dtype, int32_t mean,
                            void* cu_stream) {
   if (!comm) HE_FAIL(HE_ERR_INVALID, "he_allreduce_grads: communicator is null");
+  TraceRange range("he_allreduce_grads");
   if (comm->aborted) HE_FAIL(HE_ERR_COMM, "he_allreduce_grads: the communicator was aborted; create a new one");
   if (n < 0 || (n > 0 && (!bufs || !counts))) HE_FAIL(HE_ERR_INVALID, "he_allreduce_grads: null argument");
   ncclDataType_t dt;

@@ -122,6 +122,17 @@ class DeviceGuard {
   bool switched_ = false, failed_ = false;
 };
 
+// NVTX range for the scope of a library call (visible in Nsight Systems / Compute timelines; the reference marks
+// its planner, executor and instruction scopes with `#[profiling::function]`, helium/src/cuda.rs:178,190,225).
+// The header-only NVTX v3 costs one indirect call when no tool is attached; HE_NVTX=0 removes even that.
+class TraceRange {
+ public:
+  explicit TraceRange(const char* name);
+  ~TraceRange();
+ private:
+  bool on_;
+};
+
 // ---- validated subgraph -----------------------------------------------------------------------
 struct Graph {
   std::vector<he_node> nodes;

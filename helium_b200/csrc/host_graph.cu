@@ -646,6 +646,7 @@ int32_t heh_exec_create(he_ctx* ctx, heh_graph* g, const void* const* inputs, vo
 
 int32_t heh_exec_run(heh_exec* e, void* cu_stream) {
   if (!e) HE_FAIL(HE_ERR_INVALID, "heh_exec_run: null argument");
+  TraceRange range("heh_exec_run");
   if (e->graph_exec) {
     HE_CUDA(cudaGraphLaunch(e->graph_exec, (cudaStream_t)cu_stream));
     return HE_OK;

@@ -202,6 +202,8 @@ int32_t he_plan_workspace_bytes(const he_plan* plan, size_t* out);
 /* Replaces {PointwiseGraph,PermuteDims,CudnnGraph}::execute (pointwise.rs:57-86,
  * permute_dims.rs:33-53, cudnn_graph.rs:64-105).  Pre-filling of reduction / bool outputs
  * (pointwise.rs:62-74) happens inside, on the same stream. */
+/* Every he_launch, heh_exec_run and he_allreduce_grads call is wrapped in an NVTX range named after the plan
+ * (header-only NVTX v3: one indirect call when no tool is attached; HE_NVTX=0 switches the ranges off). */
 int32_t he_launch(he_plan* plan, const void* const* inputs, void* const* outputs,
                   void* workspace, void* cu_stream);
 
