@@ -826,7 +826,7 @@ class WorkloadC1:
 
 class WorkloadC5:
     """configs[4]: one training step of the convolutional network of resnet-train (the model the reference trains on
-    ImageNet; BASELINE calls it ResNet-50, the reference contains no 50-layer network), batch 128 per GPU of synthetic
+    ImageNet; the benchmark list calls it ResNet-50, the reference contains no 50-layer network), batch 128 per GPU of synthetic
     3 x 224 x 224 images, 1000 classes, bf16 activations / f32 master weights, SGD with helium's momentum 0.9."""
     key = "c5"
     metric, unit = "train_steps_per_s", "step/s"

@@ -1,5 +1,5 @@
 /*
- * CPU restatement (C + OpenMP) of the timed parts of the hot path.  TEST / BASELINE INFRASTRUCTURE
+ * CPU restatement (C + OpenMP) of the timed parts of the hot path.  TEST AND CPU-BASELINE INFRASTRUCTURE
  * ONLY: used by tests/ as a second opinion next to oracle/oracle.py and by bench.py's cpu_baseline
  * and `--impl reference` legs.  The product library never links or calls it.
  *
