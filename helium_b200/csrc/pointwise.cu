@@ -33,17 +33,6 @@ __global__ void __launch_bounds__(kPwThreads) pw_elementwise_kernel(const __grid
   pw_run<V>(P, idx0, nvalid, nullptr, nullptr);
 }
 
-struct PwReduceLaunch {
-  uint32_t num_groups;
-  uint32_t blocks_per_group;   // CTAs per group (block mode) -- 1 in warp mode
-  uint32_t chunk;              // elements of a group handled by one CTA
-  int warp_mode;               // 0: CTA slices of one group; 1: one warp per group, 8 groups per CTA;
-                               // 2: column mode, a lane per group, 32 groups x one slice per CTA
-  int red_ops[4];
-  int red_out_slot[4];
-  float* partials;             // [n_red][num_groups][blocks_per_group] when blocks_per_group > 1
-};
-
 // Reduction kernel.  Iteration space = [num_groups][group_size] (the reduce input, row-major with
 // the reduced dims trailing, jit.rs:137-162).
 __global__ void __launch_bounds__(kPwThreads) pw_reduce_kernel(const __grid_constant__ PwProgram P,
@@ -144,6 +133,30 @@ __global__ void __launch_bounds__(kPwThreads) pw_reduce_finalize_kernel(const __
   F.out[s][g] = v;
 }
 
+// Many partials per group (one huge group cut into thousands of CTA slices): a warp per (reduction, group).  Lane l
+// combines partials l, l + 32, ... in order, then the 32 lane values meet in a shuffle tree -- a fixed function of
+// the partials, so results stay bit-stable across launches; one thread walking 9000 partials took ~0.4 ms.
+__global__ void __launch_bounds__(kPwThreads) pw_reduce_finalize_warp_kernel(const __grid_constant__ PwFinalize F) {
+  const uint32_t w = (blockIdx.x * kPwThreads + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  if (w >= F.num_groups * (uint32_t)F.n_red) return;   // whole warps leave together
+  const uint32_t s = w / F.num_groups, g = w - s * F.num_groups;
+  const float* p = F.partials + ((size_t)s * F.num_groups + g) * F.blocks_per_group;
+  float v = pw_reduce_identity(F.red_ops[s]);
+#pragma unroll 4
+  for (uint32_t b = lane; b < F.blocks_per_group; b += 32) v = pw_reduce_combine(F.red_ops[s], v, p[b]);
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) v = pw_reduce_combine(F.red_ops[s], v, __shfl_down_sync(0xffffffffu, v, off));
+  if (lane == 0) F.out[s][g] = v;
+}
+
+int32_t launch_finalize(const PwFinalize& F, cudaStream_t stream) {
+  const uint32_t items = F.num_groups * (uint32_t)F.n_red;
+  if (F.blocks_per_group >= 64) pw_reduce_finalize_warp_kernel<<<(items * 32 + kPwThreads - 1) / kPwThreads, kPwThreads, 0, stream>>>(F);
+  else pw_reduce_finalize_kernel<<<(items + kPwThreads - 1) / kPwThreads, kPwThreads, 0, stream>>>(F);
+  HE_CUDA(cudaGetLastError());
+  return HE_OK;
+}
+
 namespace {
 // HE_PW_JIT=0 keeps every program outside the catalogue on the interpreter (A/B measurements, parity tests)
 bool jit_enabled() {
@@ -229,8 +242,7 @@ struct PointwisePlan : he_plan {
         F.red_ops[0] = HE_RED_SUM;
         F.out[0] = reinterpret_cast<float*>(outputs[L.red_out_slot[0]]);
         F.partials = L.partials;
-        pw_reduce_finalize_kernel<<<(F.num_groups + kPwThreads - 1) / kPwThreads, kPwThreads, 0, stream>>>(F);
-        HE_CUDA(cudaGetLastError());
+        HE_TRY(launch_finalize(F, stream));
         last_launches = 2;
       }
       return HE_OK;
@@ -238,8 +250,12 @@ struct PointwisePlan : he_plan {
     unsigned grid = L.warp_mode == 1 ? (L.num_groups + 7) / 8
                     : L.warp_mode == 2 ? (L.num_groups + 31) / 32 * L.blocks_per_group
                                        : L.num_groups * L.blocks_per_group;
-    pw_reduce_kernel<<<grid, kPwThreads, 0, stream>>>(P, L);
-    HE_CUDA(cudaGetLastError());
+    if (jit) {
+      HE_TRY(pw_jit_launch_reduce(*jit, P, L, grid, stream));
+    } else {
+      pw_reduce_kernel<<<grid, kPwThreads, 0, stream>>>(P, L);
+      HE_CUDA(cudaGetLastError());
+    }
     last_launches = 1;
     if (L.warp_mode != 1 && L.blocks_per_group > 1) {
       PwFinalize F{};
@@ -251,9 +267,7 @@ struct PointwisePlan : he_plan {
         F.out[s] = reinterpret_cast<float*>(P.out[L.red_out_slot[s]]);
       }
       F.partials = L.partials;
-      unsigned fg = (L.num_groups * P.n_reductions + kPwThreads - 1) / kPwThreads;
-      pw_reduce_finalize_kernel<<<fg, kPwThreads, 0, stream>>>(F);
-      HE_CUDA(cudaGetLastError());
+      HE_TRY(launch_finalize(F, stream));
       last_launches = 2;
     }
     return HE_OK;
@@ -587,12 +601,18 @@ int32_t plan_pointwise(he_ctx* ctx, const Graph& g_in, he_plan** out, int* tier_
       L.chunk = chunk;
       if (bpg > 1) plan->workspace_bytes = (size_t)P.n_reductions * L.num_groups * bpg * sizeof(float);
     }
+    const bool red_jit = !plan->cs_dense && jit_enabled() && !plan->c.has_bool_io && [&] {
+      const std::string saved = he_last_error_string();
+      const bool ok = pw_jit_compile(plan->c, &plan->jit) == HE_OK;
+      if (!ok) set_error("%s", saved.c_str());
+      return ok;
+    }();
     if (plan->cs_dense)
       snprintf(desc, sizeof desc, "pointwise tier 2 (dense column-sum kernel, [%u x %u x %u], %u row slices; column-mode interpreter for unaligned tensors)",
                plan->cs_batch, plan->cs_M, plan->cs_N, plan->cs_slices);
     else
-    snprintf(desc, sizeof desc, "pointwise tier 1 (interpreter, %d instr, %d regs), reduce: %u groups of %u, %s, %u CTAs/group",
-             P.n_instr, plan->c.n_regs, L.num_groups, P.group_size, L.warp_mode == 1 ? "warp per group" : L.warp_mode == 2 ? "column mode (lane per group)" : "CTA slices", L.blocks_per_group);
+    snprintf(desc, sizeof desc, "pointwise tier 1 (%s, %d instr, %d regs), reduce: %u groups of %u, %s, %u CTAs/group",
+             red_jit ? "program specialised at plan time with NVRTC" : "interpreter", P.n_instr, plan->c.n_regs, L.num_groups, P.group_size, L.warp_mode == 1 ? "warp per group" : L.warp_mode == 2 ? "column mode (lane per group)" : "CTA slices", L.blocks_per_group);
   } else if (plan->ew.kind >= 0) {
     snprintf(desc, sizeof desc, "pointwise tier 2 (dense elementwise kernel %s, 16-byte vectors; interpreter fallback for unaligned tensors)",
              plan->ew.name);

@@ -333,17 +333,133 @@ bool emit_instr(Src& o, const PwProgram& P, const PwInstr& in, bool vec, std::st
       }
       return true;
     }
-    case PW_REDUCE: *why = "reduction"; return false;
+    case PW_REDUCE:
+      if (vec) { *why = "reduction in the vector body"; return false; }
+      o.f("      red[%d] = red_combine(%d, red[%d], __uint_as_float(r%d));\n", in.slot2, in.sub, in.slot2, in.a);
+      return true;
     case PW_ACC: *why = "matmul accumulator"; return false;
     default: *why = "unknown instruction"; return false;
   }
+}
+
+
+// The reduction kernel: pw_reduce_kernel of pointwise.cu with the interpreter call replaced by the printed program.
+// Thread-to-element mapping, shuffle trees, shared-memory folds and partial layout are the same text, so the
+// two kernels combine the same values in the same order (tests/test_pointwise_jit_gpu.py compares their bits).
+const char* kReduceSkeleton = R"SRC(
+struct RedL { u32 num_groups, blocks_per_group, chunk; int warp_mode; int red_ops[4]; int red_out_slot[4]; float* partials; };
+extern "C" __global__ void __launch_bounds__(256) pw_jit(const JitParams p, const RedL L) {
+  __shared__ float sred[4][8];
+  float red[4];
+#pragma unroll
+  for (int s = 0; s < 4; ++s) red[s] = s < NRED ? red_identity(L.red_ops[s]) : 0.0f;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (L.warp_mode == 1) {
+    const u32 group = blockIdx.x * 8 + warp;
+    if (group >= L.num_groups) return;
+    const u32 base = group * GS;
+    const u32 iters = (GS + 31) / 32;
+    for (u32 it = 0; it < iters; ++it) {
+      const u32 e = it * 32 + lane;
+      pw_elem(p, base + e, e < GS, red);
+    }
+#pragma unroll
+    for (int s = 0; s < 4; ++s) {
+      if (s >= NRED) break;
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) red[s] = red_combine(L.red_ops[s], red[s], __shfl_down_sync(0xffffffffu, red[s], off));
+      if (lane == 0) ((float*)p.out[L.red_out_slot[s]])[group] = red[s];
+    }
+    return;
+  }
+  if (L.warp_mode == 2) {
+    __shared__ float scol[4][8][32];
+    const u32 gblocks = (L.num_groups + 31) / 32;
+    const u32 blk = blockIdx.x / gblocks, gb = blockIdx.x - blk * gblocks;
+    const u32 group = gb * 32 + lane;
+    const bool gvalid = group < L.num_groups;
+    const u32 start = blk * L.chunk, end = min(start + L.chunk, (u32)GS);
+    const u32 base = gvalid ? group * GS : 0u;
+#pragma unroll 4
+    for (u32 e = start + warp; e < end; e += 8) pw_elem(p, base + e, gvalid, red);
+#pragma unroll
+    for (int s = 0; s < 4; ++s)
+      if (s < NRED) scol[s][warp][lane] = red[s];
+    __syncthreads();
+    if (warp == 0 && gvalid) {
+      for (int s = 0; s < NRED; ++s) {
+        float v = scol[s][0][lane];
+        for (int w = 1; w < 8; ++w) v = red_combine(L.red_ops[s], v, scol[s][w][lane]);
+        if (L.blocks_per_group == 1) ((float*)p.out[L.red_out_slot[s]])[group] = v;
+        else L.partials[((size_t)s * L.num_groups + group) * L.blocks_per_group + blk] = v;
+      }
+    }
+    return;
+  }
+  const u32 group = blockIdx.x / L.blocks_per_group;
+  const u32 blk = blockIdx.x - group * L.blocks_per_group;
+  const u32 start = blk * L.chunk;
+  const u32 end = min(start + L.chunk, (u32)GS);
+  const u32 base = group * GS;
+  const u32 iters = (end - start + 255) / 256;
+#pragma unroll 4
+  for (u32 it = 0; it < iters; ++it) {
+    const u32 e = start + it * 256 + threadIdx.x;
+    pw_elem(p, base + e, e < end, red);
+  }
+#pragma unroll
+  for (int s = 0; s < 4; ++s) {
+    if (s >= NRED) break;
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) red[s] = red_combine(L.red_ops[s], red[s], __shfl_down_sync(0xffffffffu, red[s], off));
+    if (lane == 0) sred[s][warp] = red[s];
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < NRED; ++s) {
+      float v = sred[s][0];
+      for (int w = 1; w < 8; ++w) v = red_combine(L.red_ops[s], v, sred[s][w]);
+      if (L.blocks_per_group == 1) ((float*)p.out[L.red_out_slot[s]])[group] = v;
+      else L.partials[((size_t)s * L.num_groups + group) * L.blocks_per_group + blk] = v;
+    }
+  }
+}
+)SRC";
+
+bool generate_reduce(const PwCompiled& c, std::string* source, std::string* why) {
+  const PwProgram& P = c.prog;
+  if (P.n_reductions > 4) { *why = "more than four reductions"; return false; }
+  int n_regs = 0;
+  for (int i = 0; i < P.n_instr; ++i) {
+    const PwInstr& in = P.instr[i];
+    if (in.op == PW_STORE) { *why = "a stored tensor beside the reductions"; return false; }
+    if (in.op != PW_REDUCE) n_regs = std::max(n_regs, in.dst + 1);
+  }
+  Src o;
+  o.s = kPrelude;
+  o.f("#define NRED %d\n#define GS %uu\n", P.n_reductions, P.group_size);
+  o.f("__device__ __forceinline__ float red_combine(int op, float a, float b) { return op == %d ? fmaxf(a, b) : op == %d ? fminf(a, b) : a + b; }\n",
+      HE_RED_MAX, HE_RED_MIN);
+  o.f("__device__ __forceinline__ float red_identity(int op) { return op == %d ? -__int_as_float(0x7f800000) : op == %d ? __int_as_float(0x7f800000) : 0.0f; }\n",
+      HE_RED_MAX, HE_RED_MIN);
+  o.f("__device__ __forceinline__ void pw_elem(const JitParams& p, u32 idx0, bool valid, float* red) {\n");
+  o.f("  if (!valid) return;\n  const u32 j = 0;\n");
+  for (int k = 0; k < n_regs; ++k) o.f("      u32 r%d;\n", k);
+  for (int i = 0; i < P.n_instr; ++i)
+    if (!emit_instr(o, P, P.instr[i], false, why)) return false;
+  o.f("}\n");
+  o.s += kReduceSkeleton;
+  *source = std::move(o.s);
+  return true;
 }
 
 }  // namespace
 
 bool pw_jit_generate(const PwCompiled& c, std::string* source, std::string* why) {
   const PwProgram& P = c.prog;
-  if (P.n_reductions != 0) { *why = "reductions run on the interpreter"; return false; }
+  if (c.has_bool_io) { *why = "bit-packed bool tensors run on the interpreter"; return false; }
+  if (P.n_elems == 0 || P.n_elems > 0x7fffff00u) { *why = "iteration space outside 1 .. 2^31"; return false; }
+  if (P.n_reductions != 0) return generate_reduce(c, source, why);
   if (c.has_bool_io) { *why = "bit-packed bool tensors run on the interpreter"; return false; }
   if (P.n_elems == 0 || P.n_elems > 0x7fffff00u) { *why = "iteration space outside 1 .. 2^31"; return false; }
   int n_regs = 0;
@@ -432,26 +548,31 @@ bool pw_jit_pointers_ok(const PwCompiled& c, const PwProgram& P) {
   return true;
 }
 
-int32_t pw_jit_launch(PwJitModule& m, const PwProgram& P, int sm_count, cudaStream_t stream) {
+namespace {
+int32_t load_kernel(PwJitModule& m, cudaKernel_t* out) {
   int dev = 0;
   HE_CUDA(cudaGetDevice(&dev));
-  cudaKernel_t fn = nullptr;
-  {
-    std::lock_guard<std::mutex> lk(m.mu);
-    auto it = m.loaded.find(dev);
-    if (it == m.loaded.end()) {
-      cudaLibrary_t lib = nullptr;
-      HE_CUDA(cudaLibraryLoadData(&lib, m.cubin.data(), nullptr, nullptr, 0, nullptr, nullptr, 0));
-      cudaKernel_t k = nullptr;
-      cudaError_t e = cudaLibraryGetKernel(&k, lib, "pw_jit");
-      if (e != cudaSuccess) {
-        cudaLibraryUnload(lib);
-        HE_FAIL(HE_ERR_CUDA, "pointwise specialisation: kernel not found in its image: %s", cudaGetErrorString(e));
-      }
-      it = m.loaded.emplace(dev, std::make_pair(lib, k)).first;
+  std::lock_guard<std::mutex> lk(m.mu);
+  auto it = m.loaded.find(dev);
+  if (it == m.loaded.end()) {
+    cudaLibrary_t lib = nullptr;
+    HE_CUDA(cudaLibraryLoadData(&lib, m.cubin.data(), nullptr, nullptr, 0, nullptr, nullptr, 0));
+    cudaKernel_t k = nullptr;
+    cudaError_t e = cudaLibraryGetKernel(&k, lib, "pw_jit");
+    if (e != cudaSuccess) {
+      cudaLibraryUnload(lib);
+      HE_FAIL(HE_ERR_CUDA, "pointwise specialisation: kernel not found in its image: %s", cudaGetErrorString(e));
     }
-    fn = it->second.second;
+    it = m.loaded.emplace(dev, std::make_pair(lib, k)).first;
   }
+  *out = it->second.second;
+  return HE_OK;
+}
+}  // namespace
+
+int32_t pw_jit_launch(PwJitModule& m, const PwProgram& P, int sm_count, cudaStream_t stream) {
+  cudaKernel_t fn = nullptr;
+  HE_TRY(load_kernel(m, &fn));
   struct { const void* in[16]; void* out[8]; } prm;
   static_assert(kPwMaxInputs == 16 && kPwMaxOutputs == 8, "JitParams layout of the generated kernel");
   for (int i = 0; i < kPwMaxInputs; ++i) prm.in[i] = P.in[i];
@@ -459,6 +580,18 @@ int32_t pw_jit_launch(PwJitModule& m, const PwProgram& P, int sm_count, cudaStre
   const unsigned long long nv = ((unsigned long long)P.n_elems + 7) / 8;
   const unsigned grid = (unsigned)std::max<unsigned long long>(1, std::min<unsigned long long>((nv + 255) / 256, (unsigned long long)sm_count * 16));
   void* args[] = {&prm};
+  HE_CUDA(cudaLaunchKernel(reinterpret_cast<const void*>(fn), dim3(grid), dim3(256), args, 0, stream));
+  return HE_OK;
+}
+
+int32_t pw_jit_launch_reduce(PwJitModule& m, const PwProgram& P, const PwReduceLaunch& L, unsigned grid, cudaStream_t stream) {
+  cudaKernel_t fn = nullptr;
+  HE_TRY(load_kernel(m, &fn));
+  struct { const void* in[16]; void* out[8]; } prm;
+  for (int i = 0; i < kPwMaxInputs; ++i) prm.in[i] = P.in[i];
+  for (int i = 0; i < kPwMaxOutputs; ++i) prm.out[i] = P.out[i];
+  PwReduceLaunch l = L;
+  void* args[] = {&prm, &l};
   HE_CUDA(cudaLaunchKernel(reinterpret_cast<const void*>(fn), dim3(grid), dim3(256), args, 0, stream));
   return HE_OK;
 }

@@ -25,6 +25,10 @@ int32_t pw_jit_compile(const PwCompiled& c, std::shared_ptr<PwJitModule>* out);
 // checks and falls back to the interpreter otherwise).
 int32_t pw_jit_launch(PwJitModule& m, const PwProgram& P, int sm_count, cudaStream_t stream);
 
+// The reduction kernel of a program with reductions (same thread-to-element mapping and combine order as the
+// interpreter's pw_reduce_kernel, so both give the same bits); `grid` as computed for that kernel.
+int32_t pw_jit_launch_reduce(PwJitModule& m, const PwProgram& P, const PwReduceLaunch& L, unsigned grid, cudaStream_t stream);
+
 // true when every tensor the kernel reads or writes with 16-byte accesses is aligned for them
 bool pw_jit_pointers_ok(const PwCompiled& c, const PwProgram& P);
 

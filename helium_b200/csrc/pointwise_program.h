@@ -62,6 +62,17 @@ struct PwProgram {
   PwView views[kPwMaxViews];
 };
 
+struct PwReduceLaunch {
+  uint32_t num_groups;
+  uint32_t blocks_per_group;   // CTAs per group (block mode) -- 1 in warp mode
+  uint32_t chunk;              // elements of a group handled by one CTA
+  int warp_mode;               // 0: CTA slices of one group; 1: one warp per group, 8 groups per CTA;
+                               // 2: column mode, a lane per group, 32 groups x one slice per CTA
+  int red_ops[4];
+  int red_out_slot[4];
+  float* partials;             // [n_red][num_groups][blocks_per_group] when blocks_per_group > 1
+};
+
 // Host-side description produced by the compiler next to the program.
 struct PwLoadInfo {
   int instr;              // index into program.instr

@@ -187,8 +187,8 @@ int32_t he_plan_fused_matmul(he_ctx* ctx, const he_graph_desc* desc, he_plan** o
  *                             within what the precision contract allows (precision.rs:3-9). */
 
 /* Backs Instruction::can_fuse_with (helium/src/backend.rs:85-95): 0 = cannot run as one kernel,
- * 1 = runs through a generic tier (pointwise: a kernel specialised at plan time with NVRTC when the program is
- * elementwise and the NVRTC library can be loaded -- HE_NVRTC_LIBRARY names it, HE_PW_JIT=0 switches the tier off
+ * 1 = runs through a generic tier (pointwise: a kernel specialised at plan time with NVRTC when the program
+ * has no bool tensor in memory and the NVRTC library can be loaded -- HE_NVRTC_LIBRARY names it, HE_PW_JIT=0 switches the tier off
  * -- else the register-program interpreter), 2 = matches a hand-written fast kernel.
  * kind: 0 pointwise, 1 permute (swap chain on one input), 2 fused matmul. */
 int32_t he_plan_supported(he_ctx* ctx, const he_graph_desc* desc, int32_t kind);

@@ -1,6 +1,6 @@
 """Plan-time specialised pointwise kernels, the part that needs no GPU: every program family of jit_cases.py is
-printed and accepted by NVRTC for sm_100a at plan time; the switch, bit-packed bool tensors, reductions and a
-missing NVRTC library leave the program on the interpreter without an error."""
+printed and accepted by NVRTC for sm_100a at plan time (reductions over a prologue included); the switch, bit-packed
+bool tensors and a missing NVRTC library leave the program on the interpreter without an error."""
 import os
 import subprocess
 import sys
@@ -34,11 +34,20 @@ def test_switch_and_out_of_range_programs_stay_on_the_interpreter(monkeypatch):
     a = gb.new_input([16, 40], ir.F32); b = gb.new_input([16, 40], ir.F32)
     gb.new_output(gb.compare(ir.CMP_LT, a, b))
     assert "interpreter, " in hb.Plan.pointwise(None, gb).description
-    # a reduction: interpreter (or its hand-written column-sum kernel), never the specialised elementwise kernel
+    # a reduction over a prologue is specialised too (its own kernel); with the switch off it is interpreted
     gr = ir.Graph()
     a = gr.new_input([16, 40], ir.F32)
     gr.new_output(gr.reduce(ir.RED_SUM, gr.unary(ir.UN_EXP, a), 1))
-    assert SPECIALISED not in hb.Plan.pointwise(None, gr).description
+    d = hb.Plan.pointwise(None, gr).description
+    assert SPECIALISED in d and "reduce: 16 groups of 40" in d
+    monkeypatch.setenv("HE_PW_JIT", "0")
+    assert "interpreter" in hb.Plan.pointwise(None, gr).description
+    monkeypatch.delenv("HE_PW_JIT")
+    # the plain column sum keeps its hand-written kernel
+    gs = ir.Graph()
+    y = gs.new_input([4096, 512], ir.BF16)
+    gs.new_output(gs.reduce(ir.RED_SUM, gs.swap_dims(y, 0, 1), 1))
+    assert "dense column-sum kernel" in hb.Plan.pointwise(None, gs).description
     # catalogue programs keep their hand-written kernels
     gc = ir.Graph()
     a = gc.new_input([16, 40], ir.BF16)

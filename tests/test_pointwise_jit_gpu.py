@@ -104,3 +104,38 @@ def test_bench_program_beyond_l2(ctx, monkeypatch):
     f = [t[:4096].double() for t in tin]
     want = torch.nn.functional.gelu(f[0] + f[1]) * f[2]
     assert torch.allclose(out[:4096].double(), want, rtol=1e-2, atol=1e-2)
+
+
+def _reduce_graph(shape, depth, dt, column=False):
+    g = ir.Graph()
+    a = g.new_input(list(shape), dt); b = g.new_input(list(shape), dt)
+    t = g.binary(ir.BIN_MUL, g.unary(ir.UN_TANH, a), b)
+    if column:
+        t = g.swap_dims(t, 0, 1)
+    g.new_output(g.reduce(ir.RED_SUM, t, depth))
+    g.new_output(g.reduce(ir.RED_MAX, t, depth))
+    g.new_output(g.reduce(ir.RED_MEAN, g.unary(ir.UN_RELU, t), depth))
+    return g
+
+
+@pytest.mark.parametrize("shape,depth,column", [((256, 10), 1, False), ((3, 70001), 1, False), ((64, 33, 7), 2, False),
+                                                ((1 << 20,), 1, False), ((1000, 96), 1, True), ((37, 5), 2, False)],
+                         ids=["warp_per_group", "cta_slices_multi", "cta_slices_one", "one_group", "column_mode", "tiny"])
+@pytest.mark.parametrize("dt", [ir.F32, ir.BF16])
+def test_reductions_with_prologues(ctx, monkeypatch, shape, depth, column, dt):
+    """Reductions over a pointwise prologue: the specialised reduction kernel walks and combines exactly like the
+    interpreter's (same bits, every launch mode), and both sit within the oracle's f32 tolerance."""
+    g = _reduce_graph(shape, depth, dt, column)
+    ins = _inputs(g, False, 9)
+    got, plan = _launch(ctx, g, ins, True, monkeypatch)
+    assert SPECIALISED in plan.description, plan.description
+    ref, plan0 = _launch(ctx, g, ins, False, monkeypatch)
+    assert "interpreter" in plan0.description
+    for a, b in zip(got, ref):
+        assert np.array_equal(np.asarray(a).view(np.uint8), np.asarray(b).view(np.uint8))
+    want = O.evaluate(g, ins)
+    for o, g_, w_ in zip(g.outputs, got, want):
+        node = g.nodes[o]
+        a = O.decode(g_, node.dtype, node.shape).reshape(-1)
+        b = O.decode(w_, node.dtype, node.shape).reshape(-1)
+        assert np.allclose(a, b, rtol=2e-5, atol=2e-5 * max(1.0, float(np.abs(b).max()))), float(np.abs(a - b).max())
