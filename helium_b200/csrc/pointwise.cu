@@ -149,9 +149,31 @@ __global__ void __launch_bounds__(kPwThreads) pw_reduce_finalize_warp_kernel(con
   if (lane == 0) F.out[s][g] = v;
 }
 
+// Thousands of partials per group: a CTA per (reduction, group); thread t combines partials t, t + 256, ... in
+// order, a shuffle tree per warp, then the eight warp values in warp order.
+__global__ void __launch_bounds__(kPwThreads) pw_reduce_finalize_cta_kernel(const __grid_constant__ PwFinalize F) {
+  __shared__ float sw[kPwThreads / 32];
+  const uint32_t w = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const uint32_t s = w / F.num_groups, g = w - s * F.num_groups;
+  const float* p = F.partials + ((size_t)s * F.num_groups + g) * F.blocks_per_group;
+  float v = pw_reduce_identity(F.red_ops[s]);
+#pragma unroll 4
+  for (uint32_t b = threadIdx.x; b < F.blocks_per_group; b += kPwThreads) v = pw_reduce_combine(F.red_ops[s], v, p[b]);
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) v = pw_reduce_combine(F.red_ops[s], v, __shfl_down_sync(0xffffffffu, v, off));
+  if (lane == 0) sw[warp] = v;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float t = sw[0];
+    for (int k = 1; k < kPwThreads / 32; ++k) t = pw_reduce_combine(F.red_ops[s], t, sw[k]);
+    F.out[s][g] = t;
+  }
+}
+
 int32_t launch_finalize(const PwFinalize& F, cudaStream_t stream) {
   const uint32_t items = F.num_groups * (uint32_t)F.n_red;
-  if (F.blocks_per_group >= 64) pw_reduce_finalize_warp_kernel<<<(items * 32 + kPwThreads - 1) / kPwThreads, kPwThreads, 0, stream>>>(F);
+  if (F.blocks_per_group >= 1024) pw_reduce_finalize_cta_kernel<<<items, kPwThreads, 0, stream>>>(F);
+  else if (F.blocks_per_group >= 64) pw_reduce_finalize_warp_kernel<<<(items * 32 + kPwThreads - 1) / kPwThreads, kPwThreads, 0, stream>>>(F);
   else pw_reduce_finalize_kernel<<<(items + kPwThreads - 1) / kPwThreads, kPwThreads, 0, stream>>>(F);
   HE_CUDA(cudaGetLastError());
   return HE_OK;

@@ -330,10 +330,38 @@ __global__ void __launch_bounds__(256) to_f8_transpose_kernel(const void* __rest
   __shared__ float tile[64][65];
   const long long b = blockIdx.z;
   const long long r0 = (long long)blockIdx.x * 64, k0 = (long long)blockIdx.y * 64;
-  const int tx = threadIdx.x & 63, ty = threadIdx.x >> 6;   // 64 x 4
-  for (int kk = ty; kk < 64; kk += 4) {
-    const long long kq = k0 + kk, r = r0 + tx;
-    tile[kk][tx] = (kq < k && r < rows) ? load_as_f32(src, dt, (b * k + kq) * rows + r) : 0.0f;
+  // a thread reads 8 consecutive rows' worth of one k (one 16-byte load of 2-byte elements, two of f32), twice
+#pragma unroll
+  for (int pass = 0; pass < 2; ++pass) {
+    const int kk = (threadIdx.x >> 3) + 32 * pass, ro = (threadIdx.x & 7) * 8;
+    const long long kq = k0 + kk, r = r0 + ro;
+    float v[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = 0.0f;
+    if (kq < k && r < rows) {
+      const long long e = (b * k + kq) * rows + r;
+      const char* ptr = reinterpret_cast<const char*>(src) + e * (dt == HE_F32 ? 4 : 2);
+      if (r + 8 <= rows && (reinterpret_cast<uintptr_t>(ptr) & 15) == 0) {
+        if (dt == HE_F32) {
+          const float4 a = __ldcs(reinterpret_cast<const float4*>(ptr)), c = __ldcs(reinterpret_cast<const float4*>(ptr) + 1);
+          v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = c.x; v[5] = c.y; v[6] = c.z; v[7] = c.w;
+        } else {
+          const uint4 a = __ldcs(reinterpret_cast<const uint4*>(ptr));
+          const unsigned w[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            v[2 * j] = dt == HE_BF16 ? __uint_as_float(w[j] << 16) : f16_bits_to_f32(w[j] & 0xffffu);
+            v[2 * j + 1] = dt == HE_BF16 ? __uint_as_float(w[j] & 0xffff0000u) : f16_bits_to_f32(w[j] >> 16);
+          }
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          if (r + j < rows) v[j] = load_as_f32(src, dt, e + j);
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) tile[kk][ro + j] = v[j];
   }
   __syncthreads();
   // a thread writes 16 consecutive k of one row: 4 threads per row, 64 rows
