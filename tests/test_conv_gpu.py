@@ -145,3 +145,46 @@ def test_batch128_layers(ctx, geom):
     want = tw.grad.permute(0, 2, 3, 1).numpy().astype(np.float64)
     err = O.rel_l2(_dec(dw, w.shape), want)
     assert err <= 1e-2, (err, plan.description)
+
+
+def test_reference_conv_vector_through_the_c_abi(ctx):
+    """helium/tests/tensor_ops.rs:379-397 (`conv_simple`: x = [1, 2], w = [[10, 20], [30, 40]], 1 x 1, Same ->
+    [50, 110]) replayed on the GPU.  The kernels take channel counts that are multiples of 8 (a 16-byte pixel for
+    TMA), so the two channels are zero-padded to eight on both sides; every value is exact in bf16 and f16."""
+    for dt in (ir.BF16, ir.F16):
+        x = np.zeros((1, 1, 1, 8)); x[0, 0, 0, :2] = [1.0, 2.0]
+        w = np.zeros((8, 1, 1, 8)); w[0, 0, 0, :2] = [10.0, 20.0]; w[1, 0, 0, :2] = [30.0, 40.0]
+        plan = hb.Plan.conv2d(ctx, "fwd", batch=1, in_hw=(1, 1), in_channels=8, out_channels=8, kernel=(1, 1), stride=1, dtype=dt,
+                              out_dtype=ir.F32)
+        import torch
+        tin = [storage_to_torch(O.encode(x, dt), dt), storage_to_torch(O.encode(w, dt), dt)]
+        (y,) = plan.launch(tin)
+        torch.cuda.synchronize()
+        ctx.poll()
+        assert y.shape == (1, 1, 1, 8)
+        assert y.reshape(-1).tolist() == [50.0, 110.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0]
+
+
+@pytest.mark.parametrize("geom", [(12, 12, 16, 24, 3, 3, 1), (14, 10, 8, 16, 3, 3, 2)], ids=lambda g: "x".join(map(str, g)))
+def test_f16_convolutions(ctx, geom):
+    """The same three kernels on f16 images and filters (tcgen05 kind::f16 with the f16 operand format), f32 outputs
+    so that only the products' input rounding and the f32 accumulation order separate them from the oracle."""
+    import torch
+    H, W, C, K, R, S, st = geom
+    batch = 3
+    r = rng(15)
+    f16 = lambda shape, s=1.0: O.encode(r.standard_normal(shape) * s, ir.F16)
+    (P, Q), _ = O.conv_geometry((H, W), (R, S), (st, st))
+    x, w, dy = f16((batch, H, W, C)), f16((K, R, S, C), 1.0 / np.sqrt(R * S * C)), f16((batch, P, Q, K))
+    dec = lambda b, shape: O.decode(b, ir.F16, shape)
+    kw = dict(batch=batch, in_hw=(H, W), in_channels=C, out_channels=K, kernel=(R, S), stride=st, dtype=ir.F16, out_dtype=ir.F32)
+    def run(kind, ins):
+        plan = hb.Plan.conv2d(ctx, kind, **kw)
+        (o,) = plan.launch([storage_to_torch(a, ir.F16) for a in ins])
+        torch.cuda.synchronize()
+        ctx.poll()
+        return o.cpu().numpy().astype(np.float64)
+    xv, wv, dyv = dec(x, (batch, H, W, C)), dec(w, (K, R, S, C)), dec(dy, (batch, P, Q, K))
+    assert O.rel_l2(run("fwd", [x, w]), O.conv2d(xv, wv, (st, st))) <= 1e-5
+    assert O.rel_l2(run("bwd_data", [dy, w]), O.conv2d_backward_data(dyv, wv, (H, W), (st, st))) <= 1e-5
+    assert O.rel_l2(run("bwd_filter", [dy, x]), O.conv2d_backward_filter(dyv, xv, (R, S), (st, st))) <= 1e-5
