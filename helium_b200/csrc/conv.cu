@@ -96,26 +96,26 @@ __global__ void conv_wgrad_fold(const float* __restrict__ partials, void* __rest
   else reinterpret_cast<unsigned short*>(out)[i] = (unsigned short)(out_dt == HE_BF16 ? f32_to_bf16_bits(s) : f32_to_f16_bits(s));
 }
 
-// out[2][N] = column sums of the two statistics partial blocks [rows][N].  A CTA is 32 columns x 8 row lanes:
-// lane y adds rows y, y + 8, ... in order (independent loads, so the L2 latency is paid once per few rows, not
-// once per row), and the eight lane sums meet in shared memory in lane order -- a fixed function of the
+// out[2][N] = column sums of the two statistics partial blocks [rows][N].  A CTA is 32 columns x 32 row lanes:
+// lane y adds rows y, y + 32, ... in order (independent loads, so the L2 latency is paid once per few rows, not
+// once per row), and the 32 lane sums meet in shared memory in lane order -- a fixed function of the
 // partials, bit-stable across launches.
-__global__ void __launch_bounds__(256) conv_stats_fold(const float* __restrict__ p0, const float* __restrict__ p1, float* __restrict__ out,
+__global__ void __launch_bounds__(1024) conv_stats_fold(const float* __restrict__ p0, const float* __restrict__ p1, float* __restrict__ out,
                                                        int rows, int N) {
-  __shared__ float sh[8][33];
+  __shared__ float sh[32][33];
   const int i = blockIdx.x * 32 + threadIdx.x;
   float s = 0.0f;
   if (i < 2 * N) {
     const float* p = (i < N ? p0 : p1) + (i < N ? i : i - N);
 #pragma unroll 4
-    for (int r = threadIdx.y; r < rows; r += 8) s += p[(size_t)r * N];
+    for (int r = threadIdx.y; r < rows; r += 32) s += p[(size_t)r * N];
   }
   sh[threadIdx.y][threadIdx.x] = s;
   __syncthreads();
   if (threadIdx.y == 0 && i < 2 * N) {
     float t = sh[0][threadIdx.x];
 #pragma unroll
-    for (int y = 1; y < 8; ++y) t += sh[y][threadIdx.x];
+    for (int y = 1; y < 32; ++y) t += sh[y][threadIdx.x];
     out[i] = t;
   }
 }
@@ -257,7 +257,7 @@ struct ConvPlan : he_plan {
     }
     if (fus.want_stats) {
       float* st = reinterpret_cast<float*>(outputs[1]);
-      conv_stats_fold<<<(2 * Nout + 31) / 32, dim3(32, 8), 0, stream>>>(ws + ws_stat_off[0], ws + ws_stat_off[1], st, total_tiles_m, Nout);
+      conv_stats_fold<<<(2 * Nout + 31) / 32, dim3(32, 32), 0, stream>>>(ws + ws_stat_off[0], ws + ws_stat_off[1], st, total_tiles_m, Nout);
       HE_CUDA(cudaGetLastError());
       ++last_launches;
     }

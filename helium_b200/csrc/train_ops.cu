@@ -103,22 +103,22 @@ __global__ void __launch_bounds__(256) bn_apply_kernel(const uint4* __restrict__
   }
 }
 
-// stats[i] = sum over the CTAs' partial rows, 32 columns x 8 row lanes per CTA: lane y adds rows y, y + 8, ...
+// stats[i] = sum over the CTAs' partial rows, 32 columns x 32 row lanes per CTA: lane y adds rows y, y + 32, ...
 // in order and the lane sums meet in shared memory in lane order (a fixed function of the partials).
-__global__ void __launch_bounds__(256) bn_fold_partials(const float* __restrict__ partials, float* __restrict__ stats, int n_parts, int C2) {
-  __shared__ float sh[8][33];
+__global__ void __launch_bounds__(1024) bn_fold_partials(const float* __restrict__ partials, float* __restrict__ stats, int n_parts, int C2) {
+  __shared__ float sh[32][33];
   const int i = blockIdx.x * 32 + threadIdx.x;
   float s = 0.0f;
   if (i < C2) {
 #pragma unroll 4
-    for (int k = threadIdx.y; k < n_parts; k += 8) s += partials[(size_t)k * C2 + i];
+    for (int k = threadIdx.y; k < n_parts; k += 32) s += partials[(size_t)k * C2 + i];
   }
   sh[threadIdx.y][threadIdx.x] = s;
   __syncthreads();
   if (threadIdx.y == 0 && i < C2) {
     float t = sh[0][threadIdx.x];
 #pragma unroll
-    for (int y = 1; y < 8; ++y) t += sh[y][threadIdx.x];
+    for (int y = 1; y < 32; ++y) t += sh[y][threadIdx.x];
     stats[i] = t;
   }
 }
@@ -456,7 +456,7 @@ int32_t he_bn_apply(const void* x, void* y, const float* scale, const float* shi
     if (relu) bn_apply_kernel<true, true><<<grid, 256, 256 * 16 * 4, st>>>(xi, yo, scale, shift, pixels, channels, parts);
     else bn_apply_kernel<true, false><<<grid, 256, 256 * 16 * 4, st>>>(xi, yo, scale, shift, pixels, channels, parts);
     HE_CUDA(cudaGetLastError());
-    bn_fold_partials<<<(2 * channels + 31) / 32, dim3(32, 8), 0, st>>>(parts, stats_out, grid, 2 * channels);
+    bn_fold_partials<<<(2 * channels + 31) / 32, dim3(32, 32), 0, st>>>(parts, stats_out, grid, 2 * channels);
   } else {
     if (relu) bn_apply_kernel<false, true><<<grid, 256, 0, st>>>(xi, yo, scale, shift, pixels, channels, nullptr);
     else bn_apply_kernel<false, false><<<grid, 256, 0, st>>>(xi, yo, scale, shift, pixels, channels, nullptr);
@@ -494,7 +494,7 @@ int32_t he_bn_backward_apply(const void* g, const void* x, const void* addend, v
     if (addend) bn_backward_apply_kernel<true, true><<<grid, 256, 256 * 16 * 4, st>>>(G, X, E, O, coef, MX, mask_scale, mask_shift, pixels, channels, parts);
     else bn_backward_apply_kernel<false, true><<<grid, 256, 256 * 16 * 4, st>>>(G, X, E, O, coef, MX, mask_scale, mask_shift, pixels, channels, parts);
     HE_CUDA(cudaGetLastError());
-    bn_fold_partials<<<(2 * channels + 31) / 32, dim3(32, 8), 0, st>>>(parts, stats_out, grid, 2 * channels);
+    bn_fold_partials<<<(2 * channels + 31) / 32, dim3(32, 32), 0, st>>>(parts, stats_out, grid, 2 * channels);
   } else if (stats_out) {
     // no mask: the statistics output is [C] column sums of `out` as stored (the bias gradient of the convolution
     // this flow enters next), folded from per-CTA partials in CTA order
@@ -502,7 +502,7 @@ int32_t he_bn_backward_apply(const void* g, const void* x, const void* addend, v
     if (addend) bn_backward_apply_kernel<true, false, true><<<grid, 256, 256 * 8 * 4, st>>>(G, X, E, O, coef, nullptr, nullptr, nullptr, pixels, channels, parts);
     else bn_backward_apply_kernel<false, false, true><<<grid, 256, 256 * 8 * 4, st>>>(G, X, E, O, coef, nullptr, nullptr, nullptr, pixels, channels, parts);
     HE_CUDA(cudaGetLastError());
-    bn_fold_partials<<<(channels + 31) / 32, dim3(32, 8), 0, st>>>(parts, stats_out, grid, channels);
+    bn_fold_partials<<<(channels + 31) / 32, dim3(32, 32), 0, st>>>(parts, stats_out, grid, channels);
   } else {
     if (addend) bn_backward_apply_kernel<true, false><<<grid, 256, 0, st>>>(G, X, E, O, coef, nullptr, nullptr, nullptr, pixels, channels, nullptr);
     else bn_backward_apply_kernel<false, false><<<grid, 256, 0, st>>>(G, X, E, O, coef, nullptr, nullptr, nullptr, pixels, channels, nullptr);
@@ -530,7 +530,7 @@ int32_t he_colsum_bf16(const void* x, float* out, void* workspace, int64_t pixel
   float* parts = reinterpret_cast<float*>(workspace);
   colsum_bf16_kernel<<<grid, 256, 256 * 8 * 4, st>>>(reinterpret_cast<const uint4*>(x), pixels, channels, parts);
   HE_CUDA(cudaGetLastError());
-  bn_fold_partials<<<(channels + 31) / 32, dim3(32, 8), 0, st>>>(parts, out, grid, channels);
+  bn_fold_partials<<<(channels + 31) / 32, dim3(32, 32), 0, st>>>(parts, out, grid, channels);
   HE_CUDA(cudaGetLastError());
   return HE_OK;
 }
