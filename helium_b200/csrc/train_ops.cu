@@ -377,6 +377,14 @@ __global__ void __launch_bounds__(256) im2col_kernel(const unsigned short* __res
     off[j] = k < rsc ? r * row_pitch + (k - r * sc) : -1;
   }
   const int pix_step = st * C;
+  bool all_valid = true;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) all_valid = all_valid && off[j] >= 0;
+  // staging slots of this thread within a source row (the same for every row and tile): element index and the
+  // source pixel it belongs to, so that the loop below does no division
+  int slot_w[4];
+#pragma unroll
+  for (int q = 0; q < 4; ++q) slot_w[q] = (threadIdx.x + 256 * q) / C;
   for (long long tile = blockIdx.x; tile < (long long)NB * P * q_tiles; tile += gridDim.x) {
     const int qt = (int)(tile % q_tiles);
     const long long np = tile / q_tiles;
@@ -387,7 +395,15 @@ __global__ void __launch_bounds__(256) im2col_kernel(const unsigned short* __res
       const int h = p * st + r - pad_h;
       const bool row_ok = h >= 0 && h < H;
       const unsigned short* src = x + (((long long)n * H + h) * W + w0) * C;
-      for (int e = threadIdx.x; e < row_pitch; e += 256) {
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const int e = threadIdx.x + 256 * q;
+        if (e < row_pitch) {
+          const int w = w0 + slot_w[q];
+          srow[r * row_pitch + e] = (row_ok && w >= 0 && w < W) ? __ldg(src + e) : (unsigned short)0;
+        }
+      }
+      for (int e = threadIdx.x + 1024; e < row_pitch; e += 256) {   // rows longer than 1024 elements (wide tiles of many channels)
         const int w = w0 + e / C;
         srow[r * row_pitch + e] = (row_ok && w >= 0 && w < W) ? __ldg(src + e) : (unsigned short)0;
       }
@@ -396,12 +412,22 @@ __global__ void __launch_bounds__(256) im2col_kernel(const unsigned short* __res
     const int nq = min(imq, Q - q0);
     if (grp < groups) {
       uint4* dst = cols + (((size_t)n * P + p) * Q + q0) * vec_per_pix + v;
-      for (int ql = grp; ql < nq; ql += groups) {
-        const unsigned short* sp = srow + ql * pix_step;
-        uint32_t e[8];
+      if (all_valid) {
+        for (int ql = grp; ql < nq; ql += groups) {
+          const unsigned short* sp = srow + ql * pix_step;
+          uint32_t e[8];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) e[j] = off[j] >= 0 ? (uint32_t)sp[off[j]] : 0u;
-        dst[(size_t)ql * vec_per_pix] = make_uint4(e[0] | (e[1] << 16), e[2] | (e[3] << 16), e[4] | (e[5] << 16), e[6] | (e[7] << 16));
+          for (int j = 0; j < 8; ++j) e[j] = sp[off[j]];
+          dst[(size_t)ql * vec_per_pix] = make_uint4(e[0] | (e[1] << 16), e[2] | (e[3] << 16), e[4] | (e[5] << 16), e[6] | (e[7] << 16));
+        }
+      } else {
+        for (int ql = grp; ql < nq; ql += groups) {
+          const unsigned short* sp = srow + ql * pix_step;
+          uint32_t e[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) e[j] = off[j] >= 0 ? (uint32_t)sp[off[j]] : 0u;
+          dst[(size_t)ql * vec_per_pix] = make_uint4(e[0] | (e[1] << 16), e[2] | (e[3] << 16), e[4] | (e[5] << 16), e[6] | (e[7] << 16));
+        }
       }
     }
   }

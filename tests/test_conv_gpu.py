@@ -188,3 +188,33 @@ def test_f16_convolutions(ctx, geom):
     assert O.rel_l2(run("fwd", [x, w]), O.conv2d(xv, wv, (st, st))) <= 1e-5
     assert O.rel_l2(run("bwd_data", [dy, w]), O.conv2d_backward_data(dyv, wv, (H, W), (st, st))) <= 1e-5
     assert O.rel_l2(run("bwd_filter", [dy, x]), O.conv2d_backward_filter(dyv, xv, (R, S), (st, st))) <= 1e-5
+
+
+@pytest.mark.parametrize("case", [(2, 20, 20, 3, 7, 7, 2, 152), (3, 9, 13, 4, 5, 5, 1, 104), (1, 300, 6, 2, 3, 3, 2, 24), (2, 16, 16, 8, 1, 1, 1, 8)],
+                         ids=lambda c: "x".join(map(str, c)))
+def test_patch_matrix(ctx, case):
+    """he_im2col_nhwc against a direct numpy gather: cols[n, p, q, (r * S + s) * C + c] = x[n, p st + r - R/2,
+    q st + s - S/2, c], zero outside the image and in the padding columns -- bit for bit (it only moves values)."""
+    import ctypes as C
+    import torch
+    from helium_b200._lib import check, lib
+    n, h, w, c, R, S, st, pitch = case
+    r = rng(16)
+    x = bf16_normal(r, (n, h, w, c))
+    P, Q = h // st, w // st
+    want = np.zeros((n, P, Q, pitch), dtype=np.uint16)
+    for rr in range(R):
+        for ss in range(S):
+            for p in range(P):
+                hh = p * st + rr - R // 2
+                if not 0 <= hh < h:
+                    continue
+                for q in range(Q):
+                    ww = q * st + ss - S // 2
+                    if 0 <= ww < w:
+                        want[:, p, q, (rr * S + ss) * c:(rr * S + ss + 1) * c] = x[:, hh, ww, :]
+    tx = storage_to_torch(x, ir.BF16)
+    cols = torch.full((n, P, Q, pitch), 7.0, dtype=torch.bfloat16, device="cuda")
+    check(lib.he_im2col_nhwc(tx.data_ptr(), cols.data_ptr(), n, h, w, c, R, S, st, pitch, C.c_void_p(torch.cuda.current_stream().cuda_stream)))
+    torch.cuda.synchronize()
+    assert np.array_equal(cols.view(torch.int16).cpu().numpy().view(np.uint16), want)
