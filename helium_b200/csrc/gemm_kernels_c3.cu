@@ -7,10 +7,12 @@ namespace he {
 int32_t launch_gemm_c3(const GemmLaunchCfg& cfg, const GemmParams<EpiC3Params>& p, cudaStream_t stream) {
   if (cfg.two_cta && cfg.bn == 256) {
     if (cfg.ml == ML_NONE) return launch_majors_2cta<6, ML_NONE, 8, EpiC3>(cfg, p, stream);
+    if (cfg.ml == ML_F8 && !cfg.a_mn && !cfg.b_mn) return launch_one_2cta<6, false, false, ML_F8, 8, EpiC3>(cfg, p, stream);
     if (cfg.ml == ML_RELU_MASK) return launch_majors_2cta<4, ML_RELU_MASK, 8, EpiC3>(cfg, p, stream);
   }
   if (cfg.bn == 256) {
     if (cfg.ml == ML_NONE) return launch_majors<256, 4, ML_NONE, 8, EpiC3>(cfg, p, stream);
+    if (cfg.ml == ML_F8 && !cfg.a_mn && !cfg.b_mn) return launch_one<256, 4, false, false, ML_F8, 8, EpiC3>(cfg, p, stream);
     if (cfg.ml == ML_RELU_MASK) return launch_majors<256, 3, ML_RELU_MASK, 8, EpiC3>(cfg, p, stream);
   }
   HE_FAIL(HE_ERR_UNSUPPORTED, "fused matmul: no kernel compiled for bn=%d mainloop=%d with this epilogue", cfg.bn, cfg.ml);

@@ -17,7 +17,7 @@ int32_t launch_one(const GemmLaunchCfg& cfg, const GemmParams<typename Epi::Para
     HE_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SM::dynamic_bytes));
     configured = true;
   }
-  constexpr int threads = 32 * (2 + NE_WARPS + (ML != ML_NONE ? 4 : 0));
+  constexpr int threads = 32 * (2 + NE_WARPS + (ml_transforms(ML) ? 4 : 0));
   kernel<<<cfg.grid, threads, SM::dynamic_bytes, stream>>>(p);
   HE_CUDA(cudaGetLastError());
   return HE_OK;
@@ -29,7 +29,7 @@ int32_t launch_one_2cta(const GemmLaunchCfg& cfg, const GemmParams<typename Epi:
   using SM = GemmSmem2<STAGES, ML, Epi::kColReductions>;
   auto kernel = gemm_tcgen05_2cta_kernel<STAGES, A_MN, B_MN, ML, NE_WARPS, Epi>;
   static_assert(SM::dynamic_bytes <= 232448, "shared memory budget of sm_100 exceeded");
-  constexpr int threads = 32 * (2 + NE_WARPS + (ML != ML_NONE ? 4 : 0));
+  constexpr int threads = 32 * (2 + NE_WARPS + (ml_transforms(ML) ? 4 : 0));
   static int max_pairs = 0;  // benign race: idempotent
   if (max_pairs == 0) {
     HE_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SM::dynamic_bytes));

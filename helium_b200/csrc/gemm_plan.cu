@@ -999,6 +999,7 @@ int32_t plan_fused_matmul_core(he_ctx* ctx, const Graph& g, he_plan** out, int* 
       plan->f8_src_mn[0] = plan->cfg.a_mn; plan->f8_src_mn[1] = plan->cfg.b_mn;
       plan->f8_src_dt[0] = An.dtype; plan->f8_src_dt[1] = Bn.dtype;
       plan->cfg.a_mn = plan->cfg.b_mn = false;   // the copies are K-major
+      plan->cfg.ml = ML_F8;                      // kernels instantiated for 8-bit tiles
       c.f8 = plan->f8;
     }
   }

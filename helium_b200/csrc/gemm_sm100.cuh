@@ -28,7 +28,10 @@ constexpr int kUmmaK = 16;
 // ML_RELU | ML_MASK is the hand-written relu(A) * mask rewrite on packed bf16 pairs.  ML_GENERIC runs a short
 // program of unary steps and at most one elementwise multiply / add with a second tensor (staged like the mask,
 // ML_MASK then says that tensor exists) on the A tile, and a unary-only program on the B tile (single-CTA kernel).
-enum MainloopKind : int { ML_NONE = 0, ML_RELU = 1, ML_MASK = 2, ML_RELU_MASK = 3, ML_GENERIC = 4, ML_GENERIC_MASK = 6 };
+enum MainloopKind : int { ML_NONE = 0, ML_RELU = 1, ML_MASK = 2, ML_RELU_MASK = 3, ML_GENERIC = 4, ML_GENERIC_MASK = 6,
+                          ML_F8 = 8 };   // ML_F8: plain mainloop over 8-bit operand tiles (tcgen05 kind::f8f6f4), no rewrite
+// true when transform warps rewrite the A (and B) tiles between TMA arrival and MMA issue
+__host__ __device__ constexpr bool ml_transforms(int ml) { return (ml & 7) != 0; }
 constexpr int kMlMaxSteps = 6;
 struct MlStep {
   unsigned char kind;   // 0 unary (op = he_unary_op, imm = constant bits), 1 multiply by the second tensor, 2 add it
@@ -903,7 +906,7 @@ __device__ __forceinline__ void epilogue_walk_chunks(const typename Epi::Params&
 }
 
 template <int BN, int STAGES, bool A_MN, bool B_MN, int ML, int NE_WARPS, class Epi>
-__global__ void __launch_bounds__(32 * (2 + NE_WARPS + (ML != ML_NONE ? 4 : 0)), 1)
+__global__ void __launch_bounds__(32 * (2 + NE_WARPS + (ml_transforms(ML) ? 4 : 0)), 1)
 gemm_tcgen05_kernel(const __grid_constant__ GemmParams<typename Epi::Params> p) {
   using SM = GemmSmem<BN, STAGES, ML, Epi::kColReductions>;
   constexpr int kXformWarp0 = 2 + NE_WARPS;
@@ -985,7 +988,7 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmParams<typename Epi::Params> p) 
         for (int kb = 0; kb < c.k_blocks; ++kb) {
           if (!ptx::mbar_wait(bar_empty(stage), phase ^ 1u, abort_flag, c.status, 1, stage, c.wait_limit_us)) { alive = false; break; }
           ptx::mbar_arrive_expect_tx(bar_full(stage), kStageBytes);
-          const int k0 = kb * (c.f8 ? 2 * kBK : kBK);   // 128 bytes of K per block
+          const int k0 = kb * ((ML & ML_F8) ? 2 * kBK : kBK);   // 128 bytes of K per block
           const uint32_t a_dst = smem_base + SM::off_a + stage * kATileBytes;
           const uint32_t b_dst = smem_base + SM::off_b + stage * SM::kBTileBytes;
           if (A_MN) {
@@ -1019,8 +1022,8 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmParams<typename Epi::Params> p) 
   } else if (warp == 1) {
     // ===================== MMA issuer =====================
     if (lane == 0) {
-      const uint32_t idesc = c.f8 ? ptx::make_idesc_f8(c.f8 & 2 ? 1 : 0, c.f8 & 4 ? 1 : 0, kBM, BN)
-                                  : ptx::make_idesc_f16(c.ab_format, A_MN ? 1 : 0, B_MN ? 1 : 0, kBM, BN);
+      const uint32_t idesc = (ML & ML_F8) ? ptx::make_idesc_f8(c.f8 & 2 ? 1 : 0, c.f8 & 4 ? 1 : 0, kBM, BN)
+                                          : ptx::make_idesc_f16(c.ab_format, A_MN ? 1 : 0, B_MN ? 1 : 0, kBM, BN);
       // K-major: 8-row groups 1024 B apart (SBO), K advances 32 B inside the swizzle row.
       // MN-major: 64-element blocks kBK*128 B apart (LBO), 8-k groups 1024 B apart (SBO),
       //           K advances two k-groups = 2048 B per MMA.
@@ -1037,7 +1040,7 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmParams<typename Epi::Params> p) 
         ptx::tcgen05_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
         for (int kb = 0; kb < c.k_blocks; ++kb) {
-          const uint32_t ready = (ML != ML_NONE) ? bar_xform(stage) : bar_full(stage);
+          const uint32_t ready = ml_transforms(ML) ? bar_xform(stage) : bar_full(stage);
           if (!ptx::mbar_wait(ready, phase, abort_flag, c.status, 3, stage, c.wait_limit_us)) { alive = false; break; }
           ptx::tcgen05_fence_after();
           const uint32_t a_addr = smem_base + SM::off_a + stage * kATileBytes;
@@ -1046,7 +1049,7 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmParams<typename Epi::Params> p) 
           for (int k = 0; k < kBK / kUmmaK; ++k) {
             const uint64_t adesc = ptx::make_smem_desc_sw128(a_addr + k * a_kadv, a_lbo, 1024);
             const uint64_t bdesc = ptx::make_smem_desc_sw128(b_addr + k * b_kadv, b_lbo, 1024);
-            if (c.f8) ptx::umma_f8(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+            if constexpr ((ML & ML_F8) != 0) ptx::umma_f8(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
             else ptx::umma_f16(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
           }
           ptx::umma_commit(bar_empty(stage));   // frees the smem stage when these MMAs retire
@@ -1095,7 +1098,7 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmParams<typename Epi::Params> p) 
     }
   } else {
     // ===================== mainloop transform =====================
-    if (ML != ML_NONE) {
+    if (ml_transforms(ML)) {
       const int tt = (warp - kXformWarp0) * 32 + lane;  // 0..127
       int stage = 0;
       uint32_t phase = 0;

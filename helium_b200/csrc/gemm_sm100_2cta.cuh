@@ -96,14 +96,14 @@ struct GemmSmem2 {
 };
 
 template <int STAGES, bool A_MN, bool B_MN, int ML, int NE_WARPS, class Epi>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(32 * (2 + NE_WARPS + (ML != ML_NONE ? 4 : 0)), 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(32 * (2 + NE_WARPS + (ml_transforms(ML) ? 4 : 0)), 1)
 gemm_tcgen05_2cta_kernel(const __grid_constant__ GemmParams<typename Epi::Params> p) {
   using SM = GemmSmem2<STAGES, ML, Epi::kColReductions>;
   constexpr int BN = kBN2;
   constexpr int kXformWarp0 = 2 + NE_WARPS;
   constexpr int kTmemCols = 512;
   constexpr int CH = Epi::kChunk;
-  constexpr bool kFused = ML != ML_NONE;
+  constexpr bool kFused = ml_transforms(ML);
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   const uint32_t smem_base = ptx::smem_u32(smem);
@@ -210,7 +210,7 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ GemmParams<typename Epi::Params
           // same time, so a wave that starts where the previous one stopped finds the tail of the operand
           // panels it shares with that wave still in L2 (the sum order within a tile changes, the result
           // stays a fixed function of the inputs).
-          const int k0 = ((c.k_serpentine && (it & 1)) ? c.k_blocks - 1 - kb : kb) * (c.f8 ? 2 * kBK : kBK);   // 128 bytes of K per block
+          const int k0 = ((c.k_serpentine && (it & 1)) ? c.k_blocks - 1 - kb : kb) * ((ML & ML_F8) ? 2 * kBK : kBK);   // 128 bytes of K per block
           const uint32_t a_dst = smem_base + SM::off_a + stage * kATileBytes;
           const uint32_t b_dst = smem_base + SM::off_b + stage * kBHalfBytes;
           // A (and the mask): this CTA's 128 rows
@@ -253,10 +253,10 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ GemmParams<typename Epi::Params
   } else if (warp == 1) {
     // ===================== MMA issuer (leader CTA only) =====================
     if (lane == 0 && leader) {
-      const uint32_t idesc_full = c.f8 ? ptx::make_idesc_f8(c.f8 & 2 ? 1 : 0, c.f8 & 4 ? 1 : 0, 256, BN)
-                                       : ptx::make_idesc_f16(c.ab_format, A_MN ? 1 : 0, B_MN ? 1 : 0, 256, BN);
-      const uint32_t idesc_half = c.f8 ? ptx::make_idesc_f8(c.f8 & 2 ? 1 : 0, c.f8 & 4 ? 1 : 0, 256, BN / 2)
-                                       : ptx::make_idesc_f16(c.ab_format, A_MN ? 1 : 0, B_MN ? 1 : 0, 256, BN / 2);
+      const uint32_t idesc_full = (ML & ML_F8) ? ptx::make_idesc_f8(c.f8 & 2 ? 1 : 0, c.f8 & 4 ? 1 : 0, 256, BN)
+                                               : ptx::make_idesc_f16(c.ab_format, A_MN ? 1 : 0, B_MN ? 1 : 0, 256, BN);
+      const uint32_t idesc_half = (ML & ML_F8) ? ptx::make_idesc_f8(c.f8 & 2 ? 1 : 0, c.f8 & 4 ? 1 : 0, 256, BN / 2)
+                                               : ptx::make_idesc_f16(c.ab_format, A_MN ? 1 : 0, B_MN ? 1 : 0, 256, BN / 2);
       constexpr uint32_t a_lbo = A_MN ? kBK * 128 : 16, b_lbo = B_MN ? kBK * 128 : 16;
       constexpr uint32_t a_kadv = A_MN ? 2048 : 32, b_kadv = B_MN ? 2048 : 32;
       int stage = 0;
@@ -280,7 +280,7 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ GemmParams<typename Epi::Params
           for (int k = 0; k < kBK / kUmmaK; ++k) {
             const uint64_t adesc = ptx::make_smem_desc_sw128(a_addr + k * a_kadv, a_lbo, 1024);
             const uint64_t bdesc = ptx::make_smem_desc_sw128(b_addr + k * b_kadv, b_lbo, 1024);
-            if (c.f8) ptx::umma_f8_2cta(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+            if constexpr ((ML & ML_F8) != 0) ptx::umma_f8_2cta(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
             else ptx::umma_f16_2cta(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
           }
           // free the stage in both CTAs once these MMAs retire
