@@ -196,10 +196,16 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ GemmParams<typename Epi::Params
       uint32_t phase = 0;
       bool alive = true;
       int it = 0;
+      // Loop-invariant fields of the parameter block live in registers: every inline-asm statement below is a
+      // memory barrier to the compiler, so a `c.field` inside the loop is a fresh constant-bank load on the one
+      // thread whose latency per k-block sets the pace of the pipeline.
+      const int k_blocks = c.k_blocks, k_serp = c.k_serpentine;
+      DeviceStatus* const status = c.status;
+      const uint32_t wait_us = c.wait_limit_us;
       for (int tile = pair; alive && !c.withhold_loads && tile < pair_tiles; tile += n_pairs, ++it) {
         const TileInfo t = decode_tile(tile);
-        for (int kb = 0; kb < c.k_blocks; ++kb) {
-          if (!ptx::mbar_wait(bar_empty(stage), phase ^ 1u, abort_flag, c.status, 1, stage, c.wait_limit_us)) { alive = false; break; }
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!ptx::mbar_wait(bar_empty(stage), phase ^ 1u, abort_flag, status, 1, stage, wait_us)) { alive = false; break; }
           const uint32_t leader_full = ptx::mapa(bar_full_b(stage), 0);
           // a half-width tile needs 64 columns of B per CTA: with N-major B that is one of the two
           // 64-column boxes; with K-major B the full 128-row box is fetched and half of it ignored
@@ -210,7 +216,7 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ GemmParams<typename Epi::Params
           // same time, so a wave that starts where the previous one stopped finds the tail of the operand
           // panels it shares with that wave still in L2 (the sum order within a tile changes, the result
           // stays a fixed function of the inputs).
-          const int k0 = ((c.k_serpentine && (it & 1)) ? c.k_blocks - 1 - kb : kb) * ((ML & ML_F8) ? 2 * kBK : kBK);   // 128 bytes of K per block
+          const int k0 = ((k_serp && (it & 1)) ? k_blocks - 1 - kb : kb) * ((ML & ML_F8) ? 2 * kBK : kBK);   // 128 bytes of K per block
           const uint32_t a_dst = smem_base + SM::off_a + stage * kATileBytes;
           const uint32_t b_dst = smem_base + SM::off_b + stage * kBHalfBytes;
           // A (and the mask): this CTA's 128 rows
@@ -263,16 +269,20 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ GemmParams<typename Epi::Params
       uint32_t phase = 0;
       int it = 0;
       bool alive = true;
+      // parameter-block fields in registers (see the producer)
+      const int k_blocks = c.k_blocks, split_from = c.split_count > 0 ? c.split_from : 0x7fffffff;
+      DeviceStatus* const status = c.status;
+      const uint32_t wait_us = c.wait_limit_us;
       for (int tile = pair; alive && tile < pair_tiles; tile += n_pairs, ++it) {
         const int acc = it & 1;
         const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
-        if (!ptx::mbar_wait(bar_tmem_empty(acc), acc_phase ^ 1u, abort_flag, c.status, 2, acc, c.wait_limit_us)) { alive = false; break; }
+        if (!ptx::mbar_wait(bar_tmem_empty(acc), acc_phase ^ 1u, abort_flag, status, 2, acc, wait_us)) { alive = false; break; }
         ptx::tcgen05_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
-        const uint32_t idesc = (c.split_count > 0 && tile >= c.split_from) ? idesc_half : idesc_full;
-        for (int kb = 0; kb < c.k_blocks; ++kb) {
-          if (!ptx::mbar_wait(bar_full_b(stage), phase, abort_flag, c.status, 3, stage, c.wait_limit_us)) { alive = false; break; }
-          if (kFused && !ptx::mbar_wait(bar_xform(stage), phase, abort_flag, c.status, 6, stage, c.wait_limit_us)) { alive = false; break; }
+        const uint32_t idesc = tile >= split_from ? idesc_half : idesc_full;
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!ptx::mbar_wait(bar_full_b(stage), phase, abort_flag, status, 3, stage, wait_us)) { alive = false; break; }
+          if (kFused && !ptx::mbar_wait(bar_xform(stage), phase, abort_flag, status, 6, stage, wait_us)) { alive = false; break; }
           ptx::tcgen05_fence_after();
           const uint32_t a_addr = smem_base + SM::off_a + stage * kATileBytes;
           const uint32_t b_addr = smem_base + SM::off_b + stage * kBHalfBytes;
