@@ -951,7 +951,9 @@ DEFAULT_STEPS = {"c1": 2000, "c2": 200, "c3": 200, "c3f": 200, "c4": 30, "c4g": 
 # what the default N = 1 run times beside its own workload, and the steps each gets
 SUB_RECORDS = (("configs[2] fused matmul 4096^3 (as planned)", "c3", 100), ("configs[2] with the in-kernel mainloop rewrite", "c3f", 100),
                ("configs[1] pointwise + permute", "c2", 100), ("configs[0] MLP training step f32", "c1", 1000),
-               ("configs[4] conv-net training step", "c5", 10))
+               ("configs[4] conv-net training step", "c5", 10),
+               ("plain matmul 8192^3 requested as MulF8AccumF32 (8-bit copies, tcgen05 kind::f8f6f4)", "gemm8", 30),
+               ("stand-alone pointwise programs on 64 Mi-element tensors", "pw", 30))
 
 
 def config_for(key: str, world: int) -> dict:
