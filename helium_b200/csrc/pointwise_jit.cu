@@ -501,8 +501,10 @@ int32_t pw_jit_compile(const PwCompiled& c, std::shared_ptr<PwJitModule>* out) {
   if (!pw_jit_generate(c, &src, &why)) HE_FAIL(HE_ERR_UNSUPPORTED, "pointwise specialisation: %s", why.c_str());
   const Nvrtc& n = nvrtc();
   if (!n.handle) HE_FAIL(HE_ERR_UNSUPPORTED, "pointwise specialisation: %s", n.why.c_str());
+  // process-wide cache by source text; deliberately never destroyed, so that no module is unloaded from a static
+  // destructor after the CUDA runtime has shut down
   static std::mutex cache_mu;
-  static std::map<std::string, std::shared_ptr<PwJitModule>> cache;
+  static auto& cache = *new std::map<std::string, std::shared_ptr<PwJitModule>>();
   {
     std::lock_guard<std::mutex> lk(cache_mu);
     auto it = cache.find(src);
