@@ -369,6 +369,26 @@ def test_native_8bit_multiplication(ctx, monkeypatch, dt, ta, tb):
         assert O.rel_l2(dec(got[0]), dec(wide[0])) > 1e-3
 
 
+@pytest.mark.parametrize("m", [100, 392])
+def test_native_8bit_with_other_epilogue_tiers(ctx, monkeypatch, m):
+    """The 8-bit mainloop under the interpreted epilogue tier (an op outside the catalogue plus a row reduction), on
+    the single-CTA kernel (one row tile) and on the CTA-pair kernel."""
+    monkeypatch.setenv("HE_GEMM_F8", "native")
+    n, k = 264, 520
+    g = ir.Graph()
+    a = g.new_input([m, k], ir.BF16); b = g.new_input([k, n], ir.BF16)
+    t = g.unary(ir.UN_SIN, g.unary(ir.UN_MUL_CONST, g.matmul(a, b, ir.prec_f8(ir.PREC_F8_F32, ir.F8_E4M3, ir.F8_E4M3)), 0.05))
+    g.new_output(t)
+    g.new_output(g.reduce(ir.RED_SUM, t, 1))
+    ins = _gen(g, 93, {})
+    got, plan = _run(ctx, g, ins)
+    assert "kind::f8f6f4" in plan.description and "interpret" in plan.description, plan.description
+    narrow = O.evaluate(g, ins, f8_quantise=True)
+    for o, x, y in zip(g.outputs, got, narrow):
+        node = g.nodes[o]
+        assert O.rel_l2(O.decode(x, node.dtype, node.shape), O.decode(y, node.dtype, node.shape)) <= 1e-5, plan.description
+
+
 def test_gelu_epilogues_at_extreme_arguments(ctx):
     """GELU and gelu' in the GEMM epilogue at arguments far from the random-normal range: the product is
     zero (A = 0), so the outputs are gelu(bias[col]) and gelu'(G[row, col]) of hand-picked values --
