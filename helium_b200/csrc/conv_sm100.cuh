@@ -169,7 +169,7 @@ struct ConvSmem {
   static constexpr int off_bar = off_scratch + scratch_bytes;
   static constexpr int n_bars = 2 * STAGES + 4;
   static constexpr int off_misc = off_bar + n_bars * 8;
-  static constexpr int total = off_misc + 16;
+  static constexpr int total = off_misc + 16 + kConvMaxTaps * (int)sizeof(ConvTap);   // flags, then the tap table
   static constexpr int dynamic_bytes = total + 1024;
 };
 
@@ -241,13 +241,25 @@ __global__ void __launch_bounds__(32 * 10, 1) conv_fprop_kernel(const __grid_con
       int stage = 0;
       uint32_t phase = 0;
       bool alive = true;
+      // This thread's latency between "stage free" and "loads issued" is part of every stage's round trip, and the
+      // round trip over the stages in flight is what paces the kernel.  An indexed read of the tap table in the
+      // kernel-parameter block goes through a generic address (hundreds of cycles), and every inline-asm statement
+      // makes the compiler reload parameter fields: the table goes to shared memory, the fields to registers,
+      // and (tap, channel block) are counted instead of divided.  Measured: 7-8 % on every 3 x 3 layer.
+      ConvTap* const s_taps = reinterpret_cast<ConvTap*>(smem + SM::off_misc + 16);
+      for (int i = 0; i < g.n_taps; ++i) s_taps[i] = g.taps[i];
+      const int c_blocks = g.c_blocks;
+      DeviceStatus* const status = c.status;
+      const uint32_t wait_us = c.wait_limit_us;
       for (int tile = blockIdx.x; alive && !c.withhold_loads && tile < c.num_tiles; tile += gridDim.x) {
         const Origin o = decode(tile);
+        int ti = 0, cb_next = 0;
         for (int kb = 0; kb < k_blocks; ++kb) {
-          if (!ptx::mbar_wait(bar_empty(stage), phase ^ 1u, abort_flag, c.status, 1, stage, c.wait_limit_us)) { alive = false; break; }
+          if (!ptx::mbar_wait(bar_empty(stage), phase ^ 1u, abort_flag, status, 1, stage, wait_us)) { alive = false; break; }
           ptx::mbar_arrive_expect_tx(bar_full(stage), kStageBytes);
-          const int ti = kb / g.c_blocks, cb = kb - ti * g.c_blocks;
-          const ConvTap tp = g.taps[ti];
+          const ConvTap tp = s_taps[ti];
+          const int cb = cb_next;
+          if (++cb_next == c_blocks) { cb_next = 0; ++ti; }
           const uint32_t a_dst = smem_base + SM::off_a + stage * kATileBytes;
           const uint32_t b_dst = smem_base + SM::off_b + stage * SM::kBTileBytes;
           // activation: 64 channels x (tw x th x tn) pixels, shifted by the tap
@@ -437,25 +449,35 @@ __global__ void __launch_bounds__(32 * 6, 1) conv_wgrad_kernel(const __grid_cons
       const uint32_t stage_bytes = kATileBytes + (uint32_t)nt * SM::kBTapBytes;
       int stage = 0;
       uint32_t phase = 0;
+      // the group's taps and the geometry in registers, the pixel-tile coordinates counted instead of divided
+      // (see the producer of conv_fprop_kernel)
+      ConvTap taps[T];
+#pragma unroll
+      for (int t = 0; t < T; ++t) taps[t] = g.taps[min(tap0 + t, g.n_taps - 1)];
+      const int tiles_q = g.tiles_q, tiles_p = g.tiles_p, tw = g.tw, th = g.th, tn = g.tn;
+      DeviceStatus* const status = c.status;
+      const uint32_t wait_us = c.wait_limit_us;
+      int qi = kt_begin % tiles_q, pi = (kt_begin / tiles_q) % tiles_p, ni = kt_begin / (tiles_q * tiles_p);
       for (int kt = kt_begin; kt < kt_end; ++kt) {
-        if (!ptx::mbar_wait(bar_empty(stage), phase ^ 1u, abort_flag, c.status, 1, stage, c.wait_limit_us)) break;
+        if (!ptx::mbar_wait(bar_empty(stage), phase ^ 1u, abort_flag, status, 1, stage, wait_us)) break;
         ptx::mbar_arrive_expect_tx(bar_full(stage), stage_bytes);
-        int m = kt;
-        const int qi = m % g.tiles_q; m /= g.tiles_q;
-        const int pi = m % g.tiles_p; m /= g.tiles_p;
-        const int q0 = qi * g.tw, p0 = pi * g.th, nb0 = m * g.tn;
+        const int q0 = qi * tw, p0 = pi * th, nb0 = ni * tn;
+        if (++qi == tiles_q) { qi = 0; if (++pi == tiles_p) { pi = 0; ++ni; } }
         const uint32_t a_dst = smem_base + SM::off_a + stage * kATileBytes;
         const uint32_t b_dst = smem_base + SM::off_b + stage * SM::kBTileBytes;
         // A = flow^T: 64 pixels (contraction) x 128 output channels, as two boxes of 64 channels
 #pragma unroll
         for (int j = 0; j < kBM / 64; ++j) tma_load_4d(a_dst + j * (kBK * 128), &p.tma_dy, bar_full(stage), m0 + 64 * j, q0, p0, nb0);
         // B = the image shifted by each tap of the group: 64 pixels x BN input channels per tap
-        for (int t = 0; t < nt; ++t) {
-          const ConvTap tp = g.taps[tap0 + t];
 #pragma unroll
-          for (int j = 0; j < BN / 64; ++j)
-            tma_load_4d(b_dst + t * SM::kBTapBytes + j * (kBK * 128), &p.tma_x[tp.map], bar_full(stage), n0 + 64 * j, q0 + tp.dw,
-                        p0 + tp.dh, nb0);
+        for (int t = 0; t < T; ++t) {
+          if (t < nt) {
+            const ConvTap tp = taps[t];
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j)
+              tma_load_4d(b_dst + t * SM::kBTapBytes + j * (kBK * 128), &p.tma_x[tp.map], bar_full(stage), n0 + 64 * j, q0 + tp.dw,
+                          p0 + tp.dh, nb0);
+          }
         }
         if (++stage == STAGES) { stage = 0; phase ^= 1u; }
       }
