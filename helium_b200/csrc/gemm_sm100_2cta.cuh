@@ -104,6 +104,13 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ GemmParams<typename Epi::Params
   constexpr int kTmemCols = 512;
   constexpr int CH = Epi::kChunk;
   constexpr bool kFused = ml_transforms(ML);
+  // Plain mainloops hand shared memory over in units of TWO k-blocks (64 KB per CTA): one barrier wait, one
+  // expect_tx and one pair of commits per eight MMAs instead of per four.  The MMA-issuing thread spends ~65 cycles
+  // per MMA and ~280 per hand-over; with four MMAs (512 tensor-pipe cycles) per hand-over it, not the tensor pipe,
+  // set the pace.  The rewriting mainloops keep one k-block per hand-over (their transform warps pace them).
+  constexpr int KSUB = kFused ? 1 : 2;
+  constexpr int GROUPS = STAGES / KSUB;
+  static_assert(STAGES % KSUB == 0, "stages are handed over in groups of KSUB");
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   const uint32_t smem_base = ptx::smem_u32(smem);
@@ -204,21 +211,26 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ GemmParams<typename Epi::Params
       const uint32_t wait_us = c.wait_limit_us;
       for (int tile = pair; alive && !c.withhold_loads && tile < pair_tiles; tile += n_pairs, ++it) {
         const TileInfo t = decode_tile(tile);
-        for (int kb = 0; kb < k_blocks; ++kb) {
+        for (int kb0 = 0; kb0 < k_blocks; kb0 += KSUB) {
+          const int nsub = min(KSUB, k_blocks - kb0);
           if (!ptx::mbar_wait(bar_empty(stage), phase ^ 1u, abort_flag, status, 1, stage, wait_us)) { alive = false; break; }
           const uint32_t leader_full = ptx::mapa(bar_full_b(stage), 0);
           // a half-width tile needs 64 columns of B per CTA: with N-major B that is one of the two
           // 64-column boxes; with K-major B the full 128-row box is fetched and half of it ignored
           const bool half_b = t.bn < BN && B_MN;
-          if (leader) ptx::mbar_arrive_expect_tx(bar_full_b(stage), kLeaderBytes - (half_b ? kBHalfBytes : 0));
+          if (leader) ptx::mbar_arrive_expect_tx(bar_full_b(stage), (uint32_t)nsub * (kLeaderBytes - (half_b ? kBHalfBytes : 0)));
           if (kFused) ptx::mbar_arrive_expect_tx(bar_full_a(stage), kABytes);
+#pragma unroll
+          for (int u = 0; u < KSUB; ++u) {
+          if (u >= nsub) break;
+          const int kb = kb0 + u, slot = stage * KSUB + u;
           // Every other tile of a CTA walks K backwards.  All pairs are on the same tile count at about the
           // same time, so a wave that starts where the previous one stopped finds the tail of the operand
           // panels it shares with that wave still in L2 (the sum order within a tile changes, the result
           // stays a fixed function of the inputs).
           const int k0 = ((k_serp && (it & 1)) ? k_blocks - 1 - kb : kb) * ((ML & ML_F8) ? 2 * kBK : kBK);   // 128 bytes of K per block
-          const uint32_t a_dst = smem_base + SM::off_a + stage * kATileBytes;
-          const uint32_t b_dst = smem_base + SM::off_b + stage * kBHalfBytes;
+          const uint32_t a_dst = smem_base + SM::off_a + slot * kATileBytes;
+          const uint32_t b_dst = smem_base + SM::off_b + slot * kBHalfBytes;
           // A (and the mask): this CTA's 128 rows
           if (kFused) {
             if (A_MN) {
@@ -228,7 +240,7 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ GemmParams<typename Epi::Params
               ptx::tma_load_3d(a_dst, &p.tma_a, bar_full_a(stage), k0, t.m0, t.b);
             }
             if (SM::kHasMask) {
-              const uint32_t m_dst = smem_base + SM::off_mask + stage * kATileBytes;
+              const uint32_t m_dst = smem_base + SM::off_mask + slot * kATileBytes;
               if (A_MN) {
 #pragma unroll
                 for (int j = 0; j < 2; ++j) ptx::tma_load_3d(m_dst + j * (kBK * 128), &p.tma_mask, bar_full_a(stage), t.m0 + 64 * j, k0, t.b);
@@ -252,7 +264,8 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ GemmParams<typename Epi::Params
           } else {
             ptx::tma_load_3d_2cta(b_dst, &p.tma_b, leader_full, k0, nb0, t.b);
           }
-          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+          }   // u
+          if (++stage == GROUPS) { stage = 0; phase ^= 1u; }
         }
       }
     }
@@ -280,23 +293,29 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ GemmParams<typename Epi::Params
         ptx::tcgen05_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
         const uint32_t idesc = tile >= split_from ? idesc_half : idesc_full;
-        for (int kb = 0; kb < k_blocks; ++kb) {
+        for (int kb0 = 0; kb0 < k_blocks; kb0 += KSUB) {
+          const int nsub = min(KSUB, k_blocks - kb0);
           if (!ptx::mbar_wait(bar_full_b(stage), phase, abort_flag, status, 3, stage, wait_us)) { alive = false; break; }
           if (kFused && !ptx::mbar_wait(bar_xform(stage), phase, abort_flag, status, 6, stage, wait_us)) { alive = false; break; }
           ptx::tcgen05_fence_after();
-          const uint32_t a_addr = smem_base + SM::off_a + stage * kATileBytes;
-          const uint32_t b_addr = smem_base + SM::off_b + stage * kBHalfBytes;
 #pragma unroll
-          for (int k = 0; k < kBK / kUmmaK; ++k) {
-            const uint64_t adesc = ptx::make_smem_desc_sw128(a_addr + k * a_kadv, a_lbo, 1024);
-            const uint64_t bdesc = ptx::make_smem_desc_sw128(b_addr + k * b_kadv, b_lbo, 1024);
-            if constexpr ((ML & ML_F8) != 0) ptx::umma_f8_2cta(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
-            else ptx::umma_f16_2cta(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+          for (int u = 0; u < KSUB; ++u) {
+            if (u >= nsub) break;
+            const int kb = kb0 + u, slot = stage * KSUB + u;
+            const uint32_t a_addr = smem_base + SM::off_a + slot * kATileBytes;
+            const uint32_t b_addr = smem_base + SM::off_b + slot * kBHalfBytes;
+#pragma unroll
+            for (int k = 0; k < kBK / kUmmaK; ++k) {
+              const uint64_t adesc = ptx::make_smem_desc_sw128(a_addr + k * a_kadv, a_lbo, 1024);
+              const uint64_t bdesc = ptx::make_smem_desc_sw128(b_addr + k * b_kadv, b_lbo, 1024);
+              if constexpr ((ML & ML_F8) != 0) ptx::umma_f8_2cta(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+              else ptx::umma_f16_2cta(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+            }
           }
-          // free the stage in both CTAs once these MMAs retire
+          // free the stage (both of its k-blocks) in both CTAs once these MMAs retire
           ptx::umma_commit_2cta(bar_empty(stage));
           ptx::umma_commit_2cta(ptx::mapa(bar_empty(stage), 1));
-          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+          if (++stage == GROUPS) { stage = 0; phase ^= 1u; }
         }
         if (alive) {
           ptx::umma_commit_2cta(bar_tmem_full(acc));
