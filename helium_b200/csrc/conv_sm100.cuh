@@ -178,6 +178,11 @@ template <int BN, int STAGES, bool B_MN>
 __global__ void __launch_bounds__(32 * 10, 1) conv_fprop_kernel(const __grid_constant__ ConvParams p) {
   using SM = ConvSmem<BN, STAGES>;
   constexpr int NE_WARPS = 8;
+  // shared memory is handed over two k-blocks at a time: the MMA-issuing thread spends ~65 cycles per MMA and
+  // ~280 per hand-over (barrier wait, commit, bookkeeping), against 128-256 tensor-pipe cycles per k-block
+  constexpr int KSUB = 2;
+  constexpr int GROUPS = STAGES / KSUB;
+  static_assert(STAGES % KSUB == 0, "stages are handed over in groups of KSUB");
   constexpr int kTmemCols = 2 * BN <= 128 ? 128 : 256;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -254,14 +259,19 @@ __global__ void __launch_bounds__(32 * 10, 1) conv_fprop_kernel(const __grid_con
       for (int tile = blockIdx.x; alive && !c.withhold_loads && tile < c.num_tiles; tile += gridDim.x) {
         const Origin o = decode(tile);
         int ti = 0, cb_next = 0;
-        for (int kb = 0; kb < k_blocks; ++kb) {
+        for (int kb0 = 0; kb0 < k_blocks; kb0 += KSUB) {
+          const int nsub = min(KSUB, k_blocks - kb0);
           if (!ptx::mbar_wait(bar_empty(stage), phase ^ 1u, abort_flag, status, 1, stage, wait_us)) { alive = false; break; }
-          ptx::mbar_arrive_expect_tx(bar_full(stage), kStageBytes);
+          ptx::mbar_arrive_expect_tx(bar_full(stage), (uint32_t)nsub * kStageBytes);
+#pragma unroll
+          for (int u = 0; u < KSUB; ++u) {
+          if (u >= nsub) break;
+          const int slot = stage * KSUB + u;
           const ConvTap tp = s_taps[ti];
           const int cb = cb_next;
           if (++cb_next == c_blocks) { cb_next = 0; ++ti; }
-          const uint32_t a_dst = smem_base + SM::off_a + stage * kATileBytes;
-          const uint32_t b_dst = smem_base + SM::off_b + stage * SM::kBTileBytes;
+          const uint32_t a_dst = smem_base + SM::off_a + slot * kATileBytes;
+          const uint32_t b_dst = smem_base + SM::off_b + slot * SM::kBTileBytes;
           // activation: 64 channels x (tw x th x tn) pixels, shifted by the tap
           tma_load_4d(a_dst, &p.tma_x[tp.map], bar_full(stage), cb * kBK, o.q0 + tp.dw, o.p0 + tp.dh, o.nb0);
           if (B_MN) {
@@ -273,7 +283,8 @@ __global__ void __launch_bounds__(32 * 10, 1) conv_fprop_kernel(const __grid_con
             // rows = BN output channels (ko), columns = 64 contraction channels c
             ptx::tma_load_3d(b_dst, &p.tma_w, bar_full(stage), cb * kBK, tp.tap, o.n0);
           }
-          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+          }   // u
+          if (++stage == GROUPS) { stage = 0; phase ^= 1u; }
         }
       }
     }
@@ -286,25 +297,33 @@ __global__ void __launch_bounds__(32 * 10, 1) conv_fprop_kernel(const __grid_con
       uint32_t phase = 0;
       int it = 0;
       bool alive = true;
+      DeviceStatus* const status = c.status;
+      const uint32_t wait_us = c.wait_limit_us;
       for (int tile = blockIdx.x; alive && tile < c.num_tiles; tile += gridDim.x, ++it) {
         const int acc = it & 1;
         const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
         if (!ptx::mbar_wait(bar_tmem_empty(acc), acc_phase ^ 1u, abort_flag, c.status, 2, acc, c.wait_limit_us)) { alive = false; break; }
         ptx::tcgen05_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
-        for (int kb = 0; kb < k_blocks; ++kb) {
-          if (!ptx::mbar_wait(bar_full(stage), phase, abort_flag, c.status, 3, stage, c.wait_limit_us)) { alive = false; break; }
+        for (int kb0 = 0; kb0 < k_blocks; kb0 += KSUB) {
+          const int nsub = min(KSUB, k_blocks - kb0);
+          if (!ptx::mbar_wait(bar_full(stage), phase, abort_flag, status, 3, stage, wait_us)) { alive = false; break; }
           ptx::tcgen05_fence_after();
-          const uint32_t a_addr = smem_base + SM::off_a + stage * kATileBytes;
-          const uint32_t b_addr = smem_base + SM::off_b + stage * SM::kBTileBytes;
 #pragma unroll
-          for (int k = 0; k < kBK / kUmmaK; ++k) {
-            const uint64_t adesc = ptx::make_smem_desc_sw128(a_addr + k * 32, 16, 1024);
-            const uint64_t bdesc = ptx::make_smem_desc_sw128(b_addr + k * b_kadv, b_lbo, 1024);
-            ptx::umma_f16(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+          for (int u = 0; u < KSUB; ++u) {
+            if (u >= nsub) break;
+            const int kb = kb0 + u, slot = stage * KSUB + u;
+            const uint32_t a_addr = smem_base + SM::off_a + slot * kATileBytes;
+            const uint32_t b_addr = smem_base + SM::off_b + slot * SM::kBTileBytes;
+#pragma unroll
+            for (int k = 0; k < kBK / kUmmaK; ++k) {
+              const uint64_t adesc = ptx::make_smem_desc_sw128(a_addr + k * 32, 16, 1024);
+              const uint64_t bdesc = ptx::make_smem_desc_sw128(b_addr + k * b_kadv, b_lbo, 1024);
+              ptx::umma_f16(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+            }
           }
           ptx::umma_commit(bar_empty(stage));
-          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+          if (++stage == GROUPS) { stage = 0; phase ^= 1u; }
         }
         if (alive) ptx::umma_commit(bar_tmem_full(acc));
       }
