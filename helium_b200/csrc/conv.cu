@@ -131,7 +131,7 @@ int32_t launch_fprop(const ConvParams& p, int grid, cudaStream_t stream) {
     HE_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SM::dynamic_bytes));
     configured = true;
   }
-  kernel<<<grid, 320, SM::dynamic_bytes, stream>>>(p);
+  kernel<<<grid, 352, SM::dynamic_bytes, stream>>>(p);   // producer, two MMA issuers, eight epilogue warps
   HE_CUDA(cudaGetLastError());
   return HE_OK;
 }

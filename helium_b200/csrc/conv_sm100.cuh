@@ -175,15 +175,20 @@ struct ConvSmem {
 
 // B_MN = false: filter tiles are K-major ([ko rows][64 c], forward); true: N-major ([64 ko rows][c], data gradient).
 template <int BN, int STAGES, bool B_MN>
-__global__ void __launch_bounds__(32 * 10, 1) conv_fprop_kernel(const __grid_constant__ ConvParams p) {
+__global__ void __launch_bounds__(32 * 11, 1) conv_fprop_kernel(const __grid_constant__ ConvParams p) {
   using SM = ConvSmem<BN, STAGES>;
   constexpr int NE_WARPS = 8;
+  // TWO MMA-issuing threads (warps 1 and 10).  A tile's hand-over groups alternate between them and each
+  // accumulates into its own TMEM half; the epilogue adds the halves.  The issuing thread was the bottleneck (~65
+  // cycles per MMA statement against 32-64 cycles of tensor-pipe work at 64-128 columns); two accumulators keep
+  // the order of every sum fixed, which two threads feeding one accumulator would not.
+  constexpr int kIssuer1Warp = 2 + NE_WARPS;
   // shared memory is handed over two k-blocks at a time: the MMA-issuing thread spends ~65 cycles per MMA and
   // ~280 per hand-over (barrier wait, commit, bookkeeping), against 128-256 tensor-pipe cycles per k-block
   constexpr int KSUB = 2;
   constexpr int GROUPS = STAGES / KSUB;
   static_assert(STAGES % KSUB == 0, "stages are handed over in groups of KSUB");
-  constexpr int kTmemCols = 2 * BN <= 128 ? 128 : 256;
+  constexpr int kTmemCols = 4 * BN <= 256 ? 256 : 512;   // two tiles in flight x two halves
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   const uint32_t smem_base = ptx::smem_u32(smem);
@@ -208,7 +213,7 @@ __global__ void __launch_bounds__(32 * 10, 1) conv_fprop_kernel(const __grid_con
       ptx::mbar_init(bar_empty(s), 1);
     }
     for (int a = 0; a < 2; ++a) {
-      ptx::mbar_init(bar_tmem_full(a), 1);
+      ptx::mbar_init(bar_tmem_full(a), 2);   // one arrival per issuing thread
       ptx::mbar_init(bar_tmem_empty(a), NE_WARPS);
     }
     ptx::fence_mbar_init();
@@ -288,8 +293,9 @@ __global__ void __launch_bounds__(32 * 10, 1) conv_fprop_kernel(const __grid_con
         }
       }
     }
-  } else if (warp == 1) {
+  } else if (warp == 1 || warp == kIssuer1Warp) {
     if (lane == 0) {
+      const int me = warp == 1 ? 0 : 1;
       const uint32_t idesc = ptx::make_idesc_f16(c.ab_format, 0, B_MN ? 1 : 0, kBM, BN);
       constexpr uint32_t b_lbo = B_MN ? kBK * 128 : 16;
       constexpr uint32_t b_kadv = B_MN ? 2048 : 32;
@@ -302,33 +308,43 @@ __global__ void __launch_bounds__(32 * 10, 1) conv_fprop_kernel(const __grid_con
       for (int tile = blockIdx.x; alive && tile < c.num_tiles; tile += gridDim.x, ++it) {
         const int acc = it & 1;
         const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
-        if (!ptx::mbar_wait(bar_tmem_empty(acc), acc_phase ^ 1u, abort_flag, c.status, 2, acc, c.wait_limit_us)) { alive = false; break; }
+        if (!ptx::mbar_wait(bar_tmem_empty(acc), acc_phase ^ 1u, abort_flag, status, 2, acc, wait_us)) { alive = false; break; }
         ptx::tcgen05_fence_after();
-        const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
-        for (int kb0 = 0; kb0 < k_blocks; kb0 += KSUB) {
+        const uint32_t d_tmem = tmem_base + (uint32_t)((acc * 2 + me) * BN);
+        bool first = true;
+        int g_idx = 0;
+        for (int kb0 = 0; kb0 < k_blocks; kb0 += KSUB, ++g_idx) {
+          // every group advances the ring for both issuers; a group belongs to the issuer of its parity
+          const int my_stage = stage;
+          const uint32_t my_phase = phase;
+          if (++stage == GROUPS) { stage = 0; phase ^= 1u; }
+          if ((g_idx & 1) != me) continue;
           const int nsub = min(KSUB, k_blocks - kb0);
-          if (!ptx::mbar_wait(bar_full(stage), phase, abort_flag, status, 3, stage, wait_us)) { alive = false; break; }
+          if (!ptx::mbar_wait(bar_full(my_stage), my_phase, abort_flag, status, 3, my_stage, wait_us)) { alive = false; break; }
           ptx::tcgen05_fence_after();
 #pragma unroll
           for (int u = 0; u < KSUB; ++u) {
             if (u >= nsub) break;
-            const int kb = kb0 + u, slot = stage * KSUB + u;
+            const int slot = my_stage * KSUB + u;
             const uint32_t a_addr = smem_base + SM::off_a + slot * kATileBytes;
             const uint32_t b_addr = smem_base + SM::off_b + slot * SM::kBTileBytes;
 #pragma unroll
             for (int k = 0; k < kBK / kUmmaK; ++k) {
               const uint64_t adesc = ptx::make_smem_desc_sw128(a_addr + k * 32, 16, 1024);
               const uint64_t bdesc = ptx::make_smem_desc_sw128(b_addr + k * b_kadv, b_lbo, 1024);
-              ptx::umma_f16(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+              ptx::umma_f16(d_tmem, adesc, bdesc, idesc, (first && u == 0 && k == 0) ? 0u : 1u);
             }
           }
-          ptx::umma_commit(bar_empty(stage));
-          if (++stage == GROUPS) { stage = 0; phase ^= 1u; }
+          first = false;
+          ptx::umma_commit(bar_empty(my_stage));
         }
-        if (alive) ptx::umma_commit(bar_tmem_full(acc));
+        if (alive) {
+          if (!first) ptx::umma_commit(bar_tmem_full(acc));   // arrives when this thread's MMAs have retired
+          else ptx::mbar_arrive(bar_tmem_full(acc));           // a tile of one group: nothing from this thread
+        }
       }
     }
-  } else {
+  } else if (warp >= 2 && warp < 2 + NE_WARPS) {
     EpiEnv env;
     env.core = &c;
     env.scratch = scratch;
@@ -362,9 +378,21 @@ __global__ void __launch_bounds__(32 * 10, 1) conv_fprop_kernel(const __grid_con
       EpiConv::tile_begin(p.epi, st);
       if (!dead) {
         ptx::tcgen05_fence_after();
-        const uint32_t taddr0 = tmem_base + ((uint32_t)(env.quadrant * 32) << 16) + (uint32_t)(acc * BN);
+        const uint32_t taddr0 = tmem_base + ((uint32_t)(env.quadrant * 32) << 16) + (uint32_t)(acc * 2 * BN);
         const int col_end = min(col_begin + kColsPerWarp, ((c.N - t.n0 + 31) / 32) * 32);
-        epilogue_walk_chunks<EpiConv>(p.epi, env, t, st, taddr0, pix, col_begin, col_end);
+        const bool two_halves = k_blocks > KSUB;   // the second issuer had at least one group
+#pragma unroll 1
+        for (int col = col_begin; col < col_end; col += EpiConv::kChunk) {
+          float v[EpiConv::kChunk];
+          tmem_ld_chunk<EpiConv::kChunk>(taddr0 + (uint32_t)col, v);
+          if (two_halves) {
+            float w[EpiConv::kChunk];
+            tmem_ld_chunk<EpiConv::kChunk>(taddr0 + (uint32_t)(BN + col), w);
+#pragma unroll
+            for (int i = 0; i < EpiConv::kChunk; ++i) v[i] += w[i];
+          }
+          EpiConv::chunk(p.epi, env, t, st, pix, col, v);
+        }
         ptx::tcgen05_fence_before();
         __syncwarp();
         if (lane == 0) ptx::mbar_arrive(bar_tmem_empty(acc));
