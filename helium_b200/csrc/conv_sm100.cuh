@@ -439,8 +439,9 @@ struct ConvWgradSmem {
 // tiles of the group, each tap into its own TMEM columns: what bounds these kernels is the rate at which TMA
 // fills shared memory, and sharing the flow tile cuts the bytes per tap from (128 + BN) to (128 / T + BN) rows.
 template <int BN, int STAGES, int T>
-__global__ void __launch_bounds__(32 * 6, 1) conv_wgrad_kernel(const __grid_constant__ ConvWgradParams p) {
+__global__ void __launch_bounds__(32 * 7, 1) conv_wgrad_kernel(const __grid_constant__ ConvWgradParams p) {
   using SM = ConvWgradSmem<BN, STAGES, T>;
+  constexpr int kIssuers = 2;
   constexpr int kTmemCols = T * BN <= 64 ? 64 : T * BN <= 128 ? 128 : T * BN <= 256 ? 256 : 512;
   static_assert(T * BN <= 512, "the taps of a group share the 512 TMEM columns");
   extern __shared__ uint8_t smem_raw[];
@@ -473,9 +474,9 @@ __global__ void __launch_bounds__(32 * 6, 1) conv_wgrad_kernel(const __grid_cons
     *abort_flag = 0;
     for (int s = 0; s < STAGES; ++s) {
       ptx::mbar_init(bar_full(s), 1);
-      ptx::mbar_init(bar_empty(s), 1);
+      ptx::mbar_init(bar_empty(s), kIssuers);   // a stage is free when both issuing threads' MMAs on it have retired
     }
-    ptx::mbar_init(bar_done, 1);
+    ptx::mbar_init(bar_done, kIssuers);
     ptx::fence_mbar_init();
   }
   if (warp == 0 && lane == 0) {
@@ -529,18 +530,25 @@ __global__ void __launch_bounds__(32 * 6, 1) conv_wgrad_kernel(const __grid_cons
         if (++stage == STAGES) { stage = 0; phase ^= 1u; }
       }
     }
-  } else if (warp == 1) {
+  } else if (warp == 1 || warp == 6) {
+    // Two MMA-issuing threads: the taps of the group alternate between them (each tap has its own TMEM columns, so
+    // every sum keeps its order); one thread paid ~65 cycles per MMA statement against 32-64 of tensor-pipe work.
     if (lane == 0) {
+      const int me = warp == 1 ? 0 : 1;
       const uint32_t idesc = ptx::make_idesc_f16(c.ab_format, 1, 1, kBM, BN);
+      DeviceStatus* const status = c.status;
+      const uint32_t wait_us = c.wait_limit_us;
       int stage = 0;
       uint32_t phase = 0;
       bool alive = true;
       for (int kt = kt_begin; kt < kt_end; ++kt) {
-        if (!ptx::mbar_wait(bar_full(stage), phase, abort_flag, c.status, 3, stage, c.wait_limit_us)) { alive = false; break; }
+        if (!ptx::mbar_wait(bar_full(stage), phase, abort_flag, status, 3, stage, wait_us)) { alive = false; break; }
         ptx::tcgen05_fence_after();
         const uint32_t a_addr = smem_base + SM::off_a + stage * kATileBytes;
         const uint32_t b_addr = smem_base + SM::off_b + stage * SM::kBTileBytes;
-        for (int t = 0; t < nt; ++t) {
+#pragma unroll
+        for (int t = 0; t < T; ++t) {
+          if (t >= nt || (t % kIssuers) != me) continue;
 #pragma unroll
           for (int k = 0; k < kBK / kUmmaK; ++k) {
             const uint64_t adesc = ptx::make_smem_desc_sw128(a_addr + k * 2048, kBK * 128, 1024);
@@ -548,12 +556,13 @@ __global__ void __launch_bounds__(32 * 6, 1) conv_wgrad_kernel(const __grid_cons
             ptx::umma_f16(tmem_base + (uint32_t)(t * BN), adesc, bdesc, idesc, (kt > kt_begin || k != 0) ? 1u : 0u);
           }
         }
+        // with a single tap the second thread has no MMAs of its own: a commit with nothing outstanding arrives at once
         ptx::umma_commit(bar_empty(stage));
         if (++stage == STAGES) { stage = 0; phase ^= 1u; }
       }
       if (alive) ptx::umma_commit(bar_done);
     }
-  } else {
+  } else if (warp >= 2 && warp < 6) {
     // four epilogue warps: rows = output channels of the filter, columns = input channels of one tap
     const int quadrant = warp & 3;
     const int row = quadrant * 32 + lane;
