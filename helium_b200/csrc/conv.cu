@@ -148,7 +148,7 @@ int32_t launch_wgrad(const ConvWgradParams& p, int grid, cudaStream_t stream) {
     HE_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SM::dynamic_bytes));
     configured = true;
   }
-  kernel<<<grid, 224, SM::dynamic_bytes, stream>>>(p);   // producer, two MMA issuers (warps 1 and 6), four epilogue warps
+  kernel<<<grid, 256, SM::dynamic_bytes, stream>>>(p);   // producer, three MMA issuers (warps 1, 6, 7), four epilogue warps
   HE_CUDA(cudaGetLastError());
   return HE_OK;
 }

@@ -439,9 +439,9 @@ struct ConvWgradSmem {
 // tiles of the group, each tap into its own TMEM columns: what bounds these kernels is the rate at which TMA
 // fills shared memory, and sharing the flow tile cuts the bytes per tap from (128 + BN) to (128 / T + BN) rows.
 template <int BN, int STAGES, int T>
-__global__ void __launch_bounds__(32 * 7, 1) conv_wgrad_kernel(const __grid_constant__ ConvWgradParams p) {
+__global__ void __launch_bounds__(32 * 8, 1) conv_wgrad_kernel(const __grid_constant__ ConvWgradParams p) {
   using SM = ConvWgradSmem<BN, STAGES, T>;
-  constexpr int kIssuers = 2;
+  constexpr int kIssuers = 3;
   constexpr int kTmemCols = T * BN <= 64 ? 64 : T * BN <= 128 ? 128 : T * BN <= 256 ? 256 : 512;
   static_assert(T * BN <= 512, "the taps of a group share the 512 TMEM columns");
   extern __shared__ uint8_t smem_raw[];
@@ -530,11 +530,11 @@ __global__ void __launch_bounds__(32 * 7, 1) conv_wgrad_kernel(const __grid_cons
         if (++stage == STAGES) { stage = 0; phase ^= 1u; }
       }
     }
-  } else if (warp == 1 || warp == 6) {
-    // Two MMA-issuing threads: the taps of the group alternate between them (each tap has its own TMEM columns, so
+  } else if (warp == 1 || warp >= 6) {
+    // Three MMA-issuing threads: the taps of the group are dealt out to them (each tap has its own TMEM columns, so
     // every sum keeps its order); one thread paid ~65 cycles per MMA statement against 32-64 of tensor-pipe work.
     if (lane == 0) {
-      const int me = warp == 1 ? 0 : 1;
+      const int me = warp == 1 ? 0 : warp - 5;
       const uint32_t idesc = ptx::make_idesc_f16(c.ab_format, 1, 1, kBM, BN);
       DeviceStatus* const status = c.status;
       const uint32_t wait_us = c.wait_limit_us;
