@@ -961,6 +961,8 @@ def config_for(key: str, world: int) -> dict:
     product arm and `--impl reference` print the same one."""
     wl = WORKLOADS[key]
     config = {"workload": wl.description, "l2": wl.l2_note}
+    if os.environ.get("HE_PLANNER"):
+        config["planner"] = os.environ["HE_PLANNER"]
     if key == "c5":
         config.update({"images_per_gpu": wl.BATCH, "sharding": "batch",
                        "grad_allreduce": "NCCL mean through he_allreduce_grads, 2 buckets (filters bf16, vectors f32) after the backward pass; "
@@ -1106,6 +1108,9 @@ def main():
     ap.add_argument("--nccl-ctas", type=int, default=NCCL_CTAS_DEFAULT,
                     help="c4 at N > 1: CTAs the gradient all-reduce may occupy (ncclConfig maxCTAs); the two GEMMs it overlaps are "
                          "planned for that many fewer SMs.  0 = NCCL's default and full-device GEMM grids")
+    ap.add_argument("--planner", default=None, choices=["pairwise", "search"],
+                    help="c1 / c4g (whole graphs through the host runtime): how instructions are formed, the reference's pairwise "
+                         "merging (default) or the fusion search")
     ap.add_argument("--brief", action="store_true",
                     help="profiler captures only: no busy loop before the timed region, no end-to-end leg, no CPU baseline "
                          "(the printed line is then not a bench value)")
@@ -1122,6 +1127,8 @@ def main():
         return 0
     if args.warmup < 3:
         args.warmup = 3
+    if args.planner:
+        os.environ["HE_PLANNER"] = args.planner   # read by heh_graph_create
 
     import torch
     import torch.distributed as dist

@@ -86,6 +86,9 @@ SIGNATURES = {
     "heh_graph_new_op": (C.c_int32, [C.c_void_p, C.POINTER(HeNode), C.POINTER(C.c_int32)]),
     "heh_graph_new_output": (C.c_int32, [C.c_void_p, C.c_int32]),
     "heh_graph_plan_text": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_char_p, C.c_size_t]),
+    "heh_graph_set_planner": (C.c_int32, [C.c_void_p, C.c_int32, C.c_int32, C.c_int32]),
+    "heh_graph_search_text": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_char_p, C.c_size_t]),
+    "heh_graph_subdivisions_text": (C.c_int32, [C.c_void_p, C.c_char_p, C.c_size_t]),
     "heh_exec_create": (C.c_int32, [C.c_void_p, C.c_void_p, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.c_int32,
                                     C.POINTER(C.c_void_p)]),
     "heh_exec_run": (C.c_int32, [C.c_void_p, C.c_void_p]),

@@ -34,6 +34,7 @@ SOURCES = [
     "gemm_kernels_prog.cu",
     "sgemm.cu",
     "host_graph.cu",
+    "fusion_search.cu",
     "reduce_noalloc.cu",
     "comm.cu",
     "conv.cu",

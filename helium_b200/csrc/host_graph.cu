@@ -22,171 +22,11 @@
 
 #include "he_internal.h"
 
+#include "host_graph.h"
+#include "fusion_search.h"
+
 namespace he {
 namespace host {
-
-using NodeId = int;
-
-struct OpGraph {
-  std::vector<he_node> nodes;           // in[] = NodeIds; topological by construction
-  std::vector<NodeId> inputs;           // HE_OP_INPUT nodes in creation order
-  std::vector<NodeId> outputs;          // nodes marked as outputs, in marking order
-  std::vector<std::vector<NodeId>> outbound;
-
-  NodeId add(const he_node& n) {
-    nodes.push_back(n);
-    outbound.emplace_back();
-    const NodeId id = (NodeId)nodes.size() - 1;
-    for (int k = 0; k < 3; ++k)
-      if (n.in[k] >= 0) outbound[n.in[k]].push_back(id);
-    if (n.kind == HE_OP_INPUT) inputs.push_back(id);
-    return id;
-  }
-  bool is_output(NodeId id) const { return std::find(outputs.begin(), outputs.end(), id) != outputs.end(); }
-  std::vector<NodeId> inbound(NodeId id) const {
-    std::vector<NodeId> r;
-    for (int k = 0; k < 3; ++k)
-      if (nodes[id].in[k] >= 0) r.push_back(nodes[id].in[k]);
-    return r;
-  }
-  // OpGraph::optimize (opgraph.rs:165-191): which intermediates are needed for the outputs
-  std::vector<bool> live() const {
-    std::vector<bool> l(nodes.size(), false);
-    std::vector<NodeId> stack(outputs.begin(), outputs.end());
-    while (!stack.empty()) {
-      NodeId n = stack.back();
-      stack.pop_back();
-      if (l[n]) continue;
-      l[n] = true;
-      for (NodeId p : inbound(n)) stack.push_back(p);
-    }
-    return l;
-  }
-};
-
-// Subset of intermediate nodes (subgraph.rs:12-79).
-struct OpSubgraph {
-  const OpGraph* graph = nullptr;
-  std::vector<NodeId> nodes, inputs, leafs;  // all sorted
-
-  static OpSubgraph from_nodes(const OpGraph* g, std::vector<NodeId> ns) {
-    OpSubgraph s;
-    s.graph = g;
-    std::sort(ns.begin(), ns.end());
-    ns.erase(std::unique(ns.begin(), ns.end()), ns.end());
-    s.nodes = ns;
-    std::set<NodeId> in_set(ns.begin(), ns.end()), inputs;
-    for (NodeId n : ns)
-      for (NodeId p : g->inbound(n))
-        if (!in_set.count(p)) inputs.insert(p);
-    s.inputs.assign(inputs.begin(), inputs.end());
-    for (NodeId n : ns) {
-      bool leaf = g->is_output(n);
-      for (NodeId c : g->outbound[n])
-        if (!in_set.count(c)) leaf = true;
-      if (leaf) s.leafs.push_back(n);
-    }
-    return s;
-  }
-  OpSubgraph merge_with(const OpSubgraph& o) const {
-    std::vector<NodeId> ns = nodes;
-    ns.insert(ns.end(), o.nodes.begin(), o.nodes.end());
-    return from_nodes(graph, ns);
-  }
-  bool contains(NodeId n) const { return std::binary_search(nodes.begin(), nodes.end(), n); }
-
-  // Flat descriptor for the C ABI: inputs first (as HE_OP_INPUT), then the nodes.
-  struct Flat {
-    std::vector<he_node> nodes;
-    std::vector<int32_t> outputs;
-    he_graph_desc desc() const { return he_graph_desc{(int32_t)nodes.size(), nodes.data(), (int32_t)outputs.size(), outputs.data()}; }
-  };
-  Flat flatten() const {
-    Flat f;
-    std::map<NodeId, int> index;
-    for (NodeId i : inputs) {
-      he_node n = graph->nodes[i];
-      n.kind = HE_OP_INPUT;
-      n.in[0] = n.in[1] = n.in[2] = -1;
-      index[i] = (int)f.nodes.size();
-      f.nodes.push_back(n);
-    }
-    for (NodeId i : nodes) {
-      he_node n = graph->nodes[i];
-      for (int k = 0; k < 3; ++k)
-        if (n.in[k] >= 0) n.in[k] = index.at(n.in[k]);
-      index[i] = (int)f.nodes.size();
-      f.nodes.push_back(n);
-    }
-    for (NodeId l : leafs) f.outputs.push_back(index.at(l));
-    return f;
-  }
-};
-
-enum class InstrKind { PointwiseGraph = 0, PermuteDims = 1, FusedMatmul = 2 };
-static const char* kind_name(InstrKind k) {
-  return k == InstrKind::PointwiseGraph ? "PointwiseGraph" : k == InstrKind::PermuteDims ? "PermuteDims" : "FusedMatmul";
-}
-
-struct Instr {
-  InstrKind kind;
-  OpSubgraph sub;
-  const std::vector<NodeId>& inputs() const { return sub.inputs; }
-  const std::vector<NodeId>& outputs() const { return sub.leafs; }
-
-  int tier(he_ctx* ctx) const {
-    OpSubgraph::Flat f = sub.flatten();
-    he_graph_desc d = f.desc();
-    return he_plan_supported(ctx, &d, (int)kind);
-  }
-
-  // Kind of the instruction that results from fusing `this` with `next`, or nothing.
-  bool fused_kind(const Instr& next, InstrKind* out) const {
-    if (kind == InstrKind::FusedMatmul && next.kind == InstrKind::FusedMatmul) return false;
-    if (kind == InstrKind::FusedMatmul || next.kind == InstrKind::FusedMatmul) {
-      *out = InstrKind::FusedMatmul;
-      return true;
-    }
-    if (kind == next.kind) {
-      *out = kind;
-      return true;
-    }
-    *out = InstrKind::PointwiseGraph;  // PermuteDims x PointwiseGraph: only via a single-pass kernel
-    return true;
-  }
-
-  bool can_fuse_with(const Instr& next, he_ctx* ctx) const {
-    InstrKind k;
-    if (!fused_kind(next, &k)) return false;
-    Instr merged{k, sub.merge_with(next.sub)};
-    const int t = merged.tier(ctx);
-    if (kind != next.kind && k == InstrKind::PointwiseGraph) {
-      // a permutation folds into a pointwise kernel when a single-pass kernel exists for the pair
-      // (tier 2), or when it only feeds reductions: those read through the swapped view in column
-      // mode, coalesced, and no permuted copy is ever written
-      bool only_reductions = true;
-      for (NodeId l : merged.sub.leafs) only_reductions = only_reductions && sub.graph->nodes[l].kind == HE_OP_REDUCE;
-      return t == 2 || (t > 0 && only_reductions);
-    }
-    // Greedy pairwise fusion passes through partial subgraphs that only the interpreter tier
-    // serves on the way to one that a hand-written kernel serves, so tier 1 is accepted here.
-    return t > 0;
-  }
-  Instr fuse_with(const Instr& next) const {
-    InstrKind k = kind;
-    fused_kind(next, &k);
-    return Instr{k, sub.merge_with(next.sub)};
-  }
-};
-
-// cuda.rs:33-60
-static Instr make_instr_for_op(const OpGraph* g, NodeId id) {
-  const he_node& n = g->nodes[id];
-  OpSubgraph s = OpSubgraph::from_nodes(g, {id});
-  if (n.kind == HE_OP_MATMUL) return Instr{InstrKind::FusedMatmul, s};
-  if (n.kind == HE_OP_SWAP_DIMS && num_elements(n) > 1000000 && n.dtype != HE_BOOL) return Instr{InstrKind::PermuteDims, s};
-  return Instr{InstrKind::PointwiseGraph, s};
-}
 
 // ---- InstrGraph (plan_generation.rs:86-249) -------------------------------------------------------
 struct InstrGraph {
@@ -259,26 +99,43 @@ static bool has_intersection(const std::vector<NodeId>& a, const std::vector<Nod
   return false;
 }
 
-static Plan generate_plan(const OpGraph& g, he_ctx* ctx) {
-  // make_instr_graph (plan_generation.rs:259-270), dead nodes pruned first (backend.rs:46)
-  InstrGraph ig;
-  const std::vector<bool> live = g.live();
-  for (NodeId id = 0; id < (NodeId)g.nodes.size(); ++id)
-    if (g.nodes[id].kind != HE_OP_INPUT && live[id]) ig.insert(make_instr_for_op(&g, id));
+// How instructions are formed from nodes: the reference's greedy pairwise merging, or the fusion search.
+struct PlannerChoice {
+  int mode = 0;   // 0 pairwise (plan_generation.rs:243-256), 1 search (fusion_search.h)
+  SearchOptions search;
+};
 
-  // do_fusions (plan_generation.rs:243-256)
-  std::set<int> working;
-  for (auto& kv : ig.instrs) working.insert(kv.first);
-  while (!working.empty()) {
-    const int current = *working.begin();
-    working.erase(working.begin());
-    for (int next : ig.dependents(current)) {
-      if (ig.instrs.at(current).can_fuse_with(ig.instrs.at(next), ctx) && !ig.exist_multiple_paths(current, next)) {
-        Instr a = ig.remove(current), b = ig.remove(next);
-        const int nid = ig.insert(a.fuse_with(b));
-        working.erase(next);
-        working.insert(nid);
-        break;
+static Plan generate_plan(const OpGraph& g, he_ctx* ctx, const PlannerChoice& choice, std::string* error) {
+  InstrGraph ig;
+  if (choice.mode == 1) {
+    // every instruction comes out of the search with its outputs chosen: a node that several instructions
+    // recompute is written to memory by one of them only
+    SearchResult r = search_fusions(g, ctx, choice.search);
+    if (!r.valid) {
+      if (error) *error = r.error;
+      return Plan{};
+    }
+    for (Instr& in : instrs_from_search(g, r)) ig.insert(std::move(in));
+  } else {
+    // make_instr_graph (plan_generation.rs:259-270), dead nodes pruned first (backend.rs:46)
+    const std::vector<bool> live = g.live();
+    for (NodeId id = 0; id < (NodeId)g.nodes.size(); ++id)
+      if (g.nodes[id].kind != HE_OP_INPUT && live[id]) ig.insert(make_instr_for_op(&g, id));
+
+    // do_fusions (plan_generation.rs:243-256)
+    std::set<int> working;
+    for (auto& kv : ig.instrs) working.insert(kv.first);
+    while (!working.empty()) {
+      const int current = *working.begin();
+      working.erase(working.begin());
+      for (int next : ig.dependents(current)) {
+        if (ig.instrs.at(current).can_fuse_with(ig.instrs.at(next), ctx) && !ig.exist_multiple_paths(current, next)) {
+          Instr a = ig.remove(current), b = ig.remove(next);
+          const int nid = ig.insert(a.fuse_with(b));
+          working.erase(next);
+          working.insert(nid);
+          break;
+        }
       }
     }
   }
@@ -356,6 +213,7 @@ using namespace he::host;
 
 struct heh_graph {
   OpGraph g;
+  PlannerChoice planner;
 };
 
 // One prepared evaluation of a graph with fixed buffers.
@@ -431,6 +289,9 @@ extern "C" {
 int32_t heh_graph_create(heh_graph** out) {
   if (!out) HE_FAIL(HE_ERR_INVALID, "heh_graph_create: null argument");
   *out = new heh_graph();
+  // HE_PLANNER=search makes the fusion search the default planner of new graphs (heh_graph_set_planner overrides)
+  const char* env = getenv("HE_PLANNER");
+  if (env && strcmp(env, "search") == 0) (*out)->planner.mode = 1;
   return HE_OK;
 }
 void heh_graph_destroy(heh_graph* g) { delete g; }
@@ -471,7 +332,9 @@ int32_t heh_graph_new_output(heh_graph* g, int32_t node) {
 int32_t heh_graph_plan_text(he_ctx* ctx, heh_graph* g, char* buf, size_t cap) {
   if (!g || !buf) HE_FAIL(HE_ERR_INVALID, "heh_graph_plan_text: null argument");
   if (g->g.outputs.empty()) HE_FAIL(HE_ERR_INVALID, "graph has no outputs");
-  Plan plan = generate_plan(g->g, ctx);
+  std::string plan_error;
+  Plan plan = generate_plan(g->g, ctx, g->planner, &plan_error);
+  if (!plan_error.empty()) HE_FAIL(HE_ERR_UNSUPPORTED, "fusion search: %s", plan_error.c_str());
   std::ostringstream os;
   for (size_t i = 0; i < plan.steps.size(); ++i) {
     for (const Instr& in : plan.steps[i].instrs) {
@@ -495,6 +358,60 @@ int32_t heh_graph_plan_text(he_ctx* ctx, heh_graph* g, char* buf, size_t cap) {
   return HE_OK;
 }
 
+int32_t heh_graph_set_planner(heh_graph* g, int32_t mode, int32_t depth, int32_t max_states) {
+  if (!g) HE_FAIL(HE_ERR_INVALID, "heh_graph_set_planner: null argument");
+  if (mode != 0 && mode != 1) HE_FAIL(HE_ERR_INVALID, "heh_graph_set_planner: mode %d (0 pairwise, 1 search)", mode);
+  if (depth < 0 || depth > 12 || max_states < 0) HE_FAIL(HE_ERR_INVALID, "heh_graph_set_planner: depth %d, max_states %d", depth, max_states);
+  g->planner.mode = mode;
+  if (depth > 0) g->planner.search.depth = depth;
+  if (max_states > 0) g->planner.search.max_states = max_states;
+  return HE_OK;
+}
+
+static void print_nodes(std::ostringstream& os, const char* name, const std::vector<NodeId>& v) {
+  os << ' ' << name << "=[";
+  for (size_t k = 0; k < v.size(); ++k) os << (k ? "," : "") << v[k];
+  os << ']';
+}
+
+int32_t heh_graph_search_text(he_ctx* ctx, heh_graph* g, char* buf, size_t cap) {
+  if (!g || !buf) HE_FAIL(HE_ERR_INVALID, "heh_graph_search_text: null argument");
+  if (g->g.outputs.empty()) HE_FAIL(HE_ERR_INVALID, "graph has no outputs");
+  SearchResult r = search_fusions(g->g, ctx, g->planner.search);
+  if (!r.valid) HE_FAIL(HE_ERR_UNSUPPORTED, "fusion search: %s", r.error.c_str());
+  std::ostringstream os;
+  os.precision(9);
+  os << "cost identity=" << r.cost_identity << " maximal=" << r.cost_maximal << " best=" << r.cost_best << " states=" << r.states
+     << " subdivisions=" << r.subdivisions << " recomputed=" << r.recomputed_nodes << "\n";
+  for (size_t i = 0; i < r.groups.size(); ++i) {
+    const SearchGroup& sg = r.groups[i];
+    os << "group " << i << (sg.anchor >= 0 ? " FusedMatmul" : " Pointwise") << " anchor=" << sg.anchor;
+    print_nodes(os, "pre", sg.pre);
+    print_nodes(os, "post", sg.post);
+    print_nodes(os, "in", sg.reads);
+    print_nodes(os, "out", sg.exports);
+    os << " seconds=" << sg.seconds << "\n";
+  }
+  const std::string s = os.str();
+  if (s.size() + 1 > cap) HE_FAIL(HE_ERR_INVALID, "heh_graph_search_text: buffer too small (need %zu)", s.size() + 1);
+  memcpy(buf, s.c_str(), s.size() + 1);
+  return HE_OK;
+}
+
+int32_t heh_graph_subdivisions_text(heh_graph* g, char* buf, size_t cap) {
+  if (!g || !buf) HE_FAIL(HE_ERR_INVALID, "heh_graph_subdivisions_text: null argument");
+  std::ostringstream os;
+  for (const Subdivision& sub : subdivide(g->g)) {
+    for (size_t k = 0; k < sub.size(); ++k)
+      os << (k ? " " : "") << sub[k].first << (sub[k].second == Portion::OperandSide ? "m" : sub[k].second == Portion::ResultSide ? "e" : "");
+    os << "\n";
+  }
+  const std::string s = os.str();
+  if (s.size() + 1 > cap) HE_FAIL(HE_ERR_INVALID, "heh_graph_subdivisions_text: buffer too small (need %zu)", s.size() + 1);
+  memcpy(buf, s.c_str(), s.size() + 1);
+  return HE_OK;
+}
+
 int32_t heh_exec_create(he_ctx* ctx, heh_graph* g, const void* const* inputs, void* const* outputs,
                         int32_t capture_cuda_graph, heh_exec** out) {
   if (!ctx || !g || !out) HE_FAIL(HE_ERR_INVALID, "heh_exec_create: null argument");
@@ -503,7 +420,9 @@ int32_t heh_exec_create(he_ctx* ctx, heh_graph* g, const void* const* inputs, vo
   if (G.outputs.empty()) HE_FAIL(HE_ERR_INVALID, "graph has no outputs");
   std::unique_ptr<heh_exec> e(new heh_exec());
   e->ctx = ctx;
-  e->plan = generate_plan(G, ctx);
+  std::string plan_error;
+  e->plan = generate_plan(G, ctx, g->planner, &plan_error);
+  if (!plan_error.empty()) HE_FAIL(HE_ERR_UNSUPPORTED, "fusion search: %s", plan_error.c_str());
   DeviceGuard device_guard(ctx->device);   // the caller's current device is restored on return
   HE_TRY(device_guard.status());
 

@@ -43,6 +43,24 @@ class HostGraph:
         check(lib.heh_graph_plan_text(ctx._h if ctx else None, self._h, buf, len(buf)))
         return buf.value.decode()
 
+    def set_planner(self, mode: str = "search", depth: int = 0, max_states: int = 0) -> None:
+        """"pairwise": the reference's greedy merging (default); "search": the fusion search."""
+        check(lib.heh_graph_set_planner(self._h, {"pairwise": 0, "search": 1}[mode], depth, max_states))
+
+    def search_text(self, ctx: Optional[Context] = None) -> str:
+        buf = C.create_string_buffer(1 << 20)
+        check(lib.heh_graph_search_text(ctx._h if ctx else None, self._h, buf, len(buf)))
+        return buf.value.decode()
+
+    def subdivisions(self):
+        """[(node, portion)] per subdivision; portion "m" / "e" for the two sides of a matmul, "" otherwise."""
+        buf = C.create_string_buffer(1 << 20)
+        check(lib.heh_graph_subdivisions_text(self._h, buf, len(buf)))
+        out = []
+        for line in buf.value.decode().splitlines():
+            out.append([(int(t.rstrip("me")), t[len(t.rstrip("me")):]) for t in line.split()])
+        return out
+
     def close(self):
         if self._h:
             lib.heh_graph_destroy(self._h)

@@ -244,6 +244,28 @@ int32_t heh_graph_new_output(heh_graph* g, int32_t node);
  * instruction "step <i> <Kind> tier=<t> nodes=[..] in=[..] out=[..]". */
 int32_t heh_graph_plan_text(he_ctx* ctx, heh_graph* g, char* buf, size_t cap);
 
+/* Chooses how instructions are formed from nodes.  mode 0 (default): the greedy pairwise merging of
+ * plan_generation.rs:243-256.  mode 1: the fusion search, the counterpart of the playground's
+ * (helium-playground/src/fused_graph.rs:113-223,285-593 states and moves, subdivision.rs:24-113,
+ * cost_model.rs:241-343): kernels are grown from single nodes by absorbing consumers into a kernel's
+ * result side, producers into its result side (recomputation instead of a read) or into a matmul's
+ * operand side, and by handing the export of a recomputed node from one kernel to another; a state is
+ * legal only if he_plan_supported accepts every kernel, its cost is an estimate fitted to this
+ * library's kernels on a B200, and the descent looks `depth` moves ahead (0 keeps 3) over at most
+ * `max_states` states per subdivision (0 keeps 12000).  heh_graph_plan_text and heh_exec_create use
+ * the chosen planner.  The environment variable HE_PLANNER=search makes mode 1 the default of graphs
+ * created afterwards. */
+int32_t heh_graph_set_planner(heh_graph* g, int32_t mode, int32_t depth, int32_t max_states);
+/* Runs the fusion search and writes its result: a first line "cost identity=<s> maximal=<s> best=<s>
+ * states=<n> subdivisions=<n> recomputed=<n>" (estimated seconds with one kernel per node, after the
+ * greedy start, and for the result), then one line per kernel in a topological order:
+ * "group <i> FusedMatmul|Pointwise anchor=<node|-1> pre=[..] post=[..] in=[..] out=[..] seconds=<s>". */
+int32_t heh_graph_search_text(he_ctx* ctx, heh_graph* g, char* buf, size_t cap);
+/* subdivide (subdivision.rs:24-113): one line per subdivision, its nodes in ascending order; a matmul
+ * node carries "m" where the subdivision holds its operand (mainloop) side and "e" for its result
+ * (epilogue) side. */
+int32_t heh_graph_subdivisions_text(heh_graph* g, char* buf, size_t cap);
+
 /* Prepares an execution: plans, creates every he_plan, allocates intermediates and workspaces
  * once, binds the caller's device buffers (`inputs[i]` for the i-th new_input, `outputs[j]` for the
  * j-th new_output) and, if `capture_cuda_graph` != 0, records the whole plan into a CUDA graph.

@@ -9,7 +9,7 @@ from helpers import O, storage_to_torch, torch_to_storage
 pytestmark = pytest.mark.gpu
 
 
-def _run_graph(ctx, g, ins, capture, repeats=1):
+def _run_graph(ctx, g, ins, capture, repeats=1, planner=None):
     import torch
     tin = [storage_to_torch(a, g.nodes[i].dtype) for a, i in zip(ins, g.inputs)]
     touts = []
@@ -18,6 +18,8 @@ def _run_graph(ctx, g, ins, capture, repeats=1):
         td = {ir.F32: torch.float32, ir.BF16: torch.bfloat16, ir.F16: torch.float16}[n.dtype]
         touts.append(torch.zeros(n.shape, dtype=td, device="cuda"))
     hg = hb.HostGraph(g)
+    if planner:
+        hg.set_planner(planner, 0, 4000)
     ex = hb.Executor(ctx, hg, tin, touts, capture=capture)
     for _ in range(repeats):
         ex.run()
@@ -109,3 +111,58 @@ def test_mlp_block_training_graph_through_the_host_runtime(ctx):
     for o, a, b in zip(g.outputs, got, want):
         node = g.nodes[o]
         assert O.rel_l2(O.decode(a, node.dtype, node.shape), O.decode(b, node.dtype, node.shape)) <= 1e-2, o
+
+
+def _shared_bias_graph(M=512, N=512, K=256):
+    g = ir.Graph()
+    x = g.new_input([M, K], ir.BF16); w1 = g.new_input([K, N], ir.BF16); w2 = g.new_input([K, N], ir.BF16)
+    b = g.new_input([N], ir.F32)
+    bb = g.broadcast_to(b, [M, N])
+    g.new_output(g.cast(g.binary(ir.BIN_ADD, g.matmul(x, w1), bb), ir.BF16))
+    g.new_output(g.cast(g.binary(ir.BIN_ADD, g.matmul(x, w2), bb), ir.BF16))
+    return g
+
+
+@pytest.mark.parametrize("name", ["mlp_step", "mlp_block", "readme", "shared_bias", "forward"])
+@pytest.mark.parametrize("capture", [False, True])
+def test_plans_of_the_fusion_search_give_the_oracle_numbers(ctx, name, capture):
+    """Graphs planned by the fusion search (kernels with chosen outputs, nodes recomputed in several kernels)
+    run through the same executor and are held to the same tolerances as the pairwise plans above."""
+    r = configs.rng(11)
+    round_nodes = []
+    if name == "mlp_step":
+        g, ins = configs.graph_mlp_train_step(), configs.mlp_inputs()
+    elif name == "mlp_block":
+        T, d, ff = 256, 128, 256
+        g, nodes = configs.graph_mlp_block_train(T, d, ff, return_nodes=True)
+        round_nodes = list(nodes.values())
+        ins = [configs.bf16_normal(r, (T, d)), configs.bf16_normal(r, (d, ff), 0.05), configs.bf16_normal(r, (ff,), 0.05),
+               configs.bf16_normal(r, (ff, d), 0.05), configs.bf16_normal(r, (d,), 0.05), configs.bf16_normal(r, (T, d))]
+    elif name == "readme":
+        g, ins = configs.graph_c3(256, 512, 128, False), configs.c3_inputs(256, 512, 128, False)
+    elif name == "shared_bias":
+        g = _shared_bias_graph()
+        ins = [configs.bf16_normal(r, (512, 256)), configs.bf16_normal(r, (256, 512), 0.05), configs.bf16_normal(r, (256, 512), 0.05),
+               r.standard_normal(512, dtype=np.float32)]
+    else:
+        T, d, ff = 256, 256, 512
+        g = ir.Graph()
+        x = g.new_input([T, d], ir.BF16); w1 = g.new_input([d, ff], ir.BF16); b1 = g.new_input([ff], ir.BF16)
+        w2 = g.new_input([ff, d], ir.BF16); b2 = g.new_input([d], ir.BF16)
+        h = g.cast(g.unary(ir.UN_GELU, g.binary(ir.BIN_ADD, g.matmul(x, w1), g.broadcast_to(b1, [T, ff]))), ir.BF16)
+        o = g.binary(ir.BIN_ADD, g.binary(ir.BIN_ADD, g.matmul(h, w2), g.broadcast_to(b2, [T, d])), x)
+        g.new_output(g.cast(o, ir.BF16))
+        round_nodes = [h]
+        ins = [configs.bf16_normal(r, (T, d)), configs.bf16_normal(r, (d, ff), 0.02), configs.bf16_normal(r, (ff,), 0.02),
+               configs.bf16_normal(r, (ff, d), 0.02), configs.bf16_normal(r, (d,), 0.02)]
+    want = O.evaluate(g, ins, round_nodes=round_nodes) if round_nodes else O.evaluate(g, ins)
+    got, ex = _run_graph(ctx, g, ins, capture=capture, repeats=2, planner="search")
+    for o, a, b in zip(g.outputs, got, want):
+        node = g.nodes[o]
+        # f32 graphs to 1e-5; graphs that keep bf16 activations to 1e-2 on every output, as for the pairwise plans
+        tol = 1e-5 if name in ("mlp_step", "readme") and node.dtype == ir.F32 else 1e-2
+        assert O.rel_l2(O.decode(a, node.dtype, node.shape), O.decode(b, node.dtype, node.shape)) <= tol, (name, o)
+    if name == "shared_bias":
+        assert ex.stats()["instrs"] == 2, ex.stats()
+    if name == "readme":
+        assert ex.stats()["instrs"] == 1
