@@ -159,6 +159,10 @@ extern "C" {
     pub fn heh_graph_new_op(g: *mut heh_graph, op: *const he_node, node_out: *mut i32) -> i32;
     pub fn heh_graph_new_output(g: *mut heh_graph, node: i32) -> i32;
     pub fn heh_graph_plan_text(ctx: *mut he_ctx, g: *mut heh_graph, buf: *mut c_char, cap: usize) -> i32;
+    /// mode 0: pairwise merging (plan_generation.rs:243-256); mode 1: fusion search (helium-playground).
+    pub fn heh_graph_set_planner(g: *mut heh_graph, mode: i32, depth: i32, max_states: i32) -> i32;
+    pub fn heh_graph_search_text(ctx: *mut he_ctx, g: *mut heh_graph, buf: *mut c_char, cap: usize) -> i32;
+    pub fn heh_graph_subdivisions_text(g: *mut heh_graph, buf: *mut c_char, cap: usize) -> i32;
     pub fn heh_exec_create(ctx: *mut he_ctx, g: *mut heh_graph, inputs: *const *const c_void,
                            outputs: *const *mut c_void, capture_cuda_graph: i32, out: *mut *mut heh_exec) -> i32;
     pub fn heh_exec_run(e: *mut heh_exec, cu_stream: *mut c_void) -> i32;
