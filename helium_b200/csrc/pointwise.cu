@@ -465,8 +465,60 @@ static Graph peel_reshaped_reduction_leaves(const Graph& g) {
   return o;
 }
 
+// A reduction leaf over dims that are not the trailing ones (the playground's rank-kept Reduction over any axes,
+// helium-playground/src/opgraph.rs:397-413: a column sum is Reduction{axes = [rows]}) is rewritten to the helium-ir
+// form the kernels take: swap_dims until the reduced dims are last, the kept ones in their old order, then a
+// reduction over the trailing dims.  The result has the same elements in the same order, so the leaf's buffer is
+// written exactly as before; the reduction kernel reads through the swapped view (column mode where a lane can
+// own a group), and no permuted copy exists.
+static Graph trail_reduction_leaves(const Graph& g) {
+  Graph o = g;
+  for (int& leaf : o.outputs) {
+    const he_node L = o.nodes[leaf];
+    if (L.kind != HE_OP_REDUCE || L.in[0] < 0) continue;
+    const he_node A = o.nodes[L.in[0]];
+    const int d = __builtin_popcount(L.axes);
+    if (d == 0 || A.rank < 2 || L.axes == (((1u << d) - 1u) << (A.rank - d))) continue;
+    std::vector<int> target, cur(A.rank);
+    for (int k = 0; k < A.rank; ++k)
+      if (!((L.axes >> k) & 1u)) target.push_back(k);
+    for (int k = 0; k < A.rank; ++k)
+      if ((L.axes >> k) & 1u) target.push_back(k);
+    for (int k = 0; k < A.rank; ++k) cur[k] = k;
+    int src = L.in[0];
+    he_node view = A;
+    for (int pos = 0; pos < A.rank; ++pos) {
+      int j = pos;
+      while (cur[j] != target[pos]) ++j;
+      if (j == pos) continue;
+      std::swap(cur[pos], cur[j]);
+      std::swap(view.shape[pos], view.shape[j]);
+      he_node sw = view;
+      sw.kind = HE_OP_SWAP_DIMS;
+      sw.sub_op = 0;
+      sw.in[0] = src;
+      sw.in[1] = sw.in[2] = -1;
+      sw.axis_a = pos;
+      sw.axis_b = j;
+      sw.axes = 0;
+      sw.const_bits = 0;
+      o.nodes.push_back(sw);
+      src = (int)o.nodes.size() - 1;
+    }
+    he_node red = L;
+    red.in[0] = src;
+    red.axes = ((1u << d) - 1u) << (A.rank - d);
+    red.rank = A.rank - d + 1;
+    for (int k = 0; k < A.rank - d; ++k) red.shape[k] = view.shape[k];
+    red.shape[A.rank - d] = 1;
+    o.nodes.push_back(red);
+    leaf = (int)o.nodes.size() - 1;
+  }
+  return o;
+}
+
 int32_t plan_pointwise(he_ctx* ctx, const Graph& g_in, he_plan** out, int* tier_only) {
-  const Graph g = peel_reshaped_reduction_leaves(g_in);
+  const Graph g = trail_reduction_leaves(peel_reshaped_reduction_leaves(g_in));
   for (const he_node& n : g.nodes)
     if (n.kind == HE_OP_MATMUL) HE_FAIL(HE_ERR_UNSUPPORTED, "pointwise: subgraph contains a matmul");
   PointwisePlan* plan = new PointwisePlan();

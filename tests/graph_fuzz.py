@@ -1,0 +1,48 @@
+"""Seeded random op graphs for the planners: a few matmuls with pointwise chains, shared operands, transposes,
+broadcast rows and column sums between them.  Everything is [S, S] bf16 (matmul results are scaled and cast back),
+so any value can feed any op and magnitudes stay near one."""
+from __future__ import annotations
+
+import numpy as np
+
+from helium_b200 import configs, ir
+
+
+def random_graph(seed: int, size: int = 128, n_ops: int = 12):
+    r = np.random.default_rng(1000 + seed)
+    g = ir.Graph()
+    S = size
+    pool = [g.new_input([S, S], ir.BF16) for _ in range(3)]
+    row = g.new_input([S], ir.BF16)
+    reductions = []
+    matmuls = 0
+    pick = lambda: pool[int(r.integers(len(pool)))] if r.random() < 0.5 else pool[-1 - int(r.integers(min(3, len(pool))))]
+    for k in range(n_ops):
+        u = r.random()
+        if u < 0.25 and matmuls < 3:
+            a, b = pick(), pick()
+            mm = g.matmul(a, b)
+            pool.append(g.cast(g.unary(ir.UN_MUL_CONST, mm, const=float(1.0 / np.sqrt(S))), ir.BF16))
+            matmuls += 1
+        elif u < 0.50:
+            op = [ir.UN_RELU, ir.UN_NEG, ir.UN_TANH, ir.UN_MUL_CONST, ir.UN_ADD_CONST][int(r.integers(5))]
+            pool.append(g.unary(op, pick(), const=0.5))
+        elif u < 0.75:
+            op = [ir.BIN_ADD, ir.BIN_MUL, ir.BIN_SUB][int(r.integers(3))]
+            pool.append(g.binary(op, pick(), pick()))
+        elif u < 0.85:
+            pool.append(g.binary(ir.BIN_ADD, pick(), g.broadcast_to(row, [S, S])))
+        elif u < 0.93:
+            pool.append(g.transpose(pick()))
+        else:
+            reductions.append(g.reduce_axes(ir.RED_SUM, pick(), [0]))
+    if matmuls == 0:
+        pool.append(g.cast(g.matmul(pool[-1], pool[0]), ir.BF16))
+    outs = [pool[-1]] + reductions
+    extra = pool[3 + int(r.integers(len(pool) - 3))]
+    if extra not in outs:
+        outs.append(extra)
+    for o in outs:
+        g.new_output(o)
+    ins = [configs.bf16_normal(r, (S, S), 0.5) for _ in range(3)] + [configs.bf16_normal(r, (S,), 0.5)]
+    return g, ins

@@ -253,3 +253,26 @@ def test_planner_arguments_are_checked():
         h.set_planner("search", depth=99)
     with pytest.raises(KeyError):
         h.set_planner("annealing")
+
+
+@pytest.mark.parametrize("seed", range(30))
+def test_invariants_on_random_graphs(seed):
+    """Shared operands, transposes, broadcast rows and column sums around up to three matmuls (tests/graph_fuzz.py):
+    every result of the search is a consistent set of kernels, each of which exists."""
+    from graph_fuzz import random_graph
+    g, _ = random_graph(seed)
+    h, head, groups = _search(g, max_states=2000)
+    text = h.plan_text()
+    assert "tier=0" not in text, text
+    assert text.count("tier=") == len(groups)
+    assert "tier=0" not in hb.HostGraph(g).plan_text()
+
+
+@pytest.mark.parametrize("shape,axes", [([128, 128], [0]), ([4, 64, 32], [1]), ([4, 64, 32], [0]), ([4, 64, 32], [0, 2]), ([8, 1, 16], [0])])
+def test_rank_kept_reductions_over_leading_axes_have_a_kernel(shape, axes):
+    """The playground's Reduction over any axes (opgraph.rs:397-413) as a kernel of its own, not only inside a
+    matmul epilogue: he_plan_supported accepts it (it is planned as swaps to a trailing reduction)."""
+    g = ir.Graph()
+    x = g.new_input(shape, ir.BF16)
+    g.new_output(g.reduce_axes(ir.RED_SUM, g.unary(ir.UN_RELU, x), axes))
+    assert hb.plan_supported(g, 0) == 1

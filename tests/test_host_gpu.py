@@ -166,3 +166,26 @@ def test_plans_of_the_fusion_search_give_the_oracle_numbers(ctx, name, capture):
         assert ex.stats()["instrs"] == 2, ex.stats()
     if name == "readme":
         assert ex.stats()["instrs"] == 1
+
+
+@pytest.mark.parametrize("planner", ["pairwise", "search"])
+@pytest.mark.parametrize("seed", range(10))
+def test_random_graphs_through_both_planners(ctx, seed, planner):
+    """Seeded random graphs (matmuls with shared operands, pointwise chains, transposes, broadcast rows, column
+    sums) planned either way and executed: the oracle, rounding exactly the tensors the plan writes to memory
+    (a kernel computes in f32 and rounds on store, pointwise/jit.rs:488-504), gives the expected numbers."""
+    import re
+    from graph_fuzz import random_graph
+    g, ins = random_graph(seed)
+    hg = hb.HostGraph(g)
+    hg.set_planner(planner, 0, 3000)
+    text = hg.plan_text()
+    written = set()
+    for m in re.finditer(r"tier=(\d) nodes=\[[\d,]*\] in=\[[\d,]*\] out=\[([\d,]*)\]", text):
+        assert int(m.group(1)) > 0, text
+        written |= {int(v) for v in m.group(2).split(",") if v}
+    want = O.evaluate(g, ins, round_nodes=sorted(written))
+    got, ex = _run_graph(ctx, g, ins, capture=bool(seed % 2), repeats=2, planner=planner)
+    for o, a, b in zip(g.outputs, got, want):
+        node = g.nodes[o]
+        assert O.rel_l2(O.decode(a, node.dtype, node.shape), O.decode(b, node.dtype, node.shape)) <= 2e-2, (seed, planner, o, text)

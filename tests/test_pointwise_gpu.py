@@ -197,6 +197,27 @@ def test_transposed_reductions_use_column_mode(ctx, shape, dtype):
     assert np.array_equal(got[0], got2[0])
 
 
+@pytest.mark.parametrize("shape,axes,dtype", [((300, 520), [0], ir.F32), ((1024, 512), [0], ir.BF16), ((4, 129, 64), [1], ir.F32),
+                                              ((4, 64, 33), [0], ir.F16), ((5, 32, 48), [0, 2], ir.F32), ((8, 1, 16), [0], ir.F32),
+                                              ((6, 7, 8, 9), [1, 2], ir.F32)])
+@pytest.mark.parametrize("op", [ir.RED_SUM, ir.RED_MAX, ir.RED_MEAN])
+def test_rank_kept_reductions_over_any_axes(ctx, shape, axes, dtype, op):
+    """The playground's Reduction{axes} (helium-playground/src/opgraph.rs:397-413) over dims that are not the
+    trailing ones, as a kernel of its own: planned as swaps to a trailing reduction, results as the oracle's in the
+    order of the kept dims, bit-stable, next to an elementwise output of the same kernel."""
+    g = ir.Graph()
+    x = g.new_input(list(shape), dtype)
+    y = g.unary(ir.UN_TANH, x)
+    g.new_output(g.reduce_axes(op, y, axes))
+    ins = [O.encode(rng(23).standard_normal(shape), dtype)]
+    got, plan = _run(ctx, g, ins)
+    want = O.evaluate(g, ins)
+    assert got[0].size == want[0].size
+    assert O.rel_l2(got[0].reshape(-1).astype(np.float64), want[0].reshape(-1).astype(np.float64)) <= 1e-5, plan.description
+    got2, _ = _run(ctx, g, ins)
+    assert np.array_equal(got[0], got2[0])
+
+
 @pytest.mark.parametrize("shape,dtype", [((4096, 1024), ir.BF16), ((300, 520), ir.F32), ((3, 513, 64), ir.F16), ((8192, 4096), ir.BF16)])
 def test_dense_column_sum_kernel(ctx, shape, dtype):
     """Bias gradient of a plain tensor (swap_dims -> reduce_sum -> reshape with nothing in front):
