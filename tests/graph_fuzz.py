@@ -8,12 +8,17 @@ import numpy as np
 from helium_b200 import configs, ir
 
 
-def random_graph(seed: int, size: int = 128, n_ops: int = 12):
+def random_graph(seed: int, size: int = 128, n_ops: int = 12, flavour: str = "bf16"):
+    """flavour "bf16": [S, S] bf16 tensors, bf16 x bf16 -> f32 matmuls; "f32": everything f32, f32 matmuls;
+    "batched": [3, S, S] bf16 tensors and batched matmuls (transposes swap the last two dims)."""
     r = np.random.default_rng(1000 + seed)
     g = ir.Graph()
     S = size
-    pool = [g.new_input([S, S], ir.BF16) for _ in range(3)]
-    row = g.new_input([S], ir.BF16)
+    dt = ir.F32 if flavour == "f32" else ir.BF16
+    prec = ir.PREC_F32_F32 if flavour == "f32" else ir.PREC_BF16_F32
+    full = [3, S, S] if flavour == "batched" else [S, S]
+    pool = [g.new_input(full, dt) for _ in range(3)]
+    row = g.new_input([S], dt)
     reductions = []
     matmuls = 0
     pick = lambda: pool[int(r.integers(len(pool)))] if r.random() < 0.5 else pool[-1 - int(r.integers(min(3, len(pool))))]
@@ -21,8 +26,8 @@ def random_graph(seed: int, size: int = 128, n_ops: int = 12):
         u = r.random()
         if u < 0.25 and matmuls < 3:
             a, b = pick(), pick()
-            mm = g.matmul(a, b)
-            pool.append(g.cast(g.unary(ir.UN_MUL_CONST, mm, const=float(1.0 / np.sqrt(S))), ir.BF16))
+            mm = g.matmul(a, b, prec)
+            pool.append(g.cast(g.unary(ir.UN_MUL_CONST, mm, const=float(1.0 / np.sqrt(S))), dt))
             matmuls += 1
         elif u < 0.50:
             op = [ir.UN_RELU, ir.UN_NEG, ir.UN_TANH, ir.UN_MUL_CONST, ir.UN_ADD_CONST][int(r.integers(5))]
@@ -31,18 +36,22 @@ def random_graph(seed: int, size: int = 128, n_ops: int = 12):
             op = [ir.BIN_ADD, ir.BIN_MUL, ir.BIN_SUB][int(r.integers(3))]
             pool.append(g.binary(op, pick(), pick()))
         elif u < 0.85:
-            pool.append(g.binary(ir.BIN_ADD, pick(), g.broadcast_to(row, [S, S])))
+            pool.append(g.binary(ir.BIN_ADD, pick(), g.broadcast_to(row, full)))
         elif u < 0.93:
             pool.append(g.transpose(pick()))
         else:
-            reductions.append(g.reduce_axes(ir.RED_SUM, pick(), [0]))
+            reductions.append(g.reduce_axes([ir.RED_SUM, ir.RED_MAX, ir.RED_MEAN][int(r.integers(3))] if flavour != "bf16" else ir.RED_SUM,
+                                            pick(), [len(full) - 2]))
     if matmuls == 0:
-        pool.append(g.cast(g.matmul(pool[-1], pool[0]), ir.BF16))
+        pool.append(g.cast(g.matmul(pool[-1], pool[0], prec), dt))
     outs = [pool[-1]] + reductions
     extra = pool[3 + int(r.integers(len(pool) - 3))]
     if extra not in outs:
         outs.append(extra)
     for o in outs:
         g.new_output(o)
-    ins = [configs.bf16_normal(r, (S, S), 0.5) for _ in range(3)] + [configs.bf16_normal(r, (S,), 0.5)]
+    if flavour == "f32":
+        ins = [(r.standard_normal(full) * 0.5).astype(np.float32) for _ in range(3)] + [(r.standard_normal(S) * 0.5).astype(np.float32)]
+    else:
+        ins = [configs.bf16_normal(r, tuple(full), 0.5) for _ in range(3)] + [configs.bf16_normal(r, (S,), 0.5)]
     return g, ins

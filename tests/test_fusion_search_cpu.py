@@ -255,12 +255,13 @@ def test_planner_arguments_are_checked():
         h.set_planner("annealing")
 
 
+@pytest.mark.parametrize("flavour", ["bf16", "f32", "batched"])
 @pytest.mark.parametrize("seed", range(30))
-def test_invariants_on_random_graphs(seed):
+def test_invariants_on_random_graphs(seed, flavour):
     """Shared operands, transposes, broadcast rows and column sums around up to three matmuls (tests/graph_fuzz.py):
     every result of the search is a consistent set of kernels, each of which exists."""
     from graph_fuzz import random_graph
-    g, _ = random_graph(seed)
+    g, _ = random_graph(seed, flavour=flavour)
     h, head, groups = _search(g, max_states=2000)
     text = h.plan_text()
     assert "tier=0" not in text, text

@@ -169,14 +169,15 @@ def test_plans_of_the_fusion_search_give_the_oracle_numbers(ctx, name, capture):
 
 
 @pytest.mark.parametrize("planner", ["pairwise", "search"])
+@pytest.mark.parametrize("flavour", ["bf16", "f32", "batched"])
 @pytest.mark.parametrize("seed", range(10))
-def test_random_graphs_through_both_planners(ctx, seed, planner):
+def test_random_graphs_through_both_planners(ctx, seed, flavour, planner):
     """Seeded random graphs (matmuls with shared operands, pointwise chains, transposes, broadcast rows, column
     sums) planned either way and executed: the oracle, rounding exactly the tensors the plan writes to memory
     (a kernel computes in f32 and rounds on store, pointwise/jit.rs:488-504), gives the expected numbers."""
     import re
     from graph_fuzz import random_graph
-    g, ins = random_graph(seed)
+    g, ins = random_graph(seed, flavour=flavour)
     hg = hb.HostGraph(g)
     hg.set_planner(planner, 0, 3000)
     text = hg.plan_text()
@@ -188,4 +189,5 @@ def test_random_graphs_through_both_planners(ctx, seed, planner):
     got, ex = _run_graph(ctx, g, ins, capture=bool(seed % 2), repeats=2, planner=planner)
     for o, a, b in zip(g.outputs, got, want):
         node = g.nodes[o]
-        assert O.rel_l2(O.decode(a, node.dtype, node.shape), O.decode(b, node.dtype, node.shape)) <= 2e-2, (seed, planner, o, text)
+        tol = 1e-4 if flavour == "f32" else 2e-2
+        assert O.rel_l2(O.decode(a, node.dtype, node.shape), O.decode(b, node.dtype, node.shape)) <= tol, (seed, flavour, planner, o, text)
