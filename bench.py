@@ -1094,6 +1094,42 @@ def measure(wl, key, steps, warmup, world, dev, barrier, brief, peaks, busy_s=0.
     return rec
 
 
+def _parse_cpulist(text: str):
+    cpus = set()
+    for part in text.strip().split(","):
+        if not part:
+            continue
+        lo, _, hi = part.partition("-")
+        cpus.update(range(int(lo), int(hi or lo) + 1))
+    return cpus
+
+
+def bind_to_gpu_numa_node(torch, local_rank: int, sysfs: str = "/sys"):
+    """With several ranks on one host every rank stages its inputs through pinned host memory; pages pinned on the
+    other socket cross the inter-socket link on every copy.  Before any pinned buffer exists the process is moved
+    to the CPUs of the NUMA node its GPU hangs off (first touch then places the buffers there).  Nothing happens
+    when the host shows one node, the GPU's node is unknown, or those CPUs are outside the process's CPU set.
+    Returns a note for the bench line, or None."""
+    try:
+        nodes = [d for d in os.listdir(os.path.join(sysfs, "devices/system/node")) if d.startswith("node") and d[4:].isdigit()]
+        if len(nodes) < 2:
+            return None
+        pr = torch.cuda.get_device_properties(local_rank)
+        addr = "%04x:%02x:%02x.0" % (pr.pci_domain_id, pr.pci_bus_id, pr.pci_device_id)
+        with open(os.path.join(sysfs, "bus/pci/devices", addr, "numa_node")) as f:
+            node = int(f.read().strip())
+        if node < 0:
+            return None
+        with open(os.path.join(sysfs, "devices/system/node", f"node{node}", "cpulist")) as f:
+            cpus = _parse_cpulist(f.read()) & os.sched_getaffinity(0)
+        if not cpus:
+            return None
+        os.sched_setaffinity(0, cpus)
+        return f"rank bound to the {len(cpus)} CPUs of NUMA node {node} (GPU {addr}) before pinned buffers were allocated"
+    except (OSError, ValueError, AttributeError):
+        return None
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -1139,6 +1175,7 @@ def main():
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: helium_b200 has no CPU path")
     torch.cuda.set_device(local_rank)
+    numa_note = bind_to_gpu_numa_node(torch, local_rank) if world > 1 else None
     if world > 1:
         import datetime
         # a short collective timeout: a rank that falls out of step must end the run in minutes, not hold the GPUs
@@ -1177,6 +1214,8 @@ def main():
         sampler.start()
     line = measure(wl, args.workload, args.steps, args.warmup, world, dev, barrier, args.brief, peaks)
     ctx.poll()
+    if numa_note:
+        line["host_affinity"] = numa_note
     if comm is not None:
         comm.poll()
         line["config"]["nccl_max_ctas"] = args.nccl_ctas
