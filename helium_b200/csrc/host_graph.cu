@@ -333,6 +333,7 @@ int32_t heh_graph_plan_text(he_ctx* ctx, heh_graph* g, char* buf, size_t cap) {
   if (!g || !buf) HE_FAIL(HE_ERR_INVALID, "heh_graph_plan_text: null argument");
   if (g->g.outputs.empty()) HE_FAIL(HE_ERR_INVALID, "graph has no outputs");
   std::string plan_error;
+  g->g.live_mask = g->g.live();
   Plan plan = generate_plan(g->g, ctx, g->planner, &plan_error);
   if (!plan_error.empty()) HE_FAIL(HE_ERR_UNSUPPORTED, "fusion search: %s", plan_error.c_str());
   std::ostringstream os;
@@ -421,6 +422,7 @@ int32_t heh_exec_create(he_ctx* ctx, heh_graph* g, const void* const* inputs, vo
   std::unique_ptr<heh_exec> e(new heh_exec());
   e->ctx = ctx;
   std::string plan_error;
+  g->g.live_mask = g->g.live();
   e->plan = generate_plan(G, ctx, g->planner, &plan_error);
   if (!plan_error.empty()) HE_FAIL(HE_ERR_UNSUPPORTED, "fusion search: %s", plan_error.c_str());
   DeviceGuard device_guard(ctx->device);   // the caller's current device is restored on return

@@ -20,6 +20,7 @@ struct OpGraph {
   std::vector<NodeId> inputs;           // HE_OP_INPUT nodes in creation order
   std::vector<NodeId> outputs;          // nodes marked as outputs, in marking order
   std::vector<std::vector<NodeId>> outbound;
+  std::vector<bool> live_mask;          // set by the planner: consumers that no output needs do not make a node a leaf
 
   NodeId add(const he_node& n) {
     nodes.push_back(n);
@@ -71,7 +72,7 @@ struct OpSubgraph {
     for (NodeId n : ns) {
       bool leaf = g->is_output(n);
       for (NodeId c : g->outbound[n])
-        if (!in_set.count(c)) leaf = true;
+        if (!in_set.count(c) && (g->live_mask.empty() || g->live_mask[c])) leaf = true;
       if (leaf) s.leafs.push_back(n);
     }
     return s;

@@ -255,7 +255,7 @@ def test_planner_arguments_are_checked():
         h.set_planner("annealing")
 
 
-@pytest.mark.parametrize("flavour", ["bf16", "f32", "batched"])
+@pytest.mark.parametrize("flavour", ["bf16", "f32", "batched", "f16_select"])
 @pytest.mark.parametrize("seed", range(30))
 def test_invariants_on_random_graphs(seed, flavour):
     """Shared operands, transposes, broadcast rows and column sums around up to three matmuls (tests/graph_fuzz.py):

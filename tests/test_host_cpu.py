@@ -86,6 +86,17 @@ def test_dead_nodes_are_pruned():
     assert len(ins) == 1 and ins[0]["nodes"] == [2]
 
 
+def test_dead_consumers_do_not_make_outputs():
+    """A value that only a dead node reads besides its live consumers is not written to memory."""
+    g = ir.Graph()
+    x = g.new_input([64, 64], ir.F32)
+    t = g.unary(ir.UN_TANH, x)
+    g.unary(ir.UN_EXP, t)  # dead consumer of t
+    g.new_output(g.unary(ir.UN_RELU, t))
+    ins = _instrs(hb.HostGraph(g).plan_text())
+    assert len(ins) == 1 and ins[0]["nodes"] == [1, 3] and ins[0]["outputs"] == [3]
+
+
 def test_matmul_epilogue_and_mainloop_fuse_through_the_planner():
     g = ir.Graph()
     a = g.new_input([512, 256], ir.BF16); mk = g.new_input([512, 256], ir.BF16); b = g.new_input([256, 512], ir.BF16)
