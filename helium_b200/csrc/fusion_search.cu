@@ -633,7 +633,7 @@ std::vector<Subdivision> subdivide(const OpGraph& g) {
   return out;
 }
 
-SearchResult search_fusions(const OpGraph& g, he_ctx* ctx, const SearchOptions& opt) {
+SearchResult search_fusions(const OpGraph& g, he_ctx* ctx, const SearchOptions& opt, const std::vector<Instr>* seed) {
   SearchResult r;
   Searcher S(g, ctx, opt);
   State s = S.identity();
@@ -670,6 +670,47 @@ SearchResult search_fusions(const OpGraph& g, he_ctx* ctx, const SearchOptions& 
   Searcher::Best from_singletons{singletons, r.cost_identity, false};
   descend_all(from_singletons);
   if (from_singletons.cost < best.cost) best = from_singletons;
+  if (seed) {
+    // the other planner's instructions as a state: operand side = the matmul's ancestors inside the instruction
+    State t;
+    t.exporter.assign(S.N, -1);
+    bool usable = true;
+    for (const Instr& in : *seed) {
+      Group G;
+      for (NodeId n : in.sub.nodes)
+        if (S.is_anchor(n)) {
+          usable = usable && G.anchor < 0;
+          G.anchor = n;
+        }
+      std::set<NodeId> pre;
+      if (G.anchor >= 0) {
+        std::vector<NodeId> stack{G.anchor};
+        while (!stack.empty()) {
+          NodeId c = stack.back();
+          stack.pop_back();
+          for (NodeId p : g.inbound(c))
+            if (in.sub.contains(p) && pre.insert(p).second) stack.push_back(p);
+        }
+      }
+      for (NodeId n : in.sub.nodes) {
+        if (n == G.anchor) continue;
+        if (pre.count(n)) G.pre.push_back(n);
+        else G.post.push_back(n);
+      }
+      const int id = t.next_id++;
+      for (NodeId o : in.sub.leafs) {
+        usable = usable && G.exportable(o) && t.exporter[o] < 0;
+        t.exporter[o] = id;
+      }
+      t.groups.emplace(id, std::move(G));
+    }
+    if (usable && S.fix(t) && S.acyclic(t) && S.legal(t)) {
+      r.cost_seed = S.cost(t);
+      Searcher::Best from_seed{t, r.cost_seed, false};
+      descend_all(from_seed);
+      if (from_seed.cost < best.cost) best = from_seed;
+    }
+  }
   r.cost_best = best.cost;
   r.states = S.states;
   std::vector<int> order;

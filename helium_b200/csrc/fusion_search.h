@@ -41,12 +41,16 @@ struct SearchGroup {        // one kernel of the result
 struct SearchResult {
   std::vector<SearchGroup> groups;   // in a topological order
   double cost_identity = 0, cost_maximal = 0, cost_best = 0;
+  double cost_seed = -1;             // estimate for the seed plan (the pairwise planner's), -1 if none was usable
   int states = 0, subdivisions = 0, recomputed_nodes = 0;
   bool valid = false;
   std::string error;
 };
 
-SearchResult search_fusions(const OpGraph& g, he_ctx* ctx, const SearchOptions& opt);
+// `seed`: instructions of another planner for the same graph (each node in exactly one of them).  When they form a
+// state of the search (no operand-side node of a matmul is written to memory) a third descent starts there, so the
+// result is never dearer, by the cost model, than the seed plan.
+SearchResult search_fusions(const OpGraph& g, he_ctx* ctx, const SearchOptions& opt, const std::vector<Instr>* seed = nullptr);
 
 // Instructions for generate_plan from a search result.
 std::vector<Instr> instrs_from_search(const OpGraph& g, const SearchResult& r);

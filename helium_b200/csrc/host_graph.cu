@@ -105,39 +105,53 @@ struct PlannerChoice {
   SearchOptions search;
 };
 
+// The reference's instruction selection: one instruction per live node, merged pairwise and greedily.
+static InstrGraph pairwise_instr_graph(const OpGraph& g, he_ctx* ctx) {
+  InstrGraph ig;
+  // make_instr_graph (plan_generation.rs:259-270), dead nodes pruned first (backend.rs:46)
+  const std::vector<bool> live = g.live();
+  for (NodeId id = 0; id < (NodeId)g.nodes.size(); ++id)
+    if (g.nodes[id].kind != HE_OP_INPUT && live[id]) ig.insert(make_instr_for_op(&g, id));
+
+  // do_fusions (plan_generation.rs:243-256)
+  std::set<int> working;
+  for (auto& kv : ig.instrs) working.insert(kv.first);
+  while (!working.empty()) {
+    const int current = *working.begin();
+    working.erase(working.begin());
+    for (int next : ig.dependents(current)) {
+      if (ig.instrs.at(current).can_fuse_with(ig.instrs.at(next), ctx) && !ig.exist_multiple_paths(current, next)) {
+        Instr a = ig.remove(current), b = ig.remove(next);
+        const int nid = ig.insert(a.fuse_with(b));
+        working.erase(next);
+        working.insert(nid);
+        break;
+      }
+    }
+  }
+  return ig;
+}
+
+// The fusion search, seeded with the pairwise plan so that its result is never dearer than that plan by the model.
+static SearchResult run_search(const OpGraph& g, he_ctx* ctx, const SearchOptions& opt) {
+  std::vector<Instr> seed;
+  for (auto& kv : pairwise_instr_graph(g, ctx).instrs) seed.push_back(kv.second);
+  return search_fusions(g, ctx, opt, &seed);
+}
+
 static Plan generate_plan(const OpGraph& g, he_ctx* ctx, const PlannerChoice& choice, std::string* error) {
   InstrGraph ig;
   if (choice.mode == 1) {
     // every instruction comes out of the search with its outputs chosen: a node that several instructions
     // recompute is written to memory by one of them only
-    SearchResult r = search_fusions(g, ctx, choice.search);
+    SearchResult r = run_search(g, ctx, choice.search);
     if (!r.valid) {
       if (error) *error = r.error;
       return Plan{};
     }
     for (Instr& in : instrs_from_search(g, r)) ig.insert(std::move(in));
   } else {
-    // make_instr_graph (plan_generation.rs:259-270), dead nodes pruned first (backend.rs:46)
-    const std::vector<bool> live = g.live();
-    for (NodeId id = 0; id < (NodeId)g.nodes.size(); ++id)
-      if (g.nodes[id].kind != HE_OP_INPUT && live[id]) ig.insert(make_instr_for_op(&g, id));
-
-    // do_fusions (plan_generation.rs:243-256)
-    std::set<int> working;
-    for (auto& kv : ig.instrs) working.insert(kv.first);
-    while (!working.empty()) {
-      const int current = *working.begin();
-      working.erase(working.begin());
-      for (int next : ig.dependents(current)) {
-        if (ig.instrs.at(current).can_fuse_with(ig.instrs.at(next), ctx) && !ig.exist_multiple_paths(current, next)) {
-          Instr a = ig.remove(current), b = ig.remove(next);
-          const int nid = ig.insert(a.fuse_with(b));
-          working.erase(next);
-          working.insert(nid);
-          break;
-        }
-      }
-    }
+    ig = pairwise_instr_graph(g, ctx);
   }
 
   // generate_plan_from_graph (plan_generation.rs:275-321): Kahn layers
@@ -378,11 +392,13 @@ static void print_nodes(std::ostringstream& os, const char* name, const std::vec
 int32_t heh_graph_search_text(he_ctx* ctx, heh_graph* g, char* buf, size_t cap) {
   if (!g || !buf) HE_FAIL(HE_ERR_INVALID, "heh_graph_search_text: null argument");
   if (g->g.outputs.empty()) HE_FAIL(HE_ERR_INVALID, "graph has no outputs");
-  SearchResult r = search_fusions(g->g, ctx, g->planner.search);
+  g->g.live_mask = g->g.live();
+  SearchResult r = run_search(g->g, ctx, g->planner.search);
   if (!r.valid) HE_FAIL(HE_ERR_UNSUPPORTED, "fusion search: %s", r.error.c_str());
   std::ostringstream os;
   os.precision(9);
-  os << "cost identity=" << r.cost_identity << " maximal=" << r.cost_maximal << " best=" << r.cost_best << " states=" << r.states
+  os << "cost identity=" << r.cost_identity << " maximal=" << r.cost_maximal << " pairwise=" << r.cost_seed << " best=" << r.cost_best
+     << " states=" << r.states
      << " subdivisions=" << r.subdivisions << " recomputed=" << r.recomputed_nodes << "\n";
   for (size_t i = 0; i < r.groups.size(); ++i) {
     const SearchGroup& sg = r.groups[i];

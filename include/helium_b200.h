@@ -256,9 +256,11 @@ int32_t heh_graph_plan_text(he_ctx* ctx, heh_graph* g, char* buf, size_t cap);
  * the chosen planner.  The environment variable HE_PLANNER=search makes mode 1 the default of graphs
  * created afterwards. */
 int32_t heh_graph_set_planner(heh_graph* g, int32_t mode, int32_t depth, int32_t max_states);
-/* Runs the fusion search and writes its result: a first line "cost identity=<s> maximal=<s> best=<s>
- * states=<n> subdivisions=<n> recomputed=<n>" (estimated seconds with one kernel per node, after the
- * greedy start, and for the result), then one line per kernel in a topological order:
+/* Runs the fusion search and writes its result: a first line "cost identity=<s> maximal=<s>
+ * pairwise=<s> best=<s> states=<n> subdivisions=<n> recomputed=<n>" (estimated seconds with one kernel
+ * per node, after the greedy start, for the plan of the pairwise planner -- which seeds a descent of
+ * its own, so best <= pairwise; -1 if that plan writes an operand-side value to memory and is no state
+ * of the search -- and for the result), then one line per kernel in a topological order:
  * "group <i> FusedMatmul|Pointwise anchor=<node|-1> pre=[..] post=[..] in=[..] out=[..] seconds=<s>". */
 int32_t heh_graph_search_text(he_ctx* ctx, heh_graph* g, char* buf, size_t cap);
 /* subdivide (subdivision.rs:24-113): one line per subdivision, its nodes in ascending order; a matmul

@@ -65,6 +65,9 @@ def _check_invariants(g, head, groups):
     assert set(g.outputs) - inputs <= written
     # the greedy start merges without looking at the cost, so it may be dearer than one kernel per node
     assert head["best"] <= min(head["maximal"], head["identity"]) * (1 + 1e-9)
+    # the pairwise planner's plan seeds a descent of its own: never dearer than the reference's planner, by the model
+    if head["pairwise"] >= 0:
+        assert head["best"] <= head["pairwise"] * (1 + 1e-9)
     assert abs(sum(grp["seconds"] for grp in groups) - head["best"]) <= 1e-6 * head["best"] + 1e-12
     count = {}
     for grp in groups:
