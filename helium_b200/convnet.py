@@ -113,16 +113,10 @@ class _Bn:
 
 
 class ConvNet:
-    def __init__(self, ctx: Context, batch: int, image_hw: int = 224, classes: int = 1000, device=None, momentum: float = 0.9,
-                 overlap_filter_gradients: bool = True):
+    def __init__(self, ctx: Context, batch: int, image_hw: int = 224, classes: int = 1000, device=None, momentum: float = 0.9):
         import torch
 
         self.torch, self.ctx = torch, ctx
-        # Filter gradients feed nothing but the optimiser, so the backward pass issues them on a second stream
-        # (with a workspace of their own): they run under the data-gradient / batch-norm chain, whose elementwise
-        # and fold kernels leave the tensor cores, and at times most SMs, idle.  Every kernel is deterministic, so
-        # the step's numbers do not depend on how the two streams interleave.
-        self.overlap_filter_gradients = overlap_filter_gradients
         self.N, self.hw, self.classes, self.momentum = batch, image_hw, classes, momentum
         dev = device if device is not None else torch.device("cuda", ctx.device)
         self.dev = dev
@@ -164,9 +158,6 @@ class ConvNet:
         self._ws_bytes = 0
         self._build()
         self.ws = torch.empty(self._ws_bytes + 256, dtype=torch.uint8, device=dev)
-        side_bytes = max([pl.workspace_bytes for k, pl in self.plans.items() if k.endswith(".wgrad")] + [0])
-        self.ws_side = torch.empty(side_bytes + 256, dtype=torch.uint8, device=dev)
-        self.side = torch.cuda.Stream(device=dev)
         self.labels = torch.zeros(batch, dtype=torch.int32, device=dev)
         self.loss = torch.zeros(batch, dtype=torch.float32, device=dev)
         self.launches = 0
@@ -261,22 +252,6 @@ class ConvNet:
         self.plans[key].launch_ptrs([t.data_ptr() for t in ins], [t.data_ptr() for t in outs], self._ws_ptr())
         self.launches += self.plans[key].last_launch_count
 
-    def _launch_wgrad(self, key, ins, outs):
-        """A filter gradient: on the side stream once everything issued so far on the main stream has finished
-        (its two operands are among that).  Returns an event the main stream must wait for before it overwrites
-        either operand, or None when the kernel was issued in line."""
-        if not self.overlap_filter_gradients:
-            self._launch(key, ins, outs)
-            return None
-        torch = self.torch
-        self.side.wait_stream(torch.cuda.current_stream(self.dev))
-        with torch.cuda.stream(self.side):
-            self.plans[key].launch_ptrs([t.data_ptr() for t in ins], [t.data_ptr() for t in outs], (self.ws_side.data_ptr() + 255) // 256 * 256)
-            done = torch.cuda.Event()
-            done.record(self.side)
-        self.launches += self.plans[key].last_launch_count
-        return done
-
     def _bn_finalize(self, name, count, gamma, beta):
         b = self.bns[name]
         rm, rv = self.running[name.replace("#2", "")]
@@ -363,7 +338,7 @@ class ConvNet:
         A, W, V, B, GW, GV = self.acts, self.W16, self.V, self.bns, self.GW, self.GV
         x = self.x_last
         # tail: 1x1 convolution, then relu(bn(x_last))
-        self._launch_wgrad("tail.wgrad", [A["dy"], A["t"]], [GW["tail.w"]])
+        self._launch("tail.wgrad", [A["dy"], A["t"]], [GW["tail.w"]])
         self._colsum(A["dy"], GV["tail.b"])
         tb = B["tail_bn"]
         self._launch("tail.dgrad", [A["dy"], W["tail.w"], x, tb.scale, tb.shift], [A["tail.g"], tb.bstats])
@@ -374,29 +349,27 @@ class ConvNet:
             xin = A[p + ".out"]
             # ---- basic block: out = conv2(relu(bn2(conv1(relu(bn1(xin)))))) + xin
             # (the bias gradients, column sums of each flow, come out of the pass that produced the flow)
-            self._launch_wgrad(q + ".conv2.wgrad", [dout, A[q + ".a2"]], [GW[q + ".conv2.w"]])
+            self._launch(q + ".conv2.wgrad", [dout, A[q + ".a2"]], [GW[q + ".conv2.w"]])
             b2 = B[q + ".bn2"]
             self._launch(q + ".conv2.dgrad", [dout, W[q + ".conv2.w"], A[q + ".c1"], b2.scale, b2.shift], [A[q + ".g"], b2.bstats])
             self._bn_backward(q + ".bn2", A[q + ".g"], A[q + ".c1"], A[q + ".gx"], q + ".bn2", colsum_to=GV[q + ".conv1.b"])   # gradient at c1
             dc1 = A[q + ".gx"]
-            gx_read = self._launch_wgrad(q + ".conv1.wgrad", [dc1, A[q + ".a"]], [GW[q + ".conv1.w"]])
+            self._launch(q + ".conv1.wgrad", [dc1, A[q + ".a"]], [GW[q + ".conv1.w"]])
             b1 = B[q + ".bn1"]
             self._launch(q + ".conv1.dgrad", [dc1, W[q + ".conv1.w"], xin, b1.scale, b1.shift], [A[q + ".g"], b1.bstats])
             self._bn_backward(q + ".bn1", A[q + ".g"], xin, A[p + ".g"], q + ".bn1", addend=dout, colsum_to=GV[p + ".conv2.b"])   # gradient at xin (+ the skip)
             dout = A[p + ".g"]
             # ---- downsample block: out = conv2(relu(bn2(conv1(relu(bn1(a)))))) + sc(a),  a = relu(bn1(x))
             xprev = A["h"] if i == 0 else A[f"seg{i - 1}.basic.out"]
-            self._launch_wgrad(p + ".conv2.wgrad", [dout, A[p + ".a3"]], [GW[p + ".conv2.w"]])
+            self._launch(p + ".conv2.wgrad", [dout, A[p + ".a3"]], [GW[p + ".conv2.w"]])
             self.torch_copy(GV[p + ".sc.b"], GV[p + ".conv2.b"])       # both biases see the same flow
-            self._launch_wgrad(p + ".sc.wgrad", [dout, A[p + ".a"]], [GW[p + ".sc.w"]])
+            self._launch(p + ".sc.wgrad", [dout, A[p + ".a"]], [GW[p + ".sc.w"]])
             self._launch(p + ".sc.dgrad", [dout, W[p + ".sc.w"]], [A[p + ".dsc"]])
             b2 = B[p + ".bn2"]
             self._launch(p + ".conv2.dgrad", [dout, W[p + ".conv2.w"], A[p + ".c1"], b2.scale, b2.shift], [A[q + ".g"], b2.bstats])
-            if gx_read is not None:
-                self.torch.cuda.current_stream(self.dev).wait_event(gx_read)   # the basic block's conv1 filter gradient still reads this buffer
             self._bn_backward(p + ".bn2", A[q + ".g"], A[p + ".c1"], A[q + ".gx"], p + ".bn2", colsum_to=GV[p + ".conv1.b"])   # gradient at c1
             dc1 = A[q + ".gx"]
-            self._launch_wgrad(p + ".conv1.wgrad", [dc1, A[p + ".a2"]], [GW[p + ".conv1.w"]])
+            self._launch(p + ".conv1.wgrad", [dc1, A[p + ".a2"]], [GW[p + ".conv1.w"]])
             b12, b11 = B[p + ".bn1#2"], B[p + ".bn1"]
             self._launch(p + ".conv1.dgrad", [dc1, W[p + ".conv1.w"], A[p + ".a"], b12.scale, b12.shift], [A[p + ".ga"], b12.bstats])
             # second application of bn1 (on a), plus the shortcut's gradient, masked by the first rectifier
@@ -417,9 +390,7 @@ class ConvNet:
             else:
                 self._bn_backward(p + ".bn1", A[p + ".gx"], xprev, A[p + ".ga"], p + ".bn1", colsum_to=GV[f"seg{i - 1}.basic.conv2.b"])
                 dout = A[p + ".ga"]
-        self._launch_wgrad("head.wgrad", [dout, A["cols"]], [GW["head.w"]])
-        if self.overlap_filter_gradients:
-            self.torch.cuda.current_stream(self.dev).wait_stream(self.side)   # the gradients are complete when backward() returns
+        self._launch("head.wgrad", [dout, A["cols"]], [GW["head.w"]])
 
     def torch_copy(self, dst, src):
         """Device-to-device copy of a small parameter-gradient vector (a cudaMemcpyAsync on the current stream)."""

@@ -318,9 +318,14 @@ __global__ void __launch_bounds__(32 * 11, 1) conv_fprop_kernel(const __grid_con
           const int my_stage = stage;
           const uint32_t my_phase = phase;
           if (++stage == GROUPS) { stage = 0; phase ^= 1u; }
+          // Both threads wait for EVERY group, also the other thread's.  A parity wait only tells "the latest phase
+          // of this parity has completed": a thread that skipped the other's phase L of a slot and came back for
+          // phase L + 1 while L was still loading (loads of different groups complete in any order) was let through
+          // by phase L - 1, issued MMAs on stale tiles and released the slot a second time -- about once in 10^4
+          // launches the ring then stopped.  Observing every phase in ring order rules that out.
+          if (!ptx::mbar_wait(bar_full(my_stage), my_phase, abort_flag, status, 3, my_stage, wait_us)) { alive = false; break; }
           if ((g_idx & 1) != me) continue;
           const int nsub = min(KSUB, k_blocks - kb0);
-          if (!ptx::mbar_wait(bar_full(my_stage), my_phase, abort_flag, status, 3, my_stage, wait_us)) { alive = false; break; }
           ptx::tcgen05_fence_after();
 #pragma unroll
           for (int u = 0; u < KSUB; ++u) {
