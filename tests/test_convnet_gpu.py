@@ -134,3 +134,25 @@ def test_graph_replay_gives_the_eager_step(ctx):
     for a, b in zip(res[0][:5], res[1][:5]):
         assert torch.equal(bits(a), bits(b))
     assert res[0][5] == res[1][5] > 200
+
+
+def test_many_steps_leave_the_device_status_clean_and_repeat_bit_for_bit(ctx):
+    """A long run of graph-replayed steps (about 2 x 10^4 convolution launches at the benchmark's layer shapes):
+    no bounded wait may give up (he_ctx_poll_device_status stays clean), and the forward pass of the same weights
+    and images gives the same loss bits every time.  Guards the pipelines of the multi-issuer convolution kernels:
+    a parity wait that skipped a barrier phase once stopped a ring about once in 10^4 launches."""
+    import torch
+    net, params, bits, labels = _setup(ctx, 64, 224, 1000)
+    net.step(0.0)                      # first step eager; lr 0 keeps the weights, momentum only accumulates zeros
+    torch.cuda.synchronize()
+    ctx.poll()
+    first = net.loss.clone()
+    for i in range(120):
+        net.step(0.0, graph=True)
+        if i % 40 == 39:
+            torch.cuda.synchronize()
+            ctx.poll()
+            assert torch.equal(net.loss, first), i
+    torch.cuda.synchronize()
+    ctx.poll()
+    assert torch.equal(net.loss, first)
