@@ -340,6 +340,7 @@ int32_t heh_graph_new_op(heh_graph* g, const he_node* op, int32_t* node_out) {
 int32_t heh_graph_new_output(heh_graph* g, int32_t node) {
   if (!g || node < 0 || node >= (int32_t)g->g.nodes.size()) HE_FAIL(HE_ERR_INVALID, "heh_graph_new_output: bad node");
   g->g.outputs.push_back(node);
+  g->g.live_mask.clear();
   return HE_OK;
 }
 

@@ -25,6 +25,7 @@ struct OpGraph {
   NodeId add(const he_node& n) {
     nodes.push_back(n);
     outbound.emplace_back();
+    live_mask.clear();   // belongs to the graph as it was when a planner last ran
     const NodeId id = (NodeId)nodes.size() - 1;
     for (int k = 0; k < 3; ++k)
       if (n.in[k] >= 0) outbound[n.in[k]].push_back(id);

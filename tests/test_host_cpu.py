@@ -97,6 +97,33 @@ def test_dead_consumers_do_not_make_outputs():
     assert len(ins) == 1 and ins[0]["nodes"] == [1, 3] and ins[0]["outputs"] == [3]
 
 
+def test_a_graph_can_grow_after_it_was_planned():
+    """Planning remembers which nodes are live; nodes and outputs added afterwards must not be judged by that."""
+    g = ir.Graph()
+    x = g.new_input([64, 64], ir.F32)
+    t = g.unary(ir.UN_TANH, x)
+    e = g.unary(ir.UN_EXP, t)          # dead for now
+    g.new_output(g.unary(ir.UN_RELU, t))
+    h = hb.HostGraph(g)
+    assert len(_instrs(h.plan_text())) == 1
+    # grow the C++ graph behind the handle: one more op on the dead branch, which becomes an output
+    from helium_b200._lib import HeNode, check, lib
+    import ctypes as C
+    c = HeNode()
+    c.kind, c.sub_op, c.dtype, c.rank = ir.OP_UNARY, ir.UN_NEG, ir.F32, 2
+    c.inp[0], c.inp[1], c.inp[2] = e, -1, -1
+    c.shape[0], c.shape[1] = 64, 64
+    out = C.c_int32()
+    check(lib.heh_graph_new_op(h._h, C.byref(c), C.byref(out)))
+    check(lib.heh_graph_new_output(h._h, out.value))
+    ins = _instrs(h.plan_text())
+    assert sorted(n for i in ins for n in i["nodes"]) == [1, 2, 3, out.value]
+    assert sorted(o for i in ins for o in i["outputs"]) == [3, out.value]
+    h.set_planner("search")
+    ins = _instrs(h.plan_text())
+    assert sorted(o for i in ins for o in i["outputs"]) == [3, out.value]
+
+
 def test_matmul_epilogue_and_mainloop_fuse_through_the_planner():
     g = ir.Graph()
     a = g.new_input([512, 256], ir.BF16); mk = g.new_input([512, 256], ir.BF16); b = g.new_input([256, 512], ir.BF16)
