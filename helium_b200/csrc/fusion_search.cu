@@ -20,10 +20,12 @@
 // if the group graph stays acyclic and he_plan_supported accepts every group: the search ranges over what the
 // kernels of this library run, not over an abstract op vocabulary.
 //
-// Search (cost_model.rs:241-343): start from singletons, merge greedily while a merge removes a kernel
-// (produce_maximal_fusions, fused_graph.rs:113-223), then repeat a depth-limited look-ahead from the best state
-// until it finds nothing cheaper.  The look-ahead follows only the cheapest few moves at each level and is cut off
-// after a fixed number of states, so planning time is bounded; the playground's is exhaustive to depth 7.
+// Search (cost_model.rs:241-343): three starting states -- the greedy one (merge while a merge removes a kernel:
+// produce_maximal_fusions, fused_graph.rs:113-223), one kernel per node, and the plan of the pairwise planner when
+// the caller hands it over -- are each improved by steepest descent, one move at a time; where that is stuck a
+// look-ahead of a few moves follows the cheapest moves of each level; the cheapest end state wins.  The number of
+// states costed per descent is capped, so planning time is bounded; the playground's descent is exhaustive to
+// depth 7.
 // Subdivisions restrict which nodes may move in one descent instead of cutting the graph into subgraphs that have to
 // be merged afterwards (fused_graph.rs:925-1079): the state is always the whole graph.
 #include "fusion_search.h"
