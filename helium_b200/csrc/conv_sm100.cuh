@@ -210,7 +210,7 @@ __global__ void __launch_bounds__(32 * 11, 1) conv_fprop_kernel(const __grid_con
     *abort_flag = 0;
     for (int s = 0; s < STAGES; ++s) {
       ptx::mbar_init(bar_full(s), 1);
-      ptx::mbar_init(bar_empty(s), 1);
+      ptx::mbar_init(bar_empty(s), 2);       // both issuing threads let go of a slot: see the MMA loop
     }
     for (int a = 0; a < 2; ++a) {
       ptx::mbar_init(bar_tmem_full(a), 2);   // one arrival per issuing thread
@@ -322,9 +322,15 @@ __global__ void __launch_bounds__(32 * 11, 1) conv_fprop_kernel(const __grid_con
           // of this parity has completed": a thread that skipped the other's phase L of a slot and came back for
           // phase L + 1 while L was still loading (loads of different groups complete in any order) was let through
           // by phase L - 1, issued MMAs on stale tiles and released the slot a second time -- about once in 10^4
-          // launches the ring then stopped.  Observing every phase in ring order rules that out.
+          // launches the ring then stopped.  Observing every phase in ring order rules that out, and because the
+          // slot goes back to the producer only when BOTH threads have let go of it (the one that multiplies it
+          // when its MMAs have retired, the other one here), neither can fall a lap behind a barrier it still has
+          // to observe.  tests/test_pipeline_model_cpu.py runs the three protocols under random interleavings.
           if (!ptx::mbar_wait(bar_full(my_stage), my_phase, abort_flag, status, 3, my_stage, wait_us)) { alive = false; break; }
-          if ((g_idx & 1) != me) continue;
+          if ((g_idx & 1) != me) {
+            ptx::mbar_arrive(bar_empty(my_stage));
+            continue;
+          }
           const int nsub = min(KSUB, k_blocks - kb0);
           ptx::tcgen05_fence_after();
 #pragma unroll
