@@ -137,3 +137,58 @@ def test_observing_without_releasing_can_still_fall_a_lap_behind():
     construction once both threads release the slot)."""
     failures = [run(5, 6, 3, OBSERVE, seed) for seed in range(300)]
     assert any(f is not None for f in failures)
+
+
+def run_shared_stages(n_issuers, stages, n_stages_total, seed, max_events=200000):
+    """The filter-gradient kernel's ring (conv_sm100.cuh, conv_wgrad_kernel): every stage holds one tap tile per
+    issuing thread, every thread waits for every stage, multiplies its taps and commits; `empty` takes one arrival
+    per thread.  Same modelling as above."""
+    rng = random.Random(seed)
+    full = [Barrier() for _ in range(stages)]
+    empty = [Barrier(n_issuers) for _ in range(stages)]
+    smem = [None] * stages
+    prod, loads, done = 0, [], 0
+    pos = [0] * n_issuers
+    commits = [[] for _ in range(n_issuers)]
+    for _ in range(max_events):
+        if done == n_stages_total * n_issuers:
+            return None
+        actions = []
+        if prod < n_stages_total and empty[prod % stages].passed(((prod // stages) & 1) ^ 1):
+            actions.append(("issue_load",))
+        actions += [("load_lands", k) for k in loads]
+        for i in range(n_issuers):
+            if pos[i] < n_stages_total and full[pos[i] % stages].passed((pos[i] // stages) & 1):
+                actions.append(("consume", i))
+            if commits[i]:
+                actions.append(("retire", i))
+        if not actions:
+            return f"deadlock: producer at {prod}, issuers at {pos}"
+        a = rng.choice(actions)
+        if a[0] == "issue_load":
+            loads.append(prod)
+            prod += 1
+        elif a[0] == "load_lands":
+            loads.remove(a[1])
+            smem[a[1] % stages] = a[1]
+            full[a[1] % stages].complete()
+        elif a[0] == "consume":
+            i = a[1]
+            if smem[pos[i] % stages] != pos[i]:
+                return f"issuer {i} multiplied stage {pos[i] % stages} holding {smem[pos[i] % stages]} instead of {pos[i]}"
+            commits[i].append(pos[i])
+            pos[i] += 1
+        else:
+            i = a[1]
+            k = commits[i].pop(0)
+            if smem[k % stages] != k:
+                return f"stage {k % stages} was overwritten while issuer {i} still read {k}"
+            empty[k % stages].complete()
+            done += 1
+    return "no progress within the event limit"
+
+
+@pytest.mark.parametrize("n_issuers,stages", [(3, 3), (3, 5), (3, 6), (1, 6)])
+def test_the_filter_gradient_ring_is_safe(n_issuers, stages):
+    for seed in range(200):
+        assert run_shared_stages(n_issuers, stages, 40, seed) is None, seed
